@@ -1,0 +1,120 @@
+"""Gemma-4 text decoder over the flattened ragged batch and the paged KV cache.
+
+Math: src/models/gemma/gemma4/{layers,decoder}.rs (restated step by step in ``mary_b200.oracle.gemma4``).
+Weights are torch ``[out, in]``; q/k/v and gate/up are stored fused (``[q;k;v]``, ``[gate;up]``) so each block
+issues four GEMMs.  Tensor parallelism shards q/k/v and gate/up by output rows (whole heads) and o/down by
+input columns; ``tp`` supplies the reduction after the row-parallel GEMMs."""
+from __future__ import annotations
+
+import math
+
+import torch
+from torch import nn
+
+from ... import ops
+from ...ops import reference as ref
+from .config import Gemma4TextConfig
+
+
+class _NoTP:
+    rank, size = 0, 1
+
+    def row_linear(self, x, w, lora=None):
+        return ops.linear(x, w)
+
+    def all_reduce(self, x):
+        return x
+
+
+class Gemma4Layer(nn.Module):
+    def __init__(self, cfg: Gemma4TextConfig, i: int, tp=None, dtype=torch.float32, device="cpu"):
+        super().__init__()
+        self.cfg, self.i, self.tp = cfg, i, tp or _NoTP()
+        H, D = cfg.hidden_size, cfg.layer_head_dim(i)
+        self.D = D
+        self.n_q = cfg.num_attention_heads // self.tp.size
+        self.n_kv = max(cfg.layer_kv_heads(i) // self.tp.size, 1)
+        F = cfg.intermediate_size // self.tp.size
+        self.F = F
+        kw = dict(dtype=dtype, device=device)
+        P = lambda *s: nn.Parameter(torch.empty(*s, **kw), requires_grad=False)  # noqa: E731
+        self.w_qkv = P((self.n_q + 2 * self.n_kv) * D, H)
+        self.w_o = P(H, self.n_q * D)
+        self.w_gu = P(2 * F, H)
+        self.w_down = P(H, F)
+        self.q_norm, self.k_norm = P(D), P(D)
+        self.ln_in, self.ln_post_attn, self.ln_pre_ffn, self.ln_post_ffn = P(H), P(H), P(H), P(H)
+        self.layer_scalar = 1.0
+        self.sliding = cfg.is_sliding(i)
+        theta = cfg.rope_theta_local if self.sliding else cfg.rope_theta_global
+        part = 1.0 if self.sliding else cfg.partial_rotary_factor_global
+        self.register_buffer("inv_freq", ref.rope_inv_freq(D, theta, part, device), persistent=False)
+        self.window = cfg.sliding_window if (self.sliding and cfg.apply_sliding_window) else 0
+        self.lora = None  # {"qkv": LoraPair, ...} set by train.lora
+
+    def forward(self, x, h, meta, cache, next_norm):
+        """``x`` = normed input, ``h`` = residual stream.  Returns ``(x_next, h)`` where ``x_next`` is already
+        normed by ``next_norm`` (the next layer's input norm or the final norm)."""
+        c, L = self.cfg, self.lora or {}
+        qkv = ops.linear(x, self.w_qkv)
+        if "qkv" in L:
+            qkv = qkv + L["qkv"](x)
+        q = ops.qk_norm_rope_append(qkv, self.n_q, self.n_kv, self.D, self.q_norm, self.k_norm, True, self.inv_freq,
+                                    meta, cache.k[self.i], cache.v[self.i], c.rms_norm_eps)
+        o = ops.paged_attention(q, cache.k[self.i], cache.v[self.i], meta, 1.0, self.window)
+        o = o.reshape(o.shape[0], -1)
+        a = self.tp.row_linear(o, self.w_o, L.get("o"))
+        x, h = ops.norm_add_norm(a, self.ln_post_attn, h, self.ln_pre_ffn, c.rms_norm_eps)
+        gu = ops.linear(x, self.w_gu)
+        if "gu" in L:
+            gu = gu + L["gu"](x)
+        m = ops.glu(gu, "geglu")
+        d = self.tp.row_linear(m, self.w_down, L.get("down"))
+        return ops.norm_add_norm(d, self.ln_post_ffn, h, next_norm, c.rms_norm_eps, self.layer_scalar)
+
+
+class Gemma4Model(nn.Module):
+    def __init__(self, cfg: Gemma4TextConfig, tp=None, dtype=torch.float32, device="cpu"):
+        super().__init__()
+        self.cfg, self.tp, self.dtype = cfg, tp or _NoTP(), dtype
+        kw = dict(dtype=dtype, device=device)
+        self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, **kw), requires_grad=False)
+        self.layers = nn.ModuleList([Gemma4Layer(cfg, i, self.tp, dtype, device) for i in range(cfg.num_hidden_layers)])
+        self.norm = nn.Parameter(torch.empty(cfg.hidden_size, **kw), requires_grad=False)
+        self.lm_head = None  # tied
+        self.embed_scale = float(torch.tensor(math.sqrt(cfg.hidden_size), dtype=torch.float32))
+
+    # -- cache geometry for the runtime
+    def kv_spec(self):
+        c = self.cfg
+        return dict(num_layers=c.num_hidden_layers,
+                    kv_heads=[max(c.layer_kv_heads(i) // self.tp.size, 1) for i in range(c.num_hidden_layers)],
+                    head_dim=[c.layer_head_dim(i) for i in range(c.num_hidden_layers)])
+
+    def hidden(self, ids, meta, cache):
+        """Final-normed hidden states ``[T, H]`` of every row."""
+        h = ops.embed(ids, self.embed, self.embed_scale)
+        x = ops.rmsnorm(h, self.layers[0].ln_in, self.cfg.rms_norm_eps)
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1].ln_in if i + 1 < n else self.norm
+            x, h = layer(x, h, meta, cache, nxt)
+        return x
+
+    def head_weight(self):
+        return self.embed if self.lm_head is None else self.lm_head
+
+    def logits(self, x):
+        return ref.softcap(ops.linear(x, self.head_weight()).float(), self.cfg.final_logit_softcapping)
+
+    def forward(self, ids, meta, cache, rows=None):
+        """Logits (f32, soft-capped) of ``rows`` (all rows when ``None``)."""
+        x = self.hidden(ids, meta, cache)
+        if rows is not None:
+            x = x[rows]
+        return self.logits(x)
+
+    def greedy(self, ids, meta, cache, rows):
+        x = self.hidden(ids, meta, cache)[rows]
+        tok, _ = ops.lm_head_argmax(x, self.head_weight(), self.cfg.final_logit_softcapping)
+        return tok

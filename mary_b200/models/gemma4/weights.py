@@ -1,0 +1,116 @@
+"""Weight naming, random initialisation into a pile, and loading a pile into a ``Gemma4Model``.
+
+Name-prefix resolution (``""``, ``model.``, ``model.language_model.`` ...) follows
+src/models/gemma/gemma4/weights.rs:100-145; ``layer_scalar`` is read per layer, 1.0 if absent (:653-656)."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from ...format import jsonfacts
+from ...format.ingest import ingest_tensors
+from ...format.model import build_model_root
+from ...pile.trible import TribleBuilder
+from .config import Gemma4TextConfig
+
+PREFIXES = ("", "model.", "model.language_model.", "language_model.model.", "language_model.")
+
+
+def tensor_names(cfg: Gemma4TextConfig) -> dict[str, tuple]:
+    """Every tensor of the text decoder with its shape (torch ``[out, in]``)."""
+    H, F, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    out = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,)}
+    for i in range(cfg.num_hidden_layers):
+        D, Hq, Hkv = cfg.layer_head_dim(i), cfg.num_attention_heads, cfg.layer_kv_heads(i)
+        p = f"model.layers.{i}."
+        out.update({
+            p + "input_layernorm.weight": (H,), p + "post_attention_layernorm.weight": (H,),
+            p + "pre_feedforward_layernorm.weight": (H,), p + "post_feedforward_layernorm.weight": (H,),
+            p + "self_attn.q_proj.weight": (Hq * D, H), p + "self_attn.k_proj.weight": (Hkv * D, H),
+            p + "self_attn.v_proj.weight": (Hkv * D, H), p + "self_attn.o_proj.weight": (H, Hq * D),
+            p + "self_attn.q_norm.weight": (D,), p + "self_attn.k_norm.weight": (D,),
+            p + "mlp.gate_proj.weight": (F, H), p + "mlp.up_proj.weight": (F, H), p + "mlp.down_proj.weight": (H, F)})
+    if not cfg.tie_word_embeddings:
+        out["lm_head.weight"] = (V, H)
+    return out
+
+
+def random_weights(cfg: Gemma4TextConfig, seed: int = 0, std: float = 0.02):
+    """``normal(0, std)`` for matrices, ones for norm gains — generated tensor by tensor in name order."""
+    rng = np.random.default_rng(seed)
+    for name, shape in sorted(tensor_names(cfg).items()):
+        if name.endswith("norm.weight") or "layernorm" in name:
+            yield name, np.ones(shape, dtype=np.float32)
+        else:
+            yield name, (rng.standard_normal(shape, dtype=np.float32) * np.float32(std))
+
+
+def write_random_pile(pile, key, cfg: Gemma4TextConfig, name: str = "gemma4-tiny", seed: int = 0, dtype: str = "f32") -> bytes:
+    """Random-init model + its ``config.json`` as facts, published to the model-graph collection."""
+    from ...format.persist import publish_fragment
+    tb = TribleBuilder()
+    members = ingest_tensors(pile, tb, random_weights(cfg, seed), dtype)
+    root = build_model_root(pile, tb, members, name=name, source=f"random-init seed={seed}",
+                            quantization=None if dtype == "f32" else dtype)
+    jsonfacts.save_document(pile, tb, "config.json", cfg.to_json(), owner=root)
+    publish_fragment(pile, key, tb.build(), f"random {name}"[:32])
+    return root
+
+
+def resolve_prefix(loader, probe: str = "embed_tokens.weight") -> str:
+    for p in PREFIXES:
+        if loader.has_weight(p + probe):
+            return p
+    raise LookupError(f"no tensor named *{probe} under any known prefix {PREFIXES}")
+
+
+def load_into(model, loader, device=None) -> None:
+    """Fill a ``Gemma4Model`` from a ``WeightLoader``; TP ranks take their shard of every projection."""
+    cfg, tp = model.cfg, model.tp
+    pre = resolve_prefix(loader)
+    dt = model.dtype
+
+    def get(n):
+        return loader.load_tensor(pre + n, dt)
+
+    def put(param, t):
+        param.data.copy_(t.to(param.device, dt))
+
+    put(model.embed, get("embed_tokens.weight"))
+    put(model.norm, get("norm.weight"))
+    for i, L in enumerate(model.layers):
+        p = f"layers.{i}."
+        D = cfg.layer_head_dim(i)
+        r, n = tp.rank, tp.size
+        q = get(p + "self_attn.q_proj.weight").view(cfg.num_attention_heads, D, -1)
+        k = get(p + "self_attn.k_proj.weight").view(cfg.layer_kv_heads(i), D, -1)
+        v = get(p + "self_attn.v_proj.weight").view(cfg.layer_kv_heads(i), D, -1)
+        qs = q[r * L.n_q:(r + 1) * L.n_q]
+        kv0 = (r * cfg.layer_kv_heads(i)) // n if cfg.layer_kv_heads(i) >= n else 0
+        ks, vs = k[kv0:kv0 + L.n_kv], v[kv0:kv0 + L.n_kv]
+        put(L.w_qkv, torch.cat([qs.reshape(-1, q.shape[-1]), ks.reshape(-1, k.shape[-1]), vs.reshape(-1, v.shape[-1])], 0))
+        o = get(p + "self_attn.o_proj.weight")
+        put(L.w_o, o[:, r * L.n_q * D:(r + 1) * L.n_q * D])
+        g, u = get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")
+        put(L.w_gu, torch.cat([g[r * L.F:(r + 1) * L.F], u[r * L.F:(r + 1) * L.F]], 0))
+        put(L.w_down, get(p + "mlp.down_proj.weight")[:, r * L.F:(r + 1) * L.F])
+        put(L.q_norm, get(p + "self_attn.q_norm.weight"))
+        put(L.k_norm, get(p + "self_attn.k_norm.weight"))
+        put(L.ln_in, get(p + "input_layernorm.weight"))
+        put(L.ln_post_attn, get(p + "post_attention_layernorm.weight"))
+        put(L.ln_pre_ffn, get(p + "pre_feedforward_layernorm.weight"))
+        put(L.ln_post_ffn, get(p + "post_feedforward_layernorm.weight"))
+        if loader.has_weight(pre + p + "layer_scalar"):
+            L.layer_scalar = float(loader.load_host_f32(pre + p + "layer_scalar").reshape(-1)[0])
+    if not cfg.tie_word_embeddings and loader.has_weight("lm_head.weight"):
+        model.lm_head = torch.nn.Parameter(loader.load_tensor("lm_head.weight", dt).to(model.embed.device), requires_grad=False)
+
+
+def init_random_(model, seed: int = 0, std: float = 0.02) -> None:
+    """Random-init directly on the model's device (benchmarks of the large configs: no host round trip)."""
+    g = torch.Generator(device=model.embed.device).manual_seed(seed)
+    for n, p in model.named_parameters():
+        if p.dim() == 1:
+            p.data.fill_(1.0)
+        else:
+            p.data.normal_(0.0, std, generator=g)

@@ -1,0 +1,105 @@
+"""Op entry points.  A CUDA tensor runs the hand-written sm_100a kernel (``ops.cuda``; a missing kernel
+library is an error, never a silent fallback); a CPU tensor runs the PyTorch reference (``ops.reference``),
+which is also the oracle the kernels are tested against."""
+from __future__ import annotations
+
+import torch
+
+from . import reference as ref
+
+
+def _cuda(x) -> bool:
+    return isinstance(x, torch.Tensor) and x.is_cuda
+
+
+def _k():
+    from . import cuda
+    return cuda
+
+
+def rmsnorm(x, weight=None, eps=1e-6):
+    return _k().rmsnorm(x, weight, eps) if _cuda(x) else ref.rmsnorm(x, weight, eps)
+
+
+def add_rmsnorm(x, residual, weight, eps=1e-6):
+    return _k().add_rmsnorm(x, residual, weight, eps) if _cuda(x) else ref.add_rmsnorm(x, residual, weight, eps)
+
+
+def norm_add_norm(a, w_post, h, w_next, eps=1e-6, scalar: float = 1.0):
+    """Gemma sandwich step: ``h' = (h + rms(a, w_post)) * scalar``; ``x = rms(h', w_next)``.  Returns ``(x, h')``;
+    ``w_next=None`` skips the second norm and returns ``(None, h')``."""
+    if _cuda(a):
+        return _k().norm_add_norm(a, w_post, h, w_next, eps, scalar)
+    hn = (h.float() + ref.rmsnorm(a, w_post, eps).float()) * scalar
+    hn = hn.to(h.dtype)
+    return (ref.rmsnorm(hn, w_next, eps) if w_next is not None else None), hn
+
+
+def linear(x, w, bias=None):
+    return _k().linear(x, w, bias) if _cuda(x) else ref.linear(x, w, bias)
+
+
+def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm: bool, inv_freq, meta, kcache, vcache, eps):
+    """Split ``qkv[T, (n_q+2 n_kv) D]``; per-head RMSNorm on q and k (learned gains) and optionally a weightless
+    norm on v; split-half RoPE on q and k at ``meta.positions``; append k, v to the paged cache.
+    Returns ``q[T, n_q, D]``."""
+    if _cuda(qkv):
+        return _k().qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm, inv_freq, meta, kcache, vcache, eps)
+    T = qkv.shape[0]
+    q, k, v = qkv.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], dim=-1)
+    q, k, v = q.reshape(T, n_q, head_dim), k.reshape(T, n_kv, head_dim), v.reshape(T, n_kv, head_dim)
+    if q_norm is not None:
+        q = ref.rmsnorm(q, q_norm, eps)
+    if k_norm is not None:
+        k = ref.rmsnorm(k, k_norm, eps)
+    if v_norm:
+        v = ref.rmsnorm(v, None, eps)
+    if inv_freq is not None:
+        q, k = ref.rope(q, meta.positions, inv_freq), ref.rope(k, meta.positions, inv_freq)
+    ref.kv_append(k, v, kcache, vcache, meta.slot_mapping)
+    return q
+
+
+def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0):
+    if _cuda(q):
+        return _k().paged_attention(q, kcache, vcache, meta, scale, window, softcap)
+    return ref.paged_attention(q, kcache, vcache, meta, scale, window, softcap)
+
+
+def glu(gate_up, act: str = "geglu"):
+    """``act(gate) * up`` over ``gate_up[T, 2F] = [gate | up]``."""
+    if _cuda(gate_up):
+        return _k().glu(gate_up, act)
+    F = gate_up.shape[-1] // 2
+    return {"geglu": ref.geglu, "swiglu": ref.swiglu, "situ": ref.situ}[act](gate_up[..., :F], gate_up[..., F:])
+
+
+def embed(ids, table, scale=1.0):
+    return _k().embed(ids, table, scale) if _cuda(table) else ref.embed(ids, table, scale)
+
+
+def lm_head_argmax(h, table, softcap=0.0, vocab_limit: int | None = None):
+    """``argmax(softcap(h @ table^T))`` per row (first maximum wins) and the max logit.  Returns ``(ids, logit)``."""
+    if _cuda(h):
+        return _k().lm_head_argmax(h, table, softcap, vocab_limit)
+    logits = ref.softcap(ref.linear(h, table).float(), softcap)
+    if vocab_limit:
+        logits = logits[:, :vocab_limit]
+    ids = ref.argmax_first(logits)
+    return ids, logits.gather(-1, ids[:, None])[:, 0]
+
+
+def router_topk(logits, k, mode="softmax", bias=None, n_group=1, topk_group=1, scale=1.0, renorm=True):
+    if _cuda(logits):
+        return _k().router_topk(logits, k, mode, bias, n_group, topk_group, scale, renorm)
+    if mode == "softmax":
+        return ref.router_softmax_topk(logits, k, renorm)
+    return ref.router_sigmoid_topk(logits, bias, k, n_group, topk_group, scale, renorm)
+
+
+def quantize_nvfp4(x):
+    return _k().quantize_nvfp4(x) if _cuda(x) else ref.quantize_nvfp4(x)
+
+
+def short_conv(x, w, history=None):
+    return _k().short_conv(x, w, history) if _cuda(x) else ref.short_conv(x, w, history)

@@ -1,0 +1,53 @@
+"""``BatchMeta``: the flattened ragged batch that every model forward consumes.
+
+Rows of all sequences are concatenated: a prefill chunk contributes ``q_len`` rows, a decode step one row
+(or ``1+k`` rows with ``k`` speculative drafts).  ``kv_len[i]`` counts the tokens of sequence ``i`` in the
+cache AFTER this step's rows were appended, so row ``j`` of sequence ``i`` sits at absolute position
+``kv_len[i] - q_len[i] + j`` and may attend to positions ``<=`` its own."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+
+@dataclass
+class BatchMeta:
+    positions: torch.Tensor      # int32 [T] absolute position of every row
+    seq_index: torch.Tensor      # int32 [T] which sequence a row belongs to
+    q_start: torch.Tensor        # int32 [S+1] row offsets (cumulative)
+    kv_len: torch.Tensor         # int32 [S]
+    page_table: torch.Tensor     # int32 [S, max_pages]
+    slot_mapping: torch.Tensor   # int64 [T] flat cache slot (page * page_size + offset) of every row
+    page_size: int
+    max_q_len: int
+    max_kv_len: int
+    num_seqs: int
+    num_tokens: int
+    all_decode: bool
+    # host copies (no device sync needed to read them)
+    q_lens_host: np.ndarray | None = None
+    kv_lens_host: np.ndarray | None = None
+
+    @staticmethod
+    def build(q_lens, kv_lens, page_table: np.ndarray, page_size: int, device="cpu") -> "BatchMeta":
+        q_lens = np.asarray(q_lens, dtype=np.int32)
+        kv_lens = np.asarray(kv_lens, dtype=np.int32)
+        S, T = len(q_lens), int(q_lens.sum())
+        q_start = np.zeros(S + 1, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        seq_index = np.repeat(np.arange(S, dtype=np.int32), q_lens)
+        pos = (np.arange(T, dtype=np.int32) - q_start[seq_index]) + (kv_lens - q_lens)[seq_index]
+        pages = page_table[seq_index, pos // page_size].astype(np.int64)
+        slots = pages * page_size + (pos % page_size)
+        dev = torch.device(device)
+
+        def t(a, dt):
+            x = torch.from_numpy(np.ascontiguousarray(a)).to(dt)
+            return x.to(dev, non_blocking=True) if dev.type != "cpu" else x
+        return BatchMeta(positions=t(pos, torch.int32), seq_index=t(seq_index, torch.int32), q_start=t(q_start, torch.int32),
+                         kv_len=t(kv_lens, torch.int32), page_table=t(page_table, torch.int32),
+                         slot_mapping=t(slots, torch.int64), page_size=page_size, max_q_len=int(q_lens.max()) if S else 0,
+                         max_kv_len=int(kv_lens.max()) if S else 0, num_seqs=S, num_tokens=T,
+                         all_decode=bool(S and q_lens.max() == 1), q_lens_host=q_lens, kv_lens_host=kv_lens)

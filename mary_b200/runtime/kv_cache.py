@@ -1,0 +1,130 @@
+"""Paged KV cache: native page allocator (``_core.so``) + the device tensors that hold the pages.
+
+Pages are 16 tokens by default.  One cache instance serves all layers: ``k[layer]`` / ``v[layer]`` have shape
+``[num_pages, page_size, kv_heads, head_dim]``; MLA models use a single latent tensor per layer
+(``[num_pages, page_size, kv_lora + rope_dim]``).  A sequence's page list is shared by every layer."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from .. import _native
+
+
+def _declare(lib):
+    if getattr(lib, "_kv_declared", False):
+        return
+    c = ctypes
+    lib.kv_create.restype = c.c_void_p
+    lib.kv_create.argtypes = [c.c_int32, c.c_int32]
+    lib.kv_destroy.argtypes = [c.c_void_p]
+    lib.kv_free_pages.argtypes = [c.c_void_p]
+    lib.kv_peak_used.restype = c.c_int64
+    lib.kv_peak_used.argtypes = [c.c_void_p]
+    lib.kv_seq_len.restype = c.c_int64
+    lib.kv_seq_len.argtypes = [c.c_void_p, c.c_int64]
+    lib.kv_extend.restype = c.c_int64
+    lib.kv_extend.argtypes = [c.c_void_p, c.c_int64, c.c_int64]
+    lib.kv_truncate.restype = c.c_int64
+    lib.kv_truncate.argtypes = [c.c_void_p, c.c_int64, c.c_int64]
+    lib.kv_release.argtypes = [c.c_void_p, c.c_int64]
+    lib.kv_pages.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int32]
+    lib.kv_page_table.argtypes = [c.c_void_p, c.c_void_p, c.c_int32, c.c_void_p, c.c_int32, c.c_void_p]
+    lib.sched_create.restype = c.c_void_p
+    lib.sched_create.argtypes = [c.c_void_p, c.c_int32, c.c_int32, c.c_int32]
+    lib.sched_destroy.argtypes = [c.c_void_p]
+    lib.sched_add.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int32, c.c_int32]
+    lib.sched_num_waiting.argtypes = [c.c_void_p]
+    lib.sched_num_running.argtypes = [c.c_void_p]
+    lib.sched_set_drafts.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int32]
+    lib.sched_next.argtypes = [c.c_void_p] + [c.c_void_p] * 9
+    lib.sched_commit.argtypes = [c.c_void_p, c.c_int64, c.c_int32, c.c_int32, c.c_int32, c.c_int32]
+    lib.sched_is_finished.argtypes = [c.c_void_p, c.c_int64]
+    lib.sched_remove.argtypes = [c.c_void_p, c.c_int64]
+    lib._kv_declared = True
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+class PageAllocator:
+    def __init__(self, num_pages: int, page_size: int = 16):
+        self.lib = _native.core()
+        _declare(self.lib)
+        self.num_pages, self.page_size = num_pages, page_size
+        self.h = self.lib.kv_create(num_pages, page_size)
+
+    def extend(self, seq: int, tokens: int) -> int:
+        n = self.lib.kv_extend(self.h, seq, tokens)
+        if n < 0:
+            raise OutOfPages(f"sequence {seq}: no free pages for {tokens} more tokens "
+                             f"({self.free_pages} of {self.num_pages} pages free)")
+        return n
+
+    def truncate(self, seq: int, new_len: int) -> None:
+        if self.lib.kv_truncate(self.h, seq, new_len) < 0:
+            raise ValueError(f"cannot truncate sequence {seq} to {new_len}")
+
+    def release(self, seq: int) -> None:
+        self.lib.kv_release(self.h, seq)
+
+    def seq_len(self, seq: int) -> int:
+        return self.lib.kv_seq_len(self.h, seq)
+
+    @property
+    def free_pages(self) -> int:
+        return self.lib.kv_free_pages(self.h)
+
+    @property
+    def peak_used(self) -> int:
+        return self.lib.kv_peak_used(self.h)
+
+    def pages(self, seq: int) -> list[int]:
+        buf = np.empty(self.num_pages, dtype=np.int32)
+        n = self.lib.kv_pages(self.h, seq, buf.ctypes.data, buf.size)
+        if n < 0:
+            raise KeyError(seq)
+        return buf[:n].tolist()
+
+    def page_table(self, seqs, max_pages: int | None = None):
+        """``(table int32[n, max_pages] padded with -1, kv_lens int32[n])`` as NumPy arrays."""
+        s = np.asarray(seqs, dtype=np.int64)
+        if max_pages is None:
+            max_pages = max(1, max((self.seq_len(int(x)) + self.page_size - 1) // self.page_size for x in s))
+        table = np.empty((len(s), max_pages), dtype=np.int32)
+        lens = np.empty(len(s), dtype=np.int32)
+        rc = self.lib.kv_page_table(self.h, s.ctypes.data, len(s), table.ctypes.data, max_pages, lens.ctypes.data)
+        if rc != 0:
+            raise ValueError("page table: unknown sequence or max_pages too small")
+        return table, lens
+
+    def __del__(self):
+        try:
+            self.lib.kv_destroy(self.h)
+        except Exception:
+            pass
+
+
+class PagedKVCache:
+    """Device storage for the pages of every layer."""
+
+    def __init__(self, num_layers: int, num_pages: int, page_size: int, kv_heads: int | list[int], head_dim: int | list[int],
+                 dtype=torch.bfloat16, device="cpu", latent_dim: int | None = None, alias_v_to_k: bool = False):
+        self.alloc = PageAllocator(num_pages, page_size)
+        self.page_size, self.num_pages, self.num_layers = page_size, num_pages, num_layers
+        self.latent = latent_dim is not None
+        heads = kv_heads if isinstance(kv_heads, list) else [kv_heads] * num_layers
+        dims = head_dim if isinstance(head_dim, list) else [head_dim] * num_layers
+        if self.latent:
+            self.k = [torch.zeros(num_pages, page_size, latent_dim, dtype=dtype, device=device) for _ in range(num_layers)]
+            self.v = self.k
+        else:
+            self.k = [torch.zeros(num_pages, page_size, heads[i], dims[i], dtype=dtype, device=device) for i in range(num_layers)]
+            self.v = self.k if alias_v_to_k else [torch.zeros_like(t) for t in self.k]
+
+    def bytes(self) -> int:
+        n = sum(t.numel() * t.element_size() for t in self.k)
+        return n if (self.latent or self.v is self.k) else 2 * n

@@ -1,0 +1,264 @@
+import io
+import json
+import pickle
+import struct
+import zipfile
+
+import numpy as np
+import pytest
+
+from mary_b200.format import jsonfacts, schema as S
+from mary_b200.format.formats import detect_format, iter_gguf, iter_pickle
+from mary_b200.format.ingest import f32_to_bf16_bits, ingest_model, ingest_tensors
+from mary_b200.format.leaf import (Elem, LeafError, put_array, put_leaf, put_leaf_legacy, resolve, tensor_blob)
+from mary_b200.format.model import build_model_root, index_keymap, put_fp4_tensor, put_tensor
+from mary_b200.format.persist import (derive_half_root, import_model_to_collection, load_config, read_model_pile)
+from mary_b200.format.safetensors import SafeTensors, save_file
+from mary_b200.format.selection import ModelSelector, SelectedModelIndex, SelectionError, select_model_root
+from mary_b200.format.tiktoken import TikToken
+from mary_b200.format.tokenizer import (build_tokenizer, load_tiktoken, load_tokenizer_json, save_tiktoken,
+                                        save_tokenizer_json)
+from mary_b200.nn.fp4 import quantize_weight_nvfp4
+from mary_b200.pile import MemoryBlobStore, Pile, TribleBuilder
+from mary_b200.pile.trible import v_handle
+
+
+@pytest.mark.parametrize("form", ["typed", "legacy"])
+def test_leaf_both_forms_roundtrip(form):
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    a = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    e = put_array(st, tb, a) if form == "typed" else put_leaf_legacy(st, tb, a)
+    leaf = resolve(st, tb.build(), e)
+    assert leaf.dims == (2, 3, 4) and np.array_equal(leaf.to_f32(), a)
+    assert leaf.view_f32().base is not None          # zero-copy view
+
+
+def test_leaf_scalar_rank0_and_rank_limits():
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    e = put_array(st, tb, np.float32(3.5).reshape(()))
+    assert resolve(st, tb.build(), e).to_f32().reshape(()) == 3.5
+    put_array(st, tb, np.zeros((1,) * 6, dtype=np.float32))
+    with pytest.raises(LeafError, match="rank 7"):
+        put_array(st, tb, np.zeros((1,) * 7, dtype=np.float32))
+
+
+def test_leaf_identical_tensors_dedupe_and_two_payloads_refused():
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    a = np.ones((4, 4), dtype=np.float32)
+    e1, e2 = put_array(st, tb, a), put_array(st, tb, a.copy())
+    assert e1 == e2 and st.bytes_dedup > 0
+    h = st.put(a.tobytes())
+    tb.add(e1, S.DATA, v_handle(h))                  # a second payload on the same entity
+    with pytest.raises(LeafError, match="payloads"):
+        resolve(st, tb.build(), e1)
+
+
+def test_leaf_header_payload_mismatch_refused():
+    with pytest.raises(LeafError):
+        tensor_blob(Elem.F32, (2, 2), b"\x00" * 15)
+
+
+def test_f16_bf16_and_nvfp4_leaves():
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    a = np.random.default_rng(0).standard_normal((8, 64)).astype(np.float32)
+    e16 = put_array(st, tb, a.astype(np.float16))
+    eb = put_array(st, tb, f32_to_bf16_bits(a), Elem.BF16)
+    codes, scales, s2 = quantize_weight_nvfp4(a)
+    m = put_fp4_tensor(st, tb, "experts.0.w13", codes, scales, s2, layer=3, expert=0)
+    facts = tb.build()
+    assert np.allclose(resolve(st, facts, e16).to_f32(), a, atol=2e-3)
+    assert np.allclose(resolve(st, facts, eb).to_f32(), a, atol=2e-2)
+    from mary_b200.format.model import load_module_leaf
+    leaf = load_module_leaf(st, facts, m)
+    assert leaf.elem == Elem.NVFP4 and leaf.dims == (8, 64)
+    c2, sc2, g2 = leaf.fp4_parts()
+    assert np.array_equal(c2, codes) and np.array_equal(sc2, scales) and g2 == pytest.approx(s2)
+    assert np.abs(leaf.to_f32() - a).max() < 0.6
+
+
+def test_root_id_depends_on_members_only_and_names_unique():
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    m1 = put_tensor(st, tb, "a.weight", np.ones((2, 2), np.float32))
+    m2 = put_tensor(st, tb, "b.weight", np.zeros((2,), np.float32))
+    r1 = build_model_root(st, tb, [m1, m2], name="x", source="s1")
+    r2 = build_model_root(st, TribleBuilder(), [m2, m1], name="other", source="s2")
+    assert r1 == r2
+    facts = tb.build()
+    assert set(index_keymap(st, facts, r1)) == {"a.weight", "b.weight"}
+    dup = put_tensor(st, tb, "a.weight", np.full((2, 2), 2, np.float32))
+    r3 = build_model_root(st, tb, [m1, dup])
+    with pytest.raises(LookupError, match="twice"):
+        index_keymap(st, tb.build(), r3)
+
+
+def test_selection_is_exact_cardinality_and_shards_merge():
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    a = put_tensor(st, tb, "l0.w", np.ones((2, 2), np.float32))
+    b = put_tensor(st, tb, "l1.w", np.zeros((2, 2), np.float32))
+    ra = build_model_root(st, tb, [a], name="m", source="src")
+    rb = build_model_root(st, tb, [b], name="m", source="src")
+    facts = tb.build()
+    with pytest.raises(SelectionError):
+        select_model_root(st, facts, ModelSelector.only())
+    with pytest.raises(SelectionError):
+        select_model_root(st, facts, ModelSelector.by_name("absent"))
+    assert select_model_root(st, facts, ModelSelector.by_root(ra)) == ra
+    idx = SelectedModelIndex.from_snapshot(st, facts, ModelSelector.by_name("m"), shards=True)
+    assert idx.names() == ["l0.w", "l1.w"] and idx.leaf("l1.w").dims == (2, 2)
+    c = put_tensor(st, tb, "l0.w", np.full((2, 2), 7, np.float32))
+    build_model_root(st, tb, [c], name="m", source="src")
+    with pytest.raises(SelectionError, match="overlap"):
+        SelectedModelIndex.from_snapshot(st, tb.build(), ModelSelector.by_name("m"), shards=True)
+
+
+def test_experts_in_layers_is_a_query():
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    rng = np.random.default_rng(0)
+    mem = []
+    for layer in range(3):
+        for ex in range(2):
+            c, s, g = quantize_weight_nvfp4(rng.standard_normal((4, 32)).astype(np.float32))
+            mem.append(put_fp4_tensor(st, tb, f"layers.{layer}.experts.{ex}.w13", c, s, g, layer, ex))
+    r = build_model_root(st, tb, mem)
+    idx = SelectedModelIndex(st, tb.build(), [r])
+    q = idx.experts_in_layers(1, 3)
+    assert sorted(q) == [(1, 0), (1, 1), (2, 0), (2, 1)] and q[(2, 1)] == ["layers.2.experts.1.w13"]
+
+
+def test_jsonfacts_roundtrip_exact():
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    doc = {"hidden_size": 256, "eps": 1e-6, "one": 1.0, "flag": True, "none": None, "name": "gemma",
+           "layers": ["a", "b", {"x": [1, 2.5, False]}], "nested": {"k": {"deep": -7}}, "big": 2 ** 70}
+    jsonfacts.save_document(st, tb, "config.json", doc)
+    back = jsonfacts.load_document(st, tb.build(), "config.json")
+    assert back == doc and list(back) == list(doc)
+    assert isinstance(back["one"], float) and isinstance(back["hidden_size"], int)
+    with pytest.raises(LookupError):
+        jsonfacts.load_document(st, tb.build(), "missing.json")
+
+
+def _tiny_tokenizer_json():
+    from tokenizers import Tokenizer, models, pre_tokenizers, decoders
+    vocab = {"<unk>": 0, "h": 1, "e": 2, "l": 3, "o": 4, "he": 5, "ll": 6, "hell": 7, "hello": 8, "Ġ": 9, "w": 10}
+    merges = [("h", "e"), ("l", "l"), ("he", "ll"), ("hell", "o")]
+    tok = Tokenizer(models.BPE(vocab=vocab, merges=merges, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tok.decoder = decoders.ByteLevel()
+    tok.add_special_tokens(["<bos>", "<turn|>"])
+    return tok
+
+
+def test_tokenizer_graph_roundtrip_and_build_without_json():
+    tok = _tiny_tokenizer_json()
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    tid = save_tokenizer_json(st, tb, "tiny", tok.to_str())
+    facts = tb.build()
+    assert load_tokenizer_json(st, facts, tid) == json.loads(tok.to_str())
+    rebuilt = build_tokenizer(st, facts)
+    for s in ("hello", "hello hello", "<bos>hello<turn|>"):
+        assert rebuilt.encode(s).ids == tok.encode(s).ids
+    # mutant: dropping one merge fact changes the encoding (the comparison can fail)
+    from mary_b200.format.tokenizer import MERGE_RANK
+    from mary_b200.pile.trible import r_u256
+    victim = [e for e, v in facts.with_attr(MERGE_RANK) if r_u256(v) == 3][0]
+    keep = [i for i, (e, _a, _v) in enumerate(facts) if e != victim]
+    from mary_b200.pile import TribleSet
+    mutant = TribleSet(facts.data[keep])
+    assert build_tokenizer(st, mutant).encode("hello").ids != tok.encode("hello").ids
+
+
+def test_tiktoken_bpe_and_pile_roundtrip():
+    ranks = {bytes([b]): b for b in range(256)}
+    for i, t in enumerate([b"he", b"ll", b"hell", b"hello", b" w", b"or", b" wor"]):
+        ranks[t] = 256 + i
+    tk = TikToken(ranks, special={"<|im_end|>": 1000})
+    ids = tk.encode("hello world<|im_end|>")
+    assert ids[0] == ranks[b"hello"] and ids[-1] == 1000 and tk.decode(ids) == "hello world<|im_end|>"
+    assert tk.decode(tk.encode("数字 123456 tests")) == "数字 123456 tests"
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    tid = save_tiktoken(st, tb, "k3", ranks, tk._re.pattern, {"<|im_end|>": 1000})
+    tk2 = load_tiktoken(st, tb.build(), tid)
+    assert tk2.encode("hello world<|im_end|>") == ids
+
+
+def test_safetensors_and_import_idempotent(tmp_path):
+    rng = np.random.default_rng(0)
+    tensors = {"model.a.weight": rng.standard_normal((4, 8)).astype(np.float32),
+               "model.b.weight": rng.standard_normal((8,)).astype(np.float16),
+               "model.ids": np.arange(4, dtype=np.int64)}
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    save_file(tensors, str(d / "model.safetensors"))
+    (d / "config.json").write_text(json.dumps({"hidden_size": 8, "eps": 1e-5}))
+    st = SafeTensors(str(d / "model.safetensors"))
+    assert np.array_equal(st.array("model.a.weight"), tensors["model.a.weight"]) and st.f32("model.ids") is None
+    from mary_b200.pile import signing_key_file
+    key = signing_key_file(str(tmp_path / "k"))
+    pile = Pile.open(str(tmp_path / "m.pile"))
+    r1 = import_model_to_collection(pile, key, d, name="toy")
+    size1 = len(read_model_pile(pile))
+    r2 = import_model_to_collection(pile, key, d, name="toy")          # idempotent re-import
+    facts = read_model_pile(pile)
+    assert r1 == r2 and len(facts) == size1
+    idx = SelectedModelIndex.from_snapshot(pile, facts)
+    assert idx.names() == ["model.a.weight", "model.b.weight"]          # the int tensor was skipped
+    assert load_config(pile, facts, r1) == {"hidden_size": 8, "eps": 1e-5}
+    h = derive_half_root(pile, key, facts, r1, "bf16")
+    facts = read_model_pile(pile)
+    idx16 = SelectedModelIndex.from_snapshot(pile, facts, ModelSelector.by_root(h))
+    assert idx16.leaf("model.a.weight").elem == Elem.BF16
+    assert np.allclose(idx16.leaf("model.a.weight").to_f32(), tensors["model.a.weight"], atol=2e-2)
+    pile.close()
+
+
+def _write_gguf(path, tensors):
+    def s(x):
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+    kv = s("general.alignment") + struct.pack("<I", 4) + struct.pack("<I", 32)
+    infos, data = b"", b""
+    for name, (t, shape, raw) in tensors.items():
+        pad = (-len(data)) % 32
+        data += b"\x00" * pad
+        infos += s(name) + struct.pack("<I", len(shape)) + b"".join(struct.pack("<Q", d) for d in reversed(shape))
+        infos += struct.pack("<I", t) + struct.pack("<Q", len(data))
+        data += raw
+    head = b"GGUF" + struct.pack("<I", 3) + struct.pack("<Q", len(tensors)) + struct.pack("<Q", 1) + kv + infos
+    head += b"\x00" * ((-len(head)) % 32)
+    path.write_bytes(head + data)
+
+
+def test_gguf_f32_f16_q8_q4(tmp_path):
+    rng = np.random.default_rng(1)
+    a = rng.standard_normal((2, 32)).astype(np.float32)
+    d = (np.abs(a).max(1) / 127).astype(np.float16)
+    q8 = np.rint(a / d.astype(np.float32)[:, None]).astype(np.int8)
+    raw8 = b"".join(d[i].tobytes() + q8[i].tobytes() for i in range(2))
+    d4 = (np.abs(a).max(1) / 7).astype(np.float16)
+    q4 = np.clip(np.rint(a / d4.astype(np.float32)[:, None]) + 8, 0, 15).astype(np.uint8)
+    raw4 = b"".join(d4[i].tobytes() + (q4[i, :16] | (q4[i, 16:] << 4)).tobytes() for i in range(2))
+    p = tmp_path / "m.gguf"
+    _write_gguf(p, {"f32": (0, (2, 32), a.tobytes()), "f16": (1, (2, 32), a.astype(np.float16).tobytes()),
+                    "q8": (8, (2, 32), raw8), "q4": (2, (2, 32), raw4)})
+    out = dict(iter_gguf(p))
+    assert np.array_equal(out["f32"], a) and np.allclose(out["f16"], a, atol=2e-3)
+    assert np.allclose(out["q8"], q8 * d.astype(np.float32)[:, None])
+    assert np.allclose(out["q4"], (q4.astype(np.float32) - 8) * d4.astype(np.float32)[:, None])
+    assert detect_format(p)[0] == "gguf"
+
+
+def test_torch_pickle_reader_and_refusal(tmp_path):
+    import torch
+    sd = {"w": torch.arange(12, dtype=torch.float32).reshape(3, 4), "h": torch.ones(5, dtype=torch.float16),
+          "t": torch.arange(6, dtype=torch.float32).reshape(2, 3).t(), "ids": torch.arange(3)}
+    p = tmp_path / "m.pth"
+    torch.save(sd, str(p))
+    out = dict(iter_pickle(p))
+    assert set(out) == {"w", "h", "t"}
+    assert np.array_equal(out["w"], sd["w"].numpy()) and np.array_equal(out["t"], sd["t"].numpy())
+    # a pickle that names an arbitrary callable is refused
+    evil = tmp_path / "evil.pth"
+    with zipfile.ZipFile(evil, "w") as z:
+        z.writestr("archive/data.pkl", pickle.dumps(print))
+    with pytest.raises(pickle.UnpicklingError):
+        list(iter_pickle(evil))
