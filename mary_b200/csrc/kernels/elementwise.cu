@@ -1,0 +1,277 @@
+// Bandwidth-bound row kernels: RMSNorm family, GLU, embedding gather, q/k norm + RoPE + paged-cache append,
+// short convolution.  Reference kernels: src/models/inkling/resid.rs:180-389 (add_resid, rms_norm),
+// src/models/inkling/fp4gemm.rs:154-189 (gate_up_silu), src/models/inkling/sconv.rs:70-340,
+// src/models/qwen3tts/megakernel.rs (qkv_rope_cache).  One CTA per token row, 16-byte vector accesses, f32 math,
+// a single rounding to bf16 on the way out.
+#include "common.cuh"
+#include "host_utils.h"
+
+using namespace mary;
+
+namespace {
+
+constexpr int NT = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+template <typename T> __device__ __forceinline__ float ld(const T* p, int64_t i);
+template <> __device__ __forceinline__ float ld<float>(const float* p, int64_t i) { return p[i]; }
+template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
+
+// y = rms(x) * w   (w may be null).  x is bf16 or f32, y bf16.
+template <typename TI>
+__global__ void rmsnorm_kernel(const TI* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                               int H, int64_t ldx, int64_t ldy, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const TI* xr = x + (int64_t)blockIdx.x * ldx;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = ld(xr, i); row[i] = v; ss += v * v; }
+  const float inv = rsqrtf(block_sum(ss, red) / H + eps);
+  __nv_bfloat16* yr = y + (int64_t)blockIdx.x * ldy;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = row[i] * inv;
+    if (w) v *= __bfloat162float(w[i]);
+    yr[i] = __float2bfloat16(v);
+  }
+}
+
+// residual += x (one rounding to bf16); y = rms(residual) * w
+template <typename TI>
+__global__ void add_rmsnorm_kernel(const TI* __restrict__ x, __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
+                                   __nv_bfloat16* __restrict__ y, int H, float eps) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int64_t o = (int64_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    __nv_bfloat16 r = __float2bfloat16(__bfloat162float(res[o + i]) + ld(x, o + i));
+    res[o + i] = r;
+    float v = __bfloat162float(r);
+    row[i] = v; ss += v * v;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) y[o + i] = __float2bfloat16(row[i] * inv * __bfloat162float(w[i]));
+}
+
+// Gemma sandwich step: h = (h + rms(a) * w_post) * scalar ; x = rms(h) * w_next (skipped when w_next is null)
+template <typename TI>
+__global__ void norm_add_norm_kernel(const TI* __restrict__ a, const __nv_bfloat16* __restrict__ w_post, __nv_bfloat16* __restrict__ h,
+                                     const __nv_bfloat16* __restrict__ w_next, __nv_bfloat16* __restrict__ xo, int H, float eps, float scalar) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int64_t o = (int64_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = ld(a, o + i); row[i] = v; ss += v * v; }
+  const float inv = rsqrtf(block_sum(ss, red) / H + eps);
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    // the normed branch output is rounded to bf16 like the unfused op sequence would
+    float n = __bfloat162float(__float2bfloat16(row[i] * inv * __bfloat162float(w_post[i])));
+    __nv_bfloat16 r = __float2bfloat16((__bfloat162float(h[o + i]) + n) * scalar);
+    h[o + i] = r;
+    float v = __bfloat162float(r);
+    row[i] = v; ss2 += v * v;
+  }
+  if (w_next == nullptr) return;
+  const float inv2 = rsqrtf(block_sum(ss2, red) / H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) xo[o + i] = __float2bfloat16(row[i] * inv2 * __bfloat162float(w_next[i]));
+}
+
+__global__ void glu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int F, int64_t n, int act) {
+  int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (idx >= n) return;
+  const int64_t t = idx / F, f = idx % F;
+  const uint4 g = *(const uint4*)(gu + t * 2 * F + f);
+  const uint4 u = *(const uint4*)(gu + t * 2 * F + F + f);
+  const __nv_bfloat162* gp = (const __nv_bfloat162*)&g;
+  const __nv_bfloat162* up = (const __nv_bfloat162*)&u;
+  uint4 o;
+  __nv_bfloat162* op = (__nv_bfloat162*)&o;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 gf = __bfloat1622float2(gp[j]), uf = __bfloat1622float2(up[j]);
+    op[j] = __floats2bfloat162_rn(glu_f(act, gf.x, uf.x), glu_f(act, gf.y, uf.y));
+  }
+  *(uint4*)(out + idx) = o;
+}
+
+__global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
+                             int H, float scale, int vocab) {
+  int id = ids[blockIdx.x];
+  if (id < 0 || id >= vocab) id = 0;
+  const __nv_bfloat16* src = table + (int64_t)id * H;
+  __nv_bfloat16* dst = out + (int64_t)blockIdx.x * H;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 v = *(const uint4*)(src + i);
+    if (scale != 1.0f) {
+      __nv_bfloat162* p = (__nv_bfloat162*)&v;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(p[j]); p[j] = __floats2bfloat162_rn(f.x * scale, f.y * scale); }
+    }
+    *(uint4*)(dst + i) = v;
+  }
+}
+
+// One warp per (token, head) of the fused qkv row: optional RMSNorm over the head (learned gain for q and k,
+// none for v), split-half RoPE for q and k, then q goes to qo[T, n_q, D] and k, v into their cache slots.
+__global__ void qk_norm_rope_append_kernel(const __nv_bfloat16* __restrict__ qkv, int n_q, int n_kv, int D,
+                                           const __nv_bfloat16* __restrict__ q_norm, const __nv_bfloat16* __restrict__ k_norm,
+                                           int v_norm, const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                           const int64_t* __restrict__ slots, __nv_bfloat16* __restrict__ qo,
+                                           __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, float eps, int T) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int heads = n_q + 2 * n_kv;
+  const int64_t gw = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  if (gw >= (int64_t)T * heads) return;
+  const int t = (int)(gw / heads), hh = (int)(gw % heads);
+  const int lane = threadIdx.x & 31;
+  const __nv_bfloat16* src = qkv + (int64_t)t * heads * D + (int64_t)hh * D;
+  const int half = D >> 1;
+  // lane handles pairs (i, i + half) for i = lane, lane + 32, ...
+  float x1[8], x2[8];   // D <= 512
+  const int np = (half + 31) / 32;
+  float ss = 0.f;
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    const int i = lane + 32 * m;
+    if (m < np && i < half) {
+      x1[m] = __bfloat162float(src[i]); x2[m] = __bfloat162float(src[i + half]);
+      ss += x1[m] * x1[m] + x2[m] * x2[m];
+    }
+  }
+  const bool is_q = hh < n_q, is_k = !is_q && hh < n_q + n_kv;
+  const __nv_bfloat16* gain = is_q ? q_norm : (is_k ? k_norm : nullptr);
+  const bool do_norm = is_q ? (q_norm != nullptr) : (is_k ? (k_norm != nullptr) : (v_norm != 0));
+  float inv = 1.f;
+  if (do_norm) inv = rsqrtf(warp_sum(ss) / D + eps);
+  const float pos = (float)positions[t];
+  __nv_bfloat16* dst;
+  if (is_q) dst = qo + ((int64_t)t * n_q + hh) * D;
+  else if (is_k) dst = kc + (slots[t] * n_kv + (hh - n_q)) * D;
+  else dst = vc + (slots[t] * n_kv + (hh - n_q - n_kv)) * D;
+#pragma unroll
+  for (int m = 0; m < 8; ++m) {
+    const int i = lane + 32 * m;
+    if (m < np && i < half) {
+      float a = x1[m] * inv, b = x2[m] * inv;
+      if (do_norm) {
+        // round the normed value to bf16 first, as the unfused sequence (norm kernel then rope kernel) does
+        a = __bfloat162float(__float2bfloat16(a * (gain ? __bfloat162float(gain[i]) : 1.f)));
+        b = __bfloat162float(__float2bfloat16(b * (gain ? __bfloat162float(gain[i + half]) : 1.f)));
+      }
+      if (!is_q && !is_k) { dst[i] = __float2bfloat16(a); dst[i + half] = __float2bfloat16(b); continue; }
+      if (inv_freq) {
+        float s, c;
+        sincosf(pos * inv_freq[i], &s, &c);
+        const float ra = a * c - b * s, rb = a * s + b * c;
+        a = ra; b = rb;
+      }
+      dst[i] = __float2bfloat16(a); dst[i + half] = __float2bfloat16(b);
+    }
+  }
+}
+
+// y = x + depthwise causal conv_k(x) with history of the previous k-1 pre-conv rows; one thread per channel,
+// rows of one sequence are walked in order (src/models/inkling/block.rs:48-127).  hist is updated in place.
+__global__ void short_conv_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w, __nv_bfloat16* __restrict__ hist,
+                                  __nv_bfloat16* __restrict__ y, int T, int D, int k) {
+  const int d = blockIdx.x * blockDim.x + threadIdx.x;
+  if (d >= D) return;
+  float win[8];
+  float wk[8];
+  for (int j = 0; j < k; ++j) wk[j] = w[d * k + j];
+  for (int j = 0; j < k - 1; ++j) win[j] = __bfloat162float(hist[(int64_t)j * D + d]);
+  for (int t = 0; t < T; ++t) {
+    const float cur = __bfloat162float(x[(int64_t)t * D + d]);
+    win[k - 1] = cur;
+    float acc = cur;
+    for (int j = 0; j < k; ++j) acc += win[j] * wk[j];
+    y[(int64_t)t * D + d] = __float2bfloat16(acc);
+    for (int j = 0; j < k - 1; ++j) win[j] = win[j + 1];
+  }
+  for (int j = 0; j < k - 1; ++j) hist[(int64_t)j * D + d] = __float2bfloat16(win[j]);
+}
+
+}  // namespace
+
+MARY_API int mary_rmsnorm(const void* x, int x_is_f32, const void* w, void* y, int T, int H, int64_t ldx, int64_t ldy, float eps,
+                          cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  size_t sm = (size_t)H * 4;
+  if (sm > 48 * 1024) return MARY_ERR_BAD_ARG;
+  if (x_is_f32) rmsnorm_kernel<float><<<T, NT, sm, s>>>((const float*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
+  else rmsnorm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_add_rmsnorm(const void* x, int x_is_f32, void* res, const void* w, void* y, int T, int H, float eps, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  size_t sm = (size_t)H * 4;
+  if (sm > 48 * 1024) return MARY_ERR_BAD_ARG;
+  if (x_is_f32) add_rmsnorm_kernel<float><<<T, NT, sm, s>>>((const float*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
+  else add_rmsnorm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_norm_add_norm(const void* a, int a_is_f32, const void* w_post, void* h, const void* w_next, void* xo, int T, int H,
+                                float eps, float scalar, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  size_t sm = (size_t)H * 4;
+  if (sm > 48 * 1024) return MARY_ERR_BAD_ARG;
+  if (a_is_f32) norm_add_norm_kernel<float><<<T, NT, sm, s>>>((const float*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
+  else norm_add_norm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_glu(const void* gu, void* out, int T, int F, int act, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  if (F % 8) return MARY_ERR_BAD_ARG;
+  int64_t n = (int64_t)T * F;
+  int blocks = (int)((n / 8 + NT - 1) / NT);
+  glu_kernel<<<blocks, NT, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, n, act);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_embed(const int* ids, const void* table, void* out, int T, int H, float scale, int vocab, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  if (H % 8) return MARY_ERR_BAD_ARG;
+  embed_kernel<<<T, 128, 0, s>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, H, scale, vocab);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_qk_norm_rope_append(const void* qkv, int n_q, int n_kv, int D, const void* q_norm, const void* k_norm, int v_norm,
+                                      const float* inv_freq, const int* positions, const int64_t* slots, void* qo, void* kc, void* vc,
+                                      float eps, int T, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  if (D > 512 || (D & 1)) return MARY_ERR_BAD_ARG;
+  const int64_t warps = (int64_t)T * (n_q + 2 * n_kv);
+  const int wpb = 8;
+  qk_norm_rope_append_kernel<<<(int)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+      (const __nv_bfloat16*)qkv, n_q, n_kv, D, (const __nv_bfloat16*)q_norm, (const __nv_bfloat16*)k_norm, v_norm, inv_freq, positions,
+      slots, (__nv_bfloat16*)qo, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, eps, T);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_short_conv(const void* x, const float* w, void* hist, void* y, int T, int D, int k, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  if (k > 8 || k < 1) return MARY_ERR_BAD_ARG;
+  short_conv_kernel<<<(D + 127) / 128, 128, 0, s>>>((const __nv_bfloat16*)x, w, (__nv_bfloat16*)hist, (__nv_bfloat16*)y, T, D, k);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}

@@ -1,0 +1,182 @@
+// MoE plumbing around the grouped expert GEMM: routing plan (counting sort by expert, padded to the token-tile
+// width), gather + NVFP4 activation quantisation, and the weighted un-permute.
+//
+// Reference pieces: host `RowPlan` (src/models/inkling/moegroup.rs:978-1083), `gather_grouped`
+// (moegroup.rs:146-240), `quantize_nvfp4_kernel` (src/models/inkling/fp4quant.rs:122-244; rules :10-54 —
+// per 16 elements amax -> min(amax/6, 448) -> E4M3 round-to-nearest-even -> codes by the thresholds
+// .25 .75 1.25 1.75 2.5 3.5 5 with ties away from zero, signed zero kept, zero block -> scale byte 0),
+// `scatter_weighted` (moegroup.rs:841-939: out[t] = sum_j y[row_j] * w[row_j] in ascending order with fma).
+// Here the plan is built on the device, so no readback separates the router from the expert GEMMs
+// (the reference blocks on a router readback once per MoE layer, src/bin/inkling_forward.rs:4442-4478).
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+#include "host_utils.h"
+
+using namespace mary;
+
+namespace {
+
+struct Tile { int expert, row0, rows, sf_tile; };
+
+// One CTA.  idx[n_entries] = expert of every (token, slot) entry (negative = entry not routed here).
+// Outputs: row_of[n_entries] padded row of each entry (-1 if skipped), src_of[max_rows] token of each padded row
+// (-1 for padding), tiles/n_tiles for the grouped GEMM, counts[E], meta = {n_tiles, padded rows}.
+__global__ void moe_plan_kernel(const int* __restrict__ idx, int n_entries, int k, int E, int NT, int max_rows, int* __restrict__ row_of,
+                                int* __restrict__ src_of, Tile* __restrict__ tiles, int* __restrict__ meta, int* __restrict__ counts_out) {
+  extern __shared__ int sh[];
+  int* cnt = sh;            // [E]
+  int* off = sh + E;        // [E + 1]
+  for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+  for (int r = threadIdx.x; r < max_rows; r += blockDim.x) src_of[r] = -1;
+  __syncthreads();
+  // Slots inside an expert come from a shared-memory counter.  Their order within a chunk of blockDim entries
+  // depends on scheduling, which does not matter: every row of the grouped GEMM is independent and the un-permute
+  // sums a token's k results in fixed slot order.
+  for (int base = 0; base < n_entries; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const int e = (i < n_entries) ? idx[i] : -1;
+    int slot = -1;
+    if (e >= 0 && e < E) slot = atomicAdd(&cnt[e], 1);
+    if (i < n_entries) row_of[i] = slot;       // provisional: slot inside the expert
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) { off[e] = acc; acc += (cnt[e] + NT - 1) / NT * NT; }
+    off[E] = acc;
+    meta[0] = acc / NT;
+    meta[1] = acc;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    if (counts_out) counts_out[e] = cnt[e];
+    const int c = cnt[e];
+    for (int i = 0; i * NT < c; ++i) {
+      Tile t{e, off[e] + i * NT, min(NT, c - i * NT), off[e] / NT + i};
+      tiles[off[e] / NT + i] = t;
+    }
+  }
+  for (int i = threadIdx.x; i < n_entries; i += blockDim.x) {
+    const int e = idx[i];
+    if (e >= 0 && e < E) {
+      const int row = off[e] + row_of[i];
+      row_of[i] = row;
+      src_of[row] = i / k;
+    } else row_of[i] = -1;
+  }
+}
+
+__device__ __forceinline__ uint32_t e2m1_code(float y) {
+  const float m = fabsf(y);
+  uint32_t c = (m >= 0.25f) + (m >= 0.75f) + (m >= 1.25f) + (m >= 1.75f) + (m >= 2.5f) + (m >= 3.5f) + (m >= 5.0f);
+  return c | (signbit(y) ? 8u : 0u);
+}
+
+// One CTA per destination row.  src_of[row] < 0 -> padding row, skipped.  identity != 0 -> the source row is `row`
+// itself (re-quantising an intermediate that is already in padded-row order; src_of only marks validity, may be null).
+// Scales go to the 512-byte block layout of the row's NT-row tile; optionally also row-major (tests, dense users).
+__global__ void quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int* __restrict__ src_of, int identity,
+                                        int Kd, int NT, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf_tiles,
+                                        uint8_t* __restrict__ sf_rowmajor, const int* __restrict__ n_rows) {
+  const int row = blockIdx.x;
+  if (n_rows && row >= *n_rows) return;
+  int src = row;
+  if (src_of) { const int s = src_of[row]; if (s < 0) return; if (!identity) src = s; }
+  const __nv_bfloat16* xr = x + (int64_t)src * ldx;
+  const int tile = row / NT, r = row % NT;
+  const int64_t sf_base = (int64_t)tile * (Kd / 64) * 512 + (r % 32) * 16 + (r / 32) * 4;
+  for (int b = threadIdx.x; b < Kd / 16; b += blockDim.x) {
+    const uint4 v0 = *(const uint4*)(xr + b * 16), v1 = *(const uint4*)(xr + b * 16 + 8);
+    float f[16];
+    const __nv_bfloat162* p0 = (const __nv_bfloat162*)&v0;
+    const __nv_bfloat162* p1 = (const __nv_bfloat162*)&v1;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 a = __bfloat1622float2(p0[j]), c = __bfloat1622float2(p1[j]);
+      f[2 * j] = a.x; f[2 * j + 1] = a.y; f[8 + 2 * j] = c.x; f[8 + 2 * j + 1] = c.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    const float sfv = fminf(__fdiv_rn(amax, 6.0f), 448.0f);
+    const __nv_fp8_storage_t sb = __nv_cvt_float_to_fp8(sfv, __NV_SATFINITE, __NV_E4M3);
+    const float s = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3)));
+    uint32_t lo = 0, hi = 0;
+    if (s > 0.f) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { lo |= e2m1_code(__fdiv_rn(f[j], s)) << (4 * j); hi |= e2m1_code(__fdiv_rn(f[8 + j], s)) << (4 * j); }
+    }
+    *(uint2*)(xq + (int64_t)row * (Kd / 2) + b * 8) = make_uint2(lo, hi);
+    if (sf_tiles) sf_tiles[sf_base + (int64_t)(b / 4) * 512 + (b % 4)] = (uint8_t)sb;
+    if (sf_rowmajor) sf_rowmajor[(int64_t)row * (Kd / 16) + b] = (uint8_t)sb;
+  }
+}
+
+// out[t, :] = sum_j w[t, j] * y[row_of[t*k + j], :]  (+ add[t, :]) in ascending j with fma; one CTA per token.
+__global__ void moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, int64_t ldy, const int* __restrict__ row_of,
+                                     const float* __restrict__ w, int k, int H, const __nv_bfloat16* __restrict__ add,
+                                     __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (add) {
+      const uint4 a = *(const uint4*)(add + (int64_t)t * H + c);
+      const __nv_bfloat162* ap = (const __nv_bfloat162*)&a;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(ap[j]); acc[2 * j] = f.x; acc[2 * j + 1] = f.y; }
+    }
+    for (int j = 0; j < k; ++j) {
+      const int row = row_of[t * k + j];
+      if (row < 0) continue;
+      const float wj = w[t * k + j];
+      const uint4 v = *(const uint4*)(y + (int64_t)row * ldy + c);
+      const __nv_bfloat162* vp = (const __nv_bfloat162*)&v;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) { float2 f = __bfloat1622float2(vp[q]); acc[2 * q] = fmaf(f.x, wj, acc[2 * q]); acc[2 * q + 1] = fmaf(f.y, wj, acc[2 * q + 1]); }
+    }
+    uint4 o;
+    __nv_bfloat162* op = (__nv_bfloat162*)&o;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) op[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *(uint4*)(out + (int64_t)t * H + c) = o;
+  }
+}
+
+}  // namespace
+
+MARY_API int mary_moe_plan(const int* idx, int n_entries, int k, int E, int NT, int max_rows, int* row_of, int* src_of, void* tiles,
+                           int* meta, int* counts, cudaStream_t s) {
+  if (E > 4096 || NT <= 0) return MARY_ERR_BAD_ARG;
+  moe_plan_kernel<<<1, 1024, (2 * E + 1) * sizeof(int), s>>>(idx, n_entries, k, E, NT, max_rows, row_of, src_of, (Tile*)tiles, meta, counts);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// Upper bound of padded rows for n_entries routed entries over E experts with tile width NT.
+MARY_API int mary_moe_max_rows(int n_entries, int E, int NT) {
+  const int worst = n_entries + (n_entries < E ? n_entries : E) * (NT - 1);
+  return (worst + NT - 1) / NT * NT;
+}
+
+MARY_API int mary_quant_nvfp4_rows(const void* x, int64_t ldx, const int* src_of, int identity, int rows, int K, int NT, void* xq,
+                                   void* sf_tiles, void* sf_rowmajor, const int* n_rows, cudaStream_t s) {
+  if (rows <= 0) return MARY_OK;
+  if ((K % 64) || (ldx % 8)) return MARY_ERR_BAD_ARG;
+  int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
+  quant_nvfp4_rows_kernel<<<rows, threads, 0, s>>>((const __nv_bfloat16*)x, ldx, src_of, identity, K, NT, (uint8_t*)xq, (uint8_t*)sf_tiles,
+                                                   (uint8_t*)sf_rowmajor, n_rows);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_moe_unpermute(const void* y, int64_t ldy, const int* row_of, const float* w, int T, int k, int H, const void* add,
+                                void* out, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  if (H % 8) return MARY_ERR_BAD_ARG;
+  moe_unpermute_kernel<<<T, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, row_of, w, k, H, (const __nv_bfloat16*)add, (__nv_bfloat16*)out);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}

@@ -65,10 +65,10 @@ class Gemma4Layer(nn.Module):
         o = o.reshape(o.shape[0], -1)
         a = self.tp.row_linear(o, self.w_o, L.get("o"))
         x, h = ops.norm_add_norm(a, self.ln_post_attn, h, self.ln_pre_ffn, c.rms_norm_eps)
-        gu = ops.linear(x, self.w_gu)
         if "gu" in L:
-            gu = gu + L["gu"](x)
-        m = ops.glu(gu, "geglu")
+            m = ops.glu(ops.linear(x, self.w_gu) + L["gu"](x), "geglu")
+        else:
+            m = ops.linear_glu(x, self.w_gu, "geglu")
         d = self.tp.row_linear(m, self.w_down, L.get("down"))
         return ops.norm_add_norm(d, self.ln_post_ffn, h, next_norm, c.rms_norm_eps, self.layer_scalar)
 

@@ -74,6 +74,13 @@ def glu(gate_up, act: str = "geglu"):
     return {"geglu": ref.geglu, "swiglu": ref.swiglu, "situ": ref.situ}[act](gate_up[..., :F], gate_up[..., F:])
 
 
+def linear_glu(x, w_gu, act: str = "geglu"):
+    """``act(x @ gate^T) * (x @ up^T)`` with ``w_gu = [gate; up]``; fused into the GEMM epilogue on the GPU."""
+    if _cuda(x):
+        return _k().linear_glu(x, w_gu, act)
+    return glu(ref.linear(x, w_gu), act)
+
+
 def embed(ids, table, scale=1.0):
     return _k().embed(ids, table, scale) if _cuda(table) else ref.embed(ids, table, scale)
 

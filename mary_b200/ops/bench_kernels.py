@@ -1,0 +1,95 @@
+"""Kernel micro-benchmarks: CUDA-event timing after warm-up with an L2 flush between iterations, reported against
+the measured peaks of the machine (``MEASURED_PEAKS.json`` at the repository root when present, else the stated
+fallback).  ``python -m mary_b200.ops.bench_kernels [gemm|attn|all]``."""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+
+def peaks():
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"], d["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+_flush = None
+
+
+def time_op(fn, iters: int = 10, warmup: int = 3) -> float:
+    """Median milliseconds of ``fn()``; a 256 MiB write between iterations evicts L2."""
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        _flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def bench_gemm():
+    from . import cuda as K
+    hbm, tf, tag = peaks()
+    print(f"{'M':>6} {'N':>6} {'K':>6} {'ours ms':>9} {'torch ms':>9} {'TFLOP/s':>8} {'GB/s':>7}  frac {tag}")
+    for M, N, Kd in [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 15360 * 2, 3840), (32, 6144, 3840), (32, 3840, 4096),
+                     (32, 30720, 3840), (32, 3840, 15360), (384, 2112, 7168), (384, 12288, 1536), (384, 7168, 8192),
+                     (128, 163840, 7168)]:
+        x = torch.randn(M, Kd, device="cuda").bfloat16()
+        w = (torch.randn(N, Kd, device="cuda") * 0.02).bfloat16()
+        sk = K._auto_split_k(M, N, Kd)
+        if sk > 1:
+            out = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+            ours = time_op(lambda: K.gemm(x, w, out=out, epi="red", split_k=sk))
+        else:
+            out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            ours = time_op(lambda: K.gemm(x, w, out=out))
+        th = time_op(lambda: torch.matmul(x, w.T))
+        fl = 2.0 * M * N * Kd / ours / 1e9
+        gb = (M * Kd + N * Kd + M * N) * 2 / ours / 1e6
+        frac = max(fl / tf, gb / hbm)
+        print(f"{M:>6} {N:>6} {Kd:>6} {ours:>9.4f} {th:>9.4f} {fl:>8.1f} {gb:>7.0f}  {frac:.2f} (split_k={sk})")
+    assert K.last_status() == 0
+
+
+def bench_attn():
+    from . import cuda as K
+    from ..runtime.batch import BatchMeta
+    from ..runtime.kv_cache import PagedKVCache
+    hbm, tf, tag = peaks()
+    for (B, L, Hq, Hkv, D, win) in [(32, 2304, 16, 8, 256, 0), (32, 2304, 16, 8, 256, 1024), (64, 1536, 32, 8, 128, 0)]:
+        pages = B * ((L + 15) // 16) + 1
+        cache = PagedKVCache(1, pages, 16, Hkv, D, dtype=torch.bfloat16, device="cuda")
+        for s in range(B):
+            cache.alloc.extend(s, L)
+        table, lens = cache.alloc.page_table(list(range(B)))
+        meta = BatchMeta.build([1] * B, lens, table, 16, "cuda")
+        cache.k[0].normal_()
+        cache.v[0].normal_()
+        q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+        ms = time_op(lambda: K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, win))
+        span = L if win == 0 else min(L, win)
+        gb = B * span * Hkv * D * 2 * 2 / ms / 1e6
+        print(f"decode attn B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, {gb:.0f} GB/s, {gb / hbm:.2f} {tag}")
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if what in ("gemm", "all"):
+        bench_gemm()
+    if what in ("attn", "all"):
+        bench_attn()

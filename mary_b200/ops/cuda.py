@@ -1,0 +1,295 @@
+"""CUDA (sm_100a) implementations of the ops: thin ctypes wrappers over ``_kernels.so``.
+
+Tensors are passed as raw device pointers plus the current CUDA stream, so the launches are captured by CUDA
+graphs like any other stream work.  Every wrapper checks the launcher's return code; activations are bf16."""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from .. import _native
+
+_SIG = {
+    # name: argument codes — p pointer, i int32, l int64, f float, s stream
+    "mary_gemm_bf16": "pppiiilllpfiiiis",
+    "mary_rmsnorm": "pippiillfs",
+    "mary_add_rmsnorm": "pipppiifs",
+    "mary_norm_add_norm": "pippppiiffs",
+    "mary_glu": "ppiiis",
+    "mary_embed": "pppiifis",
+    "mary_qk_norm_rope_append": "piiippipppppp" + "fis",
+    "mary_short_conv": "ppppiiis",
+    "mary_paged_attention": "ppppppppp" + "iii" + "llll" + "iiiiiii" + "ff" + "ps",
+    "mary_paged_attention_scratch_floats": "iiii",
+    "mary_paged_attention_max_rows": "i",
+    "mary_last_status": "",
+    "mary_sm_count": "",
+}
+_CT = {"p": ctypes.c_void_p, "i": ctypes.c_int32, "l": ctypes.c_int64, "f": ctypes.c_float, "s": ctypes.c_void_p}
+_RET64 = {"mary_paged_attention_scratch_floats"}
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        l = _native.kernels()
+        for name, sig in _SIG.items():
+            try:
+                fn = getattr(l, name)
+            except AttributeError:
+                continue
+            fn.argtypes = [_CT[c] for c in sig]
+            fn.restype = ctypes.c_int64 if name in _RET64 else ctypes.c_int32
+        _lib = l
+    return _lib
+
+
+def declare(name: str, sig: str, ret64: bool = False):
+    """Register one more launcher signature (used by the other op modules)."""
+    _SIG[name] = sig
+    if ret64:
+        _RET64.add(name)
+    global _lib
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = [_CT[c] for c in sig]
+        fn.restype = ctypes.c_int64 if ret64 else ctypes.c_int32
+
+
+_STATUS = {1: "a TMA pipeline wait timed out", 2: "an accumulator wait timed out", 3: "a peer flag wait timed out",
+           4: "bad argument", 5: "CUDA launch error", 6: "bounds check failed"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str):
+    if rc != 0:
+        raise KernelError(f"{what}: {_STATUS.get(rc, rc)}")
+
+
+def last_status() -> int:
+    """Read and clear the device status word (synchronises)."""
+    return lib().mary_last_status()
+
+
+def _bf16(t):
+    if t.dtype != torch.bfloat16:
+        raise TypeError(f"expected a bf16 tensor, got {t.dtype}")
+    return t
+
+
+# --------------------------------------------------------------------------- GEMM
+def gemm(x, w, out=None, bias=None, alpha: float = 1.0, glu: str | None = None, epi: str = "bf16", split_k: int = 1,
+         swap: int = -1):
+    """``out[M, N] = alpha * x[M, K] @ w[N, K]^T``.  ``glu``: ``w = [gate; up]`` (2N rows) and the epilogue writes
+    ``act(gate) * up``.  ``epi``: ``"bf16"`` store, ``"f32"`` store, ``"red"`` accumulate into a zeroed f32 ``out``."""
+    _bf16(x), _bf16(w)
+    M, K = x.shape
+    n_w = w.shape[0]
+    N = n_w // 2 if glu else n_w
+    assert w.shape[1] == K and x.stride(1) == 1 and w.stride(1) == 1
+    e = {"bf16": 0, "red": 1, "f32": 2}[epi]
+    if out is None:
+        out = (torch.zeros if e == 1 else torch.empty)(M, N, dtype=torch.bfloat16 if e == 0 else torch.float32, device=x.device)
+    g = 0 if glu is None else {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
+    rc = lib().mary_gemm_bf16(_p(x), _p(w), _p(out), M, N, K, x.stride(0), w.stride(0), out.stride(0), _p(bias), alpha, g, e,
+                              split_k, swap, _stream())
+    check(rc, "gemm_bf16")
+    return out
+
+
+def _auto_split_k(M: int, N: int, K: int) -> int:
+    """Decode-sized GEMMs have too few output tiles to fill 148 SMs; split K until they do."""
+    tiles = ((N + 127) // 128) * max(1, (M + 255) // 256)
+    if M > 256 or tiles >= 120:
+        return 1
+    return max(1, min(K // 512, (148 + tiles - 1) // tiles))
+
+
+def linear(x, w, bias=None):
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    sk = _auto_split_k(M, w.shape[0], K)
+    if sk > 1 and bias is None:
+        out = gemm(x2, w, epi="red", split_k=sk).to(torch.bfloat16)
+    else:
+        out = gemm(x2, w, bias=bias)
+    return out.reshape(*shp[:-1], w.shape[0])
+
+
+def linear_f32(x, w, split_k: int | None = None):
+    """Row-parallel style GEMM whose f32 result feeds a norm kernel directly (no bf16 rounding in between)."""
+    M, K = x.shape
+    sk = split_k or _auto_split_k(M, w.shape[0], K)
+    return gemm(x, w, epi="red", split_k=sk)
+
+
+def linear_glu(x, w_gu, act: str = "geglu"):
+    M = x.shape[0]
+    if M <= 128:
+        return gemm(x, w_gu, glu=act)
+    return glu(gemm(x, w_gu), act)
+
+
+# --------------------------------------------------------------------------- norms and friends
+def rmsnorm(x, weight=None, eps=1e-6):
+    shp = x.shape
+    x2 = x.reshape(-1, shp[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    y = torch.empty(x2.shape, dtype=torch.bfloat16, device=x.device)
+    check(lib().mary_rmsnorm(_p(x2), int(x2.dtype == torch.float32), _p(weight), _p(y), x2.shape[0], x2.shape[1],
+                             x2.stride(0), y.stride(0), eps, _stream()), "rmsnorm")
+    return y.reshape(shp)
+
+
+def add_rmsnorm(x, residual, weight, eps=1e-6):
+    y = torch.empty_like(residual)
+    check(lib().mary_add_rmsnorm(_p(x), int(x.dtype == torch.float32), _p(residual), _p(weight), _p(y), residual.shape[0],
+                                 residual.shape[1], eps, _stream()), "add_rmsnorm")
+    return y, residual
+
+
+def norm_add_norm(a, w_post, h, w_next, eps=1e-6, scalar=1.0):
+    xo = torch.empty_like(h) if w_next is not None else None
+    check(lib().mary_norm_add_norm(_p(a), int(a.dtype == torch.float32), _p(w_post), _p(h), _p(w_next), _p(xo), h.shape[0],
+                                   h.shape[1], eps, scalar, _stream()), "norm_add_norm")
+    return xo, h
+
+
+def glu(gate_up, act="geglu"):
+    T, F2 = gate_up.shape
+    out = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=gate_up.device)
+    check(lib().mary_glu(_p(gate_up.contiguous()), _p(out), T, F2 // 2, {"geglu": 0, "swiglu": 1, "situ": 2}[act], _stream()), "glu")
+    return out
+
+
+def embed(ids, table, scale=1.0):
+    ids = ids.to(torch.int32)
+    out = torch.empty(ids.shape[0], table.shape[1], dtype=torch.bfloat16, device=table.device)
+    check(lib().mary_embed(_p(ids), _p(table), _p(out), ids.shape[0], table.shape[1], scale, table.shape[0], _stream()), "embed")
+    return out
+
+
+def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm, inv_freq, meta, kcache, vcache, eps):
+    T = qkv.shape[0]
+    q = torch.empty(T, n_q, head_dim, dtype=torch.bfloat16, device=qkv.device)
+    check(lib().mary_qk_norm_rope_append(_p(qkv.contiguous()), n_q, n_kv, head_dim, _p(q_norm), _p(k_norm), int(bool(v_norm)),
+                                         _p(inv_freq), _p(meta.positions), _p(meta.slot_mapping), _p(q), _p(kcache), _p(vcache),
+                                         eps, T, _stream()), "qk_norm_rope_append")
+    return q
+
+
+def short_conv(x, w, history=None):
+    T, D = x.shape
+    k = w.shape[1]
+    hist = history.clone() if history is not None else torch.zeros(k - 1, D, dtype=torch.bfloat16, device=x.device)
+    y = torch.empty_like(x)
+    check(lib().mary_short_conv(_p(x.contiguous()), _p(w.float().contiguous()), _p(hist), _p(y), T, D, k, _stream()), "short_conv")
+    return y, hist
+
+
+# --------------------------------------------------------------------------- attention
+def _q_blocks(meta, rq: int):
+    key = ("qblk", rq)
+    cache = meta.__dict__.setdefault("_cache", {})
+    if key not in cache:
+        import numpy as np
+        seqs, q0 = [], []
+        start = 0
+        for s, n in enumerate(meta.q_lens_host.tolist()):
+            for b in range(0, n, rq):
+                seqs.append(s)
+                q0.append(start + b)
+            start += n
+        dev = meta.positions.device
+        cache[key] = (torch.tensor(seqs, dtype=torch.int32).to(dev, non_blocking=True),
+                      torch.tensor(q0, dtype=torch.int32).to(dev, non_blocking=True), len(seqs))
+    return cache[key]
+
+
+def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: int | None = None, nsplit: int | None = None):
+    """``q[T, Hq, DK]``; caches ``[pages, page, Hkv, D]`` (a latent cache is ``Hkv = 1`` with ``dv`` < DK and
+    ``vcache is kcache``).  Returns ``[T, Hq, DV]``."""
+    T, Hq, DK = q.shape
+    Hkv = kcache.shape[2] if kcache.dim() == 4 else 1
+    DV = dv or vcache.shape[-1]
+    G = Hq // Hkv
+    maxr = lib().mary_paged_attention_max_rows(DV)
+    if G > maxr:
+        # more query heads per kv head than one CTA can hold: fold the surplus into extra "kv heads" that alias
+        # the same cache rows (head stride 0 is expressed by Hkv' = Hkv * fold with DK-strided q only)
+        raise NotImplementedError("GQA group larger than the row budget; use the tensor-core MLA kernel")
+    rq = max(1, min(maxr // G, meta.max_q_len))
+    blk_seq, blk_q0, NB = _q_blocks(meta, rq)
+    if nsplit is None:
+        want = max(1, 296 // max(1, NB * Hkv))
+        span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
+        nsplit = max(1, min(want, 32, span // 128))
+    out = torch.empty(T, Hq, DV, dtype=torch.bfloat16, device=q.device)
+    scratch = None
+    if nsplit > 1:
+        n = lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, DV)
+        scratch = torch.empty(n, dtype=torch.float32, device=q.device)
+    ktok, kpage = kcache.stride(1), kcache.stride(0)
+    vtok, vpage = vcache.stride(1), vcache.stride(0)
+    check(lib().mary_paged_attention(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
+                                     _p(meta.q_start), _p(blk_seq), _p(blk_q0), NB, meta.page_table.shape[1], meta.page_size,
+                                     ktok, kpage, vtok, vpage, Hq, Hkv, DK, DV, rq, nsplit, window, scale, softcap,
+                                     _p(scratch), _stream()), "paged_attention")
+    return out
+
+
+# --------------------------------------------------------------------------- selection
+declare("mary_argmax", "pliififfllpps")
+declare("mary_router_topk", "plpiiiiiifipppps")
+
+
+def argmax(logits, softcap=0.0, temperature: float = 0.0, margin: float = 20.0, seed: int = 0, step: int = 0):
+    """Per-row arg-max (first maximum wins) or, with ``temperature > 0``, a Gumbel-max sample.  Returns ``(ids, value)``."""
+    rows, V = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    idx = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    val = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    check(lib().mary_argmax(_p(logits), logits.stride(0), rows, V, softcap, 1 if temperature > 0 else 0, temperature, margin,
+                            seed, step, _p(idx), _p(val), _stream()), "argmax")
+    return idx, val
+
+
+def lm_head_argmax(h, table, softcap=0.0, vocab_limit=None):
+    logits = gemm(h.contiguous(), table, epi="f32")
+    if vocab_limit:
+        logits = logits[:, :vocab_limit]
+    return argmax(logits, softcap)
+
+
+def router_topk(logits, k, mode="softmax", bias=None, n_group=1, topk_group=1, scale=1.0, renorm=True, counts=None, flag=None):
+    T, E = logits.shape
+    lg = logits if logits.dtype == torch.float32 else logits.float()
+    idx = torch.empty(T, k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    b = bias.float().contiguous() if bias is not None else None
+    check(lib().mary_router_topk(_p(lg), lg.stride(0), _p(b), T, E, k, 0 if mode == "softmax" else 1, n_group, topk_group, scale,
+                                 int(renorm), _p(idx), _p(w), _p(counts), _p(flag), _stream()), "router_topk")
+    return idx, w
+
+
+def quantize_nvfp4(x):
+    from . import cuda_moe
+    return cuda_moe.quantize_nvfp4(x)

@@ -1,0 +1,81 @@
+"""ctypes wrappers for the MoE kernels (plan, quantise, grouped NVFP4 GEMM, un-permute)."""
+from __future__ import annotations
+
+import torch
+
+from .cuda import _p, _stream, check, declare, lib
+
+declare("mary_moe_plan", "piiiiippppps")
+declare("mary_moe_max_rows", "iii")
+declare("mary_quant_nvfp4_rows", "plpiiiipppps")
+declare("mary_moe_unpermute", "plppiiipps")
+declare("mary_gemm_nvfp4_grouped", "pppppppp" + "liiilii" + "s")
+
+
+def quantize_rows(x, nt: int = 128, src_of=None, identity: bool = True, rows: int | None = None, rowmajor: bool = False,
+                  n_rows=None):
+    """NVFP4-quantise rows of ``x`` (bf16).  Returns ``(codes[rows, K/2], sf_blocks[ceil(rows/nt), K/64, 512], rowmajor|None)``.
+    With ``src_of`` (int32 per destination row) rows are gathered (``identity=False``) or merely validated."""
+    K = x.shape[1]
+    rows = rows if rows is not None else x.shape[0]
+    tiles = (rows + nt - 1) // nt
+    xq = torch.empty(rows, K // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.zeros(tiles, K // 64, 512, dtype=torch.uint8, device=x.device)
+    rm = torch.empty(rows, K // 16, dtype=torch.uint8, device=x.device) if rowmajor else None
+    check(lib().mary_quant_nvfp4_rows(_p(x), x.stride(0), _p(src_of), int(identity), rows, K, nt, _p(xq), _p(sf), _p(rm),
+                                      _p(n_rows), _stream()), "quant_nvfp4_rows")
+    return xq, sf, rm
+
+
+def quantize_nvfp4(x):
+    """Row-major twin of the reference quantiser: ``(codes, scales[rows, K/16])``."""
+    xq, _, rm = quantize_rows(x.contiguous(), nt=128, rowmajor=True)
+    return xq, rm
+
+
+class Plan:
+    __slots__ = ("row_of", "src_of", "tiles", "meta", "counts", "max_rows", "nt")
+
+
+def moe_plan(idx, E: int, nt: int) -> Plan:
+    T, k = idx.shape
+    p = Plan()
+    p.nt = nt
+    p.max_rows = lib().mary_moe_max_rows(T * k, E, nt)
+    dev = idx.device
+    p.row_of = torch.empty(T * k, dtype=torch.int32, device=dev)
+    p.src_of = torch.empty(p.max_rows, dtype=torch.int32, device=dev)
+    p.tiles = torch.empty(p.max_rows // nt, 4, dtype=torch.int32, device=dev)
+    p.meta = torch.empty(2, dtype=torch.int32, device=dev)
+    p.counts = torch.empty(E, dtype=torch.int32, device=dev)
+    check(lib().mary_moe_plan(_p(idx.contiguous()), T * k, k, E, nt, p.max_rows, _p(p.row_of), _p(p.src_of), _p(p.tiles),
+                              _p(p.meta), _p(p.counts), _stream()), "moe_plan")
+    return p
+
+
+def grouped_gemm(wq, sfw, scale2, xq, sfx, plan: Plan, n_out: int, K: int, E: int, glu: str | None):
+    out = torch.empty(plan.max_rows, n_out, dtype=torch.bfloat16, device=xq.device)
+    g = 0 if glu is None else {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
+    check(lib().mary_gemm_nvfp4_grouped(_p(wq), _p(sfw), _p(scale2), _p(xq), _p(sfx), _p(plan.tiles), _p(plan.meta), _p(out),
+                                        out.stride(0), E, n_out, K, plan.max_rows, plan.nt, g, _stream()), "gemm_nvfp4_grouped")
+    return out
+
+
+def unpermute(y, plan: Plan, w, T: int, k: int, add=None):
+    H = y.shape[1]
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+    check(lib().mary_moe_unpermute(_p(y), y.stride(0), _p(plan.row_of), _p(w.float().contiguous()), T, k, H, _p(add), _p(out),
+                                   _stream()), "moe_unpermute")
+    return out
+
+
+def experts_forward(x, idx, w, ex, shared=None, nt: int | None = None):
+    T, k = idx.shape
+    if nt is None:
+        nt = 32 if T * k <= 32 * ex.E else 128
+    plan = moe_plan(idx, ex.E, nt)
+    xq, sfx, _ = quantize_rows(x, nt, plan.src_of, identity=False, rows=plan.max_rows)
+    h = grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
+    hq, sfh, _ = quantize_rows(h, nt, plan.src_of, identity=True, rows=plan.max_rows)
+    y = grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, ex.H, ex.F, ex.E, None)
+    return unpermute(y, plan, w, T, k, shared)

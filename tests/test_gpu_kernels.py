@@ -1,0 +1,190 @@
+"""CUDA kernels against plain PyTorch fp32 references of the same op (needs a B200)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from mary_b200.ops import reference as ref
+
+
+@pytest.fixture(scope="module")
+def K():
+    from mary_b200.ops import cuda
+    cuda.lib()
+    return cuda
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-9)).item()
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 512), (300, 520, 1096), (1024, 1024, 2048), (32, 3840, 4096), (1, 128, 64),
+                                     (64, 264, 7168), (257, 4104, 1536)])
+def test_gemm_bf16_vs_fp32(K, M, N, K_):
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K_, device="cuda").bfloat16()
+    w = (torch.randn(N, K_, device="cuda") * 0.05).bfloat16()
+    want = x.float() @ w.float().T
+    for swap in (0, 1):
+        got = K.gemm(x, w, swap=swap)
+        assert _rel(got, want) < 1e-2, (swap, _rel(got, want))
+        g32 = K.gemm(x, w, epi="f32", swap=swap)
+        assert _rel(g32, want) < 2e-5 * np.sqrt(K_), (swap, _rel(g32, want))
+    assert K.last_status() == 0
+
+
+def test_gemm_split_k_bias_alpha_and_strided_input(K):
+    torch.manual_seed(0)
+    xf = torch.randn(48, 2 * 2048, device="cuda").bfloat16()
+    x = xf[:, :2048]                                   # row pitch 4096, K 2048
+    w = (torch.randn(520, 2048, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(520, device="cuda")
+    want = x.float() @ w.float().T
+    for sk in (2, 4, 7):
+        got = K.gemm(x, w, epi="red", split_k=sk)
+        assert _rel(got, want) < 1e-4
+    got = K.gemm(x, w, bias=b, alpha=0.5, epi="f32")
+    assert _rel(got, 0.5 * want + b) < 1e-4
+    assert K.last_status() == 0
+
+
+@pytest.mark.parametrize("M,F,act", [(8, 256, "geglu"), (64, 1536, "swiglu"), (100, 520, "situ"), (1, 128, "swiglu")])
+def test_gemm_glu_epilogue(K, M, F, act):
+    torch.manual_seed(F)
+    x = torch.randn(M, 1024, device="cuda").bfloat16()
+    w = (torch.randn(2 * F, 1024, device="cuda") * 0.04).bfloat16()
+    h = x.float() @ w.float().T
+    want = {"geglu": ref.geglu, "swiglu": ref.swiglu, "situ": ref.situ}[act](h[:, :F], h[:, F:])
+    got = K.gemm(x, w, glu=act)
+    assert _rel(got, want) < 1.5e-2
+    assert K.last_status() == 0
+
+
+def test_norm_family(K):
+    torch.manual_seed(1)
+    T, H = 37, 3840
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    assert _rel(K.rmsnorm(x, w, 1e-6), ref.rmsnorm(x.float(), w.float(), 1e-6)) < 1e-2
+    assert _rel(K.rmsnorm(x.float(), None, 1e-6), ref.rmsnorm(x.float(), None, 1e-6)) < 1e-2
+    res = torch.randn(T, H, device="cuda").bfloat16()
+    y, r = K.add_rmsnorm(x, res.clone(), w, 1e-6)
+    wy, wr = ref.add_rmsnorm(x, res.clone(), w, 1e-6)
+    assert torch.equal(r, wr) and _rel(y, wy) < 1e-2
+    h = torch.randn(T, H, device="cuda").bfloat16()
+    w2 = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    for a in (x, x.float()):
+        xo, hn = K.norm_add_norm(a, w, h.clone(), w2, 1e-6, 0.5)
+        whn = ((h.float() + ref.rmsnorm(a.float(), w.float(), 1e-6)) * 0.5)
+        assert _rel(hn, whn) < 1e-2 and _rel(xo, ref.rmsnorm(whn, w2.float(), 1e-6)) < 2e-2
+    gu = torch.randn(T, 2 * 1024, device="cuda").bfloat16()
+    for act in ("geglu", "swiglu", "situ"):
+        F = 1024
+        want = {"geglu": ref.geglu, "swiglu": ref.swiglu, "situ": ref.situ}[act](gu[:, :F].float(), gu[:, F:].float())
+        assert _rel(K.glu(gu, act), want) < 1e-2
+    tab = torch.randn(1000, 256, device="cuda").bfloat16()
+    ids = torch.randint(0, 1000, (50,), device="cuda")
+    assert _rel(K.embed(ids, tab, 16.0), tab[ids].float() * 16.0) < 1e-2
+
+
+def _mk_cache(S_lens, q_lens, Hkv, D, dtype=torch.bfloat16):
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    pages = sum((l + 15) // 16 for l in S_lens) + 4
+    cache = PagedKVCache(1, pages, 16, Hkv, D, dtype=dtype, device="cuda")
+    # interleave allocation so that page lists are not contiguous
+    for rnd in range(max((l + 15) // 16 for l in S_lens)):
+        for s, l in enumerate(S_lens):
+            if rnd * 16 < l:
+                cache.alloc.extend(s, min(16, l - rnd * 16))
+    table, lens = cache.alloc.page_table(list(range(len(S_lens))))
+    return cache, BatchMeta.build(q_lens, lens, table, 16, "cuda")
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,window,softcap", [(16, 8, 256, 0, 0.0), (16, 8, 256, 64, 0.0), (32, 8, 128, 0, 30.0),
+                                                      (4, 1, 64, 24, 0.0), (8, 8, 128, 0, 0.0)])
+def test_paged_attention_decode_and_prefill(K, Hq, Hkv, D, window, softcap):
+    torch.manual_seed(D + Hq)
+    for S_lens, q_lens in (([300, 17, 129, 64], [1, 1, 1, 1]), ([40, 90, 33], [40, 7, 33]), ([200, 50], [3, 3])):
+        cache, meta = _mk_cache(S_lens, q_lens, Hkv, D)
+        cache.k[0].normal_()
+        cache.v[0].normal_()
+        q = torch.randn(sum(q_lens), Hq, D, device="cuda").bfloat16()
+        want = ref.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, window, softcap)
+        for nsplit in (None, 1, 3):
+            got = K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, window, softcap, nsplit=nsplit)
+            assert _rel(got, want) < 2e-2, (S_lens, nsplit, _rel(got, want))
+
+
+def test_qk_norm_rope_append_matches_reference(K):
+    from mary_b200 import ops
+    torch.manual_seed(3)
+    n_q, n_kv, D = 4, 2, 64
+    cache, meta = _mk_cache([50, 20], [50, 20], n_kv, D)
+    cpu_cache, cpu_meta = cache, meta
+    qkv = torch.randn(70, (n_q + 2 * n_kv) * D, device="cuda").bfloat16()
+    qn = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    kn = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    inv = ref.rope_inv_freq(D, 1e4, 1.0, "cuda")
+    q = K.qk_norm_rope_append(qkv, n_q, n_kv, D, qn, kn, True, inv, meta, cache.k[0], cache.v[0], 1e-6)
+    kc, vc = torch.zeros_like(cache.k[0]), torch.zeros_like(cache.v[0])
+    T = 70
+    qq, kk, vv = qkv.float().split([n_q * D, n_kv * D, n_kv * D], -1)
+    wq = ref.rope(ref.rmsnorm(qq.reshape(T, n_q, D), qn.float(), 1e-6), meta.positions, inv)
+    wk = ref.rope(ref.rmsnorm(kk.reshape(T, n_kv, D), kn.float(), 1e-6), meta.positions, inv)
+    wv = ref.rmsnorm(vv.reshape(T, n_kv, D), None, 1e-6)
+    assert _rel(q, wq) < 2e-2
+    flat_k = cache.k[0].view(-1, n_kv, D)[meta.slot_mapping]
+    flat_v = cache.v[0].view(-1, n_kv, D)[meta.slot_mapping]
+    assert _rel(flat_k, wk) < 2e-2 and _rel(flat_v, wv) < 2e-2
+
+
+def test_argmax_first_max_and_gumbel(K):
+    torch.manual_seed(5)
+    lg = torch.randn(9, 262144, device="cuda")
+    lg[0, 100] = 50.0
+    lg[0, 70000] = 50.0                                  # tie: the lower index must win
+    ids, val = K.argmax(lg, softcap=30.0)
+    assert ids.tolist() == ref.argmax_first(lg).tolist() and ids[0].item() == 100
+    assert torch.allclose(val, 30 * torch.tanh(lg.max(-1).values / 30), atol=1e-4)
+    # sampling: the empirical distribution over a 4-way logit set follows softmax(l / T)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]], device="cuda").repeat(4096, 1).contiguous()
+    cnt = torch.zeros(4)
+    for step in range(4):
+        s, _ = K.argmax(small, temperature=1.0, seed=7, step=step)
+        cnt += torch.bincount(s.cpu(), minlength=4).float()
+    p = cnt / cnt.sum()
+    assert (p - torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0)).abs().max() < 0.02
+    s1, _ = K.argmax(small, temperature=1.0, seed=7, step=0)
+    s2, _ = K.argmax(small, temperature=1.0, seed=7, step=0)
+    assert torch.equal(s1, s2)                           # seeded: reproducible
+
+
+@pytest.mark.parametrize("E,k", [(128, 8), (384, 8), (256, 6), (8, 2)])
+def test_router_topk_softmax_and_sigmoid_grouped(K, E, k):
+    torch.manual_seed(E)
+    T = 77
+    lg = torch.randn(T, E, device="cuda")
+    lg[3, 5] = lg[3, 2] = 4.0                            # tie
+    idx, w = K.router_topk(lg, k, "softmax")
+    ri, rw = ref.router_softmax_topk(lg, k)
+    assert torch.equal(idx, ri) and torch.allclose(w, rw, rtol=1e-4, atol=1e-6)
+    bias = torch.randn(E, device="cuda") * 0.1
+    idx, w = K.router_topk(lg, k, "sigmoid", bias=bias, scale=2.5)
+    ri, rw = ref.router_sigmoid_topk(lg, bias, k, scale=2.5)
+    assert torch.equal(idx, ri) and torch.allclose(w, rw, rtol=1e-4, atol=1e-6)
+    if E % 8 == 0 and E >= 64:
+        idx, w = K.router_topk(lg, k, "sigmoid", bias=bias, n_group=8, topk_group=4, scale=2.5)
+        ri, rw = ref.router_sigmoid_topk(lg, bias, k, n_group=8, topk_group=4, scale=2.5)
+        assert torch.equal(idx, ri) and torch.allclose(w, rw, rtol=1e-4, atol=1e-6)
+
+
+def test_short_conv(K):
+    torch.manual_seed(9)
+    x = torch.randn(19, 512, device="cuda").bfloat16()
+    w = torch.randn(512, 4, device="cuda") * 0.3
+    hist = torch.randn(3, 512, device="cuda").bfloat16()
+    y, h = K.short_conv(x, w, hist)
+    wy, wh = ref.short_conv(x, w, hist)
+    assert _rel(y, wy) < 1e-2 and torch.equal(h, wh)

@@ -1,0 +1,73 @@
+"""NVFP4 quantiser, grouped block-scaled GEMM and the MoE pipeline against fp32 references (needs a B200)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from mary_b200.ops import reference as ref
+from mary_b200.ops.moe import NVFP4Experts, experts_reference, swizzle_scales, unswizzle_scales
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-9)).item()
+
+
+def test_swizzle_roundtrip_cpu_twin():
+    sc = torch.randint(0, 255, (256, 28), dtype=torch.uint8)
+    assert torch.equal(unswizzle_scales(swizzle_scales(sc), 256, 28), sc)
+    from mary_b200.nn.fp4 import swizzle_scales_128x4
+    assert np.array_equal(swizzle_scales_128x4(sc.numpy()), swizzle_scales(sc).numpy())
+
+
+def test_activation_quantiser_is_bit_exact():
+    from mary_b200.ops import cuda_moe
+    torch.manual_seed(0)
+    x = (torch.randn(67, 1024, device="cuda") * 3).bfloat16()
+    x[0, :16] = 0
+    x[1, :16] = 3e4
+    x[2, 0] = -1e-30
+    # exact ties on the code thresholds: block scale 1.0 (amax 6) with values .25 .75 1.25 1.75 2.5 3.5 5
+    x[3, :16] = torch.tensor([6, .25, .75, 1.25, 1.75, 2.5, 3.5, 5, -.25, -.75, -1.25, -1.75, -2.5, -3.5, -5, 0.0]).bfloat16()
+    codes, sf, rm = cuda_moe.quantize_rows(x, nt=128, rowmajor=True)
+    wc, ws = ref.quantize_nvfp4(x.cpu())
+    assert torch.equal(codes.cpu(), wc) and torch.equal(rm.cpu(), ws)
+    assert torch.equal(unswizzle_scales(sf.cpu(), 67, 64), ws)
+    assert codes[3, :8].tolist() == [0x17, 0x32, 0x54, 0x76, 0xA9, 0xCB, 0xED, 0x0F]
+
+
+@pytest.mark.parametrize("E,H,F,T,k,nt", [(4, 512, 256, 24, 2, 32), (16, 1024, 512, 200, 4, 32), (8, 512, 256, 700, 2, 128),
+                                          (8, 1024, 256, 3, 2, 32)])
+def test_moe_pipeline_matches_oracle(E, H, F, T, k, nt):
+    from mary_b200.ops import cuda, cuda_moe
+    torch.manual_seed(E + T)
+    ex = NVFP4Experts.random(E, H, F, "cuda", std=0.05, seed=1)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    lg = torch.randn(T, E, device="cuda")
+    idx, w = cuda.router_topk(lg, k, "softmax")
+    got = cuda_moe.experts_forward(x, idx, w, ex, None, nt)
+    want = experts_reference(x, idx, w, ex)
+    assert cuda.last_status() == 0
+    assert _rel(got.cpu(), want) < 3e-2, _rel(got.cpu(), want)
+
+
+def test_grouped_gemm_is_exact_on_its_quantised_operands():
+    """f64 arbiter over the SAME quantised operands: the block-scaled MMA must reproduce it to f32 accuracy."""
+    from mary_b200.ops import cuda, cuda_moe
+    torch.manual_seed(3)
+    E, H, F, T = 3, 512, 256, 40
+    ex = NVFP4Experts.random(E, H, F, "cuda", std=0.05, seed=2)
+    idx = torch.randint(0, E, (T, 1), device="cuda", dtype=torch.int32)
+    plan = cuda_moe.moe_plan(idx, E, 32)
+    # plain (non-GLU) GEMM over w2-shaped operands: K = F on a quantised [T, F] input
+    h = torch.randn(T, F, device="cuda").bfloat16()
+    hq, sfh, hrm = cuda_moe.quantize_rows(h, 32, plan.src_of, identity=False, rows=plan.max_rows, rowmajor=True)
+    y = cuda_moe.grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, H, F, E, None)
+    assert cuda.last_status() == 0
+    row_of = plan.row_of.cpu()
+    for t in range(T):
+        r = int(row_of[t])
+        e = int(idx[t, 0])
+        a = ref.dequantize_nvfp4(hq[r:r + 1].cpu(), hrm[r:r + 1].cpu()).double()
+        want = (a @ ex.dense("w2", e).double().T).float()
+        assert _rel(y[r:r + 1].cpu(), want) < 1e-2      # bf16 output rounding only
