@@ -39,6 +39,8 @@ struct GemmParams {
   int epi;
   int swap;                  // 1: row operand = weights, D[i][j] -> out[j * ldo + i]
   int64_t ldo;
+  int batch;                 // independent problems (z coordinate of both tensor maps)
+  int64_t out_batch_stride;  // elements
   void* out;
   const float* bias;         // optional, indexed by output feature
   float alpha;
@@ -95,13 +97,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.tiles_r * p.tiles_c * p.split_k;
+  const int per_batch = p.tiles_r * p.tiles_c * p.split_k;
+  const int total_tiles = per_batch * p.batch;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       int stage = 0; uint32_t phase = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      for (int tt = blockIdx.x; tt < total_tiles; tt += gridDim.x) {
+        const int bz = tt / per_batch, t = tt % per_batch;
         const int tc = t % p.tiles_c, ks = (t / p.tiles_c) % p.split_k, tr = t / (p.tiles_c * p.split_k);
         const int kb0 = ks * p.k_blocks_per_split;
         const int kb1 = min(kb0 + p.k_blocks_per_split, p.k_blocks);
@@ -109,9 +113,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
           uint8_t* st = smem + stage * C::STAGE_BYTES;
           mbar_expect_tx(&full[stage], C::STAGE_BYTES);
-          tma_load_2d(st, &tm_r, &full[stage], kb * BK, tr * BM);
-          if (GLU) tma_load_2d(st + C::A_BYTES, &tm_r, &full[stage], kb * BK, p.glu_offset + tr * BM);
-          tma_load_2d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN);
+          tma_load_3d(st, &tm_r, &full[stage], kb * BK, tr * BM, bz);
+          if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[stage], kb * BK, p.glu_offset + tr * BM, bz);
+          tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, bz);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -122,7 +126,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       const uint32_t idesc = idesc_bf16(BM, BN);
       int stage = 0; uint32_t phase = 0;
       int it = 0;
-      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      for (int tt = blockIdx.x; tt < total_tiles; tt += gridDim.x, ++it) {
+        const int t = tt % per_batch;
         const int ks = (t / p.tiles_c) % p.split_k;
         const int kb0 = ks * p.k_blocks_per_split;
         const int kb1 = min(kb0 + p.k_blocks_per_split, p.k_blocks);
@@ -153,8 +158,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                // TMEM lane quarter this warp may access
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int tt = blockIdx.x; tt < total_tiles; tt += gridDim.x, ++it) {
+      const int bz = tt / per_batch, t = tt % per_batch;
       const int tc = t % p.tiles_c, tr = t / (p.tiles_c * p.split_k);
+      const int64_t obase = (int64_t)bz * p.out_batch_stride;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
@@ -181,7 +188,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               if (j0 + j < p.rows_c) {
-                const int64_t o = (int64_t)(j0 + j) * p.ldo + i;
+                const int64_t o = obase + (int64_t)(j0 + j) * p.ldo + i;
                 if (p.epi == EPI_STORE_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16(v[j] + b);
                 else if (p.epi == EPI_STORE_F32) ((float*)p.out)[o] = v[j] + b;
                 else atomicAdd((float*)p.out + o, v[j]);
@@ -191,7 +198,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
         } else {
           // i = token, j = output feature: out[i * ldo + j]; each thread writes 32 consecutive features
           if (i < p.rows_r) {
-            const int64_t o = (int64_t)i * p.ldo + j0;
+            const int64_t o = obase + (int64_t)i * p.ldo + j0;
             if (p.epi == EPI_STORE_BF16) {
               __nv_bfloat16* dst = (__nv_bfloat16*)p.out + o;
               if (j0 + 32 <= p.rows_c && ((uintptr_t)dst & 15) == 0) {
@@ -239,7 +246,7 @@ int launch(const CUtensorMap& tr, const CUtensorMap& tc, const GemmParams& p, cu
       return MARY_ERR_CUDA;
     attr_set = true;
   }
-  int total = p.tiles_r * p.tiles_c * p.split_k;
+  int total = p.tiles_r * p.tiles_c * p.split_k * p.batch;
   int grid = total < mary_num_sms() ? total : mary_num_sms();
   gemm_bf16_kernel<BN, GLU><<<grid, NTHREADS, C::SMEM, stream>>>(tr, tc, p);
   MARY_CHECK_LAUNCH();
@@ -253,10 +260,27 @@ int launch(const CUtensorMap& tr, const CUtensorMap& tc, const GemmParams& p, cu
 //   epi: 0 store bf16, 1 atomically add f32 into `out` (caller zeroes it; required when split_k > 1), 2 store f32.
 //   swap: -1 = choose automatically, 0 = activations are the row operand, 1 = weights are the row operand.
 // Leading dimensions are in elements; all of ldx, ldw must be multiples of 8 and the bases 16-byte aligned.
-MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
-                            int64_t ldo, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
-                            cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7)) return MARY_ERR_BAD_ARG;
+static int make_tmap_3d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint64_t batch,
+                        uint64_t batch_stride, uint32_t box_rows) {
+  PFN_encodeTiled enc = mary_encode_fn();
+  if (!enc) return MARY_ERR_CUDA;
+  if (batch <= 1) { batch = 1; batch_stride = rows * ld; if (batch_stride & 7) batch_stride = (batch_stride + 7) & ~7ull; }
+  cuuint64_t dims[3] = {cols, rows, batch};
+  cuuint64_t strides[2] = {ld * 2, batch_stride * 2};
+  cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (((uintptr_t)base & 15) || (strides[0] & 15) || (strides[1] & 15)) return MARY_ERR_BAD_ARG;
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MARY_OK : MARY_ERR_CUDA;
+}
+
+// Batched form: `batch` independent problems; operand b starts at base + b * batch_stride (elements).
+MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
+                                    int64_t ldo, int batch, int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha,
+                                    int glu, int epi, int split_k, int swap, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || batch < 1) return MARY_ERR_BAD_ARG;
   if (split_k < 1) split_k = 1;
   if (split_k > 1 && epi != EPI_RED_F32) return MARY_ERR_BAD_ARG;
   if (glu && epi == EPI_RED_F32) return MARY_ERR_BAD_ARG;
@@ -274,12 +298,15 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
   p.epi = epi;
   p.swap = use_swap ? 1 : 0;
   p.ldo = ldo;
+  p.batch = batch;
+  p.out_batch_stride = bso;
   p.out = out;
   p.bias = bias;
   p.alpha = alpha;
   p.status = mary_status_ptr();
   const void *R = use_swap ? W : X, *Cc = use_swap ? X : W;
   const int64_t ldr = use_swap ? ldw : ldx, ldc = use_swap ? ldx : ldw;
+  const int64_t bsr = use_swap ? bsw : bsx, bsc = use_swap ? bsx : bsw;
   p.rows_r = use_swap ? N : M;
   p.rows_c = use_swap ? M : N;
   const int rows_r_total = use_swap ? (glu ? 2 * N : N) : M;
@@ -289,9 +316,9 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
   p.tiles_r = (p.rows_r + BM - 1) / BM;
   p.tiles_c = (p.rows_c + bn - 1) / bn;
   CUtensorMap tr, tc;
-  int rc = mary_make_tmap_2d(&tr, R, 4, rows_r_total, K, ldr, BM, BK, 1);
+  int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, batch, bsr, BM);
   if (rc) return rc;
-  rc = mary_make_tmap_2d(&tc, Cc, 4, p.rows_c, K, ldc, bn, BK, 1);
+  rc = make_tmap_3d(&tc, Cc, p.rows_c, K, ldc, batch, bsc, bn);
   if (rc) return rc;
   if (glu) {
     switch (bn) {
@@ -306,4 +333,10 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
     case 128: return launch<128, false>(tr, tc, p, stream);
     default: return launch<256, false>(tr, tc, p, stream);
   }
+}
+
+MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
+                            int64_t ldo, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
+                            cudaStream_t stream) {
+  return mary_gemm_bf16_batched(X, W, out, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, bias, alpha, glu, epi, split_k, swap, stream);
 }

@@ -1,0 +1,99 @@
+// Small row kernels around multi-head latent attention (MLA):
+//   mla_prep:   from the fused projection row [q_a (q_lora) | c_kv (512) | k_rope (64)]:
+//               q_a -> RMSNorm (learned gain) -> qa_out;  c_kv -> RMSNorm (learned gain) and k_rope -> split-half RoPE,
+//               both written to the latent cache slot of the row ([c_kv_normed (512) | k_rope (64)]).
+//   mla_q_rope: RoPE on the 64-dim rope part of every query head, written behind the absorbed 512 latent dims of
+//               q_full[T, H, 576].
+// Math of the reference MLA: src/models/k3/mla.rs:49-63,102-111 (eps 1e-6 inside MLA; the reference runs NoPE and an
+// expanded cache — `inv_freq == nullptr` gives NoPE here, the latent cache is this build's).
+#include "common.cuh"
+#include "host_utils.h"
+
+using namespace mary;
+
+namespace {
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+__global__ void mla_prep_kernel(const __nv_bfloat16* __restrict__ qakv, int64_t ld, int q_lora, const __nv_bfloat16* __restrict__ w_qa,
+                                const __nv_bfloat16* __restrict__ w_kv, const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                const int64_t* __restrict__ slots, __nv_bfloat16* __restrict__ qa_out, __nv_bfloat16* __restrict__ cache,
+                                float eps) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const __nv_bfloat16* row = qakv + (int64_t)t * ld;
+  // q_a norm
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < q_lora; i += blockDim.x) { float v = __bfloat162float(row[i]); ss += v * v; }
+  const float inv_q = rsqrtf(block_sum_256(ss, red) / q_lora + eps);
+  for (int i = threadIdx.x; i < q_lora; i += blockDim.x)
+    qa_out[(int64_t)t * q_lora + i] = __float2bfloat16(__bfloat162float(row[i]) * inv_q * __bfloat162float(w_qa[i]));
+  // latent norm
+  const __nv_bfloat16* ckv = row + q_lora;
+  ss = 0.f;
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) { float v = __bfloat162float(ckv[i]); ss += v * v; }
+  const float inv_k = rsqrtf(block_sum_256(ss, red) / 512 + eps);
+  __nv_bfloat16* dst = cache + slots[t] * 576;
+  for (int i = threadIdx.x; i < 512; i += blockDim.x)
+    dst[i] = __float2bfloat16(__bfloat162float(ckv[i]) * inv_k * __bfloat162float(w_kv[i]));
+  // rope on the 64 carried dims (split-half pairs (i, i + 32))
+  if (threadIdx.x < 32) {
+    const int i = threadIdx.x;
+    float a = __bfloat162float(ckv[512 + i]), b = __bfloat162float(ckv[512 + 32 + i]);
+    if (inv_freq) {
+      float s, c;
+      sincosf((float)positions[t] * inv_freq[i], &s, &c);
+      const float ra = a * c - b * s, rb = a * s + b * c;
+      a = ra; b = rb;
+    }
+    dst[512 + i] = __float2bfloat16(a);
+    dst[512 + 32 + i] = __float2bfloat16(b);
+  }
+}
+
+// qb [T, H, 192] = [nope 128 | rope 64] per head -> q_full[T, H, 512 + i] for the rope part
+__global__ void mla_q_rope_kernel(const __nv_bfloat16* __restrict__ qb, const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                  __nv_bfloat16* __restrict__ q_full, int H, int T) {
+  const int64_t gw = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= (int64_t)T * H) return;
+  const int t = (int)(gw / H), i = threadIdx.x & 31;
+  const __nv_bfloat16* src = qb + gw * 192 + 128;
+  float a = __bfloat162float(src[i]), b = __bfloat162float(src[32 + i]);
+  if (inv_freq) {
+    float s, c;
+    sincosf((float)positions[t] * inv_freq[i], &s, &c);
+    const float ra = a * c - b * s, rb = a * s + b * c;
+    a = ra; b = rb;
+  }
+  __nv_bfloat16* dst = q_full + gw * 576 + 512;
+  dst[i] = __float2bfloat16(a);
+  dst[32 + i] = __float2bfloat16(b);
+}
+
+}  // namespace
+
+MARY_API int mary_mla_prep(const void* qakv, int64_t ld, int q_lora, const void* w_qa, const void* w_kv, const float* inv_freq,
+                           const int* positions, const int64_t* slots, void* qa_out, void* cache, float eps, int T, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  mla_prep_kernel<<<T, 256, 0, s>>>((const __nv_bfloat16*)qakv, ld, q_lora, (const __nv_bfloat16*)w_qa, (const __nv_bfloat16*)w_kv, inv_freq,
+                                    positions, slots, (__nv_bfloat16*)qa_out, (__nv_bfloat16*)cache, eps);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_mla_q_rope(const void* qb, const float* inv_freq, const int* positions, void* q_full, int H, int T, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  const int64_t warps = (int64_t)T * H;
+  mla_q_rope_kernel<<<(int)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)qb, inv_freq, positions, (__nv_bfloat16*)q_full, H, T);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}

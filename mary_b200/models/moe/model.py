@@ -1,0 +1,252 @@
+"""Sparse-MoE decoder (GQA or MLA attention, NVFP4 routed experts, shared expert, MTP draft layers) over the
+flattened ragged batch and the paged cache.
+
+Layer: ``h += attn(rms(h)); h += ffn(rms(h))``.  Routed experts live in :class:`NVFP4Experts`; attention, router,
+shared expert, dense FFN and head are bf16.  Parallel layout (``par``): attention heads and dense/shared FFN columns are
+sharded over the group (tensor parallel), routed experts are sharded by expert index (expert parallel); both produce
+partial sums of the hidden state that one reduction per block combines."""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+from ... import ops
+from ...ops import reference as ref
+from ...ops.moe import NVFP4Experts, experts_forward
+from .config import MoEConfig
+
+
+class NoParallel:
+    rank, size = 0, 1
+
+    def reduce(self, partial, residual=None):
+        """Sum the partial hidden states over the group.  Returns a tensor every rank holds."""
+        return partial
+
+    def row_linear(self, x, w):
+        return ops.linear(x, w)
+
+
+def _P(*shape, dtype, device):
+    return nn.Parameter(torch.empty(*shape, dtype=dtype, device=device), requires_grad=False)
+
+
+class GQAAttention(nn.Module):
+    def __init__(self, c: MoEConfig, layer_idx: int, par, dtype, device):
+        super().__init__()
+        self.c, self.li, self.par = c, layer_idx, par
+        self.n_q = c.num_attention_heads // par.size
+        self.n_kv = max(c.num_key_value_heads // par.size, 1)
+        D = c.head_dim
+        self.w_qkv = _P((self.n_q + 2 * self.n_kv) * D, c.hidden_size, dtype=dtype, device=device)
+        self.w_o = _P(c.hidden_size, self.n_q * D, dtype=dtype, device=device)
+        self.register_buffer("inv_freq", ref.rope_inv_freq(D, c.rope_theta, 1.0, device), persistent=False)
+
+    def forward(self, x, meta, cache):
+        c = self.c
+        qkv = ops.linear(x, self.w_qkv)
+        q = ops.qk_norm_rope_append(qkv, self.n_q, self.n_kv, c.head_dim, None, None, False, self.inv_freq, meta,
+                                    cache.k[self.li], cache.v[self.li], c.rms_norm_eps)
+        o = ops.paged_attention(q, cache.k[self.li], cache.v[self.li], meta, c.attn_scale)
+        return self.par.row_linear(o.reshape(o.shape[0], -1), self.w_o)
+
+
+class MLAAttention(nn.Module):
+    """Latent attention with absorbed W_UK / W_UV and a latent cache row ``[c_kv (512) | k_rope (64)]``."""
+
+    def __init__(self, c: MoEConfig, layer_idx: int, par, dtype, device):
+        super().__init__()
+        assert c.kv_lora_rank == 512 and c.qk_rope_head_dim == 64 and c.qk_nope_head_dim == 128 and c.v_head_dim == 128
+        self.c, self.li, self.par = c, layer_idx, par
+        self.H = c.num_attention_heads // par.size
+        kw = dict(dtype=dtype, device=device)
+        self.w_qa_kva = _P(c.q_lora_rank + 576, c.hidden_size, **kw)       # replicated
+        self.qa_norm = _P(c.q_lora_rank, **kw)
+        self.kv_norm = _P(512, **kw)
+        self.w_qb = _P(self.H * 192, c.q_lora_rank, **kw)                  # heads sharded
+        self.w_uk = _P(self.H, 512, 128, **kw)                             # q_lat = W_UK q_nope
+        self.w_uv = _P(self.H, 128, 512, **kw)                             # o = W_UV o_lat
+        self.w_o = _P(c.hidden_size, self.H * 128, **kw)
+        inv = None if c.use_nope else ref.rope_inv_freq(64, c.rope_theta, 1.0, device)
+        self.register_buffer("inv_freq", inv, persistent=False)
+
+    def forward(self, x, meta, cache):
+        c = self.c
+        qakv = ops.linear(x, self.w_qa_kva)
+        qa = ops.mla_prep(qakv, c.q_lora_rank, self.qa_norm, self.kv_norm, self.inv_freq, meta, cache.k[self.li], 1e-6)
+        qb = ops.linear(qa, self.w_qb)
+        q_full = ops.mla_absorb_q(qb, self.w_uk, self.inv_freq, meta, self.H)
+        o_lat = ops.mla_attention(q_full, cache.k[self.li], meta, c.attn_scale)
+        o = ops.mla_unabsorb_o(o_lat, self.w_uv, self.H)
+        return self.par.row_linear(o, self.w_o)
+
+
+class DenseFFN(nn.Module):
+    def __init__(self, H, F, par, act, dtype, device):
+        super().__init__()
+        self.par, self.act = par, act
+        Fl = F // par.size
+        self.w_gu = _P(2 * Fl, H, dtype=dtype, device=device)
+        self.w_down = _P(H, Fl, dtype=dtype, device=device)
+
+    def forward(self, x):
+        return self.par.row_linear(ops.linear_glu(x, self.w_gu, self.act), self.w_down)
+
+
+class MoEFFN(nn.Module):
+    def __init__(self, c: MoEConfig, par, dtype, device):
+        super().__init__()
+        self.c, self.par = c, par
+        E = c.n_routed_experts
+        self.e_local = E // par.size
+        self.e0 = par.rank * self.e_local
+        self.w_router = _P(E, c.hidden_size, dtype=dtype, device=device)
+        self.router_bias = nn.Parameter(torch.zeros(E, dtype=torch.float32, device=device), requires_grad=False) \
+            if c.router == "sigmoid" else None
+        self.shared = DenseFFN(c.hidden_size, c.moe_intermediate_size * c.n_shared_experts, par, c.act, dtype, device) \
+            if c.n_shared_experts else None
+        self.experts: NVFP4Experts | None = None        # set by the loader / random init
+
+    def route(self, x):
+        c = self.c
+        logits = ops.linear_f32(x, self.w_router)
+        return ops.router_topk(logits, c.num_experts_per_tok, c.router, self.router_bias, c.n_group, c.topk_group,
+                               c.routed_scaling_factor, c.norm_topk_prob)
+
+    def forward(self, x):
+        idx, w = self.route(x)
+        if self.par.size > 1:                 # keep the entries of the local experts, renumbered from zero
+            local = (idx >= self.e0) & (idx < self.e0 + self.e_local)
+            idx = torch.where(local, idx - self.e0, torch.full_like(idx, -1))
+        # the shared expert's partial sum rides along in the un-permute (one pass over the hidden state)
+        shared = ops.linear(ops.linear_glu(x, self.shared.w_gu, self.c.act), self.shared.w_down) if self.shared is not None else None
+        return experts_forward(x, idx, w, self.experts, shared)
+
+
+class MoELayer(nn.Module):
+    def __init__(self, c: MoEConfig, i: int, par, dtype, device, cache_index: int | None = None):
+        super().__init__()
+        self.c, self.par = c, par
+        li = i if cache_index is None else cache_index
+        self.attn = (MLAAttention if c.attention == "mla" else GQAAttention)(c, li, par, dtype, device)
+        self.dense = c.is_dense(i) and cache_index is None
+        self.ffn = DenseFFN(c.hidden_size, c.dense_intermediate_size, par, c.act, dtype, device) if self.dense \
+            else MoEFFN(c, par, dtype, device)
+        self.ln_attn = _P(c.hidden_size, dtype=dtype, device=device)
+        self.ln_ffn = _P(c.hidden_size, dtype=dtype, device=device)
+
+    def forward(self, x, h, meta, cache, next_norm):
+        """``x`` normed input, ``h`` residual.  Returns ``(next normed x, h)``."""
+        a = self.par.reduce(self.attn(x, meta, cache))
+        x, h = ops.add_rmsnorm(a, h, self.ln_ffn, self.c.rms_norm_eps)
+        f = self.par.reduce(self.ffn(x))
+        if next_norm is None:
+            return None, (h.float() + f.float()).to(h.dtype)
+        return ops.add_rmsnorm(f, h, next_norm, self.c.rms_norm_eps)
+
+
+class MTPLayer(nn.Module):
+    """Multi-token-prediction draft layer: ``x = proj([rms(h_prev) ; rms(embed(next token))])`` (hidden first, as in
+    src/models/inkling/mtp.rs:108-244), one decoder block with its own cache rows, then the shared head."""
+
+    def __init__(self, c: MoEConfig, d: int, par, dtype, device):
+        super().__init__()
+        self.c = c
+        H = c.hidden_size
+        self.h_norm = _P(H, dtype=dtype, device=device)
+        self.e_norm = _P(H, dtype=dtype, device=device)
+        self.proj = _P(H, 2 * H, dtype=dtype, device=device)
+        self.block = MoELayer(c, c.num_hidden_layers + d, par, dtype, device, cache_index=c.num_hidden_layers + d)
+        self.out_norm = _P(H, dtype=dtype, device=device)
+
+    def forward(self, h_prev, tok_emb, meta, cache):
+        c = self.c
+        x = torch.cat([ops.rmsnorm(h_prev, self.h_norm, c.rms_norm_eps), ops.rmsnorm(tok_emb, self.e_norm, c.rms_norm_eps)], -1)
+        h = ops.linear(x, self.proj)
+        x = ops.rmsnorm(h, self.block.ln_attn, c.rms_norm_eps)
+        _, h = self.block(x, h, meta, cache, None)
+        return h
+
+
+class MoEDecoder(nn.Module):
+    def __init__(self, c: MoEConfig, par=None, dtype=torch.bfloat16, device="cpu"):
+        super().__init__()
+        self.cfg, self.par, self.dtype = c, par or NoParallel(), dtype
+        kw = dict(dtype=dtype, device=device)
+        self.embed = _P(c.vocab_size, c.hidden_size, **kw)
+        self.layers = nn.ModuleList([MoELayer(c, i, self.par, dtype, device) for i in range(c.num_hidden_layers)])
+        self.norm = _P(c.hidden_size, **kw)
+        self.lm_head = None if c.tie_word_embeddings else _P(c.vocab_size, c.hidden_size, **kw)
+        self.mtp = nn.ModuleList([MTPLayer(c, d, self.par, dtype, device) for d in range(c.num_mtp_layers)])
+
+    def kv_spec(self):
+        c = self.cfg
+        n = c.num_hidden_layers + c.num_mtp_layers
+        if c.attention == "mla":
+            return dict(num_layers=n, kv_heads=1, head_dim=576, latent_dim=576)
+        return dict(num_layers=n, kv_heads=max(c.num_key_value_heads // self.par.size, 1), head_dim=c.head_dim)
+
+    def head_weight(self):
+        return self.embed if self.lm_head is None else self.lm_head
+
+    def trunk(self, ids, meta, cache):
+        """Residual stream after the last layer (before the final norm), every row."""
+        c = self.cfg
+        h = ops.embed(ids, self.embed)
+        x = ops.rmsnorm(h, self.layers[0].ln_attn, c.rms_norm_eps)
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            nxt = self.layers[i + 1].ln_attn if i + 1 < n else None
+            x, h = layer(x, h, meta, cache, nxt)
+        return h
+
+    def hidden(self, ids, meta, cache):
+        return ops.rmsnorm(self.trunk(ids, meta, cache), self.norm, self.cfg.rms_norm_eps)
+
+    def forward(self, ids, meta, cache, rows=None):
+        x = self.hidden(ids, meta, cache)
+        if rows is not None:
+            x = x[rows]
+        return ops.linear(x, self.head_weight()).float()
+
+    def greedy(self, ids, meta, cache, rows):
+        x = self.hidden(ids, meta, cache)[rows]
+        tok, _ = ops.lm_head_argmax(x, self.head_weight())
+        return tok
+
+    # -- speculative decoding -------------------------------------------------
+    def verify(self, ids, meta, cache):
+        """One forward over the fed rows.  Returns ``(arg-max token of every row, trunk hidden of every row)``."""
+        h = self.trunk(ids, meta, cache)
+        x = ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
+        tok, _ = ops.lm_head_argmax(x, self.head_weight())
+        return tok, h
+
+    def draft(self, d: int, h_prev, next_ids, meta, cache):
+        """Draft head ``d``: hidden of the rows + the token that follows each row -> ``(draft token, its hidden)``."""
+        emb = ops.embed(next_ids, self.embed)
+        h = self.mtp[min(d, len(self.mtp) - 1)](h_prev, emb, meta, cache)
+        x = ops.rmsnorm(h, self.mtp[min(d, len(self.mtp) - 1)].out_norm, self.cfg.rms_norm_eps)
+        tok, _ = ops.lm_head_argmax(x, self.head_weight())
+        return tok, h
+
+
+def init_random_(model: MoEDecoder, seed: int = 0, std: float = 0.02, expert_slabs: int | None = None) -> None:
+    """Random-init in place on the model's device: ``normal(0, std)`` matrices, unit gains, NVFP4 experts quantised from
+    ``normal(0, std)``.  ``expert_slabs`` < number of MoE layers makes layers share physical expert storage cyclically
+    (a memory-fitting device for benchmarks on fewer GPUs than the model needs; every layer still streams a full slab)."""
+    c = model.cfg
+    dev = model.embed.device
+    g = torch.Generator(device=dev).manual_seed(seed)
+    for n, p in model.named_parameters():
+        if p.dim() == 1:
+            p.data.fill_(0.0 if "router_bias" in n else 1.0)
+        else:
+            p.data.normal_(0.0, std, generator=g)
+    moes = [m for m in model.modules() if isinstance(m, MoEFFN)]
+    slabs: list[NVFP4Experts] = []
+    n_slabs = len(moes) if expert_slabs is None else max(1, min(expert_slabs, len(moes)))
+    for i, m in enumerate(moes):
+        if i < n_slabs:
+            slabs.append(NVFP4Experts.random(m.e_local, c.hidden_size, c.moe_intermediate_size, dev, std, seed + 1 + i, c.act))
+        m.experts = slabs[i % n_slabs]

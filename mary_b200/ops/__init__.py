@@ -39,6 +39,13 @@ def linear(x, w, bias=None):
     return _k().linear(x, w, bias) if _cuda(x) else ref.linear(x, w, bias)
 
 
+def linear_f32(x, w):
+    """``x @ w^T`` with an f32 result (router logits, row-parallel partial sums)."""
+    if _cuda(x):
+        return _k().linear_f32(x, w)
+    return ref.linear(x.float(), w.float())
+
+
 def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm: bool, inv_freq, meta, kcache, vcache, eps):
     """Split ``qkv[T, (n_q+2 n_kv) D]``; per-head RMSNorm on q and k (learned gains) and optionally a weightless
     norm on v; split-half RoPE on q and k at ``meta.positions``; append k, v to the paged cache.
@@ -64,6 +71,45 @@ def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0):
     if _cuda(q):
         return _k().paged_attention(q, kcache, vcache, meta, scale, window, softcap)
     return ref.paged_attention(q, kcache, vcache, meta, scale, window, softcap)
+
+
+def mla_attention(q, cache, meta, scale):
+    """Latent attention: ``q[T, Hq, 576]`` against the latent cache ``[pages, page, 576]`` (keys = all 576 dims,
+    values = the first 512).  Returns ``[T, Hq, 512]``."""
+    if _cuda(q):
+        return _k().mla_attention(q, cache, meta, scale)
+    return ref.paged_attention(q, cache, cache, meta, scale, dv=512)
+
+
+def mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps):
+    """Norm the q_a part, norm the latent, rotate the carried rope dims and append ``[c_kv | k_rope]`` to the cache."""
+    if _cuda(qakv):
+        return _k().mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps)
+    qa = ref.rmsnorm(qakv[:, :q_lora], w_qa, eps)
+    ckv = ref.rmsnorm(qakv[:, q_lora:q_lora + 512], w_kv, eps)
+    kr = qakv[:, q_lora + 512:q_lora + 576]
+    if inv_freq is not None:
+        kr = ref.rope(kr[:, None, :], meta.positions, inv_freq)[:, 0]
+    cache.view(-1, 576)[meta.slot_mapping] = torch.cat([ckv, kr], -1).to(cache.dtype)
+    return qa
+
+
+def mla_absorb_q(qb, w_uk, inv_freq, meta, H):
+    if _cuda(qb):
+        return _k().mla_absorb_q(qb, w_uk, inv_freq, meta, H)
+    T = qb.shape[0]
+    q = qb.view(T, H, 192)
+    lat = torch.einsum("thd,hnd->thn", q[..., :128].float(), w_uk.float()).to(qb.dtype)
+    qr = q[..., 128:]
+    if inv_freq is not None:
+        qr = ref.rope(qr, meta.positions, inv_freq)
+    return torch.cat([lat, qr], -1)
+
+
+def mla_unabsorb_o(o_lat, w_uv, H):
+    if _cuda(o_lat):
+        return _k().mla_unabsorb_o(o_lat, w_uv, H)
+    return torch.einsum("thk,hnk->thn", o_lat.float(), w_uv.float()).to(o_lat.dtype).reshape(o_lat.shape[0], H * 128)
 
 
 def glu(gate_up, act: str = "geglu"):

@@ -75,7 +75,12 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = 0      # launcher calls made through this module (each starts at least one kernel)
+
+
 def check(rc: int, what: str):
+    global LAUNCHES
+    LAUNCHES += 1
     if rc != 0:
         raise KernelError(f"{what}: {_STATUS.get(rc, rc)}")
 
@@ -293,3 +298,81 @@ def router_topk(logits, k, mode="softmax", bias=None, n_group=1, topk_group=1, s
 def quantize_nvfp4(x):
     from . import cuda_moe
     return cuda_moe.quantize_nvfp4(x)
+
+
+# --------------------------------------------------------------------------- MLA
+declare("mary_mla_attention", "pppppppp" + "iiii" + "ll" + "ii" + "f" + "ps")
+declare("mary_mla_scratch_floats", "ii", ret64=True)
+
+
+def _row_tiles(meta, hq: int):
+    key = ("rowtiles", hq)
+    cache = meta.__dict__.setdefault("_cache", {})
+    if key not in cache:
+        seqs, r0 = [], []
+        start = 0
+        for s, n in enumerate(meta.q_lens_host.tolist()):
+            rows = n * hq
+            for b in range(0, rows, 128):
+                seqs.append(s)
+                r0.append(start * hq + b)
+            start += n
+        dev = meta.positions.device
+        cache[key] = (torch.tensor(seqs, dtype=torch.int32).to(dev, non_blocking=True),
+                      torch.tensor(r0, dtype=torch.int32).to(dev, non_blocking=True), len(seqs))
+    return cache[key]
+
+
+def mla_attention(q, cache, meta, scale, nsplit: int | None = None):
+    """``q[T, Hq, 576]`` bf16, ``cache[pages, 16, 576]`` bf16 (finite everywhere) -> ``[T, Hq, 512]``."""
+    T, Hq, DK = q.shape
+    assert DK == 576 and cache.shape[1] == 16 and cache.shape[-1] == 576 and meta.page_size == 16
+    blk_seq, blk_r0, NB = _row_tiles(meta, Hq)
+    if nsplit is None:
+        nsplit = max(1, min(8, 148 // max(1, 2 * NB), meta.max_kv_len // 512))
+    out = torch.empty(T, Hq, 512, dtype=torch.bfloat16, device=q.device)
+    scratch = None
+    if nsplit > 1:
+        scratch = torch.empty(lib().mary_mla_scratch_floats(NB, nsplit), dtype=torch.float32, device=q.device)
+    c = cache.view(cache.shape[0], 16, 576)
+    check(lib().mary_mla_attention(_p(q.contiguous()), _p(c), _p(out), _p(meta.page_table), _p(meta.kv_len), _p(meta.q_start),
+                                   _p(blk_seq), _p(blk_r0), NB, T * Hq, c.shape[0], meta.page_table.shape[1], c.stride(1),
+                                   c.stride(0), Hq, nsplit, scale, _p(scratch), _stream()), "mla_attention")
+    return out
+
+
+declare("mary_mla_prep", "plippppppp" + "fis")
+declare("mary_mla_q_rope", "ppppiis")
+declare("mary_gemm_bf16_batched", "pppiiilll" + "illl" + "pfiiiis")
+
+
+def gemm_batched(x, w, out, M, N, K, ldx, ldw, ldo, batch, bsx, bsw, bso):
+    """``batch`` independent bf16 GEMMs ``out_b[M, N] = x_b[M, K] @ w_b[N, K]^T`` over strided views (element strides)."""
+    check(lib().mary_gemm_bf16_batched(_p(x), _p(w), _p(out), M, N, K, ldx, ldw, ldo, batch, bsx, bsw, bso, None, 1.0, 0, 0, 1, -1,
+                                       _stream()), "gemm_bf16_batched")
+    return out
+
+
+def mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps):
+    T = qakv.shape[0]
+    qa = torch.empty(T, q_lora, dtype=torch.bfloat16, device=qakv.device)
+    check(lib().mary_mla_prep(_p(qakv), qakv.stride(0), q_lora, _p(w_qa), _p(w_kv), _p(inv_freq), _p(meta.positions),
+                              _p(meta.slot_mapping), _p(qa), _p(cache), eps, T, _stream()), "mla_prep")
+    return qa
+
+
+def mla_absorb_q(qb, w_uk, inv_freq, meta, H):
+    """``qb[T, H*192]`` -> ``q_full[T, H, 576]``: nope part times ``w_uk[H, 512, 128]`` (absorbed W_UK), rope part rotated."""
+    T = qb.shape[0]
+    q_full = torch.empty(T, H, 576, dtype=torch.bfloat16, device=qb.device)
+    gemm_batched(qb, w_uk, q_full, T, 512, 128, H * 192, 128, H * 576, H, 192, 512 * 128, 576)
+    check(lib().mary_mla_q_rope(_p(qb), _p(inv_freq), _p(meta.positions), _p(q_full), H, T, _stream()), "mla_q_rope")
+    return q_full
+
+
+def mla_unabsorb_o(o_lat, w_uv, H):
+    """``o_lat[T, H, 512]`` -> ``o[T, H*128]`` with ``w_uv[H, 128, 512]``."""
+    T = o_lat.shape[0]
+    o = torch.empty(T, H * 128, dtype=torch.bfloat16, device=o_lat.device)
+    gemm_batched(o_lat, w_uv, o, T, 128, 512, H * 512, 512, H * 128, H, 512, 128 * 512, 128)
+    return o

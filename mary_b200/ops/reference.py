@@ -60,10 +60,16 @@ def gather_pages(cache, page_row, kv_len: int):
     return cache[page_row[:n].long()].reshape(n * ps, *cache.shape[2:])[:kv_len]
 
 
-def paged_attention(q, kcache, vcache, meta, scale: float, window: int = 0, softcap: float = 0.0):
+def paged_attention(q, kcache, vcache, meta, scale: float, window: int = 0, softcap: float = 0.0, dv: int | None = None):
     """Causal (optionally sliding-window) attention of the flattened batch over the paged cache.
-    ``q[T, Hq, D]``; caches ``[pages, page, Hkv, D]``; GQA by index; softmax in f32."""
+    ``q[T, Hq, D]``; caches ``[pages, page, Hkv, D]``; GQA by index; softmax in f32.  A latent cache
+    (``[pages, page, D]``, one shared kv head) passes ``vcache is kcache`` and ``dv`` = value width (the first ``dv`` dims)."""
     T, Hq, D = q.shape
+    if kcache.dim() == 3:
+        kcache = kcache.unsqueeze(2)
+        vcache = vcache.unsqueeze(2)
+    if dv is not None:
+        vcache = vcache[..., :dv]
     Hkv = kcache.shape[2]
     g = Hq // Hkv
     out = torch.empty(T, Hq, vcache.shape[-1], dtype=q.dtype, device=q.device)

@@ -1,0 +1,51 @@
+"""Parallel group used by the models: tensor-parallel attention / dense FFN and expert-parallel routed experts, both of
+which leave a PARTIAL hidden state on every rank that one sum over the group completes.
+
+``mode="nccl"`` is the library baseline (``torch.distributed.all_reduce``); ``mode="fused"`` uses this package's own
+kernels over peer memory (``parallel.symm``): partial sums are written into a symmetric buffer and reduced by a
+one-shot / two-shot kernel that reads the peers directly (or through the NVSwitch multicast address).
+The reference has no collective at all: its only multi-device mode is a 2-stage layer pipeline over TCP
+(src/bin/inkling_forward.rs:1192-1271); tensor parallelism is priced there but not built (:68-99)."""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+
+
+class ParallelGroup:
+    def __init__(self, rank: int = 0, size: int = 1, mode: str = "nccl", group=None, symm=None):
+        self.rank, self.size, self.mode, self.group, self.symm = rank, size, mode, group, symm
+        self.bytes_reduced = 0
+        self.calls = 0
+
+    def reduce(self, partial, residual=None):
+        if self.size == 1:
+            return partial
+        self.calls += 1
+        self.bytes_reduced += partial.numel() * partial.element_size()
+        if self.mode == "fused" and self.symm is not None and partial.is_cuda:
+            return self.symm.all_reduce(partial)
+        import torch.distributed as dist
+        out = partial.contiguous()
+        dist.all_reduce(out, group=self.group)
+        return out
+
+    def row_linear(self, x, w):
+        """Row-parallel GEMM: the result is this rank's partial sum (the caller reduces it)."""
+        return ops.linear(x, w)
+
+
+def init_distributed(device_index: int | None = None):
+    """``torch.distributed`` over NCCL from the torchrun environment.  Returns ``(rank, world, local_rank)``."""
+    import os
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    if torch.cuda.is_available():
+        torch.cuda.set_device(local if device_index is None else device_index)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl" if torch.cuda.is_available() else "gloo",
+                                device_id=torch.device("cuda", local) if torch.cuda.is_available() else None)
+    return rank, world, local

@@ -188,3 +188,27 @@ def test_short_conv(K):
     y, h = K.short_conv(x, w, hist)
     wy, wh = ref.short_conv(x, w, hist)
     assert _rel(y, wy) < 1e-2 and torch.equal(h, wh)
+
+
+@pytest.mark.parametrize("Hq", [64, 8, 16])
+def test_mla_latent_attention_tensor_core(K, Hq):
+    """tcgen05 MLA kernel against the fp32 reference: decode with speculative rows, chunked prefill, kv splits."""
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    torch.manual_seed(Hq)
+    for S_lens, q_lens in (([300, 17, 1000, 64], [3, 1, 3, 2]), ([40, 90], [40, 7]), ([4096 + 3], [3])):
+        pages = sum((l + 15) // 16 for l in S_lens) + 3
+        cache = PagedKVCache(1, pages, 16, 1, 1, dtype=torch.bfloat16, device="cuda", latent_dim=576)
+        for rnd in range(max((l + 15) // 16 for l in S_lens)):
+            for s, l in enumerate(S_lens):
+                if rnd * 16 < l:
+                    cache.alloc.extend(s, min(16, l - rnd * 16))
+        table, lens = cache.alloc.page_table(list(range(len(S_lens))))
+        meta = BatchMeta.build(q_lens, lens, table, 16, "cuda")
+        cache.k[0].normal_()
+        q = (torch.randn(sum(q_lens), Hq, 576, device="cuda") * 0.5).bfloat16()
+        want = ref.paged_attention(q, cache.k[0], cache.k[0], meta, 576 ** -0.5, dv=512)
+        for nsplit in (1, None, 3):
+            got = K.mla_attention(q, cache.k[0], meta, 576 ** -0.5, nsplit=nsplit)
+            assert K.last_status() == 0
+            assert _rel(got, want) < 2e-2, (S_lens, nsplit, _rel(got, want))
