@@ -81,6 +81,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line then names a reduced config)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-ttft", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="print a per-op device-time table of one eager step and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -143,6 +144,18 @@ def main():
     rng = np.random.default_rng(0)
     dec.set_context(np.full(B, ctx), rng.integers(0, cfg.vocab_size, B), rng.integers(0, cfg.vocab_size, (B, max(k, 1)))[:, :k])
     build_s = time.time() - t0
+
+    if args.trace:
+        from mary_b200.utils.trace import Tracer
+        with torch.no_grad():
+            for _ in range(2):
+                dec._step_device()
+            torch.cuda.synchronize()
+            with Tracer() as tr:
+                dec._step_device()
+        if rank == 0:
+            print(tr.report())
+        return
 
     # ---------------------------------------------------------------- capture + launch census
     K.LAUNCHES = 0

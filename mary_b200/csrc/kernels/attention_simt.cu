@@ -258,3 +258,66 @@ MARY_API int mary_paged_attention(const void* q, const void* kc, const void* vc,
     default: return MARY_ERR_BAD_ARG;
   }
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant (see no_alloc.h for who needs it and what it costs).
+#include "no_alloc.h"
+
+namespace {
+
+// Partial results of the split-KV pass for callers that cannot hand us a buffer.  It is part of the library's device
+// image: each GPU that loads the library carries these 16 MiB until the process ends.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MARY_NOALLOC_SCRATCH_BYTES];
+
+// Device address of the array per device ordinal, looked up on the first call made with that device current.  The
+// array's NAME is only a host-side handle here; handing it to a kernel would pass a host address.
+float* g_noalloc_ptr[64] = {nullptr};
+
+int noalloc_setup(float** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MARY_ERR_CUDA;
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) return MARY_ERR_CUDA;
+    g_noalloc_ptr[dev] = (float*)p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return MARY_OK;
+}
+
+}  // namespace
+
+MARY_API int64_t mary_noalloc_scratch_bytes(void) { return (int64_t)MARY_NOALLOC_SCRATCH_BYTES; }
+
+MARY_API const char* mary_status_string(int code) {
+  switch (code) {
+    case MARY_OK: return "ok";
+    case MARY_ERR_TIMEOUT_TMA: return "a TMA pipeline wait timed out";
+    case MARY_ERR_TIMEOUT_MMA: return "an accumulator wait timed out";
+    case MARY_ERR_TIMEOUT_PEER: return "a wait on another GPU's flag timed out";
+    case MARY_ERR_BAD_ARG: return "bad argument";
+    case MARY_ERR_CUDA: return "CUDA runtime error";
+    case MARY_ERR_BOUNDS: return "bounds check failed";
+    case MARY_ERR_SCRATCH_TOO_LARGE:
+      return "the split-KV partial results exceed the library's built-in 16 MiB scratch array: use fewer splits or fewer "
+             "query blocks per call, or call mary_paged_attention with a buffer of your own";
+    default: return "unknown status";
+  }
+}
+
+// Same contract as mary_paged_attention, minus the scratch argument.  The first call on a device performs the one-time
+// set-up described in no_alloc.h and should be made outside stream capture.
+MARY_API int mary_paged_attention_noalloc(const void* q, const void* kc, const void* vc, void* out, const int* page_table,
+                                          const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
+                                          int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok,
+                                          int64_t v_page, int Hq, int Hkv, int DK, int DV, int RQ, int nsplit, int window,
+                                          float scale, float softcap, cudaStream_t stream) {
+  if (nsplit < 1) nsplit = 1;
+  const int64_t need = mary_paged_attention_scratch_floats(NB, Hkv, nsplit, DV) * (int64_t)sizeof(float);
+  if (need > (int64_t)MARY_NOALLOC_SCRATCH_BYTES) return MARY_ERR_SCRATCH_TOO_LARGE;
+  float* scratch = nullptr;
+  const int rc = noalloc_setup(&scratch);
+  if (rc != MARY_OK) return rc;
+  return mary_paged_attention(q, kc, vc, out, page_table, kv_len, q_start, blk_seq, blk_q0, NB, max_pages, page_size, k_tok, k_page,
+                              v_tok, v_page, Hq, Hkv, DK, DV, RQ, nsplit, window, scale, softcap, scratch, stream);
+}

@@ -76,11 +76,14 @@ def _stream():
 
 
 LAUNCHES = 0      # launcher calls made through this module (each starts at least one kernel)
+TRACE = None      # an active mary_b200.utils.trace.Tracer, or None
 
 
 def check(rc: int, what: str):
     global LAUNCHES
     LAUNCHES += 1
+    if TRACE is not None:
+        TRACE.mark(what)
     if rc != 0:
         raise KernelError(f"{what}: {_STATUS.get(rc, rc)}")
 
