@@ -5,15 +5,19 @@
 // speculative tokens of a sequence — share ONE stream of 1152-byte cache rows.  The reference keeps an expanded
 // K/V cache and plain matmuls (src/models/k3/mla.rs:281-293); the latent cache and this kernel are new.
 //
-// One CTA = (tile of 128 query rows of one sequence, half of the 512 value dims, kv split).  A query row is a
-// (token, head) pair; rows of one sequence are contiguous in q[T * Hq, 576].
-//   warp 0   TMA: the Q tile once (9 chunks of [128 x 64]), then one 4-D TMA per 16-token page
-//            ([9 chunks][16 tokens][64 dims], 128-byte swizzle) into a ring of 32-key stages;
-//   warp 1   MMA: S[128 x 32] = Q K^T (per page: 9 chunks x 4 MMAs of 128x16x16, S double buffered in TMEM), then
-//            O[128 x 256] += P V with V^T taken from the SAME shared-memory page as an MN-major B operand;
-//   warps 2-5 softmax: one row per thread, tcgen05.ld of S, causal mask, running max with lazy rescale of O
-//            (only when the max grows by more than 2^8), P written to shared memory as bf16 in the un-swizzled
-//            K-major core-matrix layout, final O / l to global (or f32 partials when the kv range is split).
+// One CTA = (tile of 64 query rows of one sequence, half of the 512 value dims, kv split).  A query row is a
+// (token, head) pair; rows of one sequence are contiguous in q[T * Hq, 576].  The head dimension (576) makes shared
+// memory the binding resource: 64 query rows (72 KB) leave room for FOUR 32-key stages of the cache (4 x 36 KB), deep
+// enough that the tensor pipe always has a queued Q K^T while the softmax of an earlier block runs.
+//   warp 0   TMA: the Q tile once (9 chunks of [64 x 64]); per 32-key stage 18 small TMAs (one per page and 64-dim
+//            chunk, issued by different lanes) that lay the stage out as [9 chunks][32 keys][64 dims], 128-byte swizzle;
+//   warp 1   MMA (M = 64): S[64 x 32] = Q K^T (9 chunks x 4 MMAs of 64x32x16; three S buffers in TMEM, issued two
+//            blocks ahead), then O[64 x 256] += P V with V^T taken from the SAME shared-memory stage as an MN-major
+//            B operand (P double buffered in shared memory);
+//   warps 2-5 softmax: TMEM holds row r of an M = 64 accumulator in lane (r % 16) + 32 * (r / 16), so each warp owns 16
+//            rows in its lanes 0-15: tcgen05.ld of S, causal mask, running max with lazy rescale of O (only when the
+//            max grows by more than 2^8), P written to shared memory as bf16 in the un-swizzled K-major core-matrix
+//            layout, final O / l to global (or f32 partials when the kv range is split).
 // All waits are bounded.
 #include "common.cuh"
 #include "host_utils.h"
@@ -24,35 +28,31 @@ namespace {
 
 constexpr int DK = 576, DV = 512, DVH = 256;
 constexpr int PAGE = 16, KB = 32;                 // keys per stage
+constexpr int TR = 64;                            // query rows per CTA (MMA M)
 constexpr int CHUNK = 64;                         // dims per 128-byte row
 constexpr int NCHUNK = DK / CHUNK;                // 9
-constexpr int Q_CHUNK_BYTES = 128 * 128;          // 16 KB
-constexpr int Q_BYTES = NCHUNK * Q_CHUNK_BYTES;   // 144 KB
-constexpr int PAGE_BYTES = NCHUNK * PAGE * 128;   // 18 KB
-constexpr int STAGE_BYTES = 2 * PAGE_BYTES;       // 36 KB
-constexpr int STAGES = 2;
-constexpr int P_BYTES = 128 * KB * 2;             // 8 KB
-constexpr int SMEM = Q_BYTES + STAGES * STAGE_BYTES + P_BYTES + 1024 + 256;
-constexpr int TMEM_COLS = 512;                    // S 2 x 32, O 256
+constexpr int Q_CHUNK_BYTES = TR * 128;           // 8 KB
+constexpr int Q_BYTES = NCHUNK * Q_CHUNK_BYTES;   // 72 KB
+constexpr int K_CHUNK_BYTES = KB * 128;           // 4 KB: 32 keys of one 64-dim chunk
+constexpr int STAGE_BYTES = NCHUNK * K_CHUNK_BYTES;   // 36 KB
+constexpr int STAGES = 4;
+constexpr int NSBUF = 3;                          // S accumulators in TMEM
+constexpr int NPBUF = 2;                          // P tiles in shared memory
+constexpr int P_BYTES = TR * KB * 2;              // 4 KB
+constexpr int SMEM = Q_BYTES + STAGES * STAGE_BYTES + NPBUF * P_BYTES + 1024 + 256;
+constexpr int TMEM_COLS = 512;                    // S 3 x 32 at columns 0..95, O 256 at columns 128..383
 constexpr int NTHREADS = 192;
 constexpr float RESCALE_THRESHOLD = 8.0f;
 
 struct MlaParams {
   const int* page_table; const int* kv_len; const int* q_start; const int* blk_seq; const int* blk_row0;
   __nv_bfloat16* out;      // [T * Hq, 512]
-  float* part_o;           // [NB, nsplit, 128, 512] when nsplit > 1
-  float* part_ml;          // [NB, nsplit, 128, 2]
+  float* part_o;           // [NB, nsplit, 64, 512] when nsplit > 1
+  float* part_ml;          // [NB, nsplit, 64, 2]
   int max_pages, Hq, nsplit;
   float scale_log2;        // softmax scale * log2(e)
   int* status;
 };
-
-__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1, int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(m), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
 
 // K-major, no swizzle: 8-row core matrices of 128 bytes; LBO = distance between the two 16-byte K chunks of one
 // MMA, SBO = distance between 8-row groups.
@@ -73,28 +73,28 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sQ = smem;
   uint8_t* sK = smem + Q_BYTES;
   uint8_t* sP = sK + STAGES * STAGE_BYTES;
-  uint64_t* bars = (uint64_t*)(sP + P_BYTES);
-  uint64_t* q_full = bars;               // 1
-  uint64_t* k_full = bars + 1;           // [STAGES]
-  uint64_t* k_empty = k_full + STAGES;   // [STAGES]
-  uint64_t* s_full = k_empty + STAGES;   // [2]
-  uint64_t* s_empty = s_full + 2;        // [2]
-  uint64_t* p_full = s_empty + 2;        // 1
-  uint64_t* o_done = p_full + 1;         // 1
-  uint32_t* tmem_slot = (uint32_t*)(o_done + 1);
+  uint64_t* bars = (uint64_t*)(sP + NPBUF * P_BYTES);
+  uint64_t* q_full = bars;                 // 1
+  uint64_t* k_full = q_full + 1;           // [STAGES]
+  uint64_t* k_empty = k_full + STAGES;     // [STAGES]
+  uint64_t* s_full = k_empty + STAGES;     // [NSBUF]
+  uint64_t* s_empty = s_full + NSBUF;      // [NSBUF]
+  uint64_t* p_full = s_empty + NSBUF;      // [NPBUF]
+  uint64_t* pv_done = p_full + NPBUF;      // [NPBUF]
+  uint32_t* tmem_slot = (uint32_t*)(pv_done + NPBUF);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nb = blockIdx.x, half = blockIdx.y, split = blockIdx.z;
+  // the two value halves of a tile are neighbours in the grid so that they share the tile's cache rows in L2
+  const int half = blockIdx.x & 1, nb = blockIdx.x >> 1, split = blockIdx.y;
   const int seq = p.blk_seq[nb], row0 = p.blk_row0[nb];          // row0: global row index (token * Hq + head)
   const int seq_row0 = p.q_start[seq] * p.Hq, seq_row1 = p.q_start[seq + 1] * p.Hq;
-  const int nrows = min(128, seq_row1 - row0);
+  const int nrows = min(TR, seq_row1 - row0);
   const int kvlen = p.kv_len[seq];
   const int qlen = p.q_start[seq + 1] - p.q_start[seq];
   const int pos_first = kvlen - qlen;                             // position of the sequence's first query token
-  const int tok_lo = (row0 - seq_row0) / p.Hq, tok_hi = (row0 - seq_row0 + nrows - 1) / p.Hq;
+  const int tok_hi = (row0 - seq_row0 + nrows - 1) / p.Hq;
   const int k_hi = pos_first + tok_hi + 1;                        // keys [0, k_hi) are visible to some row of the tile
-  // this split's key range, in whole stages of KB keys
   const int nblk_total = (k_hi + KB - 1) / KB;
   const int per = (nblk_total + p.nsplit - 1) / p.nsplit;
   const int b_lo = split * per, b_hi = min(nblk_total, b_lo + per);
@@ -103,9 +103,8 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     for (int s = 0; s < STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4); }
-    mbar_init(p_full, 4);
-    mbar_init(o_done, 1);
+    for (int b = 0; b < NSBUF; ++b) { mbar_init(&s_full[b], 1); mbar_init(&s_empty[b], 4); }
+    for (int b = 0; b < NPBUF; ++b) { mbar_init(&p_full[b], 4); mbar_init(&pv_done[b], 1); }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_q);
@@ -116,92 +115,104 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S = tmem_base;            // 2 x 32 columns
-  const uint32_t tmem_O = tmem_base + 64;       // 256 columns
+  const uint32_t tmem_S = tmem_base;            // NSBUF x 32 columns
+  const uint32_t tmem_O = tmem_base + 128;      // 256 columns
 
   if (warp == 0) {
-    if (elect_one() && nblk > 0) {
-      mbar_expect_tx(q_full, Q_BYTES);
-      for (int c = 0; c < NCHUNK; ++c) tma_load_2d(sQ + c * Q_CHUNK_BYTES, &tm_q, q_full, c * CHUNK, row0);
+    if (nblk > 0) {
+      // every lane of the producer warp issues its own TMA operations; lane 0 owns the barrier bookkeeping
+      if (lane == 0) {
+        mbar_expect_tx(q_full, Q_BYTES);
+        for (int c = 0; c < NCHUNK; ++c) tma_load_2d(sQ + c * Q_CHUNK_BYTES, &tm_q, q_full, c * CHUNK, row0);
+      }
       const int* pt = p.page_table + (int64_t)seq * p.max_pages;
       int stage = 0; uint32_t phase = 0;
       for (int b = b_lo; b < b_hi; ++b) {
-        if (!mbar_wait(&k_empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
-        mbar_expect_tx(&k_full[stage], STAGE_BYTES);
-        for (int pg = 0; pg < 2; ++pg) {
-          const int key0 = b * KB + pg * PAGE;
-          // pages past the sequence end read page 0 (their scores are masked)
-          const int page = (key0 < kvlen) ? pt[key0 / PAGE] : pt[0];
-          tma_load_4d(sK + stage * STAGE_BYTES + pg * PAGE_BYTES, &tm_kv, &k_full[stage], 0, 0, 0, page);
+        int ok = 1;
+        if (lane == 0) {
+          ok = mbar_wait(&k_empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA) ? 1 : 0;
+          if (ok) mbar_expect_tx(&k_full[stage], STAGE_BYTES);
         }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) goto done;
+        // 2 pages x 9 chunks = 18 operations of [16 tokens x 64 dims] (2 KB each)
+        if (lane < (KB / PAGE) * NCHUNK) {
+          const int pg = lane / NCHUNK, c = lane % NCHUNK;
+          const int key0 = b * KB + pg * PAGE;
+          // pages past the sequence end read the first page (their scores are masked)
+          const int page = (key0 < kvlen) ? pt[key0 / PAGE] : pt[0];
+          tma_load_3d(sK + stage * STAGE_BYTES + c * K_CHUNK_BYTES + pg * (PAGE * 128), &tm_kv, &k_full[stage], c * CHUNK, 0, page);
+        }
+        __syncwarp();
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (elect_one() && nblk > 0) {
-      const uint32_t idesc_s = idesc_bf16(128, 16);
-      const uint32_t idesc_o = idesc_bf16(128, DVH) | (1u << 16);          // B operand MN-major
+      const uint32_t idesc_s = idesc_bf16(TR, KB);
+      const uint32_t idesc_o = idesc_bf16(TR, DVH) | (1u << 16);           // B operand MN-major
       if (!mbar_wait(q_full, 0, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       auto issue_qk = [&](int i) -> bool {        // i = block index relative to b_lo
-        const int stage = i % STAGES;
-        const uint32_t kphase = (i / STAGES) & 1;
-        const int sb = i & 1;
-        if (!mbar_wait(&s_empty[sb], ((i >> 1) & 1) ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) return false;
-        if (!mbar_wait(&k_full[stage], kphase, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) return false;
+        const int stage = i % STAGES, sb = i % NSBUF;
+        if (!mbar_wait(&s_empty[sb], ((i / NSBUF) & 1) ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) return false;
+        if (!mbar_wait(&k_full[stage], (i / STAGES) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) return false;
         tc_fence_after();
         const uint32_t kb_addr = smem_u32(sK + stage * STAGE_BYTES);
-        for (int pg = 0; pg < 2; ++pg) {
-          for (int c = 0; c < NCHUNK; ++c) {
+        for (int c = 0; c < NCHUNK; ++c) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              umma_f16(tmem_S + sb * 32 + pg * 16, umma_desc_sw128(q_addr + c * Q_CHUNK_BYTES + k * 32),
-                       umma_desc_sw128(kb_addr + pg * PAGE_BYTES + c * 2048 + k * 32), idesc_s, (c > 0 || k > 0) ? 1u : 0u);
-            }
+          for (int k = 0; k < 4; ++k) {
+            umma_f16(tmem_S + sb * KB, umma_desc_sw128(q_addr + c * Q_CHUNK_BYTES + k * 32),
+                     umma_desc_sw128(kb_addr + c * K_CHUNK_BYTES + k * 32), idesc_s, (c > 0 || k > 0) ? 1u : 0u);
           }
         }
         umma_commit(&s_full[sb]);
         return true;
       };
       if (!issue_qk(0)) goto done;
+      if (nblk > 1 && !issue_qk(1)) goto done;
       for (int i = 0; i < nblk; ++i) {
-        if (i + 1 < nblk && !issue_qk(i + 1)) goto done;
-        if (!mbar_wait(p_full, i & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
+        if (i + 2 < nblk && !issue_qk(i + 2)) goto done;
+        const int pb = i & 1;
+        if (!mbar_wait(&p_full[pb], (i >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
         tc_fence_after();
         const int stage = i % STAGES;
         const uint32_t kb_addr = smem_u32(sK + stage * STAGE_BYTES);
-        for (int pg = 0; pg < 2; ++pg) {
-          // A = P[:, 16 keys of this page] (K-major, no swizzle), B = V^T from the page (MN-major, 128B swizzle)
-          umma_f16(tmem_O, desc_kmajor_noswz(p_addr + pg * 2 * 2048, 2048, 128),
-                   desc_mnmajor_sw128(kb_addr + pg * PAGE_BYTES + half * 4 * 2048, 2048, 1024), idesc_o, (i > 0 || pg > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < KB / 16; ++kk) {
+          // A = P[:, 16 keys] (K-major, no swizzle: 16-byte key chunks TR*16 bytes apart, 8-row groups 128 bytes apart),
+          // B = V^T of those keys from the stage (MN-major, 128B swizzle: 64-dim groups one chunk apart, 8-key groups 1 KB apart)
+          umma_f16(tmem_O, desc_kmajor_noswz(p_addr + pb * P_BYTES + kk * 2 * (TR * 16), TR * 16, 128),
+                   desc_mnmajor_sw128(kb_addr + half * 4 * K_CHUNK_BYTES + kk * 16 * 128, K_CHUNK_BYTES, 1024), idesc_o,
+                   (i > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(&k_empty[stage]);       // the page buffers may be overwritten once PV has read them
-        umma_commit(o_done);
+        umma_commit(&k_empty[stage]);       // the stage may be overwritten once PV has read it
+        umma_commit(&pv_done[pb]);
       }
     }
   } else if (nblk > 0) {
-    // ------------------------------------------------------------------ softmax warps: one query row per thread
+    // ------------------------------------------------------------------ softmax warps: 16 query rows per warp
     const int q4 = warp & 3;
-    const int r = q4 * 32 + lane;
-    const bool row_ok = r < nrows;
+    const int r = q4 * 16 + (lane & 15);            // accumulator row held by this lane (lanes 16-31 hold nothing)
+    const bool row_ok = lane < 16 && r < nrows;
     const int qpos = pos_first + (row0 - seq_row0 + r) / p.Hq;
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     for (int i = 0; i < nblk; ++i) {
-      const int sb = i & 1;
-      if (!mbar_wait(&s_full[sb], (i >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
+      const int sb = i % NSBUF, pb = i & 1;
+      if (!mbar_wait(&s_full[sb], (i / NSBUF) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
       tc_fence_after();
-      uint32_t sr[32];
-      tmem_ld_32x32b_x32(tmem_S + lane_off + sb * 32, sr);
+      uint32_t sr[KB];
+      tmem_ld_32x32b_x32(tmem_S + lane_off + sb * KB, sr);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
       const int key0 = (b_lo + i) * KB;
-      float sv[32];
+      float sv[KB];
       float mx = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) {
+      for (int j = 0; j < KB; ++j) {
         const bool ok = row_ok && (key0 + j) <= qpos;
         sv[j] = ok ? __uint_as_float(sr[j]) * p.scale_log2 : -INFINITY;
         mx = fmaxf(mx, sv[j]);
@@ -211,13 +222,23 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool first = (m_ref == -INFINITY);
       float corr = 1.f;
       if (need) { corr = first ? 0.f : exp2f(m_ref - mx); m_ref = mx; }
-      const bool any_rescale = __any_sync(0xffffffffu, need && !first);
-      if (i > 0) {
-        // the previous PV must have finished before O is touched or P is overwritten
-        if (!mbar_wait(o_done, (i - 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
-        tc_fence_after();
+      // probabilities in registers first: the waits below then overlap this arithmetic of the other warps
+      uint32_t pw[KB / 2];
+      float psum = 0.f;
+#pragma unroll
+      for (int j = 0; j < KB / 2; ++j) {
+        const float a = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j] - m_ref);
+        const float b = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j + 1] - m_ref);
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        pw[j] = *(uint32_t*)&h;
+        float2 back = __bfloat1622float2(h);
+        psum += back.x + back.y;
       }
-      if (any_rescale && i > 0) {
+      l = l * corr + psum;
+      if (__any_sync(0xffffffffu, need && !first) && i > 0) {
+        // O may only be touched once the previous P V has completed
+        if (!mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
+        tc_fence_after();
 #pragma unroll 1
         for (int c0 = 0; c0 < DVH; c0 += 32) {
           uint32_t o[32];
@@ -230,31 +251,23 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         tmem_st_wait();
       }
-      l *= corr;
-      // P (bf16) -> shared memory: chunk c holds keys 8c..8c+7 of every row, 16 bytes per row
-      float psum = 0.f;
-#pragma unroll
-      for (int c = 0; c < KB / 8; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a = (m_ref == -INFINITY) ? 0.f : exp2f(sv[8 * c + 2 * j] - m_ref);
-          const float b = (m_ref == -INFINITY) ? 0.f : exp2f(sv[8 * c + 2 * j + 1] - m_ref);
-          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-          w[j] = *(uint32_t*)&h;
-          float2 back = __bfloat1622float2(h);
-          psum += back.x + back.y;
-        }
-        *(uint4*)(sP + c * 2048 + r * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+      if (i >= NPBUF) {
+        // this P buffer was last read by the P V of block i - 2
+        if (!mbar_wait(&pv_done[pb], ((i - NPBUF) >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
       }
-      l += psum;
+      // P (bf16) -> shared memory: chunk c holds keys 8c..8c+7 of every row, 16 bytes per row
+      if (lane < 16) {
+#pragma unroll
+        for (int c = 0; c < KB / 8; ++c)
+          *(uint4*)(sP + pb * P_BYTES + c * (TR * 16) + r * 16) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
+      }
       fence_proxy_async();       // make the generic-proxy writes of P visible to the tensor core
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[pb]);
     }
     // ------------------------------------------------------------------ write out
-    if (!mbar_wait(o_done, (nblk - 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
+    if (!mbar_wait(&pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
     tc_fence_after();
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll 1
@@ -275,21 +288,21 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 4; ++j) ((uint4*)dst)[j] = w[j];
         } else {
-          float* dst = p.part_o + (((int64_t)nb * p.nsplit + split) * 128 + r) * DV + half * DVH + c0;
+          float* dst = p.part_o + (((int64_t)nb * p.nsplit + split) * TR + r) * DV + half * DVH + c0;
 #pragma unroll
           for (int j = 0; j < 32; j += 4) *(float4*)(dst + j) = make_float4(__uint_as_float(o[j]), __uint_as_float(o[j + 1]), __uint_as_float(o[j + 2]), __uint_as_float(o[j + 3]));
         }
       }
     }
     if (row_ok && p.nsplit > 1 && half == 0) {
-      float* ml = p.part_ml + (((int64_t)nb * p.nsplit + split) * 128 + r) * 2;
+      float* ml = p.part_ml + (((int64_t)nb * p.nsplit + split) * TR + r) * 2;
       ml[0] = m_ref; ml[1] = l;
     }
   } else if (warp >= 2 && p.nsplit > 1) {
     // an empty split still has to publish neutral partials
-    const int r = (warp & 3) * 32 + lane;
-    if (r < nrows && half == 0) {
-      float* ml = p.part_ml + (((int64_t)nb * p.nsplit + split) * 128 + r) * 2;
+    const int r = (warp & 3) * 16 + (lane & 15);
+    if (lane < 16 && r < nrows && half == 0) {
+      float* ml = p.part_ml + (((int64_t)nb * p.nsplit + split) * TR + r) * 2;
       ml[0] = -INFINITY; ml[1] = 0.f;
     }
   }
@@ -303,19 +316,19 @@ done:
 __global__ void mla_combine_kernel(const MlaParams p, int NB) {
   const int nb = blockIdx.x, r = blockIdx.y;
   const int seq = p.blk_seq[nb], row0 = p.blk_row0[nb];
-  const int nrows = min(128, p.q_start[seq + 1] * p.Hq - row0);
+  const int nrows = min(TR, p.q_start[seq + 1] * p.Hq - row0);
   if (r >= nrows) return;
   float mm = -INFINITY;
-  for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, p.part_ml[(((int64_t)nb * p.nsplit + s) * 128 + r) * 2]);
+  for (int s = 0; s < p.nsplit; ++s) mm = fmaxf(mm, p.part_ml[(((int64_t)nb * p.nsplit + s) * TR + r) * 2]);
   float ll = 0.f;
   for (int s = 0; s < p.nsplit; ++s) {
-    const float* ml = p.part_ml + (((int64_t)nb * p.nsplit + s) * 128 + r) * 2;
+    const float* ml = p.part_ml + (((int64_t)nb * p.nsplit + s) * TR + r) * 2;
     if (ml[0] != -INFINITY) ll += ml[1] * exp2f(ml[0] - mm);
   }
   for (int d = threadIdx.x; d < DV; d += blockDim.x) {
     float acc = 0.f;
     for (int s = 0; s < p.nsplit; ++s) {
-      const int64_t pi = ((int64_t)nb * p.nsplit + s) * 128 + r;
+      const int64_t pi = ((int64_t)nb * p.nsplit + s) * TR + r;
       const float ms = p.part_ml[pi * 2];
       if (ms != -INFINITY) acc += p.part_o[pi * DV + d] * exp2f(ms - mm);
     }
@@ -329,11 +342,12 @@ typedef CUresult (*PFN_encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, vo
 
 }  // namespace
 
-MARY_API int64_t mary_mla_scratch_floats(int NB, int nsplit) { return nsplit > 1 ? (int64_t)NB * nsplit * 128 * (DV + 2) : 0; }
+MARY_API int64_t mary_mla_scratch_floats(int NB, int nsplit) { return nsplit > 1 ? (int64_t)NB * nsplit * TR * (DV + 2) : 0; }
+MARY_API int mary_mla_tile_rows() { return TR; }
 
 // q [T * Hq, 576] bf16 (rows = token-major, head-minor); cache [pages, 16, 576] bf16 with element strides
-// tok_stride / page_stride; out [T * Hq, 512] bf16.  blk_seq / blk_row0: NB tiles of up to 128 rows (row0 is a global
-// row index; a tile never crosses a sequence).
+// tok_stride / page_stride; out [T * Hq, 512] bf16.  blk_seq / blk_row0: NB tiles of query rows (row0 is a global
+// row index; a tile never crosses a sequence).  Tiles hold at most mary_mla_tile_rows() rows.
 MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, const int* page_table, const int* kv_len, const int* q_start,
                                 const int* blk_seq, const int* blk_row0, int NB, int total_rows, int num_pages, int max_pages,
                                 int64_t tok_stride, int64_t page_stride, int Hq, int nsplit, float scale, float* scratch,
@@ -345,15 +359,15 @@ MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, con
   PFN_encode enc = (PFN_encode)mary_encode_fn();
   if (!enc) return MARY_ERR_CUDA;
   CUtensorMap tq, tkv;
-  int rc = mary_make_tmap_2d(&tq, q, 4, (uint64_t)total_rows, DK, DK, 128, CHUNK, 1);
+  int rc = mary_make_tmap_2d(&tq, q, 4, (uint64_t)total_rows, DK, DK, TR, CHUNK, 1);
   if (rc) return rc;
   {
-    // dims: 64 contiguous elements, 16 tokens, 9 chunks, pages; box = one whole page
-    cuuint64_t dims[4] = {CHUNK, PAGE, NCHUNK, (cuuint64_t)num_pages};
-    cuuint64_t strides[3] = {(cuuint64_t)tok_stride * 2, CHUNK * 2, (cuuint64_t)page_stride * 2};
-    cuuint32_t box[4] = {CHUNK, PAGE, NCHUNK, 1};
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    if (enc(&tkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    // dims: 576 elements of a token row, 16 tokens of a page, pages; box = [64 dims x 16 tokens] of one page
+    cuuint64_t dims[3] = {DK, PAGE, (cuuint64_t)num_pages};
+    cuuint64_t strides[2] = {(cuuint64_t)tok_stride * 2, (cuuint64_t)page_stride * 2};
+    cuuint32_t box[3] = {CHUNK, PAGE, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(&tkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return MARY_ERR_CUDA;
   }
@@ -364,12 +378,12 @@ MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, con
   }
   MlaParams p;
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_row0 = blk_row0;
-  p.out = (__nv_bfloat16*)out; p.part_o = scratch; p.part_ml = scratch ? scratch + (int64_t)NB * nsplit * 128 * DV : nullptr;
+  p.out = (__nv_bfloat16*)out; p.part_o = scratch; p.part_ml = scratch ? scratch + (int64_t)NB * nsplit * TR * DV : nullptr;
   p.max_pages = max_pages; p.Hq = Hq; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f; p.status = mary_status_ptr();
-  mla_attn_kernel<<<dim3(NB, 2, nsplit), NTHREADS, SMEM, s>>>(tq, tkv, p);
+  mla_attn_kernel<<<dim3(NB * 2, nsplit), NTHREADS, SMEM, s>>>(tq, tkv, p);
   MARY_CHECK_LAUNCH();
   if (nsplit > 1) {
-    mla_combine_kernel<<<dim3(NB, 128), 128, 0, s>>>(p, NB);
+    mla_combine_kernel<<<dim3(NB, TR), 128, 0, s>>>(p, NB);
     MARY_CHECK_LAUNCH();
   }
   return MARY_OK;

@@ -1,0 +1,144 @@
+// Collectives over peer memory (NVLink 5 / NVSwitch) written as ordinary kernels.
+//
+// The reference has no collective backend: its one multi-device mode is a two-stage layer pipeline over a TCP socket
+// (src/bin/inkling_forward.rs:1192-1271) and NCCL appears only in a probe script (scripts/interconnect_probe.sh:57-126).
+// Here every rank owns a buffer in a symmetric allocation (same size on every rank, all peers' base addresses known)
+// plus a small pad of 32-bit flags.  Kernels read and write the peers' buffers directly (P2P ld/st), or through the
+// multicast address of the allocation when the switch supports it: `multimem.ld_reduce` returns the sum over all ranks
+// computed inside NVSwitch, `multimem.st` writes to all ranks at once.
+//
+// all-reduce (two-shot): rank r owns slice r of the vector.  barrier -> each rank reduces its slice (one in-switch
+// reduction per 16 bytes, or P2P loads from every peer) and writes the result into the output region of EVERY rank ->
+// barrier.  Each block synchronises with the same-numbered block of the other ranks only, and touches only chunks
+// assigned to its block number, so all ranks must launch the same grid.
+//
+// Flags are monotonic epochs (one value per call); every wait is bounded in time and records
+// MARY_ERR_TIMEOUT_PEER in the status word instead of hanging, after which the kernel returns.
+#include "common.cuh"
+#include "host_utils.h"
+
+using namespace mary;
+
+namespace {
+
+constexpr int MAX_RANKS = 8;
+
+struct CommCtx {
+  uint8_t* bufs[MAX_RANKS];     // peers' symmetric buffers (this rank's own at [rank])
+  uint32_t* sigs[MAX_RANKS];    // peers' flag pads
+  uint8_t* mc;                  // multicast address of the buffer, or null
+  int rank, world;
+  uint64_t wait_ns;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Barrier between block `blockIdx.x` of every rank.  slot layout: sig[(blockIdx.x * 2 + which) * MAX_RANKS + src].
+// Returns false when a peer did not arrive in time.
+__device__ bool rank_barrier(const CommCtx& c, int which, uint32_t epoch) {
+  __shared__ int ok_s;
+  __syncthreads();                 // all of this block's earlier writes are issued
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (threadIdx.x < c.world) {
+    const int peer = threadIdx.x;
+    const size_t slot = ((size_t)blockIdx.x * 2 + which) * MAX_RANKS;
+    __threadfence_system();
+    st_release_sys(c.sigs[peer] + slot + c.rank, epoch);
+    const uint32_t* mine = c.sigs[c.rank] + slot + peer;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > c.wait_ns) {
+        atomicCAS(c.status, 0, MARY_ERR_TIMEOUT_PEER);
+        ok_s = 0;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+               ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// In-place on the symmetric buffer: input region at in_off, output region at out_off (bytes), n bf16 elements (n % 8 == 0).
+__global__ void __launch_bounds__(512)
+allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int use_mc) {
+  if (!rank_barrier(c, 0, epoch)) return;
+  const int64_t nvec = n / 8;                                  // 16-byte vectors
+  const int64_t per = (nvec + c.world - 1) / c.world;
+  const int64_t lo = (int64_t)c.rank * per, hi = min(nvec, lo + per);
+  for (int64_t v = lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < hi; v += (int64_t)gridDim.x * blockDim.x) {
+    uint4 r;
+    if (use_mc) {
+      r = multimem_ld_reduce_bf16x8(c.mc + in_off + v * 16);
+      multimem_st_v4(c.mc + out_off + v * 16, r);
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < c.world; ++p) {
+        uint4 x;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(c.bufs[(c.rank + p) % c.world] + in_off + v * 16) : "memory");
+        const __nv_bfloat162* xp = (const __nv_bfloat162*)&x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(xp[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+      }
+      __nv_bfloat162* rp = (__nv_bfloat162*)&r;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) rp[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      for (int p = 0; p < c.world; ++p) *(uint4*)(c.bufs[(c.rank + p) % c.world] + out_off + v * 16) = r;
+    }
+  }
+  rank_barrier(c, 1, epoch);
+}
+
+// A wait that nothing satisfies (used by the failure-detection test): returns after wait_ns with the status set.
+__global__ void wait_flag_kernel(const CommCtx c, uint32_t slot, uint32_t want) {
+  const uint32_t* mine = c.sigs[c.rank] + slot;
+  const uint64_t t0 = globaltimer_ns();
+  while ((int32_t)(ld_acquire_sys(mine) - want) < 0) {
+    if (globaltimer_ns() - t0 > c.wait_ns) { atomicCAS(c.status, 0, MARY_ERR_TIMEOUT_PEER); return; }
+  }
+}
+
+}  // namespace
+
+// bufs / sigs: arrays of `world` device addresses (as integers).  grid blocks x 512 threads; every rank must pass the
+// same grid, n, offsets and epoch.  Flag pad: at least grid * 2 * 8 words, zeroed once at set-up.
+MARY_API int mary_allreduce_bf16(const uint64_t* bufs, const uint64_t* sigs, uint64_t mc, int rank, int world, uint64_t in_off,
+                                 uint64_t out_off, int64_t n, uint32_t epoch, int grid, int use_mc, uint64_t wait_ns, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || (n % 8) || (in_off % 16) || (out_off % 16) || grid < 1) return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epoch, (use_mc && mc) ? 1 : 0);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_wait_flag(const uint64_t* sigs, int rank, int world, uint32_t slot, uint32_t want, uint64_t wait_ns, cudaStream_t s) {
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = nullptr; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  wait_flag_kernel<<<1, 1, 0, s>>>(c, slot, want);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}

@@ -311,9 +311,15 @@ MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int
   p.rows_c = use_swap ? M : N;
   const int rows_r_total = use_swap ? (glu ? 2 * N : N) : M;
   int bn;
-  if (glu) bn = p.rows_c <= 32 ? 32 : (p.rows_c <= 64 ? 64 : 128);
-  else bn = p.rows_c <= 32 ? 32 : (p.rows_c <= 64 ? 64 : (p.rows_c <= 128 ? 128 : 256));
   p.tiles_r = (p.rows_r + BM - 1) / BM;
+  if (glu) bn = p.rows_c <= 32 ? 32 : (p.rows_c <= 64 ? 64 : 128);
+  else if (use_swap) bn = p.rows_c <= 32 ? 32 : (p.rows_c <= 64 ? 64 : (p.rows_c <= 128 ? 128 : 256));
+  else {
+    // activations are the row operand: take the widest column tile that still gives every SM a tile
+    const int sms = mary_num_sms();
+    bn = 256;
+    while (bn > 64 && (int64_t)p.tiles_r * ((p.rows_c + bn - 1) / bn) * split_k * batch < sms) bn >>= 1;
+  }
   p.tiles_c = (p.rows_c + bn - 1) / bn;
   CUtensorMap tr, tc;
   int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, batch, bsr, BM);

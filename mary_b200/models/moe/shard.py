@@ -1,0 +1,69 @@
+"""Cut a full (single-rank) ``MoEDecoder`` into the shard of one rank of a tensor/expert-parallel group.
+
+Attention heads, dense-FFN and shared-expert columns are split by rank (column-parallel weights by output rows, the
+following row-parallel weights by input columns); routed experts are split by expert index; everything else is replicated."""
+from __future__ import annotations
+
+import torch
+
+from ...ops.moe import NVFP4Experts
+from .model import DenseFFN, GQAAttention, MLAAttention, MoEDecoder, MoEFFN
+
+
+def _rows(t, r, n):
+    k = t.shape[0] // n
+    return t[r * k:(r + 1) * k]
+
+
+def _cols(t, r, n):
+    k = t.shape[1] // n
+    return t[:, r * k:(r + 1) * k]
+
+
+def _gu(t, r, n):
+    F = t.shape[0] // 2
+    k = F // n
+    return torch.cat([t[r * k:(r + 1) * k], t[F + r * k:F + (r + 1) * k]], 0)
+
+
+def slice_experts(ex: NVFP4Experts, r: int, n: int) -> NVFP4Experts:
+    e = ex.E // n
+    a, b = r * e, (r + 1) * e
+    r13, r2 = 2 * ex.F, ex.H
+    return NVFP4Experts(e, ex.H, ex.F, ex.w13_q[a * r13:b * r13], ex.w13_sf[a * r13 // 128:b * r13 // 128], ex.w13_s2[a:b],
+                        ex.w2_q[a * r2:b * r2], ex.w2_sf[a * r2 // 128:b * r2 // 128], ex.w2_s2[a:b], ex.act)
+
+
+def shard_from_full(full: MoEDecoder, par, device=None) -> MoEDecoder:
+    r, n = par.rank, par.size
+    dev = device or full.embed.device
+    m = MoEDecoder(full.cfg, par=par, dtype=full.dtype, device=dev)
+    fm = dict(full.named_modules())
+    with torch.no_grad():
+        for name, p in m.named_parameters():
+            src = dict(full.named_parameters())[name]
+            mod_name, _, leaf = name.rpartition(".")
+            mod = fm.get(mod_name)
+            if isinstance(mod, GQAAttention):
+                c = full.cfg
+                D = c.head_dim
+                if leaf == "w_qkv":
+                    q, k, v = src.split([c.num_attention_heads * D, c.num_key_value_heads * D, c.num_key_value_heads * D], 0)
+                    src = torch.cat([_rows(q, r, n), _rows(k, r, n), _rows(v, r, n)], 0)
+                elif leaf == "w_o":
+                    src = _cols(src, r, n)
+            elif isinstance(mod, MLAAttention):
+                if leaf in ("w_qb", "w_uk", "w_uv"):
+                    src = _rows(src, r, n)
+                elif leaf == "w_o":
+                    src = _cols(src, r, n)
+            elif isinstance(mod, DenseFFN):
+                src = _gu(src, r, n) if leaf == "w_gu" else _cols(src, r, n)
+            p.copy_(src.to(dev))
+    for (_, a), (_, b) in zip(m.named_modules(), full.named_modules()):
+        if isinstance(a, MoEFFN):
+            ex = slice_experts(b.experts, r, n)
+            for f in ("w13_q", "w13_sf", "w13_s2", "w2_q", "w2_sf", "w2_s2"):
+                setattr(ex, f, getattr(ex, f).to(dev))
+            a.experts = ex
+    return m

@@ -87,9 +87,34 @@ def bench_attn():
         print(f"decode attn B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, {gb:.0f} GB/s, {gb / hbm:.2f} {tag}")
 
 
+def bench_mla(B: int = 32, L: int = 4096, Hq: int = 64, q_len: int = 3, iters: int = 5):
+    """MLA latent attention, decode-shaped: B sequences of L cached tokens, q_len query tokens x Hq heads each."""
+    from . import cuda as K
+    from ..runtime.batch import BatchMeta
+    from ..runtime.kv_cache import PagedKVCache
+    hbm, tf, tag = peaks()
+    pages = B * ((L + 15) // 16) + 1
+    cache = PagedKVCache(1, pages, 16, 1, 1, dtype=torch.bfloat16, device="cuda", latent_dim=576)
+    for s in range(B):
+        cache.alloc.extend(s, L)
+    table, lens = cache.alloc.page_table(list(range(B)))
+    meta = BatchMeta.build([q_len] * B, lens, table, 16, "cuda")
+    cache.k[0].normal_()
+    q = (torch.randn(B * q_len, Hq, 576, device="cuda") * 0.3).bfloat16()
+    ms = time_op(lambda: K.mla_attention(q, cache.k[0], meta, 576 ** -0.5), iters=iters)
+    flops = 2.0 * B * q_len * Hq * L * (576 + 512)
+    gb = B * L * 1152 / ms / 1e6
+    print(f"mla attn B={B} L={L} Hq={Hq} q_len={q_len}: {ms:.4f} ms, {flops / ms / 1e9:.1f} TFLOP/s ({flops / ms / 1e9 / tf:.2f} {tag}), "
+          f"KV stream {gb:.0f} GB/s ({gb / hbm:.2f} {tag})")
+    assert K.last_status() == 0
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     if what in ("gemm", "all"):
         bench_gemm()
     if what in ("attn", "all"):
         bench_attn()
+    if what in ("mla", "all"):
+        bench_mla()
+        bench_mla(Hq=8)

@@ -120,9 +120,17 @@ def gemm(x, w, out=None, bias=None, alpha: float = 1.0, glu: str | None = None, 
 
 
 def _auto_split_k(M: int, N: int, K: int) -> int:
-    """Decode-sized GEMMs have too few output tiles to fill 148 SMs; split K until they do."""
-    tiles = ((N + 127) // 128) * max(1, (M + 255) // 256)
-    if M > 256 or tiles >= 120:
+    """GEMMs with few output tiles cannot fill 148 SMs; split K until they do (mirrors the launcher's tile choice)."""
+    if M <= 256:
+        bn = 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+        tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
+    else:
+        tr = (M + 127) // 128
+        bn = 256
+        while bn > 64 and tr * ((N + bn - 1) // bn) < 148:
+            bn //= 2
+        tiles = tr * ((N + bn - 1) // bn)
+    if tiles >= 100:
         return 1
     return max(1, min(K // 512, (148 + tiles - 1) // tiles))
 
@@ -306,6 +314,7 @@ def quantize_nvfp4(x):
 # --------------------------------------------------------------------------- MLA
 declare("mary_mla_attention", "pppppppp" + "iiii" + "ll" + "ii" + "f" + "ps")
 declare("mary_mla_scratch_floats", "ii", ret64=True)
+declare("mary_mla_tile_rows", "")
 
 
 def _row_tiles(meta, hq: int):
@@ -314,9 +323,10 @@ def _row_tiles(meta, hq: int):
     if key not in cache:
         seqs, r0 = [], []
         start = 0
+        tr = lib().mary_mla_tile_rows()
         for s, n in enumerate(meta.q_lens_host.tolist()):
             rows = n * hq
-            for b in range(0, rows, 128):
+            for b in range(0, rows, tr):
                 seqs.append(s)
                 r0.append(start * hq + b)
             start += n

@@ -1,0 +1,84 @@
+"""Symmetric heap: one buffer per rank whose peer addresses (and NVSwitch multicast address) every rank knows, plus the
+collectives this package runs on it with its own kernels (``csrc/kernels/comm.cu``).
+
+``torch.distributed._symmetric_memory`` does the plumbing only (allocation, handle exchange, multicast binding); the
+data movement is ours: the all-reduce reads the peers through ``multimem.ld_reduce`` (in-switch sum) or plain peer
+loads and writes the result to every rank with ``multimem.st`` / peer stores."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from ..ops.cuda import _stream, check, declare, lib
+
+declare("mary_allreduce_bf16", "pplii" + "llliiils")
+declare("mary_wait_flag", "piiiils")
+
+FLAG_WORDS = 64 * 2 * 8        # grid <= 64 blocks, two barriers, eight ranks
+
+
+class SymmetricHeap:
+    def __init__(self, rank: int, world: int, device, max_bytes: int, use_multicast: bool | None = None, grid: int = 48,
+                 wait_ms: float = 2000.0):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.rank, self.world, self.dev = rank, world, torch.device(device)
+        self.region = (max_bytes + 255) // 256 * 256
+        self.grid = grid
+        self.wait_ns = int(wait_ms * 1e6)
+        self.buf = symm_mem.empty(2 * self.region, dtype=torch.uint8, device=self.dev)
+        self.hdl = symm_mem.rendezvous(self.buf, dist.group.WORLD)
+        self.flags = symm_mem.empty(FLAG_WORDS, dtype=torch.int32, device=self.dev)
+        self.flags.zero_()
+        self.fhdl = symm_mem.rendezvous(self.flags, dist.group.WORLD)
+        self.buf_ptrs = (ctypes.c_uint64 * 8)(*list(self.hdl.buffer_ptrs)[:world])
+        self.sig_ptrs = (ctypes.c_uint64 * 8)(*list(self.fhdl.buffer_ptrs)[:world])
+        mc = 0
+        want_mc = use_multicast if use_multicast is not None else os.environ.get("MARY_MULTIMEM", "1") != "0"
+        if want_mc:
+            try:
+                mc = int(self.hdl.multicast_ptr or 0)
+            except Exception:
+                mc = 0
+        self.mc = mc
+        self.epoch = 0
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    @property
+    def multicast(self) -> bool:
+        return self.mc != 0
+
+    def input_view(self, shape, dtype=torch.bfloat16):
+        """A tensor over the start of the input region: producers (the row-parallel GEMM) write their partial sums
+        here directly, which saves the staging copy."""
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        if nbytes > self.region:
+            raise ValueError(f"{nbytes} bytes exceed the symmetric region of {self.region}")
+        return self.buf[:nbytes].view(dtype).view(*shape)
+
+    def all_reduce(self, partial):
+        """Sum ``partial`` (bf16) over all ranks; returns a tensor over the output region (valid until the next call)."""
+        assert partial.dtype == torch.bfloat16
+        n = partial.numel()
+        pad = (-n) % 8
+        nbytes = (n + pad) * 2
+        if nbytes > self.region:
+            raise ValueError(f"{nbytes} bytes exceed the symmetric region of {self.region}")
+        if partial.data_ptr() != self.buf.data_ptr():
+            self.buf[:n * 2].view(torch.bfloat16).copy_(partial.reshape(-1))
+        if pad:
+            self.buf[n * 2:nbytes].zero_()
+        self.epoch += 1
+        check(lib().mary_allreduce_bf16(self.buf_ptrs, self.sig_ptrs, self.mc, self.rank, self.world, 0, self.region, n + pad,
+                                        self.epoch, self.grid, 1 if self.mc else 0, self.wait_ns, _stream()), "allreduce_bf16")
+        return self.buf[self.region:self.region + n * 2].view(torch.bfloat16).view(partial.shape)
+
+    def wait_flag(self, slot: int, want: int):
+        """Launch a bounded wait on one of this rank's flags (failure-detection tests)."""
+        check(lib().mary_wait_flag(self.sig_ptrs, self.rank, self.world, slot, want, self.wait_ns, _stream()), "wait_flag")

@@ -1,0 +1,67 @@
+"""Tensor/expert-parallel execution on CPU ranks (gloo): the sharded model must reproduce the single-rank model."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _logits(model, ids, n):
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    spec = model.kv_spec()
+    cache = PagedKVCache(spec["num_layers"], 16, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32,
+                         latent_dim=spec.get("latent_dim"))
+    cache.alloc.extend(0, n)
+    table, lens = cache.alloc.page_table([0])
+    meta = BatchMeta.build([n], lens, table, 16)
+    with torch.no_grad():
+        return model(ids, meta, cache)
+
+
+def _worker(rank, world, port, attention, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mary_b200.models.moe import MoEDecoder, init_random_, tiny_moe_config
+    from mary_b200.models.moe.shard import shard_from_full
+    from mary_b200.parallel.group import ParallelGroup
+    torch.manual_seed(0)
+    cfg = tiny_moe_config(attention)
+    full = MoEDecoder(cfg, dtype=torch.float32)
+    init_random_(full, 0)
+    par = ParallelGroup(rank, world, "nccl")
+    shard = shard_from_full(full, par)
+    ids = torch.arange(1, 20, dtype=torch.int32)
+    lg = _logits(shard, ids, 19)
+    if rank == 0:
+        ref = _logits(full, ids, 19)
+        out.put((float((lg - ref).abs().max()), float(ref.abs().max()), par.calls))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("attention", ["mla", "gqa"])
+def test_tp_ep_two_cpu_ranks_match_single_rank(attention):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, attention, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    err, scale, calls = q.get(timeout=240)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert err < 2e-2 * scale, (err, scale)
+    assert calls > 0                      # the group really reduced partial sums
