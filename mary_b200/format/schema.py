@@ -68,6 +68,7 @@ LORA_B = _completed("1F21DAE6", "124D")
 TRAIN_STEP = derived_id(b"mary_b200.train", b"step")
 TRAIN_STATE = derived_id(b"mary_b200.train", b"state_blob")
 TRAIN_RUN = derived_id(b"mary_b200.train", b"run")
+TRAIN_ADAPTER = derived_id(b"mary_b200.train", b"adapter")
 
 KINDS = ("vector", "matrix", "conv", "tensor")
 # ownership label that ties a document or tokenizer to a model root (MODEL_ROOT marks roots only)

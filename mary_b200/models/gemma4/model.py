@@ -20,10 +20,13 @@ class _NoTP:
     rank, size = 0, 1
 
     def row_linear(self, x, w, lora=None):
-        return ops.linear(x, w)
+        y = ops.linear(x, w)
+        return y if lora is None else y + lora(x)
 
-    def all_reduce(self, x):
+    def reduce(self, x, residual=None):
         return x
+
+    all_reduce = reduce
 
 
 class Gemma4Layer(nn.Module):
@@ -63,13 +66,13 @@ class Gemma4Layer(nn.Module):
                                     meta, cache.k[self.i], cache.v[self.i], c.rms_norm_eps)
         o = ops.paged_attention(q, cache.k[self.i], cache.v[self.i], meta, 1.0, self.window)
         o = o.reshape(o.shape[0], -1)
-        a = self.tp.row_linear(o, self.w_o, L.get("o"))
+        a = self.tp.reduce(self.tp.row_linear(o, self.w_o, L.get("o")))
         x, h = ops.norm_add_norm(a, self.ln_post_attn, h, self.ln_pre_ffn, c.rms_norm_eps)
         if "gu" in L:
             m = ops.glu(ops.linear(x, self.w_gu) + L["gu"](x), "geglu")
         else:
             m = ops.linear_glu(x, self.w_gu, "geglu")
-        d = self.tp.row_linear(m, self.w_down, L.get("down"))
+        d = self.tp.reduce(self.tp.row_linear(m, self.w_down, L.get("down")))
         return ops.norm_add_norm(d, self.ln_post_ffn, h, next_norm, c.rms_norm_eps, self.layer_scalar)
 
 

@@ -31,9 +31,25 @@ class ParallelGroup:
         dist.all_reduce(out, group=self.group)
         return out
 
-    def row_linear(self, x, w):
-        """Row-parallel GEMM: the result is this rank's partial sum (the caller reduces it)."""
-        return ops.linear(x, w)
+    all_reduce = reduce
+
+    def row_linear(self, x, w, lora=None):
+        """Row-parallel GEMM: the result is this rank's partial sum (the caller reduces it).  In fused mode the GEMM
+        epilogue stores straight into the symmetric input region, so the reduction kernel needs no staging copy."""
+        if self.size > 1 and self.mode == "fused" and self.symm is not None and x.is_cuda:
+            from ..ops import cuda as K
+            M, N, Kd = x.shape[0], w.shape[0], x.shape[1]
+            out = self.symm.input_view((M, N))
+            sk = K._auto_split_k(M, N, Kd)
+            if sk > 1:
+                out.copy_(K.gemm(x.contiguous(), w, epi="red", split_k=sk))
+            else:
+                K.gemm(x.contiguous(), w, out=out)
+            if lora is not None:
+                out += lora(x)
+            return out
+        y = ops.linear(x, w)
+        return y if lora is None else y + lora(x)
 
 
 def init_distributed(device_index: int | None = None):

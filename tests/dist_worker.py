@@ -1,0 +1,96 @@
+"""Worker for tests/test_multigpu.py (launched by torch.distributed.run, one rank per GPU)."""
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def main():
+    what = sys.argv[1]
+    from mary_b200.parallel.group import ParallelGroup, init_distributed
+    from mary_b200.parallel.symm import SymmetricHeap
+    from mary_b200.ops import cuda as K
+    rank, world, local = init_distributed()
+    dev = torch.device("cuda", local)
+    if what == "allreduce":
+        for use_mc in (False, True):
+            heap = SymmetricHeap(rank, world, dev, max_bytes=8 << 20, use_multicast=use_mc)
+            if use_mc and not heap.multicast:
+                if rank == 0:
+                    print("multicast not available: in-switch path skipped")
+                continue
+            for n in (8, 1000 * 8, 384 * 7168, 3 * 1024 * 1024 + 8):
+                torch.manual_seed(100 + rank)
+                x = torch.randn(n, device=dev).bfloat16()
+                want = x.clone()
+                dist.all_reduce(want)
+                for _ in range(3):                       # repeated calls reuse the flags with growing epochs
+                    got = heap.all_reduce(x).clone()
+                torch.cuda.synchronize()
+                err = (got.float() - want.float()).abs().max().item()
+                scale = want.float().abs().max().item()
+                assert err <= 2e-2 * scale, (use_mc, n, err, scale)
+                # the GEMM can write straight into the symmetric input region
+                v = heap.input_view((n,))
+                v.copy_(x)
+                got2 = heap.all_reduce(v).clone()
+                assert torch.equal(got2, got)
+            assert K.last_status() == 0
+        dist.barrier()
+        if rank == 0:
+            print("ALLREDUCE_OK")
+    elif what == "model":
+        from mary_b200.models.moe import MoEDecoder, init_random_, tiny_moe_config
+        from mary_b200.models.moe.shard import shard_from_full
+        from mary_b200.runtime.batch import BatchMeta
+        from mary_b200.runtime.kv_cache import PagedKVCache
+        for mode in ("nccl", "fused"):
+            for attention in ("mla", "gqa"):
+                torch.manual_seed(0)
+                cfg = tiny_moe_config(attention)
+                full = MoEDecoder(cfg, dtype=torch.bfloat16, device=dev)
+                init_random_(full, 0)
+                heap = SymmetricHeap(rank, world, dev, max_bytes=1 << 20) if mode == "fused" else None
+                par = ParallelGroup(rank, world, mode, symm=heap)
+                shard = shard_from_full(full, par)
+                ids = torch.arange(1, 40, dtype=torch.int32, device=dev)
+                outs = []
+                for m in (full, shard):
+                    spec = m.kv_spec()
+                    cache = PagedKVCache(spec["num_layers"], 16, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16,
+                                         device=dev, latent_dim=spec.get("latent_dim"))
+                    cache.alloc.extend(0, 39)
+                    table, lens = cache.alloc.page_table([0])
+                    meta = BatchMeta.build([39], lens, table, 16, dev)
+                    with torch.no_grad():
+                        outs.append(m(ids, meta, cache).float())
+                torch.cuda.synchronize()
+                err = (outs[0] - outs[1]).abs().max().item()
+                scale = outs[0].abs().max().item()
+                assert err < 0.08 * scale, (mode, attention, err, scale)
+                assert par.calls > 0
+        assert K.last_status() == 0
+        dist.barrier()
+        if rank == 0:
+            print("MODEL_OK")
+    elif what == "timeout":
+        heap = SymmetricHeap(rank, world, dev, max_bytes=1 << 16, use_multicast=False, wait_ms=300.0)
+        dist.barrier()
+        if rank == 0:
+            heap.wait_flag(slot=900, want=12345)         # nothing ever writes this flag
+            torch.cuda.synchronize()
+            st = K.last_status()
+            assert st == 3, st                           # MARY_ERR_TIMEOUT_PEER
+            y = torch.ones(4, device=dev) * 2            # the context is still usable
+            assert y.sum().item() == 8
+        dist.barrier()
+        if rank == 0:
+            print("TIMEOUT_OK")
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
