@@ -5,7 +5,7 @@
 // speculative tokens of a sequence — share ONE stream of 1152-byte cache rows.  The reference keeps an expanded
 // K/V cache and plain matmuls (src/models/k3/mla.rs:281-293); the latent cache and this kernel are new.
 //
-// One CTA = (tile of 64 query rows of one sequence, half of the 512 value dims, kv split).  A query row is a
+// One CTA = (tile of 64 query rows of one sequence, kv split).  A query row is a
 // (token, head) pair; rows of one sequence are contiguous in q[T * Hq, 576].  The head dimension (576) makes shared
 // memory the binding resource: 64 query rows (72 KB) leave room for FOUR 32-key stages of the cache (4 x 36 KB), deep
 // enough that the tensor pipe always has a queued Q K^T while the softmax of an earlier block runs.
@@ -13,7 +13,9 @@
 //            chunk, issued by different lanes) that lay the stage out as [9 chunks][32 keys][64 dims], 128-byte swizzle;
 //   warp 1   MMA (M = 64): S[64 x 32] = Q K^T (9 chunks x 4 MMAs of 64x32x16; three S buffers in TMEM, issued two
 //            blocks ahead), then O[64 x 256] += P V with V^T taken from the SAME shared-memory stage as an MN-major
-//            B operand (P double buffered in shared memory);
+//            B operand (P double buffered in shared memory).  An M = 64 accumulator occupies only lanes 0-15 of each
+//            32-lane TMEM group, so the two 256-wide halves of O share the same 256 columns: dims 0-255 in lanes 0-15,
+//            dims 256-511 in lanes 16-31;
 //   warps 2-5 softmax: TMEM holds row r of an M = 64 accumulator in lane (r % 16) + 32 * (r / 16), so each warp owns 16
 //            rows in its lanes 0-15: tcgen05.ld of S, causal mask, running max with lazy rescale of O (only when the
 //            max grows by more than 2^8), P written to shared memory as bf16 in the un-swizzled K-major core-matrix
@@ -85,8 +87,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // the two value halves of a tile are neighbours in the grid so that they share the tile's cache rows in L2
-  const int half = blockIdx.x & 1, nb = blockIdx.x >> 1, split = blockIdx.y;
+  const int nb = blockIdx.x, split = blockIdx.y;
   const int seq = p.blk_seq[nb], row0 = p.blk_row0[nb];          // row0: global row index (token * Hq + head)
   const int seq_row0 = p.q_start[seq] * p.Hq, seq_row1 = p.q_start[seq + 1] * p.Hq;
   const int nrows = min(TR, seq_row1 - row0);
@@ -179,12 +180,16 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int stage = i % STAGES;
         const uint32_t kb_addr = smem_u32(sK + stage * STAGE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < KB / 16; ++kk) {
-          // A = P[:, 16 keys] (K-major, no swizzle: 16-byte key chunks TR*16 bytes apart, 8-row groups 128 bytes apart),
-          // B = V^T of those keys from the stage (MN-major, 128B swizzle: 64-dim groups one chunk apart, 8-key groups 1 KB apart)
-          umma_f16(tmem_O, desc_kmajor_noswz(p_addr + pb * P_BYTES + kk * 2 * (TR * 16), TR * 16, 128),
-                   desc_mnmajor_sw128(kb_addr + half * 4 * K_CHUNK_BYTES + kk * 16 * 128, K_CHUNK_BYTES, 1024), idesc_o,
-                   (i > 0 || kk > 0) ? 1u : 0u);
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+          for (int kk = 0; kk < KB / 16; ++kk) {
+            // A = P[:, 16 keys] (K-major, no swizzle: 16-byte key chunks TR*16 bytes apart, 8-row groups 128 bytes apart),
+            // B = V^T of those keys from the stage (MN-major, 128B swizzle: 64-dim groups one chunk apart, 8-key groups
+            // 1 KB apart); the second half of the value dims accumulates in lanes 16-31 of the same columns
+            umma_f16(tmem_O + ((uint32_t)(half * 16) << 16), desc_kmajor_noswz(p_addr + pb * P_BYTES + kk * 2 * (TR * 16), TR * 16, 128),
+                     desc_mnmajor_sw128(kb_addr + half * 4 * K_CHUNK_BYTES + kk * 16 * 128, K_CHUNK_BYTES, 1024), idesc_o,
+                     (i > 0 || kk > 0) ? 1u : 0u);
+          }
         }
         umma_commit(&k_empty[stage]);       // the stage may be overwritten once PV has read it
         umma_commit(&pv_done[pb]);
@@ -235,6 +240,8 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         psum += back.x + back.y;
       }
       l = l * corr + psum;
+      // lanes 16-31 hold the upper value half of row (lane - 16): they rescale with that row's factor
+      const float corr_o = __shfl_sync(0xffffffffu, corr, lane & 15);
       if (__any_sync(0xffffffffu, need && !first) && i > 0) {
         // O may only be touched once the previous P V has completed
         if (!mbar_wait(&pv_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
@@ -245,7 +252,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_ld_32x32b_x32(tmem_O + lane_off + c0, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+          for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr_o);
 #pragma unroll
           for (int j = 0; j < 32; j += 8) tmem_st_32x32b_x8(tmem_O + lane_off + c0 + j, o + j);
         }
@@ -269,13 +276,16 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // ------------------------------------------------------------------ write out
     if (!mbar_wait(&pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
     tc_fence_after();
-    const float inv_l = l > 0.f ? 1.f / l : 0.f;
+    const float l_row = __shfl_sync(0xffffffffu, l, lane & 15);
+    const float inv_l = l_row > 0.f ? 1.f / l_row : 0.f;
+    const int half = lane >> 4;                        // lanes 16-31: value dims 256-511 of row (lane - 16)
+    const bool out_ok = r < nrows;
 #pragma unroll 1
     for (int c0 = 0; c0 < DVH; c0 += 32) {
       uint32_t o[32];
       tmem_ld_32x32b_x32(tmem_O + lane_off + c0, o);
       tmem_ld_wait();
-      if (row_ok) {
+      if (out_ok) {
         if (p.nsplit == 1) {
           __nv_bfloat16* dst = p.out + (int64_t)(row0 + r) * DV + half * DVH + c0;
           uint4 w[4];
@@ -294,14 +304,14 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
     }
-    if (row_ok && p.nsplit > 1 && half == 0) {
+    if (row_ok && p.nsplit > 1) {
       float* ml = p.part_ml + (((int64_t)nb * p.nsplit + split) * TR + r) * 2;
       ml[0] = m_ref; ml[1] = l;
     }
   } else if (warp >= 2 && p.nsplit > 1) {
     // an empty split still has to publish neutral partials
     const int r = (warp & 3) * 16 + (lane & 15);
-    if (lane < 16 && r < nrows && half == 0) {
+    if (lane < 16 && r < nrows) {
       float* ml = p.part_ml + (((int64_t)nb * p.nsplit + split) * TR + r) * 2;
       ml[0] = -INFINITY; ml[1] = 0.f;
     }
@@ -380,7 +390,7 @@ MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, con
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_row0 = blk_row0;
   p.out = (__nv_bfloat16*)out; p.part_o = scratch; p.part_ml = scratch ? scratch + (int64_t)NB * nsplit * TR * DV : nullptr;
   p.max_pages = max_pages; p.Hq = Hq; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f; p.status = mary_status_ptr();
-  mla_attn_kernel<<<dim3(NB * 2, nsplit), NTHREADS, SMEM, s>>>(tq, tkv, p);
+  mla_attn_kernel<<<dim3(NB, nsplit), NTHREADS, SMEM, s>>>(tq, tkv, p);
   MARY_CHECK_LAUNCH();
   if (nsplit > 1) {
     mla_combine_kernel<<<dim3(NB, TR), 128, 0, s>>>(p, NB);

@@ -43,14 +43,14 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 
 // Barrier between block `blockIdx.x` of every rank.  slot layout: sig[(blockIdx.x * 2 + which) * MAX_RANKS + src].
 // Returns false when a peer did not arrive in time.
-__device__ bool rank_barrier(const CommCtx& c, int which, uint32_t epoch) {
+__device__ bool rank_barrier(const CommCtx& c, int which, uint32_t epoch, int blk) {
   __shared__ int ok_s;
   __syncthreads();                 // all of this block's earlier writes are issued
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   if (threadIdx.x < c.world) {
     const int peer = threadIdx.x;
-    const size_t slot = ((size_t)blockIdx.x * 2 + which) * MAX_RANKS;
+    const size_t slot = ((size_t)blk * 2 + which) * MAX_RANKS;
     __threadfence_system();
     st_release_sys(c.sigs[peer] + slot + c.rank, epoch);
     const uint32_t* mine = c.sigs[c.rank] + slot + peer;
@@ -80,13 +80,14 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
 }
 
 // In-place on the symmetric buffer: input region at in_off, output region at out_off (bytes), n bf16 elements (n % 8 == 0).
-__global__ void __launch_bounds__(512)
-allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int use_mc) {
-  if (!rank_barrier(c, 0, epoch)) return;
+// `blk` of `nblk` is this block's index within its rank's grid.
+__device__ void allreduce_bf16_body(const CommCtx& c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int use_mc, int blk,
+                                    int nblk) {
+  if (!rank_barrier(c, 0, epoch, blk)) return;
   const int64_t nvec = n / 8;                                  // 16-byte vectors
   const int64_t per = (nvec + c.world - 1) / c.world;
   const int64_t lo = (int64_t)c.rank * per, hi = min(nvec, lo + per);
-  for (int64_t v = lo + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; v < hi; v += (int64_t)gridDim.x * blockDim.x) {
+  for (int64_t v = lo + (int64_t)blk * blockDim.x + threadIdx.x; v < hi; v += (int64_t)nblk * blockDim.x) {
     uint4 r;
     if (use_mc) {
       r = multimem_ld_reduce_bf16x8(c.mc + in_off + v * 16);
@@ -107,7 +108,21 @@ allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n,
       for (int p = 0; p < c.world; ++p) *(uint4*)(c.bufs[(c.rank + p) % c.world] + out_off + v * 16) = r;
     }
   }
-  rank_barrier(c, 1, epoch);
+  rank_barrier(c, 1, epoch, blk);
+}
+
+__global__ void __launch_bounds__(512)
+allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int use_mc) {
+  allreduce_bf16_body(c, in_off, out_off, n, epoch, use_mc, blockIdx.x, gridDim.x);
+}
+
+// Every rank of the group inside ONE cooperative launch on one GPU (block groups play the ranks, plain loads and stores
+// play the peer accesses): the way to exercise the flag protocol and the data movement where only one GPU is available,
+// because kernels that wait on one another must never be separate launches on the same GPU.
+__global__ void __launch_bounds__(512)
+allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int nblk) {
+  c.rank = blockIdx.x / nblk;
+  allreduce_bf16_body(c, in_off, out_off, n, epoch, 0, blockIdx.x % nblk, nblk);
 }
 
 // A wait that nothing satisfies (used by the failure-detection test): returns after wait_ns with the status set.
@@ -131,6 +146,20 @@ MARY_API int mary_allreduce_bf16(const uint64_t* bufs, const uint64_t* sigs, uin
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
   allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epoch, (use_mc && mc) ? 1 : 0);
   MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// Single-GPU emulation of a `world`-rank all-reduce: bufs / sigs are `world` distinct buffers on the current device.
+MARY_API int mary_allreduce_bf16_emulated(const uint64_t* bufs, const uint64_t* sigs, int world, uint64_t in_off, uint64_t out_off,
+                                          int64_t n, uint32_t epoch, int grid, uint64_t wait_ns, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || (n % 8) || grid < 1 || grid * world > mary_num_sms()) return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = nullptr; c.rank = 0; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  size_t io = in_off, oo = out_off;
+  void* args[] = {&c, &io, &oo, &n, &epoch, &grid};
+  if (cudaLaunchCooperativeKernel((void*)allreduce_bf16_emulated_kernel, dim3(grid * world), dim3(512), args, 0, s) != cudaSuccess)
+    return MARY_ERR_CUDA;
   return MARY_OK;
 }
 

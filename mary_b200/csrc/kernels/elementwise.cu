@@ -27,6 +27,26 @@ template <typename T> __device__ __forceinline__ float ld(const T* p, int64_t i)
 template <> __device__ __forceinline__ float ld<float>(const float* p, int64_t i) { return p[i]; }
 template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) { return __bfloat162float(p[i]); }
 
+// 8-element vector access helpers (H % 8 == 0, rows 16-byte aligned)
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* f);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* f) {
+  const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  const uint4 v = *(const uint4*)p;
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { float2 t = __bfloat1622float2(h[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
+  uint4 v;
+  __nv_bfloat162* h = (__nv_bfloat162*)&v;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  *(uint4*)p = v;
+}
+
 // y = rms(x) * w   (w may be null).  x is bf16 or f32, y bf16.
 template <typename TI>
 __global__ void rmsnorm_kernel(const TI* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
@@ -35,13 +55,20 @@ __global__ void rmsnorm_kernel(const TI* __restrict__ x, const __nv_bfloat16* __
   __shared__ float red[32];
   const TI* xr = x + (int64_t)blockIdx.x * ldx;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = ld(xr, i); row[i] = v; ss += v * v; }
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float f[8];
+    load8(xr + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { row[i + j] = f[j]; ss += f[j] * f[j]; }
+  }
   const float inv = rsqrtf(block_sum(ss, red) / H + eps);
   __nv_bfloat16* yr = y + (int64_t)blockIdx.x * ldy;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = row[i] * inv;
-    if (w) v *= __bfloat162float(w[i]);
-    yr[i] = __float2bfloat16(v);
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float f[8], g[8];
+    if (w) load8(w + i, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = row[i + j] * inv * (w ? g[j] : 1.f);
+    store8(yr + i, f);
   }
 }
 
@@ -53,14 +80,24 @@ __global__ void add_rmsnorm_kernel(const TI* __restrict__ x, __nv_bfloat16* __re
   __shared__ float red[32];
   const int64_t o = (int64_t)blockIdx.x * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    __nv_bfloat16 r = __float2bfloat16(__bfloat162float(res[o + i]) + ld(x, o + i));
-    res[o + i] = r;
-    float v = __bfloat162float(r);
-    row[i] = v; ss += v * v;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float a[8], r[8];
+    load8(x + o + i, a);
+    load8(res + o + i, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = __bfloat162float(__float2bfloat16(r[j] + a[j]));
+    store8(res + o + i, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { row[i + j] = r[j]; ss += r[j] * r[j]; }
   }
   const float inv = rsqrtf(block_sum(ss, red) / H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) y[o + i] = __float2bfloat16(row[i] * inv * __bfloat162float(w[i]));
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float f[8], g[8];
+    load8(w + i, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = row[i + j] * inv * g[j];
+    store8(y + o + i, f);
+  }
 }
 
 // Gemma sandwich step: h = (h + rms(a) * w_post) * scalar ; x = rms(h) * w_next (skipped when w_next is null)
@@ -71,20 +108,36 @@ __global__ void norm_add_norm_kernel(const TI* __restrict__ a, const __nv_bfloat
   __shared__ float red[32];
   const int64_t o = (int64_t)blockIdx.x * H;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) { float v = ld(a, o + i); row[i] = v; ss += v * v; }
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float f[8];
+    load8(a + o + i, f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { row[i + j] = f[j]; ss += f[j] * f[j]; }
+  }
   const float inv = rsqrtf(block_sum(ss, red) / H + eps);
   float ss2 = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    // the normed branch output is rounded to bf16 like the unfused op sequence would
-    float n = __bfloat162float(__float2bfloat16(row[i] * inv * __bfloat162float(w_post[i])));
-    __nv_bfloat16 r = __float2bfloat16((__bfloat162float(h[o + i]) + n) * scalar);
-    h[o + i] = r;
-    float v = __bfloat162float(r);
-    row[i] = v; ss2 += v * v;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float g[8], r[8];
+    load8(w_post + i, g);
+    load8(h + o + i, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      // the normed branch output is rounded to bf16 like the unfused op sequence would
+      const float n = __bfloat162float(__float2bfloat16(row[i + j] * inv * g[j]));
+      r[j] = __bfloat162float(__float2bfloat16((r[j] + n) * scalar));
+      row[i + j] = r[j]; ss2 += r[j] * r[j];
+    }
+    store8(h + o + i, r);
   }
   if (w_next == nullptr) return;
   const float inv2 = rsqrtf(block_sum(ss2, red) / H + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x) xo[o + i] = __float2bfloat16(row[i] * inv2 * __bfloat162float(w_next[i]));
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float f[8], g[8];
+    load8(w_next + i, g);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = row[i + j] * inv2 * g[j];
+    store8(xo + o + i, f);
+  }
 }
 
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int F, int64_t n, int act) {
@@ -208,7 +261,7 @@ MARY_API int mary_rmsnorm(const void* x, int x_is_f32, const void* w, void* y, i
                           cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   size_t sm = (size_t)H * 4;
-  if (sm > 48 * 1024) return MARY_ERR_BAD_ARG;
+  if (sm > 48 * 1024 || (H & 7) || (ldx & 7) || (ldy & 7)) return MARY_ERR_BAD_ARG;
   if (x_is_f32) rmsnorm_kernel<float><<<T, NT, sm, s>>>((const float*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
   else rmsnorm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
   MARY_CHECK_LAUNCH();
@@ -218,7 +271,7 @@ MARY_API int mary_rmsnorm(const void* x, int x_is_f32, const void* w, void* y, i
 MARY_API int mary_add_rmsnorm(const void* x, int x_is_f32, void* res, const void* w, void* y, int T, int H, float eps, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   size_t sm = (size_t)H * 4;
-  if (sm > 48 * 1024) return MARY_ERR_BAD_ARG;
+  if (sm > 48 * 1024 || (H & 7)) return MARY_ERR_BAD_ARG;
   if (x_is_f32) add_rmsnorm_kernel<float><<<T, NT, sm, s>>>((const float*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
   else add_rmsnorm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
   MARY_CHECK_LAUNCH();
@@ -229,7 +282,7 @@ MARY_API int mary_norm_add_norm(const void* a, int a_is_f32, const void* w_post,
                                 float eps, float scalar, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   size_t sm = (size_t)H * 4;
-  if (sm > 48 * 1024) return MARY_ERR_BAD_ARG;
+  if (sm > 48 * 1024 || (H & 7)) return MARY_ERR_BAD_ARG;
   if (a_is_f32) norm_add_norm_kernel<float><<<T, NT, sm, s>>>((const float*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
   else norm_add_norm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
   MARY_CHECK_LAUNCH();

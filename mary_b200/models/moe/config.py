@@ -43,6 +43,7 @@ class MoEConfig:
     rms_norm_eps: float = 1e-6
     num_mtp_layers: int = 0
     tie_word_embeddings: bool = False
+    shared_expert_nvfp4: bool = False    # run the shared expert through the NVFP4 grouped GEMM as one more expert
 
     def to_json(self) -> dict:
         d = asdict(self)
@@ -78,7 +79,7 @@ def k3_class_config() -> MoEConfig:
                      q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
                      first_k_dense=1, dense_intermediate_size=18432, n_routed_experts=384, num_experts_per_tok=8,
                      n_shared_experts=1, moe_intermediate_size=2048, router="sigmoid", n_group=8, topk_group=4,
-                     routed_scaling_factor=2.5, vocab_size=163840, num_mtp_layers=1, act="swiglu")
+                     routed_scaling_factor=2.5, vocab_size=163840, num_mtp_layers=1, act="swiglu", shared_expert_nvfp4=True)
 
 
 def tiny_moe_config(attention: str = "mla", **kw) -> MoEConfig:

@@ -103,9 +103,13 @@ class MoEFFN(nn.Module):
         self.w_router = _P(E, c.hidden_size, dtype=dtype, device=device)
         self.router_bias = nn.Parameter(torch.zeros(E, dtype=torch.float32, device=device), requires_grad=False) \
             if c.router == "sigmoid" else None
+        # the shared expert is either a bf16 dense FFN (tensor parallel) or, with `shared_expert_nvfp4`, one more NVFP4
+        # expert appended behind the local routed ones (index e_local) that every token visits with weight 1
+        self.shared_in_experts = bool(c.shared_expert_nvfp4 and c.n_shared_experts == 1)
         self.shared = DenseFFN(c.hidden_size, c.moe_intermediate_size * c.n_shared_experts, par, c.act, dtype, device) \
-            if c.n_shared_experts else None
+            if (c.n_shared_experts and not self.shared_in_experts) else None
         self.experts: NVFP4Experts | None = None        # set by the loader / random init
+        self._tail = {}
 
     def route(self, x):
         c = self.c
@@ -118,6 +122,18 @@ class MoEFFN(nn.Module):
         if self.par.size > 1:                 # keep the entries of the local experts, renumbered from zero
             local = (idx >= self.e0) & (idx < self.e0 + self.e_local)
             idx = torch.where(local, idx - self.e0, torch.full_like(idx, -1))
+        if self.shared_in_experts:
+            T = x.shape[0]
+            tail = self._tail.get((T, x.device))
+            if tail is None:
+                # with replicated tokens every rank holds the shared expert; rank r serves the tokens t = r (mod size)
+                mine = (torch.arange(T, device=x.device) % self.par.size) == self.par.rank
+                sh = torch.where(mine, self.e_local, -1).to(torch.int32)[:, None]
+                tail = (sh, torch.ones(T, 1, dtype=torch.float32, device=x.device))
+                self._tail[(T, x.device)] = tail
+            idx = torch.cat([idx.to(torch.int32), tail[0]], 1)
+            w = torch.cat([w.float(), tail[1]], 1)
+            return experts_forward(x, idx, w, self.experts, None)
         # the shared expert's partial sum rides along in the un-permute (one pass over the hidden state)
         shared = ops.linear(ops.linear_glu(x, self.shared.w_gu, self.c.act), self.shared.w_down) if self.shared is not None else None
         return experts_forward(x, idx, w, self.experts, shared)
@@ -248,5 +264,6 @@ def init_random_(model: MoEDecoder, seed: int = 0, std: float = 0.02, expert_sla
     n_slabs = len(moes) if expert_slabs is None else max(1, min(expert_slabs, len(moes)))
     for i, m in enumerate(moes):
         if i < n_slabs:
-            slabs.append(NVFP4Experts.random(m.e_local, c.hidden_size, c.moe_intermediate_size, dev, std, seed + 1 + i, c.act))
+            slabs.append(NVFP4Experts.random(m.e_local + (1 if m.shared_in_experts else 0), c.hidden_size, c.moe_intermediate_size,
+                                             dev, std, seed + 1 + i, c.act))
         m.experts = slabs[i % n_slabs]

@@ -26,12 +26,19 @@ def _gu(t, r, n):
     return torch.cat([t[r * k:(r + 1) * k], t[F + r * k:F + (r + 1) * k]], 0)
 
 
-def slice_experts(ex: NVFP4Experts, r: int, n: int) -> NVFP4Experts:
-    e = ex.E // n
+def slice_experts(ex: NVFP4Experts, r: int, n: int, tail: int = 0) -> NVFP4Experts:
+    """Experts ``[r*e, (r+1)*e)`` of the routed ones, followed by the ``tail`` shared experts that every rank keeps."""
+    e = (ex.E - tail) // n
     a, b = r * e, (r + 1) * e
     r13, r2 = 2 * ex.F, ex.H
-    return NVFP4Experts(e, ex.H, ex.F, ex.w13_q[a * r13:b * r13], ex.w13_sf[a * r13 // 128:b * r13 // 128], ex.w13_s2[a:b],
-                        ex.w2_q[a * r2:b * r2], ex.w2_sf[a * r2 // 128:b * r2 // 128], ex.w2_s2[a:b], ex.act)
+
+    def cut(t, per):
+        parts = [t[a * per:b * per]]
+        if tail:
+            parts.append(t[(ex.E - tail) * per:ex.E * per])
+        return torch.cat(parts, 0) if tail else parts[0]
+    return NVFP4Experts(e + tail, ex.H, ex.F, cut(ex.w13_q, r13), cut(ex.w13_sf, r13 // 128), cut(ex.w13_s2, 1),
+                        cut(ex.w2_q, r2), cut(ex.w2_sf, r2 // 128), cut(ex.w2_s2, 1), ex.act)
 
 
 def shard_from_full(full: MoEDecoder, par, device=None) -> MoEDecoder:
@@ -62,7 +69,7 @@ def shard_from_full(full: MoEDecoder, par, device=None) -> MoEDecoder:
             p.copy_(src.to(dev))
     for (_, a), (_, b) in zip(m.named_modules(), full.named_modules()):
         if isinstance(a, MoEFFN):
-            ex = slice_experts(b.experts, r, n)
+            ex = slice_experts(b.experts, r, n, 1 if b.shared_in_experts else 0)
             for f in ("w13_q", "w13_sf", "w13_s2", "w2_q", "w2_sf", "w2_s2"):
                 setattr(ex, f, getattr(ex, f).to(dev))
             a.experts = ex

@@ -342,7 +342,7 @@ def mla_attention(q, cache, meta, scale, nsplit: int | None = None):
     assert DK == 576 and cache.shape[1] == 16 and cache.shape[-1] == 576 and meta.page_size == 16
     blk_seq, blk_r0, NB = _row_tiles(meta, Hq)
     if nsplit is None:
-        nsplit = max(1, min(8, 148 // max(1, 2 * NB), meta.max_kv_len // 512))
+        nsplit = max(1, min(8, 148 // max(1, NB), meta.max_kv_len // 512))
     out = torch.empty(T, Hq, 512, dtype=torch.bfloat16, device=q.device)
     scratch = None
     if nsplit > 1:

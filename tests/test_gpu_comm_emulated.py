@@ -1,0 +1,50 @@
+"""The all-reduce kernel's protocol and data movement on ONE GPU: all ranks run as block groups of one cooperative launch
+(kernels that wait on each other are never separate launches on a GPU); plus the bounded wait."""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_emulated_allreduce_matches_sum(world):
+    from mary_b200.ops.cuda import _stream, check, declare, last_status, lib
+    declare("mary_allreduce_bf16_emulated", "ppillliils")
+    region = 4 << 20
+    bufs = [torch.zeros(2 * region, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    sigs = [torch.zeros(1024, dtype=torch.int32, device="cuda") for _ in range(world)]
+    bp = (ctypes.c_uint64 * 8)(*[b.data_ptr() for b in bufs])
+    sp = (ctypes.c_uint64 * 8)(*[s.data_ptr() for s in sigs])
+    epoch = 0
+    for n in (8, 4096 + 8, 384 * 2048):
+        torch.manual_seed(n)
+        xs = [torch.randn(n, device="cuda").bfloat16() for _ in range(world)]
+        want = torch.stack([x.float() for x in xs]).sum(0)
+        for rep in range(2):                                   # flags are reused with a growing epoch
+            for b, x in zip(bufs, xs):
+                b[:n * 2].view(torch.bfloat16).copy_(x)
+            epoch += 1
+            check(lib().mary_allreduce_bf16_emulated(bp, sp, world, 0, region, n, epoch, 16, int(2e9), _stream()), "allreduce_emulated")
+            torch.cuda.synchronize()
+            assert last_status() == 0
+            for b in bufs:                                      # every rank holds the full sum
+                got = b[region:region + n * 2].view(torch.bfloat16).float()
+                assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+            assert torch.equal(bufs[0][region:region + n * 2], bufs[-1][region:region + n * 2])
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    from mary_b200.ops.cuda import _stream, check, declare, last_status, lib
+    declare("mary_wait_flag", "piiiils")
+    sig = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    sp = (ctypes.c_uint64 * 8)(sig.data_ptr())
+    check(lib().mary_wait_flag(sp, 0, 1, 5, 77, int(0.2e9), _stream()), "wait_flag")     # nothing ever sets flag 5
+    torch.cuda.synchronize()
+    assert last_status() == 3                                   # MARY_ERR_TIMEOUT_PEER, and the kernel returned
+    assert (torch.ones(8, device="cuda") * 3).sum().item() == 24
+    sig[6] = 99
+    check(lib().mary_wait_flag(sp, 0, 1, 6, 99, int(0.2e9), _stream()), "wait_flag")     # a satisfied wait sets nothing
+    torch.cuda.synchronize()
+    assert last_status() == 0
