@@ -81,10 +81,12 @@ def bench_attn():
         cache.k[0].normal_()
         cache.v[0].normal_()
         q = torch.randn(B, Hq, D, device="cuda").bfloat16()
-        ms = time_op(lambda: K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, win))
         span = L if win == 0 else min(L, win)
-        gb = B * span * Hkv * D * 2 * 2 / ms / 1e6
-        print(f"decode attn B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, {gb:.0f} GB/s, {gb / hbm:.2f} {tag}")
+        for kernel in ("general", "decode"):
+            ms = time_op(lambda: K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, win, kernel=kernel))
+            gb = B * span * Hkv * D * 2 * 2 / ms / 1e6
+            print(f"decode attn [{kernel}] B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, {gb:.0f} GB/s, "
+                  f"{gb / hbm:.2f} {tag}")
 
 
 def bench_mla(B: int = 32, L: int = 4096, Hq: int = 64, q_len: int = 3, iters: int = 5):
@@ -109,12 +111,40 @@ def bench_mla(B: int = 32, L: int = 4096, Hq: int = 64, q_len: int = 3, iters: i
     assert K.last_status() == 0
 
 
+def bench_moe(E: int = 48, H: int = 7168, F: int = 2048, T: int = 384, k: int = 8, iters: int = 5):
+    """Decode-shaped expert MLP: every expert is visited, so the step streams all expert weights once (HBM-bound)."""
+    from . import cuda as K, cuda_moe
+    from .moe import NVFP4Experts
+    hbm, tf, tag = peaks()
+    ex = NVFP4Experts.random(E, H, F, "cuda", seed=0)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    idx = torch.stack([torch.randperm(E, device="cuda")[:k] for _ in range(T)]).to(torch.int32)
+    w = torch.rand(T, k, device="cuda")
+    plan = cuda_moe.moe_plan(idx, E, 32)
+    xq, sfx, _ = cuda_moe.quantize_rows(x, 32, plan.src_of, identity=False, rows=plan.max_rows)
+    ms13 = time_op(lambda: cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, F, H, E, "swiglu"), iters=iters)
+    h = cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, F, H, E, "swiglu")
+    hq, sfh, _ = cuda_moe.quantize_rows(h, 32, plan.src_of, identity=True, rows=plan.max_rows)
+    ms2 = time_op(lambda: cuda_moe.grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, H, F, E, None), iters=iters)
+    b13 = E * 2 * F * H * (0.5 + 1 / 16)
+    b2 = E * H * F * (0.5 + 1 / 16)
+    for name, ms, b in (("w13+glu", ms13, b13), ("w2", ms2, b2)):
+        print(f"nvfp4 grouped {name} E={E} H={H} F={F} T={T} k={k}: {ms:.4f} ms, weights {b / 1e6:.0f} MB, {b / ms / 1e6:.0f} GB/s "
+              f"({b / ms / 1e6 / hbm:.2f} {tag})")
+    full = time_op(lambda: cuda_moe.experts_forward(x, idx, w, ex), iters=iters)
+    print(f"whole expert MLP (plan, quantise, 2 GEMMs, un-permute): {full:.4f} ms, {(b13 + b2) / full / 1e6:.0f} GB/s "
+          f"({(b13 + b2) / full / 1e6 / hbm:.2f} {tag})")
+    assert K.last_status() == 0
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     if what in ("gemm", "all"):
         bench_gemm()
     if what in ("attn", "all"):
         bench_attn()
+    if what in ("moe", "all"):
+        bench_moe()
     if what in ("mla", "all"):
         bench_mla()
         bench_mla(Hq=8)

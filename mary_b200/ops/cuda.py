@@ -240,13 +240,43 @@ def _q_blocks(meta, rq: int):
     return cache[key]
 
 
-def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: int | None = None, nsplit: int | None = None):
+declare("mary_paged_attention_decode", "ppppppppp" + "iii" + "llll" + "iiiiii" + "ff" + "ps")
+
+
+def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsplit):
+    """Decode-shaped batches (few rows per kv head, equal K and V widths of 64/128/256): the bandwidth-oriented kernel."""
+    T, Hq, D = q.shape
+    Hkv = kcache.shape[2]
+    G = Hq // Hkv
+    cap = 4 if D == 256 else 8
+    rq = max(1, min(cap // G, meta.max_q_len))
+    blk_seq, blk_q0, NB = _q_blocks(meta, rq)
+    if nsplit is None:
+        want = max(1, 592 // max(1, NB * Hkv))
+        span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
+        nsplit = max(1, min(want, 32, span // 64))
+    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    scratch = None
+    if nsplit > 1:
+        scratch = torch.empty(lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
+    check(lib().mary_paged_attention_decode(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
+                                            _p(meta.q_start), _p(blk_seq), _p(blk_q0), NB, meta.page_table.shape[1], meta.page_size,
+                                            kcache.stride(1), kcache.stride(0), vcache.stride(1), vcache.stride(0), Hq, Hkv, D, rq,
+                                            nsplit, window, scale, softcap, _p(scratch), _stream()), "paged_attention_decode")
+    return out
+
+
+def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: int | None = None, nsplit: int | None = None,
+                    kernel: str = "auto"):
     """``q[T, Hq, DK]``; caches ``[pages, page, Hkv, D]`` (a latent cache is ``Hkv = 1`` with ``dv`` < DK and
     ``vcache is kcache``).  Returns ``[T, Hq, DV]``."""
     T, Hq, DK = q.shape
     Hkv = kcache.shape[2] if kcache.dim() == 4 else 1
     DV = dv or vcache.shape[-1]
     G = Hq // Hkv
+    if kernel != "general" and kcache.dim() == 4 and DK == DV and DK in (64, 128, 256) and G <= (4 if DK == 256 else 8) \
+            and (meta.max_q_len <= 8 or kernel == "decode"):
+        return _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsplit)
     maxr = lib().mary_paged_attention_max_rows(DV)
     if G > maxr:
         # more query heads per kv head than one CTA can hold: fold the surplus into extra "kv heads" that alias

@@ -112,9 +112,12 @@ def test_paged_attention_decode_and_prefill(K, Hq, Hkv, D, window, softcap):
         cache.v[0].normal_()
         q = torch.randn(sum(q_lens), Hq, D, device="cuda").bfloat16()
         want = ref.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, window, softcap)
-        for nsplit in (None, 1, 3):
-            got = K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, window, softcap, nsplit=nsplit)
-            assert _rel(got, want) < 2e-2, (S_lens, nsplit, _rel(got, want))
+        for kernel in ("general", "decode"):
+            if kernel == "decode" and Hq // Hkv > (4 if D == 256 else 8):
+                continue
+            for nsplit in (None, 1, 3):
+                got = K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, window, softcap, nsplit=nsplit, kernel=kernel)
+                assert _rel(got, want) < 2e-2, (kernel, S_lens, nsplit, _rel(got, want))
 
 
 def test_qk_norm_rope_append_matches_reference(K):
