@@ -125,6 +125,8 @@ allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t
   allreduce_bf16_body(c, in_off, out_off, n, epoch, 0, blockIdx.x % nblk, nblk);
 }
 
+__global__ void rank_barrier_kernel(const CommCtx c, uint32_t epoch, int slot_block) { rank_barrier(c, 0, epoch, slot_block); }
+
 // A wait that nothing satisfies (used by the failure-detection test): returns after wait_ns with the status set.
 __global__ void wait_flag_kernel(const CommCtx c, uint32_t slot, uint32_t want) {
   const uint32_t* mine = c.sigs[c.rank] + slot;
@@ -145,6 +147,18 @@ MARY_API int mary_allreduce_bf16(const uint64_t* bufs, const uint64_t* sigs, uin
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
   allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epoch, (use_mc && mc) ? 1 : 0);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// Barrier between the ranks as a kernel of its own (one block): everything launched before it on every rank's stream has
+// completed and is visible when it returns.  `slot_block` selects the flag slots (use one that no all-reduce grid touches).
+MARY_API int mary_rank_barrier(const uint64_t* sigs, int rank, int world, uint32_t epoch, int slot_block, uint64_t wait_ns, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS) return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = nullptr; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  rank_barrier_kernel<<<1, 32, 0, s>>>(c, epoch, slot_block);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

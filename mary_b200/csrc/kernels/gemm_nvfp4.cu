@@ -43,6 +43,7 @@ struct FP4Params {
   const uint8_t* sfx;             // [tile, K/64, 512]
   const float* scale2;            // [E]
   __nv_bfloat16* out;             // [padded rows, n_out]
+  const uint64_t* row_ptrs;       // optional: destination address of every padded row (may point into a peer GPU)
   int64_t ldo;
   int n_out;                      // output features (F with GLU)
   int rows_total;                 // weight rows per expert (2F with GLU)
@@ -191,7 +192,9 @@ gemm_nvfp4_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
             if (c0 + j < t.rows) {
               const float a = __uint_as_float(r[j]) * s2;
               const float v = GLU ? glu_f(p.act, a, __uint_as_float(r2[j]) * s2) : a;
-              p.out[(int64_t)(t.row0 + c0 + j) * p.ldo + n] = __float2bfloat16(v);
+              __nv_bfloat16* dst = p.row_ptrs ? (__nv_bfloat16*)p.row_ptrs[t.row0 + c0 + j]
+                                              : p.out + (int64_t)(t.row0 + c0 + j) * p.ldo;
+              dst[n] = __float2bfloat16(v);
             }
           }
         }
@@ -229,14 +232,18 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const FP4Params& p, cud
 //       tile at byte (r%32)*16 + (r/32)*4 + j)
 // tiles [max_tiles] of {expert, row0, rows, sf_tile}, *n_tiles valid; nt = token-tile width (32 or 128)
 // out   [padded rows, n_out] bf16
-MARY_API int mary_gemm_nvfp4_grouped(const void* wq, const void* sfw, const float* scale2, const void* xq, const void* sfx,
-                                     const void* tiles, const int* n_tiles, void* out, int64_t ldo, int E, int n_out, int K,
-                                     int64_t x_rows, int nt, int glu, cudaStream_t s) {
+//
+// row_ptrs (optional, [padded rows] device addresses): when given, row r of the result is written to row_ptrs[r] instead
+// of out + r * ldo.  The addresses may lie in another GPU's memory (peer mapping): this is how the expert-parallel
+// combine sends every expert output row straight to the rank that owns the token, from inside the GEMM epilogue.
+MARY_API int mary_gemm_nvfp4_grouped_ex(const void* wq, const void* sfw, const float* scale2, const void* xq, const void* sfx,
+                                        const void* tiles, const int* n_tiles, void* out, int64_t ldo, int E, int n_out, int K,
+                                        int64_t x_rows, int nt, int glu, const uint64_t* row_ptrs, cudaStream_t s) {
   const int rows_total = glu ? 2 * n_out : n_out;
   if ((K % KSTEP) || (n_out % BM) || (nt != 32 && nt != 128)) return MARY_ERR_BAD_ARG;
   FP4Params p;
   p.tiles = (const Tile*)tiles; p.n_tiles = n_tiles; p.sfw = (const uint8_t*)sfw; p.sfx = (const uint8_t*)sfx;
-  p.scale2 = scale2; p.out = (__nv_bfloat16*)out; p.ldo = ldo; p.n_out = n_out; p.rows_total = rows_total; p.K = K;
+  p.scale2 = scale2; p.out = (__nv_bfloat16*)out; p.row_ptrs = row_ptrs; p.ldo = ldo; p.n_out = n_out; p.rows_total = rows_total; p.K = K;
   p.k_blocks = K / KSTEP; p.w_tiles = n_out / BM; p.act = glu ? glu - 1 : 0; p.status = mary_status_ptr();
   CUtensorMap tw, tx;
   int rc = mary_make_tmap_2d(&tw, wq, 2, (uint64_t)E * rows_total, K / 2, K / 2, BM, BKB, 1);
@@ -245,4 +252,10 @@ MARY_API int mary_gemm_nvfp4_grouped(const void* wq, const void* sfw, const floa
   if (rc) return rc;
   if (glu) return nt == 32 ? launch<32, true>(tw, tx, p, s) : launch<128, true>(tw, tx, p, s);
   return nt == 32 ? launch<32, false>(tw, tx, p, s) : launch<128, false>(tw, tx, p, s);
+}
+
+MARY_API int mary_gemm_nvfp4_grouped(const void* wq, const void* sfw, const float* scale2, const void* xq, const void* sfx,
+                                     const void* tiles, const int* n_tiles, void* out, int64_t ldo, int E, int n_out, int K,
+                                     int64_t x_rows, int nt, int glu, cudaStream_t s) {
+  return mary_gemm_nvfp4_grouped_ex(wq, sfw, scale2, xq, sfx, tiles, n_tiles, out, ldo, E, n_out, K, x_rows, nt, glu, nullptr, s);
 }

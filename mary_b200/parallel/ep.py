@@ -1,0 +1,134 @@
+"""Expert parallelism with tokens on their home rank: dispatch / combine as peer stores from our own kernels
+(``csrc/kernels/ep_a2a.cu``), no library all-to-all.
+
+Every rank owns ``E / world`` experts and four symmetric slabs: received activation codes, their scale tiles, the return
+address of every received row, and the combine buffer its own tokens' expert outputs come back into.  One MoE layer is
+
+    counts -> barrier -> plan -> dispatch (quantise + peer stores) -> barrier -> w13 GEMM -> quantise -> w2 GEMM whose
+    epilogue stores each row into the home rank's combine buffer -> barrier -> weighted sum over the k slots.
+
+``EPLayer`` runs that sequence for one rank; ``emulate`` drives several ranks that live on ONE device phase by phase (the
+barriers are kernels of their own, never waits inside the data kernels, so stream order can stand in for them), which is
+how the path is tested where only one GPU is available."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from ..ops import cuda_moe
+from ..ops.cuda import _p, _stream, check, declare, lib
+from ..ops.moe import NVFP4Experts
+
+declare("mary_ep_counts", "piiiips")
+declare("mary_ep_plan", "piiiiipppps")
+declare("mary_ep_dispatch", "plp" + "iiiiiiiii" + "pp" + "ppp" + "s")
+declare("mary_ep_return_ptrs", "pppiiiiipps")
+declare("mary_rank_barrier", "piiiils")
+declare("mary_gemm_nvfp4_grouped_ex", "pppppppp" + "liiilii" + "ps")
+
+
+def _ptrs(tensors):
+    return (ctypes.c_uint64 * 8)(*[int(t.data_ptr()) if hasattr(t, "data_ptr") else int(t) for t in tensors])
+
+
+class EPBuffers:
+    """The symmetric slabs of one rank (plain tensors; ``peer_*`` hold every rank's base address)."""
+
+    def __init__(self, world: int, E: int, H: int, F: int, t_cap: int, k: int, nt: int, device, alloc=None):
+        alloc = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
+        self.world, self.E, self.H, self.F, self.t_cap, self.k, self.nt = world, E, H, F, t_cap, k, nt
+        e_local = E // world
+        entries = world * t_cap * k
+        self.cap_rows = (entries + min(entries, e_local) * (nt - 1) + nt - 1) // nt * nt
+        self.entry_stride = t_cap * k
+        self.count_mat = alloc(world * E, torch.int32)
+        self.xq = alloc(self.cap_rows * (H // 2), torch.uint8)
+        self.sf = alloc((self.cap_rows // nt) * (H // 64) * 512, torch.uint8)
+        self.meta = alloc(self.cap_rows, torch.int32)
+        self.comb = alloc(self.entry_stride * H, torch.bfloat16)
+
+
+class EPLayer:
+    def __init__(self, rank: int, world: int, experts: NVFP4Experts, bufs: EPBuffers, peers: list[EPBuffers], sig_ptrs=None,
+                 wait_ns: int = int(2e9)):
+        self.rank, self.world, self.ex, self.b = rank, world, experts, bufs
+        self.e_local = bufs.E // world
+        dev = bufs.xq.device
+        self.p_count = _ptrs([p.count_mat for p in peers])
+        self.p_xq = _ptrs([p.xq for p in peers])
+        self.p_sf = _ptrs([p.sf for p in peers])
+        self.p_meta = _ptrs([p.meta for p in peers])
+        self.p_comb = _ptrs([p.comb for p in peers])
+        self.tiles = torch.empty(bufs.cap_rows // bufs.nt, 4, dtype=torch.int32, device=dev)
+        self.plan_meta = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.send_base = torch.empty(bufs.E, dtype=torch.int32, device=dev)
+        self.send_cnt = torch.empty(bufs.E, dtype=torch.int32, device=dev)
+        self.row_ptrs = torch.zeros(bufs.cap_rows, dtype=torch.int64, device=dev)
+        self.ident = torch.arange(bufs.entry_stride, dtype=torch.int32, device=dev)
+        self.sig_ptrs, self.wait_ns, self.epoch = sig_ptrs, wait_ns, 0
+
+    # ---- phases (each is a few kernel launches on the current stream)
+    def barrier(self):
+        if self.sig_ptrs is None:
+            return                      # single-device emulation: stream order separates the phases
+        self.epoch += 1
+        check(lib().mary_rank_barrier(self.sig_ptrs, self.rank, self.world, self.epoch, 60, self.wait_ns, _stream()), "rank_barrier")
+
+    def counts(self, idx):
+        T, k = idx.shape
+        check(lib().mary_ep_counts(_p(idx), T * k, self.b.E, self.rank, self.world, self.p_count, _stream()), "ep_counts")
+
+    def plan_and_dispatch(self, x, idx):
+        b = self.b
+        T, k = idx.shape
+        check(lib().mary_ep_plan(_p(b.count_mat), self.world, self.rank, b.E, self.e_local, b.nt, _p(self.tiles), _p(self.plan_meta),
+                                 _p(self.send_base), _p(self.send_cnt), _stream()), "ep_plan")
+        check(lib().mary_ep_dispatch(_p(x), x.stride(0), _p(idx), T * k, k, b.E, self.e_local, b.H, b.nt, self.rank, self.world,
+                                     b.entry_stride, _p(self.send_base), _p(self.send_cnt), self.p_xq, self.p_sf, self.p_meta,
+                                     _stream()), "ep_dispatch")
+
+    def experts(self):
+        b, ex = self.b, self.ex
+        plan = cuda_moe.Plan()
+        plan.tiles, plan.meta, plan.max_rows, plan.nt = self.tiles, self.plan_meta, b.cap_rows, b.nt
+        xq = b.xq.view(b.cap_rows, b.H // 2)
+        sfx = b.sf.view(b.cap_rows // b.nt, b.H // 64, 512)
+        h = cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
+        hq, sfh, _ = cuda_moe.quantize_rows(h, b.nt, None, identity=True, rows=b.cap_rows, n_rows=self.plan_meta[1:2])
+        check(lib().mary_ep_return_ptrs(_p(b.meta), _p(self.plan_meta), _p(self.tiles), b.cap_rows // b.nt, b.nt, b.entry_stride, b.H,
+                                        self.world, self.p_comb, _p(self.row_ptrs), _stream()), "ep_return_ptrs")
+        check(lib().mary_gemm_nvfp4_grouped_ex(_p(ex.w2_q), _p(ex.w2_sf), _p(ex.w2_s2), _p(hq), _p(sfh), _p(self.tiles), _p(self.plan_meta),
+                                               None, 0, ex.E, ex.H, ex.F, b.cap_rows, b.nt, 0, _p(self.row_ptrs), _stream()),
+              "gemm_nvfp4_grouped")
+
+    def finish(self, w, T, shared=None):
+        b = self.b
+        k = w.shape[1]
+        comb = b.comb.view(b.entry_stride, b.H)
+        plan = cuda_moe.Plan()
+        plan.row_of = self.ident
+        return cuda_moe.unpermute(comb, plan, w, T, k, shared)
+
+    def forward(self, x, idx, w, shared=None):
+        """One MoE layer for this rank's tokens (``idx`` holds GLOBAL expert ids)."""
+        idx = idx.to(torch.int32).contiguous()
+        self.counts(idx)
+        self.barrier()
+        self.plan_and_dispatch(x, idx)
+        self.barrier()
+        self.experts()
+        self.barrier()
+        return self.finish(w, x.shape[0], shared)
+
+
+def emulate(layers: list[EPLayer], xs, idxs, ws):
+    """Drive ``world`` ranks that share one device, phase by phase; returns each rank's output."""
+    idxs = [i.to(torch.int32).contiguous() for i in idxs]
+    for l, i in zip(layers, idxs):
+        l.counts(i)
+    for l, x, i in zip(layers, xs, idxs):
+        l.plan_and_dispatch(x, i)
+    for l in layers:
+        l.experts()
+    return [l.finish(w, x.shape[0]) for l, x, w in zip(layers, xs, ws)]

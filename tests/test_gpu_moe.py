@@ -71,3 +71,29 @@ def test_grouped_gemm_is_exact_on_its_quantised_operands():
         a = ref.dequantize_nvfp4(hq[r:r + 1].cpu(), hrm[r:r + 1].cpu()).double()
         want = (a @ ex.dense("w2", e).double().T).float()
         assert _rel(y[r:r + 1].cpu(), want) < 1e-2      # bf16 output rounding only
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ep_all_to_all_dispatch_combine_emulated(world):
+    """Expert-parallel all-to-all (dispatch by peer stores, combine from the GEMM epilogue) with all ranks on one device:
+    every rank's output must equal the single-rank expert MLP over the union of the experts."""
+    from mary_b200.ops import cuda, cuda_moe
+    from mary_b200.models.moe.shard import slice_experts
+    from mary_b200.parallel.ep import EPBuffers, EPLayer, emulate
+    torch.manual_seed(world)
+    E, H, F, k, T = 8 * world, 512, 256, 2, 40
+    ex = NVFP4Experts.random(E, H, F, "cuda", std=0.05, seed=3)
+    bufs = [EPBuffers(world, E, H, F, t_cap=64, k=k, nt=32, device="cuda") for _ in range(world)]
+    layers = [EPLayer(r, world, slice_experts(ex, r, world), bufs[r], bufs) for r in range(world)]
+    xs = [torch.randn(T - 3 * r, H, device="cuda").bfloat16() for r in range(world)]       # ranks hold different token counts
+    routed = [cuda.router_topk(torch.randn(x.shape[0], E, device="cuda"), k, "softmax") for x in xs]
+    outs = emulate(layers, xs, [i for i, _ in routed], [w for _, w in routed])
+    torch.cuda.synchronize()
+    assert cuda.last_status() == 0
+    for x, (idx, w), got in zip(xs, routed, outs):
+        want = cuda_moe.experts_forward(x, idx, w, ex, None, 32)
+        assert _rel(got, want) < 2e-2, _rel(got, want)
+    # a second layer call reuses the slabs
+    outs2 = emulate(layers, xs, [i for i, _ in routed], [w for _, w in routed])
+    for a, b in zip(outs, outs2):
+        assert torch.equal(a, b)
