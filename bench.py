@@ -73,7 +73,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--model", default="k3", choices=["k3", "inkling", "tiny"])
+    ap.add_argument("--model", default="k3", choices=["k3", "inkling", "gemma12b", "tiny"],
+                    help="k3 is the headline; the others time the remaining workload configurations with the same harness")
+    ap.add_argument("--ep", default="replicated", choices=["replicated", "a2a"],
+                    help="expert parallel layout for N > 1: replicated tokens + reduction, or home-rank tokens + all-to-all")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--spec", type=int, default=None)
@@ -96,10 +99,22 @@ def main():
     from mary_b200.runtime.kv_cache import PagedKVCache
     from mary_b200.runtime.spec_decode import SpecDecoder
 
-    cfg = {"k3": k3_class_config, "inkling": inkling_style_config, "tiny": tiny_moe_config}[args.model]()
-    B = args.batch or {"k3": 128, "inkling": 64, "tiny": 8}[args.model]
-    ctx = args.ctx or {"k3": 4096, "inkling": 1024, "tiny": 256}[args.model]
+    is_gemma = args.model == "gemma12b"
+    if is_gemma:
+        from mary_b200.models.gemma4 import Gemma4Model, gemma_12b_config
+        cfg = gemma_12b_config()
+        cfg.name, cfg.num_mtp_layers, cfg.attention = "gemma-4-12b-style", 0, "gqa"
+    else:
+        cfg = {"k3": k3_class_config, "inkling": inkling_style_config, "tiny": tiny_moe_config}[args.model]()
+    B = args.batch or {"k3": 128, "inkling": 64, "tiny": 8, "gemma12b": 32}[args.model]
+    ctx = args.ctx or {"k3": 4096, "inkling": 1024, "tiny": 256, "gemma12b": 2048}[args.model]
     k = args.spec if args.spec is not None else (2 if cfg.num_mtp_layers else 0)
+    a2a = args.ep == "a2a" and world > 1 and not is_gemma
+    if a2a:
+        assert B % world == 0
+        B_local = B // world
+    else:
+        B_local = B
     reduced = False
     if args.layers:
         cfg.num_hidden_layers, reduced = args.layers, True
@@ -111,25 +126,34 @@ def main():
             symm = SymmetricHeap(rank, world, dev, max_bytes=(B * (1 + k)) * cfg.hidden_size * 4 * 2)
         except Exception as ex:  # the fused path must never be silently absent
             raise RuntimeError(f"fused communication requested but the symmetric heap failed: {ex}") from ex
-    par = ParallelGroup(rank, world, "fused" if symm else "nccl", symm=symm)
+    par = ParallelGroup(rank, world, "fused" if symm else "nccl", symm=symm, ep_mode="a2a" if a2a else "replicated")
+    if a2a:
+        from mary_b200.parallel.ep import distributed_factory
+        par.ep_factory = distributed_factory(rank, world, dev, t_cap=B_local * (1 + k))
 
     # ---------------------------------------------------------------- model
     t0 = time.time()
-    model = MoEDecoder(cfg, par=par, dtype=torch.bfloat16, device=dev)
+    model = Gemma4Model(cfg, tp=par, dtype=torch.bfloat16, device=dev) if is_gemma else MoEDecoder(cfg, par=par, dtype=torch.bfloat16, device=dev)
+    B_global, B = B, B_local
     steps_total = W + args.steps + 8
     max_len = ctx + (steps_total + 8) * (1 + k) + 16
     max_len = (max_len + 15) // 16 * 16
     n_cache_layers = cfg.num_hidden_layers + cfg.num_mtp_layers
     page = 16
     pages = B * (max_len // page) + 8
-    kv_bytes = pages * page * (576 if cfg.attention == "mla" else 2 * max(cfg.num_key_value_heads // world, 1) * cfg.head_dim) * 2 * n_cache_layers
-    e_local = cfg.n_routed_experts // world
-    slab_bytes = e_local * (3 * cfg.hidden_size * cfg.moe_intermediate_size) * (0.5 + 1 / 16) + 1
-    free, total = torch.cuda.mem_get_info(dev)
-    n_moe = sum(1 for i in range(cfg.num_hidden_layers) if not cfg.is_dense(i)) + cfg.num_mtp_layers
-    budget = free - kv_bytes - 12 * (1 << 30)
-    slabs = int(max(1, min(n_moe, budget // slab_bytes)))
-    init_random_(model, seed=0, expert_slabs=slabs)
+    if is_gemma:
+        from mary_b200.models.gemma4.weights import init_random_ as gemma_init
+        gemma_init(model, 0)
+        slabs = n_moe = 0
+    else:
+        kv_bytes = pages * page * (576 if cfg.attention == "mla" else 2 * max(cfg.num_key_value_heads // par.tp_size, 1) * cfg.head_dim) * 2 * n_cache_layers
+        e_local = cfg.n_routed_experts // world
+        slab_bytes = e_local * (3 * cfg.hidden_size * cfg.moe_intermediate_size) * (0.5 + 1 / 16) + 1
+        free, total = torch.cuda.mem_get_info(dev)
+        n_moe = sum(1 for i in range(cfg.num_hidden_layers) if not cfg.is_dense(i)) + cfg.num_mtp_layers
+        budget = free - kv_bytes - 12 * (1 << 30)
+        slabs = int(max(1, min(n_moe, budget // slab_bytes)))
+        init_random_(model, seed=0, expert_slabs=slabs)
     # non-expert weights must be identical on every rank that replicates them; experts differ per rank by construction
     spec = model.kv_spec()
     cache = PagedKVCache(spec["num_layers"], pages, page, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16, device=dev,
@@ -191,7 +215,10 @@ def main():
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
-    emitted = int(total_emitted.item())
+    em_t = total_emitted.clone()
+    if a2a:
+        dist.all_reduce(em_t)                        # every rank decodes its own sequences
+    emitted = int(em_t.item())
     t_ms = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t_ms, op=dist.ReduceOp.MAX)
@@ -213,6 +240,10 @@ def main():
         fed_pin.copy_(outs[2])
     barrier()
     e2e_s = time.perf_counter() - t_start
+    if a2a:
+        tt = torch.tensor([e2e_tokens], dtype=torch.int64, device=dev)
+        dist.all_reduce(tt)
+        e2e_tokens = int(tt.item())
     t_e = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
@@ -221,7 +252,7 @@ def main():
 
     # ---------------------------------------------------------------- TTFT: a real prefill of one context
     ttft = None
-    if not args.no_ttft:
+    if not args.no_ttft and not a2a:
         try:
             pc = PagedKVCache(spec["num_layers"], (ctx + 64) // page + 2, page, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16,
                               device=dev, latent_dim=spec.get("latent_dim"))
@@ -241,7 +272,7 @@ def main():
             ttft = f"failed: {type(ex).__name__}: {ex}"
 
     if rank == 0:
-        tok_per_seq_step = emitted / (B * args.steps)
+        tok_per_seq_step = emitted / (B_global * args.steps)
         line = {
             "metric": "decode tok/s (max over ranks), K3-class MLA + NVFP4 MoE, 2-token MTP speculation" if args.model == "k3" else f"decode tok/s {cfg.name}",
             "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": W,
@@ -249,8 +280,9 @@ def main():
             "dtype": "bf16 activations, NVFP4 experts", "data": "synthetic token ids, random-init weights, synthetic KV context",
             "impl": "ours",
             "config": {"model": cfg.name + (" (REDUCED layers: debug)" if reduced else ""), "layers": cfg.num_hidden_layers,
-                       "global_batch": B, "seq_len": ctx, "spec_tokens": k,
-                       "parallelism": f"ep{world}+tp{world}-attention" if world > 1 else "single",
+                       "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,
+                       "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
+                                       f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
                        "comm": par.mode if world > 1 else "none", "cuda_graph": dec.graph is not None,
                        "expert_slabs_resident": slabs, "moe_layers": n_moe,
                        "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",

@@ -18,6 +18,7 @@ from .config import MoEConfig
 
 class NoParallel:
     rank, size = 0, 1
+    tp_rank, tp_size, ep_rank, ep_size, ep_mode = 0, 1, 0, 1, "replicated"
 
     def reduce(self, partial, residual=None):
         """Sum the partial hidden states over the group.  Returns a tensor every rank holds."""
@@ -35,8 +36,8 @@ class GQAAttention(nn.Module):
     def __init__(self, c: MoEConfig, layer_idx: int, par, dtype, device):
         super().__init__()
         self.c, self.li, self.par = c, layer_idx, par
-        self.n_q = c.num_attention_heads // par.size
-        self.n_kv = max(c.num_key_value_heads // par.size, 1)
+        self.n_q = c.num_attention_heads // par.tp_size
+        self.n_kv = max(c.num_key_value_heads // par.tp_size, 1)
         D = c.head_dim
         self.w_qkv = _P((self.n_q + 2 * self.n_kv) * D, c.hidden_size, dtype=dtype, device=device)
         self.w_o = _P(c.hidden_size, self.n_q * D, dtype=dtype, device=device)
@@ -58,7 +59,7 @@ class MLAAttention(nn.Module):
         super().__init__()
         assert c.kv_lora_rank == 512 and c.qk_rope_head_dim == 64 and c.qk_nope_head_dim == 128 and c.v_head_dim == 128
         self.c, self.li, self.par = c, layer_idx, par
-        self.H = c.num_attention_heads // par.size
+        self.H = c.num_attention_heads // par.tp_size
         kw = dict(dtype=dtype, device=device)
         self.w_qa_kva = _P(c.q_lora_rank + 576, c.hidden_size, **kw)       # replicated
         self.qa_norm = _P(c.q_lora_rank, **kw)
@@ -85,7 +86,7 @@ class DenseFFN(nn.Module):
     def __init__(self, H, F, par, act, dtype, device):
         super().__init__()
         self.par, self.act = par, act
-        Fl = F // par.size
+        Fl = F // par.tp_size
         self.w_gu = _P(2 * Fl, H, dtype=dtype, device=device)
         self.w_down = _P(H, Fl, dtype=dtype, device=device)
 
@@ -98,8 +99,9 @@ class MoEFFN(nn.Module):
         super().__init__()
         self.c, self.par = c, par
         E = c.n_routed_experts
-        self.e_local = E // par.size
-        self.e0 = par.rank * self.e_local
+        self.e_local = E // par.ep_size
+        self.e0 = par.ep_rank * self.e_local
+        self.ep_layer = None                             # parallel.ep.EPLayer in all-to-all mode
         self.w_router = _P(E, c.hidden_size, dtype=dtype, device=device)
         self.router_bias = nn.Parameter(torch.zeros(E, dtype=torch.float32, device=device), requires_grad=False) \
             if c.router == "sigmoid" else None
@@ -119,7 +121,13 @@ class MoEFFN(nn.Module):
 
     def forward(self, x):
         idx, w = self.route(x)
-        if self.par.size > 1:                 # keep the entries of the local experts, renumbered from zero
+        if self.par.ep_mode == "a2a" and self.par.ep_size > 1:
+            # tokens are local: routed experts through the all-to-all (global expert ids), shared expert computed at home
+            if self.ep_layer is None:
+                self.ep_layer = self.par.ep_factory(self.experts, self.c)
+            shared = ops.linear(ops.linear_glu(x, self.shared.w_gu, self.c.act), self.shared.w_down) if self.shared is not None else None
+            return self.ep_layer.forward(x, idx, w, shared)
+        if self.par.ep_size > 1:              # keep the entries of the local experts, renumbered from zero
             local = (idx >= self.e0) & (idx < self.e0 + self.e_local)
             idx = torch.where(local, idx - self.e0, torch.full_like(idx, -1))
         if self.shared_in_experts:
@@ -127,7 +135,7 @@ class MoEFFN(nn.Module):
             tail = self._tail.get((T, x.device))
             if tail is None:
                 # with replicated tokens every rank holds the shared expert; rank r serves the tokens t = r (mod size)
-                mine = (torch.arange(T, device=x.device) % self.par.size) == self.par.rank
+                mine = (torch.arange(T, device=x.device) % self.par.ep_size) == self.par.ep_rank
                 sh = torch.where(mine, self.e_local, -1).to(torch.int32)[:, None]
                 tail = (sh, torch.ones(T, 1, dtype=torch.float32, device=x.device))
                 self._tail[(T, x.device)] = tail
@@ -200,7 +208,7 @@ class MoEDecoder(nn.Module):
         n = c.num_hidden_layers + c.num_mtp_layers
         if c.attention == "mla":
             return dict(num_layers=n, kv_heads=1, head_dim=576, latent_dim=576)
-        return dict(num_layers=n, kv_heads=max(c.num_key_value_heads // self.par.size, 1), head_dim=c.head_dim)
+        return dict(num_layers=n, kv_heads=max(c.num_key_value_heads // self.par.tp_size, 1), head_dim=c.head_dim)
 
     def head_weight(self):
         return self.embed if self.lm_head is None else self.lm_head

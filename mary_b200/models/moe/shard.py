@@ -42,7 +42,8 @@ def slice_experts(ex: NVFP4Experts, r: int, n: int, tail: int = 0) -> NVFP4Exper
 
 
 def shard_from_full(full: MoEDecoder, par, device=None) -> MoEDecoder:
-    r, n = par.rank, par.size
+    r, n = par.tp_rank, par.tp_size        # attention / dense split; experts split by the expert-parallel coordinates
+    er, en = par.ep_rank, par.ep_size
     dev = device or full.embed.device
     m = MoEDecoder(full.cfg, par=par, dtype=full.dtype, device=dev)
     fm = dict(full.named_modules())
@@ -69,7 +70,7 @@ def shard_from_full(full: MoEDecoder, par, device=None) -> MoEDecoder:
             p.copy_(src.to(dev))
     for (_, a), (_, b) in zip(m.named_modules(), full.named_modules()):
         if isinstance(a, MoEFFN):
-            ex = slice_experts(b.experts, r, n, 1 if b.shared_in_experts else 0)
+            ex = slice_experts(b.experts, er, en, 1 if b.shared_in_experts else 0)
             for f in ("w13_q", "w13_sf", "w13_s2", "w2_q", "w2_sf", "w2_s2"):
                 setattr(ex, f, getattr(ex, f).to(dev))
             a.experts = ex

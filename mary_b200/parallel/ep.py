@@ -66,14 +66,15 @@ class EPLayer:
         self.send_cnt = torch.empty(bufs.E, dtype=torch.int32, device=dev)
         self.row_ptrs = torch.zeros(bufs.cap_rows, dtype=torch.int64, device=dev)
         self.ident = torch.arange(bufs.entry_stride, dtype=torch.int32, device=dev)
-        self.sig_ptrs, self.wait_ns, self.epoch = sig_ptrs, wait_ns, 0
+        self.sig_ptrs, self.wait_ns = sig_ptrs, wait_ns
+        self._epoch_box = [0]           # shared between the layers that use the same flag slots
 
     # ---- phases (each is a few kernel launches on the current stream)
     def barrier(self):
         if self.sig_ptrs is None:
             return                      # single-device emulation: stream order separates the phases
-        self.epoch += 1
-        check(lib().mary_rank_barrier(self.sig_ptrs, self.rank, self.world, self.epoch, 60, self.wait_ns, _stream()), "rank_barrier")
+        self._epoch_box[0] += 1
+        check(lib().mary_rank_barrier(self.sig_ptrs, self.rank, self.world, self._epoch_box[0], 60, self.wait_ns, _stream()), "rank_barrier")
 
     def counts(self, idx):
         T, k = idx.shape
@@ -132,3 +133,44 @@ def emulate(layers: list[EPLayer], xs, idxs, ws):
     for l in layers:
         l.experts()
     return [l.finish(w, x.shape[0]) for l, x, w in zip(layers, xs, ws)]
+
+
+def distributed_factory(rank: int, world: int, device, t_cap: int, nt: int = 32, sig_ptrs=None, wait_ns: int = int(2e9)):
+    """Returns ``factory(experts, cfg) -> EPLayer`` for real multi-GPU runs: the slabs come from the symmetric-memory
+    allocator (every rank learns every peer's base address) and the phases are separated by the rank-barrier kernel.
+    All layers of a model share ONE set of slabs (layers run one after the other on the stream)."""
+    import types
+
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    state = {}
+
+    def factory(experts, cfg):
+        if "bufs" not in state:
+            def alloc(n, dt):
+                t = symm_mem.empty(n, dtype=dt, device=device)
+                t.zero_()
+                return t
+            b = EPBuffers(world, cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, t_cap, cfg.num_experts_per_tok, nt,
+                          device, alloc)
+            peers = [types.SimpleNamespace() for _ in range(world)]
+            for name in ("count_mat", "xq", "sf", "meta", "comb"):
+                hdl = symm_mem.rendezvous(getattr(b, name), dist.group.WORLD)
+                for r in range(world):
+                    setattr(peers[r], name, int(hdl.buffer_ptrs[r]))
+            sp = sig_ptrs
+            if sp is None:
+                flags = symm_mem.empty(1024, dtype=torch.int32, device=device)
+                flags.zero_()
+                fh = symm_mem.rendezvous(flags, dist.group.WORLD)
+                sp = (ctypes.c_uint64 * 8)(*list(fh.buffer_ptrs)[:world])
+                state["flags"] = flags
+            torch.cuda.synchronize()
+            dist.barrier()
+            state.update(bufs=b, peers=peers, sig=sp, shared_layer_state={})
+        layer = EPLayer(rank, world, experts, state["bufs"], state["peers"], state["sig"], wait_ns)
+        # one epoch counter for all layers: they share the flag slots
+        layer._epoch_box = state.setdefault("epoch_box", [0])
+        return layer
+
+    return factory

@@ -14,13 +14,21 @@ from .. import ops
 
 
 class ParallelGroup:
-    def __init__(self, rank: int = 0, size: int = 1, mode: str = "nccl", group=None, symm=None):
+    def __init__(self, rank: int = 0, size: int = 1, mode: str = "nccl", group=None, symm=None, ep_mode: str = "replicated"):
+        """``ep_mode="replicated"``: tokens are replicated, attention is tensor parallel over the group and every rank adds
+        the partial sums of its own experts (one reduction per block).  ``ep_mode="a2a"``: tokens stay on their home rank
+        (data-parallel attention, full heads everywhere) and the routed experts are reached through the all-to-all of
+        ``parallel.ep``; nothing is reduced."""
         self.rank, self.size, self.mode, self.group, self.symm = rank, size, mode, group, symm
+        self.ep_mode = ep_mode
+        self.tp_rank, self.tp_size = (0, 1) if ep_mode == "a2a" else (rank, size)
+        self.ep_rank, self.ep_size = rank, size
+        self.ep_factory = None          # callable(experts, cfg) -> EPLayer, set by the launcher in a2a mode
         self.bytes_reduced = 0
         self.calls = 0
 
     def reduce(self, partial, residual=None):
-        if self.size == 1:
+        if self.tp_size == 1:
             return partial
         self.calls += 1
         self.bytes_reduced += partial.numel() * partial.element_size()
@@ -36,7 +44,7 @@ class ParallelGroup:
     def row_linear(self, x, w, lora=None):
         """Row-parallel GEMM: the result is this rank's partial sum (the caller reduces it).  In fused mode the GEMM
         epilogue stores straight into the symmetric input region, so the reduction kernel needs no staging copy."""
-        if self.size > 1 and self.mode == "fused" and self.symm is not None and x.is_cuda:
+        if self.tp_size > 1 and self.mode == "fused" and self.symm is not None and x.is_cuda:
             from ..ops import cuda as K
             M, N, Kd = x.shape[0], w.shape[0], x.shape[1]
             out = self.symm.input_view((M, N))

@@ -32,6 +32,11 @@ def test_sharded_model_matches_single_gpu():
     assert "MODEL_OK" in out, out[-2000:]
 
 
+def test_expert_parallel_all_to_all_matches_single_gpu():
+    out = _torchrun(["a2a"])
+    assert "A2A_OK" in out, out[-2000:]
+
+
 def test_peer_wait_times_out_with_status_and_context_survives():
     # NVLS off: a rank that leaves must not hold a multicast binding (plain peer loads only)
     out = _torchrun(["timeout"], env={"NCCL_NVLS_ENABLE": "0", "MARY_MULTIMEM": "0"})
