@@ -150,13 +150,15 @@ class Leaf:
     def torch(self):
         """Zero-copy torch view over the mapping (read-only memory: clone before writing)."""
         import torch
+        import warnings
         if self.elem == Elem.BF16:
-            return torch.frombuffer(self.payload, dtype=torch.bfloat16).reshape(self.dims)
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")
+                return torch.frombuffer(self.payload, dtype=torch.bfloat16).reshape(self.dims)
         if self.elem in (Elem.NVFP4, Elem.MXFP4):
             raise LeafError("use fp4_parts() for block-scaled leaves")
         dt = {Elem.F32: torch.float32, Elem.F16: torch.float16, Elem.I32: torch.int32, Elem.I64: torch.int64,
               Elem.U8: torch.uint8}[self.elem]
-        import warnings
         with warnings.catch_warnings():
             warnings.simplefilter("ignore")
             return torch.frombuffer(self.payload, dtype=dt).reshape(self.dims)
