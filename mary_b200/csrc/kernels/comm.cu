@@ -81,8 +81,14 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
 
 // In-place on the symmetric buffer: input region at in_off, output region at out_off (bytes), n bf16 elements (n % 8 == 0).
 // `blk` of `nblk` is this block's index within its rank's grid.
-__device__ void allreduce_bf16_body(const CommCtx& c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int use_mc, int blk,
+// The epoch of the flags lives in device memory (`epoch_slot`, one word per block, advanced by the block itself), so a
+// launch recorded in a CUDA graph uses a fresh epoch at every replay.
+__device__ void allreduce_bf16_body(const CommCtx& c, size_t in_off, size_t out_off, int64_t n, uint32_t* epoch_slot, int use_mc, int blk,
                                     int nblk) {
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
   if (!rank_barrier(c, 0, epoch, blk)) return;
   const int64_t nvec = n / 8;                                  // 16-byte vectors
   const int64_t per = (nvec + c.world - 1) / c.world;
@@ -109,23 +115,30 @@ __device__ void allreduce_bf16_body(const CommCtx& c, size_t in_off, size_t out_
     }
   }
   rank_barrier(c, 1, epoch, blk);
+  if (threadIdx.x == 0) *epoch_slot = epoch;
 }
 
 __global__ void __launch_bounds__(512)
-allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int use_mc) {
-  allreduce_bf16_body(c, in_off, out_off, n, epoch, use_mc, blockIdx.x, gridDim.x);
+allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t* epochs, int use_mc) {
+  allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, use_mc, blockIdx.x, gridDim.x);
 }
 
 // Every rank of the group inside ONE cooperative launch on one GPU (block groups play the ranks, plain loads and stores
 // play the peer accesses): the way to exercise the flag protocol and the data movement where only one GPU is available,
 // because kernels that wait on one another must never be separate launches on the same GPU.
 __global__ void __launch_bounds__(512)
-allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t epoch, int nblk) {
+allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t* epochs, int nblk) {
   c.rank = blockIdx.x / nblk;
-  allreduce_bf16_body(c, in_off, out_off, n, epoch, 0, blockIdx.x % nblk, nblk);
+  allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, 0, blockIdx.x % nblk, nblk);
 }
 
-__global__ void rank_barrier_kernel(const CommCtx c, uint32_t epoch, int slot_block) { rank_barrier(c, 0, epoch, slot_block); }
+__global__ void rank_barrier_kernel(const CommCtx c, uint32_t* epoch_slot, int slot_block) {
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
+  __syncthreads();
+  rank_barrier(c, 0, epoch_s, slot_block);
+  if (threadIdx.x == 0) *epoch_slot = epoch_s;
+}
 
 // A wait that nothing satisfies (used by the failure-detection test): returns after wait_ns with the status set.
 __global__ void wait_flag_kernel(const CommCtx c, uint32_t slot, uint32_t want) {
@@ -139,39 +152,40 @@ __global__ void wait_flag_kernel(const CommCtx c, uint32_t slot, uint32_t want) 
 }  // namespace
 
 // bufs / sigs: arrays of `world` device addresses (as integers).  grid blocks x 512 threads; every rank must pass the
-// same grid, n, offsets and epoch.  Flag pad: at least grid * 2 * 8 words, zeroed once at set-up.
+// same grid, n and offsets, and make the same sequence of calls.  Flag pad: at least grid * 2 * 8 words, zeroed once at
+// set-up; `epochs`: `grid` device words of this rank (zeroed at set-up), advanced by the kernel.
 MARY_API int mary_allreduce_bf16(const uint64_t* bufs, const uint64_t* sigs, uint64_t mc, int rank, int world, uint64_t in_off,
-                                 uint64_t out_off, int64_t n, uint32_t epoch, int grid, int use_mc, uint64_t wait_ns, cudaStream_t s) {
+                                 uint64_t out_off, int64_t n, uint32_t* epochs, int grid, int use_mc, uint64_t wait_ns, cudaStream_t s) {
   if (world < 1 || world > MAX_RANKS || (n % 8) || (in_off % 16) || (out_off % 16) || grid < 1) return MARY_ERR_BAD_ARG;
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
-  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epoch, (use_mc && mc) ? 1 : 0);
+  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
 
 // Barrier between the ranks as a kernel of its own (one block): everything launched before it on every rank's stream has
 // completed and is visible when it returns.  `slot_block` selects the flag slots (use one that no all-reduce grid touches).
-MARY_API int mary_rank_barrier(const uint64_t* sigs, int rank, int world, uint32_t epoch, int slot_block, uint64_t wait_ns, cudaStream_t s) {
+MARY_API int mary_rank_barrier(const uint64_t* sigs, int rank, int world, uint32_t* epoch_slot, int slot_block, uint64_t wait_ns, cudaStream_t s) {
   if (world < 1 || world > MAX_RANKS) return MARY_ERR_BAD_ARG;
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = nullptr; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
-  rank_barrier_kernel<<<1, 32, 0, s>>>(c, epoch, slot_block);
+  rank_barrier_kernel<<<1, 32, 0, s>>>(c, epoch_slot, slot_block);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
 
 // Single-GPU emulation of a `world`-rank all-reduce: bufs / sigs are `world` distinct buffers on the current device.
 MARY_API int mary_allreduce_bf16_emulated(const uint64_t* bufs, const uint64_t* sigs, int world, uint64_t in_off, uint64_t out_off,
-                                          int64_t n, uint32_t epoch, int grid, uint64_t wait_ns, cudaStream_t s) {
+                                          int64_t n, uint32_t* epochs, int grid, uint64_t wait_ns, cudaStream_t s) {
   if (world < 1 || world > MAX_RANKS || (n % 8) || grid < 1 || grid * world > mary_num_sms()) return MARY_ERR_BAD_ARG;
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = nullptr; c.rank = 0; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
   size_t io = in_off, oo = out_off;
-  void* args[] = {&c, &io, &oo, &n, &epoch, &grid};
+  void* args[] = {&c, &io, &oo, &n, &epochs, &grid};
   if (cudaLaunchCooperativeKernel((void*)allreduce_bf16_emulated_kernel, dim3(grid * world), dim3(512), args, 0, s) != cudaSuccess)
     return MARY_ERR_CUDA;
   return MARY_OK;

@@ -24,7 +24,7 @@ declare("mary_ep_counts", "piiiips")
 declare("mary_ep_plan", "piiiiipppps")
 declare("mary_ep_dispatch", "plp" + "iiiiiiiii" + "pp" + "ppp" + "s")
 declare("mary_ep_return_ptrs", "pppiiiiipps")
-declare("mary_rank_barrier", "piiiils")
+declare("mary_rank_barrier", "piipils")
 declare("mary_gemm_nvfp4_grouped_ex", "pppppppp" + "liiilii" + "ps")
 
 
@@ -67,14 +67,14 @@ class EPLayer:
         self.row_ptrs = torch.zeros(bufs.cap_rows, dtype=torch.int64, device=dev)
         self.ident = torch.arange(bufs.entry_stride, dtype=torch.int32, device=dev)
         self.sig_ptrs, self.wait_ns = sig_ptrs, wait_ns
-        self._epoch_box = [0]           # shared between the layers that use the same flag slots
+        self.epoch_slot = torch.zeros(1, dtype=torch.int32, device=dev)   # device-resident, so graph replays advance it
 
     # ---- phases (each is a few kernel launches on the current stream)
     def barrier(self):
         if self.sig_ptrs is None:
             return                      # single-device emulation: stream order separates the phases
-        self._epoch_box[0] += 1
-        check(lib().mary_rank_barrier(self.sig_ptrs, self.rank, self.world, self._epoch_box[0], 60, self.wait_ns, _stream()), "rank_barrier")
+        check(lib().mary_rank_barrier(self.sig_ptrs, self.rank, self.world, self.epoch_slot.data_ptr(), 60, self.wait_ns, _stream()),
+              "rank_barrier")
 
     def counts(self, idx):
         T, k = idx.shape
@@ -169,8 +169,10 @@ def distributed_factory(rank: int, world: int, device, t_cap: int, nt: int = 32,
             dist.barrier()
             state.update(bufs=b, peers=peers, sig=sp, shared_layer_state={})
         layer = EPLayer(rank, world, experts, state["bufs"], state["peers"], state["sig"], wait_ns)
-        # one epoch counter for all layers: they share the flag slots
-        layer._epoch_box = state.setdefault("epoch_box", [0])
+        # one epoch word for all layers: they share the flag slots
+        if "epoch_slot" not in state:
+            state["epoch_slot"] = layer.epoch_slot
+        layer.epoch_slot = state["epoch_slot"]
         return layer
 
     return factory

@@ -13,7 +13,7 @@ import torch
 
 from ..ops.cuda import _stream, check, declare, lib
 
-declare("mary_allreduce_bf16", "pplii" + "llliiils")
+declare("mary_allreduce_bf16", "pplii" + "lllpiils")
 declare("mary_wait_flag", "piiiils")
 
 FLAG_WORDS = 64 * 2 * 8        # grid <= 64 blocks, two barriers, eight ranks
@@ -43,7 +43,7 @@ class SymmetricHeap:
             except Exception:
                 mc = 0
         self.mc = mc
-        self.epoch = 0
+        self.epochs = torch.zeros(64 + 8, dtype=torch.int32, device=self.dev)     # per-block flag epochs (+ barrier slots)
         torch.cuda.synchronize()
         dist.barrier()
 
@@ -74,9 +74,9 @@ class SymmetricHeap:
             self.buf[:n * 2].view(torch.bfloat16).copy_(partial.reshape(-1))
         if pad:
             self.buf[n * 2:nbytes].zero_()
-        self.epoch += 1
         check(lib().mary_allreduce_bf16(self.buf_ptrs, self.sig_ptrs, self.mc, self.rank, self.world, 0, self.region, n + pad,
-                                        self.epoch, self.grid, 1 if self.mc else 0, self.wait_ns, _stream()), "allreduce_bf16")
+                                        self.epochs.data_ptr(), self.grid, 1 if self.mc else 0, self.wait_ns, _stream()),
+              "allreduce_bf16")
         return self.buf[self.region:self.region + n * 2].view(torch.bfloat16).view(partial.shape)
 
     def wait_flag(self, slot: int, want: int):

@@ -11,13 +11,13 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_emulated_allreduce_matches_sum(world):
     from mary_b200.ops.cuda import _stream, check, declare, last_status, lib
-    declare("mary_allreduce_bf16_emulated", "ppillliils")
+    declare("mary_allreduce_bf16_emulated", "ppilllpils")
     region = 4 << 20
     bufs = [torch.zeros(2 * region, dtype=torch.uint8, device="cuda") for _ in range(world)]
     sigs = [torch.zeros(1024, dtype=torch.int32, device="cuda") for _ in range(world)]
     bp = (ctypes.c_uint64 * 8)(*[b.data_ptr() for b in bufs])
     sp = (ctypes.c_uint64 * 8)(*[s.data_ptr() for s in sigs])
-    epoch = 0
+    epochs = torch.zeros(16 * world, dtype=torch.int32, device="cuda")
     for n in (8, 4096 + 8, 384 * 2048):
         torch.manual_seed(n)
         xs = [torch.randn(n, device="cuda").bfloat16() for _ in range(world)]
@@ -25,8 +25,8 @@ def test_emulated_allreduce_matches_sum(world):
         for rep in range(2):                                   # flags are reused with a growing epoch
             for b, x in zip(bufs, xs):
                 b[:n * 2].view(torch.bfloat16).copy_(x)
-            epoch += 1
-            check(lib().mary_allreduce_bf16_emulated(bp, sp, world, 0, region, n, epoch, 16, int(2e9), _stream()), "allreduce_emulated")
+            check(lib().mary_allreduce_bf16_emulated(bp, sp, world, 0, region, n, epochs.data_ptr(), 16, int(2e9), _stream()),
+                  "allreduce_emulated")
             torch.cuda.synchronize()
             assert last_status() == 0
             for b in bufs:                                      # every rank holds the full sum
