@@ -89,6 +89,13 @@ def main():
     if args.impl == "reference":
         return reference_arm(args)
     W = max(args.warmup, 3)
+    # a benchmark that stops making progress must end by itself: dump the stacks and exit after the limit
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("MARY_BENCH_LIMIT_S", "540")), exit=True)
+
+    def say(msg):
+        if os.environ.get("RANK", "0") == "0":
+            print(f"[bench {time.strftime('%H:%M:%S')}] {msg}", file=sys.stderr, flush=True)
 
     from mary_b200.parallel.group import ParallelGroup, init_distributed
     rank, world, local = init_distributed()
@@ -119,6 +126,10 @@ def main():
     if args.layers:
         cfg.num_hidden_layers, reduced = args.layers, True
 
+    say(f"model {cfg.name}, {world} rank(s), batch {B}, ctx {ctx}, spec {k}, comm {args.comm}")
+    if world > 1 and args.comm == "nccl":
+        # the library arm is launched op by op: recording NCCL collectives into the step graph is not relied upon here
+        args.no_graph = True
     symm = None
     if world > 1 and args.comm == "fused":
         try:
@@ -168,6 +179,7 @@ def main():
     rng = np.random.default_rng(0)
     dec.set_context(np.full(B, ctx), rng.integers(0, cfg.vocab_size, B), rng.integers(0, cfg.vocab_size, (B, max(k, 1)))[:, :k])
     build_s = time.time() - t0
+    say(f"model and cache built in {build_s:.1f} s ({slabs} expert slabs resident)")
 
     if args.trace:
         from mary_b200.utils.trace import Tracer
@@ -188,7 +200,9 @@ def main():
     torch.cuda.synchronize()
     launches_per_step = K.LAUNCHES
     dec.set_context(np.full(B, ctx), rng.integers(0, cfg.vocab_size, B), rng.integers(0, cfg.vocab_size, (B, max(k, 1)))[:, :k])
+    say(f"eager step done ({launches_per_step} launches); capturing")
     dec.capture(warmup=1)
+    say("captured" if dec.graph is not None else "running without a graph")
     st = K.last_status()
     if st:
         raise RuntimeError(f"kernel status {st} during warm-up")
@@ -215,6 +229,7 @@ def main():
     barrier()
     ms = e0.elapsed_time(e1)
     clocks = sampler.stop()
+    say(f"timed region: {ms / args.steps:.3f} ms/step")
     em_t = total_emitted.clone()
     if a2a:
         dist.all_reduce(em_t)                        # every rank decodes its own sequences
@@ -249,6 +264,7 @@ def main():
         dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
     e2e_value = e2e_tokens / float(t_e.item())
     status = K.last_status()
+    say(f"end-to-end loop done, kernel status {status}")
 
     # ---------------------------------------------------------------- TTFT: a real prefill of one context
     ttft = None
@@ -296,6 +312,7 @@ def main():
             "kernel_status": status, "build_seconds": round(build_s, 1),
         }
         print(json.dumps(line))
+    faulthandler.cancel_dump_traceback_later()
     if world > 1:
         dist.destroy_process_group()
 

@@ -132,6 +132,67 @@ allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t
   allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, 0, blockIdx.x % nblk, nblk);
 }
 
+// Owner side of the reduce-scatter: one CTA per local token row.  Sums the `world` staged partial rows in rank order
+// (deterministic), adds the residual slice (kept sequence-sharded: every rank holds only its own rows), applies RMSNorm and
+// writes the normed row to EVERY rank's activation buffer — the all-gather — with one multimem store per 16 bytes, or
+// peer stores.  w == nullptr: no norm, the reduced row itself is broadcast (plain all-reduce of the partial sums).
+__global__ void rs_add_rmsnorm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ staging, __nv_bfloat16* __restrict__ h_slice,
+                                      const __nv_bfloat16* __restrict__ w, size_t x_off, int rpr, int H, float eps, int use_mc) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  float ss = 0.f;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < c.world; ++s) {
+      const uint4 v = *(const uint4*)(staging + ((int64_t)s * rpr + r) * H + i);
+      const __nv_bfloat162* vp = (const __nv_bfloat162*)&v;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(vp[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+    }
+    if (h_slice) {
+      uint4 hv = *(const uint4*)(h_slice + (int64_t)r * H + i);
+      __nv_bfloat162* hp = (__nv_bfloat162*)&hv;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(hp[j]);
+        hp[j] = __floats2bfloat162_rn(f.x + acc[2 * j], f.y + acc[2 * j + 1]);
+        float2 b = __bfloat1622float2(hp[j]);
+        acc[2 * j] = b.x; acc[2 * j + 1] = b.y;
+      }
+      *(uint4*)(h_slice + (int64_t)r * H + i) = hv;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { row[i + j] = acc[j]; ss += acc[j] * acc[j]; }
+  }
+  float inv = 1.f;
+  if (w) {
+    ss = warp_sum(ss);
+    const int wi = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) red[wi] = ss;
+    __syncthreads();
+    float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+    t = warp_sum(t);
+    inv = rsqrtf(t / H + eps);
+  }
+  const int64_t grow = (int64_t)c.rank * rpr + r;
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    uint4 o;
+    __nv_bfloat162* op = (__nv_bfloat162*)&o;
+    uint4 wv = make_uint4(0, 0, 0, 0);
+    if (w) wv = *(const uint4*)(w + i);
+    const __nv_bfloat162* wp = (const __nv_bfloat162*)&wv;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 g = w ? __bfloat1622float2(wp[j]) : make_float2(1.f, 1.f);
+      op[j] = __floats2bfloat162_rn(row[i + 2 * j] * inv * g.x, row[i + 2 * j + 1] * inv * g.y);
+    }
+    const size_t off = x_off + ((size_t)grow * H + i) * sizeof(__nv_bfloat16);
+    if (use_mc) multimem_st_v4(c.mc + off, o);
+    else for (int p = 0; p < c.world; ++p) *(uint4*)(c.bufs[(c.rank + p) % c.world] + off) = o;
+  }
+}
+
 __global__ void rank_barrier_kernel(const CommCtx c, uint32_t* epoch_slot, int slot_block) {
   __shared__ uint32_t epoch_s;
   if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
@@ -173,6 +234,21 @@ MARY_API int mary_rank_barrier(const uint64_t* sigs, int rank, int world, uint32
   for (int i = 0; i < world; ++i) { c.bufs[i] = nullptr; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
   rank_barrier_kernel<<<1, 32, 0, s>>>(c, epoch_slot, slot_block);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// staging: this rank's [world][rows_per_rank][H] bf16 (filled by the peers' GEMM epilogues); h_slice: this rank's residual rows
+// (updated in place; may be null); w: norm gain (null = no norm); the result row is written at byte offset x_off + row * H * 2 of
+// EVERY rank's symmetric buffer bufs[r] (multicast when mc != 0).  H % 8 == 0, H * 4 <= 48 KB.
+MARY_API int mary_rs_add_rmsnorm(const void* staging, void* h_slice, const void* w, const uint64_t* bufs, uint64_t mc, int rank, int world,
+                                 uint64_t x_off, int rows_per_rank, int H, float eps, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || (H & 7) || (size_t)H * 4 > 48 * 1024 || (x_off & 15)) return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = nullptr; }
+  c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = 0; c.status = mary_status_ptr();
+  rs_add_rmsnorm_kernel<<<rows_per_rank, 256, (size_t)H * 4, s>>>(c, (const __nv_bfloat16*)staging, (__nv_bfloat16*)h_slice,
+                                                                 (const __nv_bfloat16*)w, x_off, rows_per_rank, H, eps, mc ? 1 : 0);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

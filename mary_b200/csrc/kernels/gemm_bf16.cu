@@ -28,7 +28,7 @@ constexpr int BK = 64;       // K per stage: 64 bf16 = 128 bytes = one swizzle r
 constexpr int UMMA_K = 16;
 constexpr int NTHREADS = 192;
 
-enum { EPI_STORE_BF16 = 0, EPI_RED_F32 = 1, EPI_STORE_F32 = 2 };
+enum { EPI_STORE_BF16 = 0, EPI_RED_F32 = 1, EPI_STORE_F32 = 2, EPI_RS_BF16 = 3 };
 
 struct GemmParams {
   int rows_r, rows_c;        // extents of the row operand and the column operand (tiles are clipped to them)
@@ -42,10 +42,19 @@ struct GemmParams {
   int batch;                 // independent problems (z coordinate of both tensor maps)
   int64_t out_batch_stride;  // elements
   void* out;
+  // reduce-scatter epilogue (EPI_RS_BF16): token row t belongs to rank t / rs_rpr; this rank's partial row is stored into
+  // the owner's staging buffer rs_bufs[owner][rs_src][t % rs_rpr][:] (peer memory for owner != this rank)
+  uint64_t rs_bufs[8];
+  int rs_rpr, rs_src;
   const float* bias;         // optional, indexed by output feature
   float alpha;
   int* status;
 };
+
+__device__ __forceinline__ __nv_bfloat16* rs_row(const GemmParams& p, int token_row) {
+  const int owner = token_row / p.rs_rpr, lr = token_row - owner * p.rs_rpr;
+  return (__nv_bfloat16*)p.rs_bufs[owner] + ((int64_t)p.rs_src * p.rs_rpr + lr) * p.ldo;
+}
 
 template <int BN, bool GLU>
 struct Cfg {
@@ -189,7 +198,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
             for (int j = 0; j < 32; ++j) {
               if (j0 + j < p.rows_c) {
                 const int64_t o = obase + (int64_t)(j0 + j) * p.ldo + i;
-                if (p.epi == EPI_STORE_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16(v[j] + b);
+                if (p.epi == EPI_RS_BF16) rs_row(p, j0 + j)[i] = __float2bfloat16(v[j] + b);
+                else if (p.epi == EPI_STORE_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16(v[j] + b);
                 else if (p.epi == EPI_STORE_F32) ((float*)p.out)[o] = v[j] + b;
                 else atomicAdd((float*)p.out + o, v[j]);
               }
@@ -199,8 +209,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
           // i = token, j = output feature: out[i * ldo + j]; each thread writes 32 consecutive features
           if (i < p.rows_r) {
             const int64_t o = obase + (int64_t)i * p.ldo + j0;
-            if (p.epi == EPI_STORE_BF16) {
-              __nv_bfloat16* dst = (__nv_bfloat16*)p.out + o;
+            if (p.epi == EPI_STORE_BF16 || p.epi == EPI_RS_BF16) {
+              __nv_bfloat16* dst = p.epi == EPI_RS_BF16 ? rs_row(p, i) + j0 : (__nv_bfloat16*)p.out + o;
               if (j0 + 32 <= p.rows_c && ((uintptr_t)dst & 15) == 0) {
                 uint4 w[4];
                 uint32_t* wp = (uint32_t*)w;
@@ -277,9 +287,30 @@ static int make_tmap_3d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
 }
 
 // Batched form: `batch` independent problems; operand b starts at base + b * batch_stride (elements).
+static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
+                     int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
+                     const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream);
+
 MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
                                     int64_t ldo, int batch, int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha,
                                     int glu, int epi, int split_k, int swap, cudaStream_t stream) {
+  return gemm_impl(X, W, out, M, N, K, ldx, ldw, ldo, batch, bsx, bsw, bso, bias, alpha, glu, epi, split_k, swap, nullptr, 0, 0, 0, stream);
+}
+
+// Row-parallel GEMM fused with the reduce-scatter transfer: this rank's partial out[M, N] is not stored locally; row t goes
+// straight from the epilogue into the staging buffer of the rank that owns token t (rows_per_rank tokens per rank), slot
+// `src_rank`, over NVLink peer stores — tile by tile while the next tile's main loop runs.  rs_bufs[r] = address of rank r's
+// staging buffer [world][rows_per_rank][ldo] bf16.  The owner sums the `world` slots in a fixed order (comm.cu).
+MARY_API int mary_gemm_bf16_rs(const void* X, const void* W, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo,
+                               const uint64_t* rs_bufs, int world, int src_rank, int rows_per_rank, int swap, cudaStream_t stream) {
+  if (world < 1 || world > 8 || rows_per_rank * world < M) return MARY_ERR_BAD_ARG;
+  return gemm_impl(X, W, nullptr, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, nullptr, 1.0f, 0, EPI_RS_BF16, 1, swap, rs_bufs, world, src_rank,
+                   rows_per_rank, stream);
+}
+
+static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
+                     int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
+                     const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || batch < 1) return MARY_ERR_BAD_ARG;
   if (split_k < 1) split_k = 1;
   if (split_k > 1 && epi != EPI_RED_F32) return MARY_ERR_BAD_ARG;
@@ -301,6 +332,9 @@ MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int
   p.batch = batch;
   p.out_batch_stride = bso;
   p.out = out;
+  for (int i = 0; i < 8; ++i) p.rs_bufs[i] = (rs_bufs && i < rs_world) ? rs_bufs[i] : 0;
+  p.rs_rpr = rs_rpr > 0 ? rs_rpr : 1;
+  p.rs_src = rs_src;
   p.bias = bias;
   p.alpha = alpha;
   p.status = mary_status_ptr();
