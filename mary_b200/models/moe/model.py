@@ -224,6 +224,17 @@ class MoEDecoder(nn.Module):
             x, h = layer(x, h, meta, cache, nxt)
         return h
 
+    def trunk_range(self, ids_or_h, lo: int, hi: int, meta, cache):
+        """Layers ``[lo, hi)`` only (a pipeline stage): the first stage takes token ids, later stages take the residual
+        stream that the previous stage produced.  Returns the residual stream after layer ``hi - 1``."""
+        c = self.cfg
+        h = ops.embed(ids_or_h, self.embed) if lo == 0 else ids_or_h
+        x = ops.rmsnorm(h, self.layers[lo].ln_attn, c.rms_norm_eps)
+        for i in range(lo, hi):
+            nxt = self.layers[i + 1].ln_attn if i + 1 < hi else None
+            x, h = self.layers[i](x, h, meta, cache, nxt)
+        return h
+
     def hidden(self, ids, meta, cache):
         return ops.rmsnorm(self.trunk(ids, meta, cache), self.norm, self.cfg.rms_norm_eps)
 

@@ -48,3 +48,36 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     check(lib().mary_wait_flag(sp, 0, 1, 6, 99, int(0.2e9), _stream()), "wait_flag")     # a satisfied wait sets nothing
     torch.cuda.synchronize()
     assert last_status() == 0
+
+
+@pytest.mark.parametrize("world,T", [(2, 64), (4, 384), (8, 384)])
+def test_gemm_reduce_scatter_epilogue_and_fused_norm_allgather(world, T):
+    """GEMM -> reduce-scatter from the epilogue, then reduce + residual + RMSNorm -> all-gather, with the ranks as buffer
+    sets on one device (no kernel waits on another, so running the ranks one after the other is exact)."""
+    from mary_b200.ops import cuda
+    from mary_b200.ops import reference as ref
+    from mary_b200.parallel.sp import SequenceParallel
+    torch.manual_seed(world)
+    H, Kl = 512, 256
+    rpr = T // world
+    stag = [torch.zeros(world * rpr * H, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    xbuf = [torch.zeros(T * H, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    sps = [SequenceParallel(r, world, T, H, "cuda", stag[r], xbuf[r], [s.data_ptr() for s in stag], [x.data_ptr() for x in xbuf])
+           for r in range(world)]
+    xs = [torch.randn(T, Kl, device="cuda").bfloat16() for _ in range(world)]
+    ws = [(torch.randn(H, Kl, device="cuda") * 0.05).bfloat16() for _ in range(world)]
+    h = torch.randn(T, H, device="cuda").bfloat16()
+    gain = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    slices = [h[r * rpr:(r + 1) * rpr].clone() for r in range(world)]
+    for r in range(world):
+        sps[r].row_linear_rs(xs[r], ws[r])
+    outs = [sps[r].reduce_add_rmsnorm(slices[r], gain, 1e-6) for r in range(world)]
+    torch.cuda.synchronize()
+    assert cuda.last_status() == 0
+    partials = [(x.float() @ w.float().T).bfloat16().float() for x, w in zip(xs, ws)]
+    h_new = (h.float() + sum(partials)).bfloat16()
+    want = ref.rmsnorm(h_new, gain, 1e-6)
+    for r in range(world):
+        assert ((outs[r].float() - want.float()).abs().max() / want.float().abs().max()).item() < 2e-2
+        assert ((slices[r].float() - h_new[r * rpr:(r + 1) * rpr].float()).abs().max()).item() < 0.1
+    assert torch.equal(outs[0], outs[-1])                      # every rank holds the same gathered activations

@@ -68,3 +68,81 @@ def test_tp_ep_two_cpu_ranks_match_single_rank(attention, shared_fp4):
         assert p.exitcode == 0
     assert med < 1e-2 * scale and frac_ok >= 0.85, (med, frac_ok, scale)
     assert calls > 0                      # the group really reduced partial sums
+
+
+def test_balanced_split_minimises_the_heaviest_stage():
+    from mary_b200.parallel.pp import balanced_split
+    assert balanced_split([1, 1, 1, 1], 2) == [(0, 2), (2, 4)]
+    r = balanced_split([10, 1, 1, 1, 1, 10], 3)
+    assert r[0][0] == 0 and r[-1][1] == 6 and all(a[1] == b[0] for a, b in zip(r, r[1:]))
+    assert max(sum([10, 1, 1, 1, 1, 10][lo:hi]) for lo, hi in r) == 10
+    assert balanced_split([5], 1) == [(0, 1)]
+
+
+def _pp_worker(rank, world, port, cohorts, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mary_b200.models.moe import MoEDecoder, init_random_, tiny_moe_config
+        from mary_b200.parallel.pp import PipeChannel, PipelineStage, balanced_split
+        from mary_b200.runtime.batch import BatchMeta
+        from mary_b200.runtime.kv_cache import PagedKVCache
+        torch.manual_seed(0)
+        cfg = tiny_moe_config("gqa")
+        m = MoEDecoder(cfg, dtype=torch.float32)
+        init_random_(m, 0)
+        B, L, n_new = 2, 9, 5
+        rng = np.random.default_rng(5)
+        prompts = [rng.integers(0, cfg.vocab_size, (B, L)) for _ in range(cohorts)]
+        spec = m.kv_spec()
+        caches = []
+        for c in range(cohorts):
+            ca = PagedKVCache(spec["num_layers"], B * 2 + 1, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32)
+            for s in range(B):
+                ca.alloc.extend(s, L + n_new)
+            caches.append(ca)
+
+        def make_meta(c, q, kv_len):
+            table, _ = caches[c].alloc.page_table(list(range(B)))
+            return BatchMeta.build([q] * B, [kv_len] * B, table, 16), caches[c]
+
+        ranges = balanced_split([1] * cfg.num_hidden_layers, world)
+        st = PipelineStage(m, ranges, rank, PipeChannel(cfg.hidden_size, B * L, torch.float32, "cpu"))
+        res = st.generate(prompts, n_new, make_meta)
+        if rank == 0:
+            # single-process greedy on fresh caches
+            want = []
+            for c in range(cohorts):
+                ca = PagedKVCache(spec["num_layers"], B * 2 + 1, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32)
+                for s in range(B):
+                    ca.alloc.extend(s, L + n_new)
+                table, _ = ca.alloc.page_table(list(range(B)))
+                fed, kv, toks = torch.as_tensor(prompts[c], dtype=torch.int32), 0, [[] for _ in range(B)]
+                for _ in range(n_new):
+                    q = fed.shape[1]
+                    meta = BatchMeta.build([q] * B, [kv + q] * B, table, 16)
+                    with torch.no_grad():
+                        t = m.greedy(fed.reshape(-1), meta, ca, torch.arange(B) * q + (q - 1))
+                    kv += q
+                    for b in range(B):
+                        toks[b].append(int(t[b]))
+                    fed = t.to(torch.int32).view(B, 1)
+                want.append(toks)
+            out.put((res, want))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cohorts", [1, 3])
+def test_layer_pipeline_two_stages_with_cohorts_matches_single_process(cohorts):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_pp_worker, args=(r, 2, port, cohorts, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    res, want = q.get(timeout=240)
+    for p in ps:
+        p.join(60)
+    assert res == want
