@@ -83,6 +83,7 @@ def main():
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line then names a reduced config)")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--replicated-head", action="store_true", help="keep the whole LM head on every rank (default: vocabulary-parallel head)")
     ap.add_argument("--no-ttft", action="store_true")
     ap.add_argument("--trace", action="store_true", help="print a per-op device-time table of one eager step and exit")
     args = ap.parse_args()
@@ -137,7 +138,8 @@ def main():
             symm = SymmetricHeap(rank, world, dev, max_bytes=(B * (1 + k)) * cfg.hidden_size * 4 * 2)
         except Exception as ex:  # the fused path must never be silently absent
             raise RuntimeError(f"fused communication requested but the symmetric heap failed: {ex}") from ex
-    par = ParallelGroup(rank, world, "fused" if symm else "nccl", symm=symm, ep_mode="a2a" if a2a else "replicated")
+    par = ParallelGroup(rank, world, "fused" if symm else "nccl", symm=symm, ep_mode="a2a" if a2a else "replicated",
+                        vocab_parallel=not args.replicated_head)
     if a2a:
         from mary_b200.parallel.ep import distributed_factory
         par.ep_factory = distributed_factory(rank, world, dev, t_cap=B_local * (1 + k))
@@ -300,6 +302,7 @@ def main():
                        "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
                                        f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
                        "comm": par.mode if world > 1 else "none", "cuda_graph": dec.graph is not None,
+                       "lm_head": "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated",
                        "expert_slabs_resident": slabs, "moe_layers": n_moe,
                        "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",
                        "accepted_drafts_per_step": round(tok_per_seq_step - 1, 4)},

@@ -193,6 +193,57 @@ __global__ void rs_add_rmsnorm_kernel(const CommCtx c, const __nv_bfloat16* __re
   }
 }
 
+// Cross-rank arg-max merge for a vocabulary-parallel LM head.  Every rank holds, per token, the best (value, index) of its
+// own vocabulary shard; it stores the pair into slot [rank] of EVERY rank's pair table (8-byte peer stores), one barrier
+// makes the tables complete, and every rank picks the overall winner locally (larger value; equal values -> lower global
+// index, which is what one arg-max over the whole vocabulary would return).  The tables are double-buffered by epoch
+// parity, so a rank that races ahead into the next call never overwrites pairs a slower rank still reads.
+// Table layout at bufs[r] + pair_off: [2][world][Tmax] of uint2 {value bits, global index}.
+__device__ void argmax_merge_body(const CommCtx& c, size_t pair_off, int Tmax, const float* __restrict__ val,
+                                  const int64_t* __restrict__ idx, int T, int vocab_off, uint32_t* epoch_slot, int slot_block,
+                                  int64_t* __restrict__ out_idx, float* __restrict__ out_val) {
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
+  const size_t par = epoch & 1u;
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    const uint2 pr = make_uint2(__float_as_uint(val[t]), (uint32_t)((int)idx[t] + vocab_off));
+    for (int p = 0; p < c.world; ++p)
+      *(uint2*)(c.bufs[(c.rank + p) % c.world] + pair_off + ((par * c.world + c.rank) * Tmax + t) * 8) = pr;
+  }
+  if (!rank_barrier(c, 0, epoch, slot_block)) return;
+  for (int t = threadIdx.x; t < T; t += blockDim.x) {
+    float bv = 0.f;
+    uint32_t bi = 0xffffffffu;
+    for (int p = 0; p < c.world; ++p) {
+      uint2 pr;
+      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];"
+                   : "=r"(pr.x), "=r"(pr.y) : "l"(c.bufs[c.rank] + pair_off + ((par * c.world + p) * Tmax + t) * 8) : "memory");
+      const float v = __uint_as_float(pr.x);
+      if (bi == 0xffffffffu || v > bv || (v == bv && pr.y < bi)) { bv = v; bi = pr.y; }
+    }
+    out_idx[t] = (int64_t)bi;
+    out_val[t] = bv;
+  }
+  if (threadIdx.x == 0) *epoch_slot = epoch;
+}
+
+__global__ void __launch_bounds__(256)
+argmax_merge_kernel(const CommCtx c, size_t pair_off, int Tmax, const float* val, const int64_t* idx, int T, int vocab_off,
+                    uint32_t* epoch_slot, int slot_block, int64_t* out_idx, float* out_val) {
+  argmax_merge_body(c, pair_off, Tmax, val, idx, T, vocab_off, epoch_slot, slot_block, out_idx, out_val);
+}
+
+// All ranks in one cooperative launch on one GPU (block r plays rank r); inputs and outputs are [world][T] arrays.
+__global__ void __launch_bounds__(256)
+argmax_merge_emulated_kernel(CommCtx c, size_t pair_off, int Tmax, const float* val, const int64_t* idx, int T, int vocab_per_rank,
+                             uint32_t* epoch_slots, int slot_block, int64_t* out_idx, float* out_val) {
+  c.rank = blockIdx.x;
+  argmax_merge_body(c, pair_off, Tmax, val + (size_t)c.rank * T, idx + (size_t)c.rank * T, T, c.rank * vocab_per_rank,
+                    epoch_slots + c.rank, slot_block, out_idx + (size_t)c.rank * T, out_val + (size_t)c.rank * T);
+}
+
 __global__ void rank_barrier_kernel(const CommCtx c, uint32_t* epoch_slot, int slot_block) {
   __shared__ uint32_t epoch_s;
   if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
@@ -273,5 +324,35 @@ MARY_API int mary_wait_flag(const uint64_t* sigs, int rank, int world, uint32_t 
   c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
   wait_flag_kernel<<<1, 1, 0, s>>>(c, slot, want);
   MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// val / idx: this rank's per-token best logit and LOCAL index within its vocabulary shard (which starts at vocab_off).
+// The pair tables need 2 * world * Tmax * 8 bytes at byte offset pair_off (16-byte aligned) of every rank's symmetric
+// buffer.  Every rank must make the same sequence of calls with the same T.
+MARY_API int mary_argmax_merge(const void* val, const void* idx, int T, int Tmax, int vocab_off, const uint64_t* bufs, const uint64_t* sigs,
+                               uint64_t pair_off, int rank, int world, uint32_t* epoch_slot, int slot_block, uint64_t wait_ns,
+                               void* out_idx, void* out_val, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || T < 0 || T > Tmax || (pair_off & 15)) return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  argmax_merge_kernel<<<1, 256, 0, s>>>(c, pair_off, Tmax, (const float*)val, (const int64_t*)idx, T, vocab_off, epoch_slot, slot_block,
+                                        (int64_t*)out_idx, (float*)out_val);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_argmax_merge_emulated(const void* val, const void* idx, int T, int Tmax, int vocab_per_rank, const uint64_t* bufs,
+                                        const uint64_t* sigs, uint64_t pair_off, int world, uint32_t* epoch_slots, int slot_block,
+                                        uint64_t wait_ns, void* out_idx, void* out_val, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || T < 0 || T > Tmax || (pair_off & 15)) return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = nullptr; c.rank = 0; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  size_t po = pair_off;
+  void* args[] = {&c, &po, &Tmax, &val, &idx, &T, &vocab_per_rank, &epoch_slots, &slot_block, &out_idx, &out_val};
+  if (cudaLaunchCooperativeKernel((void*)argmax_merge_emulated_kernel, dim3(world), dim3(256), args, 0, s) != cudaSuccess)
+    return MARY_ERR_CUDA;
   return MARY_OK;
 }

@@ -200,7 +200,12 @@ class MoEDecoder(nn.Module):
         self.embed = _P(c.vocab_size, c.hidden_size, **kw)
         self.layers = nn.ModuleList([MoELayer(c, i, self.par, dtype, device) for i in range(c.num_hidden_layers)])
         self.norm = _P(c.hidden_size, **kw)
-        self.lm_head = None if c.tie_word_embeddings else _P(c.vocab_size, c.hidden_size, **kw)
+        # vocabulary-parallel head: every rank keeps V / tp rows of the head and the ranks merge (value, index) candidates
+        self.vocab_parallel = bool(getattr(self.par, "vocab_parallel", False)) and self.par.tp_size > 1 \
+            and c.vocab_size % self.par.tp_size == 0
+        head_rows = c.vocab_size // self.par.tp_size if self.vocab_parallel else c.vocab_size
+        self.lm_head = None if c.tie_word_embeddings else _P(head_rows, c.hidden_size, **kw)
+        self._vhead = None
         self.mtp = nn.ModuleList([MTPLayer(c, d, self.par, dtype, device) for d in range(c.num_mtp_layers)])
 
     def kv_spec(self):
@@ -212,6 +217,18 @@ class MoEDecoder(nn.Module):
 
     def head_weight(self):
         return self.embed if self.lm_head is None else self.lm_head
+
+    def head_argmax(self, x):
+        """Greedy token of every row of ``x`` (normed hidden states)."""
+        if not self.vocab_parallel:
+            return ops.lm_head_argmax(x, self.head_weight())[0]
+        if self._vhead is None:
+            from ...parallel.vocab import VocabParallelHead
+            par = self.par
+            w = self.lm_head if self.lm_head is not None else VocabParallelHead.shard(self.embed, par.tp_rank, par.tp_size)
+            fused = getattr(par, "mode", "") == "fused" and getattr(par, "symm", None) is not None and w.is_cuda
+            self._vhead = VocabParallelHead(w, par.tp_rank, par.tp_size, symm=par.symm if fused else None, group=getattr(par, "group", None))
+        return self._vhead.argmax(x)[0]
 
     def trunk(self, ids, meta, cache):
         """Residual stream after the last layer (before the final norm), every row."""
@@ -242,28 +259,31 @@ class MoEDecoder(nn.Module):
         x = self.hidden(ids, meta, cache)
         if rows is not None:
             x = x[rows]
+        if self.vocab_parallel:                       # full logits are a debugging aid here: gather the shards
+            import torch.distributed as dist
+            w = self.lm_head if self.lm_head is not None else self.embed.chunk(self.par.tp_size, 0)[self.par.tp_rank]
+            loc = ops.linear(x, w).float().contiguous()
+            parts = [torch.empty_like(loc) for _ in range(self.par.tp_size)]
+            dist.all_gather(parts, loc, group=getattr(self.par, "group", None))
+            return torch.cat(parts, -1)
         return ops.linear(x, self.head_weight()).float()
 
     def greedy(self, ids, meta, cache, rows):
-        x = self.hidden(ids, meta, cache)[rows]
-        tok, _ = ops.lm_head_argmax(x, self.head_weight())
-        return tok
+        return self.head_argmax(self.hidden(ids, meta, cache)[rows])
 
     # -- speculative decoding -------------------------------------------------
     def verify(self, ids, meta, cache):
         """One forward over the fed rows.  Returns ``(arg-max token of every row, trunk hidden of every row)``."""
         h = self.trunk(ids, meta, cache)
         x = ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
-        tok, _ = ops.lm_head_argmax(x, self.head_weight())
-        return tok, h
+        return self.head_argmax(x), h
 
     def draft(self, d: int, h_prev, next_ids, meta, cache):
         """Draft head ``d``: hidden of the rows + the token that follows each row -> ``(draft token, its hidden)``."""
         emb = ops.embed(next_ids, self.embed)
         h = self.mtp[min(d, len(self.mtp) - 1)](h_prev, emb, meta, cache)
         x = ops.rmsnorm(h, self.mtp[min(d, len(self.mtp) - 1)].out_norm, self.cfg.rms_norm_eps)
-        tok, _ = ops.lm_head_argmax(x, self.head_weight())
-        return tok, h
+        return self.head_argmax(x), h
 
 
 def init_random_(model: MoEDecoder, seed: int = 0, std: float = 0.02, expert_slabs: int | None = None) -> None:

@@ -67,6 +67,8 @@ def shard_from_full(full: MoEDecoder, par, device=None) -> MoEDecoder:
                     src = _cols(src, r, n)
             elif isinstance(mod, DenseFFN):
                 src = _gu(src, r, n) if leaf == "w_gu" else _cols(src, r, n)
+            elif name == "lm_head" and m.vocab_parallel:
+                src = _rows(src, r, n)
             p.copy_(src.to(dev))
     for (_, a), (_, b) in zip(m.named_modules(), full.named_modules()):
         if isinstance(a, MoEFFN):

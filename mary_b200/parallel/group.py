@@ -14,13 +14,15 @@ from .. import ops
 
 
 class ParallelGroup:
-    def __init__(self, rank: int = 0, size: int = 1, mode: str = "nccl", group=None, symm=None, ep_mode: str = "replicated"):
+    def __init__(self, rank: int = 0, size: int = 1, mode: str = "nccl", group=None, symm=None, ep_mode: str = "replicated",
+                 vocab_parallel: bool = False):
         """``ep_mode="replicated"``: tokens are replicated, attention is tensor parallel over the group and every rank adds
         the partial sums of its own experts (one reduction per block).  ``ep_mode="a2a"``: tokens stay on their home rank
         (data-parallel attention, full heads everywhere) and the routed experts are reached through the all-to-all of
         ``parallel.ep``; nothing is reduced."""
         self.rank, self.size, self.mode, self.group, self.symm = rank, size, mode, group, symm
         self.ep_mode = ep_mode
+        self.vocab_parallel = vocab_parallel and ep_mode != "a2a"      # tokens must be replicated over the group
         self.tp_rank, self.tp_size = (0, 1) if ep_mode == "a2a" else (rank, size)
         self.ep_rank, self.ep_size = rank, size
         self.ep_factory = None          # callable(experts, cfg) -> EPLayer, set by the launcher in a2a mode

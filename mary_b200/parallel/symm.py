@@ -15,8 +15,12 @@ from ..ops.cuda import _stream, check, declare, lib
 
 declare("mary_allreduce_bf16", "pplii" + "lllpiils")
 declare("mary_wait_flag", "piiiils")
+declare("mary_argmax_merge", "ppiiipplii" + "pilpps")
 
 FLAG_WORDS = 64 * 2 * 8        # grid <= 64 blocks, two barriers, eight ranks
+PAIR_TOKENS = 4096             # rows one arg-max merge can carry
+PAIR_BYTES = 2 * 8 * PAIR_TOKENS * 8
+MERGE_SLOT = 62                # flag block of the arg-max merge (all-reduce grids stay below it)
 
 
 class SymmetricHeap:
@@ -28,7 +32,8 @@ class SymmetricHeap:
         self.region = (max_bytes + 255) // 256 * 256
         self.grid = grid
         self.wait_ns = int(wait_ms * 1e6)
-        self.buf = symm_mem.empty(2 * self.region, dtype=torch.uint8, device=self.dev)
+        self.buf = symm_mem.empty(2 * self.region + PAIR_BYTES, dtype=torch.uint8, device=self.dev)
+        self.buf[2 * self.region:].zero_()
         self.hdl = symm_mem.rendezvous(self.buf, dist.group.WORLD)
         self.flags = symm_mem.empty(FLAG_WORDS, dtype=torch.int32, device=self.dev)
         self.flags.zero_()
@@ -82,3 +87,18 @@ class SymmetricHeap:
     def wait_flag(self, slot: int, want: int):
         """Launch a bounded wait on one of this rank's flags (failure-detection tests)."""
         check(lib().mary_wait_flag(self.sig_ptrs, self.rank, self.world, slot, want, self.wait_ns, _stream()), "wait_flag")
+
+    def argmax_merge(self, val, idx_local, vocab_offset: int):
+        """Merge per-rank ``(max logit, local index)`` candidates of a vocabulary-parallel head: returns the global
+        ``(ids, value)`` of the overall arg-max (ties -> lower index), the same on every rank."""
+        T = val.numel()
+        if T > PAIR_TOKENS:
+            raise ValueError(f"{T} rows exceed the merge table of {PAIR_TOKENS}")
+        val = val.float().contiguous()
+        idx_local = idx_local.to(torch.int64).contiguous()
+        out_i = torch.empty(T, dtype=torch.int64, device=self.dev)
+        out_v = torch.empty(T, dtype=torch.float32, device=self.dev)
+        check(lib().mary_argmax_merge(val.data_ptr(), idx_local.data_ptr(), T, PAIR_TOKENS, vocab_offset, self.buf_ptrs, self.sig_ptrs,
+                                      2 * self.region, self.rank, self.world, self.epochs[MERGE_SLOT:].data_ptr(), MERGE_SLOT,
+                                      self.wait_ns, out_i.data_ptr(), out_v.data_ptr(), _stream()), "argmax_merge")
+        return out_i, out_v

@@ -111,6 +111,107 @@ def main():
         dist.barrier()
         if rank == 0:
             print("A2A_OK")
+    elif what == "sp":
+        # GEMM -> reduce-scatter from the epilogue (peer stores), reduce + residual + RMSNorm -> all-gather (multimem / peer stores)
+        from mary_b200.ops import reference as ref
+        from mary_b200.parallel.sp import SequenceParallel
+        for use_mc in (False, True):
+            T, H, Kl = 64 * world, 1024, 512
+            sp = SequenceParallel.distributed(rank, world, T, H, dev, use_multicast=use_mc)
+            if use_mc and not sp.x_mc:
+                continue
+            torch.manual_seed(7)
+            xs = [torch.randn(T, Kl, device=dev).bfloat16() for _ in range(world)]
+            ws = [(torch.randn(H, Kl, device=dev) * 0.05).bfloat16() for _ in range(world)]
+            h = torch.randn(T, H, device=dev).bfloat16()
+            gain = (1 + 0.1 * torch.randn(H, device=dev)).bfloat16()
+            rpr = T // world
+            for it in range(3):
+                mine = h[rank * rpr:(rank + 1) * rpr].clone()
+                sp.row_linear_rs(xs[rank], ws[rank])
+                got = sp.reduce_add_rmsnorm(mine, gain, 1e-6).clone()
+            torch.cuda.synchronize()
+            assert K.last_status() == 0
+            partial = (xs[rank].float() @ ws[rank].float().T).bfloat16().float()
+            dist.all_reduce(partial)
+            h_new = (h.float() + partial).bfloat16()
+            want = ref.rmsnorm(h_new, gain, 1e-6).float()
+            err = (got.float() - want).abs().max().item() / want.abs().max().item()
+            assert err < 3e-2, (use_mc, err)
+            assert (mine.float() - h_new[rank * rpr:(rank + 1) * rpr].float()).abs().max().item() < 0.1
+        dist.barrier()
+        if rank == 0:
+            print("SP_OK")
+    elif what == "vocab":
+        from mary_b200.parallel.vocab import VocabParallelHead
+        heap = SymmetricHeap(rank, world, dev, max_bytes=1 << 16)
+        torch.manual_seed(0)
+        W = (torch.randn(4096, 256, device=dev) * 0.1).bfloat16()
+        W[3000] = W[11]
+        x = torch.randn(96, 256, device=dev).bfloat16()
+        x[0] = W[11] * 4
+        head = VocabParallelHead(VocabParallelHead.shard(W, rank, world), rank, world, symm=heap)
+        lib_head = VocabParallelHead(VocabParallelHead.shard(W, rank, world), rank, world)
+        for _ in range(3):
+            ids, val = head.argmax(x)
+        ids2, val2 = lib_head.argmax(x)
+        full_ids, full_val = K.lm_head_argmax(x, W)
+        torch.cuda.synchronize()
+        assert K.last_status() == 0
+        assert torch.equal(ids, ids2) and torch.equal(ids, full_ids), (ids[:8], ids2[:8], full_ids[:8])
+        assert int(ids[0]) == 11
+        assert torch.allclose(val, full_val, atol=1e-3)
+        dist.barrier()
+        if rank == 0:
+            print("VOCAB_OK")
+    elif what == "pp":
+        # layer pipeline over NCCL send/recv: activations on a side stream, token replies on a second communicator
+        import numpy as np
+        from mary_b200.models.moe import MoEDecoder, init_random_, tiny_moe_config
+        from mary_b200.parallel.pp import PipeChannel, PipelineStage, balanced_split
+        from mary_b200.runtime.batch import BatchMeta
+        from mary_b200.runtime.kv_cache import PagedKVCache
+        fwd, back = dist.new_group(list(range(world))), dist.new_group(list(range(world)))
+        torch.manual_seed(0)
+        cfg = tiny_moe_config("gqa")
+        m = MoEDecoder(cfg, dtype=torch.bfloat16, device=dev)
+        init_random_(m, 0)
+        B, L, n_new, C = 2, 9, 4, 3
+        rng = np.random.default_rng(5)
+        prompts = [rng.integers(0, cfg.vocab_size, (B, L)) for _ in range(C)]
+        spec = m.kv_spec()
+
+        def new_cache():
+            ca = PagedKVCache(spec["num_layers"], B * 2 + 1, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16, device=dev)
+            for s in range(B):
+                ca.alloc.extend(s, L + n_new)
+            return ca
+        caches = [new_cache() for _ in range(C)]
+
+        def make_meta(c, q, kv_len):
+            table, _ = caches[c].alloc.page_table(list(range(B)))
+            return BatchMeta.build([q] * B, [kv_len] * B, table, 16, dev), caches[c]
+        st = PipelineStage(m, balanced_split([1] * cfg.num_hidden_layers, world), rank,
+                           PipeChannel(cfg.hidden_size, B * L, torch.bfloat16, dev, fwd, back))
+        res = st.generate(prompts, n_new, make_meta)
+        torch.cuda.synchronize()
+        if rank == 0:
+            for c in range(C):
+                ca = new_cache()
+                table, _ = ca.alloc.page_table(list(range(B)))
+                fed, kv = torch.as_tensor(prompts[c], dtype=torch.int32, device=dev), 0
+                for step in range(n_new):
+                    q = fed.shape[1]
+                    meta = BatchMeta.build([q] * B, [kv + q] * B, table, 16, dev)
+                    with torch.no_grad():
+                        t = m.greedy(fed.reshape(-1), meta, ca, torch.arange(B, device=dev) * q + (q - 1))
+                    kv += q
+                    assert [int(v) for v in t] == [res[c][b][step] for b in range(B)], (c, step)
+                    fed = t.to(torch.int32).view(B, 1)
+        assert K.last_status() == 0
+        dist.barrier()
+        if rank == 0:
+            print("PP_OK")
     elif what == "timeout":
         heap = SymmetricHeap(rank, world, dev, max_bytes=1 << 16, use_multicast=False, wait_ms=300.0)
         dist.barrier()

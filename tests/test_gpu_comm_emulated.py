@@ -81,3 +81,35 @@ def test_gemm_reduce_scatter_epilogue_and_fused_norm_allgather(world, T):
         assert ((outs[r].float() - want.float()).abs().max() / want.float().abs().max()).item() < 2e-2
         assert ((slices[r].float() - h_new[r * rpr:(r + 1) * rpr].float()).abs().max()).item() < 0.1
     assert torch.equal(outs[0], outs[-1])                      # every rank holds the same gathered activations
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_vocab_parallel_argmax_merge_emulated(world):
+    """All ranks of the arg-max merge inside one cooperative launch: every rank must end with the arg-max of the whole
+    vocabulary, ties going to the lower global index, on two calls in a row (epoch parity flips the pair tables)."""
+    import ctypes
+    from mary_b200.ops import cuda
+    cuda.declare("mary_argmax_merge_emulated", "ppiiipplipilpps")
+    T, Tmax, vpr = 100, 128, 1000
+    bufs = [torch.zeros(2 * 8 * Tmax * 8, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    sigs = [torch.zeros(64 * 2 * 8, dtype=torch.int32, device="cuda") for _ in range(world)]
+    bp = (ctypes.c_uint64 * 8)(*[b.data_ptr() for b in bufs])
+    sp = (ctypes.c_uint64 * 8)(*[s.data_ptr() for s in sigs])
+    epochs = torch.zeros(world, dtype=torch.int32, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(1)
+    for call in range(3):
+        val = torch.randn(world, T, device="cuda", generator=g)
+        idx = torch.randint(0, vpr, (world, T), device="cuda", generator=g)
+        val[:, :10] = 7.0                                        # ties across all ranks: lowest global index must win
+        out_i = torch.empty(world, T, dtype=torch.int64, device="cuda")
+        out_v = torch.empty(world, T, dtype=torch.float32, device="cuda")
+        cuda.check(cuda.lib().mary_argmax_merge_emulated(val.data_ptr(), idx.data_ptr(), T, Tmax, vpr, bp, sp, 0, world, epochs.data_ptr(),
+                                                         62, int(2e9), out_i.data_ptr(), out_v.data_ptr(), cuda._stream()), "merge")
+        torch.cuda.synchronize()
+        assert cuda.last_status() == 0
+        from mary_b200.parallel.vocab import merge_candidates
+        gi = idx + torch.arange(world, device="cuda")[:, None] * vpr
+        want_i, want_v = merge_candidates(val, gi)
+        for r in range(world):
+            assert torch.equal(out_i[r], want_i) and torch.equal(out_v[r], want_v), (call, r)
+    assert epochs.tolist() == [3] * world

@@ -37,6 +37,21 @@ def test_expert_parallel_all_to_all_matches_single_gpu():
     assert "A2A_OK" in out, out[-2000:]
 
 
+def test_gemm_reduce_scatter_and_fused_norm_all_gather_match_nccl():
+    out = _torchrun(["sp"])
+    assert "SP_OK" in out, out[-2000:]
+
+
+def test_vocab_parallel_head_merge_kernel_matches_full_head():
+    out = _torchrun(["vocab"])
+    assert "VOCAB_OK" in out, out[-2000:]
+
+
+def test_layer_pipeline_over_nccl_matches_single_gpu():
+    out = _torchrun(["pp"])
+    assert "PP_OK" in out, out[-2000:]
+
+
 def test_peer_wait_times_out_with_status_and_context_survives():
     # NVLS off: a rank that leaves must not hold a multicast binding (plain peer loads only)
     out = _torchrun(["timeout"], env={"NCCL_NVLS_ENABLE": "0", "MARY_MULTIMEM": "0"})

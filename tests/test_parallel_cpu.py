@@ -40,10 +40,14 @@ def _worker(rank, world, port, attention, out, shared_fp4=False):
     cfg = tiny_moe_config(attention, shared_expert_nvfp4=shared_fp4)
     full = MoEDecoder(cfg, dtype=torch.float32)
     init_random_(full, 0)
-    par = ParallelGroup(rank, world, "nccl")
+    par = ParallelGroup(rank, world, "nccl", vocab_parallel=(attention == "mla"))      # MLA cases also shard the LM head by rows
     shard = shard_from_full(full, par)
+    assert shard.vocab_parallel == (attention == "mla")
     ids = torch.arange(1, 20, dtype=torch.int32)
     lg = _logits(shard, ids, 19)
+    if shard.vocab_parallel:
+        x = torch.randn(5, cfg.hidden_size, generator=torch.Generator().manual_seed(3))
+        assert torch.equal(shard.head_argmax(x), full.head_argmax(x))
     if rank == 0:
         ref = _logits(full, ids, 19)
         # a rounding-level difference in the hidden state can flip one expert choice of one token (a discontinuity of
@@ -146,3 +150,44 @@ def test_layer_pipeline_two_stages_with_cohorts_matches_single_process(cohorts):
     for p in ps:
         p.join(60)
     assert res == want
+
+
+def _vocab_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from mary_b200.parallel.vocab import VocabParallelHead
+        torch.manual_seed(0)
+        W = torch.randn(512, 64)
+        W[300] = W[17]                                          # a duplicated row: exact ties between shards
+        x = torch.randn(40, 64)
+        x[0] = W[17] * 3
+        head = VocabParallelHead(VocabParallelHead.shard(W, rank, world), rank, world, softcap=30.0)
+        ids, val = head.argmax(x)
+        draws = torch.stack([head.sample(x[:4], 0.7, top_k=5, seed=3, step=s) for s in range(200)])
+        if rank == 0:
+            out.put((ids, val, draws, W, x))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_vocab_parallel_head_matches_full_argmax_and_samples_inside_top_k():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_vocab_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    ids, val, draws, W, x = q.get(timeout=120)
+    for p in ps:
+        p.join(30)
+    logits = 30.0 * torch.tanh((x @ W.T) / 30.0)
+    from mary_b200.ops import reference as ref
+    assert torch.equal(ids, ref.argmax_first(logits))
+    assert ids[0] == 17                                           # the tie between rows 17 and 300 goes to the lower index
+    assert torch.allclose(val, logits.max(-1).values, atol=1e-5)
+    top5 = torch.topk(logits[:4], 5, dim=-1).indices
+    for r in range(4):
+        seen = set(draws[:, r].tolist())
+        assert seen <= set(top5[r].tolist()) and len(seen) >= 2  # draws stay inside the global top-k and do vary
