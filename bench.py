@@ -80,7 +80,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--spec", type=int, default=None)
-    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl", "sp"],
+                    help="fused: own all-reduce kernels over peer memory; sp: GEMM->reduce-scatter epilogue + fused norm/all-gather (dense decoders); nccl: library arm")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line then names a reduced config)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--replicated-head", action="store_true", help="keep the whole LM head on every rank (default: vocabulary-parallel head)")
@@ -135,11 +136,15 @@ def main():
     if world > 1 and args.comm == "fused":
         try:
             from mary_b200.parallel.symm import SymmetricHeap
-            symm = SymmetricHeap(rank, world, dev, max_bytes=(B * (1 + k)) * cfg.hidden_size * 4 * 2)
+            symm = SymmetricHeap(rank, world, dev, max_bytes=max(B * (1 + k), 1024) * cfg.hidden_size * 4)   # decode rows or one prefill chunk
         except Exception as ex:  # the fused path must never be silently absent
             raise RuntimeError(f"fused communication requested but the symmetric heap failed: {ex}") from ex
     par = ParallelGroup(rank, world, "fused" if symm else "nccl", symm=symm, ep_mode="a2a" if a2a else "replicated",
                         vocab_parallel=not args.replicated_head)
+    if world > 1 and args.comm == "sp":
+        assert is_gemma, "--comm sp is the dense decoders' arm"
+        from mary_b200.parallel.sp import SequenceParallel
+        par.sp = SequenceParallel.distributed(rank, world, max(B * (1 + k), 1024), cfg.hidden_size, dev)
     if a2a:
         from mary_b200.parallel.ep import distributed_factory
         par.ep_factory = distributed_factory(rank, world, dev, t_cap=B_local * (1 + k))
@@ -301,7 +306,7 @@ def main():
                        "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,
                        "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
                                        f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
-                       "comm": par.mode if world > 1 else "none", "cuda_graph": dec.graph is not None,
+                       "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": dec.graph is not None,
                        "lm_head": "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated",
                        "expert_slabs_resident": slabs, "moe_layers": n_moe,
                        "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",

@@ -133,11 +133,25 @@ allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t
 }
 
 // Owner side of the reduce-scatter: one CTA per local token row.  Sums the `world` staged partial rows in rank order
-// (deterministic), adds the residual slice (kept sequence-sharded: every rank holds only its own rows), applies RMSNorm and
-// writes the normed row to EVERY rank's activation buffer — the all-gather — with one multimem store per 16 bytes, or
-// peer stores.  w == nullptr: no norm, the reduced row itself is broadcast (plain all-reduce of the partial sums).
+// (deterministic) into a = sum, then
+//   w_post == nullptr:  h' = h + a                               (pre-norm decoders)
+//   w_post != nullptr:  h' = (h + rms(a) * w_post) * scalar      (sandwich norms: the sum is normed before it joins the residual)
+// keeps h' in the residual slice (sequence-sharded: every rank holds only its own rows), applies x = rms(h') * w and writes x
+// to EVERY rank's activation buffer — the all-gather — with one multimem store per 16 bytes, or peer stores.
+// w == nullptr: no final norm, h' itself (or a, without a residual) is broadcast.
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  const int wi = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[wi] = v;
+  __syncthreads();
+  float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
+  return warp_sum(t);
+}
+
 __global__ void rs_add_rmsnorm_kernel(const CommCtx c, const __nv_bfloat16* __restrict__ staging, __nv_bfloat16* __restrict__ h_slice,
-                                      const __nv_bfloat16* __restrict__ w, size_t x_off, int rpr, int H, float eps, int use_mc) {
+                                      const __nv_bfloat16* __restrict__ w_post, const __nv_bfloat16* __restrict__ w, float scalar,
+                                      size_t x_off, int rpr, int H, float eps, int use_mc) {
   extern __shared__ float row[];
   __shared__ float red[32];
   const int r = blockIdx.x;
@@ -150,7 +164,7 @@ __global__ void rs_add_rmsnorm_kernel(const CommCtx c, const __nv_bfloat16* __re
 #pragma unroll
       for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(vp[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
     }
-    if (h_slice) {
+    if (h_slice && !w_post) {
       uint4 hv = *(const uint4*)(h_slice + (int64_t)r * H + i);
       __nv_bfloat162* hp = (__nv_bfloat162*)&hv;
 #pragma unroll
@@ -165,16 +179,30 @@ __global__ void rs_add_rmsnorm_kernel(const CommCtx c, const __nv_bfloat16* __re
 #pragma unroll
     for (int j = 0; j < 8; ++j) { row[i + j] = acc[j]; ss += acc[j] * acc[j]; }
   }
-  float inv = 1.f;
-  if (w) {
-    ss = warp_sum(ss);
-    const int wi = threadIdx.x >> 5, l = threadIdx.x & 31;
-    if (l == 0) red[wi] = ss;
-    __syncthreads();
-    float t = (l < (blockDim.x >> 5)) ? red[l] : 0.f;
-    t = warp_sum(t);
-    inv = rsqrtf(t / H + eps);
+  if (w_post) {
+    const float inv_a = rsqrtf(block_sum_256(ss, red) / H + eps);
+    ss = 0.f;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {        // every thread revisits the columns it wrote
+      const uint4 pv = *(const uint4*)(w_post + i);
+      const __nv_bfloat162* pp = (const __nv_bfloat162*)&pv;
+      uint4 hv = make_uint4(0, 0, 0, 0);
+      if (h_slice) hv = *(const uint4*)(h_slice + (int64_t)r * H + i);
+      __nv_bfloat162* hp = (__nv_bfloat162*)&hv;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 g = __bfloat1622float2(pp[j]);
+        const float2 n = __bfloat1622float2(__floats2bfloat162_rn(row[i + 2 * j] * inv_a * g.x, row[i + 2 * j + 1] * inv_a * g.y));
+        const float2 f = __bfloat1622float2(hp[j]);
+        hp[j] = __floats2bfloat162_rn((f.x + n.x) * scalar, (f.y + n.y) * scalar);
+        const float2 b = __bfloat1622float2(hp[j]);
+        row[i + 2 * j] = b.x; row[i + 2 * j + 1] = b.y;
+        ss += b.x * b.x + b.y * b.y;
+      }
+      if (h_slice) *(uint4*)(h_slice + (int64_t)r * H + i) = hv;
+    }
   }
+  float inv = 1.f;
+  if (w) inv = rsqrtf(block_sum_256(ss, red) / H + eps);
   const int64_t grow = (int64_t)c.rank * rpr + r;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
     uint4 o;
@@ -290,16 +318,19 @@ MARY_API int mary_rank_barrier(const uint64_t* sigs, int rank, int world, uint32
 }
 
 // staging: this rank's [world][rows_per_rank][H] bf16 (filled by the peers' GEMM epilogues); h_slice: this rank's residual rows
-// (updated in place; may be null); w: norm gain (null = no norm); the result row is written at byte offset x_off + row * H * 2 of
-// EVERY rank's symmetric buffer bufs[r] (multicast when mc != 0).  H % 8 == 0, H * 4 <= 48 KB.
-MARY_API int mary_rs_add_rmsnorm(const void* staging, void* h_slice, const void* w, const uint64_t* bufs, uint64_t mc, int rank, int world,
-                                 uint64_t x_off, int rows_per_rank, int H, float eps, cudaStream_t s) {
+// (updated in place; may be null); w_post: gain of a norm applied to the reduced sum before the residual add (null = none);
+// scalar multiplies the new residual (sandwich-norm decoders; 1 otherwise); w: gain of the final norm (null = no norm); the result
+// row is written at byte offset x_off + row * H * 2 of EVERY rank's symmetric buffer bufs[r] (multicast when mc != 0).
+// H % 8 == 0, H * 4 <= 48 KB.
+MARY_API int mary_rs_add_rmsnorm(const void* staging, void* h_slice, const void* w_post, const void* w, float scalar, const uint64_t* bufs,
+                                 uint64_t mc, int rank, int world, uint64_t x_off, int rows_per_rank, int H, float eps, cudaStream_t s) {
   if (world < 1 || world > MAX_RANKS || (H & 7) || (size_t)H * 4 > 48 * 1024 || (x_off & 15)) return MARY_ERR_BAD_ARG;
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = nullptr; }
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = 0; c.status = mary_status_ptr();
   rs_add_rmsnorm_kernel<<<rows_per_rank, 256, (size_t)H * 4, s>>>(c, (const __nv_bfloat16*)staging, (__nv_bfloat16*)h_slice,
-                                                                 (const __nv_bfloat16*)w, x_off, rows_per_rank, H, eps, mc ? 1 : 0);
+                                                                 (const __nv_bfloat16*)w_post, (const __nv_bfloat16*)w, scalar, x_off,
+                                                                 rows_per_rank, H, eps, mc ? 1 : 0);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

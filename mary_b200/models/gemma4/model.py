@@ -3,7 +3,9 @@
 Math: src/models/gemma/gemma4/{layers,decoder}.rs (restated step by step in ``mary_b200.oracle.gemma4``).
 Weights are torch ``[out, in]``; q/k/v and gate/up are stored fused (``[q;k;v]``, ``[gate;up]``) so each block
 issues four GEMMs.  Tensor parallelism shards q/k/v and gate/up by output rows (whole heads) and o/down by
-input columns; ``tp`` supplies the reduction after the row-parallel GEMMs."""
+input columns; ``tp`` supplies the reduction after the row-parallel GEMMs — an all-reduce, or, when ``tp.sp`` is set
+(``parallel.sp.SequenceParallel``), a reduce-scatter from the GEMM epilogue followed by a fused sum + sandwich norms +
+all-gather kernel with the residual stream sharded by token rows."""
 from __future__ import annotations
 
 import math
@@ -66,6 +68,16 @@ class Gemma4Layer(nn.Module):
                                     meta, cache.k[self.i], cache.v[self.i], c.rms_norm_eps)
         o = ops.paged_attention(q, cache.k[self.i], cache.v[self.i], meta, 1.0, self.window)
         o = o.reshape(o.shape[0], -1)
+        sp = getattr(self.tp, "sp", None)
+        if sp is not None and x.is_cuda and not L:
+            # sequence-parallel residual: ``h`` holds this rank's token rows only.  The row-parallel GEMMs deliver their partial
+            # rows to the owners from the epilogue; the owner sums, applies the sandwich norms and all-gathers the next input.
+            sp.row_linear_rs(o, self.w_o)
+            x = sp.reduce_add_rmsnorm(h, self.ln_pre_ffn, c.rms_norm_eps, w_post=self.ln_post_attn)
+            m = ops.linear_glu(x, self.w_gu, "geglu")
+            sp.row_linear_rs(m, self.w_down)
+            x = sp.reduce_add_rmsnorm(h, next_norm, c.rms_norm_eps, w_post=self.ln_post_ffn, scalar=self.layer_scalar)
+            return x, h
         a = self.tp.reduce(self.tp.row_linear(o, self.w_o, L.get("o")))
         x, h = ops.norm_add_norm(a, self.ln_post_attn, h, self.ln_pre_ffn, c.rms_norm_eps)
         if "gu" in L:
@@ -98,6 +110,9 @@ class Gemma4Model(nn.Module):
         """Final-normed hidden states ``[T, H]`` of every row."""
         h = ops.embed(ids, self.embed, self.embed_scale)
         x = ops.rmsnorm(h, self.layers[0].ln_in, self.cfg.rms_norm_eps)
+        sp = getattr(self.tp, "sp", None)
+        if sp is not None and h.is_cuda and not any(l.lora for l in self.layers):
+            h = sp.residual_slice(h)                 # from here on every rank carries only its own rows of the residual
         n = len(self.layers)
         for i, layer in enumerate(self.layers):
             nxt = self.layers[i + 1].ln_in if i + 1 < n else self.norm

@@ -114,3 +114,31 @@ def init_random_(model, seed: int = 0, std: float = 0.02) -> None:
             p.data.fill_(1.0)
         else:
             p.data.normal_(0.0, std, generator=g)
+
+
+def shard_from_full(full, tp, device=None):
+    """A tensor-parallel ``Gemma4Model`` (rank ``tp.rank`` of ``tp.size``) cut out of an unsharded one: q/k/v and gate/up by
+    output rows (whole heads), o/down by input columns, everything else replicated."""
+    from .model import Gemma4Model
+    cfg = full.cfg
+    dev = device or full.embed.device
+    m = Gemma4Model(cfg, tp=tp, dtype=full.dtype, device=dev)
+    r, n = tp.rank, tp.size
+    with torch.no_grad():
+        m.embed.copy_(full.embed)
+        m.norm.copy_(full.norm)
+        for L, Fl in zip(m.layers, full.layers):
+            D, H = L.D, cfg.hidden_size
+            q, k, v = Fl.w_qkv.split([Fl.n_q * D, Fl.n_kv * D, Fl.n_kv * D], 0)
+            kv0 = (r * Fl.n_kv) // n if Fl.n_kv >= n else 0
+            L.w_qkv.copy_(torch.cat([q.view(Fl.n_q, D, H)[r * L.n_q:(r + 1) * L.n_q].reshape(-1, H),
+                                     k.view(Fl.n_kv, D, H)[kv0:kv0 + L.n_kv].reshape(-1, H),
+                                     v.view(Fl.n_kv, D, H)[kv0:kv0 + L.n_kv].reshape(-1, H)], 0))
+            L.w_o.copy_(Fl.w_o[:, r * L.n_q * D:(r + 1) * L.n_q * D])
+            g, u = Fl.w_gu[:Fl.F], Fl.w_gu[Fl.F:]
+            L.w_gu.copy_(torch.cat([g[r * L.F:(r + 1) * L.F], u[r * L.F:(r + 1) * L.F]], 0))
+            L.w_down.copy_(Fl.w_down[:, r * L.F:(r + 1) * L.F])
+            for nm in ("q_norm", "k_norm", "ln_in", "ln_post_attn", "ln_pre_ffn", "ln_post_ffn"):
+                getattr(L, nm).copy_(getattr(Fl, nm))
+            L.layer_scalar = Fl.layer_scalar
+    return m

@@ -42,13 +42,15 @@ def time_op(fn, iters: int = 10, warmup: int = 3) -> float:
     return ts[len(ts) // 2]
 
 
-def bench_gemm():
+GEMM_SHAPES = [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 15360 * 2, 3840), (32, 6144, 3840), (32, 3840, 4096),
+               (32, 30720, 3840), (32, 3840, 15360), (384, 2112, 7168), (384, 12288, 1536), (384, 7168, 8192), (128, 163840, 7168)]
+
+
+def bench_gemm(shapes=None):
     from . import cuda as K
     hbm, tf, tag = peaks()
     print(f"{'M':>6} {'N':>6} {'K':>6} {'ours ms':>9} {'torch ms':>9} {'TFLOP/s':>8} {'GB/s':>7}  frac {tag}")
-    for M, N, Kd in [(8192, 8192, 8192), (4096, 4096, 4096), (2048, 15360 * 2, 3840), (32, 6144, 3840), (32, 3840, 4096),
-                     (32, 30720, 3840), (32, 3840, 15360), (384, 2112, 7168), (384, 12288, 1536), (384, 7168, 8192),
-                     (128, 163840, 7168)]:
+    for M, N, Kd in shapes or GEMM_SHAPES:
         x = torch.randn(M, Kd, device="cuda").bfloat16()
         w = (torch.randn(N, Kd, device="cuda") * 0.02).bfloat16()
         sk = K._auto_split_k(M, N, Kd)
@@ -66,12 +68,12 @@ def bench_gemm():
     assert K.last_status() == 0
 
 
-def bench_attn():
+def bench_attn(cases=None):
     from . import cuda as K
     from ..runtime.batch import BatchMeta
     from ..runtime.kv_cache import PagedKVCache
     hbm, tf, tag = peaks()
-    for (B, L, Hq, Hkv, D, win) in [(32, 2304, 16, 8, 256, 0), (32, 2304, 16, 8, 256, 1024), (64, 1536, 32, 8, 128, 0)]:
+    for (B, L, Hq, Hkv, D, win) in cases or [(32, 2304, 16, 8, 256, 0), (32, 2304, 16, 8, 256, 1024), (64, 1536, 32, 8, 128, 0)]:
         pages = B * ((L + 15) // 16) + 1
         cache = PagedKVCache(1, pages, 16, Hkv, D, dtype=torch.bfloat16, device="cuda")
         for s in range(B):
@@ -138,13 +140,18 @@ def bench_moe(E: int = 48, H: int = 7168, F: int = 2048, T: int = 384, k: int = 
 
 
 if __name__ == "__main__":
+    # ``gemm M N K`` / ``attn B L Hq Hkv D window`` / ``mla B L Hq q_len`` / ``moe E H F T k`` run that one case only
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
+    nums = [int(v) for v in sys.argv[2:]]
     if what in ("gemm", "all"):
-        bench_gemm()
+        bench_gemm([tuple(nums)] if nums and what == "gemm" else None)
     if what in ("attn", "all"):
-        bench_attn()
-    if what in ("moe", "all"):
-        bench_moe()
+        bench_attn([tuple(nums)] if nums and what == "attn" else None)
     if what in ("mla", "all"):
-        bench_mla()
-        bench_mla(Hq=8)
+        if nums and what == "mla":
+            bench_mla(*nums)
+        else:
+            bench_mla()
+            bench_mla(Hq=8)
+    if what in ("moe", "all"):
+        bench_moe(*(nums if what == "moe" else []))

@@ -25,6 +25,7 @@ class ParallelGroup:
         self.vocab_parallel = vocab_parallel and ep_mode != "a2a"      # tokens must be replicated over the group
         self.tp_rank, self.tp_size = (0, 1) if ep_mode == "a2a" else (rank, size)
         self.ep_rank, self.ep_size = rank, size
+        self.sp = None                  # parallel.sp.SequenceParallel: reduce-scatter / all-gather arm of the dense decoders
         self.ep_factory = None          # callable(experts, cfg) -> EPLayer, set by the launcher in a2a mode
         self.bytes_reduced = 0
         self.calls = 0

@@ -212,6 +212,45 @@ def main():
         dist.barrier()
         if rank == 0:
             print("PP_OK")
+    elif what == "gemma_sp":
+        # Gemma-4 decoder, tensor parallel: all-reduce arm (library and own kernel) and the sequence-parallel arm
+        # (GEMM -> reduce-scatter epilogue, fused sum + sandwich norms + all-gather) against the unsharded model
+        from mary_b200.models.gemma4 import Gemma4Model, Gemma4TextConfig
+        from mary_b200.models.gemma4.weights import init_random_ as ginit, shard_from_full as gshard
+        from mary_b200.parallel.sp import SequenceParallel
+        from mary_b200.runtime.batch import BatchMeta
+        from mary_b200.runtime.kv_cache import PagedKVCache
+        cfg = Gemma4TextConfig(hidden_size=512, num_hidden_layers=3, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+                               intermediate_size=2048, vocab_size=4096, sliding_window=32)
+        full = Gemma4Model(cfg, dtype=torch.bfloat16, device=dev)
+        ginit(full, 0, std=0.05)
+        ids = torch.randint(0, 4096, (71,), generator=torch.Generator().manual_seed(1)).to(dev)
+
+        def run(m):
+            spec = m.kv_spec()
+            cache = PagedKVCache(spec["num_layers"], 32, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16, device=dev)
+            cache.alloc.extend(1, 50)
+            cache.alloc.extend(2, 21)
+            table, lens = cache.alloc.page_table([1, 2])
+            meta = BatchMeta.build([50, 21], lens, table, 16, dev)
+            with torch.no_grad():
+                return m(ids, meta, cache).float()
+        want = run(full)
+        for arm in ("nccl", "fused", "sp"):
+            heap = SymmetricHeap(rank, world, dev, max_bytes=1 << 20) if arm == "fused" else None
+            par = ParallelGroup(rank, world, "fused" if arm == "fused" else "nccl", symm=heap)
+            if arm == "sp":
+                par.sp = SequenceParallel.distributed(rank, world, 128, cfg.hidden_size, dev)
+            shard = gshard(full, par)
+            got = run(shard)
+            torch.cuda.synchronize()
+            assert K.last_status() == 0
+            err = (got - want).abs().max().item() / want.abs().max().item()
+            agree = (got.argmax(-1) == want.argmax(-1)).float().mean().item()
+            assert err < 0.08 and agree > 0.9, (arm, err, agree)
+        dist.barrier()
+        if rank == 0:
+            print("GEMMA_SP_OK")
     elif what == "timeout":
         heap = SymmetricHeap(rank, world, dev, max_bytes=1 << 16, use_multicast=False, wait_ms=300.0)
         dist.barrier()

@@ -81,6 +81,31 @@ def test_gemm_reduce_scatter_epilogue_and_fused_norm_allgather(world, T):
         assert ((outs[r].float() - want.float()).abs().max() / want.float().abs().max()).item() < 2e-2
         assert ((slices[r].float() - h_new[r * rpr:(r + 1) * rpr].float()).abs().max()).item() < 0.1
     assert torch.equal(outs[0], outs[-1])                      # every rank holds the same gathered activations
+    # sandwich norms: the sum is normed before it joins the residual, the new residual is scaled, then normed again
+    from mary_b200 import ops
+    post = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    slices = [h[r * rpr:(r + 1) * rpr].clone() for r in range(world)]
+    for r in range(world):
+        sps[r].row_linear_rs(xs[r], ws[r])
+    outs = [sps[r].reduce_add_rmsnorm(slices[r], gain, 1e-6, w_post=post, scalar=0.5).clone() for r in range(world)]
+    torch.cuda.synchronize()
+    a = sum(partials).bfloat16()
+    want_x, want_h = ops.norm_add_norm(a, post, h.clone(), gain, 1e-6, 0.5)
+    for r in range(world):
+        assert ((outs[r].float() - want_x.float()).abs().max() / want_x.float().abs().max()).item() < 2e-2
+        assert ((slices[r].float() - want_h[r * rpr:(r + 1) * rpr].float()).abs().max()).item() < 0.05
+    # a row count that does not divide over the ranks: the last rank's tail rows are padding
+    T2 = T - 3
+    rpr2 = sps[0].rows_per_rank(T2)
+    slices = [sps[r].residual_slice(h[:T2]) for r in range(world)]
+    for r in range(world):
+        sps[r].row_linear_rs(xs[r][:T2], ws[r])
+    outs = [sps[r].reduce_add_rmsnorm(slices[r], gain, 1e-6).clone() for r in range(world)]
+    torch.cuda.synchronize()
+    want2 = ref.rmsnorm((h[:T2].float() + sum(p[:T2] for p in partials)).bfloat16(), gain, 1e-6)
+    assert outs[0].shape == (T2, H) and rpr2 * world >= T2
+    assert ((outs[0].float() - want2.float()).abs().max() / want2.float().abs().max()).item() < 2e-2
+    assert cuda.last_status() == 0
 
 
 @pytest.mark.parametrize("world", [2, 8])

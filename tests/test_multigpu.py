@@ -42,6 +42,11 @@ def test_gemm_reduce_scatter_and_fused_norm_all_gather_match_nccl():
     assert "SP_OK" in out, out[-2000:]
 
 
+def test_gemma_tensor_parallel_all_reduce_and_sequence_parallel_arms_match_single_gpu():
+    out = _torchrun(["gemma_sp"])
+    assert "GEMMA_SP_OK" in out, out[-2000:]
+
+
 def test_vocab_parallel_head_merge_kernel_matches_full_head():
     out = _torchrun(["vocab"])
     assert "VOCAB_OK" in out, out[-2000:]
