@@ -163,8 +163,11 @@ class MistralModel(nn.Module):
         return self.embed if self.lm_head is None else self.lm_head
 
     def hidden(self, ids, meta, cache):
+        return self.hidden_from_embeds(ops.embed(ids, self.embed), meta, cache)
+
+    def hidden_from_embeds(self, h, meta, cache):
+        """The stack over given input embeddings ``[T, H]`` (speech models assemble them from several tables)."""
         c = self.cfg
-        h = ops.embed(ids, self.embed)
         x = ops.rmsnorm(h, self.layers[0].ln_attn, c.rms_norm_eps)
         n = len(self.layers)
         for i, layer in enumerate(self.layers):

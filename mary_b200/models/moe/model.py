@@ -71,11 +71,46 @@ class MLAAttention(nn.Module):
         inv = None if c.use_nope else ref.rope_inv_freq(64, c.rope_theta, 1.0, device)
         self.register_buffer("inv_freq", inv, persistent=False)
 
+    PREFILL_MIN_ROWS = 48     # mean query tokens per sequence from which the expanded (non-absorbed) prefill path is used
+
+    def _prefill_expanded(self, qb, meta, cache):
+        """Prefill with the keys and values EXPANDED from the latent rows (per-head K = [W_UK^T c_kv | k_rope], V = W_UV c_kv)
+        and ordinary causal attention with 192-wide keys and 128-wide values: a third of the arithmetic of attending in the
+        576 / 512-wide latent space, which is what long query blocks are bound by.  The scores are identical
+        (q_nope . W_UK^T c_kv = W_UK q_nope . c_kv); decode keeps the absorbed form, where the cache stream is the bound."""
+        import dataclasses
+        T, H = qb.shape[0], self.H
+        q = qb.view(T, H, 192)
+        if self.inv_freq is not None:
+            q = torch.cat([q[..., :128], ref.rope(q[..., 128:], meta.positions, self.inv_freq).to(q.dtype)], -1)
+        lat = cache.k[self.li]                                              # [pages, 16, 576]
+        ps = meta.page_size
+        n_pages = [(int(n) + ps - 1) // ps for n in meta.kv_lens_host]
+        table = torch.zeros(meta.num_seqs, max(n_pages), dtype=torch.int32, device=qb.device)
+        picks, off = [], 0
+        for s, n in enumerate(n_pages):
+            picks.append(meta.page_table[s, :n])
+            table[s, :n] = torch.arange(off, off + n, dtype=torch.int32, device=qb.device)
+            off += n
+        rows = lat[torch.cat(picks).long()]                                 # [P, 16, 576] context of every sequence, page-aligned
+        P = rows.shape[0]
+        ckv = rows[..., :512].reshape(P * ps, 512)
+        if getattr(self, "_w_uk_t", None) is None:
+            self._w_uk_t = self.w_uk.permute(0, 2, 1).reshape(H * 128, 512).contiguous()      # k_nope[h, n] = sum_k c_kv[k] W_UK[h, k, n]
+        k_nope = ops.linear(ckv, self._w_uk_t).view(P, ps, H, 128)
+        v = ops.linear(ckv, self.w_uv.reshape(H * 128, 512)).view(P, ps, H, 128)
+        k = torch.cat([k_nope, rows[..., 512:].unsqueeze(2).expand(P, ps, H, 64)], -1).contiguous()
+        meta2 = dataclasses.replace(meta, page_table=table)
+        o = ops.paged_attention(q.contiguous(), k, v, meta2, self.c.attn_scale)
+        return self.par.row_linear(o.reshape(T, H * 128), self.w_o)
+
     def forward(self, x, meta, cache):
         c = self.c
         qakv = ops.linear(x, self.w_qa_kva)
         qa = ops.mla_prep(qakv, c.q_lora_rank, self.qa_norm, self.kv_norm, self.inv_freq, meta, cache.k[self.li], 1e-6)
         qb = ops.linear(qa, self.w_qb)
+        if meta.kv_lens_host is not None and meta.num_tokens >= self.PREFILL_MIN_ROWS * meta.num_seqs:
+            return self._prefill_expanded(qb, meta, cache)
         q_full = ops.mla_absorb_q(qb, self.w_uk, self.inv_freq, meta, self.H)
         o_lat = ops.mla_attention(q_full, cache.k[self.li], meta, c.attn_scale)
         o = ops.mla_unabsorb_o(o_lat, self.w_uv, self.H)

@@ -1,0 +1,2 @@
+from .model import (CodePredictor, Qwen3TTSConfig, SamplingParams, Talker, generate_frames, init_random_,  # noqa: F401
+                    load_into, process_talker_logits)

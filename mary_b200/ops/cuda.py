@@ -266,14 +266,39 @@ def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsp
     return out
 
 
+declare("mary_attention_prefill", "ppppppppp" + "iiiiiiii" + "llll" + "ifs")
+declare("mary_attention_prefill_supported", "ii")
+PREFILL_MIN_ROWS = 48     # mean query tokens per sequence from which the 128-row tensor-core tiles pay off
+
+
+def attention_prefill(q, kcache, vcache, meta, scale, window=0):
+    """Causal / sliding-window attention of whole query blocks on the tensor cores (``csrc/kernels/attention_fa.cu``):
+    ``q[T, Hq, DK]``, caches ``[pages, 16, Hkv, D]``; 128 query tokens of one head per CTA."""
+    T, Hq, DK = q.shape
+    Hkv, DV = kcache.shape[2], vcache.shape[-1]
+    assert meta.page_size == 16 and kcache.shape[1] == 16
+    blk_seq, blk_tok0, NB = _q_blocks(meta, 128)
+    out = torch.empty(T, Hq, DV, dtype=torch.bfloat16, device=q.device)
+    check(lib().mary_attention_prefill(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
+                                       _p(meta.q_start), _p(blk_seq), _p(blk_tok0), NB, T, Hq, Hkv, DK, DV, kcache.shape[0],
+                                       meta.page_table.shape[1], kcache.stride(1), kcache.stride(0), vcache.stride(1), vcache.stride(0),
+                                       int(window), float(scale), _stream()), "attention_prefill")
+    return out
+
+
 def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: int | None = None, nsplit: int | None = None,
                     kernel: str = "auto"):
     """``q[T, Hq, DK]``; caches ``[pages, page, Hkv, D]`` (a latent cache is ``Hkv = 1`` with ``dv`` < DK and
-    ``vcache is kcache``).  Returns ``[T, Hq, DV]``."""
+    ``vcache is kcache``).  Returns ``[T, Hq, DV]``.  ``kernel``: ``auto`` picks the tensor-core prefill kernel for long query
+    blocks, the bandwidth-oriented kernel for decode-shaped batches and the general split-KV kernel otherwise."""
     T, Hq, DK = q.shape
     Hkv = kcache.shape[2] if kcache.dim() == 4 else 1
     DV = dv or vcache.shape[-1]
     G = Hq // Hkv
+    if kernel in ("auto", "prefill") and kcache.dim() == 4 and dv is None and softcap == 0.0 and meta.page_size == 16 \
+            and lib().mary_attention_prefill_supported(DK, DV) and q.dtype == torch.bfloat16 \
+            and (kernel == "prefill" or T >= PREFILL_MIN_ROWS * meta.num_seqs):
+        return attention_prefill(q, kcache, vcache, meta, scale, window)
     if kernel != "general" and kcache.dim() == 4 and DK == DV and DK in (64, 128, 256) and G <= (4 if DK == 256 else 8) \
             and (meta.max_q_len <= 8 or kernel == "decode"):
         return _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsplit)

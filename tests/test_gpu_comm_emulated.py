@@ -87,7 +87,7 @@ def test_gemm_reduce_scatter_epilogue_and_fused_norm_allgather(world, T):
     slices = [h[r * rpr:(r + 1) * rpr].clone() for r in range(world)]
     for r in range(world):
         sps[r].row_linear_rs(xs[r], ws[r])
-    outs = [sps[r].reduce_add_rmsnorm(slices[r], gain, 1e-6, w_post=post, scalar=0.5).clone() for r in range(world)]
+    outs = [sps[r].reduce_add_rmsnorm(slices[r], gain, 1e-6, w_post=post, scalar=0.5) for r in range(world)]   # views: read after ALL ranks ran
     torch.cuda.synchronize()
     a = sum(partials).bfloat16()
     want_x, want_h = ops.norm_add_norm(a, post, h.clone(), gain, 1e-6, 0.5)
@@ -100,7 +100,7 @@ def test_gemm_reduce_scatter_epilogue_and_fused_norm_allgather(world, T):
     slices = [sps[r].residual_slice(h[:T2]) for r in range(world)]
     for r in range(world):
         sps[r].row_linear_rs(xs[r][:T2], ws[r])
-    outs = [sps[r].reduce_add_rmsnorm(slices[r], gain, 1e-6).clone() for r in range(world)]
+    outs = [sps[r].reduce_add_rmsnorm(slices[r], gain, 1e-6) for r in range(world)]
     torch.cuda.synchronize()
     want2 = ref.rmsnorm((h[:T2].float() + sum(p[:T2] for p in partials)).bfloat16(), gain, 1e-6)
     assert outs[0].shape == (T2, H) and rpr2 * world >= T2

@@ -120,6 +120,33 @@ def test_paged_attention_decode_and_prefill(K, Hq, Hkv, D, window, softcap):
                 assert _rel(got, want) < 2e-2, (kernel, S_lens, nsplit, _rel(got, want))
 
 
+@pytest.mark.parametrize("Hq,Hkv,DK,DV,window", [(4, 2, 64, 64, 0), (8, 2, 128, 128, 0), (4, 4, 128, 128, 96), (4, 2, 256, 256, 0),
+                                                  (4, 2, 256, 256, 200), (6, 6, 192, 128, 0)])
+def test_tensor_core_prefill_attention_matches_reference(K, Hq, Hkv, DK, DV, window):
+    """128-token query tiles on tcgen05: ragged batches, prior context in the cache, tiles that end inside a sequence,
+    sliding windows that skip whole key blocks, separate K / V widths."""
+    torch.manual_seed(DK + Hq)
+    for S_lens, q_lens in (([300, 130, 517], [300, 130, 517]), ([700, 64, 257], [190, 64, 129]), ([1500], [1500])):
+        from mary_b200.runtime.batch import BatchMeta
+        from mary_b200.runtime.kv_cache import PagedKVCache
+        pages = sum((n + 15) // 16 for n in S_lens) + 1
+        kc = torch.randn(pages, 16, Hkv, DK, device="cuda").bfloat16()
+        vc = torch.randn(pages, 16, Hkv, DV, device="cuda").bfloat16()
+        alloc = PagedKVCache(1, pages, 16, 1, 8, dtype=torch.bfloat16, device="cuda").alloc
+        for i, n in enumerate(S_lens):
+            alloc.extend(i, n)
+        table, lens = alloc.page_table(list(range(len(S_lens))))
+        meta = BatchMeta.build(q_lens, lens, table, 16, "cuda")
+        q = torch.randn(sum(q_lens), Hq, DK, device="cuda").bfloat16()
+        scale = DK ** -0.5
+        want = ref.paged_attention(q, kc, vc, meta, scale, window, 0.0)
+        got = K.paged_attention(q, kc, vc, meta, scale, window, kernel="prefill")
+        torch.cuda.synchronize()
+        assert K.last_status() == 0
+        assert got.shape == want.shape
+        assert _rel(got, want) < 2e-2, (S_lens, q_lens, _rel(got, want))
+
+
 def test_qk_norm_rope_append_matches_reference(K):
     from mary_b200 import ops
     torch.manual_seed(3)

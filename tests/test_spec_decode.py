@@ -80,3 +80,31 @@ def test_speculative_graph_replay_matches_eager_gpu():
     assert out == eager
     from mary_b200.ops import cuda
     assert cuda.last_status() == 0
+
+
+def test_mla_expanded_prefill_equals_absorbed_attention_cpu():
+    """The non-absorbed prefill path (keys / values expanded per head from the latent rows) must give the scores of the
+    absorbed latent attention: same layer, same cache, long query blocks vs the same tokens fed in short blocks."""
+    from mary_b200.models.moe.model import MLAAttention
+    from mary_b200.runtime.batch import BatchMeta
+    torch.manual_seed(0)
+    cfg = tiny_moe_config("mla")
+    m = MoEDecoder(cfg, dtype=torch.float32)
+    init_random_(m, 0)
+    attn = m.layers[0].attn
+    assert isinstance(attn, MLAAttention)
+    lens = [70, 55]
+    x = torch.randn(sum(lens), cfg.hidden_size) * 0.5
+    outs = []
+    for thresh in (1, 10 ** 6):                       # expanded path for every block / never
+        attn.PREFILL_MIN_ROWS = thresh
+        spec = m.kv_spec()
+        cache = PagedKVCache(spec["num_layers"], 12, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32, latent_dim=576)
+        for s, n in enumerate(lens):
+            cache.alloc.extend(s, n)
+        table, kl = cache.alloc.page_table([0, 1])
+        meta = BatchMeta.build(lens, kl, table, 16)
+        with torch.no_grad():
+            outs.append(attn(x, meta, cache))
+    del attn.PREFILL_MIN_ROWS
+    assert torch.allclose(outs[0], outs[1], atol=1e-4, rtol=1e-3), (outs[0] - outs[1]).abs().max()
