@@ -86,7 +86,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--replicated-head", action="store_true", help="keep the whole LM head on every rank (default: vocabulary-parallel head)")
     ap.add_argument("--no-ttft", action="store_true")
+    ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill chunk of the TTFT measurement")
     ap.add_argument("--trace", action="store_true", help="print a per-op device-time table of one eager step and exit")
+    ap.add_argument("--trace-prefill", action="store_true", help="print a per-op device-time table of one real prefill of one context and exit")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -136,7 +138,7 @@ def main():
     if world > 1 and args.comm == "fused":
         try:
             from mary_b200.parallel.symm import SymmetricHeap
-            symm = SymmetricHeap(rank, world, dev, max_bytes=max(B * (1 + k), 1024) * cfg.hidden_size * 4)   # decode rows or one prefill chunk
+            symm = SymmetricHeap(rank, world, dev, max_bytes=max(B * (1 + k), args.prefill_chunk) * cfg.hidden_size * 4)   # decode rows or one prefill chunk
         except Exception as ex:  # the fused path must never be silently absent
             raise RuntimeError(f"fused communication requested but the symmetric heap failed: {ex}") from ex
     par = ParallelGroup(rank, world, "fused" if symm else "nccl", symm=symm, ep_mode="a2a" if a2a else "replicated",
@@ -144,7 +146,7 @@ def main():
     if world > 1 and args.comm == "sp":
         assert is_gemma, "--comm sp is the dense decoders' arm"
         from mary_b200.parallel.sp import SequenceParallel
-        par.sp = SequenceParallel.distributed(rank, world, max(B * (1 + k), 1024), cfg.hidden_size, dev)
+        par.sp = SequenceParallel.distributed(rank, world, max(B * (1 + k), args.prefill_chunk), cfg.hidden_size, dev)
     if a2a:
         from mary_b200.parallel.ep import distributed_factory
         par.ep_factory = distributed_factory(rank, world, dev, t_cap=B_local * (1 + k))
@@ -188,6 +190,19 @@ def main():
     build_s = time.time() - t0
     say(f"model and cache built in {build_s:.1f} s ({slabs} expert slabs resident)")
 
+    if args.trace_prefill:
+        from mary_b200.utils.trace import Tracer
+        pc = PagedKVCache(spec["num_layers"], (ctx + 64) // page + 2, page, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16,
+                          device=dev, latent_dim=spec.get("latent_dim"))
+        pd = SpecDecoder(model, pc, 1, spec_k=k, max_len=ctx + 32, device=dev, use_graph=False)
+        prompt = rng.integers(0, cfg.vocab_size, (1, ctx))
+        pd.prefill(prompt, chunk=args.prefill_chunk)
+        torch.cuda.synchronize()
+        with Tracer() as tr:
+            pd.prefill(prompt, chunk=args.prefill_chunk)
+        if rank == 0:
+            print(tr.report())
+        return
     if args.trace:
         from mary_b200.utils.trace import Tracer
         with torch.no_grad():
@@ -286,7 +301,7 @@ def main():
                 barrier()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
-                pd.prefill(prompt, chunk=1024)
+                pd.prefill(prompt, chunk=args.prefill_chunk)
                 b.record()
                 barrier()
                 ts.append(a.elapsed_time(b))

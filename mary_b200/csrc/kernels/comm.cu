@@ -74,6 +74,12 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) 
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
   return v;
 }
+__device__ __forceinline__ uint4 multimem_ld_reduce_f32x4(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc_addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
                ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
@@ -83,21 +89,32 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, uint4 v) {
 // `blk` of `nblk` is this block's index within its rank's grid.
 // The epoch of the flags lives in device memory (`epoch_slot`, one word per block, advanced by the block itself), so a
 // launch recorded in a CUDA graph uses a fresh epoch at every replay.
+// f32 != 0: the elements are 32-bit floats (n % 4 == 0), summed in f32 (gradient buckets).
 __device__ void allreduce_bf16_body(const CommCtx& c, size_t in_off, size_t out_off, int64_t n, uint32_t* epoch_slot, int use_mc, int blk,
-                                    int nblk) {
+                                    int nblk, int f32 = 0) {
   __shared__ uint32_t epoch_s;
   if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
   __syncthreads();
   const uint32_t epoch = epoch_s;
   if (!rank_barrier(c, 0, epoch, blk)) return;
-  const int64_t nvec = n / 8;                                  // 16-byte vectors
+  const int64_t nvec = f32 ? n / 4 : n / 8;                    // 16-byte vectors
   const int64_t per = (nvec + c.world - 1) / c.world;
   const int64_t lo = (int64_t)c.rank * per, hi = min(nvec, lo + per);
   for (int64_t v = lo + (int64_t)blk * blockDim.x + threadIdx.x; v < hi; v += (int64_t)nblk * blockDim.x) {
     uint4 r;
     if (use_mc) {
-      r = multimem_ld_reduce_bf16x8(c.mc + in_off + v * 16);
+      r = f32 ? multimem_ld_reduce_f32x4(c.mc + in_off + v * 16) : multimem_ld_reduce_bf16x8(c.mc + in_off + v * 16);
       multimem_st_v4(c.mc + out_off + v * 16, r);
+    } else if (f32) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < c.world; ++p) {
+        uint4 x;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(c.bufs[p] + in_off + v * 16) : "memory");   // rank order: same sum everywhere
+        acc.x += __uint_as_float(x.x); acc.y += __uint_as_float(x.y); acc.z += __uint_as_float(x.z); acc.w += __uint_as_float(x.w);
+      }
+      r = make_uint4(__float_as_uint(acc.x), __float_as_uint(acc.y), __float_as_uint(acc.z), __float_as_uint(acc.w));
+      for (int p = 0; p < c.world; ++p) *(uint4*)(c.bufs[(c.rank + p) % c.world] + out_off + v * 16) = r;
     } else {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int p = 0; p < c.world; ++p) {
@@ -119,17 +136,17 @@ __device__ void allreduce_bf16_body(const CommCtx& c, size_t in_off, size_t out_
 }
 
 __global__ void __launch_bounds__(512)
-allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t* epochs, int use_mc) {
-  allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, use_mc, blockIdx.x, gridDim.x);
+allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t* epochs, int use_mc, int f32) {
+  allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, use_mc, blockIdx.x, gridDim.x, f32);
 }
 
 // Every rank of the group inside ONE cooperative launch on one GPU (block groups play the ranks, plain loads and stores
 // play the peer accesses): the way to exercise the flag protocol and the data movement where only one GPU is available,
 // because kernels that wait on one another must never be separate launches on the same GPU.
 __global__ void __launch_bounds__(512)
-allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t* epochs, int nblk) {
+allreduce_bf16_emulated_kernel(CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t* epochs, int nblk, int f32) {
   c.rank = blockIdx.x / nblk;
-  allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, 0, blockIdx.x % nblk, nblk);
+  allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, 0, blockIdx.x % nblk, nblk, f32);
 }
 
 // Owner side of the reduce-scatter: one CTA per local token row.  Sums the `world` staged partial rows in rank order
@@ -300,7 +317,19 @@ MARY_API int mary_allreduce_bf16(const uint64_t* bufs, const uint64_t* sigs, uin
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
-  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0);
+  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0, 0);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// The same two-shot all-reduce over 32-bit floats (n % 4 == 0), summed in f32: gradient buckets of the data-parallel trainer.
+MARY_API int mary_allreduce_f32(const uint64_t* bufs, const uint64_t* sigs, uint64_t mc, int rank, int world, uint64_t in_off,
+                                uint64_t out_off, int64_t n, uint32_t* epochs, int grid, int use_mc, uint64_t wait_ns, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || (n % 4) || (in_off % 16) || (out_off % 16) || grid < 1) return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0, 1);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -336,14 +365,20 @@ MARY_API int mary_rs_add_rmsnorm(const void* staging, void* h_slice, const void*
 }
 
 // Single-GPU emulation of a `world`-rank all-reduce: bufs / sigs are `world` distinct buffers on the current device.
+MARY_API int mary_allreduce_emulated(const uint64_t* bufs, const uint64_t* sigs, int world, uint64_t in_off, uint64_t out_off,
+                                     int64_t n, uint32_t* epochs, int grid, uint64_t wait_ns, int f32, cudaStream_t s);
 MARY_API int mary_allreduce_bf16_emulated(const uint64_t* bufs, const uint64_t* sigs, int world, uint64_t in_off, uint64_t out_off,
                                           int64_t n, uint32_t* epochs, int grid, uint64_t wait_ns, cudaStream_t s) {
-  if (world < 1 || world > MAX_RANKS || (n % 8) || grid < 1 || grid * world > mary_num_sms()) return MARY_ERR_BAD_ARG;
+  return mary_allreduce_emulated(bufs, sigs, world, in_off, out_off, n, epochs, grid, wait_ns, 0, s);
+}
+MARY_API int mary_allreduce_emulated(const uint64_t* bufs, const uint64_t* sigs, int world, uint64_t in_off, uint64_t out_off,
+                                     int64_t n, uint32_t* epochs, int grid, uint64_t wait_ns, int f32, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || (n % (f32 ? 4 : 8)) || grid < 1 || grid * world > mary_num_sms()) return MARY_ERR_BAD_ARG;
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = nullptr; c.rank = 0; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
   size_t io = in_off, oo = out_off;
-  void* args[] = {&c, &io, &oo, &n, &epochs, &grid};
+  void* args[] = {&c, &io, &oo, &n, &epochs, &grid, &f32};
   if (cudaLaunchCooperativeKernel((void*)allreduce_bf16_emulated_kernel, dim3(grid * world), dim3(512), args, 0, s) != cudaSuccess)
     return MARY_ERR_CUDA;
   return MARY_OK;

@@ -91,6 +91,29 @@ def bench_attn(cases=None):
                   f"{gb / hbm:.2f} {tag}")
 
 
+def bench_fa(B: int = 1, L: int = 4096, Hq: int = 16, Hkv: int = 16, DK: int = 192, DV: int = 128, window: int = 0, iters: int = 5):
+    """Tensor-core prefill attention: B sequences of L tokens, all of them queries (causal)."""
+    from . import cuda as K
+    from ..runtime.batch import BatchMeta
+    from ..runtime.kv_cache import PagedKVCache
+    hbm, tf, tag = peaks()
+    pages = B * ((L + 15) // 16) + 1
+    alloc = PagedKVCache(1, pages, 16, 1, 8, dtype=torch.bfloat16, device="cuda").alloc
+    for s in range(B):
+        alloc.extend(s, L)
+    table, lens = alloc.page_table(list(range(B)))
+    meta = BatchMeta.build([L] * B, lens, table, 16, "cuda")
+    kc = torch.randn(pages, 16, Hkv, DK, device="cuda").bfloat16()
+    vc = torch.randn(pages, 16, Hkv, DV, device="cuda").bfloat16()
+    q = torch.randn(B * L, Hq, DK, device="cuda").bfloat16()
+    ms = time_op(lambda: K.paged_attention(q, kc, vc, meta, DK ** -0.5, window, kernel="prefill"), iters=iters)
+    span = L / 2 if window == 0 else min(window, L / 2)
+    flops = 2.0 * B * L * Hq * span * (DK + DV)
+    print(f"prefill attn B={B} L={L} Hq={Hq} Hkv={Hkv} DK={DK} DV={DV} window={window}: {ms:.4f} ms, {flops / ms / 1e9:.1f} TFLOP/s "
+          f"({flops / ms / 1e9 / tf:.2f} {tag})")
+    assert K.last_status() == 0
+
+
 def bench_mla(B: int = 32, L: int = 4096, Hq: int = 64, q_len: int = 3, iters: int = 5):
     """MLA latent attention, decode-shaped: B sequences of L cached tokens, q_len query tokens x Hq heads each."""
     from . import cuda as K
@@ -140,13 +163,21 @@ def bench_moe(E: int = 48, H: int = 7168, F: int = 2048, T: int = 384, k: int = 
 
 
 if __name__ == "__main__":
-    # ``gemm M N K`` / ``attn B L Hq Hkv D window`` / ``mla B L Hq q_len`` / ``moe E H F T k`` run that one case only
+    # ``gemm M N K`` / ``attn B L Hq Hkv D window`` / ``fa B L Hq Hkv DK DV window`` / ``mla B L Hq q_len`` / ``moe E H F T k`` run that one case only
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     nums = [int(v) for v in sys.argv[2:]]
     if what in ("gemm", "all"):
         bench_gemm([tuple(nums)] if nums and what == "gemm" else None)
     if what in ("attn", "all"):
         bench_attn([tuple(nums)] if nums and what == "attn" else None)
+    if what in ("fa", "all"):
+        if nums and what == "fa":
+            bench_fa(*nums)
+        else:
+            bench_fa()
+            bench_fa(1, 4096, 16, 8, 256, 256)
+            bench_fa(1, 4096, 32, 8, 128, 128)
+            bench_fa(1, 4096, 16, 8, 256, 256, 1024)
     if what in ("mla", "all"):
         if nums and what == "mla":
             bench_mla(*nums)

@@ -14,6 +14,7 @@ import torch
 from ..ops.cuda import _stream, check, declare, lib
 
 declare("mary_allreduce_bf16", "pplii" + "lllpiils")
+declare("mary_allreduce_f32", "pplii" + "lllpiils")
 declare("mary_wait_flag", "piiiils")
 declare("mary_argmax_merge", "ppiiipplii" + "pilpps")
 
@@ -83,6 +84,24 @@ class SymmetricHeap:
                                         self.epochs.data_ptr(), self.grid, 1 if self.mc else 0, self.wait_ns, _stream()),
               "allreduce_bf16")
         return self.buf[self.region:self.region + n * 2].view(torch.bfloat16).view(partial.shape)
+
+    def all_reduce_f32_(self, t):
+        """In-place sum of an f32 tensor over all ranks (gradient buckets): staged through the symmetric region, reduced by the
+        same two-shot kernel in f32 (``multimem.ld_reduce.add.f32`` in the switch, or peer loads in rank order)."""
+        assert t.dtype == torch.float32
+        n = t.numel()
+        pad = (-n) % 4
+        nbytes = (n + pad) * 4
+        if nbytes > self.region:
+            raise ValueError(f"{nbytes} bytes exceed the symmetric region of {self.region}")
+        self.buf[:n * 4].view(torch.float32).copy_(t.reshape(-1))
+        if pad:
+            self.buf[n * 4:nbytes].zero_()
+        check(lib().mary_allreduce_f32(self.buf_ptrs, self.sig_ptrs, self.mc, self.rank, self.world, 0, self.region, n + pad,
+                                       self.epochs.data_ptr(), self.grid, 1 if self.mc else 0, self.wait_ns, _stream()),
+              "allreduce_f32")
+        t.reshape(-1).copy_(self.buf[self.region:self.region + n * 4].view(torch.float32))
+        return t
 
     def wait_flag(self, slot: int, want: int):
         """Launch a bounded wait on one of this rank's flags (failure-detection tests)."""

@@ -1,0 +1,77 @@
+"""LoRA finetuning step time on the Gemma-4-12B-style decoder (rank 16, alpha 32, AdamW lr 1e-4, sequences of 4096 tokens),
+data parallel over the ranks of a ``torchrun`` launch with the adapter gradients reduced per layer bucket, overlapped with
+the backward pass of the earlier layers.
+
+    python -m mary_b200.train.bench_lora [--seq 4096] [--batch 1] [--steps 5] [--layers 48] [--comm fused|nccl|none]
+
+Prints one JSON line: tokens/s over all ranks (device time, max over ranks).  Data are synthetic token ids, weights random."""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--batch", type=int, default=1, help="sequences per rank")
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--no-overlap", action="store_true")
+    a = ap.parse_args()
+    from ..models.gemma4 import Gemma4Model, gemma_12b_config
+    from ..models.gemma4.weights import init_random_
+    from ..ops import cuda as K
+    from ..parallel.group import init_distributed
+    from .trainer import LoraTrainer
+    rank, world, local = init_distributed()
+    dev = torch.device("cuda", local)
+    cfg = gemma_12b_config()
+    cfg.num_hidden_layers = a.layers
+    cfg.layer_types = cfg.layer_types[:a.layers]
+    model = Gemma4Model(cfg, dtype=torch.bfloat16, device=dev)
+    init_random_(model, 0)
+    reduce_fn = None
+    if world > 1:
+        import torch.distributed as dist
+        if a.comm == "fused":
+            from ..parallel.symm import SymmetricHeap
+            heap = SymmetricHeap(rank, world, dev, max_bytes=8 << 20)
+            reduce_fn = heap.all_reduce_f32_
+        else:
+            reduce_fn = lambda g: dist.all_reduce(g)  # noqa: E731
+    tr = LoraTrainer(model, rank=16, alpha=32.0, lr=1e-4, dp_size=world, reduce_fn=reduce_fn, overlap=not a.no_overlap)
+    g = torch.Generator(device=dev).manual_seed(rank)
+    ids = torch.randint(0, cfg.vocab_size, (a.batch, a.seq), device=dev, generator=g)
+    for _ in range(a.warmup):
+        loss = tr.step(ids)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    K.LAUNCHES = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        loss = tr.step(ids)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms = float(ms) / a.steps
+    if rank == 0:
+        print(json.dumps({"metric": "LoRA finetune tokens/s (Gemma-4-12B-style, rank 16, seq %d)" % a.seq,
+                          "value": round(world * a.batch * a.seq / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world,
+                          "ms_per_step": round(ms, 2), "loss": round(loss, 4), "layers": a.layers, "comm": a.comm if world > 1 else "none",
+                          "overlap": not a.no_overlap, "gpu_launches_per_step": K.LAUNCHES // a.steps,
+                          "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1), "kernel_status": K.last_status()}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -38,6 +38,14 @@ def main():
                 v.copy_(x)
                 got2 = heap.all_reduce(v).clone()
                 assert torch.equal(got2, got)
+            for n in (4, 1000 * 4 + 4, 1363968):                 # f32 gradient buckets (one layer of rank-16 adapters)
+                torch.manual_seed(200 + rank)
+                g = torch.randn(n, device=dev)
+                want = g.clone()
+                dist.all_reduce(want)
+                got = heap.all_reduce_f32_(g.clone())
+                torch.cuda.synchronize()
+                assert torch.allclose(got, want, atol=1e-5, rtol=1e-5), (use_mc, n, (got - want).abs().max().item())
             assert K.last_status() == 0
         dist.barrier()
         if rank == 0:
