@@ -38,22 +38,22 @@ def test_expert_parallel_all_to_all_matches_single_gpu():
 
 
 def test_gemm_reduce_scatter_and_fused_norm_all_gather_match_nccl():
-    out = _torchrun(["sp"])
+    out = _torchrun(["sp"], timeout=240)
     assert "SP_OK" in out, out[-2000:]
 
 
 def test_gemma_tensor_parallel_all_reduce_and_sequence_parallel_arms_match_single_gpu():
-    out = _torchrun(["gemma_sp"])
+    out = _torchrun(["gemma_sp"], timeout=240)
     assert "GEMMA_SP_OK" in out, out[-2000:]
 
 
 def test_vocab_parallel_head_merge_kernel_matches_full_head():
-    out = _torchrun(["vocab"])
+    out = _torchrun(["vocab"], timeout=240)
     assert "VOCAB_OK" in out, out[-2000:]
 
 
 def test_layer_pipeline_over_nccl_matches_single_gpu():
-    out = _torchrun(["pp"])
+    out = _torchrun(["pp"], timeout=240)
     assert "PP_OK" in out, out[-2000:]
 
 
