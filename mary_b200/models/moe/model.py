@@ -85,14 +85,18 @@ class MLAAttention(nn.Module):
             q = torch.cat([q[..., :128], ref.rope(q[..., 128:], meta.positions, self.inv_freq).to(q.dtype)], -1)
         lat = cache.k[self.li]                                              # [pages, 16, 576]
         ps = meta.page_size
-        n_pages = [(int(n) + ps - 1) // ps for n in meta.kv_lens_host]
-        table = torch.zeros(meta.num_seqs, max(n_pages), dtype=torch.int32, device=qb.device)
-        picks, off = [], 0
-        for s, n in enumerate(n_pages):
-            picks.append(meta.page_table[s, :n])
-            table[s, :n] = torch.arange(off, off + n, dtype=torch.int32, device=qb.device)
-            off += n
-        rows = lat[torch.cat(picks).long()]                                 # [P, 16, 576] context of every sequence, page-aligned
+        memo = meta.__dict__.setdefault("_cache", {})
+        if "mla_expand" not in memo:                                        # the same for every layer of this step
+            n_pages = [(int(n) + ps - 1) // ps for n in meta.kv_lens_host]
+            table = torch.zeros(meta.num_seqs, max(n_pages), dtype=torch.int32, device=qb.device)
+            picks, off = [], 0
+            for s, n in enumerate(n_pages):
+                picks.append(meta.page_table[s, :n])
+                table[s, :n] = torch.arange(off, off + n, dtype=torch.int32, device=qb.device)
+                off += n
+            memo["mla_expand"] = (torch.cat(picks).long(), dataclasses.replace(meta, page_table=table))
+        pick, meta2 = memo["mla_expand"]
+        rows = lat[pick]                                                    # [P, 16, 576] context of every sequence, page-aligned
         P = rows.shape[0]
         ckv = rows[..., :512].reshape(P * ps, 512)
         if getattr(self, "_w_uk_t", None) is None:
@@ -100,7 +104,6 @@ class MLAAttention(nn.Module):
         k_nope = ops.linear(ckv, self._w_uk_t).view(P, ps, H, 128)
         v = ops.linear(ckv, self.w_uv.reshape(H * 128, 512)).view(P, ps, H, 128)
         k = torch.cat([k_nope, rows[..., 512:].unsqueeze(2).expand(P, ps, H, 64)], -1).contiguous()
-        meta2 = dataclasses.replace(meta, page_table=table)
         o = ops.paged_attention(q.contiguous(), k, v, meta2, self.c.attn_scale)
         return self.par.row_linear(o.reshape(T, H * 128), self.w_o)
 
