@@ -1,4 +1,5 @@
-"""``mary import <checkpoint dir|file> --pile P --key K [--dtype f16|bf16|f32] [--name N]`` and ``mary keys --pile P``.
+"""``mary import <checkpoint dir|file> --pile P --key K [--dtype f16|bf16|f32] [--name N]``, ``mary keys --pile P``, and the pile
+maintenance commands ``mary branches|verify|stats --pile P`` (the reference's ``pile_branches`` / ``pile_leaf_verify`` binaries).
 
 The front-door CLI of the reference (src/bin/mary.rs:54-240): import a checkpoint (safetensors > gguf > pickle) with its
 ``config.json`` and ``tokenizer.json`` into a pile as one signed commit of the model-graph collection (idempotent: re-importing
@@ -43,6 +44,65 @@ def cmd_keys(a) -> int:
     return 0
 
 
+def cmd_branches(a) -> int:
+    """Branches of a pile with their heads and commit counts (the reference's ``pile_branches`` binary)."""
+    from ..pile.repo import Repository
+    pile = Pile.open(a.pile, create=False)
+    repo = Repository(pile)
+    for name, ids in sorted(repo.branches().items()):
+        for bid in ids:
+            head = repo.head(bid)
+            n = len(repo.ancestors(head, verify=not a.no_verify)) if head else 0
+            print(f"{name}  id={bid.hex()}  head={head.hex() if head else '-'}  commits={n}")
+    pile.close()
+    return 0
+
+
+def cmd_verify(a) -> int:
+    """Re-hash every blob record and parse every tensor leaf of every model root (``pile_leaf_verify``): exit 1 on the first
+    record whose bytes do not hash to its handle or whose leaf header is inconsistent with its payload."""
+    from ..format.model import load_module_leaf
+    from ..pile.hashing import blake3
+    from ..pile.store import KIND_BLOB
+    pile = Pile.open(a.pile, create=False, validate=False)
+    n = bad = 0
+    for rec in pile.records():
+        if rec.kind != KIND_BLOB:
+            continue
+        n += 1
+        if blake3(pile.get(rec.hash)) != rec.hash:
+            print(f"CORRUPT blob {rec.hash.hex()} at offset {rec.offset}")
+            bad += 1
+    facts = read_model_pile(pile)
+    leaves = 0
+    for r in model_roots(facts):
+        for name, ent in index_keymap(pile, facts, r).items():
+            try:
+                leaf = load_module_leaf(pile, facts, ent)
+                leaf.to_f32() if a.deep else None
+                leaves += 1
+            except Exception as ex:  # report and count every broken leaf
+                print(f"BAD leaf {name}: {ex}")
+                bad += 1
+    print(f"{n} blobs, {leaves} tensor leaves, {bad} problems")
+    pile.close()
+    return 1 if bad else 0
+
+
+def cmd_stats(a) -> int:
+    pile = Pile.open(a.pile, create=False)
+    kinds = {}
+    for rec in pile.records():
+        k = kinds.setdefault(rec.kind, [0, 0])
+        k[0] += 1
+        k[1] += rec.length
+    print(f"{a.pile}: {pile.size} bytes")
+    for kind, (cnt, nbytes) in sorted(kinds.items()):
+        print(f"  kind {kind}: {cnt} records, {nbytes} payload bytes")
+    pile.close()
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mary")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -57,6 +117,17 @@ def main(argv=None) -> int:
     k.add_argument("--pile", required=True)
     k.add_argument("-v", "--verbose", action="store_true")
     k.set_defaults(fn=cmd_keys)
+    b = sub.add_parser("branches")
+    b.add_argument("--pile", required=True)
+    b.add_argument("--no-verify", action="store_true", help="skip the signature check of every commit")
+    b.set_defaults(fn=cmd_branches)
+    v = sub.add_parser("verify")
+    v.add_argument("--pile", required=True)
+    v.add_argument("--deep", action="store_true", help="also decode every leaf to f32")
+    v.set_defaults(fn=cmd_verify)
+    st = sub.add_parser("stats")
+    st.add_argument("--pile", required=True)
+    st.set_defaults(fn=cmd_stats)
     a = ap.parse_args(argv)
     return a.fn(a)
 

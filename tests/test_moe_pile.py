@@ -51,3 +51,29 @@ def test_admission_bill_and_metrics():
     log.emit("request", ttft_s=0.5)
     s = log.summary()
     assert abs(s["tokens_per_s"] - 1280) < 1e-6 and abs(s["acceptance"] - 30 / 256) < 1e-9
+
+
+def test_moe_forward_cli_serves_a_pile_and_maintenance_commands(tmp_path, capsys):
+    """The serving CLI loads a persisted decoder config-free and decodes batched slots with MTP speculation; its tokens equal
+    plain greedy decoding; ``mary branches|verify|stats`` read the same pile."""
+    from mary_b200.cli import mary, moe_forward
+    from mary_b200.models.moe.weights import save_to_pile
+    from mary_b200.pile import Pile, signing_key_file
+    torch.manual_seed(0)
+    cfg = tiny_moe_config("mla")
+    m = MoEDecoder(cfg, dtype=torch.bfloat16)
+    init_random_(m, 0)
+    path = str(tmp_path / "m.pile")
+    pile = Pile.open(path)
+    save_to_pile(pile, signing_key_file(str(tmp_path / "key")), m, name="tiny-moe")
+    pile.close()
+    outs = {}
+    for spec in (0, 2):
+        assert moe_forward.main(["--pile", path, "--ids", "5,6,7,8,9;11,12,13,14,15", "--max-new", "6", "--spec", str(spec), "--device", "cpu"]) == 0
+        outs[spec] = [l for l in capsys.readouterr().out.strip().splitlines() if l]
+    assert len(outs[0]) == 2 and outs[0] == outs[2]                    # speculation never changes the tokens
+    assert all(len(l.split(",")) == 6 for l in outs[0])
+    assert mary.main(["branches", "--pile", path]) == 0
+    assert mary.main(["verify", "--pile", path, "--deep"]) == 0
+    assert "0 problems" in capsys.readouterr().out
+    assert mary.main(["stats", "--pile", path]) == 0
