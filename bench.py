@@ -198,7 +198,10 @@ def main():
     max_len = ctx + (steps_total + 8) * (1 + k) + 16
     max_len = (max_len + 15) // 16 * 16
     n_cache_layers = cfg.num_hidden_layers + cfg.num_mtp_layers
-    page = 16
+    # latent (MLA) caches use 32-token pages: the attention kernel then fetches a whole 32-key stage with one TMA operation;
+    # the GQA decoders keep the 16-token pages their workload names
+    page = 32 if getattr(cfg, "attention", "") == "mla" else 16
+    max_len = (max_len + 31) // 32 * 32
     pages = B * (max_len // page) + 8
     if is_gemma:
         from mary_b200.models.gemma4.weights import init_random_ as gemma_init
@@ -360,7 +363,7 @@ def main():
                        "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,
                        "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
                                        f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
-                       "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": dec.graph is not None,
+                       "kv_page_tokens": page, "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": dec.graph is not None,
                        "lm_head": "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated",
                        "expert_slabs_resident": slabs, "moe_layers": n_moe,
                        "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",

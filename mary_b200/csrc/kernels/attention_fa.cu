@@ -4,8 +4,10 @@
 // (src/models/inkling/banded.rs:109-299) or with materialised score blocks and library matmuls
 // (src/models/inkling/burn.rs:550-797).  Here one CTA owns 128 query tokens of one head (MMA M = 128) and streams the
 // keys and values of its KV head through shared memory 64 keys at a time, page by page:
-//   warp 0    TMA for Q (once) and the K ring: per 64-key stage one [16 tokens x 64 dims] operation per page and
-//             64-dim chunk, laid out [chunks][64 keys][64 dims] with the 128-byte swizzle;
+//   warp 0    TMA for Q (once) and the K ring, a stage laid out [chunks][64 keys][64 dims] with the 128-byte swizzle.  With
+//             64-token pages a stage is ONE 4-D operation (the tensor map orders the cache as dims-in-chunk, tokens,
+//             chunks, pages, so the box [64, 64, chunks, 1] lands chunk-major); with 16-token pages it takes one
+//             [16 tokens x 64 dims] operation per page and chunk, and the TMA unit's per-operation cost bounds the kernel;
 //   warp 6    TMA for the V ring (same layout) — a ring of its own, so a K stage is refilled as soon as Q K^T has read
 //             it and does not wait for the P V of that block;
 //   warp 1    MMA: S[128 x 64] = Q K^T into one of two TMEM buffers (issued two blocks ahead), O[128 x DV] += P V with
@@ -45,7 +47,7 @@ struct FaCfg {
 struct FaParams {
   const int* page_table; const int* kv_len; const int* q_start; const int* blk_seq; const int* blk_tok0;
   __nv_bfloat16* out;      // [T, Hq, DV]
-  int max_pages, Hq, Hkv, window;
+  int max_pages, Hq, Hkv, window, page;
   float scale_log2;
   int* status;
 };
@@ -140,6 +142,13 @@ fa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) goto done;
+        if (p.page == KB) {
+          if (lane == 0) {
+            const int key0 = b * KB;
+            const int page = (key0 < kvlen) ? pt[key0 / KB] : pt[0];
+            tma_load_4d(ring + stage * stage_bytes, tm, &full[stage], 0, 0, kvh * nchunk, page);
+          }
+        } else
         // (KB / PAGE) pages x nchunk chunks operations of [16 tokens x 64 dims] (2 KB each), spread over the lanes
         for (int op = lane; op < (KB / PAGE) * nchunk; op += 32) {
           const int pg = op / nchunk, c = op % nchunk;
@@ -299,18 +308,28 @@ done:
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
-int make_cache_map(CUtensorMap* m, const void* cache, int row_elems, int num_pages, int64_t tok_stride, int64_t page_stride) {
+int make_cache_map(CUtensorMap* m, const void* cache, int heads, int hd, int num_pages, int64_t tok_stride, int64_t page_stride, int page) {
   PFN_encodeTiled enc = mary_encode_fn();
   if (!enc) return MARY_ERR_CUDA;
-  // dims: elements of one token row (all KV heads), 16 tokens of a page, pages; box = [64 dims x 16 tokens] of one page
-  cuuint64_t dims[3] = {(cuuint64_t)row_elems, PAGE, (cuuint64_t)num_pages};
-  cuuint64_t strides[2] = {(cuuint64_t)tok_stride * 2, (cuuint64_t)page_stride * 2};
-  cuuint32_t box[3] = {CHUNK, PAGE, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  if (enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return MARY_ERR_CUDA;
-  return MARY_OK;
+  CUresult r;
+  if (page == KB) {
+    // dims: 64 elements of a chunk, 64 tokens of a page, chunks of a token row (all KV heads), pages; box = all chunks of one head
+    cuuint64_t dims[4] = {CHUNK, KB, (cuuint64_t)(heads * hd / CHUNK), (cuuint64_t)num_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)tok_stride * 2, CHUNK * 2, (cuuint64_t)page_stride * 2};
+    cuuint32_t box[4] = {CHUNK, KB, (cuuint32_t)(hd / CHUNK), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  } else {
+    // dims: elements of one token row (all KV heads), 16 tokens of a page, pages; box = [64 dims x 16 tokens] of one page
+    cuuint64_t dims[3] = {(cuuint64_t)(heads * hd), PAGE, (cuuint64_t)num_pages};
+    cuuint64_t strides[2] = {(cuuint64_t)tok_stride * 2, (cuuint64_t)page_stride * 2};
+    cuuint32_t box[3] = {CHUNK, PAGE, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  return r == CUDA_SUCCESS ? MARY_OK : MARY_ERR_CUDA;
 }
 
 template <int DK, int DV>
@@ -335,25 +354,26 @@ MARY_API int mary_attention_prefill_supported(int DK, int DV) {
   return (DK == 64 && DV == 64) || (DK == 128 && DV == 128) || (DK == 192 && DV == 128) || (DK == 256 && DV == 256);
 }
 
-// q [T, Hq, DK] bf16 contiguous; kcache [pages, 16, Hkv, DK] and vcache [pages, 16, Hkv, DV] bf16 with element strides per token
+// q [T, Hq, DK] bf16 contiguous; kcache [pages, page_size (16 or 64), Hkv, DK] and vcache [.., Hkv, DV] bf16 with element strides per token
 // and per page (heads contiguous inside a token row); out [T, Hq, DV] bf16.  blk_seq / blk_tok0: NB tiles of at most 128 query
 // tokens that never cross a sequence.  Causal with the last query token of a sequence at position kv_len - 1; window > 0 keeps
 // keys (pos - window, pos].  Returns MARY_ERR_BAD_ARG for head dims without an instantiation.
 MARY_API int mary_attention_prefill(const void* q, const void* kcache, const void* vcache, void* out, const int* page_table,
                                     const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_tok0, int NB, int T, int Hq,
                                     int Hkv, int DK, int DV, int num_pages, int max_pages, int64_t k_tok_stride, int64_t k_page_stride,
-                                    int64_t v_tok_stride, int64_t v_page_stride, int window, float scale, cudaStream_t s) {
+                                    int64_t v_tok_stride, int64_t v_page_stride, int window, float scale, int page_size,
+                                    cudaStream_t s) {
   if (NB <= 0) return MARY_OK;
-  if (!mary_attention_prefill_supported(DK, DV) || Hkv < 1 || Hq % Hkv) return MARY_ERR_BAD_ARG;
+  if (!mary_attention_prefill_supported(DK, DV) || Hkv < 1 || Hq % Hkv || (page_size != PAGE && page_size != KB)) return MARY_ERR_BAD_ARG;
   if ((k_tok_stride * 2) % 16 || (k_page_stride * 2) % 16 || (v_tok_stride * 2) % 16 || (v_page_stride * 2) % 16) return MARY_ERR_BAD_ARG;
   CUtensorMap tq, tk, tv;
   int rc = mary_make_tmap_2d(&tq, q, 4, (uint64_t)T, (uint64_t)Hq * DK, (uint64_t)Hq * DK, TR, CHUNK, 1);
   if (rc) return rc;
-  if ((rc = make_cache_map(&tk, kcache, Hkv * DK, num_pages, k_tok_stride, k_page_stride))) return rc;
-  if ((rc = make_cache_map(&tv, vcache, Hkv * DV, num_pages, v_tok_stride, v_page_stride))) return rc;
+  if ((rc = make_cache_map(&tk, kcache, Hkv, DK, num_pages, k_tok_stride, k_page_stride, page_size))) return rc;
+  if ((rc = make_cache_map(&tv, vcache, Hkv, DV, num_pages, v_tok_stride, v_page_stride, page_size))) return rc;
   FaParams p;
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_tok0 = blk_tok0;
-  p.out = (__nv_bfloat16*)out; p.max_pages = max_pages; p.Hq = Hq; p.Hkv = Hkv; p.window = window;
+  p.out = (__nv_bfloat16*)out; p.max_pages = max_pages; p.Hq = Hq; p.Hkv = Hkv; p.window = window; p.page = page_size;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = mary_status_ptr();
   if (DK == 64) return launch_fa<64, 64>(tq, tk, tv, p, NB, s);
   if (DK == 128) return launch_fa<128, 128>(tq, tk, tv, p, NB, s);

@@ -9,8 +9,11 @@
 // (token, head) pair; rows of one sequence are contiguous in q[T * Hq, 576].  The head dimension (576) makes shared
 // memory the binding resource: 64 query rows (72 KB) leave room for FOUR 32-key stages of the cache (4 x 36 KB), deep
 // enough that the tensor pipe always has a queued Q K^T while the softmax of an earlier block runs.
-//   warp 0   TMA: the Q tile once (9 chunks of [64 x 64]); per 32-key stage 18 small TMAs (one per page and 64-dim
-//            chunk, issued by different lanes) that lay the stage out as [9 chunks][32 keys][64 dims], 128-byte swizzle;
+//   warp 0   TMA: the Q tile once (9 chunks of [64 x 64]); a 32-key stage is laid out [9 chunks][32 keys][64 dims] with the
+//            128-byte swizzle.  With 32-token pages that is ONE 4-D TMA operation per stage (the tensor map orders the cache
+//            as dims-in-chunk, tokens, chunks, pages, so the box [64, 32, 9, 1] lands chunk-major): 36 KB per operation.
+//            With 16-token pages it takes 18 operations of 2 KB (one per page and chunk, issued by different lanes), and
+//            the TMA unit's per-operation cost, not HBM, then bounds the stream;
 //   warp 1   MMA (M = 64): S[64 x 32] = Q K^T (9 chunks x 4 MMAs of 64x32x16; three S buffers in TMEM, issued two
 //            blocks ahead), then O[64 x 256] += P V with V^T taken from the SAME shared-memory stage as an MN-major
 //            B operand (P double buffered in shared memory).  An M = 64 accumulator occupies only lanes 0-15 of each
@@ -51,7 +54,7 @@ struct MlaParams {
   __nv_bfloat16* out;      // [T * Hq, 512]
   float* part_o;           // [NB, nsplit, 64, 512] when nsplit > 1
   float* part_ml;          // [NB, nsplit, 64, 2]
-  int max_pages, Hq, nsplit;
+  int max_pages, Hq, nsplit, page;
   float scale_log2;        // softmax scale * log2(e)
   int* status;
 };
@@ -136,8 +139,15 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         ok = __shfl_sync(0xffffffffu, ok, 0);
         if (!ok) goto done;
-        // 2 pages x 9 chunks = 18 operations of [16 tokens x 64 dims] (2 KB each)
-        if (lane < (KB / PAGE) * NCHUNK) {
+        if (p.page == KB) {
+          // one operation brings the whole stage: box [64 dims, 32 tokens, 9 chunks] of one page
+          if (lane == 0) {
+            const int key0 = b * KB;
+            const int page = (key0 < kvlen) ? pt[key0 / KB] : pt[0];
+            tma_load_4d(sK + stage * STAGE_BYTES, &tm_kv, &k_full[stage], 0, 0, 0, page);
+          }
+        } else if (lane < (KB / PAGE) * NCHUNK) {
+          // 2 pages x 9 chunks = 18 operations of [16 tokens x 64 dims] (2 KB each)
           const int pg = lane / NCHUNK, c = lane % NCHUNK;
           const int key0 = b * KB + pg * PAGE;
           // pages past the sequence end read the first page (their scores are masked)
@@ -355,23 +365,32 @@ typedef CUresult (*PFN_encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, vo
 MARY_API int64_t mary_mla_scratch_floats(int NB, int nsplit) { return nsplit > 1 ? (int64_t)NB * nsplit * TR * (DV + 2) : 0; }
 MARY_API int mary_mla_tile_rows() { return TR; }
 
-// q [T * Hq, 576] bf16 (rows = token-major, head-minor); cache [pages, 16, 576] bf16 with element strides
+// q [T * Hq, 576] bf16 (rows = token-major, head-minor); cache [pages, page_size (16 or 32), 576] bf16 with element strides
 // tok_stride / page_stride; out [T * Hq, 512] bf16.  blk_seq / blk_row0: NB tiles of query rows (row0 is a global
 // row index; a tile never crosses a sequence).  Tiles hold at most mary_mla_tile_rows() rows.
 MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, const int* page_table, const int* kv_len, const int* q_start,
                                 const int* blk_seq, const int* blk_row0, int NB, int total_rows, int num_pages, int max_pages,
                                 int64_t tok_stride, int64_t page_stride, int Hq, int nsplit, float scale, float* scratch,
-                                cudaStream_t s) {
+                                int page_size, cudaStream_t s) {
   if (NB <= 0) return MARY_OK;
   if (nsplit < 1) nsplit = 1;
   if (nsplit > 1 && !scratch) return MARY_ERR_BAD_ARG;
-  if ((tok_stride * 2) % 16 || (page_stride * 2) % 16) return MARY_ERR_BAD_ARG;
+  if ((tok_stride * 2) % 16 || (page_stride * 2) % 16 || (page_size != PAGE && page_size != KB)) return MARY_ERR_BAD_ARG;
   PFN_encode enc = (PFN_encode)mary_encode_fn();
   if (!enc) return MARY_ERR_CUDA;
   CUtensorMap tq, tkv;
   int rc = mary_make_tmap_2d(&tq, q, 4, (uint64_t)total_rows, DK, DK, TR, CHUNK, 1);
   if (rc) return rc;
-  {
+  if (page_size == KB) {
+    // dims: 64 elements of a chunk, 32 tokens of a page, 9 chunks of a token row, pages; box = one whole page, chunk-major
+    cuuint64_t dims[4] = {CHUNK, KB, NCHUNK, (cuuint64_t)num_pages};
+    cuuint64_t strides[3] = {(cuuint64_t)tok_stride * 2, CHUNK * 2, (cuuint64_t)page_stride * 2};
+    cuuint32_t box[4] = {CHUNK, KB, NCHUNK, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tkv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return MARY_ERR_CUDA;
+  } else {
     // dims: 576 elements of a token row, 16 tokens of a page, pages; box = [64 dims x 16 tokens] of one page
     cuuint64_t dims[3] = {DK, PAGE, (cuuint64_t)num_pages};
     cuuint64_t strides[2] = {(cuuint64_t)tok_stride * 2, (cuuint64_t)page_stride * 2};
@@ -389,7 +408,7 @@ MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, con
   MlaParams p;
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_row0 = blk_row0;
   p.out = (__nv_bfloat16*)out; p.part_o = scratch; p.part_ml = scratch ? scratch + (int64_t)NB * nsplit * TR * DV : nullptr;
-  p.max_pages = max_pages; p.Hq = Hq; p.nsplit = nsplit; p.scale_log2 = scale * 1.4426950408889634f; p.status = mary_status_ptr();
+  p.max_pages = max_pages; p.Hq = Hq; p.nsplit = nsplit; p.page = page_size; p.scale_log2 = scale * 1.4426950408889634f; p.status = mary_status_ptr();
   mla_attn_kernel<<<dim3(NB, nsplit), NTHREADS, SMEM, s>>>(tq, tkv, p);
   MARY_CHECK_LAUNCH();
   if (nsplit > 1) {

@@ -78,26 +78,14 @@ class MLAAttention(nn.Module):
         and ordinary causal attention with 192-wide keys and 128-wide values: a third of the arithmetic of attending in the
         576 / 512-wide latent space, which is what long query blocks are bound by.  The scores are identical
         (q_nope . W_UK^T c_kv = W_UK q_nope . c_kv); decode keeps the absorbed form, where the cache stream is the bound."""
-        import dataclasses
         T, H = qb.shape[0], self.H
         q = qb.view(T, H, 192)
         if self.inv_freq is not None:
             q = torch.cat([q[..., :128], ref.rope(q[..., 128:], meta.positions, self.inv_freq).to(q.dtype)], -1)
-        lat = cache.k[self.li]                                              # [pages, 16, 576]
-        ps = meta.page_size
-        memo = meta.__dict__.setdefault("_cache", {})
-        if "mla_expand" not in memo:                                        # the same for every layer of this step
-            n_pages = [(int(n) + ps - 1) // ps for n in meta.kv_lens_host]
-            table = torch.zeros(meta.num_seqs, max(n_pages), dtype=torch.int32, device=qb.device)
-            picks, off = [], 0
-            for s, n in enumerate(n_pages):
-                picks.append(meta.page_table[s, :n])
-                table[s, :n] = torch.arange(off, off + n, dtype=torch.int32, device=qb.device)
-                off += n
-            memo["mla_expand"] = (torch.cat(picks).long(), dataclasses.replace(meta, page_table=table))
-        pick, meta2 = memo["mla_expand"]
-        rows = lat[pick]                                                    # [P, 16, 576] context of every sequence, page-aligned
-        P = rows.shape[0]
+        lat = cache.k[self.li]                                              # [pages, page, 576]
+        pick, meta2 = meta.repage(64)                                       # the same for every layer of this step
+        rows = lat[pick].view(-1, 64, 576)                                  # context of every sequence in 64-token pages
+        P, ps = rows.shape[0], 64
         ckv = rows[..., :512].reshape(P * ps, 512)
         if getattr(self, "_w_uk_t", None) is None:
             self._w_uk_t = self.w_uk.permute(0, 2, 1).reshape(H * 128, 512).contiguous()      # k_nope[h, n] = sum_k c_kv[k] W_UK[h, k, n]

@@ -114,24 +114,24 @@ def bench_fa(B: int = 1, L: int = 4096, Hq: int = 16, Hkv: int = 16, DK: int = 1
     assert K.last_status() == 0
 
 
-def bench_mla(B: int = 32, L: int = 4096, Hq: int = 64, q_len: int = 3, iters: int = 5):
+def bench_mla(B: int = 32, L: int = 4096, Hq: int = 64, q_len: int = 3, page: int = 16, iters: int = 5):
     """MLA latent attention, decode-shaped: B sequences of L cached tokens, q_len query tokens x Hq heads each."""
     from . import cuda as K
     from ..runtime.batch import BatchMeta
     from ..runtime.kv_cache import PagedKVCache
     hbm, tf, tag = peaks()
-    pages = B * ((L + 15) // 16) + 1
-    cache = PagedKVCache(1, pages, 16, 1, 1, dtype=torch.bfloat16, device="cuda", latent_dim=576)
+    pages = B * ((L + page - 1) // page) + 1
+    cache = PagedKVCache(1, pages, page, 1, 1, dtype=torch.bfloat16, device="cuda", latent_dim=576)
     for s in range(B):
         cache.alloc.extend(s, L)
     table, lens = cache.alloc.page_table(list(range(B)))
-    meta = BatchMeta.build([q_len] * B, lens, table, 16, "cuda")
+    meta = BatchMeta.build([q_len] * B, lens, table, page, "cuda")
     cache.k[0].normal_()
     q = (torch.randn(B * q_len, Hq, 576, device="cuda") * 0.3).bfloat16()
     ms = time_op(lambda: K.mla_attention(q, cache.k[0], meta, 576 ** -0.5), iters=iters)
     flops = 2.0 * B * q_len * Hq * L * (576 + 512)
     gb = B * L * 1152 / ms / 1e6
-    print(f"mla attn B={B} L={L} Hq={Hq} q_len={q_len}: {ms:.4f} ms, {flops / ms / 1e9:.1f} TFLOP/s ({flops / ms / 1e9 / tf:.2f} {tag}), "
+    print(f"mla attn B={B} L={L} Hq={Hq} q_len={q_len} page={page}: {ms:.4f} ms, {flops / ms / 1e9:.1f} TFLOP/s ({flops / ms / 1e9 / tf:.2f} {tag}), "
           f"KV stream {gb:.0f} GB/s ({gb / hbm:.2f} {tag})")
     assert K.last_status() == 0
 
@@ -182,7 +182,9 @@ if __name__ == "__main__":
         if nums and what == "mla":
             bench_mla(*nums)
         else:
-            bench_mla()
-            bench_mla(Hq=8)
+            for pg in (16, 32):
+                bench_mla(page=pg)
+                bench_mla(Hq=8, page=pg)
+                bench_mla(B=16, page=pg)
     if what in ("moe", "all"):
         bench_moe(*(nums if what == "moe" else []))

@@ -266,23 +266,32 @@ def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsp
     return out
 
 
-declare("mary_attention_prefill", "ppppppppp" + "iiiiiiii" + "llll" + "ifs")
+declare("mary_attention_prefill", "ppppppppp" + "iiiiiiii" + "llll" + "ifis")
 declare("mary_attention_prefill_supported", "ii")
 PREFILL_MIN_ROWS = 48     # mean query tokens per sequence from which the 128-row tensor-core tiles pay off
 
 
 def attention_prefill(q, kcache, vcache, meta, scale, window=0):
     """Causal / sliding-window attention of whole query blocks on the tensor cores (``csrc/kernels/attention_fa.cu``):
-    ``q[T, Hq, DK]``, caches ``[pages, 16, Hkv, D]``; 128 query tokens of one head per CTA."""
+    ``q[T, Hq, DK]``, caches ``[pages, page, Hkv, D]``; 128 query tokens of one head per CTA.  A cache with 64-token pages is
+    streamed with one TMA operation per 64-key stage; a cache with smaller pages is first regrouped into 64-token pages (one
+    gather, small beside the attention arithmetic) when the host knows the sequence lengths."""
     T, Hq, DK = q.shape
     Hkv, DV = kcache.shape[2], vcache.shape[-1]
-    assert meta.page_size == 16 and kcache.shape[1] == 16
+    ps = meta.page_size
+    assert kcache.shape[1] == ps
+    if ps in (16, 32) and meta.kv_lens_host is not None:
+        pick, meta = meta.repage(64)
+        kcache = kcache[pick].view(-1, 64, Hkv, DK)
+        vcache = vcache[pick].view(-1, 64, Hkv, DV)
+        ps = 64
+    assert ps in (16, 64)
     blk_seq, blk_tok0, NB = _q_blocks(meta, 128)
     out = torch.empty(T, Hq, DV, dtype=torch.bfloat16, device=q.device)
     check(lib().mary_attention_prefill(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
                                        _p(meta.q_start), _p(blk_seq), _p(blk_tok0), NB, T, Hq, Hkv, DK, DV, kcache.shape[0],
                                        meta.page_table.shape[1], kcache.stride(1), kcache.stride(0), vcache.stride(1), vcache.stride(0),
-                                       int(window), float(scale), _stream()), "attention_prefill")
+                                       int(window), float(scale), ps, _stream()), "attention_prefill")
     return out
 
 
@@ -295,7 +304,7 @@ def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: i
     Hkv = kcache.shape[2] if kcache.dim() == 4 else 1
     DV = dv or vcache.shape[-1]
     G = Hq // Hkv
-    if kernel in ("auto", "prefill") and kcache.dim() == 4 and dv is None and softcap == 0.0 and meta.page_size == 16 \
+    if kernel in ("auto", "prefill") and kcache.dim() == 4 and dv is None and softcap == 0.0 and meta.page_size in (16, 32, 64) \
             and lib().mary_attention_prefill_supported(DK, DV) and q.dtype == torch.bfloat16 \
             and (kernel == "prefill" or T >= PREFILL_MIN_ROWS * meta.num_seqs):
         return attention_prefill(q, kcache, vcache, meta, scale, window)
@@ -367,7 +376,7 @@ def quantize_nvfp4(x):
 
 
 # --------------------------------------------------------------------------- MLA
-declare("mary_mla_attention", "pppppppp" + "iiii" + "ll" + "ii" + "f" + "ps")
+declare("mary_mla_attention", "pppppppp" + "iiii" + "ll" + "ii" + "f" + "pis")
 declare("mary_mla_scratch_floats", "ii", ret64=True)
 declare("mary_mla_tile_rows", "")
 
@@ -392,9 +401,11 @@ def _row_tiles(meta, hq: int):
 
 
 def mla_attention(q, cache, meta, scale, nsplit: int | None = None):
-    """``q[T, Hq, 576]`` bf16, ``cache[pages, 16, 576]`` bf16 (finite everywhere) -> ``[T, Hq, 512]``."""
+    """``q[T, Hq, 576]`` bf16, ``cache[pages, page (16 or 32), 576]`` bf16 (finite everywhere) -> ``[T, Hq, 512]``.  With
+    32-token pages the kernel fetches a whole 32-key stage with one TMA operation."""
     T, Hq, DK = q.shape
-    assert DK == 576 and cache.shape[1] == 16 and cache.shape[-1] == 576 and meta.page_size == 16
+    ps = meta.page_size
+    assert DK == 576 and ps in (16, 32) and cache.shape[1] == ps and cache.shape[-1] == 576
     blk_seq, blk_r0, NB = _row_tiles(meta, Hq)
     if nsplit is None:
         nsplit = max(1, min(8, 148 // max(1, NB), meta.max_kv_len // 512))
@@ -402,10 +413,10 @@ def mla_attention(q, cache, meta, scale, nsplit: int | None = None):
     scratch = None
     if nsplit > 1:
         scratch = torch.empty(lib().mary_mla_scratch_floats(NB, nsplit), dtype=torch.float32, device=q.device)
-    c = cache.view(cache.shape[0], 16, 576)
+    c = cache.view(cache.shape[0], ps, 576)
     check(lib().mary_mla_attention(_p(q.contiguous()), _p(c), _p(out), _p(meta.page_table), _p(meta.kv_len), _p(meta.q_start),
                                    _p(blk_seq), _p(blk_r0), NB, T * Hq, c.shape[0], meta.page_table.shape[1], c.stride(1),
-                                   c.stride(0), Hq, nsplit, scale, _p(scratch), _stream()), "mla_attention")
+                                   c.stride(0), Hq, nsplit, scale, _p(scratch), ps, _stream()), "mla_attention")
     return out
 
 

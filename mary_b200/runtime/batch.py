@@ -51,3 +51,30 @@ class BatchMeta:
                          slot_mapping=t(slots, torch.int64), page_size=page_size, max_q_len=int(q_lens.max()) if S else 0,
                          max_kv_len=int(kv_lens.max()) if S else 0, num_seqs=S, num_tokens=T,
                          all_decode=bool(S and q_lens.max() == 1), q_lens_host=q_lens, kv_lens_host=kv_lens)
+
+    def repage(self, target: int = 64):
+        """Regroup every sequence's pages into ``target``-token pages: returns ``(pick, meta)`` where ``cache[pick]`` viewed as
+        ``[-1, target, ...]`` holds the sequences' rows in ``target``-token pages and ``meta`` addresses them (``pick`` lists each
+        sequence's pages in order, padded to a multiple of ``target / page_size`` with its first page; the padding lies beyond
+        ``kv_len`` and is never visible).  Needs the host copy of the lengths; memoised, since every layer asks for the same."""
+        import dataclasses
+        memo = self.__dict__.setdefault("_cache", {})
+        key = ("repage", target)
+        if key not in memo:
+            ps = self.page_size
+            assert target % ps == 0 and self.kv_lens_host is not None
+            per = target // ps
+            nbig = [(int(n) + target - 1) // target for n in self.kv_lens_host]
+            dev = self.page_table.device
+            table = torch.zeros(self.num_seqs, max(max(nbig), 1), dtype=torch.int32, device=dev)
+            picks, off = [], 0
+            for s, n in enumerate(nbig):
+                have = (int(self.kv_lens_host[s]) + ps - 1) // ps
+                row = self.page_table[s, :have]
+                if n * per > have:
+                    row = torch.cat([row, self.page_table[s, :1].expand(n * per - have)])
+                picks.append(row)
+                table[s, :n] = torch.arange(off, off + n, dtype=torch.int32, device=dev)
+                off += n
+            memo[key] = (torch.cat(picks).long(), dataclasses.replace(self, page_table=table, page_size=target))
+        return memo[key]

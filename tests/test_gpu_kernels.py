@@ -140,11 +140,16 @@ def test_tensor_core_prefill_attention_matches_reference(K, Hq, Hkv, DK, DV, win
         q = torch.randn(sum(q_lens), Hq, DK, device="cuda").bfloat16()
         scale = DK ** -0.5
         want = ref.paged_attention(q, kc, vc, meta, scale, window, 0.0)
-        got = K.paged_attention(q, kc, vc, meta, scale, window, kernel="prefill")
+        got = K.paged_attention(q, kc, vc, meta, scale, window, kernel="prefill")     # regrouped into 64-token pages: one TMA per stage
         torch.cuda.synchronize()
         assert K.last_status() == 0
         assert got.shape == want.shape
         assert _rel(got, want) < 2e-2, (S_lens, q_lens, _rel(got, want))
+        import dataclasses
+        direct = dataclasses.replace(meta, kv_lens_host=None)                           # no host lengths: the 16-token pages are read in place
+        got16 = K.paged_attention(q, kc, vc, direct, scale, window, kernel="prefill")
+        torch.cuda.synchronize()
+        assert K.last_status() == 0 and _rel(got16, want) < 2e-2, (S_lens, q_lens, _rel(got16, want))
 
 
 def test_qk_norm_rope_append_matches_reference(K):
@@ -222,26 +227,28 @@ def test_short_conv(K):
 
 @pytest.mark.parametrize("Hq", [64, 8, 16])
 def test_mla_latent_attention_tensor_core(K, Hq):
-    """tcgen05 MLA kernel against the fp32 reference: decode with speculative rows, chunked prefill, kv splits."""
+    """tcgen05 MLA kernel against the fp32 reference: decode with speculative rows, chunked prefill, kv splits; 16-token pages
+    (one TMA operation per page and chunk) and 32-token pages (one 4-D TMA operation per 32-key stage)."""
     from mary_b200.runtime.batch import BatchMeta
     from mary_b200.runtime.kv_cache import PagedKVCache
     torch.manual_seed(Hq)
-    for S_lens, q_lens in (([300, 17, 1000, 64], [3, 1, 3, 2]), ([40, 90], [40, 7]), ([4096 + 3], [3])):
-        pages = sum((l + 15) // 16 for l in S_lens) + 3
-        cache = PagedKVCache(1, pages, 16, 1, 1, dtype=torch.bfloat16, device="cuda", latent_dim=576)
-        for rnd in range(max((l + 15) // 16 for l in S_lens)):
-            for s, l in enumerate(S_lens):
-                if rnd * 16 < l:
-                    cache.alloc.extend(s, min(16, l - rnd * 16))
-        table, lens = cache.alloc.page_table(list(range(len(S_lens))))
-        meta = BatchMeta.build(q_lens, lens, table, 16, "cuda")
-        cache.k[0].normal_()
-        q = (torch.randn(sum(q_lens), Hq, 576, device="cuda") * 0.5).bfloat16()
-        want = ref.paged_attention(q, cache.k[0], cache.k[0], meta, 576 ** -0.5, dv=512)
-        for nsplit in (1, None, 3):
-            got = K.mla_attention(q, cache.k[0], meta, 576 ** -0.5, nsplit=nsplit)
-            assert K.last_status() == 0
-            assert _rel(got, want) < 2e-2, (S_lens, nsplit, _rel(got, want))
+    for ps in (16, 32):
+        for S_lens, q_lens in (([300, 17, 1000, 64], [3, 1, 3, 2]), ([40, 90], [40, 7]), ([4096 + 3], [3])):
+            pages = sum((l + ps - 1) // ps for l in S_lens) + 3
+            cache = PagedKVCache(1, pages, ps, 1, 1, dtype=torch.bfloat16, device="cuda", latent_dim=576)
+            for rnd in range(max((l + ps - 1) // ps for l in S_lens)):
+                for s, l in enumerate(S_lens):
+                    if rnd * ps < l:
+                        cache.alloc.extend(s, min(ps, l - rnd * ps))
+            table, lens = cache.alloc.page_table(list(range(len(S_lens))))
+            meta = BatchMeta.build(q_lens, lens, table, ps, "cuda")
+            cache.k[0].normal_()
+            q = (torch.randn(sum(q_lens), Hq, 576, device="cuda") * 0.5).bfloat16()
+            want = ref.paged_attention(q, cache.k[0], cache.k[0], meta, 576 ** -0.5, dv=512)
+            for nsplit in (1, None, 3):
+                got = K.mla_attention(q, cache.k[0], meta, 576 ** -0.5, nsplit=nsplit)
+                assert K.last_status() == 0
+                assert _rel(got, want) < 2e-2, (ps, S_lens, nsplit, _rel(got, want))
 
 
 def test_codec_cuda_arm_matches_cpu_oracle(K):
