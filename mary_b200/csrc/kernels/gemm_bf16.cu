@@ -28,7 +28,7 @@ constexpr int BK = 64;       // K per stage: 64 bf16 = 128 bytes = one swizzle r
 constexpr int UMMA_K = 16;
 constexpr int NTHREADS = 192;
 
-enum { EPI_STORE_BF16 = 0, EPI_RED_F32 = 1, EPI_STORE_F32 = 2, EPI_RS_BF16 = 3 };
+enum { EPI_STORE_BF16 = 0, EPI_RED_F32 = 1, EPI_STORE_F32 = 2, EPI_RS_BF16 = 3, EPI_SK_BF16 = 4, EPI_SK_F32 = 5 };
 
 struct GemmParams {
   int rows_r, rows_c;        // extents of the row operand and the column operand (tiles are clipped to them)
@@ -49,6 +49,10 @@ struct GemmParams {
   const float* bias;         // optional, indexed by output feature
   float alpha;
   int* status;
+  // split-K without atomics (EPI_SK_*): every split stores its f32 partial tile in `ws`, bumps the tile's counter, and the split
+  // that arrives last sums the partials in split order and stores the finished tile; the counter goes back to zero.
+  float* ws;
+  int* counters;
 };
 
 __device__ __forceinline__ __nv_bfloat16* rs_row(const GemmParams& p, int token_row) {
@@ -89,6 +93,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
   uint64_t* acc_empty = acc_full + 2;         // [2]
   uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* sk_last = abort_flag + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -177,18 +182,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       tc_fence_after();
       const int i = tr * BM + q * 32 + lane;              // row-operand index of this thread
       const uint32_t taddr = tmem_base + buf * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32], r2[32];
-        tmem_ld_32x32b_x32(taddr + c0, r);
-        if (GLU) tmem_ld_32x32b_x32(taddr + BN + c0, r2);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float a = __uint_as_float(r[j]) * p.alpha;
-          v[j] = GLU ? glu_f(p.act, a, __uint_as_float(r2[j]) * p.alpha) : a;
-        }
+      const bool sk = p.epi == EPI_SK_BF16 || p.epi == EPI_SK_F32;
+      const int ks = (t / p.tiles_c) % p.split_k;
+      const int tile = (bz * p.tiles_r + tr) * p.tiles_c + tc;
+      float* slot = sk ? p.ws + ((int64_t)tile * p.split_k + ks) * (BM * BN) : nullptr;
+      // stores 32 finished values of this thread's row (columns tc * BN + c0 ..) in the requested form
+      auto emit = [&](int c0, const float* v, int epi) {
         const int j0 = tc * BN + c0;
         if (p.swap) {
           // i = output feature, j = token: out[j * ldo + i]; a warp writes 32 consecutive features per token
@@ -198,9 +197,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
             for (int j = 0; j < 32; ++j) {
               if (j0 + j < p.rows_c) {
                 const int64_t o = obase + (int64_t)(j0 + j) * p.ldo + i;
-                if (p.epi == EPI_RS_BF16) rs_row(p, j0 + j)[i] = __float2bfloat16(v[j] + b);
-                else if (p.epi == EPI_STORE_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16(v[j] + b);
-                else if (p.epi == EPI_STORE_F32) ((float*)p.out)[o] = v[j] + b;
+                if (epi == EPI_RS_BF16) rs_row(p, j0 + j)[i] = __float2bfloat16(v[j] + b);
+                else if (epi == EPI_STORE_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16(v[j] + b);
+                else if (epi == EPI_STORE_F32) ((float*)p.out)[o] = v[j] + b;
                 else atomicAdd((float*)p.out + o, v[j]);
               }
             }
@@ -209,8 +208,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
           // i = token, j = output feature: out[i * ldo + j]; each thread writes 32 consecutive features
           if (i < p.rows_r) {
             const int64_t o = obase + (int64_t)i * p.ldo + j0;
-            if (p.epi == EPI_STORE_BF16 || p.epi == EPI_RS_BF16) {
-              __nv_bfloat16* dst = p.epi == EPI_RS_BF16 ? rs_row(p, i) + j0 : (__nv_bfloat16*)p.out + o;
+            if (epi == EPI_STORE_BF16 || epi == EPI_RS_BF16) {
+              __nv_bfloat16* dst = epi == EPI_RS_BF16 ? rs_row(p, i) + j0 : (__nv_bfloat16*)p.out + o;
               if (j0 + 32 <= p.rows_c && ((uintptr_t)dst & 15) == 0) {
                 uint4 w[4];
                 uint32_t* wp = (uint32_t*)w;
@@ -226,7 +225,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
                 for (int j = 0; j < 32; ++j)
                   if (j0 + j < p.rows_c) dst[j] = __float2bfloat16(v[j] + (p.bias ? p.bias[j0 + j] : 0.f));
               }
-            } else if (p.epi == EPI_STORE_F32) {
+            } else if (epi == EPI_STORE_F32) {
               for (int j = 0; j < 32; ++j)
                 if (j0 + j < p.rows_c) ((float*)p.out)[o + j] = v[j] + (p.bias ? p.bias[j0 + j] : 0.f);
             } else {
@@ -235,10 +234,54 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
             }
           }
         }
+      };
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32], r2[32];
+        tmem_ld_32x32b_x32(taddr + c0, r);
+        if (GLU) tmem_ld_32x32b_x32(taddr + BN + c0, r2);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float a = __uint_as_float(r[j]) * p.alpha;
+          v[j] = GLU ? glu_f(p.act, a, __uint_as_float(r2[j]) * p.alpha) : a;
+        }
+        if (sk) {
+          // partial tile, column-major so that a warp's 32 rows are contiguous: slot[(c0 + j) * BM + row]
+#pragma unroll
+          for (int j = 0; j < 32; ++j) __stcg(slot + (c0 + j) * BM + q * 32 + lane, v[j]);
+        } else {
+          emit(c0, v, p.epi);
+        }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (sk) {
+        // publish the partials, count this split in; the split that arrives last owns the tile
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) *sk_last = (atomicAdd(p.counters + tile, 1) == p.split_k - 1) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*sk_last) {
+          __threadfence();
+          const float* base = p.ws + (int64_t)tile * p.split_k * (BM * BN);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.f;
+            for (int s2 = 0; s2 < p.split_k; ++s2) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += __ldcg(base + (int64_t)s2 * (BM * BN) + (c0 + j) * BM + q * 32 + lane);
+            }
+            emit(c0, v, p.epi == EPI_SK_BF16 ? EPI_STORE_BF16 : EPI_STORE_F32);
+          }
+          if (threadIdx.x == 64) p.counters[tile] = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // sk_last is rewritten by the next work item
+      }
     }
   }
 done:
@@ -289,7 +332,8 @@ static int make_tmap_3d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
 // Batched form: `batch` independent problems; operand b starts at base + b * batch_stride (elements).
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
-                     const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream);
+                     const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream, float* ws = nullptr,
+                     int64_t ws_floats = 0, int* counters = nullptr, int n_counters = 0);
 
 MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
                                     int64_t ldo, int batch, int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha,
@@ -310,10 +354,13 @@ MARY_API int mary_gemm_bf16_rs(const void* X, const void* W, int M, int N, int K
 
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
-                     const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream) {
+                     const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream, float* ws, int64_t ws_floats,
+                     int* counters, int n_counters) {
   if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || batch < 1) return MARY_ERR_BAD_ARG;
   if (split_k < 1) split_k = 1;
-  if (split_k > 1 && epi != EPI_RED_F32) return MARY_ERR_BAD_ARG;
+  const bool sk_epi = epi == EPI_SK_BF16 || epi == EPI_SK_F32;
+  if (split_k > 1 && epi != EPI_RED_F32 && !sk_epi) return MARY_ERR_BAD_ARG;
+  if (sk_epi && (glu || !ws || !counters)) return MARY_ERR_BAD_ARG;
   if (glu && epi == EPI_RED_F32) return MARY_ERR_BAD_ARG;
   const bool use_swap = glu ? true : (swap < 0 ? (M <= 256) : swap != 0);
   // GLU without swap would need the weight operand on the column side; for large M the host falls back to
@@ -355,6 +402,12 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
     while (bn > 64 && (int64_t)p.tiles_r * ((p.rows_c + bn - 1) / bn) * split_k * batch < sms) bn >>= 1;
   }
   p.tiles_c = (p.rows_c + bn - 1) / bn;
+  p.ws = ws;
+  p.counters = counters;
+  if (sk_epi) {
+    const int64_t tiles = (int64_t)p.tiles_r * p.tiles_c * batch;
+    if (tiles > n_counters || tiles * p.split_k * BM * bn > ws_floats) return MARY_ERR_BAD_ARG;     // workspace too small
+  }
   CUtensorMap tr, tc;
   int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, batch, bsr, BM);
   if (rc) return rc;
@@ -379,4 +432,15 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
                             int64_t ldo, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
                             cudaStream_t stream) {
   return mary_gemm_bf16_batched(X, W, out, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, bias, alpha, glu, epi, split_k, swap, stream);
+}
+
+// Split-K without atomics, memset or a cast pass: out (bf16, or f32 when out_f32) = alpha * X W^T + bias with K cut into
+// split_k slices that run as separate tiles.  `ws` (ws_floats f32) holds the partial tiles and `counters` (n_counters ints, zero
+// before the first call; the kernel leaves them zero) one arrival count per output tile; both are scratch that calls on one
+// stream may share.  Returns MARY_ERR_BAD_ARG when the scratch is too small for this shape.
+MARY_API int mary_gemm_bf16_splitk(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo,
+                                   const float* bias, float alpha, int out_f32, int split_k, int swap, float* ws, int64_t ws_floats,
+                                   int* counters, int n_counters, cudaStream_t stream) {
+  return gemm_impl(X, W, out, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, bias, alpha, 0, out_f32 ? EPI_SK_F32 : EPI_SK_BF16, split_k, swap,
+                   nullptr, 0, 0, 0, stream, ws, ws_floats, counters, n_counters);
 }

@@ -55,8 +55,8 @@ def bench_gemm(shapes=None):
         w = (torch.randn(N, Kd, device="cuda") * 0.02).bfloat16()
         sk = K._auto_split_k(M, N, Kd)
         if sk > 1:
-            out = torch.zeros(M, N, dtype=torch.float32, device="cuda")
-            ours = time_op(lambda: K.gemm(x, w, out=out, epi="red", split_k=sk))
+            out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            ours = time_op(lambda: K.gemm_splitk(x, w, sk, out=out))
         else:
             out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
             ours = time_op(lambda: K.gemm(x, w, out=out))

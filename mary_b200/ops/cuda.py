@@ -135,6 +135,42 @@ def _auto_split_k(M: int, N: int, K: int) -> int:
     return max(1, min(K // 512, (148 + tiles - 1) // tiles))
 
 
+declare("mary_gemm_bf16_splitk", "pppiiilllpfiiiplpis")
+_SK_WS: dict = {}
+SK_WS_FLOATS = 8 << 20          # 32 MiB of partial tiles
+SK_COUNTERS = 8192
+
+
+def _sk_workspace(dev):
+    """Scratch of the atomics-free split-K GEMM (partial tiles + per-tile arrival counters), one per device; calls on one
+    stream share it.  Created on first use — before any stream capture, since warm-up steps run eagerly first."""
+    key = dev.index if dev.index is not None else torch.cuda.current_device()
+    if key not in _SK_WS:
+        _SK_WS[key] = (torch.empty(SK_WS_FLOATS, dtype=torch.float32, device=dev), torch.zeros(SK_COUNTERS, dtype=torch.int32, device=dev))
+    return _SK_WS[key]
+
+
+def gemm_splitk(x, w, split_k: int, out=None, f32: bool = False, bias=None, swap: int = -1):
+    """``x @ w^T`` with K cut into ``split_k`` slices reduced inside the kernel (the slice that finishes last sums the partial
+    tiles): no zero-fill, no atomics, no cast pass.  Falls back to the atomic path when the shape outgrows the scratch."""
+    _bf16(x), _bf16(w)
+    M, K = x.shape
+    N = w.shape[0]
+    ws, cnt = _sk_workspace(x.device)
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+    rc = lib().mary_gemm_bf16_splitk(_p(x), _p(w), _p(out), M, N, K, x.stride(0), w.stride(0), out.stride(0), _p(bias), 1.0, int(f32),
+                                     split_k, swap, _p(ws), ws.numel(), _p(cnt), cnt.numel(), _stream())
+    if rc == 4:                                             # scratch too small for this shape
+        red = gemm(x, w, epi="red", split_k=split_k)
+        if bias is not None:
+            red += bias
+        out.copy_(red)
+        return out
+    check(rc, "gemm_bf16_splitk")
+    return out
+
+
 def linear(x, w, bias=None):
     shp = x.shape
     x2 = x.reshape(-1, shp[-1])
@@ -142,10 +178,7 @@ def linear(x, w, bias=None):
         x2 = x2.contiguous()
     M, K = x2.shape
     sk = _auto_split_k(M, w.shape[0], K)
-    if sk > 1 and bias is None:
-        out = gemm(x2, w, epi="red", split_k=sk).to(torch.bfloat16)
-    else:
-        out = gemm(x2, w, bias=bias)
+    out = gemm_splitk(x2, w, sk, bias=bias) if sk > 1 else gemm(x2, w, bias=bias)
     return out.reshape(*shp[:-1], w.shape[0])
 
 
@@ -153,7 +186,7 @@ def linear_f32(x, w, split_k: int | None = None):
     """Row-parallel style GEMM whose f32 result feeds a norm kernel directly (no bf16 rounding in between)."""
     M, K = x.shape
     sk = split_k or _auto_split_k(M, w.shape[0], K)
-    return gemm(x, w, epi="red", split_k=sk)
+    return gemm_splitk(x, w, sk, f32=True) if sk > 1 else gemm(x, w, epi="f32")
 
 
 def linear_glu(x, w_gu, act: str = "geglu"):

@@ -120,6 +120,28 @@ def test_paged_attention_decode_and_prefill(K, Hq, Hkv, D, window, softcap):
                 assert _rel(got, want) < 2e-2, (kernel, S_lens, nsplit, _rel(got, want))
 
 
+@pytest.mark.parametrize("M,N,K_,sk", [(48, 2112, 7168, 8), (3, 520, 4096, 5), (384, 384, 7168, 16), (130, 1000, 2048, 3), (32, 7168, 8192, 4)])
+def test_gemm_split_k_reduced_by_the_last_slice(K, M, N, K_, sk):
+    """K slices as separate tiles, partial tiles in scratch, the slice that arrives last sums them in slice order: bf16 and
+    f32 outputs, bias, both operand orders, repeated calls (the arrival counters must come back to zero)."""
+    torch.manual_seed(M + N)
+    x = torch.randn(M, K_, device="cuda").bfloat16()
+    w = (torch.randn(N, K_, device="cuda") * 0.05).bfloat16()
+    bias = torch.randn(N, device="cuda")
+    want = x.float() @ w.float().T
+    for rep in range(3):
+        for swap in (0, 1):
+            g = K.gemm_splitk(x, w, sk, swap=swap)
+            assert _rel(g, want) < 1e-2, (swap, _rel(g, want))
+            g32 = K.gemm_splitk(x, w, sk, f32=True, bias=bias, swap=swap)
+            assert _rel(g32, want + bias) < 2e-5 * np.sqrt(K_), (swap, _rel(g32, want + bias))
+    torch.cuda.synchronize()
+    assert int(K._sk_workspace(x.device)[1].abs().sum()) == 0
+    assert K.last_status() == 0
+    # deterministic: the sum order is fixed, so two runs agree bit for bit (unlike the atomic path)
+    assert torch.equal(K.gemm_splitk(x, w, sk, f32=True), K.gemm_splitk(x, w, sk, f32=True))
+
+
 @pytest.mark.parametrize("Hq,Hkv,DK,DV,window", [(4, 2, 64, 64, 0), (8, 2, 128, 128, 0), (4, 4, 128, 128, 96), (4, 2, 256, 256, 0),
                                                   (4, 2, 256, 256, 200), (6, 6, 192, 128, 0)])
 def test_tensor_core_prefill_attention_matches_reference(K, Hq, Hkv, DK, DV, window):
