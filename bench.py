@@ -125,6 +125,8 @@ def main():
     ap.add_argument("--no-ttft", action="store_true")
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill chunk of the TTFT measurement")
     ap.add_argument("--trace", action="store_true", help="print a per-op device-time table of one eager step and exit")
+    ap.add_argument("--profile-step", action="store_true",
+                    help="run one eager step between cudaProfilerStart/Stop and exit (for ncu --profile-from-start off)")
     ap.add_argument("--trace-prefill", action="store_true", help="print a per-op device-time table of one real prefill of one context and exit")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -244,6 +246,18 @@ def main():
             pd.prefill(prompt, chunk=args.prefill_chunk)
         if rank == 0:
             print(tr.report())
+        return
+    if args.profile_step:
+        with torch.no_grad():
+            for _ in range(2):
+                dec._step_device()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+            dec._step_device()
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
+        if world > 1:
+            dist.destroy_process_group()
         return
     if args.trace:
         from mary_b200.utils.trace import Tracer

@@ -94,28 +94,31 @@ def main():
         from mary_b200.parallel.ep import distributed_factory
         from mary_b200.runtime.batch import BatchMeta
         from mary_b200.runtime.kv_cache import PagedKVCache
-        torch.manual_seed(0)
-        cfg = tiny_moe_config("gqa")
-        full = MoEDecoder(cfg, dtype=torch.bfloat16, device=dev)
-        init_random_(full, 0)
-        par = ParallelGroup(rank, world, "nccl", ep_mode="a2a")
-        par.ep_factory = distributed_factory(rank, world, dev, t_cap=64)
-        shard = shard_from_full(full, par)
-        ids = torch.arange(1, 40, dtype=torch.int32, device=dev)
-        outs = []
-        for m in (full, shard):
-            spec = m.kv_spec()
-            cache = PagedKVCache(spec["num_layers"], 16, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16, device=dev)
-            cache.alloc.extend(0, 39)
-            table, lens = cache.alloc.page_table([0])
-            meta = BatchMeta.build([39], lens, table, 16, dev)
-            with torch.no_grad():
-                outs.append(m(ids, meta, cache).float())
-        torch.cuda.synchronize()
-        assert K.last_status() == 0
-        row_err = (outs[0] - outs[1]).abs().amax(-1)
-        scale = outs[0].abs().max().item()
-        assert row_err.median().item() < 0.05 * scale and (row_err < 0.1 * scale).float().mean().item() >= 0.85, (row_err.tolist(), scale)
+        for attention, shared_fp4 in (("gqa", False), ("mla", True)):      # the second keeps its shared expert as one more NVFP4 expert
+            torch.manual_seed(0)
+            cfg = tiny_moe_config(attention, shared_expert_nvfp4=shared_fp4)
+            full = MoEDecoder(cfg, dtype=torch.bfloat16, device=dev)
+            init_random_(full, 0)
+            par = ParallelGroup(rank, world, "nccl", ep_mode="a2a")
+            par.ep_factory = distributed_factory(rank, world, dev, t_cap=64)
+            shard = shard_from_full(full, par)
+            ids = torch.arange(1, 40, dtype=torch.int32, device=dev)
+            outs = []
+            for m in (full, shard):
+                spec = m.kv_spec()
+                cache = PagedKVCache(spec["num_layers"], 16, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16, device=dev,
+                                     latent_dim=spec.get("latent_dim"))
+                cache.alloc.extend(0, 39)
+                table, lens = cache.alloc.page_table([0])
+                meta = BatchMeta.build([39], lens, table, 16, dev)
+                with torch.no_grad():
+                    outs.append(m(ids, meta, cache).float())
+            torch.cuda.synchronize()
+            assert K.last_status() == 0
+            row_err = (outs[0] - outs[1]).abs().amax(-1)
+            scale = outs[0].abs().max().item()
+            assert row_err.median().item() < 0.05 * scale and (row_err < 0.1 * scale).float().mean().item() >= 0.85, \
+                (attention, row_err.tolist(), scale)
         dist.barrier()
         if rank == 0:
             print("A2A_OK")
