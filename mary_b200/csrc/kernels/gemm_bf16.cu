@@ -53,6 +53,57 @@ struct GemmParams {
   // that arrives last sums the partials in split order and stores the finished tile; the counter goes back to zero.
   float* ws;
   int* counters;
+  // stream-K (sk_units > 0, batch 1): the tiles_r * tiles_c * k_blocks K-blocks are dealt out in equal contiguous runs of
+  // sk_units blocks per CTA, so every CTA streams the same number of weight bytes whatever the tile count; a tile whose
+  // blocks fall to several CTAs is finished by whichever of them arrives last.
+  int sk_units;
+};
+
+// One unit of work of a CTA: K-blocks [kb0, kb1) of output tile (tr, tc) of problem bz; `seg` of `nseg` partial results of that
+// tile, stored in scratch slot `slot`.
+struct WorkItem { int bz, tr, tc, tile, kb0, kb1, seg, nseg, slot; };
+
+struct WorkIter {
+  const GemmParams& p;
+  int tt, unit, end;
+  __device__ WorkIter(const GemmParams& p_) : p(p_) {
+    tt = blockIdx.x;
+    unit = blockIdx.x * p.sk_units;
+    end = min(unit + p.sk_units, p.tiles_r * p.tiles_c * p.k_blocks);
+  }
+  __device__ bool next(WorkItem& w) {
+    if (p.sk_units > 0) {
+      if (unit >= end) return false;
+      const int kb = p.k_blocks, u = p.sk_units;
+      w.tile = unit / kb;
+      w.kb0 = unit - w.tile * kb;
+      w.kb1 = min(kb, w.kb0 + (end - unit));
+      w.bz = 0;
+      w.tc = w.tile % p.tiles_c;
+      w.tr = w.tile / p.tiles_c;
+      const int first = (w.tile * kb) / u, last = ((w.tile + 1) * kb - 1) / u;
+      w.seg = (int)blockIdx.x - first;
+      w.nseg = last - first + 1;
+      w.slot = first + w.tile + w.seg;
+      unit += w.kb1 - w.kb0;
+      return true;
+    }
+    const int per_batch = p.tiles_r * p.tiles_c * p.split_k;
+    if (tt >= per_batch * p.batch) return false;
+    const int t = tt % per_batch;
+    w.bz = tt / per_batch;
+    w.tc = t % p.tiles_c;
+    const int ks = (t / p.tiles_c) % p.split_k;
+    w.tr = t / (p.tiles_c * p.split_k);
+    w.kb0 = ks * p.k_blocks_per_split;
+    w.kb1 = min(w.kb0 + p.k_blocks_per_split, p.k_blocks);
+    w.tile = (w.bz * p.tiles_r + w.tr) * p.tiles_c + w.tc;
+    w.seg = ks;
+    w.nseg = p.split_k;
+    w.slot = w.tile * p.split_k + ks;
+    tt += gridDim.x;
+    return true;
+  }
 };
 
 __device__ __forceinline__ __nv_bfloat16* rs_row(const GemmParams& p, int token_row) {
@@ -111,19 +162,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int per_batch = p.tiles_r * p.tiles_c * p.split_k;
-  const int total_tiles = per_batch * p.batch;
-
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       int stage = 0; uint32_t phase = 0;
-      for (int tt = blockIdx.x; tt < total_tiles; tt += gridDim.x) {
-        const int bz = tt / per_batch, t = tt % per_batch;
-        const int tc = t % p.tiles_c, ks = (t / p.tiles_c) % p.split_k, tr = t / (p.tiles_c * p.split_k);
-        const int kb0 = ks * p.k_blocks_per_split;
-        const int kb1 = min(kb0 + p.k_blocks_per_split, p.k_blocks);
-        for (int kb = kb0; kb < kb1; ++kb) {
+      WorkIter iter(p);
+      WorkItem w;
+      while (iter.next(w)) {
+        const int bz = w.bz, tr = w.tr, tc = w.tc;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
           uint8_t* st = smem + stage * C::STAGE_BYTES;
           mbar_expect_tx(&full[stage], C::STAGE_BYTES);
@@ -140,11 +187,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       const uint32_t idesc = idesc_bf16(BM, BN);
       int stage = 0; uint32_t phase = 0;
       int it = 0;
-      for (int tt = blockIdx.x; tt < total_tiles; tt += gridDim.x, ++it) {
-        const int t = tt % per_batch;
-        const int ks = (t / p.tiles_c) % p.split_k;
-        const int kb0 = ks * p.k_blocks_per_split;
-        const int kb1 = min(kb0 + p.k_blocks_per_split, p.k_blocks);
+      WorkIter iter(p);
+      WorkItem w;
+      for (; iter.next(w); ++it) {
+        const int kb0 = w.kb0, kb1 = w.kb1;
         const int buf = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&acc_empty[buf], acc_phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
@@ -172,9 +218,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;                // TMEM lane quarter this warp may access
     int it = 0;
-    for (int tt = blockIdx.x; tt < total_tiles; tt += gridDim.x, ++it) {
-      const int bz = tt / per_batch, t = tt % per_batch;
-      const int tc = t % p.tiles_c, tr = t / (p.tiles_c * p.split_k);
+    WorkIter iter(p);
+    WorkItem w;
+    for (; iter.next(w); ++it) {
+      const int bz = w.bz, tc = w.tc, tr = w.tr;
       const int64_t obase = (int64_t)bz * p.out_batch_stride;
       const int buf = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -182,10 +229,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       tc_fence_after();
       const int i = tr * BM + q * 32 + lane;              // row-operand index of this thread
       const uint32_t taddr = tmem_base + buf * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
-      const bool sk = p.epi == EPI_SK_BF16 || p.epi == EPI_SK_F32;
-      const int ks = (t / p.tiles_c) % p.split_k;
-      const int tile = (bz * p.tiles_r + tr) * p.tiles_c + tc;
-      float* slot = sk ? p.ws + ((int64_t)tile * p.split_k + ks) * (BM * BN) : nullptr;
+      const bool sk_epi = p.epi == EPI_SK_BF16 || p.epi == EPI_SK_F32;
+      const int final_epi = p.epi == EPI_SK_BF16 ? EPI_STORE_BF16 : (p.epi == EPI_SK_F32 ? EPI_STORE_F32 : p.epi);
+      const bool sk = sk_epi && w.nseg > 1;             // a tile computed by one CTA alone is stored directly
+      const int tile = w.tile;
+      float* slot = sk ? p.ws + (int64_t)w.slot * (BM * BN) : nullptr;
       // stores 32 finished values of this thread's row (columns tc * BN + c0 ..) in the requested form
       auto emit = [&](int c0, const float* v, int epi) {
         const int j0 = tc * BN + c0;
@@ -252,7 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 32; ++j) __stcg(slot + (c0 + j) * BM + q * 32 + lane, v[j]);
         } else {
-          emit(c0, v, p.epi);
+          emit(c0, v, final_epi);
         }
       }
       tc_fence_before();
@@ -262,21 +310,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
         // publish the partials, count this split in; the split that arrives last owns the tile
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64) *sk_last = (atomicAdd(p.counters + tile, 1) == p.split_k - 1) ? 1 : 0;
+        if (threadIdx.x == 64) *sk_last = (atomicAdd(p.counters + tile, 1) == w.nseg - 1) ? 1 : 0;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*sk_last) {
           __threadfence();
-          const float* base = p.ws + (int64_t)tile * p.split_k * (BM * BN);
+          const float* base = p.ws + (int64_t)(w.slot - w.seg) * (BM * BN);
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 32) {
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = 0.f;
-            for (int s2 = 0; s2 < p.split_k; ++s2) {
+            for (int s2 = 0; s2 < w.nseg; ++s2) {
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] += __ldcg(base + (int64_t)s2 * (BM * BN) + (c0 + j) * BM + q * 32 + lane);
             }
-            emit(c0, v, p.epi == EPI_SK_BF16 ? EPI_STORE_BF16 : EPI_STORE_F32);
+            emit(c0, v, final_epi);
           }
           if (threadIdx.x == 64) p.counters[tile] = 0;
         }
@@ -301,6 +349,7 @@ int launch(const CUtensorMap& tr, const CUtensorMap& tc, const GemmParams& p, cu
   }
   int total = p.tiles_r * p.tiles_c * p.split_k * p.batch;
   int grid = total < mary_num_sms() ? total : mary_num_sms();
+  if (p.sk_units > 0) grid = (p.tiles_r * p.tiles_c * p.k_blocks + p.sk_units - 1) / p.sk_units;
   gemm_bf16_kernel<BN, GLU><<<grid, NTHREADS, C::SMEM, stream>>>(tr, tc, p);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
@@ -333,7 +382,7 @@ static int make_tmap_3d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
                      const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream, float* ws = nullptr,
-                     int64_t ws_floats = 0, int* counters = nullptr, int n_counters = 0);
+                     int64_t ws_floats = 0, int* counters = nullptr, int n_counters = 0, bool stream_k = false);
 
 MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
                                     int64_t ldo, int batch, int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha,
@@ -355,7 +404,7 @@ MARY_API int mary_gemm_bf16_rs(const void* X, const void* W, int M, int N, int K
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
                      const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream, float* ws, int64_t ws_floats,
-                     int* counters, int n_counters) {
+                     int* counters, int n_counters, bool stream_k) {
   if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || batch < 1) return MARY_ERR_BAD_ARG;
   if (split_k < 1) split_k = 1;
   const bool sk_epi = epi == EPI_SK_BF16 || epi == EPI_SK_F32;
@@ -404,9 +453,20 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   p.tiles_c = (p.rows_c + bn - 1) / bn;
   p.ws = ws;
   p.counters = counters;
+  p.sk_units = 0;
   if (sk_epi) {
     const int64_t tiles = (int64_t)p.tiles_r * p.tiles_c * batch;
-    if (tiles > n_counters || tiles * p.split_k * BM * bn > ws_floats) return MARY_ERR_BAD_ARG;     // workspace too small
+    int64_t slots = tiles * p.split_k;
+    if (stream_k && batch == 1) {
+      // equal runs of K-blocks per CTA; at least 4 blocks each so that the partial-tile traffic stays small beside the weights
+      const int64_t units = tiles * p.k_blocks;
+      int64_t g = mary_num_sms();
+      if (g > units / 4) g = units / 4 > 0 ? units / 4 : 1;
+      p.sk_units = (int)((units + g - 1) / g);
+      p.split_k = 1;
+      slots = (units + p.sk_units - 1) / p.sk_units + tiles;
+    }
+    if (tiles > n_counters || slots * BM * bn > ws_floats) return MARY_ERR_BAD_ARG;     // workspace too small
   }
   CUtensorMap tr, tc;
   int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, batch, bsr, BM);
@@ -441,6 +501,7 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
 MARY_API int mary_gemm_bf16_splitk(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo,
                                    const float* bias, float alpha, int out_f32, int split_k, int swap, float* ws, int64_t ws_floats,
                                    int* counters, int n_counters, cudaStream_t stream) {
-  return gemm_impl(X, W, out, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, bias, alpha, 0, out_f32 ? EPI_SK_F32 : EPI_SK_BF16, split_k, swap,
-                   nullptr, 0, 0, 0, stream, ws, ws_floats, counters, n_counters);
+  // split_k == 0: stream-K (equal runs of K-blocks per CTA)
+  return gemm_impl(X, W, out, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, bias, alpha, 0, out_f32 ? EPI_SK_F32 : EPI_SK_BF16,
+                   split_k == 0 ? 1 : split_k, swap, nullptr, 0, 0, 0, stream, ws, ws_floats, counters, n_counters, split_k == 0);
 }

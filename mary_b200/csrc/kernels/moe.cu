@@ -41,12 +41,37 @@ __global__ void moe_plan_kernel(const int* __restrict__ idx, int n_entries, int 
     if (i < n_entries) row_of[i] = slot;       // provisional: slot inside the expert
     __syncthreads();
   }
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int e = 0; e < E; ++e) { off[e] = acc; acc += (cnt[e] + NT - 1) / NT * NT; }
-    off[E] = acc;
-    meta[0] = acc / NT;
-    meta[1] = acc;
+  // exclusive prefix sum of the padded counts as a block scan (warp shuffles + one pass over the warp totals)
+  {
+    __shared__ int warp_tot[33];
+    __shared__ int carry_s;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int base = 0; base < E; base += blockDim.x) {
+      const int e = base + threadIdx.x;
+      const int padded = e < E ? (cnt[e] + NT - 1) / NT * NT : 0;
+      int incl = padded;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+      if (lane == 31) warp_tot[wid] = incl;
+      __syncthreads();
+      if (wid == 0) {
+        const int wt = lane < nw ? warp_tot[lane] : 0;
+        int wi = wt;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int v = __shfl_up_sync(0xffffffffu, wi, o); if (lane >= o) wi += v; }
+        __syncwarp();
+        warp_tot[lane] = wi - wt;                      // exclusive offset of warp `lane`
+        if (lane == 31) warp_tot[32] = wi;             // total of this pass
+      }
+      __syncthreads();
+      if (e < E) off[e] = carry_s + warp_tot[wid] + incl - padded;
+      __syncthreads();
+      if (threadIdx.x == 0) carry_s += warp_tot[32];
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) { off[E] = carry_s; meta[0] = carry_s / NT; meta[1] = carry_s; }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -113,12 +138,13 @@ __global__ void quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, int
   }
 }
 
-// out[t, :] = sum_j w[t, j] * y[row_of[t*k + j], :]  (+ add[t, :]) in ascending j with fma; one CTA per token.
+// out[t, :] = sum_j w[t, j] * y[row_of[t*k + j], :]  (+ add[t, :]) in ascending j with fma; grid (token, column slab): a
+// decode batch has few tokens, so the hidden dimension is spread over gridDim.y CTAs to fill the machine.
 __global__ void moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, int64_t ldy, const int* __restrict__ row_of,
                                      const float* __restrict__ w, int k, int H, const __nv_bfloat16* __restrict__ add,
                                      __nv_bfloat16* __restrict__ out) {
   const int t = blockIdx.x;
-  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < H; c += gridDim.y * blockDim.x * 8) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
@@ -176,7 +202,9 @@ MARY_API int mary_moe_unpermute(const void* y, int64_t ldy, const int* row_of, c
                                 void* out, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   if (H % 8) return MARY_ERR_BAD_ARG;
-  moe_unpermute_kernel<<<T, 256, 0, s>>>((const __nv_bfloat16*)y, ldy, row_of, w, k, H, (const __nv_bfloat16*)add, (__nv_bfloat16*)out);
+  const int slabs = (H / 8 + 127) / 128;       // 128 threads x 8 columns per CTA
+  moe_unpermute_kernel<<<dim3(T, slabs), 128, 0, s>>>((const __nv_bfloat16*)y, ldy, row_of, w, k, H, (const __nv_bfloat16*)add,
+                                                     (__nv_bfloat16*)out);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

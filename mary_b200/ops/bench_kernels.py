@@ -56,7 +56,7 @@ def bench_gemm(shapes=None):
         sk = K._auto_split_k(M, N, Kd)
         if sk > 1:
             out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-            ours = time_op(lambda: K.gemm_splitk(x, w, sk, out=out))
+            ours = time_op(lambda: K.gemm_splitk(x, w, 0, out=out))
         else:
             out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
             ours = time_op(lambda: K.gemm(x, w, out=out))
@@ -64,7 +64,7 @@ def bench_gemm(shapes=None):
         fl = 2.0 * M * N * Kd / ours / 1e9
         gb = (M * Kd + N * Kd + M * N) * 2 / ours / 1e6
         frac = max(fl / tf, gb / hbm)
-        print(f"{M:>6} {N:>6} {Kd:>6} {ours:>9.4f} {th:>9.4f} {fl:>8.1f} {gb:>7.0f}  {frac:.2f} (split_k={sk})")
+        print(f"{M:>6} {N:>6} {Kd:>6} {ours:>9.4f} {th:>9.4f} {fl:>8.1f} {gb:>7.0f}  {frac:.2f} ({"stream-K" if sk > 1 else "whole tiles"})")
     assert K.last_status() == 0
 
 

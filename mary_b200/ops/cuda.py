@@ -152,7 +152,9 @@ def _sk_workspace(dev):
 
 def gemm_splitk(x, w, split_k: int, out=None, f32: bool = False, bias=None, swap: int = -1):
     """``x @ w^T`` with K cut into ``split_k`` slices reduced inside the kernel (the slice that finishes last sums the partial
-    tiles): no zero-fill, no atomics, no cast pass.  Falls back to the atomic path when the shape outgrows the scratch."""
+    tiles): no zero-fill, no atomics, no cast pass.  ``split_k=0`` is stream-K: the K-blocks of all tiles are dealt out in
+    equal contiguous runs, one per SM, so every SM streams the same share of the weights whatever the tile count.  Falls back
+    to the atomic path when the shape outgrows the scratch."""
     _bf16(x), _bf16(w)
     M, K = x.shape
     N = w.shape[0]
@@ -162,7 +164,7 @@ def gemm_splitk(x, w, split_k: int, out=None, f32: bool = False, bias=None, swap
     rc = lib().mary_gemm_bf16_splitk(_p(x), _p(w), _p(out), M, N, K, x.stride(0), w.stride(0), out.stride(0), _p(bias), 1.0, int(f32),
                                      split_k, swap, _p(ws), ws.numel(), _p(cnt), cnt.numel(), _stream())
     if rc == 4:                                             # scratch too small for this shape
-        red = gemm(x, w, epi="red", split_k=split_k)
+        red = gemm(x, w, epi="red", split_k=split_k or _auto_split_k(M, N, K))
         if bias is not None:
             red += bias
         out.copy_(red)
@@ -178,7 +180,7 @@ def linear(x, w, bias=None):
         x2 = x2.contiguous()
     M, K = x2.shape
     sk = _auto_split_k(M, w.shape[0], K)
-    out = gemm_splitk(x2, w, sk, bias=bias) if sk > 1 else gemm(x2, w, bias=bias)
+    out = gemm_splitk(x2, w, 0, bias=bias) if sk > 1 else gemm(x2, w, bias=bias)
     return out.reshape(*shp[:-1], w.shape[0])
 
 
@@ -186,7 +188,7 @@ def linear_f32(x, w, split_k: int | None = None):
     """Row-parallel style GEMM whose f32 result feeds a norm kernel directly (no bf16 rounding in between)."""
     M, K = x.shape
     sk = split_k or _auto_split_k(M, w.shape[0], K)
-    return gemm_splitk(x, w, sk, f32=True) if sk > 1 else gemm(x, w, epi="f32")
+    return gemm_splitk(x, w, 0 if split_k is None else sk, f32=True) if sk > 1 else gemm(x, w, epi="f32")
 
 
 def linear_glu(x, w_gu, act: str = "geglu"):

@@ -13,14 +13,15 @@ declare("mary_gemm_nvfp4_grouped", "pppppppp" + "liiilii" + "s")
 
 
 def quantize_rows(x, nt: int = 128, src_of=None, identity: bool = True, rows: int | None = None, rowmajor: bool = False,
-                  n_rows=None):
+                  n_rows=None, zero_sf: bool = True):
     """NVFP4-quantise rows of ``x`` (bf16).  Returns ``(codes[rows, K/2], sf_blocks[ceil(rows/nt), K/64, 512], rowmajor|None)``.
-    With ``src_of`` (int32 per destination row) rows are gathered (``identity=False``) or merely validated."""
+    With ``src_of`` (int32 per destination row) rows are gathered (``identity=False``) or merely validated.  ``zero_sf=False``
+    leaves the scale bytes of skipped (padding) rows unwritten: their products stay inside those rows, which nothing reads."""
     K = x.shape[1]
     rows = rows if rows is not None else x.shape[0]
     tiles = (rows + nt - 1) // nt
     xq = torch.empty(rows, K // 2, dtype=torch.uint8, device=x.device)
-    sf = torch.zeros(tiles, K // 64, 512, dtype=torch.uint8, device=x.device)
+    sf = (torch.zeros if zero_sf else torch.empty)(tiles, K // 64, 512, dtype=torch.uint8, device=x.device)
     rm = torch.empty(rows, K // 16, dtype=torch.uint8, device=x.device) if rowmajor else None
     check(lib().mary_quant_nvfp4_rows(_p(x), x.stride(0), _p(src_of), int(identity), rows, K, nt, _p(xq), _p(sf), _p(rm),
                                       _p(n_rows), _stream()), "quant_nvfp4_rows")
@@ -74,8 +75,8 @@ def experts_forward(x, idx, w, ex, shared=None, nt: int | None = None):
     if nt is None:
         nt = 32 if T * k <= 32 * ex.E else 128
     plan = moe_plan(idx, ex.E, nt)
-    xq, sfx, _ = quantize_rows(x, nt, plan.src_of, identity=False, rows=plan.max_rows)
+    xq, sfx, _ = quantize_rows(x, nt, plan.src_of, identity=False, rows=plan.max_rows, zero_sf=False)
     h = grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
-    hq, sfh, _ = quantize_rows(h, nt, plan.src_of, identity=True, rows=plan.max_rows)
+    hq, sfh, _ = quantize_rows(h, nt, plan.src_of, identity=True, rows=plan.max_rows, zero_sf=False)
     y = grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, ex.H, ex.F, ex.E, None)
     return unpermute(y, plan, w, T, k, shared)

@@ -96,7 +96,7 @@ class EPLayer:
         xq = b.xq.view(b.cap_rows, b.H // 2)
         sfx = b.sf.view(b.cap_rows // b.nt, b.H // 64, 512)
         h = cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
-        hq, sfh, _ = cuda_moe.quantize_rows(h, b.nt, None, identity=True, rows=b.cap_rows, n_rows=self.plan_meta[1:2])
+        hq, sfh, _ = cuda_moe.quantize_rows(h, b.nt, None, identity=True, rows=b.cap_rows, n_rows=self.plan_meta[1:2], zero_sf=False)
         check(lib().mary_ep_return_ptrs(_p(b.meta), _p(self.plan_meta), _p(self.tiles), b.cap_rows // b.nt, b.nt, b.entry_stride, b.H,
                                         self.world, self.p_comb, _p(self.row_ptrs), _stream()), "ep_return_ptrs")
         check(lib().mary_gemm_nvfp4_grouped_ex(_p(ex.w2_q), _p(ex.w2_sf), _p(ex.w2_s2), _p(hq), _p(sfh), _p(self.tiles), _p(self.plan_meta),

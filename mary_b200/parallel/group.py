@@ -53,7 +53,7 @@ class ParallelGroup:
             out = self.symm.input_view((M, N))
             sk = K._auto_split_k(M, N, Kd)
             if sk > 1:
-                K.gemm_splitk(x.contiguous(), w, sk, out=out)
+                K.gemm_splitk(x.contiguous(), w, 0, out=out)
             else:
                 K.gemm(x.contiguous(), w, out=out)
             if lora is not None:

@@ -120,10 +120,13 @@ def test_paged_attention_decode_and_prefill(K, Hq, Hkv, D, window, softcap):
                 assert _rel(got, want) < 2e-2, (kernel, S_lens, nsplit, _rel(got, want))
 
 
-@pytest.mark.parametrize("M,N,K_,sk", [(48, 2112, 7168, 8), (3, 520, 4096, 5), (384, 384, 7168, 16), (130, 1000, 2048, 3), (32, 7168, 8192, 4)])
+@pytest.mark.parametrize("M,N,K_,sk", [(48, 2112, 7168, 8), (3, 520, 4096, 5), (384, 384, 7168, 16), (130, 1000, 2048, 3), (32, 7168, 8192, 4),
+                                       (48, 2112, 7168, 0), (48, 7168, 8192, 0), (3, 520, 4096, 0), (384, 384, 7168, 0), (48, 12288, 1536, 0),
+                                       (300, 1000, 2048, 0)])
 def test_gemm_split_k_reduced_by_the_last_slice(K, M, N, K_, sk):
     """K slices as separate tiles, partial tiles in scratch, the slice that arrives last sums them in slice order: bf16 and
-    f32 outputs, bias, both operand orders, repeated calls (the arrival counters must come back to zero)."""
+    f32 outputs, bias, both operand orders, repeated calls (the arrival counters must come back to zero).  ``sk = 0`` is
+    stream-K: equal runs of K-blocks per CTA that cross tile boundaries."""
     torch.manual_seed(M + N)
     x = torch.randn(M, K_, device="cuda").bfloat16()
     w = (torch.randn(N, K_, device="cuda") * 0.05).bfloat16()
