@@ -49,8 +49,9 @@ struct GemmParams {
   const float* bias;         // optional, indexed by output feature
   float alpha;
   int* status;
-  // split-K without atomics (EPI_SK_*): every split stores its f32 partial tile in `ws`, bumps the tile's counter, and the split
-  // that arrives last sums the partials in split order and stores the finished tile; the counter goes back to zero.
+  // split-K finished inside the kernel (EPI_SK_*): every K-slice adds its partial tile into the tile's f32 accumulator in `ws`
+  // (red.global.add, spread over L2) and bumps the tile's counter; the slice that arrives last reads the sum once, stores the
+  // finished tile in the output type and writes the zeros back, so accumulator and counter are ready for the next call.
   float* ws;
   int* counters;
   // stream-K (sk_units > 0, batch 1): the tiles_r * tiles_c * k_blocks K-blocks are dealt out in equal contiguous runs of
@@ -148,14 +149,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+  if (threadIdx.x < C::STAGES) { mbar_init(&full[threadIdx.x], 1); mbar_init(&empty[threadIdx.x], 1); }
+  if (threadIdx.x >= 32 && threadIdx.x < 34) { mbar_init(&acc_full[threadIdx.x - 32], 1); mbar_init(&acc_empty[threadIdx.x - 32], 4); }
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
     *abort_flag = 0;
-    fence_barrier_init();
     tma_prefetch_desc(&tm_r);
     tma_prefetch_desc(&tm_c);
   }
+  fence_barrier_init();
   if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -233,7 +234,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       const int final_epi = p.epi == EPI_SK_BF16 ? EPI_STORE_BF16 : (p.epi == EPI_SK_F32 ? EPI_STORE_F32 : p.epi);
       const bool sk = sk_epi && w.nseg > 1;             // a tile computed by one CTA alone is stored directly
       const int tile = w.tile;
-      float* slot = sk ? p.ws + (int64_t)w.slot * (BM * BN) : nullptr;
+      float* slot = sk ? p.ws + (int64_t)tile * (BM * BN) : nullptr;      // the tile's f32 accumulator (zero between calls)
       // stores 32 finished values of this thread's row (columns tc * BN + c0 ..) in the requested form
       auto emit = [&](int c0, const float* v, int epi) {
         const int j0 = tc * BN + c0;
@@ -296,9 +297,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
           v[j] = GLU ? glu_f(p.act, a, __uint_as_float(r2[j]) * p.alpha) : a;
         }
         if (sk) {
-          // partial tile, column-major so that a warp's 32 rows are contiguous: slot[(c0 + j) * BM + row]
+          // add this K-slice into the tile's f32 accumulator in scratch (column-major, so a warp's 32 rows are contiguous:
+          // acc[(c0 + j) * BM + row]); the additions of the slices run in L2 in parallel
 #pragma unroll
-          for (int j = 0; j < 32; ++j) __stcg(slot + (c0 + j) * BM + q * 32 + lane, v[j]);
+          for (int j = 0; j < 32; ++j) atomicAdd(slot + (c0 + j) * BM + q * 32 + lane, v[j]);
         } else {
           emit(c0, v, final_epi);
         }
@@ -314,16 +316,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (*sk_last) {
           __threadfence();
-          const float* base = p.ws + (int64_t)(w.slot - w.seg) * (BM * BN);
 #pragma unroll 1
           for (int c0 = 0; c0 < BN; c0 += 32) {
             float v[32];
+            float* a = slot + c0 * BM + q * 32 + lane;
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.f;
-            for (int s2 = 0; s2 < w.nseg; ++s2) {
+            for (int j = 0; j < 32; ++j) v[j] = __ldcg(a + j * BM);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] += __ldcg(base + (int64_t)s2 * (BM * BN) + (c0 + j) * BM + q * 32 + lane);
-            }
+            for (int j = 0; j < 32; ++j) __stcg(a + j * BM, 0.f);          // the accumulator is left zero for the next call
             emit(c0, v, final_epi);
           }
           if (threadIdx.x == 64) p.counters[tile] = 0;
@@ -456,15 +456,16 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   p.sk_units = 0;
   if (sk_epi) {
     const int64_t tiles = (int64_t)p.tiles_r * p.tiles_c * batch;
-    int64_t slots = tiles * p.split_k;
+    const int64_t slots = tiles;                 // one f32 accumulator tile per output tile
     if (stream_k && batch == 1) {
       // equal runs of K-blocks per CTA; at least 4 blocks each so that the partial-tile traffic stays small beside the weights
       const int64_t units = tiles * p.k_blocks;
       int64_t g = mary_num_sms();
       if (g > units / 4) g = units / 4 > 0 ? units / 4 : 1;
       p.sk_units = (int)((units + g - 1) / g);
+      // at most 16 slices per tile: bounds the contention on one accumulator tile
+      if (p.sk_units < (p.k_blocks + 15) / 16) p.sk_units = (p.k_blocks + 15) / 16;
       p.split_k = 1;
-      slots = (units + p.sk_units - 1) / p.sk_units + tiles;
     }
     if (tiles > n_counters || slots * BM * bn > ws_floats) return MARY_ERR_BAD_ARG;     // workspace too small
   }
@@ -494,10 +495,10 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
   return mary_gemm_bf16_batched(X, W, out, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, bias, alpha, glu, epi, split_k, swap, stream);
 }
 
-// Split-K without atomics, memset or a cast pass: out (bf16, or f32 when out_f32) = alpha * X W^T + bias with K cut into
-// split_k slices that run as separate tiles.  `ws` (ws_floats f32) holds the partial tiles and `counters` (n_counters ints, zero
-// before the first call; the kernel leaves them zero) one arrival count per output tile; both are scratch that calls on one
-// stream may share.  Returns MARY_ERR_BAD_ARG when the scratch is too small for this shape.
+// Split-K finished inside the kernel, without a zero-fill or a cast pass: out (bf16, or f32 when out_f32) = alpha * X W^T + bias
+// with K cut into slices that run as separate CTAs.  `ws` (ws_floats f32, ZERO before the first call; the kernel leaves it zero)
+// holds one f32 accumulator tile per output tile and `counters` (n_counters ints, zero likewise) one arrival count per tile; both
+// are scratch that calls on one stream may share.  Returns MARY_ERR_BAD_ARG when the scratch is too small for this shape.
 MARY_API int mary_gemm_bf16_splitk(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo,
                                    const float* bias, float alpha, int out_f32, int split_k, int swap, float* ws, int64_t ws_floats,
                                    int* counters, int n_counters, cudaStream_t stream) {

@@ -137,22 +137,22 @@ def _auto_split_k(M: int, N: int, K: int) -> int:
 
 declare("mary_gemm_bf16_splitk", "pppiiilllpfiiiplpis")
 _SK_WS: dict = {}
-SK_WS_FLOATS = 8 << 20          # 32 MiB of partial tiles
+SK_WS_FLOATS = 4 << 20          # 16 MiB of accumulator tiles
 SK_COUNTERS = 8192
 
 
 def _sk_workspace(dev):
-    """Scratch of the atomics-free split-K GEMM (partial tiles + per-tile arrival counters), one per device; calls on one
-    stream share it.  Created on first use — before any stream capture, since warm-up steps run eagerly first."""
+    """Scratch of the split-K GEMM (f32 accumulator tiles + per-tile arrival counters, zero between calls), one per device;
+    calls on one stream share it.  Created on first use — before any stream capture, since warm-up steps run eagerly first."""
     key = dev.index if dev.index is not None else torch.cuda.current_device()
     if key not in _SK_WS:
-        _SK_WS[key] = (torch.empty(SK_WS_FLOATS, dtype=torch.float32, device=dev), torch.zeros(SK_COUNTERS, dtype=torch.int32, device=dev))
+        _SK_WS[key] = (torch.zeros(SK_WS_FLOATS, dtype=torch.float32, device=dev), torch.zeros(SK_COUNTERS, dtype=torch.int32, device=dev))
     return _SK_WS[key]
 
 
 def gemm_splitk(x, w, split_k: int, out=None, f32: bool = False, bias=None, swap: int = -1):
-    """``x @ w^T`` with K cut into ``split_k`` slices reduced inside the kernel (the slice that finishes last sums the partial
-    tiles): no zero-fill, no atomics, no cast pass.  ``split_k=0`` is stream-K: the K-blocks of all tiles are dealt out in
+    """``x @ w^T`` with K cut into ``split_k`` slices reduced inside the kernel (every slice adds into an f32 accumulator tile in
+    scratch; the slice that finishes last converts and stores it and leaves the scratch zero): no zero-fill, no cast pass.  ``split_k=0`` is stream-K: the K-blocks of all tiles are dealt out in
     equal contiguous runs, one per SM, so every SM streams the same share of the weights whatever the tile count.  Falls back
     to the atomic path when the shape outgrows the scratch."""
     _bf16(x), _bf16(w)
