@@ -101,13 +101,22 @@ __device__ __forceinline__ uint32_t e2m1_code(float y) {
 // One CTA per destination row.  src_of[row] < 0 -> padding row, skipped.  identity != 0 -> the source row is `row`
 // itself (re-quantising an intermediate that is already in padded-row order; src_of only marks validity, may be null).
 // Scales go to the 512-byte block layout of the row's NT-row tile; optionally also row-major (tests, dense users).
+// With row_of (entry -> padded row, k entries per token) the grid runs over the ENTRIES instead of the padded rows: a decode
+// batch has a few hundred entries but thousands of padded rows, most of them padding.
 __global__ void quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int* __restrict__ src_of, int identity,
                                         int Kd, int NT, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf_tiles,
-                                        uint8_t* __restrict__ sf_rowmajor, const int* __restrict__ n_rows) {
-  const int row = blockIdx.x;
-  if (n_rows && row >= *n_rows) return;
+                                        uint8_t* __restrict__ sf_rowmajor, const int* __restrict__ n_rows,
+                                        const int* __restrict__ row_of, int k) {
+  int row = blockIdx.x;
   int src = row;
-  if (src_of) { const int s = src_of[row]; if (s < 0) return; if (!identity) src = s; }
+  if (row_of) {
+    row = row_of[blockIdx.x];
+    if (row < 0) return;
+    src = identity ? row : (int)blockIdx.x / k;
+  } else {
+    if (n_rows && row >= *n_rows) return;
+    if (src_of) { const int s = src_of[row]; if (s < 0) return; if (!identity) src = s; }
+  }
   const __nv_bfloat16* xr = x + (int64_t)src * ldx;
   const int tile = row / NT, r = row % NT;
   const int64_t sf_base = (int64_t)tile * (Kd / 64) * 512 + (r % 32) * 16 + (r / 32) * 4;
@@ -193,7 +202,20 @@ MARY_API int mary_quant_nvfp4_rows(const void* x, int64_t ldx, const int* src_of
   if ((K % 64) || (ldx % 8)) return MARY_ERR_BAD_ARG;
   int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
   quant_nvfp4_rows_kernel<<<rows, threads, 0, s>>>((const __nv_bfloat16*)x, ldx, src_of, identity, K, NT, (uint8_t*)xq, (uint8_t*)sf_tiles,
-                                                   (uint8_t*)sf_rowmajor, n_rows);
+                                                   (uint8_t*)sf_rowmajor, n_rows, nullptr, 1);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// The same quantiser driven by the routed entries: entry i (token i / k) goes to padded row row_of[i] (negative: not routed here).
+// identity != 0 re-quantises x's own row row_of[i] (an intermediate already in padded-row order).
+MARY_API int mary_quant_nvfp4_entries(const void* x, int64_t ldx, const int* row_of, int n_entries, int k, int identity, int K, int NT,
+                                      void* xq, void* sf_tiles, cudaStream_t s) {
+  if (n_entries <= 0) return MARY_OK;
+  if ((K % 64) || (ldx % 8) || k < 1) return MARY_ERR_BAD_ARG;
+  int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
+  quant_nvfp4_rows_kernel<<<n_entries, threads, 0, s>>>((const __nv_bfloat16*)x, ldx, nullptr, identity, K, NT, (uint8_t*)xq,
+                                                        (uint8_t*)sf_tiles, nullptr, nullptr, row_of, k);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

@@ -28,6 +28,21 @@ def quantize_rows(x, nt: int = 128, src_of=None, identity: bool = True, rows: in
     return xq, sf, rm
 
 
+declare("mary_quant_nvfp4_entries", "plpiiiiipps")
+
+
+def quantize_entries(x, plan, k: int, identity: bool):
+    """The quantiser of the expert pipeline driven by the routed entries (``plan.row_of``): one CTA per entry instead of one per
+    padded row.  Padding rows keep whatever bytes the buffers held; their products stay inside those rows, which nothing reads."""
+    K = x.shape[1]
+    rows, nt = plan.max_rows, plan.nt
+    xq = torch.empty(rows, K // 2, dtype=torch.uint8, device=x.device)
+    sf = torch.empty(rows // nt, K // 64, 512, dtype=torch.uint8, device=x.device)
+    check(lib().mary_quant_nvfp4_entries(_p(x), x.stride(0), _p(plan.row_of), plan.row_of.numel(), k, int(identity), K, nt, _p(xq), _p(sf),
+                                         _stream()), "quant_nvfp4_rows")
+    return xq, sf
+
+
 def quantize_nvfp4(x):
     """Row-major twin of the reference quantiser: ``(codes, scales[rows, K/16])``."""
     xq, _, rm = quantize_rows(x.contiguous(), nt=128, rowmajor=True)
@@ -75,8 +90,8 @@ def experts_forward(x, idx, w, ex, shared=None, nt: int | None = None):
     if nt is None:
         nt = 32 if T * k <= 32 * ex.E else 128
     plan = moe_plan(idx, ex.E, nt)
-    xq, sfx, _ = quantize_rows(x, nt, plan.src_of, identity=False, rows=plan.max_rows, zero_sf=False)
+    xq, sfx = quantize_entries(x, plan, k, identity=False)
     h = grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
-    hq, sfh, _ = quantize_rows(h, nt, plan.src_of, identity=True, rows=plan.max_rows, zero_sf=False)
+    hq, sfh = quantize_entries(h, plan, k, identity=True)
     y = grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, ex.H, ex.F, ex.E, None)
     return unpermute(y, plan, w, T, k, shared)
