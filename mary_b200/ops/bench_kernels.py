@@ -162,6 +162,31 @@ def bench_moe(E: int = 48, H: int = 7168, F: int = 2048, T: int = 384, k: int = 
     assert K.last_status() == 0
 
 
+def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5):
+    """One expert-parallel MoE layer in all-to-all mode with all ranks on this device, phase by phase (the barriers between
+    the phases are stream order here): the per-rank cost of counts, plan + dispatch, expert GEMMs and the weighted sum at the
+    shape one rank of an 8-GPU decode step sees (48 home rows, 384 received rows, 48 local experts).  With
+    ``torch.cuda.profiler`` the single profiled pass is bracketed for a launch list."""
+    from . import cuda as K
+    from .moe import NVFP4Experts
+    from ..parallel.ep import EPBuffers, EPLayer, emulate
+    e_local = E // world
+    slab = NVFP4Experts.random(e_local, H, F, "cuda", seed=0)          # every rank reads the same bytes: what counts is the size
+    bufs = [EPBuffers(world, E, H, F, t_cap=T, k=k, nt=32, device="cuda") for _ in range(world)]
+    layers = [EPLayer(r, world, slab, bufs[r], bufs) for r in range(world)]
+    xs = [torch.randn(T, H, device="cuda").bfloat16() for _ in range(world)]
+    routed = [K.router_topk(torch.randn(T, E, device="cuda"), k, "softmax") for _ in range(world)]
+    idxs, ws = [i for i, _ in routed], [w for _, w in routed]
+    ms = time_op(lambda: emulate(layers, xs, idxs, ws), iters=iters)
+    torch.cuda.profiler.start()
+    emulate(layers, xs, idxs, ws)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"ep all-to-all layer, {world} ranks on one device, T={T}/rank E={E} H={H} F={F} k={k}: {ms:.3f} ms for all ranks, "
+          f"{ms / world * 1e3:.1f} us per rank")
+    assert K.last_status() == 0
+
+
 if __name__ == "__main__":
     # ``gemm M N K`` / ``attn B L Hq Hkv D window`` / ``fa B L Hq Hkv DK DV window`` / ``mla B L Hq q_len`` / ``moe E H F T k`` run that one case only
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
@@ -186,5 +211,7 @@ if __name__ == "__main__":
                 bench_mla(page=pg)
                 bench_mla(Hq=8, page=pg)
                 bench_mla(B=16, page=pg)
+    if what == "ep":
+        bench_ep(*nums)
     if what in ("moe", "all"):
         bench_moe(*(nums if what == "moe" else []))
