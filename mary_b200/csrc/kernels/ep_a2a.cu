@@ -52,9 +52,13 @@ __global__ void ep_counts_kernel(const int* __restrict__ idx, int n_entries, int
 
 // cm[world][E] (local copy of the count matrix).  Outputs for this rank: tiles / meta {n_tiles, padded rows} of its own
 // experts, send_base[E] = first row of this rank's entries of global expert e on the owner, send_cnt[E] zeroed.
+// shared_rows > 0: this rank also runs a shared expert (local expert index e_local, "global" id E) over that many of its own rows;
+// they are placed behind the received rows (send_base[E]), never leave the rank, and get their own tiles.
 __global__ void ep_plan_kernel(const int* __restrict__ cm, int world, int rank, int E, int e_local, int NT, Tile* __restrict__ tiles,
-                               int* __restrict__ meta, int* __restrict__ send_base, int* __restrict__ send_cnt, int* __restrict__ recv_src_off) {
+                               int* __restrict__ meta, int* __restrict__ send_base, int* __restrict__ send_cnt, int* __restrict__ recv_src_off,
+                               int shared_rows) {
   extern __shared__ int sh[];
+  __shared__ int acc_self;
   int* tot = sh;            // [E] rows of every expert over all sources
   int* off = sh + E;        // [E] padded first row of the expert on its owner
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -68,9 +72,17 @@ __global__ void ep_plan_kernel(const int* __restrict__ cm, int world, int rank, 
     const int d = threadIdx.x;
     int acc = 0;
     for (int j = 0; j < e_local; ++j) { const int e = d * e_local + j; off[e] = acc; acc += (tot[e] + NT - 1) / NT * NT; }
-    if (d == rank) { meta[0] = acc / NT; meta[1] = acc; }
+    if (d == rank) {
+      acc_self = acc;
+      const int sp = (shared_rows + NT - 1) / NT * NT;
+      meta[0] = (acc + sp) / NT;
+      meta[1] = acc + sp;
+      if (shared_rows > 0) { send_base[E] = acc; send_cnt[E] = 0; }
+    }
   }
   __syncthreads();
+  for (int i = threadIdx.x; i * NT < shared_rows; i += blockDim.x)
+    tiles[acc_self / NT + i] = Tile{e_local, acc_self + i * NT, min(NT, shared_rows - i * NT), acc_self / NT + i};
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int before = 0;
     for (int s = 0; s < rank; ++s) before += cm[s * E + e];
@@ -97,10 +109,10 @@ __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t 
   __shared__ int s_row;
   const int i = blockIdx.x;
   const int e = idx[i];
-  if (e < 0 || e >= E) return;
+  if (e < 0 || e > E) return;                    // e == E: the shared expert, served on this rank
   if (threadIdx.x == 0) s_row = send_base[e] + atomicAdd(&send_cnt[e], 1);
   __syncthreads();
-  const int row = s_row, d = e / e_local;
+  const int row = s_row, d = (e == E) ? rank : e / e_local;
   uint8_t* xq = (uint8_t*)xq_slabs.p[d];
   uint8_t* sf = (uint8_t*)sf_slabs.p[d];
   if (threadIdx.x == 0) ((int*)meta_slabs.p[d])[row] = rank * entry_stride + i;
@@ -166,10 +178,12 @@ MARY_API int mary_ep_counts(const int* idx, int n_entries, int E, int rank, int 
   return MARY_OK;
 }
 
+// send_base / send_cnt hold E + 1 entries (the last one for the shared expert's rows when shared_rows > 0).
 MARY_API int mary_ep_plan(const int* cm, int world, int rank, int E, int e_local, int NT, void* tiles, int* meta, int* send_base,
-                          int* send_cnt, cudaStream_t s) {
-  if (E > 4096 || world > MAX_RANKS || e_local * world != E) return MARY_ERR_BAD_ARG;
-  ep_plan_kernel<<<1, 1024, 2 * E * sizeof(int), s>>>(cm, world, rank, E, e_local, NT, (Tile*)tiles, meta, send_base, send_cnt, nullptr);
+                          int* send_cnt, int shared_rows, cudaStream_t s) {
+  if (E > 4096 || world > MAX_RANKS || e_local * world != E || shared_rows < 0) return MARY_ERR_BAD_ARG;
+  ep_plan_kernel<<<1, 1024, 2 * E * sizeof(int), s>>>(cm, world, rank, E, e_local, NT, (Tile*)tiles, meta, send_base, send_cnt, nullptr,
+                                                      shared_rows);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

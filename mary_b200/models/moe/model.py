@@ -152,21 +152,7 @@ class MoEFFN(nn.Module):
             if self.ep_layer is None:
                 self.ep_layer = self.par.ep_factory(self.experts, self.c)
             shared = ops.linear(ops.linear_glu(x, self.shared.w_gu, self.c.act), self.shared.w_down) if self.shared is not None else None
-            if self.shared_in_experts:
-                # the NVFP4 shared expert sits behind the local routed ones on every rank: run it here on the home tokens
-                T = x.shape[0]
-                ex = self.experts
-                if getattr(self, "_shared_ex", None) is None or self._shared_ex[0] is not ex:
-                    def last(t, per):
-                        return t[(ex.E - 1) * per:ex.E * per]
-                    r13, r2 = 2 * ex.F, ex.H
-                    self._shared_ex = (ex, NVFP4Experts(1, ex.H, ex.F, last(ex.w13_q, r13), last(ex.w13_sf, r13 // 128), last(ex.w13_s2, 1),
-                                                        last(ex.w2_q, r2), last(ex.w2_sf, r2 // 128), last(ex.w2_s2, 1), ex.act))
-                tail = self._tail.get(("a2a", T, x.device))
-                if tail is None:
-                    tail = (torch.zeros(T, 1, dtype=torch.int32, device=x.device), torch.ones(T, 1, dtype=torch.float32, device=x.device))
-                    self._tail[("a2a", T, x.device)] = tail
-                shared = experts_forward(x, tail[0], tail[1], self._shared_ex[1], None)
+            # an NVFP4 shared expert sits behind the local routed ones on every rank; the EP layer serves it in the same launches
             return self.ep_layer.forward(x, idx, w, shared)
         if self.par.ep_size > 1:              # keep the entries of the local experts, renumbered from zero
             local = (idx >= self.e0) & (idx < self.e0 + self.e_local)

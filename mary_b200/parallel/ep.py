@@ -21,7 +21,7 @@ from ..ops.cuda import _p, _stream, check, declare, lib
 from ..ops.moe import NVFP4Experts
 
 declare("mary_ep_counts", "piiiips")
-declare("mary_ep_plan", "piiiiipppps")
+declare("mary_ep_plan", "piiiiippppis")
 declare("mary_ep_dispatch", "plp" + "iiiiiiiii" + "pp" + "ppp" + "s")
 declare("mary_ep_return_ptrs", "pppiiiiipps")
 declare("mary_rank_barrier", "piipils")
@@ -35,13 +35,17 @@ def _ptrs(tensors):
 class EPBuffers:
     """The symmetric slabs of one rank (plain tensors; ``peer_*`` hold every rank's base address)."""
 
-    def __init__(self, world: int, E: int, H: int, F: int, t_cap: int, k: int, nt: int, device, alloc=None):
+    def __init__(self, world: int, E: int, H: int, F: int, t_cap: int, k: int, nt: int, device, alloc=None, shared: bool = False):
+        """``shared``: every rank also serves one shared expert over its own ``t_cap`` rows inside the same GEMM launches; a
+        token then has ``k + 1`` entries (``self.k`` counts them all)."""
         alloc = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
-        self.world, self.E, self.H, self.F, self.t_cap, self.k, self.nt = world, E, H, F, t_cap, k, nt
+        self.shared = shared
+        self.world, self.E, self.H, self.F, self.t_cap, self.nt = world, E, H, F, t_cap, nt
+        self.k_routed, self.k = k, k + (1 if shared else 0)
         e_local = E // world
         entries = world * t_cap * k
-        self.cap_rows = (entries + min(entries, e_local) * (nt - 1) + nt - 1) // nt * nt
-        self.entry_stride = t_cap * k
+        self.cap_rows = (entries + min(entries, e_local) * (nt - 1) + nt - 1) // nt * nt + ((t_cap + nt - 1) // nt * nt if shared else 0)
+        self.entry_stride = t_cap * self.k
         self.count_mat = alloc(world * E, torch.int32)
         self.xq = alloc(self.cap_rows * (H // 2), torch.uint8)
         self.sf = alloc((self.cap_rows // nt) * (H // 64) * 512, torch.uint8)
@@ -62,8 +66,8 @@ class EPLayer:
         self.p_comb = _ptrs([p.comb for p in peers])
         self.tiles = torch.empty(bufs.cap_rows // bufs.nt, 4, dtype=torch.int32, device=dev)
         self.plan_meta = torch.zeros(2, dtype=torch.int32, device=dev)
-        self.send_base = torch.empty(bufs.E, dtype=torch.int32, device=dev)
-        self.send_cnt = torch.empty(bufs.E, dtype=torch.int32, device=dev)
+        self.send_base = torch.empty(bufs.E + 1, dtype=torch.int32, device=dev)
+        self.send_cnt = torch.empty(bufs.E + 1, dtype=torch.int32, device=dev)
         self.row_ptrs = torch.zeros(bufs.cap_rows, dtype=torch.int64, device=dev)
         self.ident = torch.arange(bufs.entry_stride, dtype=torch.int32, device=dev)
         self.sig_ptrs, self.wait_ns = sig_ptrs, wait_ns
@@ -84,7 +88,7 @@ class EPLayer:
         b = self.b
         T, k = idx.shape
         check(lib().mary_ep_plan(_p(b.count_mat), self.world, self.rank, b.E, self.e_local, b.nt, _p(self.tiles), _p(self.plan_meta),
-                                 _p(self.send_base), _p(self.send_cnt), _stream()), "ep_plan")
+                                 _p(self.send_base), _p(self.send_cnt), T if b.shared else 0, _stream()), "ep_plan")
         check(lib().mary_ep_dispatch(_p(x), x.stride(0), _p(idx), T * k, k, b.E, self.e_local, b.H, b.nt, self.rank, self.world,
                                      b.entry_stride, _p(self.send_base), _p(self.send_cnt), self.p_xq, self.p_sf, self.p_meta,
                                      _stream()), "ep_dispatch")
@@ -111,8 +115,20 @@ class EPLayer:
         plan.row_of = self.ident
         return cuda_moe.unpermute(comb, plan, w, T, k, shared)
 
+    def with_shared(self, idx, w):
+        """Append the shared expert's entry (id ``E``, weight 1) to every token's routed entries."""
+        T = idx.shape[0]
+        tail = getattr(self, "_tail", None)
+        if tail is None or tail[0].shape[0] != T:
+            tail = (torch.full((T, 1), self.b.E, dtype=torch.int32, device=idx.device), torch.ones(T, 1, dtype=torch.float32, device=idx.device))
+            self._tail = tail
+        return torch.cat([idx.to(torch.int32), tail[0]], 1), torch.cat([w.float(), tail[1]], 1)
+
     def forward(self, x, idx, w, shared=None):
-        """One MoE layer for this rank's tokens (``idx`` holds GLOBAL expert ids)."""
+        """One MoE layer for this rank's tokens (``idx`` holds GLOBAL expert ids).  With a shared expert in the buffers'
+        layout the caller passes the routed entries only; the shared entry is appended here."""
+        if self.b.shared and idx.shape[1] == self.b.k_routed:
+            idx, w = self.with_shared(idx, w)
         idx = idx.to(torch.int32).contiguous()
         self.counts(idx)
         self.barrier()
@@ -125,6 +141,9 @@ class EPLayer:
 
 def emulate(layers: list[EPLayer], xs, idxs, ws):
     """Drive ``world`` ranks that share one device, phase by phase; returns each rank's output."""
+    if layers[0].b.shared and idxs[0].shape[1] == layers[0].b.k_routed:
+        pairs = [l.with_shared(i, w) for l, i, w in zip(layers, idxs, ws)]
+        idxs, ws = [p[0] for p in pairs], [p[1] for p in pairs]
     idxs = [i.to(torch.int32).contiguous() for i in idxs]
     for l, i in zip(layers, idxs):
         l.counts(i)
@@ -152,7 +171,7 @@ def distributed_factory(rank: int, world: int, device, t_cap: int, nt: int = 32,
                 t.zero_()
                 return t
             b = EPBuffers(world, cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, t_cap, cfg.num_experts_per_tok, nt,
-                          device, alloc)
+                          device, alloc, shared=bool(cfg.shared_expert_nvfp4 and cfg.n_shared_experts == 1))
             peers = [types.SimpleNamespace() for _ in range(world)]
             for name in ("count_mat", "xq", "sf", "meta", "comb"):
                 hdl = symm_mem.rendezvous(getattr(b, name), dist.group.WORLD)

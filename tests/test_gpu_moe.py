@@ -97,3 +97,28 @@ def test_ep_all_to_all_dispatch_combine_emulated(world):
     outs2 = emulate(layers, xs, [i for i, _ in routed], [w for _, w in routed])
     for a, b in zip(outs, outs2):
         assert torch.equal(a, b)
+
+
+def test_ep_all_to_all_serves_the_shared_expert_in_the_same_launches():
+    """A shared NVFP4 expert kept behind every rank's routed experts: its rows never leave the rank, ride in the same grouped
+    GEMM launches and come back through the combine buffer as one more entry per token."""
+    from mary_b200.ops import cuda, cuda_moe
+    from mary_b200.models.moe.shard import slice_experts
+    from mary_b200.parallel.ep import EPBuffers, EPLayer, emulate
+    world = 4
+    torch.manual_seed(9)
+    E, H, F, k, T = 8 * world, 512, 256, 2, 37
+    ex = NVFP4Experts.random(E + 1, H, F, "cuda", std=0.05, seed=5)          # the last one is the shared expert
+    bufs = [EPBuffers(world, E, H, F, t_cap=64, k=k, nt=32, device="cuda", shared=True) for _ in range(world)]
+    layers = [EPLayer(r, world, slice_experts(ex, r, world, tail=1), bufs[r], bufs) for r in range(world)]
+    xs = [torch.randn(T - 5 * r, H, device="cuda").bfloat16() for r in range(world)]
+    routed = [cuda.router_topk(torch.randn(x.shape[0], E, device="cuda"), k, "softmax") for x in xs]
+    outs = emulate(layers, xs, [i for i, _ in routed], [w for _, w in routed])
+    torch.cuda.synchronize()
+    assert cuda.last_status() == 0
+    for x, (idx, w), got in zip(xs, routed, outs):
+        n = x.shape[0]
+        idx2 = torch.cat([idx.to(torch.int32), torch.full((n, 1), E, dtype=torch.int32, device="cuda")], 1)
+        w2 = torch.cat([w.float(), torch.ones(n, 1, device="cuda")], 1)
+        want = cuda_moe.experts_forward(x, idx2, w2, ex, None, 32)
+        assert _rel(got, want) < 2e-2, _rel(got, want)
