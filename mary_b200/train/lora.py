@@ -129,17 +129,26 @@ class Gemma4LoraForward(nn.Module):
         return linear_frozen(x, w.detach(), wt)
 
     def _attn(self, q, k, v, window):
-        # q [B,S,Hq,D], k/v [B,S,Hkv,D]; scale 1.0; causal, optional sliding window
+        """q [B,S,Hq,D], k/v [B,S,Hkv,D]; scale 1.0; causal, optional sliding window.  Global layers take the fused causal path
+        (no mask tensor, no materialised scores).  Sliding layers attend chunk by chunk: queries of chunk ``c`` (``window``
+        tokens) can only see keys of chunks ``c - 1`` and ``c``, so the scores are ``[W, 2W]`` blocks instead of ``[S, S]``."""
         B, Sq, Hq, D = q.shape
         g = Hq // k.shape[2]
-        k, v = k.repeat_interleave(g, 2), v.repeat_interleave(g, 2)
-        pos = torch.arange(Sq, device=q.device)
-        mask = pos[None, :] <= pos[:, None]
-        if window:
-            mask = mask & ((pos[:, None] - pos[None, :]) < window)
-        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                                             attn_mask=mask, scale=1.0)
-        return o.transpose(1, 2)
+        qt = q.transpose(1, 2)
+        kt, vt = k.transpose(1, 2), v.transpose(1, 2)
+        sdpa = torch.nn.functional.scaled_dot_product_attention
+        if not window or window >= Sq:
+            return sdpa(qt, kt, vt, is_causal=True, scale=1.0, enable_gqa=g > 1).transpose(1, 2)
+        W = window
+        outs = []
+        for c0 in range(0, Sq, W):
+            c1 = min(c0 + W, Sq)
+            k0 = max(0, c0 - W)
+            qpos = torch.arange(c0, c1, device=q.device)
+            kpos = torch.arange(k0, c1, device=q.device)
+            mask = (kpos[None, :] <= qpos[:, None]) & ((qpos[:, None] - kpos[None, :]) < W)
+            outs.append(sdpa(qt[:, :, c0:c1], kt[:, :, k0:c1], vt[:, :, k0:c1], attn_mask=mask, scale=1.0, enable_gqa=g > 1))
+        return torch.cat(outs, 2).transpose(1, 2)
 
     def forward(self, ids):
         m, c = self.model, self.model.cfg
