@@ -262,3 +262,24 @@ def test_torch_pickle_reader_and_refusal(tmp_path):
         z.writestr("archive/data.pkl", pickle.dumps(print))
     with pytest.raises(pickle.UnpicklingError):
         list(iter_pickle(evil))
+
+
+def test_dyntensor_roundtrip_alignment_and_rejections():
+    import struct
+    import torch
+    from mary_b200.format import dyntensor as dt
+    rng = np.random.default_rng(0)
+    for arr in (rng.standard_normal((3, 5)).astype(np.float32), rng.integers(-5, 5, (2, 3, 4)).astype(np.int64), np.float64(3.5).reshape(()),
+                rng.integers(0, 255, (7,)).astype(np.uint8), np.array([True, False, True])):
+        blob = dt.encode(arr)
+        back, name = dt.decode(blob)
+        assert back.dtype == arr.dtype and back.shape == arr.shape and np.array_equal(back, arr)
+        n, shape, off = dt.header(blob)
+        assert off % arr.dtype.itemsize == 0                         # data starts on the dtype's alignment
+    t = torch.randn(4, 6).bfloat16()
+    blob = dt.encode(t)
+    assert dt.header(blob)[0] == "bf16" and torch.equal(dt.decode_torch(blob), t)
+    assert struct.unpack_from("<I", blob)[0] == 0x534E5444 and blob[4] == 1 and blob[5] == 2       # magic, tag bf16 = 1, rank 2
+    for bad in (b"abc", b"\\0" * 16, blob[:-2], struct.pack("<IBBH", dt.MAGIC, 99, 0, 0)):
+        with pytest.raises(dt.DynTensorError):
+            dt.header(bad)
