@@ -22,6 +22,7 @@ def main():
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-overlap", action="store_true")
+    ap.add_argument("--checkpoint", action="store_true", help="recompute each layer in the backward pass (activation checkpointing)")
     a = ap.parse_args()
     from ..models.gemma4 import Gemma4Model, gemma_12b_config
     from ..models.gemma4.weights import init_random_
@@ -44,7 +45,7 @@ def main():
             reduce_fn = heap.all_reduce_f32_
         else:
             reduce_fn = lambda g: dist.all_reduce(g)  # noqa: E731
-    tr = LoraTrainer(model, rank=16, alpha=32.0, lr=1e-4, dp_size=world, reduce_fn=reduce_fn, overlap=not a.no_overlap)
+    tr = LoraTrainer(model, rank=16, alpha=32.0, lr=1e-4, dp_size=world, reduce_fn=reduce_fn, overlap=not a.no_overlap, checkpoint=a.checkpoint)
     g = torch.Generator(device=dev).manual_seed(rank)
     ids = torch.randint(0, cfg.vocab_size, (a.batch, a.seq), device=dev, generator=g)
     for _ in range(a.warmup):
@@ -67,7 +68,7 @@ def main():
         print(json.dumps({"metric": "LoRA finetune tokens/s (Gemma-4-12B-style, rank 16, seq %d)" % a.seq,
                           "value": round(world * a.batch * a.seq / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world,
                           "ms_per_step": round(ms, 2), "loss": round(loss, 4), "layers": a.layers, "comm": a.comm if world > 1 else "none",
-                          "overlap": not a.no_overlap, "gpu_launches_per_step": K.LAUNCHES // a.steps,
+                          "overlap": not a.no_overlap, "checkpointing": a.checkpoint, "gpu_launches_per_step": K.LAUNCHES // a.steps,
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1), "kernel_status": K.last_status()}))
     if world > 1:
         dist.destroy_process_group()

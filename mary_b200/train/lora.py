@@ -150,45 +150,56 @@ class Gemma4LoraForward(nn.Module):
             outs.append(sdpa(qt[:, :, c0:c1], kt[:, :, k0:c1], vt[:, :, k0:c1], attn_mask=mask, scale=1.0, enable_gqa=g > 1))
         return torch.cat(outs, 2).transpose(1, 2)
 
+    def _layer(self, i, h, pos, B, Sq):
+        m, c = self.model, self.model.cfg
+        L = m.layers[i]
+        ad = lambda p: self.lora.get(i, p)  # noqa: E731
+        x = ref.rmsnorm(h, L.ln_in.detach(), c.rms_norm_eps)
+        qkv = self._lin(x, L.w_qkv)
+        nq, nkv, D = L.n_q * L.D, L.n_kv * L.D, L.D
+        deltas = [ad(p)(x) if ad(p) is not None else None for p in ("q_proj", "k_proj", "v_proj")]
+        q, k, v = qkv.split([nq, nkv, nkv], -1)
+        q = q + deltas[0] if deltas[0] is not None else q
+        k = k + deltas[1] if deltas[1] is not None else k
+        v = v + deltas[2] if deltas[2] is not None else v
+        q = ref.rmsnorm(q.reshape(B * Sq, L.n_q, D), L.q_norm.detach(), c.rms_norm_eps)
+        k = ref.rmsnorm(k.reshape(B * Sq, L.n_kv, D), L.k_norm.detach(), c.rms_norm_eps)
+        v = ref.rmsnorm(v.reshape(B * Sq, L.n_kv, D), None, c.rms_norm_eps)
+        q, k = ref.rope(q, pos, L.inv_freq), ref.rope(k, pos, L.inv_freq)
+        o = self._attn(q.view(B, Sq, L.n_q, D), k.view(B, Sq, L.n_kv, D), v.view(B, Sq, L.n_kv, D), L.window)
+        o = o.reshape(B, Sq, nq)
+        a = self._lin(o, L.w_o)
+        if ad("o_proj") is not None:
+            a = a + ad("o_proj")(o)
+        a = m.tp.all_reduce(a) if m.tp.size > 1 else a
+        h = h + ref.rmsnorm(a, L.ln_post_attn.detach(), c.rms_norm_eps)
+        x = ref.rmsnorm(h, L.ln_pre_ffn.detach(), c.rms_norm_eps)
+        gu = self._lin(x, L.w_gu)
+        g_, u_ = gu[..., :L.F], gu[..., L.F:]
+        if ad("gate_proj") is not None:
+            g_ = g_ + ad("gate_proj")(x)
+        if ad("up_proj") is not None:
+            u_ = u_ + ad("up_proj")(x)
+        mm = ref.geglu(g_, u_)
+        d = self._lin(mm, L.w_down)
+        if ad("down_proj") is not None:
+            d = d + ad("down_proj")(mm)
+        d = m.tp.all_reduce(d) if m.tp.size > 1 else d
+        return (h + ref.rmsnorm(d, L.ln_post_ffn.detach(), c.rms_norm_eps)) * L.layer_scalar
+
     def forward(self, ids):
+        """``checkpoint = True`` keeps only every layer's input for the backward pass and recomputes the layer there: the
+        activations of a 4096-token sequence through 48 layers otherwise take on the order of 100 GB."""
         m, c = self.model, self.model.cfg
         B, Sq = ids.shape
         h = (m.embed.detach()[ids.long()].float() * m.embed_scale).to(m.dtype)
         pos = torch.arange(Sq, device=ids.device).repeat(B)
-        for i, L in enumerate(m.layers):
-            ad = lambda p: self.lora.get(i, p)  # noqa: E731
-            x = ref.rmsnorm(h, L.ln_in.detach(), c.rms_norm_eps)
-            qkv = self._lin(x, L.w_qkv)
-            nq, nkv, D = L.n_q * L.D, L.n_kv * L.D, L.D
-            deltas = [ad(p)(x) if ad(p) is not None else None for p in ("q_proj", "k_proj", "v_proj")]
-            q, k, v = qkv.split([nq, nkv, nkv], -1)
-            q = q + deltas[0] if deltas[0] is not None else q
-            k = k + deltas[1] if deltas[1] is not None else k
-            v = v + deltas[2] if deltas[2] is not None else v
-            q = ref.rmsnorm(q.reshape(B * Sq, L.n_q, D), L.q_norm.detach(), c.rms_norm_eps)
-            k = ref.rmsnorm(k.reshape(B * Sq, L.n_kv, D), L.k_norm.detach(), c.rms_norm_eps)
-            v = ref.rmsnorm(v.reshape(B * Sq, L.n_kv, D), None, c.rms_norm_eps)
-            q, k = ref.rope(q, pos, L.inv_freq), ref.rope(k, pos, L.inv_freq)
-            o = self._attn(q.view(B, Sq, L.n_q, D), k.view(B, Sq, L.n_kv, D), v.view(B, Sq, L.n_kv, D), L.window)
-            o = o.reshape(B, Sq, nq)
-            a = self._lin(o, L.w_o)
-            if ad("o_proj") is not None:
-                a = a + ad("o_proj")(o)
-            a = m.tp.all_reduce(a) if m.tp.size > 1 else a
-            h = h + ref.rmsnorm(a, L.ln_post_attn.detach(), c.rms_norm_eps)
-            x = ref.rmsnorm(h, L.ln_pre_ffn.detach(), c.rms_norm_eps)
-            gu = self._lin(x, L.w_gu)
-            g_, u_ = gu[..., :L.F], gu[..., L.F:]
-            if ad("gate_proj") is not None:
-                g_ = g_ + ad("gate_proj")(x)
-            if ad("up_proj") is not None:
-                u_ = u_ + ad("up_proj")(x)
-            mm = ref.geglu(g_, u_)
-            d = self._lin(mm, L.w_down)
-            if ad("down_proj") is not None:
-                d = d + ad("down_proj")(mm)
-            d = m.tp.all_reduce(d) if m.tp.size > 1 else d
-            h = (h + ref.rmsnorm(d, L.ln_post_ffn.detach(), c.rms_norm_eps)) * L.layer_scalar
+        for i in range(len(m.layers)):
+            if getattr(self, "checkpoint", False) and torch.is_grad_enabled():
+                from torch.utils.checkpoint import checkpoint
+                h = checkpoint(self._layer, i, h, pos, B, Sq, use_reentrant=False)
+            else:
+                h = self._layer(i, h, pos, B, Sq)
         x = ref.rmsnorm(h, m.norm.detach(), c.rms_norm_eps)
         return x
 

@@ -75,10 +75,11 @@ class FlatAdamW:
 
 class LoraTrainer:
     def __init__(self, model, rank: int = 16, alpha: float = 32.0, lr: float = 1e-4, seed: int = 0, dp_group=None, dp_size: int = 1,
-                 reduce_fn=None, overlap: bool = True):
+                 reduce_fn=None, overlap: bool = True, checkpoint: bool = False):
         self.model = model
         self.lora = LoraWeights.init_gemma4(model, rank, alpha, seed)
         self.fwd = Gemma4LoraForward(model, self.lora)
+        self.fwd.checkpoint = checkpoint          # recompute every layer in the backward pass instead of keeping its activations
         # parameters ordered by layer so that a layer's gradients are one contiguous bucket
         self.layer_params = []
         for i in range(len(model.layers)):

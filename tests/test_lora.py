@@ -119,3 +119,24 @@ def test_peft_safetensors_roundtrip(tmp_path):
     lw2.load_safetensors(str(tmp_path / "adapter.safetensors"))
     for k in lw.adapters:
         assert torch.equal(lw.adapters[k].A, lw2.adapters[k].A) and torch.equal(lw.adapters[k].B, lw2.adapters[k].B)
+
+
+def test_activation_checkpointing_gives_the_same_gradients():
+    from mary_b200.models.gemma4 import Gemma4Model, Gemma4TextConfig
+    from mary_b200.models.gemma4.weights import init_random_
+    from mary_b200.train.lora import Gemma4LoraForward, LoraWeights
+    cfg = Gemma4TextConfig(hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                           intermediate_size=128, vocab_size=100, sliding_window=8)
+    m = Gemma4Model(cfg)
+    init_random_(m, 0, std=0.1)
+    ids = torch.randint(0, 100, (2, 20))
+    grads = []
+    for ck in (False, True):
+        lw = LoraWeights.init_gemma4(m, rank=4, seed=1)
+        for a in lw.adapters.values():
+            a.B.data.normal_(0, 0.05, generator=torch.Generator().manual_seed(2))
+        f = Gemma4LoraForward(m, lw)
+        f.checkpoint = ck
+        f.loss(ids).backward()
+        grads.append(torch.cat([p.grad.flatten() for p in lw.parameters()]))
+    assert torch.allclose(grads[0], grads[1], atol=1e-6)
