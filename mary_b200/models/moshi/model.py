@@ -1,0 +1,261 @@
+"""Full-duplex speech LM of the Moshi family: a temporal transformer over frames (one position = one 12.5 Hz frame of
+17 token streams: text, 8 agent audio codebooks, 8 user audio codebooks), a depth transformer that emits the audio
+codebooks of a frame one after the other, and the delay machine that staggers the streams.
+
+Reference: dimensions and conventions src/models/personaplex/config.rs:17-80 (temporal 32 x 4096 full MHA, gated SiLU FFN
+11264, RMSNorm eps 1e-8, interleaved RoPE; depformer 6 x 1024, 16 heads, FFN 2816, PER-STEP weights for 16 steps); the
+stream bookkeeping src/models/personaplex/lmgen.rs:1-26,75-190 (ring of ``max_delay + 3`` positions per stream, caller
+tokens written at ``offset + delay`` and flagged provided, initial tokens seeded while ``offset <= delay``, the model fed
+position ``offset - 1``, sampled tokens written at ``offset`` where nothing was provided, the undelayed frame emitted once
+``offset > max_delay``).  The reference runs the temporal step through per-op kernels (q8 / f16 matvec, fused add+RMSNorm,
+RoPE + cache write, split-KV attention: src/models/personaplex/temporal_metal.rs:133-454) and the depformer through another
+set (src/models/personaplex/depth_gpu.rs:111-308); here the temporal transformer is the package's paged-cache decoder
+(``models.mistral``; interleaved RoPE is converted to split-half by permuting the q / k weight rows at load) and the depformer
+steps are GEMMs of its per-step weight slices with a 16-position cache."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import nn
+
+from ... import ops
+from ...ops import reference as ref
+from ...runtime.batch import BatchMeta
+from ...runtime.kv_cache import PagedKVCache
+from ..mistral.model import MistralConfig, MistralModel
+
+UNGENERATED = -2
+
+
+@dataclass
+class MoshiConfig:
+    dim: int = 4096
+    layers: int = 32
+    heads: int = 32
+    ffn: int = 11264
+    context: int = 3000
+    eps: float = 1e-8
+    rope_theta: float = 10000.0
+    text_card: int = 32000
+    card: int = 2048
+    dep_dim: int = 1024
+    dep_layers: int = 6
+    dep_heads: int = 16
+    dep_ffn: int = 2816
+    dep_q: int = 16                               # audio codebooks the depformer emits (agent 8 + user 8)
+    codebooks_per_stream: int = 8
+
+    @property
+    def num_streams(self) -> int:
+        return 1 + self.dep_q
+
+    @property
+    def delays(self) -> list[int]:
+        """Text and the semantic codebook of each audio stream are undelayed, the acoustic codebooks lag one frame."""
+        per = [0] + [1] * (self.codebooks_per_stream - 1)
+        return [0] + per * (self.dep_q // self.codebooks_per_stream)
+
+    @property
+    def max_delay(self) -> int:
+        return max(self.delays)
+
+    def initial(self, k: int) -> int:
+        return self.text_card if k == 0 else self.card
+
+    @staticmethod
+    def tiny():
+        return MoshiConfig(dim=64, layers=2, heads=4, ffn=96, context=64, text_card=50, card=24, dep_dim=32, dep_layers=2, dep_heads=4,
+                           dep_ffn=48, dep_q=4, codebooks_per_stream=2)
+
+    def temporal_cfg(self):
+        return MistralConfig(self.layers, self.dim, self.ffn, self.heads, self.heads, self.dim // self.heads, 1, self.rope_theta, self.eps,
+                             self.context, tie_word_embeddings=True, qk_norm=False, name="moshi-temporal")
+
+
+class StreamCache:
+    """The token bookkeeping of one conversation: pure integers, no tensors."""
+
+    def __init__(self, c: MoshiConfig):
+        self.c = c
+        self.ct = c.max_delay + 3
+        self.reset()
+
+    def reset(self):
+        n = self.c.num_streams
+        self.cache = [[UNGENERATED] * self.ct for _ in range(n)]
+        self.provided = [[False] * self.ct for _ in range(n)]
+        self.offset = 0
+
+    def prepare(self, user_audio=None, agent_audio=None, text=None):
+        """Write the caller's tokens of this frame, seed initial tokens, and return the step to run: ``None`` for the very first
+        call (offset 0 only seeds), else ``dict(input, target, provided, input_pos, target_pos)``."""
+        c, ct, o = self.c, self.ct, self.offset
+        d = c.delays
+        per = c.codebooks_per_stream
+
+        def put(k, t):
+            wp = (o + d[k]) % ct
+            self.cache[k][wp] = int(t)
+            self.provided[k][wp] = True
+        if user_audio is not None:
+            for q, t in enumerate(user_audio):
+                put(1 + per + q, t)
+        if agent_audio is not None:
+            for q, t in enumerate(agent_audio):
+                put(1 + q, t)
+        if text is not None:
+            put(0, text)
+        for k in range(c.num_streams):
+            if o <= d[k]:
+                self.cache[k][o % ct] = c.initial(k)
+                self.provided[k][o % ct] = True
+        if o == 0:
+            for k in range(c.num_streams):
+                self.cache[k][0] = c.initial(k)
+            self.offset += 1
+            return None
+        ip, tp = (o - 1) % ct, o % ct
+        return dict(input=[self.cache[k][ip] for k in range(c.num_streams)], target=[self.cache[k][tp] for k in range(c.num_streams)],
+                    provided=[self.provided[k][tp] for k in range(c.num_streams)], input_pos=ip, target_pos=tp)
+
+    def commit(self, p, sampled_text: int, sampled_audio):
+        """Clear the consumed flags, keep the sampled tokens where nothing was provided, emit the undelayed frame (all streams)
+        once past the delay horizon."""
+        c, ct = self.c, self.ct
+        for k in range(c.num_streams):
+            self.provided[k][p["input_pos"]] = False
+        if not self.provided[0][p["target_pos"]]:
+            self.cache[0][p["target_pos"]] = int(sampled_text)
+        for s, t in enumerate(sampled_audio):
+            if not self.provided[1 + s][p["target_pos"]]:
+                self.cache[1 + s][p["target_pos"]] = int(t)
+        out = None
+        if self.offset > c.max_delay:
+            out = [self.cache[k][(self.offset - c.max_delay + c.delays[k]) % ct] for k in range(c.num_streams)]
+        self.offset += 1
+        return out
+
+
+def _P(*shape, dtype=torch.float32, device="cpu"):
+    return nn.Parameter(torch.empty(*shape, dtype=dtype, device=device), requires_grad=False)
+
+
+class Depformer(nn.Module):
+    """Depth transformer with per-step weights: step ``t`` emits audio codebook ``t`` of the frame from the temporal hidden state
+    and the token chosen at step ``t - 1`` (the text token for ``t = 0``), attending to the earlier steps of the same frame."""
+
+    def __init__(self, c: MoshiConfig, dtype=torch.float32, device="cpu"):
+        super().__init__()
+        self.c = c
+        S, D, F = c.dep_q, c.dep_dim, c.dep_ffn
+        kw = dict(dtype=dtype, device=device)
+        self.w_in = _P(S, D, c.dim, **kw)                          # depformer_in.{t}
+        self.text_emb = _P(c.text_card + 1, D, **kw)               # step 0 is conditioned on the text token
+        self.audio_emb = _P(S - 1, c.card + 1, D, **kw)            # depformer_emb.{t-1}
+        self.norm1, self.norm2 = _P(c.dep_layers, D, **kw), _P(c.dep_layers, D, **kw)
+        self.w_qkv = _P(c.dep_layers, S, 3 * D, D, **kw)           # per-step slices of the fused in_proj
+        self.w_o = _P(c.dep_layers, S, D, D, **kw)
+        self.w_gu = _P(c.dep_layers, S, 2 * F, D, **kw)
+        self.w_down = _P(c.dep_layers, S, D, F, **kw)
+        self.heads = _P(S, c.card, D, **kw)                        # linears.{t}
+
+    def step(self, t: int, h_temporal, prev_token, cache):
+        """One codebook step for a batch of frames: ``h_temporal [B, dim]``, ``prev_token [B]``, ``cache`` = list per layer of
+        ``(k, v)`` over the steps so far (``None`` at ``t = 0``).  Returns ``(logits [B, card], cache)``."""
+        c = self.c
+        B = h_temporal.shape[0]
+        nh, hd = c.dep_heads, c.dep_dim // c.dep_heads
+        emb = ops.embed(prev_token.to(torch.int32), self.text_emb if t == 0 else self.audio_emb[t - 1])
+        x = ops.linear(h_temporal, self.w_in[t]) + emb
+        new_cache = []
+        for li in range(c.dep_layers):
+            h = ref.rmsnorm(x, self.norm1[li], c.eps)
+            q, k, v = ops.linear(h, self.w_qkv[li, t]).view(B, 3, nh, hd).unbind(1)
+            if cache is not None:
+                k, v = torch.cat([cache[li][0], k[:, None]], 1), torch.cat([cache[li][1], v[:, None]], 1)
+            else:
+                k, v = k[:, None], v[:, None]
+            new_cache.append((k, v))                                                   # [B, t + 1, nh, hd]
+            s = torch.einsum("bhd,bthd->bht", q.float(), k.float()) * hd ** -0.5
+            a = torch.einsum("bht,bthd->bhd", torch.softmax(s, -1), v.float()).reshape(B, c.dep_dim).to(x.dtype)
+            x = x + ops.linear(a, self.w_o[li, t])
+            h = ref.rmsnorm(x, self.norm2[li], c.eps)
+            x = x + ops.linear(ops.linear_glu(h, self.w_gu[li, t], "swiglu"), self.w_down[li, t])
+        return ops.linear(x, self.heads[t]).float(), new_cache
+
+    def generate(self, h_temporal, text_token, forced=None, sample=None):
+        """All ``dep_q`` codebooks of a frame.  ``forced[s]`` (or ``None``) teacher-forces step ``s``'s token into the chain;
+        ``sample(logits, s)`` picks a token (greedy when absent).  Returns tokens ``[B, dep_q]``."""
+        prev, cache, out = text_token, None, []
+        for t in range(self.c.dep_q):
+            logits, cache = self.step(t, h_temporal, prev, cache)
+            tok = sample(logits, t) if sample is not None else ref.argmax_first(logits)
+            out.append(tok)
+            prev = tok
+            if forced is not None and forced[t] is not None:
+                prev = torch.full_like(tok, int(forced[t]))
+        return torch.stack(out, 1)
+
+
+class LmGen(nn.Module):
+    """Temporal transformer + depformer + stream bookkeeping for one conversation (batch 1)."""
+
+    def __init__(self, c: MoshiConfig, dtype=torch.float32, device="cpu"):
+        super().__init__()
+        self.c = c
+        dev = torch.device(device)
+        self.temporal = MistralModel(c.temporal_cfg(), dtype=dtype, device=device)
+        kw = dict(dtype=dtype, device=device)
+        self.text_emb = _P(c.text_card + 1, c.dim, **kw)
+        self.audio_emb = _P(c.dep_q, c.card + 1, c.dim, **kw)
+        self.text_head = _P(c.text_card, c.dim, **kw)
+        self.depformer = Depformer(c, dtype, device)
+        self.stream = StreamCache(c)
+        spec = self.temporal.kv_spec()
+        pages = (c.context + 15) // 16
+        self.cache = PagedKVCache(spec["num_layers"], pages + 1, 16, spec["kv_heads"], spec["head_dim"], dtype=dtype, device=dev)
+        self.cache.alloc.extend(0, pages * 16)
+        self.table, _ = self.cache.alloc.page_table([0])
+        self.pos, self.dev = 0, dev
+
+    def reset_session(self):
+        self.stream.reset()
+        self.pos = 0
+
+    def embed_frame(self, tokens):
+        """Sum of the stream embeddings of one frame (``tokens``: one id per stream)."""
+        t = torch.as_tensor(tokens, dtype=torch.int32, device=self.dev)
+        e = ops.embed(t[:1], self.text_emb).float()
+        for s in range(self.c.dep_q):
+            e = e + ops.embed(t[1 + s:2 + s], self.audio_emb[s]).float()
+        return e.to(self.text_emb.dtype)
+
+    def step(self, user_audio=None, agent_audio=None, text=None, sample=None):
+        """One frame: returns the undelayed output frame (a list of ``num_streams`` token ids) once past the delay horizon,
+        else ``None``."""
+        p = self.stream.prepare(user_audio, agent_audio, text)
+        if p is None:
+            return None
+        if self.pos >= self.c.context:
+            raise RuntimeError("conversation longer than the attention context: start a new session")
+        with torch.no_grad():
+            x = self.embed_frame(p["input"])
+            self.pos += 1
+            meta = BatchMeta.build([1], [self.pos], self.table, 16, self.dev)
+            h = self.temporal.hidden_from_embeds(x, meta, self.cache)                    # [1, dim], final-normed
+            text_logits = ops.linear(h, self.text_head).float()
+            text_tok = sample(text_logits, -1) if sample is not None else ref.argmax_first(text_logits)
+            next_text = torch.full_like(text_tok, int(p["target"][0])) if p["provided"][0] else text_tok
+            forced = [p["target"][1 + s] if p["provided"][1 + s] else None for s in range(self.c.dep_q)]
+            audio = self.depformer.generate(h, next_text, forced, sample)[0]
+        return self.stream.commit(p, int(text_tok[0]), [int(a) for a in audio])
+
+
+def init_random_(m: LmGen, seed: int = 0, std: float = 0.08):
+    g = torch.Generator(device=m.text_emb.device).manual_seed(seed)
+    for n, p in m.named_parameters():
+        if p.dim() == 1 or n.endswith(("norm1", "norm2")):
+            p.data.fill_(1.0)
+        else:
+            p.data.normal_(0.0, std, generator=g)

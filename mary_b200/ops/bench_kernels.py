@@ -85,10 +85,13 @@ def bench_attn(cases=None):
         q = torch.randn(B, Hq, D, device="cuda").bfloat16()
         span = L if win == 0 else min(L, win)
         for kernel in ("general", "decode"):
-            ms = time_op(lambda: K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, win, kernel=kernel))
-            gb = B * span * Hkv * D * 2 * 2 / ms / 1e6
-            print(f"decode attn [{kernel}] B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, {gb:.0f} GB/s, "
-                  f"{gb / hbm:.2f} {tag}")
+            for ctas in ((592,) if kernel == "general" else (592, 1184, 2368, 4736)):
+                K.DECODE_TARGET_CTAS = ctas
+                ms = time_op(lambda: K.paged_attention(q, cache.k[0], cache.v[0], meta, D ** -0.5, win, kernel=kernel))
+                gb = B * span * Hkv * D * 2 * 2 / ms / 1e6
+                print(f"decode attn [{kernel}, target {ctas} CTAs] B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, "
+                      f"{gb:.0f} GB/s, {gb / hbm:.2f} {tag}")
+        K.DECODE_TARGET_CTAS = 592
 
 
 def bench_fa(B: int = 1, L: int = 4096, Hq: int = 16, Hkv: int = 16, DK: int = 192, DV: int = 128, window: int = 0, iters: int = 5):

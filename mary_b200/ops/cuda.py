@@ -278,6 +278,9 @@ def _q_blocks(meta, rq: int):
 declare("mary_paged_attention_decode", "ppppppppp" + "iii" + "llll" + "iiiiii" + "ff" + "ps")
 
 
+DECODE_TARGET_CTAS = 592       # CTAs the decode attention kernel aims for when it picks the number of kv splits
+
+
 def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsplit):
     """Decode-shaped batches (few rows per kv head, equal K and V widths of 64/128/256): the bandwidth-oriented kernel."""
     T, Hq, D = q.shape
@@ -287,7 +290,7 @@ def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsp
     rq = max(1, min(cap // G, meta.max_q_len))
     blk_seq, blk_q0, NB = _q_blocks(meta, rq)
     if nsplit is None:
-        want = max(1, 592 // max(1, NB * Hkv))
+        want = max(1, DECODE_TARGET_CTAS // max(1, NB * Hkv))
         span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
         nsplit = max(1, min(want, 32, span // 64))
     out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)

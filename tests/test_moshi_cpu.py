@@ -1,0 +1,78 @@
+"""Moshi-style speech LM: the stream delay machine, the per-step depformer, and the frame loop."""
+import torch
+
+from mary_b200.models.moshi import LmGen, MoshiConfig, StreamCache, init_random_
+
+
+def test_stream_cache_delays_forcing_and_undelayed_output():
+    c = MoshiConfig.tiny()                       # streams: text, agent (semantic, acoustic), user (semantic, acoustic)
+    assert c.delays == [0, 0, 1, 0, 1] and c.max_delay == 1 and c.num_streams == 5
+    sc = StreamCache(c)
+    assert sc.prepare(user_audio=[7, 8]) is None and sc.offset == 1             # offset 0 only seeds
+    assert [row[0] for row in sc.cache] == [c.text_card, c.card, c.card, c.card, c.card]
+    outs = []
+    for f in range(1, 6):
+        p = sc.prepare(user_audio=[10 + f, 20 + f])
+        # user semantic (stream 3, delay 0) is provided at the target position now; user acoustic (stream 4, delay 1) lands one ahead
+        assert p["provided"][3] and p["target"][3] == 10 + f
+        if f == 1:
+            assert p["input"] == [c.text_card] + [c.card] * 4                   # the seeded initial tokens are fed first
+            assert p["provided"][2] and p["target"][2] == c.card                # delayed streams get their initial token at offset <= delay
+        if f >= 2:
+            assert p["provided"][4] and p["target"][4] == 20 + f - 1            # what the caller gave one frame earlier
+        out = sc.commit(p, sampled_text=100 + f, sampled_audio=[200 + f, 300 + f, 400 + f, 500 + f])
+        outs.append(out)
+    assert outs[0] is None and outs[1] is not None                              # emission starts once offset > max_delay
+    # undelayed frame at offset o: stream k shows what sits at (o - max_delay + delay_k); provided tokens win over sampled ones
+    o = outs[3]                                                                 # produced at offset 4: base position 3
+    assert o[0] == 103 and o[1] == 203 and o[2] == 304                          # acoustic agent codebook taken one position later
+    assert o[3] == 13 and o[4] == 23                                            # user tokens: provided values, re-aligned
+    sc.reset()
+    assert sc.offset == 0 and all(v == -2 for row in sc.cache for v in row)
+
+
+def test_depformer_forcing_changes_only_later_steps_and_cache_matches_recompute():
+    c = MoshiConfig.tiny()
+    m = LmGen(c)
+    init_random_(m, 0)
+    torch.manual_seed(1)
+    h = torch.randn(2, c.dim)
+    text = torch.tensor([3, 9])
+    with torch.no_grad():
+        free = m.depformer.generate(h, text)
+        forced = m.depformer.generate(h, text, forced=[None, 5, None, None])
+        assert torch.equal(free[:, :2], forced[:, :2])                          # step 1's own OUTPUT is not changed by forcing its token
+        # cached steps equal recomputing the prefix from scratch
+        prev, cache, toks = text, None, []
+        for t in range(c.dep_q):
+            lg, cache = m.depformer.step(t, h, prev, cache)
+            prev2, cache2 = text, None
+            for u in range(t + 1):
+                lg2, cache2 = m.depformer.step(u, h, prev2, cache2)
+                prev2 = lg2.argmax(-1)
+            assert torch.allclose(lg, lg2, atol=1e-5)
+            prev = lg.argmax(-1)
+            toks.append(prev)
+        assert torch.equal(torch.stack(toks, 1), free)
+
+
+def test_frame_loop_is_deterministic_and_respects_provided_tokens():
+    c = MoshiConfig.tiny()
+    runs = []
+    for _ in range(2):
+        m = LmGen(c)
+        init_random_(m, 0)
+        outs = []
+        for f in range(8):
+            outs.append(m.step(user_audio=[(3 * f) % c.card, (5 * f + 1) % c.card], text=7 if f == 4 else None))
+        runs.append(outs)
+    assert runs[0] == runs[1]
+    frames = [o for o in runs[0] if o is not None]
+    assert len(frames) == 8 - 1 - c.max_delay
+    for i, o in enumerate(frames):
+        f = i + 1                                                               # frame whose tokens are emitted
+        assert o[3] == (3 * f) % c.card and o[4] == (5 * f + 1) % c.card       # user streams come back exactly as provided
+        assert 0 <= o[1] < c.card and 0 <= o[2] < c.card
+    assert frames[3][0] == 7                                                    # the forced text token of frame 4
+    m.reset_session()
+    assert m.step(user_audio=[0, 1]) is None
