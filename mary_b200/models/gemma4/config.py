@@ -24,7 +24,8 @@ class Gemma4TextConfig:
     tie_word_embeddings: bool = True
     global_head_dim: int | None = None
     num_global_key_value_heads: int | None = None
-    attention_k_eq_v: bool = False
+    attention_k_eq_v: bool = False      # full-attention layers have no v_proj: k and v come from one projection
+    num_kv_shared_layers: int = 0       # the last layers compute no K/V and read the cache of an earlier layer
     apply_sliding_window: bool = True   # the reference's text path never applies the window (layers.rs:210-234
     #                                     has no caller); it is applied here and can be switched off for parity
     max_position_embeddings: int = 131072
@@ -35,6 +36,21 @@ class Gemma4TextConfig:
                                 for i in range(self.num_hidden_layers)]
         if len(self.layer_types) != self.num_hidden_layers:
             raise ValueError("layer_types must have one entry per layer")
+
+    @property
+    def first_shared_kv_layer(self) -> int:
+        return self.num_hidden_layers - self.num_kv_shared_layers
+
+    def kv_source(self, i: int) -> int | None:
+        """The layer whose cache layer ``i`` reads, or ``None`` when it keeps its own: shared sliding layers use layer
+        ``first_shared - 2``, shared full-attention layers ``first_shared - 1`` (src/models/gemma/gemma4/decoder.rs:230-261)."""
+        fs = self.first_shared_kv_layer
+        if i < fs or self.num_kv_shared_layers == 0:
+            return None
+        return fs - 2 if self.is_sliding(i) else fs - 1
+
+    def k_eq_v(self, i: int) -> bool:
+        return self.attention_k_eq_v and not self.is_sliding(i)
 
     def is_sliding(self, i: int) -> bool:
         return self.layer_types[i] == "sliding_attention"
@@ -66,7 +82,7 @@ class Gemma4TextConfig:
             final_logit_softcapping=float(d.get("final_logit_softcapping") or 30.0),
             tie_word_embeddings=bool(d.get("tie_word_embeddings", True)),
             global_head_dim=d.get("global_head_dim"), num_global_key_value_heads=d.get("num_global_key_value_heads"),
-            attention_k_eq_v=bool(d.get("attention_k_eq_v", False)),
+            attention_k_eq_v=bool(d.get("attention_k_eq_v", False)), num_kv_shared_layers=int(d.get("num_kv_shared_layers", 0)),
             apply_sliding_window=bool(d.get("apply_sliding_window", True)),
             max_position_embeddings=d.get("max_position_embeddings", 131072))
 
@@ -81,6 +97,8 @@ class Gemma4TextConfig:
                                                    "partial_rotary_factor": self.partial_rotary_factor_global}},
             "rms_norm_eps": self.rms_norm_eps, "final_logit_softcapping": self.final_logit_softcapping,
             "tie_word_embeddings": self.tie_word_embeddings, "apply_sliding_window": self.apply_sliding_window,
+            "attention_k_eq_v": self.attention_k_eq_v, "num_kv_shared_layers": self.num_kv_shared_layers,
+            "global_head_dim": self.global_head_dim, "num_global_key_value_heads": self.num_global_key_value_heads,
             "max_position_embeddings": self.max_position_embeddings}
 
 

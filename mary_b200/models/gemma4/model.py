@@ -39,11 +39,14 @@ class Gemma4Layer(nn.Module):
         self.D = D
         self.n_q = cfg.num_attention_heads // self.tp.size
         self.n_kv = max(cfg.layer_kv_heads(i) // self.tp.size, 1)
+        # a KV-shared layer projects queries only and attends to the cache its source layer filled
+        self.kv_source = cfg.kv_source(i)
+        self.cache_layer = i if self.kv_source is None else self.kv_source
         F = cfg.intermediate_size // self.tp.size
         self.F = F
         kw = dict(dtype=dtype, device=device)
         P = lambda *s: nn.Parameter(torch.empty(*s, **kw), requires_grad=False)  # noqa: E731
-        self.w_qkv = P((self.n_q + 2 * self.n_kv) * D, H)
+        self.w_qkv = P((self.n_q + (2 * self.n_kv if self.kv_source is None else 0)) * D, H)
         self.w_o = P(H, self.n_q * D)
         self.w_gu = P(2 * F, H)
         self.w_down = P(H, F)
@@ -64,9 +67,10 @@ class Gemma4Layer(nn.Module):
         qkv = ops.linear(x, self.w_qkv)
         if "qkv" in L:
             qkv = qkv + L["qkv"](x)
-        q = ops.qk_norm_rope_append(qkv, self.n_q, self.n_kv, self.D, self.q_norm, self.k_norm, True, self.inv_freq,
-                                    meta, cache.k[self.i], cache.v[self.i], c.rms_norm_eps)
-        o = ops.paged_attention(q, cache.k[self.i], cache.v[self.i], meta, 1.0, self.window)
+        ci = self.cache_layer
+        q = ops.qk_norm_rope_append(qkv, self.n_q, self.n_kv if self.kv_source is None else 0, self.D, self.q_norm, self.k_norm, True,
+                                    self.inv_freq, meta, cache.k[ci], cache.v[ci], c.rms_norm_eps)
+        o = ops.paged_attention(q, cache.k[ci], cache.v[ci], meta, 1.0, self.window)
         o = o.reshape(o.shape[0], -1)
         sp = getattr(self.tp, "sp", None)
         if sp is not None and x.is_cuda and not L:

@@ -26,10 +26,13 @@ def tensor_names(cfg: Gemma4TextConfig) -> dict[str, tuple]:
         out.update({
             p + "input_layernorm.weight": (H,), p + "post_attention_layernorm.weight": (H,),
             p + "pre_feedforward_layernorm.weight": (H,), p + "post_feedforward_layernorm.weight": (H,),
-            p + "self_attn.q_proj.weight": (Hq * D, H), p + "self_attn.k_proj.weight": (Hkv * D, H),
-            p + "self_attn.v_proj.weight": (Hkv * D, H), p + "self_attn.o_proj.weight": (H, Hq * D),
-            p + "self_attn.q_norm.weight": (D,), p + "self_attn.k_norm.weight": (D,),
+            p + "self_attn.q_proj.weight": (Hq * D, H), p + "self_attn.o_proj.weight": (H, Hq * D),
+            p + "self_attn.q_norm.weight": (D,),
             p + "mlp.gate_proj.weight": (F, H), p + "mlp.up_proj.weight": (F, H), p + "mlp.down_proj.weight": (H, F)})
+        if cfg.kv_source(i) is None:                     # KV-shared layers carry no K/V tensors; K=V layers carry no v_proj
+            out.update({p + "self_attn.k_proj.weight": (Hkv * D, H), p + "self_attn.k_norm.weight": (D,)})
+            if not cfg.k_eq_v(i):
+                out[p + "self_attn.v_proj.weight"] = (Hkv * D, H)
     if not cfg.tie_word_embeddings:
         out["lm_head.weight"] = (V, H)
     return out
@@ -83,19 +86,27 @@ def load_into(model, loader, device=None) -> None:
         D = cfg.layer_head_dim(i)
         r, n = tp.rank, tp.size
         q = get(p + "self_attn.q_proj.weight").view(cfg.num_attention_heads, D, -1)
-        k = get(p + "self_attn.k_proj.weight").view(cfg.layer_kv_heads(i), D, -1)
-        v = get(p + "self_attn.v_proj.weight").view(cfg.layer_kv_heads(i), D, -1)
         qs = q[r * L.n_q:(r + 1) * L.n_q]
-        kv0 = (r * cfg.layer_kv_heads(i)) // n if cfg.layer_kv_heads(i) >= n else 0
-        ks, vs = k[kv0:kv0 + L.n_kv], v[kv0:kv0 + L.n_kv]
-        put(L.w_qkv, torch.cat([qs.reshape(-1, q.shape[-1]), ks.reshape(-1, k.shape[-1]), vs.reshape(-1, v.shape[-1])], 0))
+        if L.kv_source is None:
+            k = get(p + "self_attn.k_proj.weight").view(cfg.layer_kv_heads(i), D, -1)
+            # K = V layers ship no v_proj: v is the same projection as k (before the norms)
+            v = k if cfg.k_eq_v(i) and not loader.has_weight(pre + p + "self_attn.v_proj.weight") \
+                else get(p + "self_attn.v_proj.weight").view(cfg.layer_kv_heads(i), D, -1)
+            kv0 = (r * cfg.layer_kv_heads(i)) // n if cfg.layer_kv_heads(i) >= n else 0
+            ks, vs = k[kv0:kv0 + L.n_kv], v[kv0:kv0 + L.n_kv]
+            put(L.w_qkv, torch.cat([qs.reshape(-1, q.shape[-1]), ks.reshape(-1, k.shape[-1]), vs.reshape(-1, v.shape[-1])], 0))
+        else:
+            put(L.w_qkv, qs.reshape(-1, q.shape[-1]))
         o = get(p + "self_attn.o_proj.weight")
         put(L.w_o, o[:, r * L.n_q * D:(r + 1) * L.n_q * D])
         g, u = get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")
         put(L.w_gu, torch.cat([g[r * L.F:(r + 1) * L.F], u[r * L.F:(r + 1) * L.F]], 0))
         put(L.w_down, get(p + "mlp.down_proj.weight")[:, r * L.F:(r + 1) * L.F])
         put(L.q_norm, get(p + "self_attn.q_norm.weight"))
-        put(L.k_norm, get(p + "self_attn.k_norm.weight"))
+        if L.kv_source is None:
+            put(L.k_norm, get(p + "self_attn.k_norm.weight"))
+        else:
+            L.k_norm.data.fill_(1.0)
         put(L.ln_in, get(p + "input_layernorm.weight"))
         put(L.ln_post_attn, get(p + "post_attention_layernorm.weight"))
         put(L.ln_pre_ffn, get(p + "pre_feedforward_layernorm.weight"))

@@ -55,6 +55,9 @@ def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm: bool, 
     T = qkv.shape[0]
     q, k, v = qkv.split([n_q * head_dim, n_kv * head_dim, n_kv * head_dim], dim=-1)
     q, k, v = q.reshape(T, n_q, head_dim), k.reshape(T, n_kv, head_dim), v.reshape(T, n_kv, head_dim)
+    if n_kv == 0:                                  # queries only (a layer that reads another layer's cache)
+        q = ref.rmsnorm(q, q_norm, eps) if q_norm is not None else q
+        return ref.rope(q, meta.positions, inv_freq) if inv_freq is not None else q
     if q_norm is not None:
         q = ref.rmsnorm(q, q_norm, eps)
     if k_norm is not None:

@@ -60,16 +60,21 @@ class Gemma4Oracle:
             D, Hq, Hkv = c.layer_head_dim(i), c.num_attention_heads, c.layer_kv_heads(i)
             x = rms(h, w[p + "input_layernorm.weight"], c.rms_norm_eps)
             q = (x @ w[p + "self_attn.q_proj.weight"].T).reshape(S, Hq, D)
-            k = (x @ w[p + "self_attn.k_proj.weight"].T).reshape(S, Hkv, D)
-            v = (x @ w[p + "self_attn.v_proj.weight"].T).reshape(S, Hkv, D)
             q = rms(q, w[p + "self_attn.q_norm.weight"], c.rms_norm_eps)
-            k = rms(k, w[p + "self_attn.k_norm.weight"], c.rms_norm_eps)
-            v = rms(v, None, c.rms_norm_eps)
             sliding = c.is_sliding(i)
             f = inv_freq(D, c.rope_theta_local) if sliding else inv_freq(D, c.rope_theta_global, c.partial_rotary_factor_global)
-            q, k = rope(q, pos, f), rope(k, pos, f)
-            self.kc[i] = k if self.kc[i] is None else np.concatenate([self.kc[i], k], 0)
-            self.vc[i] = v if self.vc[i] is None else np.concatenate([self.vc[i], v], 0)
+            q = rope(q, pos, f)
+            src = c.kv_source(i)
+            if src is None:
+                k = (x @ w[p + "self_attn.k_proj.weight"].T).reshape(S, Hkv, D)
+                vname = p + "self_attn.v_proj.weight"
+                v = k.copy() if (c.k_eq_v(i) and vname not in w) else (x @ w[vname].T).reshape(S, Hkv, D)
+                k = rope(rms(k, w[p + "self_attn.k_norm.weight"], c.rms_norm_eps), pos, f)
+                v = rms(v, None, c.rms_norm_eps)
+                self.kc[i] = k if self.kc[i] is None else np.concatenate([self.kc[i], k], 0)
+                self.vc[i] = v if self.vc[i] is None else np.concatenate([self.vc[i], v], 0)
+            else:                                   # KV-shared layer: the source layer's keys and values, this layer's queries
+                self.kc[i], self.vc[i] = self.kc[src], self.vc[src]
             K, V = np.repeat(self.kc[i], Hq // Hkv, axis=1), np.repeat(self.vc[i], Hq // Hkv, axis=1)
             sc = np.einsum("nhd,lhd->hnl", q, K)                       # scale 1.0
             kpos = np.arange(K.shape[0])

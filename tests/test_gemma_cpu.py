@@ -88,3 +88,37 @@ def test_sliding_window_reach_property():
     out = ref.paged_attention(q, cache.k[0], cache.v[0], meta, 1.0, window=W)
     d = (out - base).abs().amax(dim=(0, 2))
     assert d[0] == 0 and d[1] == 0 and d[2] > 0 and d[3] > 0
+
+
+def test_kv_shared_and_k_eq_v_layers_match_oracle(tmp_path):
+    """The last layers read the cache of an earlier layer (no K/V projections of their own) and full-attention layers take keys
+    and values from one projection (no v_proj tensor): token-exact and within 1e-4 against the NumPy oracle, through a pile."""
+    from mary_b200.models.gemma4 import Gemma4TextConfig
+    from mary_b200.pile import Pile, signing_key_file
+    lt = ["sliding_attention", "full_attention"] * 3
+    cfg = Gemma4TextConfig(hidden_size=128, num_hidden_layers=6, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                           intermediate_size=256, vocab_size=512, layer_types=lt, sliding_window=8, attention_k_eq_v=True,
+                           num_kv_shared_layers=2)
+    assert [cfg.kv_source(i) for i in range(6)] == [None, None, None, None, 2, 3]
+    assert [cfg.k_eq_v(i) for i in range(6)] == [False, True] * 3
+    w = dict(random_weights(cfg, 1, std=0.08))
+    assert "model.layers.1.self_attn.v_proj.weight" not in w and "model.layers.0.self_attn.v_proj.weight" in w
+    assert "model.layers.4.self_attn.k_proj.weight" not in w and "model.layers.5.self_attn.k_norm.weight" not in w
+    p = Pile.open(str(tmp_path / "g.pile"))
+    write_random_pile(p, signing_key_file(str(tmp_path / "k")), cfg, seed=1, std=0.08) if "std" in write_random_pile.__code__.co_varnames \
+        else write_random_pile(p, signing_key_file(str(tmp_path / "k")), cfg, seed=1)
+    p.close()
+    lm = GemmaLM.from_pile(str(tmp_path / "g.pile"))
+    assert lm.model.cfg.num_kv_shared_layers == 2 and lm.model.cfg.attention_k_eq_v
+    std = 0.08 if "std" in write_random_pile.__code__.co_varnames else 0.02
+    orc = Gemma4Oracle(cfg, dict(random_weights(cfg, 1, std=std)))
+    prompt = np.random.default_rng(2).integers(0, 512, 21).tolist()
+    ref_tokens, _ = Gemma4Oracle(cfg, dict(random_weights(cfg, 1, std=std))).generate(prompt, 12)
+    assert lm.complete_ids(prompt, 12) == ref_tokens
+    ref = orc.forward(prompt)
+    lm2 = GemmaLM.from_pile(str(tmp_path / "g.pile"))
+    cache = lm2.cache
+    cache.alloc.extend(7, len(prompt))
+    table, lens = cache.alloc.page_table([7])
+    got = lm2.model(torch.tensor(prompt), BatchMeta.build([len(prompt)], lens, table, cache.page_size), cache).numpy()
+    assert np.abs(got - ref).max() / np.abs(ref).max() < 1e-4
