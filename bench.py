@@ -191,6 +191,7 @@ def main():
     if a2a:
         from mary_b200.parallel.ep import distributed_factory
         par.ep_factory = distributed_factory(rank, world, dev, t_cap=B_local * (1 + k))
+        par.ep_decode_cap, par.ep_prefill_cap = B_local * (1 + k), args.prefill_chunk
 
     # ---------------------------------------------------------------- model
     t0 = time.time()
@@ -346,7 +347,7 @@ def main():
 
     # ---------------------------------------------------------------- TTFT: a real prefill of one context
     ttft = None
-    if not args.no_ttft and not a2a:
+    if not args.no_ttft:          # in the all-to-all layout every rank prefills one context of its own at the same time
         try:
             pc = PagedKVCache(spec["num_layers"], (ctx + 64) // page + 2, page, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16,
                               device=dev, latent_dim=spec.get("latent_dim"))
@@ -384,6 +385,7 @@ def main():
                        "accepted_drafts_per_step": round(tok_per_seq_step - 1, 4)},
             "tpot_ms_p50": round(ms / args.steps / max(tok_per_seq_step, 1e-9), 4),
             "ttft_ms_p50_one_context": ttft,
+            "ttft_note": (f"{world} contexts prefilled concurrently, one per rank" if a2a else "one context, all ranks"),
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": B * R * 4,
                     "d2h_bytes_per_step": B * R * 4 * 2 + B * 4},

@@ -149,11 +149,16 @@ class MoEFFN(nn.Module):
         idx, w = self.route(x)
         if self.par.ep_mode == "a2a" and self.par.ep_size > 1:
             # tokens are local: routed experts through the all-to-all (global expert ids), shared expert computed at home
-            if self.ep_layer is None:
+            big = x.shape[0] > getattr(self.par, "ep_decode_cap", 1 << 30)
+            if big:
+                # prefill-sized batches get slabs of their own (and 128-row token tiles) next to the decode-sized ones
+                if getattr(self, "ep_layer_big", None) is None:
+                    self.ep_layer_big = self.par.ep_factory(self.experts, self.c, self.par.ep_prefill_cap, 128)
+            elif self.ep_layer is None:
                 self.ep_layer = self.par.ep_factory(self.experts, self.c)
             shared = ops.linear(ops.linear_glu(x, self.shared.w_gu, self.c.act), self.shared.w_down) if self.shared is not None else None
             # an NVFP4 shared expert sits behind the local routed ones on every rank; the EP layer serves it in the same launches
-            return self.ep_layer.forward(x, idx, w, shared)
+            return (self.ep_layer_big if big else self.ep_layer).forward(x, idx, w, shared)
         if self.par.ep_size > 1:              # keep the entries of the local experts, renumbered from zero
             local = (idx >= self.e0) & (idx < self.e0 + self.e_local)
             idx = torch.where(local, idx - self.e0, torch.full_like(idx, -1))

@@ -164,13 +164,18 @@ def distributed_factory(rank: int, world: int, device, t_cap: int, nt: int = 32,
     import torch.distributed._symmetric_memory as symm_mem
     state = {}
 
-    def factory(experts, cfg):
-        if "bufs" not in state:
+    def factory(experts, cfg, t_cap_override: int | None = None, nt_override: int | None = None):
+        """``t_cap_override`` / ``nt_override`` build a second set of slabs for another batch shape (prefill chunks next to decode
+        steps): every rank must ask for the same shapes in the same order."""
+        tc, tile = t_cap_override or t_cap, nt_override or nt
+        key = (tc, tile)
+        st = state.setdefault(key, {})
+        if "bufs" not in st:
             def alloc(n, dt):
                 t = symm_mem.empty(n, dtype=dt, device=device)
                 t.zero_()
                 return t
-            b = EPBuffers(world, cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, t_cap, cfg.num_experts_per_tok, nt,
+            b = EPBuffers(world, cfg.n_routed_experts, cfg.hidden_size, cfg.moe_intermediate_size, tc, cfg.num_experts_per_tok, tile,
                           device, alloc, shared=bool(cfg.shared_expert_nvfp4 and cfg.n_shared_experts == 1))
             peers = [types.SimpleNamespace() for _ in range(world)]
             for name in ("count_mat", "xq", "sf", "meta", "comb"):
@@ -179,16 +184,18 @@ def distributed_factory(rank: int, world: int, device, t_cap: int, nt: int = 32,
                     setattr(peers[r], name, int(hdl.buffer_ptrs[r]))
             sp = sig_ptrs
             if sp is None:
-                flags = symm_mem.empty(1024, dtype=torch.int32, device=device)
-                flags.zero_()
-                fh = symm_mem.rendezvous(flags, dist.group.WORLD)
-                sp = (ctypes.c_uint64 * 8)(*list(fh.buffer_ptrs)[:world])
-                state["flags"] = flags
+                if "sig" not in state:
+                    flags = symm_mem.empty(1024, dtype=torch.int32, device=device)
+                    flags.zero_()
+                    fh = symm_mem.rendezvous(flags, dist.group.WORLD)
+                    state["sig"] = (ctypes.c_uint64 * 8)(*list(fh.buffer_ptrs)[:world])
+                    state["flags"] = flags
+                sp = state["sig"]
             torch.cuda.synchronize()
             dist.barrier()
-            state.update(bufs=b, peers=peers, sig=sp, shared_layer_state={})
-        layer = EPLayer(rank, world, experts, state["bufs"], state["peers"], state["sig"], wait_ns)
-        # one epoch word for all layers: they share the flag slots
+            st.update(bufs=b, peers=peers, sig=sp)
+        layer = EPLayer(rank, world, experts, st["bufs"], st["peers"], st["sig"], wait_ns)
+        # one epoch word for all layers and shapes: they share the flag slots
         if "epoch_slot" not in state:
             state["epoch_slot"] = layer.epoch_slot
         layer.epoch_slot = state["epoch_slot"]

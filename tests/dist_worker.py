@@ -101,6 +101,9 @@ def main():
             init_random_(full, 0)
             par = ParallelGroup(rank, world, "nccl", ep_mode="a2a")
             par.ep_factory = distributed_factory(rank, world, dev, t_cap=64)
+            if shared_fp4:
+                # batches above the decode capacity take the prefill-sized slabs (128-row token tiles) built on demand
+                par.ep_decode_cap, par.ep_prefill_cap = 16, 64
             shard = shard_from_full(full, par)
             ids = torch.arange(1, 40, dtype=torch.int32, device=dev)
             outs = []
