@@ -45,6 +45,7 @@ __device__ __forceinline__ void unpack(const typename Vec<E>::T& v, float* f) {
 template <int D, int RMAX>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(const DecParams p) {
+  pdl_sync();
   constexpr int E = D / 32;
   using V = typename Vec<E>::T;
   __shared__ float red_o[WARPS][RMAX][D];
@@ -199,6 +200,7 @@ attn_decode_kernel(const DecParams p) {
 }
 
 __global__ void attn_decode_combine_kernel(const DecParams p, int D) {
+  pdl_sync();
   const int nb = blockIdx.x, kvh = blockIdx.y;
   const int seq = p.blk_seq[nb], row0 = p.blk_q0[nb];
   const int nq = min(p.RQ, p.q_start[seq + 1] - row0);
@@ -223,10 +225,10 @@ __global__ void attn_decode_combine_kernel(const DecParams p, int D) {
 
 template <int D, int RMAX>
 int launch(const DecParams& p, int NB, cudaStream_t s) {
-  attn_decode_kernel<D, RMAX><<<dim3(NB, p.Hkv, p.nsplit), WARPS * 32, 0, s>>>(p);
+  MARY_LAUNCH((attn_decode_kernel<D, RMAX>), dim3(NB, p.Hkv, p.nsplit), WARPS * 32, 0, s, p);
   MARY_CHECK_LAUNCH();
   if (p.nsplit > 1) {
-    attn_decode_combine_kernel<<<dim3(NB, p.Hkv), 256, 0, s>>>(p, D);
+    MARY_LAUNCH(attn_decode_combine_kernel, dim3(NB, p.Hkv), 256, 0, s, p, D);
     MARY_CHECK_LAUNCH();
   }
   return MARY_OK;

@@ -73,6 +73,7 @@ __device__ __forceinline__ uint64_t desc_mnmajor_sw128(uint32_t addr, uint32_t l
 
 __global__ void __launch_bounds__(NTHREADS, 1)
 mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_kv, const MlaParams p) {
+  pdl_sync();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -334,6 +335,7 @@ done:
 
 // Merge split partials: exponents are in the log2 domain.
 __global__ void mla_combine_kernel(const MlaParams p, int NB) {
+  pdl_sync();
   const int nb = blockIdx.x, r = blockIdx.y;
   const int seq = p.blk_seq[nb], row0 = p.blk_row0[nb];
   const int nrows = min(TR, p.q_start[seq + 1] * p.Hq - row0);
@@ -409,10 +411,10 @@ MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, con
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_row0 = blk_row0;
   p.out = (__nv_bfloat16*)out; p.part_o = scratch; p.part_ml = scratch ? scratch + (int64_t)NB * nsplit * TR * DV : nullptr;
   p.max_pages = max_pages; p.Hq = Hq; p.nsplit = nsplit; p.page = page_size; p.scale_log2 = scale * 1.4426950408889634f; p.status = mary_status_ptr();
-  mla_attn_kernel<<<dim3(NB, nsplit), NTHREADS, SMEM, s>>>(tq, tkv, p);
+  MARY_LAUNCH(mla_attn_kernel, dim3(NB, nsplit), NTHREADS, SMEM, s, tq, tkv, p);
   MARY_CHECK_LAUNCH();
   if (nsplit > 1) {
-    mla_combine_kernel<<<dim3(NB, TR), 128, 0, s>>>(p, NB);
+    MARY_LAUNCH(mla_combine_kernel, dim3(NB, TR), 128, 0, s, p, NB);
     MARY_CHECK_LAUNCH();
   }
   return MARY_OK;

@@ -137,6 +137,7 @@ __device__ void allreduce_bf16_body(const CommCtx& c, size_t in_off, size_t out_
 
 __global__ void __launch_bounds__(512)
 allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n, uint32_t* epochs, int use_mc, int f32) {
+  pdl_sync();
   allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, use_mc, blockIdx.x, gridDim.x, f32);
 }
 
@@ -277,6 +278,7 @@ __device__ void argmax_merge_body(const CommCtx& c, size_t pair_off, int Tmax, c
 __global__ void __launch_bounds__(256)
 argmax_merge_kernel(const CommCtx c, size_t pair_off, int Tmax, const float* val, const int64_t* idx, int T, int vocab_off,
                     uint32_t* epoch_slot, int slot_block, int64_t* out_idx, float* out_val) {
+  pdl_sync();
   argmax_merge_body(c, pair_off, Tmax, val, idx, T, vocab_off, epoch_slot, slot_block, out_idx, out_val);
 }
 
@@ -290,6 +292,7 @@ argmax_merge_emulated_kernel(CommCtx c, size_t pair_off, int Tmax, const float* 
 }
 
 __global__ void rank_barrier_kernel(const CommCtx c, uint32_t* epoch_slot, int slot_block) {
+  pdl_sync();
   __shared__ uint32_t epoch_s;
   if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
   __syncthreads();
@@ -317,7 +320,7 @@ MARY_API int mary_allreduce_bf16(const uint64_t* bufs, const uint64_t* sigs, uin
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
-  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0, 0);
+  MARY_LAUNCH(allreduce_bf16_kernel, grid, 512, 0, s, c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0, 0);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -329,7 +332,7 @@ MARY_API int mary_allreduce_f32(const uint64_t* bufs, const uint64_t* sigs, uint
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
-  allreduce_bf16_kernel<<<grid, 512, 0, s>>>(c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0, 1);
+  MARY_LAUNCH(allreduce_bf16_kernel, grid, 512, 0, s, c, in_off, out_off, n, epochs, (use_mc && mc) ? 1 : 0, 1);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -341,7 +344,7 @@ MARY_API int mary_rank_barrier(const uint64_t* sigs, int rank, int world, uint32
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = nullptr; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
-  rank_barrier_kernel<<<1, 32, 0, s>>>(c, epoch_slot, slot_block);
+  MARY_LAUNCH(rank_barrier_kernel, 1, 32, 0, s, c, epoch_slot, slot_block);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -403,7 +406,7 @@ MARY_API int mary_argmax_merge(const void* val, const void* idx, int T, int Tmax
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = nullptr; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
-  argmax_merge_kernel<<<1, 256, 0, s>>>(c, pair_off, Tmax, (const float*)val, (const int64_t*)idx, T, vocab_off, epoch_slot, slot_block,
+  MARY_LAUNCH(argmax_merge_kernel, 1, 256, 0, s, c, pair_off, Tmax, (const float*)val, (const int64_t*)idx, T, vocab_off, epoch_slot, slot_block,
                                         (int64_t*)out_idx, (float*)out_val);
   MARY_CHECK_LAUNCH();
   return MARY_OK;

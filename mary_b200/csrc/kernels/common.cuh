@@ -89,6 +89,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// Programmatic dependent launch: let the next kernel of the stream be scheduled as soon as every CTA of this one runs, then
+// wait until all earlier kernels of the stream have finished and their writes are visible.  It is the first statement of
+// every kernel launched with MARY_LAUNCH; without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(m) : "memory");

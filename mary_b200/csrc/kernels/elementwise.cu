@@ -51,6 +51,7 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float* f) {
 template <typename TI>
 __global__ void rmsnorm_kernel(const TI* __restrict__ x, const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                int H, int64_t ldx, int64_t ldy, float eps) {
+  pdl_sync();
   extern __shared__ float row[];
   __shared__ float red[32];
   const TI* xr = x + (int64_t)blockIdx.x * ldx;
@@ -76,6 +77,7 @@ __global__ void rmsnorm_kernel(const TI* __restrict__ x, const __nv_bfloat16* __
 template <typename TI>
 __global__ void add_rmsnorm_kernel(const TI* __restrict__ x, __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
                                    __nv_bfloat16* __restrict__ y, int H, float eps) {
+  pdl_sync();
   extern __shared__ float row[];
   __shared__ float red[32];
   const int64_t o = (int64_t)blockIdx.x * H;
@@ -104,6 +106,7 @@ __global__ void add_rmsnorm_kernel(const TI* __restrict__ x, __nv_bfloat16* __re
 template <typename TI>
 __global__ void norm_add_norm_kernel(const TI* __restrict__ a, const __nv_bfloat16* __restrict__ w_post, __nv_bfloat16* __restrict__ h,
                                      const __nv_bfloat16* __restrict__ w_next, __nv_bfloat16* __restrict__ xo, int H, float eps, float scalar) {
+  pdl_sync();
   extern __shared__ float row[];
   __shared__ float red[32];
   const int64_t o = (int64_t)blockIdx.x * H;
@@ -141,6 +144,7 @@ __global__ void norm_add_norm_kernel(const TI* __restrict__ a, const __nv_bfloat
 }
 
 __global__ void glu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int F, int64_t n, int act) {
+  pdl_sync();
   int64_t idx = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (idx >= n) return;
   const int64_t t = idx / F, f = idx % F;
@@ -160,6 +164,7 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* 
 
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
                              int H, float scale, int vocab) {
+  pdl_sync();
   int id = ids[blockIdx.x];
   if (id < 0 || id >= vocab) id = 0;
   const __nv_bfloat16* src = table + (int64_t)id * H;
@@ -182,6 +187,7 @@ __global__ void qk_norm_rope_append_kernel(const __nv_bfloat16* __restrict__ qkv
                                            int v_norm, const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                            const int64_t* __restrict__ slots, __nv_bfloat16* __restrict__ qo,
                                            __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, float eps, int T) {
+  pdl_sync();
   const int warps_per_block = blockDim.x >> 5;
   const int heads = n_q + 2 * n_kv;
   const int64_t gw = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
@@ -262,8 +268,8 @@ MARY_API int mary_rmsnorm(const void* x, int x_is_f32, const void* w, void* y, i
   if (T <= 0) return MARY_OK;
   size_t sm = (size_t)H * 4;
   if (sm > 48 * 1024 || (H & 7) || (ldx & 7) || (ldy & 7)) return MARY_ERR_BAD_ARG;
-  if (x_is_f32) rmsnorm_kernel<float><<<T, NT, sm, s>>>((const float*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
-  else rmsnorm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
+  if (x_is_f32) MARY_LAUNCH((rmsnorm_kernel<float>), T, NT, sm, s, (const float*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
+  else MARY_LAUNCH((rmsnorm_kernel<__nv_bfloat16>), T, NT, sm, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, ldx, ldy, eps);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -272,8 +278,8 @@ MARY_API int mary_add_rmsnorm(const void* x, int x_is_f32, void* res, const void
   if (T <= 0) return MARY_OK;
   size_t sm = (size_t)H * 4;
   if (sm > 48 * 1024 || (H & 7)) return MARY_ERR_BAD_ARG;
-  if (x_is_f32) add_rmsnorm_kernel<float><<<T, NT, sm, s>>>((const float*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
-  else add_rmsnorm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
+  if (x_is_f32) MARY_LAUNCH((add_rmsnorm_kernel<float>), T, NT, sm, s, (const float*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
+  else MARY_LAUNCH((add_rmsnorm_kernel<__nv_bfloat16>), T, NT, sm, s, (const __nv_bfloat16*)x, (__nv_bfloat16*)res, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, H, eps);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -283,8 +289,8 @@ MARY_API int mary_norm_add_norm(const void* a, int a_is_f32, const void* w_post,
   if (T <= 0) return MARY_OK;
   size_t sm = (size_t)H * 4;
   if (sm > 48 * 1024 || (H & 7)) return MARY_ERR_BAD_ARG;
-  if (a_is_f32) norm_add_norm_kernel<float><<<T, NT, sm, s>>>((const float*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
-  else norm_add_norm_kernel<__nv_bfloat16><<<T, NT, sm, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
+  if (a_is_f32) MARY_LAUNCH((norm_add_norm_kernel<float>), T, NT, sm, s, (const float*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
+  else MARY_LAUNCH((norm_add_norm_kernel<__nv_bfloat16>), T, NT, sm, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)w_post, (__nv_bfloat16*)h, (const __nv_bfloat16*)w_next, (__nv_bfloat16*)xo, H, eps, scalar);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -294,7 +300,7 @@ MARY_API int mary_glu(const void* gu, void* out, int T, int F, int act, cudaStre
   if (F % 8) return MARY_ERR_BAD_ARG;
   int64_t n = (int64_t)T * F;
   int blocks = (int)((n / 8 + NT - 1) / NT);
-  glu_kernel<<<blocks, NT, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, n, act);
+  MARY_LAUNCH(glu_kernel, blocks, NT, 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, F, n, act);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -302,7 +308,7 @@ MARY_API int mary_glu(const void* gu, void* out, int T, int F, int act, cudaStre
 MARY_API int mary_embed(const int* ids, const void* table, void* out, int T, int H, float scale, int vocab, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   if (H % 8) return MARY_ERR_BAD_ARG;
-  embed_kernel<<<T, 128, 0, s>>>(ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, H, scale, vocab);
+  MARY_LAUNCH(embed_kernel, T, 128, 0, s, ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, H, scale, vocab);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -314,7 +320,7 @@ MARY_API int mary_qk_norm_rope_append(const void* qkv, int n_q, int n_kv, int D,
   if (D > 512 || (D & 1)) return MARY_ERR_BAD_ARG;
   const int64_t warps = (int64_t)T * (n_q + 2 * n_kv);
   const int wpb = 8;
-  qk_norm_rope_append_kernel<<<(int)((warps + wpb - 1) / wpb), wpb * 32, 0, s>>>(
+  MARY_LAUNCH(qk_norm_rope_append_kernel, (int)((warps + wpb - 1) / wpb), wpb * 32, 0, s, 
       (const __nv_bfloat16*)qkv, n_q, n_kv, D, (const __nv_bfloat16*)q_norm, (const __nv_bfloat16*)k_norm, v_norm, inv_freq, positions,
       slots, (__nv_bfloat16*)qo, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, eps, T);
   MARY_CHECK_LAUNCH();

@@ -35,6 +35,7 @@ struct Peers {
 };
 
 __global__ void ep_counts_kernel(const int* __restrict__ idx, int n_entries, int E, int rank, Peers count_mats) {
+  pdl_sync();
   extern __shared__ int cnt[];
   for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
   __syncthreads();
@@ -57,6 +58,7 @@ __global__ void ep_counts_kernel(const int* __restrict__ idx, int n_entries, int
 __global__ void ep_plan_kernel(const int* __restrict__ cm, int world, int rank, int E, int e_local, int NT, Tile* __restrict__ tiles,
                                int* __restrict__ meta, int* __restrict__ send_base, int* __restrict__ send_cnt, int* __restrict__ recv_src_off,
                                int shared_rows) {
+  pdl_sync();
   extern __shared__ int sh[];
   __shared__ int acc_self;
   int* tot = sh;            // [E] rows of every expert over all sources
@@ -106,6 +108,7 @@ __device__ __forceinline__ uint32_t e2m1_code(float y) {
 __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int* __restrict__ idx, int k, int E, int e_local,
                                    int Kd, int NT, int rank, int entry_stride, const int* __restrict__ send_base, int* __restrict__ send_cnt,
                                    Peers xq_slabs, Peers sf_slabs, Peers meta_slabs) {
+  pdl_sync();
   __shared__ int s_row;
   const int i = blockIdx.x;
   const int e = idx[i];
@@ -148,6 +151,7 @@ __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t 
 // row_ptrs[row] = address of slot `entry` in the combine buffer of the row's source rank (0 for padding rows).
 __global__ void ep_return_ptrs_kernel(const int* __restrict__ meta_rows, const int* __restrict__ plan_meta, const Tile* __restrict__ tiles,
                                       int NT, int entry_stride, int H, Peers comb, uint64_t* __restrict__ row_ptrs) {
+  pdl_sync();
   const int t = blockIdx.x;
   if (t >= plan_meta[0]) return;
   const Tile tl = tiles[t];
@@ -173,7 +177,7 @@ Peers make_peers(const uint64_t* a, int world) {
 
 MARY_API int mary_ep_counts(const int* idx, int n_entries, int E, int rank, int world, const uint64_t* count_mats, cudaStream_t s) {
   if (E > 8192 || world > MAX_RANKS) return MARY_ERR_BAD_ARG;
-  ep_counts_kernel<<<1, 1024, E * sizeof(int), s>>>(idx, n_entries, E, rank, make_peers(count_mats, world));
+  MARY_LAUNCH(ep_counts_kernel, 1, 1024, E * sizeof(int), s, idx, n_entries, E, rank, make_peers(count_mats, world));
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -182,7 +186,7 @@ MARY_API int mary_ep_counts(const int* idx, int n_entries, int E, int rank, int 
 MARY_API int mary_ep_plan(const int* cm, int world, int rank, int E, int e_local, int NT, void* tiles, int* meta, int* send_base,
                           int* send_cnt, int shared_rows, cudaStream_t s) {
   if (E > 4096 || world > MAX_RANKS || e_local * world != E || shared_rows < 0) return MARY_ERR_BAD_ARG;
-  ep_plan_kernel<<<1, 1024, 2 * E * sizeof(int), s>>>(cm, world, rank, E, e_local, NT, (Tile*)tiles, meta, send_base, send_cnt, nullptr,
+  MARY_LAUNCH(ep_plan_kernel, 1, 1024, 2 * E * sizeof(int), s, cm, world, rank, E, e_local, NT, (Tile*)tiles, meta, send_base, send_cnt, nullptr,
                                                       shared_rows);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
@@ -194,7 +198,7 @@ MARY_API int mary_ep_dispatch(const void* x, int64_t ldx, const int* idx, int n_
   if (n_entries <= 0) return MARY_OK;
   if ((K % 64) || (ldx % 8) || world > MAX_RANKS) return MARY_ERR_BAD_ARG;
   const int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
-  ep_dispatch_kernel<<<n_entries, threads, 0, s>>>((const __nv_bfloat16*)x, ldx, idx, k, E, e_local, K, NT, rank, entry_stride, send_base,
+  MARY_LAUNCH(ep_dispatch_kernel, n_entries, threads, 0, s, (const __nv_bfloat16*)x, ldx, idx, k, E, e_local, K, NT, rank, entry_stride, send_base,
                                                   send_cnt, make_peers(xq_slabs, world), make_peers(sf_slabs, world),
                                                   make_peers(meta_slabs, world));
   MARY_CHECK_LAUNCH();
@@ -204,7 +208,7 @@ MARY_API int mary_ep_dispatch(const void* x, int64_t ldx, const int* idx, int n_
 MARY_API int mary_ep_return_ptrs(const int* meta_rows, const int* plan_meta, const void* tiles, int max_tiles, int NT, int entry_stride,
                                  int H, int world, const uint64_t* comb, uint64_t* row_ptrs, cudaStream_t s) {
   if (max_tiles <= 0) return MARY_OK;
-  ep_return_ptrs_kernel<<<max_tiles, 32, 0, s>>>(meta_rows, plan_meta, (const Tile*)tiles, NT, entry_stride, H, make_peers(comb, world), row_ptrs);
+  MARY_LAUNCH(ep_return_ptrs_kernel, max_tiles, 32, 0, s, meta_rows, plan_meta, (const Tile*)tiles, NT, entry_stride, H, make_peers(comb, world), row_ptrs);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

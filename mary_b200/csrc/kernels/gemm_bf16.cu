@@ -136,6 +136,7 @@ struct Cfg {
 template <int BN, bool GLU>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
+  pdl_sync();
   using C = Cfg<BN, GLU>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~uintptr_t(1023));
@@ -350,7 +351,7 @@ int launch(const CUtensorMap& tr, const CUtensorMap& tc, const GemmParams& p, cu
   int total = p.tiles_r * p.tiles_c * p.split_k * p.batch;
   int grid = total < mary_num_sms() ? total : mary_num_sms();
   if (p.sk_units > 0) grid = (p.tiles_r * p.tiles_c * p.k_blocks + p.sk_units - 1) / p.sk_units;
-  gemm_bf16_kernel<BN, GLU><<<grid, NTHREADS, C::SMEM, stream>>>(tr, tc, p);
+  MARY_LAUNCH((gemm_bf16_kernel<BN, GLU>), grid, NTHREADS, C::SMEM, stream, tr, tc, p);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

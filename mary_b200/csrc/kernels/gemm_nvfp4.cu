@@ -71,6 +71,7 @@ struct Cfg {
 template <int NT, bool GLU>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_nvfp4_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const FP4Params p) {
+  pdl_sync();
   using C = Cfg<NT, GLU>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~uintptr_t(1023));
@@ -219,7 +220,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, const FP4Params& p, cud
       return MARY_ERR_CUDA;
     attr_set = true;
   }
-  gemm_nvfp4_grouped_kernel<NT, GLU><<<mary_num_sms(), NTHREADS, C::SMEM, s>>>(tw, tx, p);
+  MARY_LAUNCH((gemm_nvfp4_grouped_kernel<NT, GLU>), mary_num_sms(), NTHREADS, C::SMEM, s, tw, tx, p);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

@@ -15,6 +15,27 @@ int* mary_status_ptr();
 int mary_make_tmap_2d(CUtensorMap* m, const void* base, int dtype_bytes_x2, uint64_t rows, uint64_t cols, uint64_t ld,
                       uint32_t box_rows, uint32_t box_cols, int swizzle128);
 
+// 1 unless the environment says MARY_PDL=0.
+int mary_pdl_enabled();
+
+// Launch with programmatic dependent launch allowed: the kernel may be scheduled while its predecessor on the stream is still
+// draining, and its threads call pdl_sync() (common.cuh) before they touch anything a predecessor wrote.  Only kernels whose
+// first statement is pdl_sync() may be launched this way.  A template kernel name goes in parentheses.
+#define MARY_LAUNCH(kernel_, grid_, block_, smem_, stream_, ...)                                                     \
+  do {                                                                                                             \
+    cudaLaunchConfig_t cfg__ = {};                                                                                 \
+    cfg__.gridDim = (grid_);                                                                                       \
+    cfg__.blockDim = (block_);                                                                                     \
+    cfg__.dynamicSmemBytes = (smem_);                                                                              \
+    cfg__.stream = (stream_);                                                                                      \
+    cudaLaunchAttribute at__[1];                                                                                   \
+    at__[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                               \
+    at__[0].val.programmaticStreamSerializationAllowed = 1;                                                        \
+    cfg__.attrs = at__;                                                                                            \
+    cfg__.numAttrs = mary_pdl_enabled() ? 1 : 0;                                                                   \
+    if (cudaLaunchKernelEx(&cfg__, kernel_, __VA_ARGS__) != cudaSuccess) return MARY_ERR_CUDA;                     \
+  } while (0)
+
 #define MARY_CHECK_LAUNCH()                                  \
   do {                                                       \
     cudaError_t e__ = cudaGetLastError();                    \

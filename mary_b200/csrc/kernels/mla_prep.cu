@@ -28,6 +28,7 @@ __global__ void mla_prep_kernel(const __nv_bfloat16* __restrict__ qakv, int64_t 
                                 const __nv_bfloat16* __restrict__ w_kv, const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                 const int64_t* __restrict__ slots, __nv_bfloat16* __restrict__ qa_out, __nv_bfloat16* __restrict__ cache,
                                 float eps) {
+  pdl_sync();
   __shared__ float red[32];
   const int t = blockIdx.x;
   const __nv_bfloat16* row = qakv + (int64_t)t * ld;
@@ -63,6 +64,7 @@ __global__ void mla_prep_kernel(const __nv_bfloat16* __restrict__ qakv, int64_t 
 // qb [T, H, 192] = [nope 128 | rope 64] per head -> q_full[T, H, 512 + i] for the rope part
 __global__ void mla_q_rope_kernel(const __nv_bfloat16* __restrict__ qb, const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                   __nv_bfloat16* __restrict__ q_full, int H, int T) {
+  pdl_sync();
   const int64_t gw = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (gw >= (int64_t)T * H) return;
   const int t = (int)(gw / H), i = threadIdx.x & 31;
@@ -84,7 +86,7 @@ __global__ void mla_q_rope_kernel(const __nv_bfloat16* __restrict__ qb, const fl
 MARY_API int mary_mla_prep(const void* qakv, int64_t ld, int q_lora, const void* w_qa, const void* w_kv, const float* inv_freq,
                            const int* positions, const int64_t* slots, void* qa_out, void* cache, float eps, int T, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
-  mla_prep_kernel<<<T, 256, 0, s>>>((const __nv_bfloat16*)qakv, ld, q_lora, (const __nv_bfloat16*)w_qa, (const __nv_bfloat16*)w_kv, inv_freq,
+  MARY_LAUNCH(mla_prep_kernel, T, 256, 0, s, (const __nv_bfloat16*)qakv, ld, q_lora, (const __nv_bfloat16*)w_qa, (const __nv_bfloat16*)w_kv, inv_freq,
                                     positions, slots, (__nv_bfloat16*)qa_out, (__nv_bfloat16*)cache, eps);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
@@ -93,7 +95,7 @@ MARY_API int mary_mla_prep(const void* qakv, int64_t ld, int q_lora, const void*
 MARY_API int mary_mla_q_rope(const void* qb, const float* inv_freq, const int* positions, void* q_full, int H, int T, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   const int64_t warps = (int64_t)T * H;
-  mla_q_rope_kernel<<<(int)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)qb, inv_freq, positions, (__nv_bfloat16*)q_full, H, T);
+  MARY_LAUNCH(mla_q_rope_kernel, (int)((warps + 7) / 8), 256, 0, s, (const __nv_bfloat16*)qb, inv_freq, positions, (__nv_bfloat16*)q_full, H, T);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

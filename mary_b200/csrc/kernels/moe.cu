@@ -24,6 +24,7 @@ struct Tile { int expert, row0, rows, sf_tile; };
 // (-1 for padding), tiles/n_tiles for the grouped GEMM, counts[E], meta = {n_tiles, padded rows}.
 __global__ void moe_plan_kernel(const int* __restrict__ idx, int n_entries, int k, int E, int NT, int max_rows, int* __restrict__ row_of,
                                 int* __restrict__ src_of, Tile* __restrict__ tiles, int* __restrict__ meta, int* __restrict__ counts_out) {
+  pdl_sync();
   extern __shared__ int sh[];
   int* cnt = sh;            // [E]
   int* off = sh + E;        // [E + 1]
@@ -107,6 +108,7 @@ __global__ void quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, int
                                         int Kd, int NT, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf_tiles,
                                         uint8_t* __restrict__ sf_rowmajor, const int* __restrict__ n_rows,
                                         const int* __restrict__ row_of, int k) {
+  pdl_sync();
   int row = blockIdx.x;
   int src = row;
   if (row_of) {
@@ -152,6 +154,7 @@ __global__ void quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, int
 __global__ void moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, int64_t ldy, const int* __restrict__ row_of,
                                      const float* __restrict__ w, int k, int H, const __nv_bfloat16* __restrict__ add,
                                      __nv_bfloat16* __restrict__ out) {
+  pdl_sync();
   const int t = blockIdx.x;
   for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < H; c += gridDim.y * blockDim.x * 8) {
     float acc[8];
@@ -185,7 +188,7 @@ __global__ void moe_unpermute_kernel(const __nv_bfloat16* __restrict__ y, int64_
 MARY_API int mary_moe_plan(const int* idx, int n_entries, int k, int E, int NT, int max_rows, int* row_of, int* src_of, void* tiles,
                            int* meta, int* counts, cudaStream_t s) {
   if (E > 4096 || NT <= 0) return MARY_ERR_BAD_ARG;
-  moe_plan_kernel<<<1, 1024, (2 * E + 1) * sizeof(int), s>>>(idx, n_entries, k, E, NT, max_rows, row_of, src_of, (Tile*)tiles, meta, counts);
+  MARY_LAUNCH(moe_plan_kernel, 1, 1024, (2 * E + 1) * sizeof(int), s, idx, n_entries, k, E, NT, max_rows, row_of, src_of, (Tile*)tiles, meta, counts);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -201,7 +204,7 @@ MARY_API int mary_quant_nvfp4_rows(const void* x, int64_t ldx, const int* src_of
   if (rows <= 0) return MARY_OK;
   if ((K % 64) || (ldx % 8)) return MARY_ERR_BAD_ARG;
   int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
-  quant_nvfp4_rows_kernel<<<rows, threads, 0, s>>>((const __nv_bfloat16*)x, ldx, src_of, identity, K, NT, (uint8_t*)xq, (uint8_t*)sf_tiles,
+  MARY_LAUNCH(quant_nvfp4_rows_kernel, rows, threads, 0, s, (const __nv_bfloat16*)x, ldx, src_of, identity, K, NT, (uint8_t*)xq, (uint8_t*)sf_tiles,
                                                    (uint8_t*)sf_rowmajor, n_rows, nullptr, 1);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
@@ -214,7 +217,7 @@ MARY_API int mary_quant_nvfp4_entries(const void* x, int64_t ldx, const int* row
   if (n_entries <= 0) return MARY_OK;
   if ((K % 64) || (ldx % 8) || k < 1) return MARY_ERR_BAD_ARG;
   int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
-  quant_nvfp4_rows_kernel<<<n_entries, threads, 0, s>>>((const __nv_bfloat16*)x, ldx, nullptr, identity, K, NT, (uint8_t*)xq,
+  MARY_LAUNCH(quant_nvfp4_rows_kernel, n_entries, threads, 0, s, (const __nv_bfloat16*)x, ldx, nullptr, identity, K, NT, (uint8_t*)xq,
                                                         (uint8_t*)sf_tiles, nullptr, nullptr, row_of, k);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
@@ -225,7 +228,7 @@ MARY_API int mary_moe_unpermute(const void* y, int64_t ldy, const int* row_of, c
   if (T <= 0) return MARY_OK;
   if (H % 8) return MARY_ERR_BAD_ARG;
   const int slabs = (H / 8 + 127) / 128;       // 128 threads x 8 columns per CTA
-  moe_unpermute_kernel<<<dim3(T, slabs), 128, 0, s>>>((const __nv_bfloat16*)y, ldy, row_of, w, k, H, (const __nv_bfloat16*)add,
+  MARY_LAUNCH(moe_unpermute_kernel, dim3(T, slabs), 128, 0, s, (const __nv_bfloat16*)y, ldy, row_of, w, k, H, (const __nv_bfloat16*)add,
                                                      (__nv_bfloat16*)out);
   MARY_CHECK_LAUNCH();
   return MARY_OK;

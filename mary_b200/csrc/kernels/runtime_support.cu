@@ -4,6 +4,7 @@
 
 #include "common.cuh"
 #include "host_utils.h"
+#include <stdlib.h>
 
 namespace {
 std::mutex g_mu;
@@ -75,3 +76,12 @@ MARY_API int mary_last_status() {
 }
 
 MARY_API int mary_sm_count() { return mary_num_sms(); }
+
+int mary_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("MARY_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v;
+}

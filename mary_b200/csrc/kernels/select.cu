@@ -43,6 +43,7 @@ __device__ __forceinline__ uint4 philox(uint2 key, uint4 ctr) {
 // Soft-capping is monotonic, so it is applied to the reported maximum only.
 __global__ void argmax_kernel(const float* __restrict__ logits, int64_t ld, int V, float softcap, int mode, float temperature,
                               float margin, uint64_t seed, uint64_t step, int64_t* __restrict__ out_idx, float* __restrict__ out_val) {
+  pdl_sync();
   __shared__ float sv[32];
   __shared__ int si[32];
   const float* row = logits + (int64_t)blockIdx.x * ld;
@@ -178,6 +179,7 @@ __global__ void __launch_bounds__(256)
 router_topk_block_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ bias, int T, int E, int k, int mode,
                          int n_group, int topk_group, float scale, int renorm, int* __restrict__ out_idx, float* __restrict__ out_w,
                          int* __restrict__ counts, int* __restrict__ flag) {
+  pdl_sync();
   __shared__ float s_sc[512], s_sel[512], s_g[32], s_red[8];
   __shared__ float s_cv[256];
   __shared__ int s_ci[256];
@@ -288,7 +290,7 @@ router_topk_block_kernel(const float* __restrict__ logits, int64_t ld, const flo
 MARY_API int mary_argmax(const float* logits, int64_t ld, int rows, int V, float softcap, int mode, float temperature, float margin,
                          uint64_t seed, uint64_t step, int64_t* out_idx, float* out_val, cudaStream_t s) {
   if (rows <= 0) return MARY_OK;
-  argmax_kernel<<<rows, 1024, 0, s>>>(logits, ld, V, softcap, mode, temperature, margin, seed, step, out_idx, out_val);
+  MARY_LAUNCH(argmax_kernel, rows, 1024, 0, s, logits, ld, V, softcap, mode, temperature, margin, seed, step, out_idx, out_val);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -300,7 +302,7 @@ MARY_API int mary_router_topk(const float* logits, int64_t ld, const float* bias
   if (E > 32 * MAXE_PER_LANE || k > 32 || n_group > 32 || (n_group > 1 && E % n_group)) return MARY_ERR_BAD_ARG;
   if (T <= 16384 && k * 8 <= 256) {
     // one CTA per token: short dependent chains (decode and ordinary prefill chunks)
-    router_topk_block_kernel<<<T, 256, 0, s>>>(logits, ld, bias, T, E, k, mode, n_group, topk_group, scale, renorm, out_idx, out_w,
+    MARY_LAUNCH(router_topk_block_kernel, T, 256, 0, s, logits, ld, bias, T, E, k, mode, n_group, topk_group, scale, renorm, out_idx, out_w,
                                                counts, flag);
     MARY_CHECK_LAUNCH();
     return MARY_OK;
