@@ -18,7 +18,7 @@ namespace {
 
 constexpr int WARPS = 4;
 constexpr int MAXR = 16;     // scratch stride, shared with attention_simt.cu
-constexpr int KG = 4;        // keys fetched together
+constexpr int KG_BYTES = 4096;   // K + V bytes a warp requests before it uses any of them (4 keys at D = 256, 8 at 128 and below)
 
 struct DecParams {
   const __nv_bfloat16* q; const __nv_bfloat16* kc; const __nv_bfloat16* vc; __nv_bfloat16* out;
@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(const DecParams p) {
   pdl_sync();
   constexpr int E = D / 32;
+  constexpr int KG = KG_BYTES / (4 * D) > 8 ? 8 : KG_BYTES / (4 * D);
   using V = typename Vec<E>::T;
   __shared__ float red_o[WARPS][RMAX][D];
   __shared__ float red_ml[WARPS][RMAX][2];
@@ -86,25 +87,16 @@ attn_decode_kernel(const DecParams p) {
   }
   const int* pt = p.page_table + (int64_t)seq * p.max_pages;
 
-  // The K and V rows of the NEXT group of keys are requested before the current group is consumed, so a warp always has
-  // one group (2 * KG rows) in flight while it computes: without this the loads and the arithmetic of a warp alternate.
-  auto load_group = [&](int kb, V* kvd, V* vvd) {
+  for (int kb = s_lo + warp * KG; kb < s_hi; kb += WARPS * KG) {
+    V kv[KG], vv[KG];
 #pragma unroll
     for (int j = 0; j < KG; ++j) {
       const int kp = min(kb + j, s_hi - 1);          // clamped: masked below
       const int page = pt[kp / p.page_size];
       const int64_t tok = kp % p.page_size;
-      kvd[j] = *(const V*)(p.kc + (int64_t)page * p.k_page + tok * p.k_tok + (int64_t)kvh * D + lane * E);
-      vvd[j] = *(const V*)(p.vc + (int64_t)page * p.v_page + tok * p.v_tok + (int64_t)kvh * D + lane * E);
+      kv[j] = *(const V*)(p.kc + (int64_t)page * p.k_page + tok * p.k_tok + (int64_t)kvh * D + lane * E);
+      vv[j] = *(const V*)(p.vc + (int64_t)page * p.v_page + tok * p.v_tok + (int64_t)kvh * D + lane * E);
     }
-  };
-  V kvn[KG], vvn[KG];
-  if (s_lo + warp * KG < s_hi) load_group(s_lo + warp * KG, kvn, vvn);
-  for (int kb = s_lo + warp * KG; kb < s_hi; kb += WARPS * KG) {
-    V kv[KG], vv[KG];
-#pragma unroll
-    for (int j = 0; j < KG; ++j) { kv[j] = kvn[j]; vv[j] = vvn[j]; }
-    if (kb + WARPS * KG < s_hi) load_group(kb + WARPS * KG, kvn, vvn);
     float s[KG][RMAX];
 #pragma unroll
     for (int j = 0; j < KG; ++j) {

@@ -141,6 +141,50 @@ allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n,
   allreduce_bf16_body(c, in_off, out_off, n, epochs + blockIdx.x, use_mc, blockIdx.x, gridDim.x, f32);
 }
 
+// One-shot all-reduce for small vectors (decode-sized partial sums): every rank stages its partial vector in a symmetric
+// staging area, ONE barrier makes the stages complete, and every rank then sums the whole vector by itself — one in-switch
+// reduction per 16 bytes through the multicast address, or peer loads in rank order — into a LOCAL output.  Nothing a peer
+// reads is written again before the next barrier: the staging area alternates with the parity of the device-resident epoch,
+// and a rank can only pass the barrier of call k + 1 after every peer has finished reading the stage of call k.  Compared with
+// the two-shot form this saves the second barrier and the all-gather step; it moves world x the bytes, which only pays for
+// small vectors.  Same-numbered blocks of all ranks own the same slice, so the barrier is per block.
+__global__ void __launch_bounds__(512)
+allreduce_oneshot_kernel(const CommCtx c, const uint4* __restrict__ partial, uint4* __restrict__ out, size_t stage_off, size_t stage_bytes,
+                         int64_t nvec, uint32_t* epochs, int use_mc) {
+  pdl_sync();
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) epoch_s = epochs[blockIdx.x] + 1;
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
+  const size_t off = stage_off + (size_t)(epoch & 1u) * stage_bytes;
+  const int64_t per = (nvec + gridDim.x - 1) / gridDim.x;
+  const int64_t lo = (int64_t)blockIdx.x * per, hi = min(nvec, lo + per);
+  uint4* mine = (uint4*)(c.bufs[c.rank] + off);
+  for (int64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) mine[v] = partial[v];
+  if (!rank_barrier(c, 0, epoch, blockIdx.x)) return;
+  for (int64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
+    uint4 r;
+    if (use_mc) {
+      r = multimem_ld_reduce_bf16x8(c.mc + off + v * 16);
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < c.world; ++p) {                    // rank order: every rank computes the same bits
+        uint4 x;
+        asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                     : "=r"(x.x), "=r"(x.y), "=r"(x.z), "=r"(x.w) : "l"(c.bufs[p] + off + v * 16) : "memory");
+        const __nv_bfloat162* xp = (const __nv_bfloat162*)&x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(xp[j]); acc[2 * j] += f.x; acc[2 * j + 1] += f.y; }
+      }
+      __nv_bfloat162* rp = (__nv_bfloat162*)&r;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) rp[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    }
+    out[v] = r;
+  }
+  if (threadIdx.x == 0) epochs[blockIdx.x] = epoch;
+}
+
 // Every rank of the group inside ONE cooperative launch on one GPU (block groups play the ranks, plain loads and stores
 // play the peer accesses): the way to exercise the flag protocol and the data movement where only one GPU is available,
 // because kernels that wait on one another must never be separate launches on the same GPU.
@@ -423,5 +467,22 @@ MARY_API int mary_argmax_merge_emulated(const void* val, const void* idx, int T,
   void* args[] = {&c, &po, &Tmax, &val, &idx, &T, &vocab_per_rank, &epoch_slots, &slot_block, &out_idx, &out_val};
   if (cudaLaunchCooperativeKernel((void*)argmax_merge_emulated_kernel, dim3(world), dim3(256), args, 0, s) != cudaSuccess)
     return MARY_ERR_CUDA;
+  return MARY_OK;
+}
+
+// One-shot form for small vectors: partial (this rank's n bf16, 16-byte aligned, any device memory) -> out (local, n bf16).
+// The symmetric buffers need two staging areas of stage_bytes >= n * 2 each at byte offset stage_off.  grid <= 64 blocks; the
+// same flag pad and epochs array as mary_allreduce_bf16 (both forms may be mixed as long as all ranks make the same calls).
+MARY_API int mary_allreduce_bf16_oneshot(const void* partial, void* out, const uint64_t* bufs, const uint64_t* sigs, uint64_t mc, int rank,
+                                         int world, uint64_t stage_off, uint64_t stage_bytes, int64_t n, uint32_t* epochs, int grid,
+                                         int use_mc, uint64_t wait_ns, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || (n % 8) || (stage_off % 16) || (stage_bytes % 16) || (uint64_t)n * 2 > stage_bytes || grid < 1 ||
+      grid > 64 || ((uintptr_t)partial & 15) || ((uintptr_t)out & 15))
+    return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  MARY_LAUNCH(allreduce_oneshot_kernel, grid, 512, 0, s, c, (const uint4*)partial, (uint4*)out, (size_t)stage_off, (size_t)stage_bytes,
+              n / 8, epochs, (use_mc && mc) ? 1 : 0);
   return MARY_OK;
 }

@@ -15,7 +15,8 @@ int* mary_status_ptr();
 int mary_make_tmap_2d(CUtensorMap* m, const void* base, int dtype_bytes_x2, uint64_t rows, uint64_t cols, uint64_t ld,
                       uint32_t box_rows, uint32_t box_cols, int swizzle128);
 
-// 1 unless the environment says MARY_PDL=0.
+// 1 when the environment says MARY_PDL=1 (off by default: in CUDA-graph replay the measured step time was the same with and
+// without it, 81.2 ms against 80.1 ms at 16 sequences).
 int mary_pdl_enabled();
 
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled while its predecessor on the stream is still

@@ -81,7 +81,7 @@ int mary_pdl_enabled() {
   static int v = -1;
   if (v < 0) {
     const char* e = getenv("MARY_PDL");
-    v = (e && e[0] == '0') ? 0 : 1;
+    v = (e && e[0] == '1') ? 1 : 0;
   }
   return v;
 }

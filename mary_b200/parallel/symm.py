@@ -15,6 +15,7 @@ from ..ops.cuda import _stream, check, declare, lib
 
 declare("mary_allreduce_bf16", "pplii" + "lllpiils")
 declare("mary_allreduce_f32", "pplii" + "lllpiils")
+declare("mary_allreduce_bf16_oneshot", "pppplii" + "lllpiils")
 declare("mary_wait_flag", "piiiils")
 declare("mary_argmax_merge", "ppiiipplii" + "pilpps")
 
@@ -22,6 +23,7 @@ FLAG_WORDS = 64 * 2 * 8        # grid <= 64 blocks, two barriers, eight ranks
 PAIR_TOKENS = 4096             # rows one arg-max merge can carry
 PAIR_BYTES = 2 * 8 * PAIR_TOKENS * 8
 MERGE_SLOT = 62                # flag block of the arg-max merge (all-reduce grids stay below it)
+ONESHOT_MAX_BYTES = 1 << 20    # vectors up to this size take the one-barrier form (every rank sums the whole vector itself)
 
 
 class SymmetricHeap:
@@ -50,6 +52,8 @@ class SymmetricHeap:
                 mc = 0
         self.mc = mc
         self.epochs = torch.zeros(64 + 8, dtype=torch.int32, device=self.dev)     # per-block flag epochs (+ barrier slots)
+        self.local_out = torch.empty(min(self.region // 2, ONESHOT_MAX_BYTES), dtype=torch.uint8, device=self.dev)
+        self.oneshot = os.environ.get("MARY_ONESHOT", "1") != "0"
         torch.cuda.synchronize()
         dist.barrier()
 
@@ -76,6 +80,15 @@ class SymmetricHeap:
         nbytes = (n + pad) * 2
         if nbytes > self.region:
             raise ValueError(f"{nbytes} bytes exceed the symmetric region of {self.region}")
+        if self.oneshot and nbytes <= self.local_out.numel() and pad == 0 and partial.is_contiguous() and partial.data_ptr() % 16 == 0:
+            # small vector: stage, one barrier, every rank sums the whole vector into a local buffer
+            out = self.local_out[:nbytes].view(torch.bfloat16)
+            grid = max(1, min(32, (n // 8 + 2047) // 2048))
+            half = self.region // 2 // 16 * 16
+            check(lib().mary_allreduce_bf16_oneshot(partial.data_ptr(), out.data_ptr(), self.buf_ptrs, self.sig_ptrs, self.mc, self.rank,
+                                                    self.world, self.region, half, n, self.epochs.data_ptr(), grid, 1 if self.mc else 0,
+                                                    self.wait_ns, _stream()), "allreduce_oneshot")
+            return out.view(partial.shape)
         if partial.data_ptr() != self.buf.data_ptr():
             self.buf[:n * 2].view(torch.bfloat16).copy_(partial.reshape(-1))
         if pad:
