@@ -117,7 +117,7 @@ def main():
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--spec", type=int, default=None)
-    ap.add_argument("--comm", default="fused", choices=["fused", "nccl", "sp"],
+    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl", "sp"],
                     help="fused: own all-reduce kernels over peer memory; sp: GEMM->reduce-scatter epilogue + fused norm/all-gather (dense decoders); nccl: library arm")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line then names a reduced config)")
     ap.add_argument("--no-graph", action="store_true")
@@ -171,6 +171,8 @@ def main():
     if args.layers:
         cfg.num_hidden_layers, reduced = args.layers, True
 
+    if args.comm == "auto":       # dense decoder: reduce-scatter / all-gather arm (measured faster at 2 and 8 GPUs); MoE decoders: all-reduce kernels
+        args.comm = "sp" if (is_gemma and world > 1) else "fused"
     say(f"model {cfg.name}, {world} rank(s), batch {B}, ctx {ctx}, spec {k}, comm {args.comm}")
     if world > 1 and args.comm == "nccl":
         # the library arm is launched op by op: recording NCCL collectives into the step graph is not relied upon here
