@@ -42,6 +42,33 @@ __device__ __forceinline__ void unpack(const typename Vec<E>::T& v, float* f) {
   for (int j = 0; j < E / 2; ++j) { float2 t = __bfloat1622float2(h[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
 }
 
+// Sums V values (a power of two, at most 32) over the 32 lanes and leaves ALL V totals in every lane.  Instead of one
+// five-step butterfly per value (5 V shuffles) the values are halved between the lanes at every step (a lane keeps the half its
+// lane bit selects and adds what its partner sends), which costs V - 1 shuffles, and the V totals are then broadcast (V more).
+template <int V>
+__device__ __forceinline__ void warp_sum_vec(float* v, int lane) {
+#pragma unroll
+  for (int o = 16; o >= V; o >>= 1) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) v[i] += __shfl_xor_sync(0xffffffffu, v[i], o);
+  }
+#pragma unroll
+  for (int o = V / 2; o >= 1; o >>= 1) {
+    const int n = 2 * o;                                  // values still held before this step
+    const bool up = (lane & o) != 0;
+#pragma unroll
+    for (int i = 0; i < o; ++i) {
+      const float send = up ? v[i] : v[i + o];
+      const float keep = up ? v[i + o] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+    }
+    (void)n;
+  }
+  const float t = v[0];                                   // the total of value (lane % V)
+#pragma unroll
+  for (int i = 0; i < V; ++i) v[i] = __shfl_sync(0xffffffffu, t, (lane & ~(V - 1)) | i);
+}
+
 template <int D, int RMAX>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(const DecParams p) {
@@ -112,15 +139,15 @@ attn_decode_kernel(const DecParams p) {
         s[j][r] = a;
       }
     }
-    // finish the dot products: butterfly over the 32 lanes for every (key, row)
+    // finish the dot products over the 32 lanes: all KG * RMAX totals end up in every lane
+    {
+      constexpr int NV = KG * RMAX;
+      float* flat = &s[0][0];
+      if constexpr (NV <= 32) {
+        warp_sum_vec<NV>(flat, lane);
+      } else {
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-      for (int j = 0; j < KG; ++j) {
-#pragma unroll
-        for (int r = 0; r < RMAX; ++r) {
-          if (r < R) s[j][r] += __shfl_xor_sync(0xffffffffu, s[j][r], off);
-        }
+        for (int h = 0; h < NV / 32; ++h) warp_sum_vec<32>(flat + 32 * h, lane);
       }
     }
 #pragma unroll

@@ -165,6 +165,38 @@ def bench_moe(E: int = 48, H: int = 7168, F: int = 2048, T: int = 384, k: int = 
     assert K.last_status() == 0
 
 
+def bench_floor(reps: int = 200):
+    """Per-launch cost of decode-sized kernels in steady state: ``reps`` back-to-back launches recorded in one CUDA graph and
+    replayed (what a decode step sees), against the same launches issued eagerly."""
+    from . import cuda as K
+    x = torch.randn(48, 7168, device="cuda").bfloat16()
+    cases = {
+        "gemm 48x128x512 (one tile)": (lambda a=torch.randn(48, 512, device="cuda").bfloat16(), w=torch.randn(128, 512, device="cuda").bfloat16(): K.gemm(a, w)),
+        "gemm 48x2112x7168 (stream-K)": (lambda w=(torch.randn(2112, 7168, device="cuda") * 0.02).bfloat16(): K.linear(x, w)),
+        "gemm 48x7168x8192 (stream-K)": (lambda a=torch.randn(48, 8192, device="cuda").bfloat16(), w=(torch.randn(7168, 8192, device="cuda") * 0.02).bfloat16(): K.linear(a, w)),
+        "gemm 48x384x7168 f32 (router)": (lambda w=(torch.randn(384, 7168, device="cuda") * 0.02).bfloat16(): K.linear_f32(x, w)),
+        "rmsnorm 48x7168": (lambda g=torch.ones(7168, device="cuda").bfloat16(): K.rmsnorm(x, g)),
+    }
+    for name, fn in cases.items():
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        for _ in range(2):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        print(f"{name}: {a.elapsed_time(b) / reps * 1e3:.2f} us per launch in a graph of {reps}")
+    assert K.last_status() == 0
+
+
 def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5):
     """One expert-parallel MoE layer in all-to-all mode with all ranks on this device, phase by phase (the barriers between
     the phases are stream order here): the per-rank cost of counts, plan + dispatch, expert GEMMs and the weighted sum at the
@@ -214,6 +246,8 @@ if __name__ == "__main__":
                 bench_mla(page=pg)
                 bench_mla(Hq=8, page=pg)
                 bench_mla(B=16, page=pg)
+    if what == "floor":
+        bench_floor(*nums)
     if what == "ep":
         bench_ep(*nums)
     if what in ("moe", "all"):
