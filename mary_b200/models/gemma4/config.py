@@ -29,6 +29,13 @@ class Gemma4TextConfig:
     apply_sliding_window: bool = True   # the reference's text path never applies the window (layers.rs:210-234
     #                                     has no caller); it is applied here and can be switched off for parity
     max_position_embeddings: int = 131072
+    hidden_size_per_layer_input: int = 0    # per-layer embeddings (PLE): width of the per-layer token signal, 0 = off
+    vocab_size_per_layer_input: int = 0     # rows of the per-layer embedding table (0 = vocab_size)
+    enable_moe_block: bool = False          # 26B-A4B: a routed expert sum runs beside the dense MLP in every layer
+    num_experts: int = 0
+    top_k_experts: int = 0
+    moe_intermediate_size: int = 0
+    use_double_wide_mlp: bool = False       # KV-shared layers carry an MLP twice as wide
 
     def __post_init__(self):
         if not self.layer_types:
@@ -42,12 +49,24 @@ class Gemma4TextConfig:
         return self.num_hidden_layers - self.num_kv_shared_layers
 
     def kv_source(self, i: int) -> int | None:
-        """The layer whose cache layer ``i`` reads, or ``None`` when it keeps its own: shared sliding layers use layer
-        ``first_shared - 2``, shared full-attention layers ``first_shared - 1`` (src/models/gemma/gemma4/decoder.rs:230-261)."""
+        """The layer whose cache layer ``i`` reads, or ``None`` when it keeps its own: the last layer of the same attention
+        type before sharing starts — ``first_shared - 2`` for sliding and ``first_shared - 1`` for full attention in the shipped
+        layer patterns (src/models/gemma/gemma4/decoder.rs:230-261)."""
         fs = self.first_shared_kv_layer
         if i < fs or self.num_kv_shared_layers == 0:
             return None
-        return fs - 2 if self.is_sliding(i) else fs - 1
+        same = [j for j in range(fs) if self.layer_types[j] == self.layer_types[i]]
+        if not same:
+            raise ValueError(f"KV-shared layer {i} has no earlier layer of type {self.layer_types[i]} to read from")
+        return same[-1]
+
+    def layer_intermediate(self, i: int) -> int:
+        wide = self.use_double_wide_mlp and self.kv_source(i) is not None
+        return self.intermediate_size * (2 if wide else 1)
+
+    @property
+    def ple_vocab(self) -> int:
+        return self.vocab_size_per_layer_input or self.vocab_size
 
     def k_eq_v(self, i: int) -> bool:
         return self.attention_k_eq_v and not self.is_sliding(i)
@@ -84,7 +103,12 @@ class Gemma4TextConfig:
             global_head_dim=d.get("global_head_dim"), num_global_key_value_heads=d.get("num_global_key_value_heads"),
             attention_k_eq_v=bool(d.get("attention_k_eq_v", False)), num_kv_shared_layers=int(d.get("num_kv_shared_layers", 0)),
             apply_sliding_window=bool(d.get("apply_sliding_window", True)),
-            max_position_embeddings=d.get("max_position_embeddings", 131072))
+            max_position_embeddings=d.get("max_position_embeddings", 131072),
+            hidden_size_per_layer_input=int(d.get("hidden_size_per_layer_input") or 0),
+            vocab_size_per_layer_input=int(d.get("vocab_size_per_layer_input") or 0),
+            enable_moe_block=bool(d.get("enable_moe_block", False)), num_experts=int(d.get("num_experts") or 0),
+            top_k_experts=int(d.get("top_k_experts") or 0), moe_intermediate_size=int(d.get("moe_intermediate_size") or 0),
+            use_double_wide_mlp=bool(d.get("use_double_wide_mlp", False)))
 
     def to_json(self) -> dict:
         return {
@@ -99,7 +123,11 @@ class Gemma4TextConfig:
             "tie_word_embeddings": self.tie_word_embeddings, "apply_sliding_window": self.apply_sliding_window,
             "attention_k_eq_v": self.attention_k_eq_v, "num_kv_shared_layers": self.num_kv_shared_layers,
             "global_head_dim": self.global_head_dim, "num_global_key_value_heads": self.num_global_key_value_heads,
-            "max_position_embeddings": self.max_position_embeddings}
+            "max_position_embeddings": self.max_position_embeddings,
+            "hidden_size_per_layer_input": self.hidden_size_per_layer_input,
+            "vocab_size_per_layer_input": self.vocab_size_per_layer_input, "enable_moe_block": self.enable_moe_block,
+            "num_experts": self.num_experts, "top_k_experts": self.top_k_experts,
+            "moe_intermediate_size": self.moe_intermediate_size, "use_double_wide_mlp": self.use_double_wide_mlp}
 
 
 def tiny_config() -> Gemma4TextConfig:

@@ -42,7 +42,7 @@ class Gemma4Layer(nn.Module):
         # a KV-shared layer projects queries only and attends to the cache its source layer filled
         self.kv_source = cfg.kv_source(i)
         self.cache_layer = i if self.kv_source is None else self.kv_source
-        F = cfg.intermediate_size // self.tp.size
+        F = cfg.layer_intermediate(i) // self.tp.size
         self.F = F
         kw = dict(dtype=dtype, device=device)
         P = lambda *s: nn.Parameter(torch.empty(*s, **kw), requires_grad=False)  # noqa: E731
@@ -53,6 +53,20 @@ class Gemma4Layer(nn.Module):
         self.q_norm, self.k_norm = P(D), P(D)
         self.ln_in, self.ln_post_attn, self.ln_pre_ffn, self.ln_post_ffn = P(H), P(H), P(H), P(H)
         self.layer_scalar = 1.0
+        # 26B-A4B: routed experts beside the dense MLP (layers.rs:269-418).  Experts are split over the TP ranks by index.
+        self.moe = bool(cfg.enable_moe_block)
+        if self.moe:
+            E, Fm = cfg.num_experts, cfg.moe_intermediate_size
+            if E % self.tp.size:
+                raise ValueError("num_experts must divide by the tensor-parallel size")
+            self.e_local = E // self.tp.size
+            self.router_scale, self.router_proj, self.per_expert_scale = P(H), P(E, H), P(E)
+            self.ex_gate_up, self.ex_down = P(self.e_local, 2 * Fm, H), P(self.e_local, H, Fm)
+            self.ln_post_ffn_1, self.ln_post_ffn_2, self.ln_pre_ffn_2 = P(H), P(H), P(H)
+        # per-layer embeddings (layers.rs:476-518): a gated low-rank injection of a per-layer token signal
+        self.ple = cfg.hidden_size_per_layer_input
+        if self.ple:
+            self.ple_gate, self.ple_proj, self.ln_post_ple = P(self.ple, H), P(H, self.ple), P(H)
         self.sliding = cfg.is_sliding(i)
         theta = cfg.rope_theta_local if self.sliding else cfg.rope_theta_global
         part = 1.0 if self.sliding else cfg.partial_rotary_factor_global
@@ -60,9 +74,22 @@ class Gemma4Layer(nn.Module):
         self.window = cfg.sliding_window if (self.sliding and cfg.apply_sliding_window) else 0
         self.lora = None  # {"qkv": LoraPair, ...} set by train.lora
 
-    def forward(self, x, h, meta, cache, next_norm):
+    def _routed(self, h):
+        """Routed expert sum of the MoE block, read from the residual BEFORE the dense MLP: weightless norm, learned scale and
+        ``1/sqrt(H)``, softmax over all experts, top-k renormalised, then the per-expert output scale."""
+        c = self.cfg
+        r = ops.rmsnorm(h, self.router_scale * c.hidden_size ** -0.5, c.rms_norm_eps)     # the scale rides on the norm's gain
+        idx, w = ops.router_topk(ops.linear_f32(r, self.router_proj), c.top_k_experts, "softmax", renorm=True)
+        w = w * self.per_expert_scale.float()[idx.long()]
+        x2 = ops.rmsnorm(h, self.ln_pre_ffn_2, c.rms_norm_eps)
+        e0 = self.tp.rank * self.e_local
+        y = dense_experts(x2, idx, w, self.ex_gate_up, self.ex_down, e0, "geglu")
+        return self.tp.reduce(y) if self.tp.size > 1 else y
+
+    def forward(self, x, h, meta, cache, next_norm, ple=None):
         """``x`` = normed input, ``h`` = residual stream.  Returns ``(x_next, h)`` where ``x_next`` is already
-        normed by ``next_norm`` (the next layer's input norm or the final norm)."""
+        normed by ``next_norm`` (the next layer's input norm or the final norm).  ``ple`` = this layer's ``[T, P]``
+        per-layer input when the model has per-layer embeddings."""
         c, L = self.cfg, self.lora or {}
         qkv = ops.linear(x, self.w_qkv)
         if "qkv" in L:
@@ -73,7 +100,7 @@ class Gemma4Layer(nn.Module):
         o = ops.paged_attention(q, cache.k[ci], cache.v[ci], meta, 1.0, self.window)
         o = o.reshape(o.shape[0], -1)
         sp = getattr(self.tp, "sp", None)
-        if sp is not None and x.is_cuda and not L:
+        if sp is not None and x.is_cuda and not L and not self.moe and not self.ple:
             # sequence-parallel residual: ``h`` holds this rank's token rows only.  The row-parallel GEMMs deliver their partial
             # rows to the owners from the epilogue; the owner sums, applies the sandwich norms and all-gathers the next input.
             sp.row_linear_rs(o, self.w_o)
@@ -89,7 +116,36 @@ class Gemma4Layer(nn.Module):
         else:
             m = ops.linear_glu(x, self.w_gu, "geglu")
         d = self.tp.reduce(self.tp.row_linear(m, self.w_down, L.get("down")))
-        return ops.norm_add_norm(d, self.ln_post_ffn, h, next_norm, c.rms_norm_eps, self.layer_scalar)
+        if self.moe:
+            d = ops.rmsnorm(d, self.ln_post_ffn_1, c.rms_norm_eps) + ops.rmsnorm(self._routed(h), self.ln_post_ffn_2, c.rms_norm_eps)
+        if not self.ple:
+            return ops.norm_add_norm(d, self.ln_post_ffn, h, next_norm, c.rms_norm_eps, self.layer_scalar)
+        _, h = ops.norm_add_norm(d, self.ln_post_ffn, h, None, c.rms_norm_eps)
+        g = ops.glu(torch.cat([ops.linear(h, self.ple_gate), ple.to(h.dtype)], -1), "geglu")
+        return ops.norm_add_norm(ops.linear(g, self.ple_proj), self.ln_post_ple, h, next_norm, c.rms_norm_eps, self.layer_scalar)
+
+
+def dense_experts(x, idx, w, gate_up, down, e0: int, act: str):
+    """``sum_k w[t,k] * down[e] (act(gate[e] x_t) * up[e] x_t)`` over the experts ``e0 .. e0 + len(gate_up)`` held here, with
+    unquantised expert weights ``gate_up[E, 2F, H]`` / ``down[E, H, F]``.  Entries are grouped by expert on the host (the
+    reference does the same, layers.rs:328-418); every expert runs the package's fused GLU GEMM on its rows, and the
+    weighted rows are summed per token in f32 in ascending expert order."""
+    T, k = idx.shape
+    out = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
+    flat = idx.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=e0 + gate_up.shape[0]).tolist()
+    start = sum(counts[:e0])
+    for e in range(gate_up.shape[0]):
+        n = counts[e0 + e]
+        if n == 0:
+            continue
+        ent = order[start:start + n]
+        start += n
+        tok = ent // k
+        y = ops.linear(ops.linear_glu(x[tok].contiguous(), gate_up[e], act), down[e])
+        out.index_add_(0, tok, y.float() * w.reshape(-1)[ent].float()[:, None])
+    return out.to(x.dtype)
 
 
 class Gemma4Model(nn.Module):
@@ -102,6 +158,24 @@ class Gemma4Model(nn.Module):
         self.norm = nn.Parameter(torch.empty(cfg.hidden_size, **kw), requires_grad=False)
         self.lm_head = None  # tied
         self.embed_scale = float(torch.tensor(math.sqrt(cfg.hidden_size), dtype=torch.float32))
+        P = cfg.hidden_size_per_layer_input
+        if P:                                          # per-layer embeddings (decoder.rs:114-175)
+            n = cfg.num_hidden_layers
+            self.ple_embed = nn.Parameter(torch.empty(cfg.ple_vocab, n * P, **kw), requires_grad=False)
+            self.ple_model_proj = nn.Parameter(torch.empty(n * P, cfg.hidden_size, **kw), requires_grad=False)
+            self.ple_proj_norm = nn.Parameter(torch.empty(P, **kw), requires_grad=False)
+
+    def per_layer_inputs(self, ids, h0):
+        """``[T, layers, P]``: (norm(proj(h0) / sqrt(H)) + embed_per_layer(ids) * sqrt(P)) / sqrt(2) — the token's own per-layer
+        embedding mixed with a projection of its scaled input embedding ``h0``."""
+        c = self.cfg
+        P, n = c.hidden_size_per_layer_input, c.num_hidden_layers
+        proj = ops.linear(h0, self.ple_model_proj) * (c.hidden_size ** -0.5)
+        proj = ops.rmsnorm(proj.reshape(-1, P), self.ple_proj_norm, c.rms_norm_eps).reshape(-1, n, P)
+        if ids is None:                                # rows given as embeddings (soft tokens) carry no per-layer embedding
+            return proj
+        tok = ops.embed(ids, self.ple_embed, float(torch.tensor(math.sqrt(P), dtype=torch.float32))).reshape(-1, n, P)
+        return ((proj.float() + tok.float()) * (2.0 ** -0.5)).to(h0.dtype)
 
     # -- cache geometry for the runtime
     def kv_spec(self):
@@ -113,14 +187,16 @@ class Gemma4Model(nn.Module):
     def hidden(self, ids, meta, cache):
         """Final-normed hidden states ``[T, H]`` of every row."""
         h = ops.embed(ids, self.embed, self.embed_scale)
+        ple = self.per_layer_inputs(ids, h) if self.cfg.hidden_size_per_layer_input else None
         x = ops.rmsnorm(h, self.layers[0].ln_in, self.cfg.rms_norm_eps)
         sp = getattr(self.tp, "sp", None)
-        if sp is not None and h.is_cuda and not any(l.lora for l in self.layers):
+        plain = not (self.cfg.enable_moe_block or self.cfg.hidden_size_per_layer_input)
+        if sp is not None and h.is_cuda and plain and not any(l.lora for l in self.layers):
             h = sp.residual_slice(h)                 # from here on every rank carries only its own rows of the residual
         n = len(self.layers)
         for i, layer in enumerate(self.layers):
             nxt = self.layers[i + 1].ln_in if i + 1 < n else self.norm
-            x, h = layer(x, h, meta, cache, nxt)
+            x, h = layer(x, h, meta, cache, nxt, None if ple is None else ple[:, i].contiguous())
         return x
 
     def head_weight(self):

@@ -18,11 +18,24 @@ PREFIXES = ("", "model.", "model.language_model.", "language_model.model.", "lan
 
 def tensor_names(cfg: Gemma4TextConfig) -> dict[str, tuple]:
     """Every tensor of the text decoder with its shape (torch ``[out, in]``)."""
-    H, F, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    H, V = cfg.hidden_size, cfg.vocab_size
+    P, n = cfg.hidden_size_per_layer_input, cfg.num_hidden_layers
     out = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,)}
+    if P:
+        out.update({"model.embed_tokens_per_layer.weight": (cfg.ple_vocab, n * P),
+                    "model.per_layer_model_projection.weight": (n * P, H), "model.per_layer_projection_norm.weight": (P,)})
     for i in range(cfg.num_hidden_layers):
-        D, Hq, Hkv = cfg.layer_head_dim(i), cfg.num_attention_heads, cfg.layer_kv_heads(i)
+        D, Hq, Hkv, F = cfg.layer_head_dim(i), cfg.num_attention_heads, cfg.layer_kv_heads(i), cfg.layer_intermediate(i)
         p = f"model.layers.{i}."
+        if P:
+            out.update({p + "per_layer_input_gate.weight": (P, H), p + "per_layer_projection.weight": (H, P),
+                        p + "post_per_layer_input_norm.weight": (H,)})
+        if cfg.enable_moe_block:
+            E, Fm = cfg.num_experts, cfg.moe_intermediate_size
+            out.update({p + "router.proj.weight": (E, H), p + "router.scale": (H,), p + "router.per_expert_scale": (E,),
+                        p + "experts.gate_up_proj": (E, 2 * Fm, H), p + "experts.down_proj": (E, H, Fm),
+                        p + "post_feedforward_layernorm_1.weight": (H,), p + "post_feedforward_layernorm_2.weight": (H,),
+                        p + "pre_feedforward_layernorm_2.weight": (H,)})
         out.update({
             p + "input_layernorm.weight": (H,), p + "post_attention_layernorm.weight": (H,),
             p + "pre_feedforward_layernorm.weight": (H,), p + "post_feedforward_layernorm.weight": (H,),
@@ -42,7 +55,7 @@ def random_weights(cfg: Gemma4TextConfig, seed: int = 0, std: float = 0.02):
     """``normal(0, std)`` for matrices, ones for norm gains — generated tensor by tensor in name order."""
     rng = np.random.default_rng(seed)
     for name, shape in sorted(tensor_names(cfg).items()):
-        if name.endswith("norm.weight") or "layernorm" in name:
+        if name.endswith("norm.weight") or "layernorm" in name or name.endswith(("router.scale", "per_expert_scale")):
             yield name, np.ones(shape, dtype=np.float32)
         else:
             yield name, (rng.standard_normal(shape, dtype=np.float32) * np.float32(std))
@@ -81,6 +94,10 @@ def load_into(model, loader, device=None) -> None:
 
     put(model.embed, get("embed_tokens.weight"))
     put(model.norm, get("norm.weight"))
+    if cfg.hidden_size_per_layer_input:
+        put(model.ple_embed, get("embed_tokens_per_layer.weight"))
+        put(model.ple_model_proj, get("per_layer_model_projection.weight"))
+        put(model.ple_proj_norm, get("per_layer_projection_norm.weight"))
     for i, L in enumerate(model.layers):
         p = f"layers.{i}."
         D = cfg.layer_head_dim(i)
@@ -111,6 +128,20 @@ def load_into(model, loader, device=None) -> None:
         put(L.ln_post_attn, get(p + "post_attention_layernorm.weight"))
         put(L.ln_pre_ffn, get(p + "pre_feedforward_layernorm.weight"))
         put(L.ln_post_ffn, get(p + "post_feedforward_layernorm.weight"))
+        if L.ple:
+            put(L.ple_gate, get(p + "per_layer_input_gate.weight"))
+            put(L.ple_proj, get(p + "per_layer_projection.weight"))
+            put(L.ln_post_ple, get(p + "post_per_layer_input_norm.weight"))
+        if L.moe:                                   # (weights.rs:807-883) experts of this rank: a contiguous index range
+            e0 = r * L.e_local
+            put(L.router_proj, get(p + "router.proj.weight"))
+            put(L.router_scale, get(p + "router.scale"))
+            put(L.per_expert_scale, get(p + "router.per_expert_scale"))
+            put(L.ex_gate_up, get(p + "experts.gate_up_proj")[e0:e0 + L.e_local])
+            put(L.ex_down, get(p + "experts.down_proj")[e0:e0 + L.e_local])
+            put(L.ln_post_ffn_1, get(p + "post_feedforward_layernorm_1.weight"))
+            put(L.ln_post_ffn_2, get(p + "post_feedforward_layernorm_2.weight"))
+            put(L.ln_pre_ffn_2, get(p + "pre_feedforward_layernorm_2.weight"))
         if loader.has_weight(pre + p + "layer_scalar"):
             L.layer_scalar = float(loader.load_host_f32(pre + p + "layer_scalar").reshape(-1)[0])
     if not cfg.tie_word_embeddings and loader.has_weight("lm_head.weight"):
@@ -138,6 +169,9 @@ def shard_from_full(full, tp, device=None):
     with torch.no_grad():
         m.embed.copy_(full.embed)
         m.norm.copy_(full.norm)
+        if cfg.hidden_size_per_layer_input:
+            for nm in ("ple_embed", "ple_model_proj", "ple_proj_norm"):
+                getattr(m, nm).copy_(getattr(full, nm))
         for L, Fl in zip(m.layers, full.layers):
             D, H = L.D, cfg.hidden_size
             q, k, v = Fl.w_qkv.split([Fl.n_q * D, Fl.n_kv * D, Fl.n_kv * D], 0)
@@ -149,7 +183,14 @@ def shard_from_full(full, tp, device=None):
             g, u = Fl.w_gu[:Fl.F], Fl.w_gu[Fl.F:]
             L.w_gu.copy_(torch.cat([g[r * L.F:(r + 1) * L.F], u[r * L.F:(r + 1) * L.F]], 0))
             L.w_down.copy_(Fl.w_down[:, r * L.F:(r + 1) * L.F])
-            for nm in ("q_norm", "k_norm", "ln_in", "ln_post_attn", "ln_pre_ffn", "ln_post_ffn"):
+            names = ["q_norm", "k_norm", "ln_in", "ln_post_attn", "ln_pre_ffn", "ln_post_ffn"]
+            if L.ple:
+                names += ["ple_gate", "ple_proj", "ln_post_ple"]
+            if L.moe:
+                names += ["router_proj", "router_scale", "per_expert_scale", "ln_post_ffn_1", "ln_post_ffn_2", "ln_pre_ffn_2"]
+                L.ex_gate_up.copy_(Fl.ex_gate_up[r * L.e_local:(r + 1) * L.e_local])
+                L.ex_down.copy_(Fl.ex_down[r * L.e_local:(r + 1) * L.e_local])
+            for nm in names:
                 getattr(L, nm).copy_(getattr(Fl, nm))
             L.layer_scalar = Fl.layer_scalar
     return m

@@ -91,7 +91,7 @@ def bench_attn(cases=None):
                 gb = B * span * Hkv * D * 2 * 2 / ms / 1e6
                 print(f"decode attn [{kernel}, target {ctas} CTAs] B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, "
                       f"{gb:.0f} GB/s, {gb / hbm:.2f} {tag}")
-        K.DECODE_TARGET_CTAS = 1184
+        K.DECODE_TARGET_CTAS = 2368
 
 
 def bench_fa(B: int = 1, L: int = 4096, Hq: int = 16, Hkv: int = 16, DK: int = 192, DV: int = 128, window: int = 0, iters: int = 5):

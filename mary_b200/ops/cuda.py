@@ -278,7 +278,7 @@ def _q_blocks(meta, rq: int):
 declare("mary_paged_attention_decode", "ppppppppp" + "iii" + "llll" + "iiiiii" + "ff" + "ps")
 
 
-DECODE_TARGET_CTAS = 1184      # CTAs the decode attention kernel aims for when it picks the number of kv splits (8 per SM)
+DECODE_TARGET_CTAS = 2368      # CTAs the decode attention kernel aims for when it picks the number of kv splits (16 per SM)
 
 
 def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsplit):
