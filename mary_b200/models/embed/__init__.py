@@ -1,1 +1,3 @@
 from .clip import ClipConfig, ClipEmbedder, load_into  # noqa: F401
+from .nomic import NomicConfig, NomicTextEmbedder  # noqa: F401
+from .siglip import SiglipConfig, SiglipEmbedder  # noqa: F401

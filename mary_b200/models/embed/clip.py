@@ -51,10 +51,16 @@ def quick_gelu(x):
     return x * torch.sigmoid(1.702 * x)
 
 
+def gelu_tanh(x):
+    return F.gelu(x, approximate="tanh")
+
+
 class Block(nn.Module):
-    def __init__(self, H, heads, ffn):
+    """Pre-LayerNorm transformer block with biases; ``act`` is the MLP's activation (quick-GELU for CLIP)."""
+
+    def __init__(self, H, heads, ffn, act=quick_gelu):
         super().__init__()
-        self.heads = heads
+        self.heads, self.act = heads, act
         self.ln1_w, self.ln1_b, self.ln2_w, self.ln2_b = _P(H), _P(H), _P(H), _P(H)
         self.w_qkv, self.b_qkv = _P(3 * H, H), _P(3 * H)
         self.w_o, self.b_o = _P(H, H), _P(H)
@@ -69,7 +75,7 @@ class Block(nn.Module):
         a = F.scaled_dot_product_attention(q, k, v, is_causal=causal).transpose(1, 2).reshape(B * T, H)
         x = x + (ops.linear(a, self.w_o).float() + self.b_o.float()).to(x.dtype).view(B, T, H)
         h = F.layer_norm(x, (H,), self.ln2_w, self.ln2_b, eps).reshape(B * T, H)
-        m = quick_gelu((ops.linear(h, self.w_fc1).float() + self.b_fc1.float())).to(x.dtype)
+        m = self.act((ops.linear(h, self.w_fc1).float() + self.b_fc1.float())).to(x.dtype)
         return x + (ops.linear(m, self.w_fc2).float() + self.b_fc2.float()).to(x.dtype).view(B, T, H)
 
 
@@ -151,6 +157,14 @@ def load_into(m: ClipEmbedder, loader) -> None:
     put(m.fin_b, "text_model.final_layer_norm.bias")
     put(m.t_proj, "text_projection.weight")
     for tower, blocks in (("vision_model", m.v_blocks), ("text_model", m.t_blocks)):
+        load_blocks(blocks, tower, get)
+
+
+def load_blocks(blocks, tower: str, get) -> None:
+    """Fill ``Block`` s from the ``<tower>.encoder.layers.<i>.*`` names that the CLIP and SigLIP checkpoints share."""
+    def put(p, n):
+        p.data.copy_(get(n).reshape(p.shape))
+    if True:
         for i, b in enumerate(blocks):
             p = f"{tower}.encoder.layers.{i}."
             b.w_qkv.data.copy_(torch.cat([get(p + f"self_attn.{n}_proj.weight") for n in "qkv"], 0))
