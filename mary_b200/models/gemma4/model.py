@@ -184,9 +184,15 @@ class Gemma4Model(nn.Module):
                     kv_heads=[max(c.layer_kv_heads(i) // self.tp.size, 1) for i in range(c.num_hidden_layers)],
                     head_dim=[c.layer_head_dim(i) for i in range(c.num_hidden_layers)])
 
-    def hidden(self, ids, meta, cache):
-        """Final-normed hidden states ``[T, H]`` of every row."""
+    def hidden(self, ids, meta, cache, soft=None):
+        """Final-normed hidden states ``[T, H]`` of every row.  ``soft = (rows, embeds)`` replaces the embedding of the placeholder
+        rows ``rows`` (a long tensor) by multimodal soft tokens ``embeds [len(rows), H]`` (unscaled, lm.rs:212-311); those rows take
+        the pad token's per-layer embedding."""
         h = ops.embed(ids, self.embed, self.embed_scale)
+        if soft is not None:
+            rows, emb = soft
+            h = h.index_copy(0, rows, emb.to(h.dtype))
+            ids = ids.clone().index_fill_(0, rows, 0)
         ple = self.per_layer_inputs(ids, h) if self.cfg.hidden_size_per_layer_input else None
         x = ops.rmsnorm(h, self.layers[0].ln_in, self.cfg.rms_norm_eps)
         sp = getattr(self.tp, "sp", None)
@@ -205,9 +211,9 @@ class Gemma4Model(nn.Module):
     def logits(self, x):
         return ref.softcap(ops.linear(x, self.head_weight()).float(), self.cfg.final_logit_softcapping)
 
-    def forward(self, ids, meta, cache, rows=None):
+    def forward(self, ids, meta, cache, rows=None, soft=None):
         """Logits (f32, soft-capped) of ``rows`` (all rows when ``None``)."""
-        x = self.hidden(ids, meta, cache)
+        x = self.hidden(ids, meta, cache, soft)
         if rows is not None:
             x = x[rows]
         return self.logits(x)

@@ -1,0 +1,88 @@
+"""Gemma-4 vision tower against the Hugging Face implementation (random tiny weights loaded by name): a non-square image, with and
+without clipped linears, through patch embedding, 2-D rotary blocks, position pooling and the multimodal projection."""
+import pytest
+import torch
+
+from mary_b200.models.gemma4.vision import Gemma4VisionConfig, Gemma4VisionTower, load_into, patchify
+
+
+class _DictLoader:
+    def __init__(self, sd):
+        self.sd = sd
+
+    def has_weight(self, n):
+        return n in self.sd
+
+    def load_tensor(self, n, dtype):
+        return self.sd[n].to(dtype)
+
+
+@pytest.mark.parametrize("clipped", [False, True])
+def test_soft_tokens_match_huggingface(clipped):
+    pytest.importorskip("transformers")
+    from transformers.models.gemma4.configuration_gemma4 import Gemma4TextConfig, Gemma4VisionConfig as HFV
+    from transformers.models.gemma4.modeling_gemma4 import Gemma4MultimodalEmbedder, Gemma4VisionModel
+    c = Gemma4VisionConfig.tiny()
+    torch.manual_seed(0)
+    hv = HFV(hidden_size=c.hidden, intermediate_size=c.ffn, num_hidden_layers=c.layers, num_attention_heads=c.heads,
+             num_key_value_heads=c.kv_heads, head_dim=c.head_dim, patch_size=c.patch, position_embedding_size=c.pos_size,
+             pooling_kernel_size=c.pool, rope_parameters={"rope_type": "default", "rope_theta": c.theta}, use_clipped_linears=clipped)
+    hv._attn_implementation = "eager"
+    tower = Gemma4VisionModel(hv).eval()
+    emb = Gemma4MultimodalEmbedder(hv, Gemma4TextConfig(hidden_size=c.text_hidden, num_hidden_layers=2, num_attention_heads=2,
+                                                        intermediate_size=32, vocab_size=64, head_dim=8, global_head_dim=8)).eval()
+    with torch.no_grad():
+        for n, p in tower.named_parameters():
+            p.copy_((1.0 + 0.1 * torch.randn_like(p)) if p.dim() == 1 else 0.2 * torch.randn_like(p))
+        if clipped:
+            for mod in tower.modules():
+                if hasattr(mod, "input_min"):
+                    mod.input_min.fill_(-0.8), mod.input_max.fill_(0.9), mod.output_min.fill_(-1.5), mod.output_max.fill_(1.2)
+    sd = {"model.vision_tower." + k: v.detach() for k, v in tower.state_dict().items()}
+    sd.update({"model.embed_vision." + k: v.detach() for k, v in emb.state_dict().items()})
+    m = Gemma4VisionTower(c)
+    load_into(m, _DictLoader(sd))
+
+    image = torch.rand(3, 4 * c.patch, 6 * c.patch)                    # 4 x 6 patches -> 2 x 3 soft tokens
+    patches, pos = patchify(image, c.patch)
+    with torch.no_grad():
+        want = emb(tower(pixel_values=patches[None], pixel_position_ids=pos[None]).last_hidden_state)
+        got = m(patches, pos)
+    assert got.shape == (6, c.text_hidden)
+    assert torch.allclose(got, want, atol=2e-4, rtol=2e-4), float((got - want).abs().max())
+    if clipped:
+        assert all(L.q.clipped for L in m.layers)
+
+
+def test_patchify_orders_patches_row_major_with_xy_positions():
+    img = torch.arange(3 * 4 * 6, dtype=torch.float32).reshape(3, 4, 6)
+    p, pos = patchify(img, 2)
+    assert p.shape == (6, 12) and pos.tolist() == [[0, 0], [1, 0], [2, 0], [0, 1], [1, 1], [2, 1]]
+    assert p[1, :3].tolist() == [img[0, 0, 2].item(), img[1, 0, 2].item(), img[2, 0, 2].item()]
+
+
+def test_soft_tokens_replace_placeholder_rows_in_the_decoder():
+    from mary_b200.models.gemma4.config import Gemma4TextConfig
+    from mary_b200.models.gemma4.model import Gemma4Model
+    from mary_b200.models.gemma4.weights import init_random_
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    cfg = Gemma4TextConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=32, intermediate_size=96, vocab_size=100,
+                           hidden_size_per_layer_input=8)
+    m = Gemma4Model(cfg)
+    init_random_(m, 0, std=0.05)
+
+    def run(ids, soft=None):
+        spec = m.kv_spec()
+        cache = PagedKVCache(spec["num_layers"], 4, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32)
+        cache.alloc.extend(0, len(ids))
+        table, lens = cache.alloc.page_table([0])
+        with torch.no_grad():
+            return m(torch.tensor(ids, dtype=torch.int32), BatchMeta.build([len(ids)], lens, table, 16), cache, soft=soft)
+    ids = [2, 7, 99, 99, 9]
+    rows = torch.tensor([2, 3])
+    # soft tokens equal to the scaled embedding of token 0 must reproduce the prompt with token 0 in the placeholder rows
+    emb0 = (m.embed[0] * m.embed_scale).expand(2, -1)
+    assert torch.allclose(run(ids, (rows, emb0)), run([2, 7, 0, 0, 9]), atol=1e-5)
+    other = run(ids, (rows, torch.randn(2, 64)))
+    assert (other[-1] - run(ids)[-1]).abs().max() > 1e-4
