@@ -66,6 +66,32 @@ class GemmaLM:
         finally:
             self.engine.eos = eos
 
+    def complete_multimodal(self, ids, soft_rows, soft_embeds, max_new: int, stop_on_eos: bool = True) -> list[int]:
+        """Greedy continuation of a prompt whose placeholder rows ``soft_rows`` carry vision / audio soft tokens ``soft_embeds``
+        (the outputs of ``Gemma4VisionTower`` / ``Gemma4AudioTower``) instead of token embeddings — the splice of
+        src/models/gemma/gemma4/lm.rs:212-311 and the ``gemma_hear`` / ``gemma_listen`` loops."""
+        from ...runtime.batch import BatchMeta
+        seq, alloc, page = (1 << 30) - 1, self.cache.alloc, self.cache.page_size        # a sequence id the engine never hands out
+        ids = [int(t) for t in ids]
+        out: list[int] = []
+        try:
+            with torch.no_grad():
+                alloc.extend(seq, len(ids))
+                table, lens = alloc.page_table([seq])
+                meta = BatchMeta.build([len(ids)], lens, table, page, device=self.device)
+                soft = (torch.as_tensor(soft_rows, dtype=torch.long, device=self.device), soft_embeds.to(self.device))
+                tok = int(self.model.greedy(torch.tensor(ids, dtype=torch.int32, device=self.device), meta, self.cache, [len(ids) - 1], soft)[0])
+                while True:
+                    out.append(tok)
+                    if len(out) >= max_new or (stop_on_eos and tok in self.engine.eos):
+                        return out
+                    alloc.extend(seq, 1)
+                    table, lens = alloc.page_table([seq])
+                    meta = BatchMeta.build([1], lens, table, page, device=self.device)
+                    tok = int(self.model.greedy(torch.tensor([tok], dtype=torch.int32, device=self.device), meta, self.cache, [0])[0])
+        finally:
+            alloc.release(seq)
+
     def complete(self, text: str, max_new: int = 128, stop: list[str] | None = None) -> str:
         if self.tokenizer is None:
             raise RuntimeError("this pile holds no tokenizer; use complete_ids")

@@ -218,7 +218,7 @@ class Gemma4Model(nn.Module):
             x = x[rows]
         return self.logits(x)
 
-    def greedy(self, ids, meta, cache, rows):
-        x = self.hidden(ids, meta, cache)[rows]
+    def greedy(self, ids, meta, cache, rows, soft=None):
+        x = self.hidden(ids, meta, cache, soft)[rows]
         tok, _ = ops.lm_head_argmax(x, self.head_weight(), self.cfg.final_logit_softcapping)
         return tok

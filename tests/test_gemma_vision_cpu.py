@@ -86,3 +86,19 @@ def test_soft_tokens_replace_placeholder_rows_in_the_decoder():
     assert torch.allclose(run(ids, (rows, emb0)), run([2, 7, 0, 0, 9]), atol=1e-5)
     other = run(ids, (rows, torch.randn(2, 64)))
     assert (other[-1] - run(ids)[-1]).abs().max() > 1e-4
+
+
+def test_lm_multimodal_completion_equals_token_completion_when_soft_tokens_are_token_embeddings():
+    from mary_b200.models.gemma4.config import Gemma4TextConfig
+    from mary_b200.models.gemma4.lm import GemmaLM
+    from mary_b200.models.gemma4.model import Gemma4Model
+    from mary_b200.models.gemma4.weights import init_random_
+    cfg = Gemma4TextConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=32, intermediate_size=96, vocab_size=100)
+    m = Gemma4Model(cfg)
+    init_random_(m, 0, std=0.05)
+    lm = GemmaLM(m, max_seq=64, max_batch=2)
+    want = lm.complete_ids([2, 7, 0, 0, 9], 6)
+    emb0 = (m.embed[0] * m.embed_scale).expand(2, -1)
+    got = lm.complete_multimodal([2, 7, 99, 99, 9], [2, 3], emb0, 6, stop_on_eos=False)
+    assert got == want
+    assert lm.cache.alloc.free_pages == lm.cache.alloc.num_pages            # the private sequence was released
