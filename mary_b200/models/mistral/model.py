@@ -174,6 +174,22 @@ class MistralModel(nn.Module):
             x, h = layer(x, h, meta, cache, self.layers[i + 1].ln_attn if i + 1 < n else self.norm)
         return x
 
+    def layer_states(self, ids, meta, cache, wanted):
+        """Residual stream after the decoder layers in ``wanted`` (1-based: entry ``i`` is the state after ``i`` layers, 0 the input
+        embeddings) — what image / speech models read when they use this decoder as a text encoder."""
+        c = self.cfg
+        h = ops.embed(ids, self.embed)
+        out = {0: h.clone()} if 0 in wanted else {}
+        x = ops.rmsnorm(h, self.layers[0].ln_attn, c.rms_norm_eps)
+        n = len(self.layers)
+        for i, layer in enumerate(self.layers):
+            if i >= max(wanted):
+                break
+            x, h = layer(x, h, meta, cache, self.layers[i + 1].ln_attn if i + 1 < n else self.norm)
+            if i + 1 in wanted:
+                out[i + 1] = h.clone()
+        return out
+
     def forward(self, ids, meta, cache, rows=None):
         x = self.hidden(ids, meta, cache)
         if rows is not None:
