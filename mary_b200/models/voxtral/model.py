@@ -188,7 +188,7 @@ class VoxtralModel(nn.Module):
         def meta(cache, n):
             cache.alloc.extend(0, n)
             table, lens = cache.alloc.page_table([0])
-            return BatchMeta.build([n], lens, table, page)
+            return BatchMeta.build([n], lens, table, page, device=self.embed.device)
         x, _ = self.stem(mel.to(self.embed.device))
         audio = self.project(self.encode(x, meta(ac, x.shape[0]), ac))
         h = (self.embed[torch.as_tensor(ids, device=self.embed.device).long()].float() + audio[:T].float()).to(self.embed.dtype)
@@ -216,7 +216,7 @@ class VoxtralListener:
     def _meta(self, cache, n):
         cache.alloc.extend(0, n)
         table, lens = cache.alloc.page_table([0])
-        return BatchMeta.build([n], lens, table, self.page)
+        return BatchMeta.build([n], lens, table, self.page, device=self.m.embed.device)
 
     @torch.no_grad()
     def feed(self, mel, forced=None):

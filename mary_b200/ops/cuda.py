@@ -105,6 +105,8 @@ def gemm(x, w, out=None, bias=None, alpha: float = 1.0, glu: str | None = None, 
     """``out[M, N] = alpha * x[M, K] @ w[N, K]^T``.  ``glu``: ``w = [gate; up]`` (2N rows) and the epilogue writes
     ``act(gate) * up``.  ``epi``: ``"bf16"`` store, ``"f32"`` store, ``"red"`` accumulate into a zeroed f32 ``out``."""
     _bf16(x), _bf16(w)
+    if bias is not None and bias.dtype != torch.float32:
+        bias = bias.float()                       # the epilogue reads an f32 bias vector
     M, K = x.shape
     n_w = w.shape[0]
     N = n_w // 2 if glu else n_w
@@ -156,6 +158,8 @@ def gemm_splitk(x, w, split_k: int, out=None, f32: bool = False, bias=None, swap
     equal contiguous runs, one per SM, so every SM streams the same share of the weights whatever the tile count.  Falls back
     to the atomic path when the shape outgrows the scratch."""
     _bf16(x), _bf16(w)
+    if bias is not None and bias.dtype != torch.float32:
+        bias = bias.float()
     M, K = x.shape
     N = w.shape[0]
     ws, cnt = _sk_workspace(x.device)

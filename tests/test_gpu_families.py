@@ -1,0 +1,145 @@
+"""Every model family beside the flagship decoders on the GPU: the same random weights run in f32 on the CPU (PyTorch reference
+ops) and in bf16 on the GPU (the package's CUDA kernels for GEMMs, norms, GLU, rotary / cache append and paged attention), and the
+outputs must agree to bf16 accuracy.  Dimensions are small but kernel-shaped (multiples of 64, head dim 64)."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _gpu(m):
+    """Parameters to bf16 on the GPU; buffers (rotary frequencies, clip bounds) keep their dtype."""
+    g = copy.deepcopy(m)
+    for p in g.parameters():
+        p.data = p.data.to("cuda", torch.bfloat16)
+    for mod in g.modules():
+        for k, b in list(mod._buffers.items()):
+            if b is not None:
+                mod._buffers[k] = b.to("cuda")
+    return g
+
+
+def _init(m, seed=0, std=0.05):
+    gen = torch.Generator().manual_seed(seed)
+    for n, p in m.named_parameters():
+        if p.dim() == 1:
+            p.data.copy_((0.0 if n.split(".")[-1].startswith("b") or "bias" in n or n.endswith("_b") else 1.0) + 0.05 * torch.randn(p.shape, generator=gen))
+        else:
+            p.data.normal_(0.0, std, generator=gen)
+    return m
+
+
+def _close(got, want, tol=0.06):
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).norm() / want.norm().clamp_min(1e-6)
+    assert torch.isfinite(got).all() and err < tol, float(err)
+
+
+def _meta(cache, n, dev, page=16):
+    from mary_b200.runtime.batch import BatchMeta
+    cache.alloc.extend(0, n)
+    table, lens = cache.alloc.page_table([0])
+    return BatchMeta.build([n], lens, table, page, device=dev)
+
+
+def test_gemma_with_per_layer_embeddings_and_routed_experts():
+    from mary_b200.models.gemma4.config import Gemma4TextConfig
+    from mary_b200.models.gemma4.model import Gemma4Model
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    cfg = Gemma4TextConfig(hidden_size=256, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                           intermediate_size=512, vocab_size=512, sliding_window=32, hidden_size_per_layer_input=64, enable_moe_block=True,
+                           num_experts=8, top_k_experts=2, moe_intermediate_size=128, num_kv_shared_layers=2)
+    m = _init(Gemma4Model(cfg), std=0.03)
+    g = _gpu(m)
+    g.dtype = torch.bfloat16
+    ids = torch.randint(0, 512, (40,), dtype=torch.int32)
+    outs = []
+    for model, dev, dt in ((m, "cpu", torch.float32), (g, "cuda", torch.bfloat16)):
+        spec = model.kv_spec()
+        cache = PagedKVCache(spec["num_layers"], 8, 16, spec["kv_heads"], spec["head_dim"], dtype=dt, device=dev)
+        with torch.no_grad():
+            outs.append(model(ids.to(dev), _meta(cache, 40, dev), cache))
+    _close(outs[1], outs[0], 0.08)
+
+
+def test_embedders_siglip_and_nomic():
+    from mary_b200.models.embed import NomicConfig, NomicTextEmbedder, SiglipConfig, SiglipEmbedder
+    c = SiglipConfig(image_size=64, patch=16, v_hidden=128, v_layers=2, v_heads=2, v_ffn=256, t_vocab=200, t_ctx=16, t_hidden=128, t_layers=2,
+                     t_heads=2, t_ffn=256)
+    m = _init(SiglipEmbedder(c))
+    g = _gpu(m)
+    px, ids = torch.randn(2, 3, 64, 64), torch.randint(0, 200, (2, 16))
+    with torch.no_grad():
+        _close(g.embed_image(px.cuda().bfloat16()), m.embed_image(px))
+        _close(g.embed_text(ids.cuda()), m.embed_text(ids))
+    n = _init(NomicTextEmbedder(NomicConfig(vocab_size=300, hidden=128, layers=2, heads=2, ffn=256)))
+    ng = _gpu(n)
+    ids = torch.randint(1, 300, (2, 24))
+    with torch.no_grad():
+        _close(ng.embed_text(ids.cuda()), n.embed_text(ids))
+
+
+def test_qwen25vl_embedder():
+    from mary_b200.models.qwen2_5_vl import BiQwenEmbedder, Qwen25VLConfig
+    c = Qwen25VLConfig(v_depth=2, v_hidden=128, v_heads=2, v_ffn=256, patch=8, temporal_patch=2, merge=2, window=32, fullatt_blocks=(1,),
+                       vocab=300, hidden=128, layers=2, heads=2, kv_heads=1, ffn=256, rope_theta=1e4, mrope_section=(8, 12, 12), image_token=299)
+    m = _init(BiQwenEmbedder(c))
+    g = _gpu(m)
+    grids = [(1, 8, 4)]
+    patches = torch.randn(32, 3 * 2 * 8 * 8)
+    ids = [5, 6] + [299] * 8 + [7, 8]
+    with torch.no_grad():
+        _close(g.embed(ids, patches.cuda().bfloat16(), grids), m.embed(ids, patches, grids))
+
+
+def test_voxtral_streaming_on_the_paged_cache():
+    from mary_b200.models.voxtral import VoxtralConfig, VoxtralModel
+    c = VoxtralConfig(n_mels=32, a_hidden=128, a_layers=2, a_heads=2, a_head_dim=64, a_ffn=256, a_window=16, a_theta=1e4, vocab=256,
+                      hidden=128, layers=2, heads=2, kv_heads=1, head_dim=64, ffn=256, theta=1e4, window=64, delay_tokens=2, pad=5)
+    m = _init(VoxtralModel(c))
+    g = _gpu(m)
+    mel = torch.randn(32, 8 * 12)
+    ids = torch.randint(6, 256, (12,)).tolist()
+    _close(g(ids, mel.cuda().bfloat16()), m(ids, mel), 0.08)
+
+
+def test_gemma_vision_and_audio_towers():
+    from mary_b200.models.gemma4.audio import Gemma4AudioConfig, Gemma4AudioTower
+    from mary_b200.models.gemma4.vision import Gemma4VisionConfig, Gemma4VisionTower, patchify
+    v = _init(Gemma4VisionTower(Gemma4VisionConfig(hidden=128, layers=2, heads=2, kv_heads=2, head_dim=64, ffn=256, patch=8, pos_size=64, pool=2,
+                                                   text_hidden=128)))
+    patches, pos = patchify(torch.rand(3, 32, 48), 8)
+    with torch.no_grad():
+        _close(_gpu(v)(patches.cuda().bfloat16(), pos.cuda()), v(patches, pos))
+    a = _init(Gemma4AudioTower(Gemma4AudioConfig(n_mels=32, hidden=128, layers=2, heads=2, conv_channels=(32, 16), context_left=13, out_dims=64,
+                                                 text_hidden=128)))
+    mel = torch.randn(96, 32)
+    with torch.no_grad():
+        _close(_gpu(a)(mel.cuda().bfloat16()), a(mel), 0.08)
+
+
+def test_flow_models_smolvla_f5_flux():
+    from mary_b200.models.f5 import DiT, F5Config
+    from mary_b200.models.flux import Flux2Config, Flux2Transformer, position_ids
+    from mary_b200.models.smolvla import SmolVLA, SmolVLAConfig, TowerConfig
+    c = SmolVLAConfig(vlm=TowerConfig(128, 2, 2, 1, 64, 256), expert=TowerConfig(64, 2, 2, 1, 64, 128), vocab=100, image_size=32, patch=8,
+                      v_hidden=64, v_layers=1, v_heads=2, v_ffn=128, shuffle=2, action_dim=8, state_dim=8, expressive_dim=3, chunk_size=8, num_steps=2)
+    s = _init(SmolVLA(c), std=0.08)
+    sg = _gpu(s)
+    img, state, noisy = torch.rand(3, 32, 32) * 2 - 1, torch.randn(8), torch.randn(8, 8)
+    with torch.no_grad():
+        want = s.denoise(s.prefix_cache(*s.embed_prefix([img], [3, 4, 5], state)), noisy, torch.tensor(0.5))
+        got = sg.denoise(sg.prefix_cache(*sg.embed_prefix([img.cuda().bfloat16()], [3, 4, 5], state.cuda())), noisy.cuda().bfloat16(), torch.tensor(0.5).cuda())
+    _close(got, want, 0.08)
+    d = _init(DiT(F5Config(dim=128, depth=2, heads=2, n_mels=16, text_vocab=40, text_dim=64, conv_layers=1, pos_kernel=7, pos_groups=4, time_freq=32)), std=0.08)
+    x, cond = torch.randn(24, 16), torch.randn(24, 16)
+    with torch.no_grad():
+        _close(_gpu(d)(x.cuda().bfloat16(), cond.cuda().bfloat16(), [1, 2, 3], 0.4), d(x, cond, [1, 2, 3], 0.4), 0.08)
+    fc = Flux2Config(heads=2, head_dim=64, layers=1, single_layers=1, joint_dim=64, in_channels=16, mlp_ratio=2.0, axes_dims=(16, 16, 16, 16), time_channels=32)
+    f = _init(Flux2Transformer(fc), std=0.08)
+    lat, txt = torch.randn(12, 16), torch.randn(5, 64)
+    with torch.no_grad():
+        _close(_gpu(f)(lat.cuda().bfloat16(), txt.cuda().bfloat16(), 0.6, position_ids(3, 4), position_ids(n_text=5)),
+               f(lat, txt, 0.6, position_ids(3, 4), position_ids(n_text=5)), 0.08)
