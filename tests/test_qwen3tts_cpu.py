@@ -1,6 +1,7 @@
 """Qwen3-TTS frame generator on a tiny configuration: the predictor's cached steps equal one uncached pass, the logits
 processor follows the reference rules, and the frame loop is deterministic, streams and stops."""
 import numpy as np
+import pytest
 import torch
 
 from mary_b200 import ops
@@ -71,3 +72,49 @@ def test_frame_loop_is_deterministic_streams_and_stops():
     d = generate_frames(t, p, prefill, trailing, pad, params, on_frame=lambda f: (seen.append(f), len(seen) < 3)[1])
     assert len(seen) == min(3, a.shape[0]) and d.shape[0] == min(2, a.shape[0])
     assert np.array_equal(d, a[:d.shape[0]])
+
+
+def test_speaker_mel_matches_the_library_filterbank_and_ecapa_pooling_rules():
+    import math
+
+    import numpy as np
+    from mary_b200.models.qwen3tts.speaker import Ecapa, EcapaConfig, slaney_mel_filters, speaker_mel
+    audio_utils = pytest.importorskip("transformers.audio_utils")
+    want = audio_utils.mel_filter_bank(num_frequency_bins=513, num_mel_filters=128, min_frequency=0.0, max_frequency=12000.0, sampling_rate=24000,
+                                       norm="slaney", mel_scale="slaney")
+    got = slaney_mel_filters(128, 1024, 24000, 0.0, 12000.0)
+    assert np.allclose(got.numpy().T, want, atol=1e-6)
+    wave = torch.randn(256 * 20)
+    mel = speaker_mel(wave)
+    assert mel.shape == (128, 20) and mel.min() >= math.log(1e-5) - 1e-6
+    # against torch.stft with the same padding convention
+    x = torch.nn.functional.pad(wave[None, None], (384, 384), mode="reflect")[0, 0]
+    spec = torch.stft(x, 1024, 256, window=torch.hann_window(1024), center=False, return_complex=True)
+    ref = (got @ torch.sqrt(spec.real ** 2 + spec.imag ** 2 + 1e-9)).clamp_min(1e-5).log()
+    assert torch.allclose(mel, ref, atol=2e-3)
+
+    c = EcapaConfig.tiny()
+    m = Ecapa(c)
+    g = torch.Generator().manual_seed(0)
+    for n, p in m.named_parameters():
+        p.data.normal_(0.0, 0.2, generator=g)
+    feats = torch.randn(c.n_mels, 37)
+    v = m(feats)
+    assert v.shape == (c.out_dim,) and torch.isfinite(v).all()
+    assert m.tdnn0(feats).shape[1] == 37 and m.blocks[2](torch.randn(c.channels, 37)).shape == (c.channels, 37)     # "same" by reflection
+    # zero attention weights: uniform attention, so the pooled statistics are the plain mean and standard deviation
+    x = torch.randn(c.channels * 3, 11)
+    m.att2.w.data.zero_(), m.att2.b.data.zero_()
+    p = m.pool(x)
+    assert torch.allclose(p[:x.shape[0], 0], x.mean(1), atol=1e-5) and torch.allclose(p[x.shape[0]:, 0], x.std(1, unbiased=False), atol=1e-5)
+    # Res2Net: the first channel group passes through the middle stage untouched
+    b = m.blocks[0]
+    h = torch.randn(c.channels, 9)
+    grp = c.channels // c.res2net_scale
+    saved = b.tdnn2.w.data.clone()
+    b.tdnn2.w.data.zero_()
+    b.tdnn2.w.data[:grp, :grp, 0] = torch.eye(grp)
+    b.tdnn2.b.data.zero_()
+    b.se2.w.data.zero_(), b.se2.b.data.fill_(20.0)                      # gate = 1
+    assert torch.allclose((b(h) - h)[:grp], torch.relu(b.tdnn1(h)[:grp]), atol=1e-5)
+    b.tdnn2.w.data.copy_(saved)
