@@ -191,6 +191,36 @@ class CFM:
         return x
 
 
+def load_into(m: DiT, loader, prefix: str = "ema_model.transformer.") -> None:
+    """Names of the ``F5TTS_v1_Base`` checkpoint (docs/F5_ARCH.md of the reference lists them)."""
+    dt = m.in_w.dtype
+
+    def get(n):
+        return loader.load_tensor(prefix + n, dt)
+
+    def put(p, n):
+        p.data.copy_(get(n).reshape(p.shape))
+    put(m.text_embed, "text_embed.text_embed.weight")
+    for i, b in enumerate(m.text_blocks):
+        t = f"text_embed.text_blocks.{i}."
+        for p, n in ((b.dw_w, "dwconv.weight"), (b.dw_b, "dwconv.bias"), (b.ln_w, "norm.weight"), (b.ln_b, "norm.bias"), (b.w1, "pwconv1.weight"),
+                     (b.b1, "pwconv1.bias"), (b.w2, "pwconv2.weight"), (b.b2, "pwconv2.bias"), (b.grn_gamma, "grn.gamma"), (b.grn_beta, "grn.beta")):
+            put(p, t + n)
+    for p, n in ((m.in_w, "input_embed.proj.weight"), (m.in_b, "input_embed.proj.bias"), (m.pos1_w, "input_embed.conv_pos_embed.conv1d.0.weight"),
+                 (m.pos1_b, "input_embed.conv_pos_embed.conv1d.0.bias"), (m.pos2_w, "input_embed.conv_pos_embed.conv1d.2.weight"),
+                 (m.pos2_b, "input_embed.conv_pos_embed.conv1d.2.bias"), (m.t1_w, "time_embed.time_mlp.0.weight"), (m.t1_b, "time_embed.time_mlp.0.bias"),
+                 (m.t2_w, "time_embed.time_mlp.2.weight"), (m.t2_b, "time_embed.time_mlp.2.bias"), (m.out_mod_w, "norm_out.linear.weight"),
+                 (m.out_mod_b, "norm_out.linear.bias"), (m.out_w, "proj_out.weight"), (m.out_b, "proj_out.bias")):
+        put(p, n)
+    for i, b in enumerate(m.blocks):
+        t = f"transformer_blocks.{i}."
+        b.w_qkv.data.copy_(torch.cat([get(t + f"attn.to_{n}.weight") for n in "qkv"], 0))
+        b.b_qkv.data.copy_(torch.cat([get(t + f"attn.to_{n}.bias") for n in "qkv"], 0))
+        for p, n in ((b.w_o, "attn.to_out.0.weight"), (b.b_o, "attn.to_out.0.bias"), (b.mod_w, "attn_norm.linear.weight"), (b.mod_b, "attn_norm.linear.bias"),
+                     (b.ff1_w, "ff.ff.0.0.weight"), (b.ff1_b, "ff.ff.0.0.bias"), (b.ff2_w, "ff.ff.2.weight"), (b.ff2_b, "ff.ff.2.bias")):
+            put(p, t + n)
+
+
 def init_random_(m: nn.Module, seed: int = 0, std: float = 0.1) -> None:
     g = torch.Generator().manual_seed(seed)
     for n, p in m.named_parameters():

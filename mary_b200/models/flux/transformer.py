@@ -169,3 +169,37 @@ class Flux2Transformer(nn.Module):
         x = joined[St:] if joined is not None else x
         sc, sh = ops.linear(st, self.out_mod)[0].chunk(2)
         return ops.linear((_ln(x) * (1 + sc) + sh).contiguous(), self.out_proj)
+
+
+def load_into(m: Flux2Transformer, loader) -> None:
+    """Names of the ``Flux2Transformer2DModel`` checkpoint layout; q / k / v of a stream are stored fused here."""
+    dt = m.x_embed.dtype
+
+    def get(n):
+        return loader.load_tensor(n, dt)
+
+    def put(p, n):
+        p.data.copy_(get(n).reshape(p.shape))
+    put(m.t1, "time_guidance_embed.timestep_embedder.linear_1.weight")
+    put(m.t2, "time_guidance_embed.timestep_embedder.linear_2.weight")
+    if m.c.guidance_embeds:
+        put(m.g1, "time_guidance_embed.guidance_embedder.linear_1.weight")
+        put(m.g2, "time_guidance_embed.guidance_embedder.linear_2.weight")
+    for p, n in ((m.mod_img, "double_stream_modulation_img.linear.weight"), (m.mod_txt, "double_stream_modulation_txt.linear.weight"),
+                 (m.mod_single, "single_stream_modulation.linear.weight"), (m.x_embed, "x_embedder.weight"),
+                 (m.ctx_embed, "context_embedder.weight"), (m.out_mod, "norm_out.linear.weight"), (m.out_proj, "proj_out.weight")):
+        put(p, n)
+    for i, b in enumerate(m.double_blocks):
+        a = f"transformer_blocks.{i}.attn."
+        b.img_qkv.data.copy_(torch.cat([get(a + f"to_{n}.weight") for n in "qkv"], 0))
+        b.txt_qkv.data.copy_(torch.cat([get(a + f"add_{n}_proj.weight") for n in "qkv"], 0))
+        for p, n in ((b.img_o, a + "to_out.0.weight"), (b.txt_o, a + "to_add_out.weight"), (b.img_qn, a + "norm_q.weight"),
+                     (b.img_kn, a + "norm_k.weight"), (b.txt_qn, a + "norm_added_q.weight"), (b.txt_kn, a + "norm_added_k.weight"),
+                     (b.img_ff_in, f"transformer_blocks.{i}.ff.linear_in.weight"), (b.img_ff_out, f"transformer_blocks.{i}.ff.linear_out.weight"),
+                     (b.txt_ff_in, f"transformer_blocks.{i}.ff_context.linear_in.weight"),
+                     (b.txt_ff_out, f"transformer_blocks.{i}.ff_context.linear_out.weight")):
+            put(p, n)
+    for i, b in enumerate(m.single_blocks):
+        a = f"single_transformer_blocks.{i}.attn."
+        for p, n in ((b.w_in, a + "to_qkv_mlp_proj.weight"), (b.w_out, a + "to_out.weight"), (b.qn, a + "norm_q.weight"), (b.kn, a + "norm_k.weight")):
+            put(p, n)

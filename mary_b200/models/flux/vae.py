@@ -64,6 +64,7 @@ class Flux2VAE(nn.Module):
         self.enc = nn.ModuleList(enc)
         self.enc_mid = nn.ModuleList([ResBlock(cin, cin, g), AttnBlock(cin, g), ResBlock(cin, cin, g)])
         self.enc_norm, self.enc_out = nn.GroupNorm(g, cin, eps=1e-6), nn.Conv2d(cin, 2 * L, 3, padding=1)
+        self.quant_conv, self.post_quant_conv = nn.Conv2d(2 * L, 2 * L, 1), nn.Conv2d(L, L, 1)
         # decoder
         self.dec_in = nn.Conv2d(L, ch[-1], 3, padding=1)
         self.dec_mid = nn.ModuleList([ResBlock(ch[-1], ch[-1], g), AttnBlock(ch[-1], g), ResBlock(ch[-1], ch[-1], g)])
@@ -93,11 +94,11 @@ class Flux2VAE(nn.Module):
             x = m(x)
         for m in self.enc_mid:
             x = m(x)
-        return self.enc_out(F.silu(self.enc_norm(x)))[:, :self.c.latent_channels]
+        return self.quant_conv(self.enc_out(F.silu(self.enc_norm(x))))[:, :self.c.latent_channels]
 
     def decode(self, z):
         """``z [B, L, h, w]`` -> image ``[B, 3, h f, w f]`` in about [-1, 1]."""
-        x = self.dec_in(z)
+        x = self.dec_in(self.post_quant_conv(z))
         for m in self.dec_mid:
             x = m(x)
         for m in self.dec:
@@ -120,3 +121,45 @@ class Flux2VAE(nn.Module):
 
     def denormalize(self, p):
         return p * torch.sqrt(self.bn_var[None, :, None, None] + self.c.bn_eps) + self.bn_mean[None, :, None, None]
+
+
+def load_into(m: Flux2VAE, loader) -> None:
+    """Names of the ``AutoencoderKLFlux2`` checkpoint layout (``encoder.*``, ``decoder.*``, ``quant_conv``, ``post_quant_conv``, ``bn.*``)."""
+    def put(mod, name):
+        mod.weight.data.copy_(loader.load_tensor(name + ".weight", mod.weight.dtype))
+        if mod.bias is not None:
+            mod.bias.data.copy_(loader.load_tensor(name + ".bias", mod.bias.dtype))
+
+    def res(r: ResBlock, p):
+        put(r.n1, p + ".norm1"), put(r.c1, p + ".conv1"), put(r.n2, p + ".norm2"), put(r.c2, p + ".conv2")
+        if r.skip is not None:
+            put(r.skip, p + ".conv_shortcut")
+
+    def mid(mods, p):
+        res(mods[0], p + ".resnets.0"), res(mods[2], p + ".resnets.1")
+        a = mods[1]
+        put(a.norm, p + ".attentions.0.group_norm")
+        for lin, n in ((a.q, "to_q"), (a.k, "to_k"), (a.v, "to_v"), (a.o, "to_out.0")):
+            put(lin, p + ".attentions.0." + n)
+    c = m.c
+    put(m.enc[0], "encoder.conv_in")
+    it = iter(m.enc[1:])
+    for i in range(len(c.channels)):
+        for j in range(c.layers_per_block):
+            res(next(it), f"encoder.down_blocks.{i}.resnets.{j}")
+        if i + 1 < len(c.channels):
+            put(next(it), f"encoder.down_blocks.{i}.downsamplers.0.conv")
+    mid(m.enc_mid, "encoder.mid_block")
+    put(m.enc_norm, "encoder.conv_norm_out"), put(m.enc_out, "encoder.conv_out")
+    put(m.quant_conv, "quant_conv"), put(m.post_quant_conv, "post_quant_conv")
+    put(m.dec_in, "decoder.conv_in")
+    mid(m.dec_mid, "decoder.mid_block")
+    it = iter(m.dec)
+    for i in range(len(c.channels)):
+        for j in range(c.layers_per_block + 1):
+            res(next(it), f"decoder.up_blocks.{i}.resnets.{j}")
+        if i + 1 < len(c.channels):
+            put(next(it), f"decoder.up_blocks.{i}.upsamplers.0.conv")
+    put(m.dec_norm, "decoder.conv_norm_out"), put(m.dec_out, "decoder.conv_out")
+    m.bn_mean.copy_(loader.load_tensor("bn.running_mean", torch.float32))
+    m.bn_var.copy_(loader.load_tensor("bn.running_var", torch.float32))
