@@ -1,0 +1,186 @@
+"""Entry points of the speech, vision and image families, all loading weights from a pile by model name:
+
+    families say       --pile P --model f5 --vocoder vocos --ref-wav r.wav --ref-text "..." --text "..." --out o.wav   (``say`` / ``say_serve``)
+    families listen    --pile P --model voxtral --wav a.wav [--delay 6]                                                  (``voxtral_listen``)
+    families embed     --pile P --model clip|siglip|nomic --kind clip|siglip|nomic [--image i.npy] [--ids 1,2,3]         (``local_demo``, ``embed_persist``)
+    families imagine   --pile P --transformer T --vae V --features f.npy --out img.npy [--steps 4] [--seed 0]            (the FLUX.2 pipeline)
+    families act       --pile P --model smolvla --image i.npy --ids 1,2,3 --state s.npy                                  (``smolvla_infer``)
+
+Checkpoints get into a pile with ``mary import`` (the reference's ``*_persist`` importers); ``--random`` instead builds the tiny
+configuration with random weights, which is what the tests drive.  Audio is read and written as 16-bit mono WAV with the standard
+library; images and feature matrices as ``.npy``."""
+from __future__ import annotations
+
+import argparse
+import sys
+import wave as wavlib
+
+import numpy as np
+import torch
+
+from ..format.persist import read_model_pile
+from ..format.selection import ModelSelector, SelectedModelIndex
+from ..nn.weight_loader import WeightLoader
+from ..pile import Pile
+
+
+def _loader(pile_path: str, name: str):
+    pile = Pile.open(pile_path, create=False)
+    facts = read_model_pile(pile)
+    ld = WeightLoader.from_pile(SelectedModelIndex.from_snapshot(pile, facts, ModelSelector.by_name(name)))
+    ld._pile = pile                     # leaf views alias the mapping
+    return ld
+
+
+def read_wav(path: str) -> tuple[np.ndarray, int]:
+    with wavlib.open(path, "rb") as f:
+        assert f.getsampwidth() == 2, "16-bit PCM expected"
+        x = np.frombuffer(f.readframes(f.getnframes()), dtype="<i2").astype(np.float32) / 32768.0
+        if f.getnchannels() > 1:
+            x = x.reshape(-1, f.getnchannels()).mean(1)
+        return x, f.getframerate()
+
+
+def write_wav(path: str, x, sr: int) -> None:
+    pcm = (np.clip(np.asarray(x, dtype=np.float32), -1.0, 1.0) * 32767.0).astype("<i2")
+    with wavlib.open(path, "wb") as f:
+        f.setnchannels(1), f.setsampwidth(2), f.setframerate(sr)
+        f.writeframes(pcm.tobytes())
+
+
+def _random_init(m, seed=0, std=0.05):
+    g = torch.Generator().manual_seed(seed)
+    for n, p in m.named_parameters():
+        if p.dim() == 1:
+            p.data.fill_(0.0 if n.split(".")[-1].endswith(("_b", "bias")) or n.split(".")[-1].startswith("b") else 1.0)
+        else:
+            p.data.normal_(0.0, std, generator=g)
+    return m
+
+
+def cmd_say(a) -> int:
+    from ..models.f5 import CFM, DiT, F5Config, Vocos, VocosConfig, mel_spectrogram
+    from ..models.f5 import dit as f5
+    if a.random:
+        c = F5Config.tiny()
+        dit, voc = _random_init(DiT(c)), _random_init(Vocos(VocosConfig(n_mels=c.n_mels, dim=16, ffn=32, layers=1, n_fft=64, hop=16)))
+        n_fft, hop = 64, 16
+    else:
+        dit, voc = DiT(F5Config()), Vocos(VocosConfig())
+        f5.load_into(dit, _loader(a.pile, a.model))
+        from ..models.f5.vocos import load_into as load_vocos
+        load_vocos(voc, _loader(a.pile, a.vocoder))
+        n_fft, hop = 1024, 256
+    wav, sr = read_wav(a.ref_wav)
+    ref = mel_spectrogram(torch.from_numpy(wav), n_mels=dit.c.n_mels, n_fft=n_fft, hop=hop, sr=sr).T.contiguous()
+    chars = [ord(ch) % (dit.c.text_vocab - 1) for ch in a.ref_text + " " + a.text]            # byte-level ids when the pile holds no vocabulary
+    # duration rule of the reference front end: target frames = reference frames * (target characters / reference characters)
+    total = ref.shape[0] + max(1, int(ref.shape[0] * len(a.text) / max(1, len(a.ref_text)) / a.speed))
+    mel = CFM(dit, nfe=a.nfe, cfg_strength=a.cfg).sample(ref, chars, total, generator=torch.Generator().manual_seed(a.seed))
+    out = voc(mel[ref.shape[0]:].T.contiguous())
+    write_wav(a.out, out.numpy(), sr)
+    print(f"{out.shape[0] / sr:.2f} s of audio -> {a.out}")
+    return 0
+
+
+def cmd_listen(a) -> int:
+    from ..models.voxtral import VoxtralConfig, VoxtralListener, VoxtralModel, load_into, log_mel
+    c = VoxtralConfig.tiny() if a.random else VoxtralConfig()
+    m = VoxtralModel(c)
+    _random_init(m) if a.random else load_into(m, _loader(a.pile, a.model))
+    wav, sr = read_wav(a.wav)
+    assert sr == 16000, "16 kHz audio expected"
+    mel = log_mel(wav, n_mels=c.n_mels)
+    step = 2 * c.downsample
+    lis = VoxtralListener(m, a.delay, n_pages=max(64, mel.shape[1] // 16 + 8))
+    out = []
+    for lo in range(0, mel.shape[1] - step + 1, step * a.chunk):          # a.chunk text positions per call: the streaming granularity
+        hi = min(mel.shape[1] // step * step, lo + step * a.chunk)
+        out += lis.feed(mel[:, lo:hi])
+    print(",".join(map(str, out)))
+    return 0
+
+
+def cmd_embed(a) -> int:
+    from ..models import embed as E
+    kinds = {"clip": (E.ClipConfig, E.ClipEmbedder, E.clip.load_into), "siglip": (E.SiglipConfig, E.SiglipEmbedder, E.siglip.load_into),
+             "nomic": (E.NomicConfig, E.NomicTextEmbedder, E.nomic.load_into)}
+    Cfg, Model, load = kinds[a.kind]
+    m = Model(Cfg.tiny() if a.random else Cfg())
+    _random_init(m) if a.random else load(m, _loader(a.pile, a.model))
+    with torch.no_grad():
+        if a.image:
+            img = torch.from_numpy(np.load(a.image)).float()
+            v = m.embed_image(m.preprocess(img)[None])[0]
+        else:
+            v = m.embed_text(torch.tensor([[int(x) for x in a.ids.split(",")]]))[0]
+    print(" ".join(f"{x:.6f}" for x in v.tolist()))
+    return 0
+
+
+def cmd_imagine(a) -> int:
+    from ..models.flux import Flux2Config, Flux2Transformer, Flux2VAE, FluxPipeline, VAEConfig
+    from ..models.flux import transformer as T, vae as V
+    if a.random:
+        vae = _random_init(Flux2VAE(VAEConfig.tiny()))
+        c = Flux2Config.tiny()
+        c.in_channels = 4 * vae.c.latent_channels
+        tr = _random_init(Flux2Transformer(c), std=0.2)
+    else:
+        tr, vae = Flux2Transformer(Flux2Config()), Flux2VAE(VAEConfig())
+        T.load_into(tr, _loader(a.pile, a.transformer))
+        V.load_into(vae, _loader(a.pile, a.vae))
+    feats = torch.from_numpy(np.load(a.features)).float()
+    img = FluxPipeline(tr, vae)(feats, a.height, a.width, steps=a.steps, seed=a.seed)
+    np.save(a.out, img.numpy())
+    print(f"image {tuple(img.shape)} -> {a.out}")
+    return 0
+
+
+def cmd_act(a) -> int:
+    from ..models.smolvla import SmolVLA, SmolVLAConfig
+    if not a.random:
+        raise SystemExit("act: only --random is wired up; the policy's checkpoint layout has no loader in this package yet")
+    m = _random_init(SmolVLA(SmolVLAConfig.tiny()), std=0.2)
+    img = torch.from_numpy(np.load(a.image)).float()
+    state = torch.from_numpy(np.load(a.state)).float()
+    chunk = m.act([img], [int(x) for x in a.ids.split(",")], state, generator=torch.Generator().manual_seed(a.seed))
+    for row in chunk.tolist():
+        print(" ".join(f"{x:.5f}" for x in row))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="families")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    def common(p):
+        p.add_argument("--pile")
+        p.add_argument("--model")
+        p.add_argument("--random", action="store_true", help="tiny configuration with random weights (no pile)")
+        p.add_argument("--seed", type=int, default=0)
+        return p
+    s = common(sub.add_parser("say"))
+    s.add_argument("--vocoder", default="vocos"), s.add_argument("--ref-wav", required=True), s.add_argument("--ref-text", required=True)
+    s.add_argument("--text", required=True), s.add_argument("--out", required=True), s.add_argument("--nfe", type=int, default=32)
+    s.add_argument("--cfg", type=float, default=2.0), s.add_argument("--speed", type=float, default=1.0)
+    s.set_defaults(fn=cmd_say)
+    li = common(sub.add_parser("listen"))
+    li.add_argument("--wav", required=True), li.add_argument("--delay", type=int), li.add_argument("--chunk", type=int, default=4)
+    li.set_defaults(fn=cmd_listen)
+    e = common(sub.add_parser("embed"))
+    e.add_argument("--kind", required=True, choices=["clip", "siglip", "nomic"]), e.add_argument("--image"), e.add_argument("--ids")
+    e.set_defaults(fn=cmd_embed)
+    im = common(sub.add_parser("imagine"))
+    im.add_argument("--transformer"), im.add_argument("--vae"), im.add_argument("--features", required=True), im.add_argument("--out", required=True)
+    im.add_argument("--height", type=int, default=1024), im.add_argument("--width", type=int, default=1024), im.add_argument("--steps", type=int, default=4)
+    im.set_defaults(fn=cmd_imagine)
+    ac = common(sub.add_parser("act"))
+    ac.add_argument("--image", required=True), ac.add_argument("--ids", required=True), ac.add_argument("--state", required=True)
+    ac.set_defaults(fn=cmd_act)
+    a = ap.parse_args(argv)
+    return a.fn(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

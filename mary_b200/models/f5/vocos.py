@@ -73,3 +73,20 @@ class Vocos(nn.Module):
     def forward(self, mel):
         """``mel [n_mels, T]`` -> waveform ``[T * hop]``."""
         return istft_matmul(self.spectrum(mel), self.c.n_fft, self.c.hop, length=mel.shape[1] * self.c.hop)
+
+
+def load_into(m: Vocos, loader) -> None:
+    """Names of the ``charactr/vocos-mel-24khz`` checkpoint (``backbone.*``, ``head.out``)."""
+    dt = m.embed_w.dtype
+
+    def put(p, n):
+        p.data.copy_(loader.load_tensor(n, dt).reshape(p.shape))
+    for p, n in ((m.embed_w, "backbone.embed.weight"), (m.embed_b, "backbone.embed.bias"), (m.ln0_w, "backbone.norm.weight"), (m.ln0_b, "backbone.norm.bias"),
+                 (m.lnf_w, "backbone.final_layer_norm.weight"), (m.lnf_b, "backbone.final_layer_norm.bias"), (m.out_w, "head.out.weight"),
+                 (m.out_b, "head.out.bias")):
+        put(p, n)
+    for i, b in enumerate(m.blocks):
+        t = f"backbone.convnext.{i}."
+        for p, n in ((b.dw_w, "dwconv.weight"), (b.dw_b, "dwconv.bias"), (b.ln_w, "norm.weight"), (b.ln_b, "norm.bias"), (b.w1, "pwconv1.weight"),
+                     (b.b1, "pwconv1.bias"), (b.w2, "pwconv2.weight"), (b.b2, "pwconv2.bias"), (b.gamma, "gamma")):
+            put(p, t + n)
