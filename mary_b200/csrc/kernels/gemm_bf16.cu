@@ -58,6 +58,12 @@ struct GemmParams {
   // sk_units blocks per CTA, so every CTA streams the same number of weight bytes whatever the tile count; a tile whose
   // blocks fall to several CTAs is finished by whichever of them arrives last.
   int sk_units;
+  // grouped (mixture-of-experts) mode, swap only: the token operand is ONE matrix of padded rows cut into column tiles of BN rows,
+  // tile t belongs to expert g_tiles[4 t] (the routing plan's tile table; g_meta[0] = number of tiles in use) and multiplies
+  // that expert's slice of the 3-D weight operand.  Tiles past g_meta[0] are skipped by every role alike.
+  const int* g_tiles;
+  const int* g_meta;
+  int g_experts;
 };
 
 // One unit of work of a CTA: K-blocks [kb0, kb1) of output tile (tr, tc) of problem bz; `seg` of `nseg` partial results of that
@@ -90,6 +96,10 @@ struct WorkIter {
       return true;
     }
     const int per_batch = p.tiles_r * p.tiles_c * p.split_k;
+    if (p.g_tiles) {
+      const int used = p.g_meta[0];
+      while (tt < per_batch && (tt % per_batch) % p.tiles_c >= used) tt += gridDim.x;      // column tiles the plan does not use
+    }
     if (tt >= per_batch * p.batch) return false;
     const int t = tt % per_batch;
     w.bz = tt / per_batch;
@@ -171,14 +181,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       WorkIter iter(p);
       WorkItem w;
       while (iter.next(w)) {
-        const int bz = w.bz, tr = w.tr, tc = w.tc;
+        const int tr = w.tr, tc = w.tc;
+        int zr = w.bz, zc = w.bz;
+        if (p.g_tiles) { zr = min(max(p.g_tiles[4 * tc], 0), p.g_experts - 1); zc = 0; }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
           uint8_t* st = smem + stage * C::STAGE_BYTES;
           mbar_expect_tx(&full[stage], C::STAGE_BYTES);
-          tma_load_3d(st, &tm_r, &full[stage], kb * BK, tr * BM, bz);
-          if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[stage], kb * BK, p.glu_offset + tr * BM, bz);
-          tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, bz);
+          tma_load_3d(st, &tm_r, &full[stage], kb * BK, tr * BM, zr);
+          if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[stage], kb * BK, p.glu_offset + tr * BM, zr);
+          tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, zc);
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -383,7 +395,8 @@ static int make_tmap_3d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
                      const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream, float* ws = nullptr,
-                     int64_t ws_floats = 0, int* counters = nullptr, int n_counters = 0, bool stream_k = false);
+                     int64_t ws_floats = 0, int* counters = nullptr, int n_counters = 0, bool stream_k = false,
+                     const int* g_tiles = nullptr, const int* g_meta = nullptr, int g_experts = 0, int g_nt = 0);
 
 MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
                                     int64_t ldo, int batch, int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha,
@@ -405,7 +418,7 @@ MARY_API int mary_gemm_bf16_rs(const void* X, const void* W, int M, int N, int K
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
                      const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream, float* ws, int64_t ws_floats,
-                     int* counters, int n_counters, bool stream_k) {
+                     int* counters, int n_counters, bool stream_k, const int* g_tiles, const int* g_meta, int g_experts, int g_nt) {
   if (M <= 0 || N <= 0 || K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || batch < 1) return MARY_ERR_BAD_ARG;
   if (split_k < 1) split_k = 1;
   const bool sk_epi = epi == EPI_SK_BF16 || epi == EPI_SK_F32;
@@ -455,6 +468,14 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   p.ws = ws;
   p.counters = counters;
   p.sk_units = 0;
+  p.g_tiles = g_tiles;
+  p.g_meta = g_meta;
+  p.g_experts = g_experts;
+  if (g_tiles) {
+    if (!use_swap || batch != 1 || split_k != 1 || (g_nt != 32 && g_nt != 64 && g_nt != 128) || p.rows_c % g_nt) return MARY_ERR_BAD_ARG;
+    bn = g_nt;                                    // one column tile = one tile of the routing plan
+    p.tiles_c = p.rows_c / bn;
+  }
   if (sk_epi) {
     const int64_t tiles = (int64_t)p.tiles_r * p.tiles_c * batch;
     const int64_t slots = tiles;                 // one f32 accumulator tile per output tile
@@ -471,7 +492,7 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
     if (tiles > n_counters || slots * BM * bn > ws_floats) return MARY_ERR_BAD_ARG;     // workspace too small
   }
   CUtensorMap tr, tc;
-  int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, batch, bsr, BM);
+  int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, g_tiles ? g_experts : batch, bsr, BM);
   if (rc) return rc;
   rc = make_tmap_3d(&tc, Cc, p.rows_c, K, ldc, batch, bsc, bn);
   if (rc) return rc;
@@ -494,6 +515,18 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
                             int64_t ldo, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
                             cudaStream_t stream) {
   return mary_gemm_bf16_batched(X, W, out, M, N, K, ldx, ldw, ldo, 1, 0, 0, 0, bias, alpha, glu, epi, split_k, swap, stream);
+}
+
+// Grouped (mixture-of-experts) GEMM with unquantised expert weights: out[rows_pad, N] = X[rows_pad, K] * W[expert of the row's tile]^T,
+// optionally with the GLU epilogue (W[e] = [gate; up], 2 N rows).  X holds the routing plan's padded rows (tiles of `nt` = 32, 64 or
+// 128 rows, one expert each); `tiles` / `meta` are the plan's tile table and {tiles in use, padded rows}; W is [E][N or 2 N][K] with
+// `bsw` elements between experts.  Tiles the plan does not use are skipped.
+MARY_API int mary_gemm_bf16_grouped(const void* X, const void* W, void* out, int rows_pad, int N, int K, int64_t ldx, int64_t ldw,
+                                    int64_t ldo, int E, int64_t bsw, const int* tiles, const int* meta, int nt, int glu,
+                                    cudaStream_t stream) {
+  if (!tiles || !meta || E < 1) return MARY_ERR_BAD_ARG;
+  return gemm_impl(X, W, out, rows_pad, N, K, ldx, ldw, ldo, 1, 0, bsw, 0, nullptr, 1.0f, glu, EPI_STORE_BF16, 1, 1, nullptr, 0, 0, 0, stream,
+                   nullptr, 0, nullptr, 0, false, tiles, meta, E, nt);
 }
 
 // Split-K finished inside the kernel, without a zero-fill or a cast pass: out (bf16, or f32 when out_f32) = alpha * X W^T + bias

@@ -83,7 +83,7 @@ class Gemma4Layer(nn.Module):
         w = w * self.per_expert_scale.float()[idx.long()]
         x2 = ops.rmsnorm(h, self.ln_pre_ffn_2, c.rms_norm_eps)
         e0 = self.tp.rank * self.e_local
-        y = dense_experts(x2, idx, w, self.ex_gate_up, self.ex_down, e0, "geglu")
+        y = ops.bf16_experts(x2, idx, w, self.ex_gate_up, self.ex_down, e0, "geglu")
         return self.tp.reduce(y) if self.tp.size > 1 else y
 
     def forward(self, x, h, meta, cache, next_norm, ple=None):
@@ -123,29 +123,6 @@ class Gemma4Layer(nn.Module):
         _, h = ops.norm_add_norm(d, self.ln_post_ffn, h, None, c.rms_norm_eps)
         g = ops.glu(torch.cat([ops.linear(h, self.ple_gate), ple.to(h.dtype)], -1), "geglu")
         return ops.norm_add_norm(ops.linear(g, self.ple_proj), self.ln_post_ple, h, next_norm, c.rms_norm_eps, self.layer_scalar)
-
-
-def dense_experts(x, idx, w, gate_up, down, e0: int, act: str):
-    """``sum_k w[t,k] * down[e] (act(gate[e] x_t) * up[e] x_t)`` over the experts ``e0 .. e0 + len(gate_up)`` held here, with
-    unquantised expert weights ``gate_up[E, 2F, H]`` / ``down[E, H, F]``.  Entries are grouped by expert on the host (the
-    reference does the same, layers.rs:328-418); every expert runs the package's fused GLU GEMM on its rows, and the
-    weighted rows are summed per token in f32 in ascending expert order."""
-    T, k = idx.shape
-    out = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
-    flat = idx.reshape(-1).long()
-    order = torch.argsort(flat, stable=True)
-    counts = torch.bincount(flat, minlength=e0 + gate_up.shape[0]).tolist()
-    start = sum(counts[:e0])
-    for e in range(gate_up.shape[0]):
-        n = counts[e0 + e]
-        if n == 0:
-            continue
-        ent = order[start:start + n]
-        start += n
-        tok = ent // k
-        y = ops.linear(ops.linear_glu(x[tok].contiguous(), gate_up[e], act), down[e])
-        out.index_add_(0, tok, y.float() * w.reshape(-1)[ent].float()[:, None])
-    return out.to(x.dtype)
 
 
 class Gemma4Model(nn.Module):

@@ -101,3 +101,71 @@ def dense_mlp(x, w_gate, w_up, w_down, global_scale: float = 1.0):
 def unembed(h, final_norm, w_unembed, mup_width_multiplier: float, real_vocab: int, eps: float = 1e-6):
     x = ref.rmsnorm(h, final_norm, eps).float() / mup_width_multiplier
     return (x @ w_unembed.float().t())[:, :real_vocab]
+
+
+# --------------------------------------------------------------------------------------------------------------------------
+# whole layer, stack ends and multi-token-prediction heads (src/models/inkling/{layer,stack,mtp}.rs)
+
+def decoder_layer(x, p: dict, cfg: dict, cache: dict | None = None, is_global: bool = True, mlp=None):
+    """One decoder layer on one sequence ``x[T, H]``:
+
+        x = x + sconv_attn(attn(rms(x, attn_norm)));   x = x + sconv_mlp(mlp(rms(x, mlp_norm)))
+
+    Both layer-level short convolutions FOLLOW their block and carry their own inner residual (``sconv(y) = y + conv(y)``), so the
+    layer has four additive paths.  Three of them keep state across steps: attention's K / V (with the K / V conv histories) and
+    the two layer-level conv histories; ``cache`` holds all of it (``attn`` sub-dict, ``hist_attn``, ``hist_mlp``).
+    ``mlp``: callable for a routed layer; default is the dense MLP from ``p`` (``w_gate, w_up, w_down``)."""
+    eps = cfg.get("eps", 1e-6)
+    if cache is not None:
+        cache.setdefault("attn", {})
+    h = attention(ref.rmsnorm(x, p["attn_norm"], eps), p, cfg, cache=None if cache is None else cache["attn"], is_global=is_global)
+    h, ha = ref.short_conv(h, p["attn_sconv"], None if cache is None else cache.get("hist_attn"))
+    x = x + h
+    y = ref.rmsnorm(x, p["mlp_norm"], eps)
+    m = mlp(y) if mlp is not None else dense_mlp(y, p["w_gate"], p["w_up"], p["w_down"], cfg.get("global_scale", 1.0))
+    m, hm = ref.short_conv(m, p["mlp_sconv"], None if cache is None else cache.get("hist_mlp"))
+    if cache is not None:
+        cache.update(hist_attn=ha, hist_mlp=hm)
+    return x + m
+
+
+def embed_in(ids, embed, embed_norm, eps: float = 1e-6):
+    """``embed_norm(embed[ids])``: the norm belongs to the embedding output, before any layer."""
+    return ref.rmsnorm(embed[torch.as_tensor(ids).long()], embed_norm, eps)
+
+
+def mtp_input(hidden, tok_embed, p: dict, hidden_first: bool = True, eps: float = 1e-6):
+    """Input of an MTP head at position ``j``: ``input_proj(cat(hidden_norm(main_hidden[j]), embed_norm(embed(token[j + 1]))))`` with
+    ``input_proj [H, 2H]``.  Upstream defines no reference for the order of the two operands; ``hidden_first`` keeps both orders
+    reachable (the acceptance rate of the drafts is the measurement that picks one: a wrong order cannot change the text,
+    only how many drafts survive verification)."""
+    a, b = ref.rmsnorm(hidden, p["hidden_norm"], eps), ref.rmsnorm(tok_embed, p["embed_norm"], eps)
+    cat = torch.cat([a, b] if hidden_first else [b, a], -1)
+    return (cat.float() @ p["input_proj"].float().t()).to(hidden.dtype)
+
+
+def mtp_block(main_hidden, next_tok_embed, p: dict, cfg: dict, cache: dict | None = None, hidden_first: bool = True):
+    """One MTP head over rows ``(main_hidden[j], embed(token[j + 1]))``: wrapper + one DENSE decoder layer.  With ``cache`` the rows
+    extend the head's own K / V and conv state (``main_hidden[j]`` never changes once produced, so its K / V are stable)."""
+    return decoder_layer(mtp_input(main_hidden, next_tok_embed, p, hidden_first, cfg.get("eps", 1e-6)), p, cfg, cache, is_global=True)
+
+
+def clone_cache(cache: dict) -> dict:
+    """Deep copy of a layer cache: drafts run on the clone, which is then dropped — rollback is the default, commitment the exception."""
+    return {k: (clone_cache(v) if isinstance(v, dict) else (v.clone() if torch.is_tensor(v) else v)) for k, v in cache.items()}
+
+
+def mtp_draft(heads: list, caches: list, main_hidden_last, embed, embed_norm_w, unembed_fn, first_token: int, cfg: dict, hidden_first=True):
+    """Chain the heads to draft ``len(heads)`` tokens after ``first_token`` (the main model's own next token): head ``d`` reads the
+    previous head's output row and the embedding of the token drafted before it.  Runs on CLONES of the heads' caches and returns
+    ``(tokens, logits_rows)``; the caller commits nothing until the main model has verified the drafts."""
+    toks, rows = [], []
+    h, tok = main_hidden_last[None], first_token
+    for p, c in zip(heads, caches):
+        e = embed[torch.tensor([tok])]
+        h = mtp_block(h, e, p, cfg, clone_cache(c) if c is not None else None, hidden_first)
+        logits = unembed_fn(h)
+        tok = int(ref.argmax_first(logits)[0])
+        toks.append(tok)
+        rows.append(logits[0])
+    return toks, rows

@@ -153,6 +153,32 @@ def router_topk(logits, k, mode="softmax", bias=None, n_group=1, topk_group=1, s
     return ref.router_sigmoid_topk(logits, bias, k, n_group, topk_group, scale, renorm)
 
 
+def bf16_experts(x, idx, w, gate_up, down, e0: int = 0, act: str = "geglu"):
+    """``sum_k w[t,k] * down[e] (act(gate[e] x_t) * up[e] x_t)`` over the experts ``e0 .. e0 + len(gate_up)`` held here, with
+    unquantised expert weights ``gate_up[E, 2F, H]`` / ``down[E, H, F]`` (src/models/inkling/moegroup.rs:556-719, the grouped bf16
+    lane; src/models/gemma/gemma4/layers.rs:328-418).  GPU: routing plan + grouped tensor-core GEMMs.  CPU: entries grouped by
+    expert, one GLU MLP per expert on its rows, weighted rows summed per token in f32."""
+    if _cuda(x):
+        from . import cuda_moe
+        return cuda_moe.experts_forward_bf16(x, idx, w, gate_up, down, act, e0)
+    T, k = idx.shape
+    out = torch.zeros(T, x.shape[1], dtype=torch.float32, device=x.device)
+    flat = idx.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=e0 + gate_up.shape[0]).tolist()
+    start = sum(counts[:e0])
+    for e in range(gate_up.shape[0]):
+        n = counts[e0 + e]
+        if n == 0:
+            continue
+        ent = order[start:start + n]
+        start += n
+        tok = ent // k
+        y = linear(linear_glu(x[tok].contiguous(), gate_up[e], act), down[e])
+        out.index_add_(0, tok, y.float() * w.reshape(-1)[ent].float()[:, None])
+    return out.to(x.dtype)
+
+
 def quantize_nvfp4(x):
     return _k().quantize_nvfp4(x) if _cuda(x) else ref.quantize_nvfp4(x)
 

@@ -95,3 +95,32 @@ def experts_forward(x, idx, w, ex, shared=None, nt: int | None = None):
     hq, sfh = quantize_entries(h, plan, k, identity=True)
     y = grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, ex.H, ex.F, ex.E, None)
     return unpermute(y, plan, w, T, k, shared)
+
+
+declare("mary_gemm_bf16_grouped", "ppp" + "iii" + "lll" + "i" + "l" + "pp" + "ii" + "s")
+
+
+def grouped_gemm_bf16(xg, w, plan: Plan, n_out: int, glu: str | None):
+    """``out[r] = act_glu(xg[r] @ w[expert of r's tile]^T)`` over the plan's padded rows; ``w [E, n_out or 2 n_out, K]`` unquantised."""
+    E, _, K = w.shape
+    out = torch.empty(plan.max_rows, n_out, dtype=torch.bfloat16, device=xg.device)
+    g = 0 if glu is None else {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
+    check(lib().mary_gemm_bf16_grouped(_p(xg), _p(w), _p(out), plan.max_rows, n_out, K, xg.stride(0), w.stride(1), out.stride(0), E,
+                                       w.stride(0), _p(plan.tiles), _p(plan.meta), plan.nt, g, _stream()), "gemm_bf16_grouped")
+    return out
+
+
+def experts_forward_bf16(x, idx, w, gate_up, down, act: str = "geglu", e0: int = 0, nt: int | None = None):
+    """Routed experts with unquantised weights (``gate_up [E, 2F, H]``, ``down [E, H, F]``; the experts held here are
+    ``e0 .. e0 + E``): device routing plan, row gather, two grouped tensor-core GEMMs (the first with the GLU epilogue), weighted
+    un-permute.  No host synchronisation: the launch sequence does not depend on the routing."""
+    T, k = idx.shape
+    E = gate_up.shape[0]
+    if nt is None:
+        nt = 32 if T * k <= 32 * E else (64 if T * k <= 64 * E else 128)
+    local = idx - e0 if e0 else idx
+    plan = moe_plan(torch.where((local >= 0) & (local < E), local, torch.full_like(local, -1)).int(), E, nt)
+    xg = x.index_select(0, plan.src_of.clamp_min(0).long())          # padding rows repeat token 0; nothing reads their results
+    h = grouped_gemm_bf16(xg, gate_up, plan, gate_up.shape[1] // 2, act)
+    y = grouped_gemm_bf16(h, down, plan, down.shape[1], None)
+    return unpermute(y, plan, w, T, k)

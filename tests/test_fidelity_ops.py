@@ -101,3 +101,52 @@ def test_k3_latent_moe_and_attn_res():
     lo = torch.minimum(bank.amin(0), acc)
     hi = torch.maximum(bank.amax(0), acc)
     assert ((mix >= lo - 1e-5) & (mix <= hi + 1e-5)).all()           # a convex combination per token
+
+
+def test_inkling_layer_has_three_stateful_paths_and_mtp_heads_roll_back():
+    from mary_b200.models.inkling import ops as ink
+    torch.manual_seed(0)
+    H, Hq, Hkv, D, F = 32, 4, 2, 8, 48
+    cfg = dict(n_heads=Hq, n_kv_heads=Hkv, head_dim=D, d_rel=4, log_alpha=0.1, log_n_floor=4.0, window=6, eps=1e-6)
+
+    def layer_params():
+        r = lambda *s: torch.randn(*s) * 0.2  # noqa: E731
+        return dict(wq=r(Hq * D, H), wk=r(Hkv * D, H), wv=r(Hkv * D, H), wo=r(H, Hq * D), wr=r(Hq * 4, H), rel_proj=r(4, 8),
+                    q_norm=torch.ones(D), k_norm=torch.ones(D), k_conv=r(Hkv * D, 4), v_conv=r(Hkv * D, 4), attn_norm=torch.ones(H),
+                    mlp_norm=torch.ones(H), attn_sconv=r(H, 4), mlp_sconv=r(H, 4), w_gate=r(F, H), w_up=r(F, H), w_down=r(H, F),
+                    hidden_norm=torch.ones(H), embed_norm=torch.ones(H), input_proj=r(H, 2 * H))
+    p = layer_params()
+    x = torch.randn(9, H)
+    full = ink.decoder_layer(x, p, cfg)
+    cache = {}
+    parts = [ink.decoder_layer(x[:4], p, cfg, cache)] + [ink.decoder_layer(x[t:t + 1], p, cfg, cache) for t in range(4, 9)]
+    assert torch.allclose(torch.cat(parts), full, atol=1e-5)
+    assert set(cache) == {"attn", "hist_attn", "hist_mlp"} and cache["attn"]["k"].shape[0] == 9
+    # a cache that forgot one of the layer-level conv histories is wrong from the first decode step
+    broken = {}
+    ink.decoder_layer(x[:4], p, cfg, broken)
+    broken.pop("hist_mlp")
+    assert not torch.allclose(ink.decoder_layer(x[4:5], p, cfg, broken), full[4:5], atol=1e-4)
+    # the four additive paths: zero conv taps leave x + attn + mlp
+    p0 = dict(p, attn_sconv=torch.zeros(H, 4), mlp_sconv=torch.zeros(H, 4))
+    h1 = x + ink.attention(ref.rmsnorm(x, p["attn_norm"], 1e-6), p0, cfg)
+    want = h1 + ink.dense_mlp(ref.rmsnorm(h1, p["mlp_norm"], 1e-6), p["w_gate"], p["w_up"], p["w_down"])
+    assert torch.allclose(ink.decoder_layer(x, p0, cfg), want, atol=1e-5)
+
+    # MTP wrapper: both operand orders are reachable and differ; drafting leaves the heads' caches untouched
+    emb = torch.randn(20, H)
+    a = ink.mtp_input(x[:3], emb[:3], p, hidden_first=True)
+    b = ink.mtp_input(x[:3], emb[:3], p, hidden_first=False)
+    assert a.shape == (3, H) and not torch.allclose(a, b)
+    swapped = dict(p, input_proj=torch.cat([p["input_proj"][:, H:], p["input_proj"][:, :H]], 1))
+    assert torch.allclose(ink.mtp_input(x[:3], emb[:3], swapped, hidden_first=False), a, atol=1e-6)
+    heads = [layer_params(), layer_params()]
+    caches = [{}, {}]
+    for hp, c in zip(heads, caches):
+        ink.mtp_block(x[:5], emb[1:6], hp, cfg, c)
+    before = [c["attn"]["k"].clone() for c in caches]
+    unembed = lambda h: h.float() @ emb.t()  # noqa: E731
+    toks, rows = ink.mtp_draft(heads, caches, x[5], emb, None, unembed, 7, cfg)
+    assert len(toks) == 2 and rows[0].shape == (20,)
+    assert all(torch.equal(c["attn"]["k"], b) for c, b in zip(caches, before))
+    assert torch.allclose(ink.embed_in([3, 4], emb, torch.full((H,), 2.0)), 2.0 * ref.rmsnorm(emb[3:5], None, 1e-6))

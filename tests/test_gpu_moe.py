@@ -122,3 +122,33 @@ def test_ep_all_to_all_serves_the_shared_expert_in_the_same_launches():
         w2 = torch.cat([w.float(), torch.ones(n, 1, device="cuda")], 1)
         want = cuda_moe.experts_forward(x, idx2, w2, ex, None, 32)
         assert _rel(got, want) < 2e-2, _rel(got, want)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("E,H,F,T,k,act", [(8, 256, 128, 40, 2, "geglu"), (32, 512, 256, 16, 4, "swiglu"), (4, 256, 384, 700, 2, "geglu")])
+def test_grouped_bf16_experts_match_the_per_expert_loop(E, H, F, T, k, act):
+    """Unquantised experts through the grouped tensor-core GEMM (routing plan tiles of 32 / 64 / 128 rows, GLU epilogue, unused tiles
+    skipped) against the f32 per-expert loop; a shard of the experts (``e0``) ignores entries routed elsewhere."""
+    from mary_b200 import ops
+    g = torch.Generator().manual_seed(E + T)
+    x = torch.randn(T, H, generator=g) * 0.5
+    gate_up, down = torch.randn(E, 2 * F, H, generator=g) * H ** -0.5, torch.randn(E, H, F, generator=g) * F ** -0.5
+    idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).int()
+    w = torch.rand(T, k, generator=g)
+    xb, gb, db = x.bfloat16(), gate_up.bfloat16(), down.bfloat16()
+    want = ops.bf16_experts(xb.float(), idx, w, gb.float(), db.float(), 0, act)
+    got = ops.bf16_experts(xb.cuda(), idx.cuda(), w.cuda(), gb.cuda(), db.cuda(), 0, act)
+    err = (got.float().cpu() - want).norm() / want.norm()
+    assert err < 0.02, float(err)
+    # the upper half of the experts only
+    e0 = E // 2
+    want_h = ops.bf16_experts(xb.float(), idx, w, gb.float()[e0:], db.float()[e0:], e0, act)
+    got_h = ops.bf16_experts(xb.cuda(), idx.cuda(), w.cuda(), gb.cuda()[e0:].contiguous(), db.cuda()[e0:].contiguous(), e0, act)
+    err = (got_h.float().cpu() - want_h).norm() / want_h.norm().clamp_min(1e-6)
+    assert err < 0.02, float(err)
+    assert mary_status_ok()
+
+
+def mary_status_ok():
+    from mary_b200.ops import cuda as K
+    return K.lib().mary_last_status() == 0
