@@ -93,3 +93,122 @@ def attn_res_mix(bank, accumulator, query, keys_proj, eps: float = 1e-5):
     scores = (normed @ (keys_proj.float() @ query.float())) if keys_proj is not None else (normed @ query.float())
     wgt = torch.softmax(scores, 0)
     return (wgt[..., None] * src.float()).sum(0).to(accumulator.dtype)
+
+
+# --------------------------------------------------------------------------------------------------------------------------
+# configuration, the KDA sublayer with its projections, and the whole decoder layer (src/models/k3/{config,kda_attn,layer}.rs)
+
+class K3Config:
+    """The attention lists are ONE-based (layer 3 of a list means the third layer, index 2); the dense-layer index is zero-based
+    (config.rs:153-370).  ``validate`` checks that the two lists partition ``1 .. n_layers``."""
+
+    def __init__(self, n_layers: int, kda_layers, full_attn_layers, first_k_dense: int = 1, snapshot_every: int = 12, n_heads: int = 4,
+                 kda_head_dim: int = 16, conv_kernel: int = 4):
+        self.n_layers, self.kda_layers, self.full_attn_layers = n_layers, list(kda_layers), list(full_attn_layers)
+        self.first_k_dense, self.snapshot_every = first_k_dense, snapshot_every
+        self.n_heads, self.kda_head_dim, self.conv_kernel = n_heads, kda_head_dim, conv_kernel
+        self.validate()
+
+    def validate(self) -> None:
+        both = self.kda_layers + self.full_attn_layers
+        if sorted(both) != list(range(1, self.n_layers + 1)):
+            dup = sorted({x for x in both if both.count(x) > 1})
+            missing = sorted(set(range(1, self.n_layers + 1)) - set(both))
+            raise ValueError(f"attention lists must partition layers 1..{self.n_layers}: duplicated {dup}, missing {missing}, "
+                             f"out of range {sorted(x for x in both if not 1 <= x <= self.n_layers)}")
+
+    def attn_kind(self, layer_index: int) -> str:
+        """``"mla"`` or ``"kda"`` for the ZERO-based layer index."""
+        return "mla" if layer_index + 1 in self.full_attn_layers else "kda"
+
+    def is_dense(self, layer_index: int) -> bool:
+        return layer_index < self.first_k_dense
+
+    def is_boundary(self, layer_index: int) -> bool:
+        """Layers at which the depth accumulator is pushed to the bank and reset."""
+        return layer_index > 0 and layer_index % self.snapshot_every == 0
+
+
+def _bf(x, like):
+    return x.to(like.dtype)
+
+
+def kda_attention(x, p: dict, cfg: K3Config, cache: dict | None = None):
+    """The whole KDA sublayer for one sequence ``x[T, H]`` (kda_attn.rs): q / k / v projections, each followed by a depthwise causal
+    short convolution (kernel 4) with SiLU; the decay-gate input from a low-rank pair ``f_b(f_a(x))``; the write strength
+    ``beta = sigmoid(b_proj(x))`` per head; the gated delta-rule recurrence per head (f32 / f64 inside, state O(1) in the sequence
+    length); a gated RMSNorm of the output, ``o_norm(o) * sigmoid(g_b(g_a(x)))``; ``o_proj``.  ``A_log``, ``dt_bias``, the
+    convolution taps and ``o_norm`` stay f32; every projection / convolution / recurrence output is rounded to the activation
+    dtype.  ``cache``: per-head recurrent state and the three convolution histories."""
+    T = x.shape[0]
+    nh, dk = cfg.n_heads, cfg.kda_head_dim
+    K = cfg.conv_kernel
+
+    def conv(name, y):
+        hist = None if cache is None else cache.get("hist_" + name)
+        if hist is None:
+            hist = torch.zeros(K - 1, y.shape[1], dtype=torch.float32)
+        ext = torch.cat([hist, y.float()], 0)
+        w = p[name + "_conv"].float()                                   # [C, K]; tap K-1 multiplies the current row
+        out = sum(ext[j:j + T] * w[:, j] for j in range(K))
+        if cache is not None:
+            cache["hist_" + name] = ext[-(K - 1):]
+        return _bf(F.silu(out), x)
+    q = conv("q", F.linear(x, p["q_proj"])).view(T, nh, dk)
+    k = conv("k", F.linear(x, p["k_proj"])).view(T, nh, dk)
+    v = conv("v", F.linear(x, p["v_proj"])).view(T, nh, dk)
+    g = F.linear(F.linear(x, p["f_a_proj"]), p["f_b_proj"]).view(T, nh, dk)
+    beta = torch.sigmoid(F.linear(x, p["b_proj"]).float())             # [T, nh]
+    outs, states = [], []
+    for h in range(nh):
+        st = None if cache is None or "state" not in cache else cache["state"][h]
+        o, S = kda_recurrent(q[:, h], k[:, h], v[:, h], g[:, h], beta[:, h], p["A_log"][h], p["dt_bias"].view(nh, dk)[h], st)
+        outs.append(o * dk ** -0.5 if p.get("scale_output") else o)
+        states.append(S)
+    if cache is not None:
+        cache["state"] = states
+    o = _bf(torch.stack(outs, 1), x)                                    # [T, nh, dk]
+    gate = torch.sigmoid(F.linear(F.linear(x, p["g_a_proj"]), p["g_b_proj"]).float()).view(T, nh, dk)
+    of = o.float()
+    normed = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + 1e-5) * p["o_norm"].float()
+    return F.linear(_bf(normed * gate, x).reshape(T, nh * dk), p["o_proj"])
+
+
+class DepthMixer:
+    """The bank of depth checkpoints shared by ALL layers of one forward pass (a layer that owned its own copy would start every
+    layer with an empty bank).  ``mix`` is the depth-axis softmax mixture of the bank and the running accumulator; with an empty
+    bank it is the identity."""
+
+    def __init__(self):
+        self.bank: list = []
+
+    def mix(self, prefix_sum, query, keys_proj=None):
+        if not self.bank:
+            return prefix_sum
+        return attn_res_mix(torch.stack(self.bank), prefix_sum, query, keys_proj)
+
+    def push(self, layer_in):
+        self.bank.append(layer_in)
+
+
+def decoder_layer(layer_in, layer_index: int, cfg: K3Config, mixer: DepthMixer, attn, ffn, p: dict):
+    """``KimiDecoderLayer`` (layer.rs): NOT a residual stream.
+
+        prefix = layer_in;  hidden = mix(prefix)                       (identity while the bank is empty)
+        if boundary: bank.push(layer_in); prefix = None
+        hidden = attn(input_layernorm(hidden));     prefix = hidden if prefix is None else prefix + hidden
+        hidden = mix(prefix);  hidden = ffn(post_attention_layernorm(hidden))
+        return prefix + hidden
+
+    ``attn`` / ``ffn`` are callables (MLA or KDA; dense MLP or latent MoE); ``p`` holds the two norms' gains and the two mixture
+    queries (``attn_res_q1``, ``attn_res_q2``)."""
+    prefix = layer_in
+    hidden = mixer.mix(prefix, p["attn_res_q1"])
+    if cfg.is_boundary(layer_index):
+        mixer.push(layer_in)
+        prefix = None
+    hidden = attn(rms_norm(hidden, p["input_layernorm"]))
+    prefix = hidden if prefix is None else prefix + hidden
+    hidden = mixer.mix(prefix, p["attn_res_q2"])
+    hidden = ffn(rms_norm(hidden, p["post_attention_layernorm"]))
+    return prefix + hidden

@@ -1,4 +1,5 @@
 """Property tests of the reference-faithful Inkling and K3 operators (perturb an input, assert which outputs may move)."""
+import pytest
 import torch
 
 from mary_b200.models.inkling import ops as ink
@@ -150,3 +151,50 @@ def test_inkling_layer_has_three_stateful_paths_and_mtp_heads_roll_back():
     assert len(toks) == 2 and rows[0].shape == (20,)
     assert all(torch.equal(c["attn"]["k"], b) for c, b in zip(caches, before))
     assert torch.allclose(ink.embed_in([3, 4], emb, torch.full((H,), 2.0)), 2.0 * ref.rmsnorm(emb[3:5], None, 1e-6))
+
+
+def test_k3_config_partition_kda_shell_and_depth_mixing_layer():
+    from mary_b200.models.k3 import ops as k3
+    cfg = k3.K3Config(6, kda_layers=[1, 2, 4, 5], full_attn_layers=[3, 6], first_k_dense=1, snapshot_every=2, n_heads=2, kda_head_dim=8)
+    assert [cfg.attn_kind(i) for i in range(6)] == ["kda", "kda", "mla", "kda", "kda", "mla"]       # one-based lists
+    assert cfg.is_dense(0) and not cfg.is_dense(1) and [cfg.is_boundary(i) for i in range(5)] == [False, False, True, False, True]
+    with pytest.raises(ValueError, match="missing \\[6\\]"):
+        k3.K3Config(6, [1, 2, 4, 5], [3])
+    with pytest.raises(ValueError, match="duplicated \\[3\\]"):
+        k3.K3Config(6, [1, 2, 3, 4, 5], [3, 6])
+
+    torch.manual_seed(0)
+    H, nh, dk = 24, 2, 8
+    r = lambda *s: torch.randn(*s) * 0.3  # noqa: E731
+    p = dict(q_proj=r(nh * dk, H), k_proj=r(nh * dk, H), v_proj=r(nh * dk, H), q_conv=r(nh * dk, 4), k_conv=r(nh * dk, 4), v_conv=r(nh * dk, 4),
+             f_a_proj=r(6, H), f_b_proj=r(nh * dk, 6), b_proj=r(nh, H), g_a_proj=r(6, H), g_b_proj=r(nh * dk, 6), A_log=r(nh), dt_bias=r(nh * dk),
+             o_norm=torch.ones(dk), o_proj=r(H, nh * dk))
+    x = torch.randn(10, H)
+    full = k3.kda_attention(x, p, cfg)
+    cache = {}
+    parts = [k3.kda_attention(x[:3], p, cfg, cache)] + [k3.kda_attention(x[t:t + 1], p, cfg, cache) for t in range(3, 10)]
+    assert torch.allclose(torch.cat(parts), full, atol=1e-5)                    # O(1) state + three conv histories carry everything
+    assert len(cache["state"]) == nh and cache["state"][0].shape == (dk, dk) and cache["hist_q"].shape == (3, nh * dk)
+    causal = k3.kda_attention(torch.cat([x[:5], torch.randn(5, H)]), p, cfg)
+    assert torch.allclose(causal[:5], full[:5], atol=1e-6)
+
+    # the layer's control flow against a hand-rolled copy, across a boundary
+    lp = dict(input_layernorm=torch.ones(H), post_attention_layernorm=torch.ones(H), attn_res_q1=r(H), attn_res_q2=r(H))
+    attn = lambda h: h * 0.5 + 1.0   # noqa: E731
+    ffn = lambda h: h * -0.25        # noqa: E731
+    mixer = k3.DepthMixer()
+    h0 = torch.randn(4, H)
+    out0 = k3.decoder_layer(h0, 0, cfg, mixer, attn, ffn, lp)                   # empty bank: an ordinary pre-norm residual layer
+    a0 = attn(k3.rms_norm(h0, lp["input_layernorm"]))
+    assert torch.allclose(out0, h0 + a0 + ffn(k3.rms_norm(h0 + a0, lp["post_attention_layernorm"])), atol=1e-6) and mixer.bank == []
+    out1 = k3.decoder_layer(out0, 1, cfg, mixer, attn, ffn, lp)
+    out2 = k3.decoder_layer(out1, 2, cfg, mixer, attn, ffn, lp)                 # boundary: the accumulator restarts from attn's output
+    assert len(mixer.bank) == 1 and torch.equal(mixer.bank[0], out1)
+    a2 = attn(k3.rms_norm(out1, lp["input_layernorm"]))                        # bank was empty before the push: mix = identity
+    m2 = k3.attn_res_mix(out1[None], a2, lp["attn_res_q2"], None)
+    assert torch.allclose(out2, a2 + ffn(k3.rms_norm(m2, lp["post_attention_layernorm"])), atol=1e-6)
+    out3 = k3.decoder_layer(out2, 3, cfg, mixer, attn, ffn, lp)
+    m3 = k3.attn_res_mix(out1[None], out2, lp["attn_res_q1"], None)             # now the first mixture reads the bank too
+    a3 = attn(k3.rms_norm(m3, lp["input_layernorm"]))
+    pre = out2 + a3
+    assert torch.allclose(out3, pre + ffn(k3.rms_norm(k3.attn_res_mix(out1[None], pre, lp["attn_res_q2"], None), lp["post_attention_layernorm"])), atol=1e-6)
