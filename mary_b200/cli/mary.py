@@ -1,5 +1,6 @@
 """``mary import <checkpoint dir|file> --pile P --key K [--dtype f16|bf16|f32] [--name N]``, ``mary keys --pile P``, and the pile
-maintenance commands ``mary branches|verify|stats --pile P`` (the reference's ``pile_branches`` / ``pile_leaf_verify`` binaries).
+maintenance commands ``mary branches|verify|stats|migrate|equiv --pile P`` (the reference's ``pile_branches`` / ``pile_leaf_verify`` /
+``pile_leaf_migrate`` / ``pile_loader_equiv`` binaries).
 
 The front-door CLI of the reference (src/bin/mary.rs:54-240): import a checkpoint (safetensors > gguf > pickle) with its
 ``config.json`` and ``tokenizer.json`` into a pile as one signed commit of the model-graph collection (idempotent: re-importing
@@ -103,6 +104,34 @@ def cmd_stats(a) -> int:
     return 0
 
 
+def cmd_migrate(a) -> int:
+    """Legacy two-blob leaves -> typed tensors, pile to pile into a NEW file (``pile_leaf_migrate``); with ``--branch`` the facts of a
+    legacy named branch are first published into the model-graph collection (the ``model-migration`` step)."""
+    from ..format.migrate import branch_to_collection, migrate_leaves
+    src = Pile.open(a.pile, create=False)
+    key = signing_key_file(a.key)
+    if a.branch:
+        print(f"published {branch_to_collection(src, key)} facts from a legacy branch into the collection")
+    dst = Pile.open(a.out)
+    st = migrate_leaves(src, dst, key)
+    print(" ".join(f"{k}={v}" for k, v in st.items()))
+    dst.close(), src.close()
+    return 0
+
+
+def cmd_equiv(a) -> int:
+    """Compare two piles through the public loader, tensor by tensor (``pile_loader_equiv``); the second must read typed leaves."""
+    from ..format.migrate import loader_equiv
+    x, y = Pile.open(a.pile, create=False), Pile.open(a.other, create=False)
+    try:
+        st = loader_equiv(x, y)
+    except AssertionError as ex:
+        print(f"NOT EQUIVALENT: {ex}")
+        return 1
+    print(f"{st['tensors']} tensors equal through the loader, {st['typed']} typed")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mary")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -128,6 +157,13 @@ def main(argv=None) -> int:
     st = sub.add_parser("stats")
     st.add_argument("--pile", required=True)
     st.set_defaults(fn=cmd_stats)
+    mg = sub.add_parser("migrate")
+    mg.add_argument("--pile", required=True), mg.add_argument("--out", required=True), mg.add_argument("--key", required=True)
+    mg.add_argument("--branch", action="store_true", help="first publish a legacy branch's facts into the model-graph collection")
+    mg.set_defaults(fn=cmd_migrate)
+    eq = sub.add_parser("equiv")
+    eq.add_argument("--pile", required=True), eq.add_argument("--other", required=True)
+    eq.set_defaults(fn=cmd_equiv)
     a = ap.parse_args(argv)
     return a.fn(a)
 

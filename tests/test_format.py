@@ -283,3 +283,43 @@ def test_dyntensor_roundtrip_alignment_and_rejections():
     for bad in (b"abc", b"\\0" * 16, blob[:-2], struct.pack("<IBBH", dt.MAGIC, 99, 0, 0)):
         with pytest.raises(dt.DynTensorError):
             dt.header(bad)
+
+
+def test_legacy_leaves_migrate_to_typed_tensors_keeping_entity_ids(tmp_path, capsys):
+    import numpy as np
+    from mary_b200.cli import mary
+    from mary_b200.format import schema as S
+    from mary_b200.format.leaf import put_array, put_leaf_legacy
+    from mary_b200.format.migrate import loader_equiv, migrate_leaves
+    from mary_b200.format.model import build_model_root, put_module
+    from mary_b200.format.persist import publish_fragment, read_model_pile
+    from mary_b200.pile import Pile, signing_key_file
+    from mary_b200.pile.trible import TribleBuilder
+    key = signing_key_file(str(tmp_path / "k"))
+    src = Pile.open(str(tmp_path / "old.pile"))
+    rng = np.random.default_rng(0)
+    arrs = {"a.weight": rng.standard_normal((4, 6)).astype(np.float32), "b.weight": rng.standard_normal((3,)).astype(np.float16),
+            "c.weight": rng.standard_normal((2, 2, 5)).astype(np.float32)}
+    tb = TribleBuilder()
+    leaves = {"a.weight": put_leaf_legacy(src, tb, arrs["a.weight"]), "b.weight": put_leaf_legacy(src, tb, arrs["b.weight"], f16=True),
+              "c.weight": put_array(src, tb, arrs["c.weight"])}                      # one leaf is typed already
+    members = [put_module(src, tb, n, leaves[n], arrs[n].ndim) for n in arrs]
+    root = build_model_root(src, tb, members, name="old-model")
+    publish_fragment(src, key, tb.build(), "legacy")
+    dst = Pile.open(str(tmp_path / "new.pile"))
+    st = migrate_leaves(src, dst, key)
+    assert st["converted"] == 2 and st["passed_through"] == 0 and st["blobs_dropped"] == 4
+    facts = read_model_pile(dst)
+    for n, e in leaves.items():
+        attrs = {a for a, _ in facts.of_entity(e)}                                 # same entity ids, no legacy facts left
+        assert attrs and not ({S.DATA, S.DATA_F16, S.SHAPE} & attrs)
+    assert loader_equiv(src, dst) == {"tensors": 3, "typed": 3}
+    with pytest.raises(AssertionError, match="typed"):
+        loader_equiv(dst, src)                                                       # the unconverted side must not pass as converted
+    again = Pile.open(str(tmp_path / "again.pile"))
+    assert migrate_leaves(dst, again, key)["converted"] == 0                         # idempotent
+    src.close(), dst.close(), again.close()
+    assert mary.main(["migrate", "--pile", str(tmp_path / "old.pile"), "--out", str(tmp_path / "cli.pile"), "--key", str(tmp_path / "k")]) == 0
+    assert "converted=2" in capsys.readouterr().out
+    assert mary.main(["equiv", "--pile", str(tmp_path / "old.pile"), "--other", str(tmp_path / "cli.pile")]) == 0
+    assert mary.main(["equiv", "--pile", str(tmp_path / "cli.pile"), "--other", str(tmp_path / "old.pile")]) == 1
