@@ -198,3 +198,46 @@ def test_k3_config_partition_kda_shell_and_depth_mixing_layer():
     a3 = attn(k3.rms_norm(m3, lp["input_layernorm"]))
     pre = out2 + a3
     assert torch.allclose(out3, pre + ffn(k3.rms_norm(k3.attn_res_mix(out1[None], pre, lp["attn_res_q2"], None), lp["post_attention_layernorm"])), atol=1e-6)
+
+
+def test_inkling_hmlp_plan_is_derived_and_dmel_sums_codebooks():
+    from mary_b200.models.inkling.towers import HMLP, dmel_embed, fold, plan_scales, stages
+    sc = plan_scales(2, 40, 4, 3)                                   # the released geometry: widths 128, 320, 4800 follow from it
+    assert sc[0] == (1, 1, 1, 3) and sc[-1][:3] == (2, 40, 40)
+    st = stages(sc, 4096)
+    assert [s["output_dim"] for s in st[:-1]] == [128, 320, 4800] and st[-1]["output_dim"] == 4096 and st[0]["input_dim"] == 75
+    assert [s["norm"] for s in st] == [True, True, True, False] and [s["hw_fold"] for s in st] == [5, 2, 4, 1] and st[-1]["t_fold"] == 2
+    assert [s["output_dim"] for s in stages(plan_scales(2, 40, 3, 3), 4096)] == [128, 1216, 4096]      # another depth, other widths
+    total = 1
+    for s in st:
+        total *= s["t_fold"] * s["hw_fold"] ** 2
+    assert total == 2 * 40 * 40
+    other = plan_scales(1, 16, 2, 3)
+    assert other[-1][:3] == (1, 16, 16) and [s["hw_fold"] for s in stages(other, 64)] == [4, 4]
+    # fold order: folded axes outside the channel axis
+    x = torch.arange(2 * 4 * 4 * 3, dtype=torch.float32).view(2, 4, 4, 3)
+    f = fold(x, 2, 2)
+    assert f.shape == (1, 2, 2, 24)
+    assert f[0, 1, 0].view(2, 2, 2, 3)[1, 0, 1].tolist() == x[1, 2, 1].tolist()
+    # a whole tower on random weights against the stage formula
+    torch.manual_seed(0)
+    h = HMLP(2, 4, 2, 3, text_hidden=16)
+    for i, s in enumerate(h.stages):
+        h.proj[i] = torch.randn(s["output_dim"], s["input_dim"]) * 0.1
+        h.norm[i] = torch.ones(s["output_dim"]) if s["norm"] else None
+    px = torch.randn(2, 8, 12, 3)
+    out = h(px)
+    assert out.shape == (1 * 2 * 3, 16)
+    y = px
+    for s, w, g in zip(h.stages, h.proj, h.norm):
+        y = fold(y, s["t_fold"], s["hw_fold"]) @ w.T
+        if s["norm"]:
+            y = torch.nn.functional.gelu(y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + 1e-6))
+    assert torch.allclose(out, y.reshape(-1, 16), atol=1e-5)
+    table = torch.randn(3 * 4, 8)
+    ids = torch.tensor([[0, 3, 1], [2, 2, 2]])
+    e = dmel_embed(ids, table, torch.ones(8), levels=4)
+    raw = table[0] + table[4 + 3] + table[8 + 1]
+    assert torch.allclose(e[0], raw * torch.rsqrt(raw.pow(2).mean() + 1e-6), atol=1e-6)
+    with pytest.raises(ValueError):
+        dmel_embed(torch.tensor([[4, 0, 0]]), table, torch.ones(8), levels=4)
