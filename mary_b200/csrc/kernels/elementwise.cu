@@ -163,10 +163,13 @@ __global__ void glu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* 
 }
 
 __global__ void embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out,
-                             int H, float scale, int vocab) {
+                             int H, float scale, int vocab, int* __restrict__ status) {
   pdl_sync();
   int id = ids[blockIdx.x];
-  if (id < 0 || id >= vocab) id = 0;
+  if (id < 0 || id >= vocab) {                 // recorded, and the access redirected to row 0: no read outside the table
+    if (threadIdx.x == 0) atomicCAS(status, 0, (int)MARY_ERR_BOUNDS);
+    id = 0;
+  }
   const __nv_bfloat16* src = table + (int64_t)id * H;
   __nv_bfloat16* dst = out + (int64_t)blockIdx.x * H;
   for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
@@ -186,7 +189,8 @@ __global__ void qk_norm_rope_append_kernel(const __nv_bfloat16* __restrict__ qkv
                                            const __nv_bfloat16* __restrict__ q_norm, const __nv_bfloat16* __restrict__ k_norm,
                                            int v_norm, const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                            const int64_t* __restrict__ slots, __nv_bfloat16* __restrict__ qo,
-                                           __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, float eps, int T) {
+                                           __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc, float eps, int T,
+                                           int64_t n_slots, int* __restrict__ status) {
   pdl_sync();
   const int warps_per_block = blockDim.x >> 5;
   const int heads = n_q + 2 * n_kv;
@@ -215,6 +219,10 @@ __global__ void qk_norm_rope_append_kernel(const __nv_bfloat16* __restrict__ qkv
   if (do_norm) inv = rsqrtf(warp_sum(ss) / D + eps);
   const float pos = (float)positions[t];
   __nv_bfloat16* dst;
+  if (!is_q && n_slots > 0 && (slots[t] < 0 || slots[t] >= n_slots)) {       // a cache slot outside the cache: record it, skip the write
+    if (lane == 0) atomicCAS(status, 0, (int)MARY_ERR_BOUNDS);
+    return;
+  }
   if (is_q) dst = qo + ((int64_t)t * n_q + hh) * D;
   else if (is_k) dst = kc + (slots[t] * n_kv + (hh - n_q)) * D;
   else dst = vc + (slots[t] * n_kv + (hh - n_q - n_kv)) * D;
@@ -308,21 +316,21 @@ MARY_API int mary_glu(const void* gu, void* out, int T, int F, int act, cudaStre
 MARY_API int mary_embed(const int* ids, const void* table, void* out, int T, int H, float scale, int vocab, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   if (H % 8) return MARY_ERR_BAD_ARG;
-  MARY_LAUNCH(embed_kernel, T, 128, 0, s, ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, H, scale, vocab);
+  MARY_LAUNCH(embed_kernel, T, 128, 0, s, ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, H, scale, vocab, mary_status_ptr());
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
 
 MARY_API int mary_qk_norm_rope_append(const void* qkv, int n_q, int n_kv, int D, const void* q_norm, const void* k_norm, int v_norm,
                                       const float* inv_freq, const int* positions, const int64_t* slots, void* qo, void* kc, void* vc,
-                                      float eps, int T, cudaStream_t s) {
+                                      float eps, int T, int64_t n_slots, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   if (D > 512 || (D & 1)) return MARY_ERR_BAD_ARG;
   const int64_t warps = (int64_t)T * (n_q + 2 * n_kv);
   const int wpb = 8;
   MARY_LAUNCH(qk_norm_rope_append_kernel, (int)((warps + wpb - 1) / wpb), wpb * 32, 0, s, 
       (const __nv_bfloat16*)qkv, n_q, n_kv, D, (const __nv_bfloat16*)q_norm, (const __nv_bfloat16*)k_norm, v_norm, inv_freq, positions,
-      slots, (__nv_bfloat16*)qo, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, eps, T);
+      slots, (__nv_bfloat16*)qo, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, eps, T, n_slots, mary_status_ptr());
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

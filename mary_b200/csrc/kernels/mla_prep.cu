@@ -27,7 +27,7 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
 __global__ void mla_prep_kernel(const __nv_bfloat16* __restrict__ qakv, int64_t ld, int q_lora, const __nv_bfloat16* __restrict__ w_qa,
                                 const __nv_bfloat16* __restrict__ w_kv, const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                 const int64_t* __restrict__ slots, __nv_bfloat16* __restrict__ qa_out, __nv_bfloat16* __restrict__ cache,
-                                float eps) {
+                                float eps, int64_t n_slots, int* __restrict__ status) {
   pdl_sync();
   __shared__ float red[32];
   const int t = blockIdx.x;
@@ -43,6 +43,10 @@ __global__ void mla_prep_kernel(const __nv_bfloat16* __restrict__ qakv, int64_t 
   ss = 0.f;
   for (int i = threadIdx.x; i < 512; i += blockDim.x) { float v = __bfloat162float(ckv[i]); ss += v * v; }
   const float inv_k = rsqrtf(block_sum_256(ss, red) / 512 + eps);
+  if (n_slots > 0 && (slots[t] < 0 || slots[t] >= n_slots)) {                 // a cache slot outside the cache: record it, skip the write
+    if (threadIdx.x == 0) atomicCAS(status, 0, (int)MARY_ERR_BOUNDS);
+    return;
+  }
   __nv_bfloat16* dst = cache + slots[t] * 576;
   for (int i = threadIdx.x; i < 512; i += blockDim.x)
     dst[i] = __float2bfloat16(__bfloat162float(ckv[i]) * inv_k * __bfloat162float(w_kv[i]));
@@ -84,10 +88,11 @@ __global__ void mla_q_rope_kernel(const __nv_bfloat16* __restrict__ qb, const fl
 }  // namespace
 
 MARY_API int mary_mla_prep(const void* qakv, int64_t ld, int q_lora, const void* w_qa, const void* w_kv, const float* inv_freq,
-                           const int* positions, const int64_t* slots, void* qa_out, void* cache, float eps, int T, cudaStream_t s) {
+                           const int* positions, const int64_t* slots, void* qa_out, void* cache, float eps, int T, int64_t n_slots,
+                           cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   MARY_LAUNCH(mla_prep_kernel, T, 256, 0, s, (const __nv_bfloat16*)qakv, ld, q_lora, (const __nv_bfloat16*)w_qa, (const __nv_bfloat16*)w_kv, inv_freq,
-                                    positions, slots, (__nv_bfloat16*)qa_out, (__nv_bfloat16*)cache, eps);
+                                    positions, slots, (__nv_bfloat16*)qa_out, (__nv_bfloat16*)cache, eps, n_slots, mary_status_ptr());
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

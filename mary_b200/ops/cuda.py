@@ -19,7 +19,7 @@ _SIG = {
     "mary_norm_add_norm": "pippppiiffs",
     "mary_glu": "ppiiis",
     "mary_embed": "pppiifis",
-    "mary_qk_norm_rope_append": "piiippipppppp" + "fis",
+    "mary_qk_norm_rope_append": "piiippipppppp" + "fils",
     "mary_short_conv": "ppppiiis",
     "mary_paged_attention": "ppppppppp" + "iii" + "llll" + "iiiiiii" + "ff" + "ps",
     "mary_paged_attention_scratch_floats": "iiii",
@@ -247,7 +247,7 @@ def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm, inv_fr
     q = torch.empty(T, n_q, head_dim, dtype=torch.bfloat16, device=qkv.device)
     check(lib().mary_qk_norm_rope_append(_p(qkv.contiguous()), n_q, n_kv, head_dim, _p(q_norm), _p(k_norm), int(bool(v_norm)),
                                          _p(inv_freq), _p(meta.positions), _p(meta.slot_mapping), _p(q), _p(kcache), _p(vcache),
-                                         eps, T, _stream()), "qk_norm_rope_append")
+                                         eps, T, kcache.shape[0] * kcache.shape[1] if n_kv else 0, _stream()), "qk_norm_rope_append")
     return q
 
 
@@ -462,7 +462,7 @@ def mla_attention(q, cache, meta, scale, nsplit: int | None = None):
     return out
 
 
-declare("mary_mla_prep", "plippppppp" + "fis")
+declare("mary_mla_prep", "plippppppp" + "fils")
 declare("mary_mla_q_rope", "ppppiis")
 declare("mary_gemm_bf16_batched", "pppiiilll" + "illl" + "pfiiiis")
 
@@ -478,7 +478,7 @@ def mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps):
     T = qakv.shape[0]
     qa = torch.empty(T, q_lora, dtype=torch.bfloat16, device=qakv.device)
     check(lib().mary_mla_prep(_p(qakv), qakv.stride(0), q_lora, _p(w_qa), _p(w_kv), _p(inv_freq), _p(meta.positions),
-                              _p(meta.slot_mapping), _p(qa), _p(cache), eps, T, _stream()), "mla_prep")
+                              _p(meta.slot_mapping), _p(qa), _p(cache), eps, T, cache.shape[0] * cache.shape[1], _stream()), "mla_prep")
     return qa
 
 

@@ -310,3 +310,40 @@ def test_codec_cuda_arm_matches_cpu_oracle(K):
         parts.append(cs)
     assert (torch.cat(parts).cpu() == cg).float().mean() > 0.95
     assert K.last_status() == 0
+
+
+@pytest.mark.gpu
+def test_out_of_range_token_ids_and_cache_slots_are_recorded_and_never_dereferenced():
+    """Data-dependent indices are checked where they enter a kernel: a token id outside the table reads row 0 and a cache slot
+    outside the cache is not written; both leave MARY_ERR_BOUNDS (6) in the status word and the context stays usable."""
+    from mary_b200.ops import cuda as K
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    K.last_status()
+    table = torch.randn(50, 64, device="cuda").bfloat16()
+    out = K.embed(torch.tensor([3, 49, 50, -1], dtype=torch.int32, device="cuda"), table)
+    assert K.last_status() == 6
+    assert torch.equal(out[0], table[3]) and torch.equal(out[1], table[49]) and torch.equal(out[2], table[0]) and torch.equal(out[3], table[0])
+    K.embed(torch.tensor([0, 49], dtype=torch.int32, device="cuda"), table)
+    assert K.last_status() == 0
+
+    cache = PagedKVCache(1, 2, 16, 1, 64, dtype=torch.bfloat16, device="cuda")
+    cache.alloc.extend(0, 3)
+    table_, lens = cache.alloc.page_table([0])
+    meta = BatchMeta.build([3], lens, table_, 16, device="cuda")
+    qkv = torch.randn(3, 3 * 64, device="cuda").bfloat16()
+    inv = torch.zeros(32, device="cuda")
+    K.qk_norm_rope_append(qkv, 1, 1, 64, None, None, False, inv, meta, cache.k[0], cache.v[0], 1e-6)
+    assert K.last_status() == 0
+    before = cache.k[0].clone()
+    meta.slot_mapping[1] = 2 * 16                                # one past the last slot of a 2-page cache
+    K.qk_norm_rope_append(qkv, 1, 1, 64, None, None, False, inv, meta, cache.k[0], cache.v[0], 1e-6)
+    assert K.last_status() == 6
+    assert torch.equal(cache.k[0], before)                       # rows 0 and 2 rewritten with the same values, row 1 skipped
+    lat = PagedKVCache(1, 2, 16, 1, 576, dtype=torch.bfloat16, device="cuda", latent_dim=576)
+    qakv = torch.randn(3, 128 + 576, device="cuda").bfloat16()
+    w1, w2 = torch.ones(128, device="cuda").bfloat16(), torch.ones(512, device="cuda").bfloat16()
+    meta.slot_mapping[1] = -5
+    K.mla_prep(qakv, 128, w1, w2, torch.zeros(32, device="cuda"), meta, lat.k[0], 1e-6)
+    assert K.last_status() == 6 and float(lat.k[0].view(-1, 576)[1].abs().sum()) == 0.0
+    assert (torch.ones(4, device="cuda") * 2).sum().item() == 8
