@@ -6,10 +6,28 @@ cache AFTER this step's rows were appended, so row ``j`` of sequence ``i`` sits 
 ``kv_len[i] - q_len[i] + j`` and may attend to positions ``<=`` its own."""
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import numpy as np
 import torch
+
+
+def check_batch(q_lens, kv_lens, page_table, page_size: int, num_pages: int | None = None) -> None:
+    """Host-side bounds check of everything the kernels will index with (run on every ``build`` under ``MARY_DEBUG_CHECKS=1``): the
+    lengths are consistent, every page a row can reach is listed, page ids are inside the cache and no page serves two sequences."""
+    q_lens, kv_lens, page_table = np.asarray(q_lens), np.asarray(kv_lens), np.asarray(page_table)
+    if (q_lens < 0).any() or (kv_lens < q_lens).any():
+        raise ValueError(f"inconsistent lengths: q_lens {q_lens.tolist()} kv_lens {kv_lens.tolist()}")
+    need = (kv_lens + page_size - 1) // page_size
+    if page_table.shape[0] != len(q_lens) or (need > page_table.shape[1]).any():
+        raise ValueError(f"page table {page_table.shape} cannot hold sequences of {kv_lens.tolist()} tokens at {page_size} per page")
+    used = [page_table[s, :need[s]] for s in range(len(q_lens))]
+    flat = np.concatenate(used) if used else np.zeros(0, dtype=np.int64)
+    if (flat < 0).any() or (num_pages is not None and (flat >= num_pages).any()):
+        raise ValueError(f"page id outside the cache (0..{num_pages}): {flat[(flat < 0) | (flat >= (num_pages or flat.max() + 1))][:4].tolist()}")
+    if len(np.unique(flat)) != len(flat):
+        raise ValueError("one page is listed for two positions")
 
 
 @dataclass
@@ -42,6 +60,8 @@ class BatchMeta:
         pages = page_table[seq_index, pos // page_size].astype(np.int64)
         slots = pages * page_size + (pos % page_size)
         dev = torch.device(device)
+        if os.environ.get("MARY_DEBUG_CHECKS") == "1":
+            check_batch(q_lens, kv_lens, page_table, page_size)
 
         def t(a, dt):
             x = torch.from_numpy(np.ascontiguousarray(a)).to(dt)
