@@ -10,7 +10,7 @@ def test_debug_checks_refuse_inconsistent_batches(monkeypatch):
     with pytest.raises(ValueError, match="cannot hold"):
         check_batch([1, 1], [40, 3], table, 16)
     with pytest.raises(ValueError, match="outside the cache"):
-        check_batch([1, 1], [17, 3], table, 16, num_pages=3)
+        check_batch([1, 1], [17, 3], table, 16, num_pages=2)
     with pytest.raises(ValueError, match="two positions"):
         check_batch([1, 1], [17, 3], np.array([[0, 1], [1, 3]], dtype=np.int32), 16)
     with pytest.raises(ValueError, match="inconsistent"):
