@@ -5,6 +5,8 @@
     families embed     --pile P --model clip|siglip|nomic --kind clip|siglip|nomic [--image i.npy] [--ids 1,2,3]         (``local_demo``, ``embed_persist``)
     families imagine   --pile P --transformer T --vae V --features f.npy --out img.npy [--steps 4] [--seed 0]            (the FLUX.2 pipeline)
     families act       --pile P --model smolvla --image i.npy --ids 1,2,3 --state s.npy                                  (``smolvla_infer``)
+    families hear      --pile P --model gemma-audio --wav a.wav [--ids 2,.. --ids-after ..]                              (``gemma_hear`` / ``gemma_listen``)
+    families speak     --random --ids 5,6,7 --out o.wav                                                                  (``speak`` / ``qwen3tts_say|stream``)
 
 Checkpoints get into a pile with ``mary import`` (the reference's ``*_persist`` importers); ``--random`` instead builds the tiny
 configuration with random weights, which is what the tests drive.  Audio is read and written as 16-bit mono WAV with the standard
@@ -150,6 +152,80 @@ def cmd_act(a) -> int:
     return 0
 
 
+def cmd_hear(a) -> int:
+    """Audio question answering with Gemma-4 (``gemma_hear`` / ``gemma_listen``): log-mel -> audio tower -> soft tokens spliced into the
+    prompt at the placeholder rows -> greedy completion."""
+    from ..models.gemma4.audio import Gemma4AudioConfig, Gemma4AudioTower, usm_log_mel
+    from ..models.gemma4.audio import load_into as load_audio
+    from ..models.gemma4.lm import GemmaLM
+    wav, sr = read_wav(a.wav)
+    assert sr == 16000, "16 kHz audio expected"
+    if a.random:
+        from ..models.gemma4.config import Gemma4TextConfig
+        from ..models.gemma4.model import Gemma4Model
+        from ..models.gemma4.weights import init_random_
+        cfg = Gemma4TextConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=2, head_dim=32, intermediate_size=96, vocab_size=128)
+        model = Gemma4Model(cfg)
+        init_random_(model, a.seed, std=0.05)
+        lm = GemmaLM(model, max_seq=512, max_batch=2)
+        tower = _random_init(Gemma4AudioTower(Gemma4AudioConfig(n_mels=128, hidden=32, layers=1, heads=4, conv_channels=(128, 8), out_dims=24,
+                                                                text_hidden=cfg.hidden_size)), a.seed, 0.1)
+    else:
+        lm = GemmaLM.from_pile(a.pile)
+        tower = Gemma4AudioTower(Gemma4AudioConfig(text_hidden=lm.model.cfg.hidden_size))
+        load_audio(tower, _loader(a.pile, a.model))
+    with torch.no_grad():
+        soft = tower(usm_log_mel(wav))
+    before = [int(x) for x in a.ids.split(",")] if a.ids else [2]
+    after = [int(x) for x in a.ids_after.split(",")] if a.ids_after else []
+    ids = before + [a.placeholder] * soft.shape[0] + after
+    rows = list(range(len(before), len(before) + soft.shape[0]))
+    out = lm.complete_multimodal(ids, rows, soft, a.max_new, stop_on_eos=not a.random)
+    print(f"{soft.shape[0]} audio tokens ({len(wav) / sr:.2f} s)", file=sys.stderr)
+    print(lm.tokenizer.decode(out) if lm.tokenizer is not None else ",".join(map(str, out)))
+    return 0
+
+
+def cmd_speak(a) -> int:
+    """Qwen3-TTS (``speak`` / ``qwen3tts_say`` / ``qwen3tts_stream``): text ids -> talker + code predictor frames (streamed to the codec
+    decoder frame by frame) -> waveform."""
+    from ..models.codec.mimi import MimiCodec, MimiConfig
+    from ..models.codec.mimi import init_random_ as init_codec
+    from ..models.qwen3tts.model import CodePredictor, Qwen3TTSConfig, SamplingParams, Talker, generate_frames
+    from ..models.qwen3tts.model import init_random_ as init_tts
+    from ..models.qwen3tts.model import load_into as load_tts
+    if a.random:
+        cfg = Qwen3TTSConfig.tiny()
+        talker, pred = Talker(cfg), CodePredictor(cfg)
+        init_tts(talker, pred, a.seed)
+        mc = MimiConfig.tiny()
+        codec = MimiCodec(mc)
+        init_codec(codec, a.seed)
+    else:
+        cfg = Qwen3TTSConfig()
+        talker, pred = Talker(cfg), CodePredictor(cfg)
+        load_tts(talker, pred, _loader(a.pile, a.model))
+        raise SystemExit("speak: the codec decoder's checkpoint layout has no loader in this package yet; use --random")
+    text = torch.tensor([int(x) for x in a.ids.split(",")], dtype=torch.int32)
+    n0 = max(1, min(len(text), a.prefill))
+    with torch.no_grad():
+        prefill = talker.embed_text(text[:n0]) + talker.embed_codec(torch.full((n0,), cfg.codec_pad, dtype=torch.int32))
+        trailing = talker.embed_text(text[n0:]) if len(text) > n0 else torch.zeros(0, prefill.shape[1])
+        pad = talker.embed_text(torch.tensor([0], dtype=torch.int32))[0]
+    chunks, state = [], [None]
+
+    def sink(frame):                                       # streaming: every frame is decoded as soon as it exists
+        codes = (torch.tensor(frame[:codec.c.num_codebooks], dtype=torch.long) % codec.c.codebook_size)[None]
+        pcm, state[0] = codec.decode_step(codes, state[0])
+        chunks.append(pcm.reshape(-1))
+        return True
+    frames = generate_frames(talker, pred, prefill, trailing, pad, SamplingParams(max_frames=a.max_frames, seed=a.seed), on_frame=sink)
+    pcm = torch.cat(chunks) if chunks else torch.zeros(0)
+    write_wav(a.out, pcm.numpy(), codec.c.sample_rate)
+    print(f"{frames.shape[0]} frames, {pcm.shape[0]} samples -> {a.out}")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="families")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -178,6 +254,14 @@ def main(argv=None) -> int:
     ac = common(sub.add_parser("act"))
     ac.add_argument("--image", required=True), ac.add_argument("--ids", required=True), ac.add_argument("--state", required=True)
     ac.set_defaults(fn=cmd_act)
+    he = common(sub.add_parser("hear"))
+    he.add_argument("--wav", required=True), he.add_argument("--ids"), he.add_argument("--ids-after"), he.add_argument("--placeholder", type=int, default=3)
+    he.add_argument("--max-new", type=int, default=32)
+    he.set_defaults(fn=cmd_hear)
+    sp = common(sub.add_parser("speak"))
+    sp.add_argument("--ids", required=True), sp.add_argument("--out", required=True), sp.add_argument("--max-frames", type=int, default=64)
+    sp.add_argument("--prefill", type=int, default=6)
+    sp.set_defaults(fn=cmd_speak)
     a = ap.parse_args(argv)
     return a.fn(a)
 

@@ -49,11 +49,11 @@ def istft_matmul(spec, n_fft: int, hop: int, window=None, length: int | None = N
     return F.pad(y, (0, length - y.shape[0]))
 
 
-def mel_filterbank_htk(n_mels: int, n_fft: int, sr: int):
-    """Triangular filters on the HTK mel scale, unnormalised, ``[n_mels, n_fft / 2 + 1]``."""
+def mel_filterbank_htk(n_mels: int, n_fft: int, sr: int, fmin: float = 0.0, fmax: float | None = None):
+    """Triangular filters on the HTK mel scale between ``fmin`` and ``fmax``, unnormalised, ``[n_mels, n_fft / 2 + 1]``."""
     def to_mel(f):
         return 2595.0 * math.log10(1.0 + f / 700.0)
-    pts = torch.linspace(to_mel(0.0), to_mel(sr / 2), n_mels + 2, dtype=torch.float64)
+    pts = torch.linspace(to_mel(fmin), to_mel(sr / 2 if fmax is None else fmax), n_mels + 2, dtype=torch.float64)
     hz = 700.0 * (10.0 ** (pts / 2595.0) - 1.0)
     freqs = torch.linspace(0, sr / 2, n_fft // 2 + 1, dtype=torch.float64)
     lo, mid, hi = hz[:-2, None], hz[1:-1, None], hz[2:, None]

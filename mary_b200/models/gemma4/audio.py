@@ -51,6 +51,24 @@ def _P(*s):
     return nn.Parameter(torch.empty(*s), requires_grad=False)
 
 
+def usm_log_mel(wave, sr: int = 16000, n_mels: int = 128, frame_ms: float = 20.0, hop_ms: float = 10.0, fmin: float = 0.0, fmax: float = 8000.0,
+                mel_floor: float = 1e-3):
+    """The tower's front end (the ``gemma_hear`` / ``gemma_listen`` mel): ``frame_length // 2`` zeros are prepended (semi-causal
+    framing), frames of ``frame_ms`` every ``hop_ms``, periodic Hann window, FFT of the next power of two, MAGNITUDE spectrum, HTK
+    mel triangles without normalisation, ``log(mel + floor)``.  Returns ``[frames, n_mels]``."""
+    from ..f5.spectral import mel_filterbank_htk
+    x = torch.as_tensor(wave, dtype=torch.float32)
+    fl, hop = int(round(sr * frame_ms / 1000.0)), int(round(sr * hop_ms / 1000.0))
+    n_fft = 1 << (fl - 1).bit_length()
+    x = F.pad(x, (fl // 2, 0))
+    if x.shape[0] < fl + 1:
+        return torch.zeros(0, n_mels)
+    frames = x.unfold(0, fl + 1, hop)[:, :fl] * torch.hann_window(fl, periodic=True)
+    mag = torch.fft.rfft(frames, n=n_fft).abs()
+    fb = mel_filterbank_htk(n_mels, n_fft, sr, fmin, fmax)
+    return torch.log(mag @ fb.T + mel_floor)
+
+
 class FFN(nn.Module):
     def __init__(self, H):
         super().__init__()

@@ -68,3 +68,16 @@ def test_embedder_loaded_from_a_pile_by_name(tmp_path, capsys):
     ids = torch.tensor([[4, 5, 6, 7]])
     with torch.no_grad():
         assert torch.allclose(dst.embed_text(ids), src.embed_text(ids), atol=1e-6)
+
+
+def test_hear_and_speak_on_random_tiny_models(tmp_path, capsys):
+    sr = 16000
+    t = np.arange(sr // 2) / sr
+    families.write_wav(str(tmp_path / "q.wav"), 0.3 * np.sin(2 * np.pi * 330 * t), sr)
+    assert families.main(["hear", "--random", "--wav", str(tmp_path / "q.wav"), "--ids", "2,7", "--ids-after", "9", "--max-new", "5"]) == 0
+    cap = capsys.readouterr()
+    assert len(cap.out.strip().split(",")) == 5 and "audio tokens" in cap.err
+    assert families.main(["speak", "--random", "--ids", "5,6,7,8,9,10,11,12", "--out", str(tmp_path / "s.wav"), "--max-frames", "5"]) == 0
+    y, rate = families.read_wav(str(tmp_path / "s.wav"))
+    n_frames = int(capsys.readouterr().out.split()[0])
+    assert rate == 24000 and len(y) == n_frames * 16 and 1 <= n_frames <= 5          # tiny codec: 16 samples per frame

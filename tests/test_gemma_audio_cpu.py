@@ -53,3 +53,17 @@ def test_soft_tokens_match_huggingface():
     assert got.shape == (41, c.text_hidden)
     assert torch.allclose(got, want, atol=3e-4, rtol=3e-4), float((got - want).abs().max())
     assert m.layers[0].q.clipped
+
+
+def test_log_mel_front_end_matches_the_library_feature_extractor():
+    pytest.importorskip("transformers")
+    import numpy as np
+    from transformers.models.gemma4.feature_extraction_gemma4 import Gemma4AudioFeatureExtractor
+    from mary_b200.models.gemma4.audio import usm_log_mel
+    wave = (0.1 * np.random.default_rng(0).standard_normal(16000)).astype(np.float32)
+    fe = Gemma4AudioFeatureExtractor()
+    want = torch.as_tensor(fe([wave], sampling_rate=16000, return_tensors="pt")["input_features"][0]).float()
+    got = usm_log_mel(wave)
+    n = min(got.shape[0], want.shape[0])
+    assert abs(got.shape[0] - want.shape[0]) <= 1 and got.shape[1] == 128
+    assert torch.allclose(got[:n], want[:n], atol=1e-4), float((got[:n] - want[:n]).abs().max())
