@@ -342,3 +342,34 @@ MARY_API int mary_short_conv(const void* x, const float* w, void* hist, void* y,
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------------------------
+// Bandwidth probes (the reference's `stream_read`, src/bin/inkling_membw.rs:50): a read-only sweep and a copy over a buffer far
+// larger than L2, 16 bytes per thread per step, grid = 8 CTAs per SM.  `sink` receives a value that depends on every word read.
+namespace {
+__global__ void stream_read_kernel(const uint4* __restrict__ src, int64_t n16, unsigned* __restrict__ sink) {
+  unsigned acc = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 v = __ldcs(src + i);
+    acc ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  if (acc == 0x9e3779b9u) atomicAdd(sink, 1u);            // practically never true: keeps the loads alive without a write per thread
+}
+__global__ void stream_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int64_t n16) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) __stcs(dst + i, __ldcs(src + i));
+}
+}  // namespace
+
+MARY_API int mary_stream_read(const void* src, int64_t bytes, void* sink, cudaStream_t s) {
+  if (((uintptr_t)src & 15) || bytes < 16) return MARY_ERR_BAD_ARG;
+  stream_read_kernel<<<mary_num_sms() * 8, 256, 0, s>>>((const uint4*)src, bytes / 16, (unsigned*)sink);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_stream_copy(const void* src, void* dst, int64_t bytes, cudaStream_t s) {
+  if (((uintptr_t)src & 15) || ((uintptr_t)dst & 15) || bytes < 16) return MARY_ERR_BAD_ARG;
+  stream_copy_kernel<<<mary_num_sms() * 8, 256, 0, s>>>((const uint4*)src, (uint4*)dst, bytes / 16);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}

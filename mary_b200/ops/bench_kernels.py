@@ -165,6 +165,23 @@ def bench_moe(E: int = 48, H: int = 7168, F: int = 2048, T: int = 384, k: int = 
     assert K.last_status() == 0
 
 
+def bench_membw(gib: int = 2, iters: int = 10):
+    """Own read and copy sweeps over a buffer far larger than L2 (the reference's ``inkling_membw``), beside the measured copy peak."""
+    from .cuda import _p, _stream, check, declare, lib
+    declare("mary_stream_read", "plps")
+    declare("mary_stream_copy", "ppls")
+    hbm, _, tag = peaks()
+    n = gib << 30
+    src = torch.empty(n, dtype=torch.uint8, device="cuda").random_()
+    dst = torch.empty_like(src)
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ms = time_op(lambda: check(lib().mary_stream_read(_p(src), n, _p(sink), _stream()), "stream_read"), iters)
+    print(f"stream read {gib} GiB: {ms:.3f} ms, {n / ms / 1e6:.0f} GB/s, {n / ms / 1e6 / hbm:.2f} {tag}")
+    ms = time_op(lambda: check(lib().mary_stream_copy(_p(src), _p(dst), n, _stream()), "stream_copy"), iters)
+    print(f"stream copy {gib} GiB: {ms:.3f} ms, {2 * n / ms / 1e6:.0f} GB/s read + write, {2 * n / ms / 1e6 / hbm:.2f} {tag}")
+    assert torch.equal(src[-4096:], dst[-4096:])
+
+
 def bench_floor(reps: int = 200):
     """Per-launch cost of decode-sized kernels in steady state: ``reps`` back-to-back launches recorded in one CUDA graph and
     replayed (what a decode step sees), against the same launches issued eagerly."""
@@ -226,6 +243,8 @@ if __name__ == "__main__":
     # ``gemm M N K`` / ``attn B L Hq Hkv D window`` / ``fa B L Hq Hkv DK DV window`` / ``mla B L Hq q_len`` / ``moe E H F T k`` run that one case only
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
     nums = [int(v) for v in sys.argv[2:]]
+    if what == "membw":
+        bench_membw(*nums)
     if what in ("gemm", "all"):
         bench_gemm([tuple(nums)] if nums and what == "gemm" else None)
     if what in ("attn", "all"):

@@ -347,3 +347,18 @@ def test_out_of_range_token_ids_and_cache_slots_are_recorded_and_never_dereferen
     K.mla_prep(qakv, 128, w1, w2, torch.zeros(32, device="cuda"), meta, lat.k[0], 1e-6)
     assert K.last_status() == 6 and float(lat.k[0].view(-1, 576)[1].abs().sum()) == 0.0
     assert (torch.ones(4, device="cuda") * 2).sum().item() == 8
+
+
+@pytest.mark.gpu
+def test_stream_probes_copy_exactly_and_reject_misaligned_buffers():
+    from mary_b200.ops.cuda import _p, _stream, declare, lib
+    declare("mary_stream_read", "plps")
+    declare("mary_stream_copy", "ppls")
+    src = torch.empty(1 << 22, dtype=torch.uint8, device="cuda").random_()
+    dst = torch.zeros_like(src)
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert lib().mary_stream_copy(_p(src), _p(dst), src.numel(), _stream()) == 0
+    assert lib().mary_stream_read(_p(src), src.numel(), _p(sink), _stream()) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(src, dst)
+    assert lib().mary_stream_copy(_p(src[1:]), _p(dst), 1024, _stream()) == 4            # MARY_ERR_BAD_ARG: not 16-byte aligned
