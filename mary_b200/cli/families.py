@@ -7,6 +7,7 @@
     families act       --pile P --model smolvla --image i.npy --ids 1,2,3 --state s.npy                                  (``smolvla_infer``)
     families hear      --pile P --model gemma-audio --wav a.wav [--ids 2,.. --ids-after ..]                              (``gemma_hear`` / ``gemma_listen``)
     families speak     --random --ids 5,6,7 --out o.wav                                                                  (``speak`` / ``qwen3tts_say|stream``)
+    families converse  --random --wav in.wav --out agent.wav                                                             (``personaplex_listen``)
 
 Checkpoints get into a pile with ``mary import`` (the reference's ``*_persist`` importers); ``--random`` instead builds the tiny
 configuration with random weights, which is what the tests drive.  Audio is read and written as 16-bit mono WAV with the standard
@@ -226,6 +227,41 @@ def cmd_speak(a) -> int:
     return 0
 
 
+def cmd_converse(a) -> int:
+    """Full-duplex speech LM (``personaplex_listen``): the user's audio is encoded frame by frame with the streaming codec, every frame
+    runs one temporal + depformer step (the user's codes are forced into their streams, text and the agent's codes are generated),
+    the agent's codes are decoded to audio frame by frame.  Prints the text tokens; writes the agent's waveform."""
+    from ..models.codec.mimi import MimiCodec, MimiConfig
+    from ..models.codec.mimi import init_random_ as init_codec
+    from ..models.moshi import LmGen, MoshiConfig
+    from ..models.moshi import init_random_ as init_lm
+    if not a.random:
+        raise SystemExit("converse: only --random is wired up; the speech LM's checkpoint layout has no loader in this package yet")
+    c = MoshiConfig.tiny()
+    mc = MimiConfig.tiny()
+    mc.num_codebooks, mc.codebook_size = c.codebooks_per_stream, c.card
+    codec, lm = MimiCodec(mc), LmGen(c)
+    init_codec(codec, a.seed), init_lm(lm, a.seed)
+    wav, sr = read_wav(a.wav)
+    spf = mc.samples_per_frame
+    n = len(wav) // spf
+    enc_state = dec_state = None
+    text, chunks = [], []
+    with torch.no_grad():
+        for f in range(min(n, c.context - 2)):
+            codes, enc_state = codec.encode_step(torch.from_numpy(wav[f * spf:(f + 1) * spf]).float(), enc_state)
+            out = lm.step(user_audio=[int(x) for x in codes.reshape(-1)[:c.codebooks_per_stream]])
+            if out is None:                              # still inside the delay horizon
+                continue
+            text.append(out[0])
+            agent = torch.tensor(out[1:1 + c.codebooks_per_stream], dtype=torch.long)[None] % mc.codebook_size
+            pcm, dec_state = codec.decode_step(agent, dec_state)
+            chunks.append(pcm.reshape(-1))
+    write_wav(a.out, (torch.cat(chunks) if chunks else torch.zeros(0)).numpy(), mc.sample_rate)
+    print(",".join(map(str, text)))
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="families")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -262,6 +298,9 @@ def main(argv=None) -> int:
     sp.add_argument("--ids", required=True), sp.add_argument("--out", required=True), sp.add_argument("--max-frames", type=int, default=64)
     sp.add_argument("--prefill", type=int, default=6)
     sp.set_defaults(fn=cmd_speak)
+    cv = common(sub.add_parser("converse"))
+    cv.add_argument("--wav", required=True), cv.add_argument("--out", required=True)
+    cv.set_defaults(fn=cmd_converse)
     a = ap.parse_args(argv)
     return a.fn(a)
 

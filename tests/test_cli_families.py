@@ -81,3 +81,13 @@ def test_hear_and_speak_on_random_tiny_models(tmp_path, capsys):
     y, rate = families.read_wav(str(tmp_path / "s.wav"))
     n_frames = int(capsys.readouterr().out.split()[0])
     assert rate == 24000 and len(y) == n_frames * 16 and 1 <= n_frames <= 5          # tiny codec: 16 samples per frame
+
+
+def test_converse_streams_user_audio_through_codec_and_speech_lm(tmp_path, capsys):
+    sr = 24000
+    t = np.arange(16 * 12) / sr                                   # 12 codec frames of the tiny codec
+    families.write_wav(str(tmp_path / "u.wav"), 0.3 * np.sin(2 * np.pi * 440 * t), sr)
+    assert families.main(["converse", "--random", "--wav", str(tmp_path / "u.wav"), "--out", str(tmp_path / "a.wav")]) == 0
+    toks = capsys.readouterr().out.strip().split(",")
+    y, _ = families.read_wav(str(tmp_path / "a.wav"))
+    assert 8 <= len(toks) <= 12 and len(y) == len(toks) * 16
