@@ -97,6 +97,8 @@ class ClockSampler:
 
 
 def reference_arm(args):
+    if int(os.environ.get("RANK", "0")) != 0:          # launched one process per GPU like the own arm: one line, from rank 0
+        return
     print(json.dumps({"impl": "reference", "unavailable":
                       "the reference is a Rust crate (Cargo.toml) whose path dependencies ../triblespace-rs and ../cubecl-fork are "
                       "not in the tree and no cargo/rustc exists in this image; pip cannot install it (no setup.py/pyproject.toml)"}))
