@@ -2,8 +2,8 @@
 
 The ids are the reference's, so that facts written by either side name the same attributes
 (src/format.rs:52-127, src/leaf.rs:51-61, src/models/inkling/pile.rs:416-464,
-src/jsonfacts.rs:89-102, src/models/gemma/lora.rs:43-53).  Ids the survey only gives in
-abbreviated form are completed deterministically from their visible prefix and suffix.
+src/jsonfacts.rs:89-102, src/models/gemma/lora.rs:43-53).  Ids known here only in abbreviated
+form are completed deterministically from their visible prefix and suffix.
 """
 from __future__ import annotations
 
