@@ -36,6 +36,10 @@ struct AttnParams {
   int64_t k_tok, k_page, v_tok, v_page;
   int Hq, Hkv, G, DK, DV, RQ, nsplit, window;
   float scale, softcap;
+  // optional additive relative-position bias (the reference's score epilogue, src/models/inkling/scorebias.rs:97-221):
+  // rel[(row * Hq + head) * rel_extent + dist] is added to the scaled score of the key `dist` positions back, dist < rel_extent
+  const float* rel;
+  int rel_extent;
 };
 
 template <int VPL, int RMAX>   // V dims per lane = DV / 32; RMAX = most score rows of a q block
@@ -112,6 +116,11 @@ paged_attn_kernel(const AttnParams p) {
       if (r < R) {
         const int qp = pos0 + r / p.G;
         float sv = s[r];
+        if (p.rel) {
+          const int dist = qp - kp;
+          if (valid && dist >= 0 && dist < p.rel_extent)
+            sv += p.rel[((int64_t)(row0 + r / p.G) * p.Hq + kvh * p.G + r % p.G) * p.rel_extent + dist];
+        }
         if (p.softcap > 0.f) sv = p.softcap * tanhf(sv / p.softcap);
         const bool ok = valid && kp <= qp && (p.window <= 0 || qp - kp < p.window);
         sv = ok ? sv : -INFINITY;
@@ -233,13 +242,40 @@ MARY_API int mary_paged_attention_max_rows(int DV) { return DV <= 128 ? 16 : (DV
 // q [T, Hq, DK] bf16, caches addressed by (page, token-in-page, kv head) with element strides, out [T, Hq, DV].
 // blk_seq / blk_q0 describe NB q blocks of at most RQ rows each; RQ * (Hq/Hkv) must not exceed
 // mary_paged_attention_max_rows(DV) (the register budget of the DV specialisation).
+static int paged_attention_impl(const void* q, const void* kc, const void* vc, void* out, const int* page_table,
+                                const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
+                                int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok, int64_t v_page,
+                                int Hq, int Hkv, int DK, int DV, int RQ, int nsplit, int window, float scale, float softcap,
+                                float* scratch, const float* rel, int rel_extent, cudaStream_t s);
+
 MARY_API int mary_paged_attention(const void* q, const void* kc, const void* vc, void* out, const int* page_table,
                                   const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
                                   int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok, int64_t v_page,
                                   int Hq, int Hkv, int DK, int DV, int RQ, int nsplit, int window, float scale, float softcap,
                                   float* scratch, cudaStream_t s) {
+  return paged_attention_impl(q, kc, vc, out, page_table, kv_len, q_start, blk_seq, blk_q0, NB, max_pages, page_size, k_tok, k_page, v_tok,
+                              v_page, Hq, Hkv, DK, DV, RQ, nsplit, window, scale, softcap, scratch, nullptr, 0, s);
+}
+
+// The same with an additive relative-position bias rel[T, Hq, rel_extent] (f32).
+MARY_API int mary_paged_attention_rel(const void* q, const void* kc, const void* vc, void* out, const int* page_table,
+                                      const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
+                                      int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok, int64_t v_page,
+                                      int Hq, int Hkv, int DK, int DV, int RQ, int nsplit, int window, float scale, float softcap,
+                                      float* scratch, const float* rel, int rel_extent, cudaStream_t s) {
+  if (rel && rel_extent <= 0) return MARY_ERR_BAD_ARG;
+  return paged_attention_impl(q, kc, vc, out, page_table, kv_len, q_start, blk_seq, blk_q0, NB, max_pages, page_size, k_tok, k_page, v_tok,
+                              v_page, Hq, Hkv, DK, DV, RQ, nsplit, window, scale, softcap, scratch, rel, rel_extent, s);
+}
+
+static int paged_attention_impl(const void* q, const void* kc, const void* vc, void* out, const int* page_table,
+                                const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
+                                int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok, int64_t v_page,
+                                int Hq, int Hkv, int DK, int DV, int RQ, int nsplit, int window, float scale, float softcap,
+                                float* scratch, const float* rel, int rel_extent, cudaStream_t s) {
   if (NB <= 0) return MARY_OK;
   AttnParams p;
+  p.rel = rel; p.rel_extent = rel_extent;
   p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)kc; p.vc = (const __nv_bfloat16*)vc; p.out = (__nv_bfloat16*)out;
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_q0 = blk_q0;
   p.max_pages = max_pages; p.page_size = page_size; p.k_tok = k_tok; p.k_page = k_page; p.v_tok = v_tok; p.v_page = v_page;

@@ -70,10 +70,11 @@ def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm: bool, 
     return q
 
 
-def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0):
+def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, rel_bias=None):
+    """``rel_bias [T, Hq, extent]`` (f32): an additive bias on the scaled score of the key ``dist`` positions back, for ``dist < extent``."""
     if _cuda(q):
-        return _k().paged_attention(q, kcache, vcache, meta, scale, window, softcap)
-    return ref.paged_attention(q, kcache, vcache, meta, scale, window, softcap)
+        return _k().paged_attention(q, kcache, vcache, meta, scale, window, softcap, rel_bias=rel_bias)
+    return ref.paged_attention(q, kcache, vcache, meta, scale, window, softcap, rel_bias=rel_bias)
 
 
 def mla_attention(q, cache, meta, scale):

@@ -337,8 +337,11 @@ def attention_prefill(q, kcache, vcache, meta, scale, window=0):
     return out
 
 
+declare("mary_paged_attention_rel", "ppppppppp" + "iii" + "llll" + "iiiiiii" + "ff" + "ppi" + "s")
+
+
 def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: int | None = None, nsplit: int | None = None,
-                    kernel: str = "auto"):
+                    kernel: str = "auto", rel_bias=None):
     """``q[T, Hq, DK]``; caches ``[pages, page, Hkv, D]`` (a latent cache is ``Hkv = 1`` with ``dv`` < DK and
     ``vcache is kcache``).  Returns ``[T, Hq, DV]``.  ``kernel``: ``auto`` picks the tensor-core prefill kernel for long query
     blocks, the bandwidth-oriented kernel for decode-shaped batches and the general split-KV kernel otherwise."""
@@ -346,6 +349,9 @@ def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: i
     Hkv = kcache.shape[2] if kcache.dim() == 4 else 1
     DV = dv or vcache.shape[-1]
     G = Hq // Hkv
+    if rel_bias is not None:                     # ``rel_bias [T, Hq, extent]`` f32, added to the scaled score of the key ``dist`` back
+        kernel = "general"
+        assert rel_bias.dtype == torch.float32 and rel_bias.shape[:2] == (T, Hq) and rel_bias.is_contiguous()
     if kernel in ("auto", "prefill") and kcache.dim() == 4 and dv is None and softcap == 0.0 and meta.page_size in (16, 32, 64) \
             and lib().mary_attention_prefill_supported(DK, DV) and q.dtype == torch.bfloat16 \
             and (kernel == "prefill" or T >= PREFILL_MIN_ROWS * meta.num_seqs):
@@ -371,6 +377,12 @@ def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: i
         scratch = torch.empty(n, dtype=torch.float32, device=q.device)
     ktok, kpage = kcache.stride(1), kcache.stride(0)
     vtok, vpage = vcache.stride(1), vcache.stride(0)
+    if rel_bias is not None:
+        check(lib().mary_paged_attention_rel(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
+                                             _p(meta.q_start), _p(blk_seq), _p(blk_q0), NB, meta.page_table.shape[1], meta.page_size,
+                                             ktok, kpage, vtok, vpage, Hq, Hkv, DK, DV, rq, nsplit, window, scale, softcap,
+                                             _p(scratch), _p(rel_bias), rel_bias.shape[2], _stream()), "paged_attention_rel")
+        return out
     check(lib().mary_paged_attention(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
                                      _p(meta.q_start), _p(blk_seq), _p(blk_q0), NB, meta.page_table.shape[1], meta.page_size,
                                      ktok, kpage, vtok, vpage, Hq, Hkv, DK, DV, rq, nsplit, window, scale, softcap,

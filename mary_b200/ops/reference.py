@@ -60,7 +60,7 @@ def gather_pages(cache, page_row, kv_len: int):
     return cache[page_row[:n].long()].reshape(n * ps, *cache.shape[2:])[:kv_len]
 
 
-def paged_attention(q, kcache, vcache, meta, scale: float, window: int = 0, softcap: float = 0.0, dv: int | None = None):
+def paged_attention(q, kcache, vcache, meta, scale: float, window: int = 0, softcap: float = 0.0, dv: int | None = None, rel_bias=None):
     """Causal (optionally sliding-window) attention of the flattened batch over the paged cache.
     ``q[T, Hq, D]``; caches ``[pages, page, Hkv, D]``; GQA by index; softmax in f32.  A latent cache
     (``[pages, page, D]``, one shared kv head) passes ``vcache is kcache`` and ``dv`` = value width (the first ``dv`` dims)."""
@@ -87,6 +87,12 @@ def paged_attention(q, kcache, vcache, meta, scale: float, window: int = 0, soft
         Kh = K.repeat_interleave(g, dim=1)
         Vh = V.repeat_interleave(g, dim=1)
         sc = torch.einsum("nhd,lhd->hnl", Q, Kh) * scale
+        if rel_bias is not None:                 # rel_bias[row, head, dist] for keys dist positions back, zero outside the extent
+            dist = qpos[:, None] - kpos[None, :]
+            ext = rel_bias.shape[-1]
+            inside = (dist >= 0) & (dist < ext)
+            rb = rel_bias[a:b].float().permute(1, 0, 2)                       # [Hq, n, ext]
+            sc = sc + torch.gather(rb, 2, dist.clamp(0, ext - 1)[None].expand(Hq, -1, -1)) * inside[None]
         if softcap > 0:
             sc = softcap * torch.tanh(sc / softcap)
         mask = kpos[None, :] <= qpos[:, None]

@@ -241,3 +241,28 @@ def test_inkling_hmlp_plan_is_derived_and_dmel_sums_codebooks():
     assert torch.allclose(e[0], raw * torch.rsqrt(raw.pow(2).mean() + 1e-6), atol=1e-6)
     with pytest.raises(ValueError):
         dmel_embed(torch.tensor([[4, 0, 0]]), table, torch.ones(8), levels=4)
+
+
+def test_inkling_paged_attention_matches_the_reference_operator():
+    from mary_b200.models.inkling import ops as ink
+    from mary_b200.models.inkling.paged import InklingPagedAttention
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    torch.manual_seed(0)
+    H, Hq, Hkv, D = 32, 4, 2, 8
+    cfg = dict(n_heads=Hq, n_kv_heads=Hkv, head_dim=D, d_rel=4, log_alpha=0.1, log_n_floor=4.0, window=6, eps=1e-6)
+    r = lambda *s: torch.randn(*s) * 0.3  # noqa: E731
+    p = dict(wq=r(Hq * D, H), wk=r(Hkv * D, H), wv=r(Hkv * D, H), wo=r(H, Hq * D), wr=r(Hq * 4, H), rel_proj=r(4, 8),
+             q_norm=1 + 0.1 * r(D), k_norm=1 + 0.1 * r(D), k_conv=r(Hkv * D, 4), v_conv=r(Hkv * D, 4))
+    x = torch.randn(21, H)
+    for is_global in (True, False):
+        want = ink.attention(x, p, cfg, is_global=is_global)
+        cache = PagedKVCache(1, 4, 16, Hkv, D, dtype=torch.float32)
+        att = InklingPagedAttention(p, cfg, is_global)
+        outs, done = [], 0
+        for n in (9, 1, 1, 7, 3):                                   # a prefill chunk, decode steps, another chunk
+            cache.alloc.extend(0, n)
+            table, lens = cache.alloc.page_table([0])
+            outs.append(att(x[done:done + n], BatchMeta.build([n], lens, table, 16), cache.k[0], cache.v[0]))
+            done += n
+        assert torch.allclose(torch.cat(outs), want, atol=2e-5), (is_global, float((torch.cat(outs) - want).abs().max()))

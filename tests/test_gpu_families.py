@@ -163,3 +163,31 @@ def test_flow_models_smolvla_f5_flux():
     with torch.no_grad():
         _close(_gpu(f)(lat.cuda().bfloat16(), txt.cuda().bfloat16(), 0.6, position_ids(3, 4), position_ids(n_text=5)),
                f(lat, txt, 0.6, position_ids(3, 4), position_ids(n_text=5)), 0.08)
+
+
+def test_inkling_attention_with_relative_bias_on_the_paged_cache():
+    """The model's own score rule (K / V short convolutions, per-head norms, relative-position bias through the attention kernel's
+    additive hook, log scaling, window) on the GPU against the f32 reference operator."""
+    from mary_b200.models.inkling import ops as ink
+    from mary_b200.models.inkling.paged import InklingPagedAttention
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    H, Hq, Hkv, D = 128, 4, 2, 64
+    cfg = dict(n_heads=Hq, n_kv_heads=Hkv, head_dim=D, d_rel=16, log_alpha=0.1, log_n_floor=8.0, window=24, eps=1e-6)
+    g = torch.Generator().manual_seed(3)
+    r = lambda *s: (torch.randn(*s, generator=g) * 0.2).bfloat16().float()  # noqa: E731
+    p = dict(wq=r(Hq * D, H), wk=r(Hkv * D, H), wv=r(Hkv * D, H), wo=r(H, Hq * D), wr=r(Hq * 16, H), rel_proj=r(16, 64),
+             q_norm=(1 + 0.1 * r(D)), k_norm=(1 + 0.1 * r(D)), k_conv=r(Hkv * D, 4), v_conv=r(Hkv * D, 4))
+    x = (torch.randn(70, H, generator=g)).bfloat16().float()
+    pg = {k: v.cuda().bfloat16() for k, v in p.items()}
+    for is_global in (True, False):
+        want = ink.attention(x, p, cfg, is_global=is_global)
+        cache = PagedKVCache(1, 6, 16, Hkv, D, dtype=torch.bfloat16, device="cuda")
+        att = InklingPagedAttention(pg, cfg, is_global)
+        outs, done = [], 0
+        for n in (40, 1, 1, 28):
+            cache.alloc.extend(0, n)
+            table, lens = cache.alloc.page_table([0])
+            outs.append(att(x[done:done + n].cuda().bfloat16(), BatchMeta.build([n], lens, table, 16, device="cuda"), cache.k[0], cache.v[0]))
+            done += n
+        _close(torch.cat(outs), want, 0.05)
