@@ -97,6 +97,9 @@ class Gemma4Layer(nn.Module):
         ci = self.cache_layer
         q = ops.qk_norm_rope_append(qkv, self.n_q, self.n_kv if self.kv_source is None else 0, self.D, self.q_norm, self.k_norm, True,
                                     self.inv_freq, meta, cache.k[ci], cache.v[ci], c.rms_norm_eps)
+        cp = getattr(self.tp, "cp", None)
+        if cp is not None and self.kv_source is None:
+            cp.share(cache.k[ci], cache.v[ci])           # context-parallel prefill: earlier chunks' K / V of this layer become local
         o = ops.paged_attention(q, cache.k[ci], cache.v[ci], meta, 1.0, self.window)
         o = o.reshape(o.shape[0], -1)
         sp = getattr(self.tp, "sp", None)

@@ -1,0 +1,66 @@
+"""Context parallelism for long prefills: the rows of ONE sequence are cut into contiguous chunks, one per rank; every rank runs all
+layers on its own rows only, and after each layer's cache append the ranks exchange that layer's new K / V rows so that a rank's
+local paged cache holds every position its (causal) queries can see.  Attention itself stays a purely local kernel over local
+pages — remote K / V are copied into this GPU's memory first and read from there (no kernel ever loads a peer's memory, no TMA
+touches a peer), which is the form the build plan asks for (the reference has no sequence parallelism at all, it scales length
+on one device by banding and query blocking).
+
+The exchange is an all-gather of equal-size row blocks through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo on CPU ranks);
+a rank copies in only the chunks BEFORE its own, since later positions are masked anyway.  All ranks build the same page table
+(the allocators are deterministic), so a position's slot is the same everywhere.  Memory and attention FLOPs per rank shrink by
+the number of ranks for the projections / MLPs and by about half of that for attention (rank ``r`` attends to ``r + 1`` chunks)."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..runtime.batch import BatchMeta
+
+
+class ContextParallel:
+    def __init__(self, rank: int, world: int, group=None):
+        self.rank, self.world, self.group = rank, world, group
+        self.bounds = None
+        self.slots = None
+
+    def begin(self, n_tokens: int, page_table: np.ndarray, page_size: int, device="cpu") -> BatchMeta:
+        """Plan one prefill of ``n_tokens`` rows (sequence 0 of ``page_table``): returns the meta of THIS rank's rows."""
+        per = -(-n_tokens // self.world)
+        self.bounds = [(min(r * per, n_tokens), min((r + 1) * per, n_tokens)) for r in range(self.world)]
+        self.per = per
+        pos = np.arange(n_tokens)
+        slots = page_table[0, pos // page_size].astype(np.int64) * page_size + pos % page_size
+        self.slots = torch.from_numpy(slots).to(device)
+        lo, hi = self.bounds[self.rank]
+        return BatchMeta.build([hi - lo], [hi], page_table, page_size, device=device)
+
+    def rows(self, x):
+        """This rank's slice of a per-row tensor of the whole prompt."""
+        lo, hi = self.bounds[self.rank]
+        return x[lo:hi]
+
+    def share(self, kcache, vcache) -> None:
+        """After this rank appended its rows of one layer: fetch the rows of all earlier chunks into the local cache."""
+        if self.world == 1:
+            return
+        lo, hi = self.bounds[self.rank]
+        for cache in ((kcache,) if vcache is kcache or vcache is None else (kcache, vcache)):
+            flat = cache.view(-1, *cache.shape[2:])
+            mine = torch.zeros(self.per, *flat.shape[1:], dtype=flat.dtype, device=flat.device)
+            if hi > lo:
+                mine[:hi - lo] = flat[self.slots[lo:hi]]
+            got = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(got, mine, group=self.group)
+            for r in range(self.rank):                        # later chunks are never visible to this rank's queries
+                a, b = self.bounds[r]
+                if b > a:
+                    flat[self.slots[a:b]] = got[r][:b - a]
+
+    def gather_rows(self, x):
+        """Concatenate every rank's rows (e.g. logits of the whole prompt) in sequence order."""
+        pad = torch.zeros(self.per, *x.shape[1:], dtype=x.dtype, device=x.device)
+        pad[:x.shape[0]] = x
+        got = [torch.empty_like(pad) for _ in range(self.world)]
+        dist.all_gather(got, pad, group=self.group)
+        return torch.cat([got[r][:b - a] for r, (a, b) in enumerate(self.bounds)], 0)

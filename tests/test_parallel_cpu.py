@@ -191,3 +191,57 @@ def test_vocab_parallel_head_matches_full_argmax_and_samples_inside_top_k():
     for r in range(4):
         seen = set(draws[:, r].tolist())
         assert seen <= set(top5[r].tolist()) and len(seen) >= 2  # draws stay inside the global top-k and do vary
+
+
+def _cp_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mary_b200.models.gemma4.config import Gemma4TextConfig
+    from mary_b200.models.gemma4.model import Gemma4Model, _NoTP
+    from mary_b200.models.gemma4.weights import init_random_
+    from mary_b200.parallel.cp import ContextParallel
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    cfg = Gemma4TextConfig(hidden_size=64, num_hidden_layers=4, num_attention_heads=2, head_dim=32, intermediate_size=96, vocab_size=100,
+                           sliding_window=8, num_kv_shared_layers=2)
+    m = Gemma4Model(cfg)
+    init_random_(m, 0, std=0.05)
+    n = 37                                                          # ragged: chunks of 13, 13, 11
+    ids = torch.randint(0, 100, (n,), dtype=torch.int32, generator=torch.Generator().manual_seed(1))
+    spec = m.kv_spec()
+
+    def fresh():
+        c = PagedKVCache(spec["num_layers"], 4, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32)
+        c.alloc.extend(0, n)
+        return c, c.alloc.page_table([0])
+    cache, (table, lens) = fresh()
+    with torch.no_grad():
+        want = m(ids, BatchMeta.build([n], lens, table, 16), cache)
+    tp = _NoTP()
+    tp.cp = ContextParallel(rank, world)
+    for layer in m.layers:
+        layer.tp = tp
+    m.tp = tp
+    cache, (table, lens) = fresh()
+    meta = tp.cp.begin(n, table, 16)
+    with torch.no_grad():
+        mine = m(tp.cp.rows(ids), meta, cache)
+        got = tp.cp.gather_rows(mine)
+    lo, hi = tp.cp.bounds[rank]
+    out.put((rank, float((got - want).abs().max()), mine.shape[0] == hi - lo, float((mine - want[lo:hi]).abs().max())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_context_parallel_prefill_equals_the_single_rank_prefill():
+    world = 3
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_cp_worker, args=(r, world, port, out)) for r in range(world)]
+    [p.start() for p in ps]
+    res = sorted(out.get(timeout=120) for _ in range(world))
+    [p.join(60) for p in ps]
+    for rank, err_all, rows_ok, err_mine in res:
+        assert rows_ok and err_all < 1e-5 and err_mine < 1e-5, res
