@@ -182,6 +182,24 @@ def bench_membw(gib: int = 2, iters: int = 10):
     assert torch.equal(src[-4096:], dst[-4096:])
 
 
+def bench_bf16moe(E: int = 128, H: int = 2816, F: int = 704, T: int = 32, k: int = 8, iters: int = 10):
+    """Unquantised routed experts (the grouped bf16 GEMM): device plan + gather + two grouped GEMMs + un-permute, against the per-expert
+    loop.  Bytes = weights of the experts that are hit (decode streams them once)."""
+    from . import bf16_experts
+    hbm, _, tag = peaks()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    gate_up = (torch.randn(E, 2 * F, H, device="cuda", generator=g) * H ** -0.5).bfloat16()
+    down = (torch.randn(E, H, F, device="cuda", generator=g) * F ** -0.5).bfloat16()
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    idx = torch.stack([torch.randperm(E, device="cuda", generator=g)[:k] for _ in range(T)]).int()
+    w = torch.rand(T, k, device="cuda", generator=g)
+    hit = int(idx.unique().numel())
+    ms = time_op(lambda: bf16_experts(x, idx, w, gate_up, down, 0, "geglu"), iters)
+    gb = hit * 3 * F * H * 2 / 1e9
+    print(f"bf16 experts E={E} H={H} F={F} T={T} k={k}: {ms:.4f} ms, {hit} experts hit, {gb / ms * 1e3:.0f} GB/s of expert weights, "
+          f"{gb / ms * 1e3 / hbm:.2f} {tag}")
+
+
 def bench_floor(reps: int = 200):
     """Per-launch cost of decode-sized kernels in steady state: ``reps`` back-to-back launches recorded in one CUDA graph and
     replayed (what a decode step sees), against the same launches issued eagerly."""
@@ -245,6 +263,8 @@ if __name__ == "__main__":
     nums = [int(v) for v in sys.argv[2:]]
     if what == "membw":
         bench_membw(*nums)
+    if what == "bf16moe":
+        bench_bf16moe(*nums)
     if what in ("gemm", "all"):
         bench_gemm([tuple(nums)] if nums and what == "gemm" else None)
     if what in ("attn", "all"):
