@@ -58,9 +58,9 @@ struct GemmParams {
   // sk_units blocks per CTA, so every CTA streams the same number of weight bytes whatever the tile count; a tile whose
   // blocks fall to several CTAs is finished by whichever of them arrives last.
   int sk_units;
-  // grouped (mixture-of-experts) mode, swap only: the token operand is ONE matrix of padded rows cut into column tiles of BN rows,
-  // tile t belongs to expert g_tiles[4 t] (the routing plan's tile table; g_meta[0] = number of tiles in use) and multiplies
-  // that expert's slice of the 3-D weight operand.  Tiles past g_meta[0] are skipped by every role alike.
+  // grouped (mixture-of-experts) mode: the token operand is ONE matrix of padded rows cut into tiles (column tiles of BN rows with
+  // swap, 128-row tiles without), tile t belongs to expert g_tiles[4 t] (the routing plan's tile table; g_meta[0] = number of tiles
+  // in use) and multiplies that expert's slice of the 3-D weight operand.  Tiles past g_meta[0] are skipped by every role alike.
   const int* g_tiles;
   const int* g_meta;
   int g_experts;
@@ -97,8 +97,9 @@ struct WorkIter {
     }
     const int per_batch = p.tiles_r * p.tiles_c * p.split_k;
     if (p.g_tiles) {
+      // token tiles the plan does not use: column tiles with swap, row tiles without
       const int used = p.g_meta[0];
-      while (tt < per_batch && (tt % per_batch) % p.tiles_c >= used) tt += gridDim.x;      // column tiles the plan does not use
+      while (tt < per_batch && (p.swap ? tt % p.tiles_c : tt / (p.tiles_c * p.split_k)) >= used) tt += gridDim.x;
     }
     if (tt >= per_batch * p.batch) return false;
     const int t = tt % per_batch;
@@ -183,7 +184,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       while (iter.next(w)) {
         const int tr = w.tr, tc = w.tc;
         int zr = w.bz, zc = w.bz;
-        if (p.g_tiles) { zr = min(max(p.g_tiles[4 * tc], 0), p.g_experts - 1); zc = 0; }
+        if (p.g_tiles) {
+          const int e = min(max(p.g_tiles[4 * (p.swap ? tc : tr)], 0), p.g_experts - 1);
+          zr = p.swap ? e : 0;
+          zc = p.swap ? 0 : e;
+        }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
           uint8_t* st = smem + stage * C::STAGE_BYTES;
@@ -472,9 +477,16 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   p.g_meta = g_meta;
   p.g_experts = g_experts;
   if (g_tiles) {
-    if (!use_swap || batch != 1 || split_k != 1 || (g_nt != 32 && g_nt != 64 && g_nt != 128) || p.rows_c % g_nt) return MARY_ERR_BAD_ARG;
-    bn = g_nt;                                    // one column tile = one tile of the routing plan
-    p.tiles_c = p.rows_c / bn;
+    if (batch != 1 || split_k != 1) return MARY_ERR_BAD_ARG;
+    if (use_swap) {
+      if ((g_nt != 32 && g_nt != 64 && g_nt != 128) || p.rows_c % g_nt) return MARY_ERR_BAD_ARG;
+      bn = g_nt;                                  // one column tile = one tile of the routing plan
+      p.tiles_c = p.rows_c / bn;
+    } else {
+      if (g_nt != BM || p.rows_r % BM) return MARY_ERR_BAD_ARG;       // one 128-row tile = one tile of the routing plan
+      bn = p.rows_c >= 256 ? 256 : (p.rows_c > 64 ? 128 : 64);
+      p.tiles_c = (p.rows_c + bn - 1) / bn;
+    }
   }
   if (sk_epi) {
     const int64_t tiles = (int64_t)p.tiles_r * p.tiles_c * batch;
@@ -492,9 +504,9 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
     if (tiles > n_counters || slots * BM * bn > ws_floats) return MARY_ERR_BAD_ARG;     // workspace too small
   }
   CUtensorMap tr, tc;
-  int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, g_tiles ? g_experts : batch, bsr, BM);
+  int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, (g_tiles && use_swap) ? g_experts : batch, bsr, BM);
   if (rc) return rc;
-  rc = make_tmap_3d(&tc, Cc, p.rows_c, K, ldc, batch, bsc, bn);
+  rc = make_tmap_3d(&tc, Cc, p.rows_c, K, ldc, (g_tiles && !use_swap) ? g_experts : batch, bsc, bn);
   if (rc) return rc;
   if (glu) {
     switch (bn) {
@@ -521,12 +533,14 @@ MARY_API int mary_gemm_bf16(const void* X, const void* W, void* out, int M, int 
 // optionally with the GLU epilogue (W[e] = [gate; up], 2 N rows).  X holds the routing plan's padded rows (tiles of `nt` = 32, 64 or
 // 128 rows, one expert each); `tiles` / `meta` are the plan's tile table and {tiles in use, padded rows}; W is [E][N or 2 N][K] with
 // `bsw` elements between experts.  Tiles the plan does not use are skipped.
+// `swap` = 1: weights are the 128-row operand, token tiles of nt = 32 / 64 / 128 columns (decode; GLU allowed).  `swap` = 0: tokens are the
+// 128-row operand (nt must be 128), the expert's weights the column operand (prefill-sized batches; no GLU epilogue).
 MARY_API int mary_gemm_bf16_grouped(const void* X, const void* W, void* out, int rows_pad, int N, int K, int64_t ldx, int64_t ldw,
-                                    int64_t ldo, int E, int64_t bsw, const int* tiles, const int* meta, int nt, int glu,
+                                    int64_t ldo, int E, int64_t bsw, const int* tiles, const int* meta, int nt, int glu, int swap,
                                     cudaStream_t stream) {
-  if (!tiles || !meta || E < 1) return MARY_ERR_BAD_ARG;
-  return gemm_impl(X, W, out, rows_pad, N, K, ldx, ldw, ldo, 1, 0, bsw, 0, nullptr, 1.0f, glu, EPI_STORE_BF16, 1, 1, nullptr, 0, 0, 0, stream,
-                   nullptr, 0, nullptr, 0, false, tiles, meta, E, nt);
+  if (!tiles || !meta || E < 1 || (glu && !swap)) return MARY_ERR_BAD_ARG;
+  return gemm_impl(X, W, out, rows_pad, N, K, ldx, ldw, ldo, 1, 0, bsw, 0, nullptr, 1.0f, glu, EPI_STORE_BF16, 1, swap ? 1 : 0, nullptr, 0, 0, 0,
+                   stream, nullptr, 0, nullptr, 0, false, tiles, meta, E, nt);
 }
 
 // Split-K finished inside the kernel, without a zero-fill or a cast pass: out (bf16, or f32 when out_f32) = alpha * X W^T + bias

@@ -97,16 +97,17 @@ def experts_forward(x, idx, w, ex, shared=None, nt: int | None = None):
     return unpermute(y, plan, w, T, k, shared)
 
 
-declare("mary_gemm_bf16_grouped", "ppp" + "iii" + "lll" + "i" + "l" + "pp" + "ii" + "s")
+declare("mary_gemm_bf16_grouped", "ppp" + "iii" + "lll" + "i" + "l" + "pp" + "iii" + "s")
 
 
-def grouped_gemm_bf16(xg, w, plan: Plan, n_out: int, glu: str | None):
-    """``out[r] = act_glu(xg[r] @ w[expert of r's tile]^T)`` over the plan's padded rows; ``w [E, n_out or 2 n_out, K]`` unquantised."""
+def grouped_gemm_bf16(xg, w, plan: Plan, n_out: int, glu: str | None, swap: bool = True):
+    """``out[r] = act_glu(xg[r] @ w[expert of r's tile]^T)`` over the plan's padded rows; ``w [E, n_out or 2 n_out, K]`` unquantised.
+    ``swap=False`` (plans with 128-row tiles, no GLU): tokens as the 128-row tensor-core operand, for prefill-sized batches."""
     E, _, K = w.shape
     out = torch.empty(plan.max_rows, n_out, dtype=torch.bfloat16, device=xg.device)
     g = 0 if glu is None else {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
     check(lib().mary_gemm_bf16_grouped(_p(xg), _p(w), _p(out), plan.max_rows, n_out, K, xg.stride(0), w.stride(1), out.stride(0), E,
-                                       w.stride(0), _p(plan.tiles), _p(plan.meta), plan.nt, g, _stream()), "gemm_bf16_grouped")
+                                       w.stride(0), _p(plan.tiles), _p(plan.meta), plan.nt, g, int(swap), _stream()), "gemm_bf16_grouped")
     return out
 
 
@@ -121,6 +122,12 @@ def experts_forward_bf16(x, idx, w, gate_up, down, act: str = "geglu", e0: int =
     local = idx - e0 if e0 else idx
     plan = moe_plan(torch.where((local >= 0) & (local < E), local, torch.full_like(local, -1)).int(), E, nt)
     xg = x.index_select(0, plan.src_of.clamp_min(0).long())          # padding rows repeat token 0; nothing reads their results
-    h = grouped_gemm_bf16(xg, gate_up, plan, gate_up.shape[1] // 2, act)
-    y = grouped_gemm_bf16(h, down, plan, down.shape[1], None)
+    if nt == 128 and T * k >= 256 * E:
+        # prefill-sized: token-major tiles (tokens are the 128-row operand), GLU as its own kernel
+        from .cuda import glu
+        h = glu(grouped_gemm_bf16(xg, gate_up, plan, gate_up.shape[1], None, swap=False), act)
+        y = grouped_gemm_bf16(h, down, plan, down.shape[1], None, swap=False)
+    else:
+        h = grouped_gemm_bf16(xg, gate_up, plan, gate_up.shape[1] // 2, act)
+        y = grouped_gemm_bf16(h, down, plan, down.shape[1], None)
     return unpermute(y, plan, w, T, k)
