@@ -125,6 +125,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--replicated-head", action="store_true", help="keep the whole LM head on every rank (default: vocabulary-parallel head)")
     ap.add_argument("--no-ttft", action="store_true")
+    ap.add_argument("--ttft-layout", default="cp", choices=["cp", "each"],
+                    help="all-to-all layout only: cp = one context with its rows split over the ranks, each = every rank prefills its own context")
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill chunk of the TTFT measurement")
     ap.add_argument("--trace", action="store_true", help="print a per-op device-time table of one eager step and exit")
     ap.add_argument("--profile-step", action="store_true",
@@ -350,23 +352,56 @@ def main():
     say(f"end-to-end loop done, kernel status {status}")
 
     # ---------------------------------------------------------------- TTFT: a real prefill of one context
-    ttft = None
-    if not args.no_ttft:          # in the all-to-all layout every rank prefills one context of its own at the same time
+    ttft, ttft_note = None, "one context, all ranks"
+    if not args.no_ttft:
         try:
             pc = PagedKVCache(spec["num_layers"], (ctx + 64) // page + 2, page, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16,
                               device=dev, latent_dim=spec.get("latent_dim"))
-            pd = SpecDecoder(model, pc, 1, spec_k=k, max_len=ctx + 32, device=dev, use_graph=False)
             prompt = rng.integers(0, cfg.vocab_size, (1, ctx))
             ts = []
-            for _ in range(3):
-                barrier()
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record()
-                pd.prefill(prompt, chunk=args.prefill_chunk)
-                b.record()
-                barrier()
-                ts.append(a.elapsed_time(b))
-            ttft = sorted(ts)[1]
+            if a2a and args.ttft_layout == "cp":
+                # data-parallel attention + expert-parallel all-to-all: ONE context, its rows cut into contiguous chunks, one per rank
+                # (context parallelism: after every layer's cache append the earlier chunks' latent rows are gathered into the local
+                # cache, attention stays a local kernel); the time is that of the slowest rank, which holds the last chunk
+                from mary_b200.parallel.cp import ContextParallel
+                cp = ContextParallel(rank, world)
+                par.cp = cp
+                pc.alloc.extend(0, ctx)
+                table, _ = pc.alloc.page_table([0])
+                ids_all = torch.as_tensor(prompt[0], dtype=torch.int32, device=dev)
+                for _ in range(3):
+                    barrier()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    with torch.no_grad():
+                        meta = cp.begin(ctx, table, page, device=dev)
+                        lo, hi = cp.bounds[rank]
+                        tok, h = model.verify(ids_all[lo:hi], meta, pc)
+                        if k:                                   # the draft layer's cache rows of this chunk, as the plain prefill fills them
+                            nxt = torch.cat([ids_all[lo + 1:hi], ids_all[hi:hi + 1] if hi < ctx else tok[-1:].to(torch.int32)])
+                            model.draft(0, h, nxt, meta, pc)
+                    cp.end()
+                    b.record()
+                    barrier()
+                    ts.append(a.elapsed_time(b))
+                ttft_note = f"one context, rows split over {world} ranks (context-parallel prefill)"
+            else:          # tensor-parallel attention: all ranks work on the same rows; "each": every rank prefills a context of its own
+                pd = SpecDecoder(model, pc, 1, spec_k=k, max_len=ctx + 32, device=dev, use_graph=False)
+                for _ in range(3):
+                    barrier()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    pd.prefill(prompt, chunk=args.prefill_chunk)
+                    b.record()
+                    barrier()
+                    ts.append(a.elapsed_time(b))
+                if a2a:
+                    ttft_note = f"{world} contexts prefilled concurrently, one per rank"
+            t_loc = torch.tensor([sorted(ts)[1]], device=dev)
+            if world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(t_loc, op=dist.ReduceOp.MAX)
+            ttft = float(t_loc[0])
         except Exception as ex:
             ttft = f"failed: {type(ex).__name__}: {ex}"
 
@@ -389,7 +424,7 @@ def main():
                        "accepted_drafts_per_step": round(tok_per_seq_step - 1, 4)},
             "tpot_ms_p50": round(ms / args.steps / max(tok_per_seq_step, 1e-9), 4),
             "ttft_ms_p50_one_context": ttft,
-            "ttft_note": (f"{world} contexts prefilled concurrently, one per rank" if a2a else "one context, all ranks"),
+            "ttft_note": ttft_note,
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": B * R * 4,
                     "d2h_bytes_per_step": B * R * 4 * 2 + B * 4},

@@ -99,6 +99,9 @@ class MLAAttention(nn.Module):
         c = self.c
         qakv = ops.linear(x, self.w_qa_kva)
         qa = ops.mla_prep(qakv, c.q_lora_rank, self.qa_norm, self.kv_norm, self.inv_freq, meta, cache.k[self.li], 1e-6)
+        cp = getattr(self.par, "cp", None)
+        if cp is not None:
+            cp.share(cache.k[self.li], None)       # context-parallel prefill: the earlier chunks' latent rows become local
         qb = ops.linear(qa, self.w_qb)
         if meta.kv_lens_host is not None and meta.num_tokens >= self.PREFILL_MIN_ROWS * meta.num_seqs:
             return self._prefill_expanded(qb, meta, cache)

@@ -23,6 +23,7 @@ class ContextParallel:
         self.rank, self.world, self.group = rank, world, group
         self.bounds = None
         self.slots = None
+        self.active = False          # layers exchange K / V rows only between begin() and end()
 
     def begin(self, n_tokens: int, page_table: np.ndarray, page_size: int, device="cpu") -> BatchMeta:
         """Plan one prefill of ``n_tokens`` rows (sequence 0 of ``page_table``): returns the meta of THIS rank's rows."""
@@ -33,7 +34,11 @@ class ContextParallel:
         slots = page_table[0, pos // page_size].astype(np.int64) * page_size + pos % page_size
         self.slots = torch.from_numpy(slots).to(device)
         lo, hi = self.bounds[self.rank]
+        self.active = True
         return BatchMeta.build([hi - lo], [hi], page_table, page_size, device=device)
+
+    def end(self) -> None:
+        self.active = False
 
     def rows(self, x):
         """This rank's slice of a per-row tensor of the whole prompt."""
@@ -42,7 +47,7 @@ class ContextParallel:
 
     def share(self, kcache, vcache) -> None:
         """After this rank appended its rows of one layer: fetch the rows of all earlier chunks into the local cache."""
-        if self.world == 1:
+        if self.world == 1 or not self.active:
             return
         lo, hi = self.bounds[self.rank]
         for cache in ((kcache,) if vcache is kcache or vcache is None else (kcache, vcache)):
