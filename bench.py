@@ -125,6 +125,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--replicated-head", action="store_true", help="keep the whole LM head on every rank (default: vocabulary-parallel head)")
     ap.add_argument("--no-ttft", action="store_true")
+    ap.add_argument("--ttft-limit", type=float, default=150.0, help="seconds after which a stalled TTFT measurement is abandoned")
     ap.add_argument("--ttft-layout", default="cp", choices=["cp", "each"],
                     help="all-to-all layout only: cp = one context with its rows split over the ranks, each = every rank prefills its own context")
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill chunk of the TTFT measurement")
@@ -351,6 +352,47 @@ def main():
     status = K.last_status()
     say(f"end-to-end loop done, kernel status {status}")
 
+    def emit_line(ttft, ttft_note):
+        if rank == 0:
+            tok_per_seq_step = emitted / (B_global * args.steps)
+            line = {
+                "metric": "decode tok/s (max over ranks), K3-class MLA + NVFP4 MoE, 2-token MTP speculation" if args.model == "k3" else f"decode tok/s {cfg.name}",
+                "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": W,
+                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "bf16 activations, NVFP4 experts", "data": "synthetic token ids, random-init weights, synthetic KV context",
+                "impl": "ours",
+                "config": {"model": cfg.name + (" (REDUCED layers: debug)" if reduced else ""), "layers": cfg.num_hidden_layers,
+                           "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,
+                           "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
+                                           f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
+                           "kv_page_tokens": page, "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": dec.graph is not None,
+                           "lm_head": "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated",
+                           "expert_slabs_resident": slabs, "moe_layers": n_moe,
+                           "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",
+                           "accepted_drafts_per_step": round(tok_per_seq_step - 1, 4)},
+                "tpot_ms_p50": round(ms / args.steps / max(tok_per_seq_step, 1e-9), 4),
+                "ttft_ms_p50_one_context": ttft,
+                "ttft_note": ttft_note,
+                "clocks": clocks,
+                "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": B * R * 4,
+                        "d2h_bytes_per_step": B * R * 4 * 2 + B * 4},
+                "gpu_launches": launches_per_step * args.steps,
+                "kernel_status": status, "build_seconds": round(build_s, 1),
+            }
+            print(json.dumps(line))
+
+    # the decode result must not be lost to a stalled prefill: if the TTFT measurement has not finished in time, the line is printed
+    # without it and the process ends
+    done = threading.Event()
+
+    def give_up():
+        if not done.is_set():
+            emit_line(f"failed: no result within {args.ttft_limit} s", "abandoned")
+            sys.stdout.flush()
+            os._exit(0)
+    stall = threading.Timer(args.ttft_limit, give_up)
+    stall.daemon = True
+    stall.start()
     # ---------------------------------------------------------------- TTFT: a real prefill of one context
     ttft, ttft_note = None, "one context, all ranks"
     if not args.no_ttft:
@@ -405,33 +447,9 @@ def main():
         except Exception as ex:
             ttft = f"failed: {type(ex).__name__}: {ex}"
 
-    if rank == 0:
-        tok_per_seq_step = emitted / (B_global * args.steps)
-        line = {
-            "metric": "decode tok/s (max over ranks), K3-class MLA + NVFP4 MoE, 2-token MTP speculation" if args.model == "k3" else f"decode tok/s {cfg.name}",
-            "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": W,
-            "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16 activations, NVFP4 experts", "data": "synthetic token ids, random-init weights, synthetic KV context",
-            "impl": "ours",
-            "config": {"model": cfg.name + (" (REDUCED layers: debug)" if reduced else ""), "layers": cfg.num_hidden_layers,
-                       "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,
-                       "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
-                                       f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
-                       "kv_page_tokens": page, "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": dec.graph is not None,
-                       "lm_head": "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated",
-                       "expert_slabs_resident": slabs, "moe_layers": n_moe,
-                       "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",
-                       "accepted_drafts_per_step": round(tok_per_seq_step - 1, 4)},
-            "tpot_ms_p50": round(ms / args.steps / max(tok_per_seq_step, 1e-9), 4),
-            "ttft_ms_p50_one_context": ttft,
-            "ttft_note": ttft_note,
-            "clocks": clocks,
-            "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": B * R * 4,
-                    "d2h_bytes_per_step": B * R * 4 * 2 + B * 4},
-            "gpu_launches": launches_per_step * args.steps,
-            "kernel_status": status, "build_seconds": round(build_s, 1),
-        }
-        print(json.dumps(line))
+    done.set()
+    stall.cancel()
+    emit_line(ttft, ttft_note)
     faulthandler.cancel_dump_traceback_later()
     if world > 1:
         dist.destroy_process_group()
