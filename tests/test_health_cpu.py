@@ -36,9 +36,9 @@ def test_threads_as_ranks_detect_a_rank_that_raises_between_steps():
     world, seen = 3, {}
 
     def rank(r):
-        hb = Heartbeat(store, r, world, interval=0.02, timeout=0.25, grace=1.0).start()
+        hb = Heartbeat(store, r, world, interval=0.02, timeout=1.0, grace=5.0).start()
         try:
-            for step in range(200):
+            for step in range(600):
                 hb.guard()
                 if r == 1 and step == 3:
                     raise RuntimeError("injected host failure")            # dies without saying goodbye
@@ -51,8 +51,8 @@ def test_threads_as_ranks_detect_a_rank_that_raises_between_steps():
             hb.stop()
     ts = [threading.Thread(target=rank, args=(r,)) for r in range(world)]
     [t.start() for t in ts]
-    [t.join(10) for t in ts]
-    assert seen == {0: [1], 2: [1]}
+    [t.join(30) for t in ts]
+    assert set(seen) == {0, 2} and all(1 in v for v in seen.values()), seen
 
 
 def test_torch_store_backend_and_wire_header_checks():
