@@ -298,3 +298,52 @@ def init_random_(m: MimiCodec, seed: int = 0):
         else:
             fan_in = p[0].numel() if p.dim() > 1 else 1
             p.data.normal_(0.0, 1.0 / math.sqrt(max(fan_in, 1)), generator=g)
+
+
+def load_into(m: MimiCodec, loader) -> None:
+    """Names of the Hugging Face ``MimiModel`` layout (``kyutai/mimi``).  That layout stores q / k projections for a split-half
+    rotation; the rows are re-ordered into consecutive pairs, which is what this implementation (and the original codec) rotates."""
+    c = m.c
+    n = len(c.ratios)
+
+    def get(name):
+        return loader.load_tensor(name, torch.float32)
+
+    def conv(mod, name):
+        mod.weight.data.copy_(get(name + ".conv.weight").reshape(mod.weight.shape))
+        if mod.bias is not None:
+            mod.bias.data.copy_(get(name + ".conv.bias"))
+
+    def res(mod, name):
+        conv(mod.c1, name + ".block.1"), conv(mod.c2, name + ".block.3")
+    conv(m.enc_stem, "encoder.layers.0")
+    for i in range(n):
+        res(m.enc_res[i], f"encoder.layers.{1 + 3 * i}")
+        conv(m.enc_down[i], f"encoder.layers.{3 + 3 * i}")
+    conv(m.enc_last, f"encoder.layers.{3 * n + 2}")
+    conv(m.dec_stem, "decoder.layers.0")
+    for i in range(n):
+        conv(m.dec_up[i], f"decoder.layers.{2 + 3 * i}")
+        res(m.dec_res[i], f"decoder.layers.{3 + 3 * i}")
+    conv(m.dec_last, f"decoder.layers.{3 * n + 2}")
+    conv(m.downsample, "downsample")
+    conv(m.upsample, "upsample")
+    hd = c.hidden // c.tr_heads
+    pair = torch.stack([torch.arange(hd // 2), torch.arange(hd // 2) + hd // 2], -1).reshape(-1)       # split-half row -> pair order
+    perm = (torch.arange(c.tr_heads)[:, None] * hd + pair[None, :]).reshape(-1)
+    for tr, name in ((m.enc_tr, "encoder_transformer"), (m.dec_tr, "decoder_transformer")):
+        for i, L in enumerate(tr.layers):
+            p = f"{name}.layers.{i}."
+            q, k, v = (get(p + f"self_attn.{x}_proj.weight") for x in "qkv")
+            L.w_qkv.data.copy_(torch.cat([q[perm], k[perm], v], 0))
+            for ours, theirs in (("w_o", "self_attn.o_proj.weight"), ("w_fc1", "mlp.fc1.weight"), ("w_fc2", "mlp.fc2.weight"),
+                                 ("ln1_w", "input_layernorm.weight"), ("ln1_b", "input_layernorm.bias"),
+                                 ("ln2_w", "post_attention_layernorm.weight"), ("ln2_b", "post_attention_layernorm.bias"),
+                                 ("scale1", "self_attn_layer_scale.scale"), ("scale2", "mlp_layer_scale.scale")):
+                getattr(L, ours).data.copy_(get(p + theirs))
+    for rvq, name in ((m.rvq_first, "quantizer.semantic_residual_vector_quantizer"), (m.rvq_rest, "quantizer.acoustic_residual_vector_quantizer")):
+        rvq.input_proj.data.copy_(get(name + ".input_proj.weight")[:, :, 0])
+        rvq.output_proj.data.copy_(get(name + ".output_proj.weight")[:, :, 0])
+        for j, b in enumerate(rvq.books):
+            b.embedding_sum.data.copy_(get(f"{name}.layers.{j}.codebook.embed_sum"))
+            b.cluster_usage.data.copy_(get(f"{name}.layers.{j}.codebook.cluster_usage"))
