@@ -89,3 +89,48 @@ def test_sgd_overfit_probe_of_the_action_expert():
         first = first if first is not None else loss.item()
         last = loss.item()
     assert last < 0.2 * first, (first, last)
+
+
+def test_vision_tower_and_pixel_shuffle_connector_match_the_huggingface_smolvlm_backbone():
+    """The perception half of the policy is a SmolVLM backbone: same weights by name, image tokens compared (the order in which the
+    pixel shuffle folds neighbouring patches into channels is invisible to any shape check)."""
+    import pytest
+    transformers = pytest.importorskip("transformers")
+    from transformers.models.smolvlm import SmolVLMConfig, SmolVLMModel
+    c = SmolVLAConfig.tiny()
+    torch.manual_seed(0)
+    hc = SmolVLMConfig(
+        vision_config=dict(hidden_size=c.v_hidden, intermediate_size=c.v_ffn, num_hidden_layers=c.v_layers, num_attention_heads=c.v_heads,
+                           image_size=c.image_size, patch_size=c.patch, hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6),
+        text_config=dict(hidden_size=c.vlm.width, intermediate_size=c.vlm.ffn_dim, num_hidden_layers=1, num_attention_heads=c.vlm.n_heads,
+                         num_key_value_heads=c.vlm.n_kv_heads, head_dim=c.vlm.head_dim, vocab_size=c.vocab, pad_token_id=0),
+        scale_factor=c.shuffle, image_token_id=c.vocab - 1, pad_token_id=0)
+    hc._attn_implementation = "eager"
+    hc.vision_config._attn_implementation = "eager"
+    hf = SmolVLMModel(hc).eval()
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = SmolVLA(c)
+    init_random_(m, 0)
+    with torch.no_grad():
+        v = "vision_model."
+        m.patch_w.copy_(sd[v + "embeddings.patch_embedding.weight"]), m.patch_b.copy_(sd[v + "embeddings.patch_embedding.bias"])
+        m.v_pos.copy_(sd[v + "embeddings.position_embedding.weight"])
+        m.v_post_w.copy_(sd[v + "post_layernorm.weight"]), m.v_post_b.copy_(sd[v + "post_layernorm.bias"])
+        m.connector.copy_(sd["connector.modality_projection.proj.weight"])
+        for i, b in enumerate(m.v_blocks):
+            p = f"{v}encoder.layers.{i}."
+            b.w_qkv.copy_(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0))
+            b.b_qkv.copy_(torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"], 0))
+            b.w_o.copy_(sd[p + "self_attn.out_proj.weight"]), b.b_o.copy_(sd[p + "self_attn.out_proj.bias"])
+            b.ln1_w.copy_(sd[p + "layer_norm1.weight"]), b.ln1_b.copy_(sd[p + "layer_norm1.bias"])
+            b.ln2_w.copy_(sd[p + "layer_norm2.weight"]), b.ln2_b.copy_(sd[p + "layer_norm2.bias"])
+            b.w_fc1.copy_(sd[p + "mlp.fc1.weight"]), b.b_fc1.copy_(sd[p + "mlp.fc1.bias"])
+            b.w_fc2.copy_(sd[p + "mlp.fc2.weight"]), b.b_fc2.copy_(sd[p + "mlp.fc2.bias"])
+    img = torch.rand(3, c.image_size, c.image_size) * 2 - 1
+    with torch.no_grad():
+        out = hf.get_image_features(pixel_values=img[None, None])
+        want = out.pooler_output if hasattr(out, "pooler_output") else out
+        want = want.reshape(-1, c.vlm.width) * math.sqrt(c.vlm.width)
+        got = m.image_tokens(img)
+    assert got.shape == want.shape == ((c.image_size // c.patch // c.shuffle) ** 2, c.vlm.width)
+    assert torch.allclose(got, want, atol=2e-4), float((got - want).abs().max())
