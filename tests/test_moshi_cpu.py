@@ -76,3 +76,48 @@ def test_frame_loop_is_deterministic_and_respects_provided_tokens():
     assert frames[3][0] == 7                                                    # the forced text token of frame 4
     m.reset_session()
     assert m.step(user_audio=[0, 1]) is None
+
+
+def test_depformer_matches_the_huggingface_depth_decoder():
+    """Same weights: per-codebook (flexible) linears for the input projection, q / k / v / o, the gated MLP and the heads; no rotary;
+    step t is conditioned on the token of step t - 1 (the text token at t = 0)."""
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.moshi.configuration_moshi import MoshiDepthConfig
+    from transformers.models.moshi.modeling_moshi import MoshiDepthDecoder
+    c = MoshiConfig.tiny()
+    torch.manual_seed(0)
+    hc = MoshiDepthConfig(vocab_size=c.text_card, hidden_size=c.dep_dim, input_size=c.dim, num_hidden_layers=c.dep_layers,
+                          num_attention_heads=c.dep_heads, audio_vocab_size=c.card, ffn_dim=2 * c.dep_ffn, rms_norm_eps=c.eps,
+                          num_codebooks=c.dep_q, max_position_embeddings=c.dep_q + 1, sliding_window=c.dep_q)
+    hc._attn_implementation = "eager"
+    hf = MoshiDepthDecoder(hc).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            p.copy_(1.0 + 0.1 * torch.randn_like(p) if "layernorm" in n else 0.15 * torch.randn_like(p))
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    m = LmGen(c)
+    init_random_(m, 0)
+    d = m.depformer
+    with torch.no_grad():
+        d.w_in.copy_(sd["input_projections.weight"]), d.text_emb.copy_(sd["text_embed_tokens.weight"]), d.heads.copy_(sd["lm_heads.weight"])
+        for t in range(c.dep_q - 1):
+            d.audio_emb[t].copy_(sd[f"embed_tokens.{t}.weight"])
+        for li in range(c.dep_layers):
+            p = f"layers.{li}."
+            d.w_qkv[li].copy_(torch.cat([sd[p + f"self_attn.{x}_proj.linear.weight"] for x in "qkv"], 1))
+            d.w_o[li].copy_(sd[p + "self_attn.o_proj.linear.weight"])
+            d.w_gu[li].copy_(sd[p + "mlp.fc1.weight"]), d.w_down[li].copy_(sd[p + "mlp.fc2.weight"])
+            d.norm1[li].copy_(sd[p + "input_layernorm.weight"]), d.norm2[li].copy_(sd[p + "post_attention_layernorm.weight"])
+    B = 3
+    h = torch.randn(B, c.dim)
+    ids = torch.cat([torch.randint(0, c.text_card, (B, 1)), torch.randint(0, c.card, (B, c.dep_q - 1))], 1)
+    with torch.no_grad():
+        # the library builds its causal mask only when an attention mask is passed
+        want = hf(input_ids=ids, last_hidden_state=h[:, None, :], attention_mask=torch.ones(B, c.dep_q, dtype=torch.long)).logits
+        cache, got = None, []
+        for t in range(c.dep_q):
+            lg, cache = d.step(t, h, ids[:, t], cache)
+            got.append(lg)
+    got = torch.stack(got, 1)
+    assert torch.allclose(got, want, atol=2e-4), float((got - want).abs().max())
