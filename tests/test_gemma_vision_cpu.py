@@ -102,3 +102,57 @@ def test_lm_multimodal_completion_equals_token_completion_when_soft_tokens_are_t
     got = lm.complete_multimodal([2, 7, 99, 99, 9], [2, 3], emb0, 6, stop_on_eos=False)
     assert got == want
     assert lm.cache.alloc.free_pages == lm.cache.alloc.num_pages            # the private sequence was released
+
+
+def test_multimodal_prompt_end_to_end_matches_huggingface():
+    """Image patches -> vision tower -> soft tokens spliced into a prompt -> decoder with per-layer embeddings: logits of the whole
+    prompt against the library's multimodal model (placeholder rows look up the pad token for both embedding tables; the soft tokens
+    are not scaled by sqrt(hidden); the per-layer projection reads the merged embeddings)."""
+    pytest.importorskip("transformers")
+    from transformers.models.gemma4 import Gemma4Config, Gemma4ForConditionalGeneration
+    from mary_b200.models.gemma4.config import Gemma4TextConfig
+    from mary_b200.models.gemma4.model import Gemma4Model
+    from mary_b200.models.gemma4.weights import load_into as load_text
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    vc = Gemma4VisionConfig.tiny()
+    vc.text_hidden = 64
+    torch.manual_seed(0)
+    text = dict(vocab_size=120, hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
+                head_dim=32, global_head_dim=32, sliding_window=16, layer_types=["sliding_attention", "full_attention"],
+                hidden_size_per_layer_input=16, vocab_size_per_layer_input=120, final_logit_softcapping=30.0, pad_token_id=0,
+                rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                                 "full_attention": {"rope_type": "proportional", "partial_rotary_factor": 0.25, "rope_theta": 1e6}})
+    vision = dict(hidden_size=vc.hidden, intermediate_size=vc.ffn, num_hidden_layers=vc.layers, num_attention_heads=vc.heads,
+                  num_key_value_heads=vc.kv_heads, head_dim=vc.head_dim, patch_size=vc.patch, position_embedding_size=vc.pos_size,
+                  pooling_kernel_size=vc.pool, rope_parameters={"rope_type": "default", "rope_theta": vc.theta})
+    hc = Gemma4Config(text_config=text, vision_config=vision, audio_config=None, image_token_id=119)
+    for c in (hc, hc.text_config, hc.vision_config):
+        c._attn_implementation = "eager"
+    hf = Gemma4ForConditionalGeneration(hc).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if p.dim() == 1:
+                p.copy_(1.0 + 0.1 * torch.randn_like(p))
+            elif "vision_tower" in n or "embed_vision" in n:
+                p.copy_(0.2 * torch.randn_like(p))
+    sd = {k: v.detach() for k, v in hf.state_dict().items()}
+    loader = _DictLoader(sd)
+    loader.load_host_f32 = lambda n: sd[n].float().numpy()
+    cfg = Gemma4TextConfig.from_json(hc.text_config.to_dict())
+    m = Gemma4Model(cfg)
+    load_text(m, loader)
+    tower = Gemma4VisionTower(vc)
+    load_into(tower, loader)
+    image = torch.rand(3, 4 * vc.patch, 6 * vc.patch)
+    patches, pos = patchify(image, vc.patch)
+    ids = [2, 7, 8] + [119] * 6 + [9, 10]
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([ids]), pixel_values=patches[None], image_position_ids=pos[None]).logits[0]
+        soft = tower(patches, pos)
+        spec = m.kv_spec()
+        cache = PagedKVCache(spec["num_layers"], 2, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32)
+        cache.alloc.extend(0, len(ids))
+        table, lens = cache.alloc.page_table([0])
+        got = m(torch.tensor(ids, dtype=torch.int32), BatchMeta.build([len(ids)], lens, table, 16), cache, soft=(torch.arange(3, 9), soft))
+    assert torch.allclose(got, want, atol=3e-4, rtol=3e-4), float((got - want).abs().max())
