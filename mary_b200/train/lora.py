@@ -153,8 +153,8 @@ class Gemma4LoraForward(nn.Module):
     def _layer(self, i, h, pos, B, Sq):
         m, c = self.model, self.model.cfg
         L = m.layers[i]
-        if L.kv_source is not None:
-            raise NotImplementedError("LoRA training of decoders with KV-shared layers is not built")
+        if L.kv_source is not None or L.moe or L.ple:
+            raise NotImplementedError("LoRA training of decoders with KV-shared layers, a routed-expert block or per-layer embeddings is not built")
         ad = lambda p: self.lora.get(i, p)  # noqa: E731
         x = ref.rmsnorm(h, L.ln_in.detach(), c.rms_norm_eps)
         qkv = self._lin(x, L.w_qkv)
