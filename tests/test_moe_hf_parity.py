@@ -95,3 +95,53 @@ def test_logits_match_huggingface_deepseek_v3(monkeypatch, n_tokens):
         step = m(nxt.int(), BatchMeta.build([1], lens, table, 16), cache)[0]
         want1 = hf(torch.cat([ids, nxt])[None]).logits[0, -1]
     assert float((step - want1).abs().max() / want1.abs().max()) < 2e-4
+
+
+def test_gqa_softmax_moe_decoder_matches_huggingface_mixtral(monkeypatch):
+    """The Inkling-style workload's decoder shape (GQA attention, softmax router over all experts with renormalised top-k, SwiGLU
+    experts, no shared expert here) against the Hugging Face Mixtral implementation."""
+    pytest.importorskip("transformers")
+    from transformers import MixtralConfig, MixtralForCausalLM
+    monkeypatch.setattr(moe_model, "experts_forward", _dense_experts)
+    cfg = tiny_moe_config("gqa", hidden_size=256, num_attention_heads=4, num_key_value_heads=2, head_dim=64, n_shared_experts=0,
+                          first_k_dense=0, moe_intermediate_size=128, vocab_size=300, rope_theta=1e4)
+    m = MoEDecoder(cfg, dtype=torch.float32)
+    init_random_(m, 0, std=0.05)
+    g = torch.Generator().manual_seed(7)
+    with torch.no_grad():
+        for L in m.layers:
+            L.ffn.w_router.mul_(20.0)
+            for p in (L.ln_attn, L.ln_ffn):
+                p.copy_(1.0 + 0.1 * torch.randn(p.shape, generator=g))
+    hc = MixtralConfig(vocab_size=cfg.vocab_size, hidden_size=cfg.hidden_size, intermediate_size=cfg.moe_intermediate_size,
+                       num_hidden_layers=cfg.num_hidden_layers, num_attention_heads=cfg.num_attention_heads,
+                       num_key_value_heads=cfg.num_key_value_heads, head_dim=cfg.head_dim, num_local_experts=cfg.n_routed_experts,
+                       num_experts_per_tok=cfg.num_experts_per_tok, rms_norm_eps=cfg.rms_norm_eps, sliding_window=None,
+                       rope_parameters={"rope_type": "default", "rope_theta": cfg.rope_theta}, max_position_embeddings=512,
+                       tie_word_embeddings=False)
+    hc._attn_implementation = "eager"
+    hf = MixtralForCausalLM(hc).eval().float()
+    D, nq, nkv = cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads
+    sd = {"model.embed_tokens.weight": m.embed, "model.norm.weight": m.norm, "lm_head.weight": m.lm_head}
+    for i, L in enumerate(m.layers):
+        p, ex = f"model.layers.{i}.", L.ffn.experts
+        q, k, v = L.attn.w_qkv.split([nq * D, nkv * D, nkv * D], 0)
+        sd.update({p + "input_layernorm.weight": L.ln_attn, p + "post_attention_layernorm.weight": L.ln_ffn,
+                   p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k, p + "self_attn.v_proj.weight": v,
+                   p + "self_attn.o_proj.weight": L.attn.w_o, p + "mlp.gate.weight": L.ffn.w_router,
+                   p + "mlp.experts.gate_up_proj": torch.stack([ex.dense("w13", e) for e in range(ex.E)]),
+                   p + "mlp.experts.down_proj": torch.stack([ex.dense("w2", e) for e in range(ex.E)])})
+    missing, unexpected = hf.load_state_dict({k: v.detach().float() for k, v in sd.items()}, strict=False)
+    assert not unexpected and not [k for k in missing if "inv_freq" not in k], (missing, unexpected)
+    n = 33
+    ids = torch.randint(0, cfg.vocab_size, (n,), generator=g)
+    with torch.no_grad():
+        want = hf(ids[None]).logits[0]
+    spec = m.kv_spec()
+    cache = PagedKVCache(spec["num_layers"], 4, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32)
+    cache.alloc.extend(0, n)
+    table, lens = cache.alloc.page_table([0])
+    with torch.no_grad():
+        got = m(ids.int(), BatchMeta.build([n], lens, table, 16), cache)
+    row_err = (got - want).abs().amax(-1) / want.abs().max()
+    assert (row_err < 2e-4).float().mean() >= 0.95, row_err
