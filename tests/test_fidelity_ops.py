@@ -266,3 +266,23 @@ def test_inkling_paged_attention_matches_the_reference_operator():
             outs.append(att(x[done:done + n], BatchMeta.build([n], lens, table, 16), cache.k[0], cache.v[0]))
             done += n
         assert torch.allclose(torch.cat(outs), want, atol=2e-5), (is_global, float((torch.cat(outs) - want).abs().max()))
+
+
+def test_k3_gated_delta_rule_matches_the_flash_linear_attention_reference():
+    """The recurrence against ``fla``'s own naive KDA implementation (the package the reference gates its port against): same
+    per-dimension log-decay, same delta-rule update; L2 normalisation of q / k and the bounded gate are applied here first."""
+    naive = pytest.importorskip("fla.ops.kda.naive")
+    from mary_b200.models.k3 import ops as k3
+    torch.manual_seed(0)
+    T, dk, dv = 19, 8, 8
+    q, k, v = torch.randn(T, dk), torch.randn(T, dk), torch.randn(T, dv)
+    g, beta = torch.randn(T, dk), torch.rand(T)
+    A_log, dt_bias = torch.tensor(0.3), torch.randn(dk) * 0.2
+    S0 = torch.randn(dk, dv) * 0.1
+    o, S = k3.kda_recurrent(q, k, v, g, beta, A_log, dt_bias, S0)
+    a = -5.0 * torch.sigmoid(torch.exp(A_log) * (g + dt_bias))
+    qn, kn = torch.nn.functional.normalize(q, dim=-1), torch.nn.functional.normalize(k, dim=-1)
+    want_o, want_S = naive.naive_recurrent_kda(qn[None, :, None], kn[None, :, None], v[None, :, None], a[None, :, None], beta[None, :, None],
+                                               scale=1.0, initial_state=S0[None, None], output_final_state=True)
+    assert torch.allclose(o, want_o[0, :, 0], atol=1e-5) and torch.allclose(S.float(), want_S[0, 0], atol=1e-5)
+    assert (a <= 0).all() and (a >= -5).all()
