@@ -110,3 +110,17 @@ def test_guidance_sway_grid_and_sampling_pipeline():
     init_random_(voc, 2, 0.1)
     wav = voc(mel[5:].T.contiguous())
     assert wav.shape == (11 * 16,)
+
+
+def test_mel_front_end_matches_torchaudio():
+    """The reference mel of F5-TTS / Vocos is torchaudio's MelSpectrogram (magnitude, HTK scale, no normalisation) followed by
+    log(clamp(1e-5)); the matrix-product version must agree with it."""
+    import pytest
+    ta = pytest.importorskip("torchaudio")
+    torch.manual_seed(0)
+    wave = torch.randn(24000 // 2) * 0.2
+    want = ta.transforms.MelSpectrogram(sample_rate=24000, n_fft=1024, win_length=1024, hop_length=256, n_mels=100, power=1, center=True,
+                                        normalized=False, norm=None)(wave).clamp_min(1e-5).log()
+    got = mel_spectrogram(wave, n_mels=100, n_fft=1024, hop=256, sr=24000)
+    assert got.shape == want.shape
+    assert torch.allclose(got, want, atol=2e-3), float((got - want).abs().max())
