@@ -323,3 +323,48 @@ def test_legacy_leaves_migrate_to_typed_tensors_keeping_entity_ids(tmp_path, cap
     assert "converted=2" in capsys.readouterr().out
     assert mary.main(["equiv", "--pile", str(tmp_path / "old.pile"), "--other", str(tmp_path / "cli.pile")]) == 0
     assert mary.main(["equiv", "--pile", str(tmp_path / "cli.pile"), "--other", str(tmp_path / "old.pile")]) == 1
+
+
+def test_quantised_leaves_round_trip_and_derive_a_sibling_root(tmp_path):
+    import numpy as np
+    from mary_b200.format import schema as S
+    from mary_b200.format.leaf import LeafError
+    from mary_b200.format.model import build_model_root, index_keymap, put_tensor
+    from mary_b200.format.persist import publish_fragment, read_model_pile
+    from mary_b200.format.qleaf import MARKER, dequantize_leaf_q, derive_q_root, load_leaf_q, module_weight_q, put_leaf_q
+    from mary_b200.format.selection import model_roots
+    from mary_b200.nn.q4 import QLinear, dequantize_q4, quantize_q4
+    from mary_b200.pile import Pile, signing_key_file
+    from mary_b200.pile.trible import TribleBuilder, r_shortstring, v_shortstring
+    key = signing_key_file(str(tmp_path / "k"))
+    pile = Pile.open(str(tmp_path / "m.pile"))
+    rng = np.random.default_rng(0)
+    w, b = rng.standard_normal((6, 64)).astype(np.float32), rng.standard_normal((6,)).astype(np.float32)
+    tb = TribleBuilder()
+    root = build_model_root(pile, tb, [put_tensor(pile, tb, "l.weight", w), put_tensor(pile, tb, "l.bias", b)], name="m")
+    publish_fragment(pile, key, tb.build(), "f32")
+    facts = read_model_pile(pile)
+    for kind, tol in (("q4", 0.2), ("q8", 0.02)):
+        qroot = derive_q_root(pile, key, facts, root, kind)
+        f2 = read_model_pile(pile)
+        assert qroot != root and r_shortstring(f2.one(qroot, S.QUANTIZATION)) == kind and len(model_roots(f2)) >= 2
+        km = index_keymap(pile, f2, qroot)
+        k2, packed, dims = module_weight_q(pile, f2, km["l.weight"])
+        assert k2 == kind and dims == (6, 64) and module_weight_q(pile, f2, km["l.bias"]) is None       # vectors stay f32 leaves
+        if kind == "q4":
+            assert np.array_equal(packed, quantize_q4(w)) and np.array_equal(dequantize_q4(packed), dequantize_q4(quantize_q4(w)))
+        from mary_b200.pile.trible import r_genid
+        deq = dequantize_leaf_q(pile, f2, r_genid(f2.one(km["l.weight"], S.WEIGHT)))
+        assert np.abs(deq - w).max() < tol * np.abs(w).max()
+    # a marker this reader does not know is refused
+    tb = TribleBuilder()
+    e = put_leaf_q(pile, tb, w, "q4")
+    bad = TribleBuilder()
+    for ent, a, v in tb.build():
+        bad.add(ent, a, v_shortstring("q4_0.v9") if a == S.FORMAT_MARKER else v)
+    with pytest.raises(LeafError, match="format marker"):
+        load_leaf_q(pile, bad.build(), e)
+    with pytest.raises(LeafError):
+        put_leaf_q(pile, TribleBuilder(), rng.standard_normal((4, 40)).astype(np.float32))
+    assert MARKER["q8"] == "q8_0.v1"
+    pile.close()
