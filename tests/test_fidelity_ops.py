@@ -286,3 +286,39 @@ def test_k3_gated_delta_rule_matches_the_flash_linear_attention_reference():
                                                scale=1.0, initial_state=S0[None, None], output_final_state=True)
     assert torch.allclose(o, want_o[0, :, 0], atol=1e-5) and torch.allclose(S.float(), want_S[0, 0], atol=1e-5)
     assert (a <= 0).all() and (a >= -5).all()
+
+
+def test_inkling_paged_attention_batches_slots_independently():
+    """Three sequences of different length in one flattened batch (prefill together, then batched decode steps): every sequence equals
+    its own single-sequence run, i.e. neighbours in the batch do not contaminate each other's K / V convolution history or cache."""
+    from mary_b200.models.inkling import ops as ink
+    from mary_b200.models.inkling.paged import InklingPagedAttention
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    torch.manual_seed(1)
+    H, Hq, Hkv, D = 32, 4, 2, 8
+    cfg = dict(n_heads=Hq, n_kv_heads=Hkv, head_dim=D, d_rel=4, log_alpha=0.1, log_n_floor=4.0, window=6, eps=1e-6)
+    r = lambda *s: torch.randn(*s) * 0.3  # noqa: E731
+    p = dict(wq=r(Hq * D, H), wk=r(Hkv * D, H), wv=r(Hkv * D, H), wo=r(H, Hq * D), wr=r(Hq * 4, H), rel_proj=r(4, 8),
+             q_norm=torch.ones(D), k_norm=torch.ones(D), k_conv=r(Hkv * D, 4), v_conv=r(Hkv * D, 4))
+    lens, steps = [5, 9, 3], 4
+    xs = [torch.randn(n + steps, H) for n in lens]
+    want = [ink.attention(x, p, cfg, is_global=False) for x in xs]
+    cache = PagedKVCache(1, 8, 16, Hkv, D, dtype=torch.float32)
+    att = InklingPagedAttention(p, cfg, is_global=False)
+    for s, n in enumerate(lens):
+        cache.alloc.extend(s, n)
+    table, kv = cache.alloc.page_table([0, 1, 2])
+    out = att(torch.cat([x[:n] for x, n in zip(xs, lens)]), BatchMeta.build(lens, kv, table, 16), cache.k[0], cache.v[0])
+    got = [[o] for o in out.split(lens)]
+    for t in range(steps):
+        for s in range(3):
+            cache.alloc.extend(s, 1)
+        table, kv = cache.alloc.page_table([0, 1, 2])
+        o = att(torch.stack([x[n + t] for x, n in zip(xs, lens)]), BatchMeta.build([1, 1, 1], kv, table, 16), cache.k[0], cache.v[0])
+        for s in range(3):
+            got[s].append(o[s:s + 1])
+    for s in range(3):
+        assert torch.allclose(torch.cat(got[s]), want[s], atol=2e-5), s
+    att.reset(1)
+    assert set(att.hist) == {0, 2}
