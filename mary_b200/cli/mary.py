@@ -132,6 +132,20 @@ def cmd_equiv(a) -> int:
     return 0
 
 
+def cmd_k3_gate(a) -> int:
+    """The K3 layout gate (tests/k3_layout_gate.rs): the two halves of the name <-> slot mapping against a checkpoint's own headers."""
+    from ..models.k3.ckpt import K3Checkpoint
+    ck = K3Checkpoint(a.dir)
+    g = ck.gate()
+    ck.close()
+    bad = sum(len(v) for v in g.values())
+    print(f"{len(ck)} tensors in {len(ck.shards())} shards; " + ", ".join(f"{k} {len(v)}" for k, v in g.items()))
+    for k, v in g.items():
+        for item in v[:a.show]:
+            print(f"  {k}: {item}")
+    return 1 if bad else 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mary")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -164,6 +178,9 @@ def main(argv=None) -> int:
     eq = sub.add_parser("equiv")
     eq.add_argument("--pile", required=True), eq.add_argument("--other", required=True)
     eq.set_defaults(fn=cmd_equiv)
+    kg = sub.add_parser("k3-gate")
+    kg.add_argument("dir"), kg.add_argument("--show", type=int, default=10)
+    kg.set_defaults(fn=cmd_k3_gate)
     a = ap.parse_args(argv)
     return a.fn(a)
 

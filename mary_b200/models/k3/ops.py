@@ -168,7 +168,8 @@ def kda_attention(x, p: dict, cfg: K3Config, cache: dict | None = None):
     if cache is not None:
         cache["state"] = states
     o = _bf(torch.stack(outs, 1), x)                                    # [T, nh, dk]
-    gate = torch.sigmoid(F.linear(F.linear(x, p["g_a_proj"]), p["g_b_proj"]).float()).view(T, nh, dk)
+    glin = F.linear(x, p["g_proj"]) if "g_proj" in p else F.linear(F.linear(x, p["g_a_proj"]), p["g_b_proj"])   # full-rank gate in K3
+    gate = torch.sigmoid(glin.float()).view(T, nh, dk)
     of = o.float()
     normed = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + 1e-5) * p["o_norm"].float()
     return F.linear(_bf(normed * gate, x).reshape(T, nh * dk), p["o_proj"])
