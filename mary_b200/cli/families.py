@@ -2,7 +2,7 @@
 
     families say       --pile P --model f5 --vocoder vocos --ref-wav r.wav --ref-text "..." --text "..." --out o.wav   (``say`` / ``say_serve``)
     families listen    --pile P --model voxtral --wav a.wav [--delay 6]                                                  (``voxtral_listen``)
-    families embed     --pile P --model clip|siglip|nomic --kind clip|siglip|nomic [--image i.npy] [--ids 1,2,3]         (``local_demo``, ``embed_persist``)
+    families embed     --pile P --model clip|siglip|nomic --kind clip|siglip|nomic|nomic-vision [--image i.npy] [--ids 1,2,3]         (``local_demo``, ``embed_persist``)
     families imagine   --pile P --transformer T --vae V --features f.npy --out img.npy [--steps 4] [--seed 0]            (the FLUX.2 pipeline)
     families act       --pile P --model smolvla --image i.npy --ids 1,2,3 --state s.npy                                  (``smolvla_infer``)
     families hear      --pile P --model gemma-audio --wav a.wav [--ids 2,.. --ids-after ..]                              (``gemma_hear`` / ``gemma_listen``)
@@ -107,7 +107,8 @@ def cmd_listen(a) -> int:
 def cmd_embed(a) -> int:
     from ..models import embed as E
     kinds = {"clip": (E.ClipConfig, E.ClipEmbedder, E.clip.load_into), "siglip": (E.SiglipConfig, E.SiglipEmbedder, E.siglip.load_into),
-             "nomic": (E.NomicConfig, E.NomicTextEmbedder, E.nomic.load_into)}
+             "nomic": (E.NomicConfig, E.NomicTextEmbedder, E.nomic.load_into),
+             "nomic-vision": (E.NomicVisionConfig, E.NomicVisionEmbedder, E.nomic.load_vision_into)}
     Cfg, Model, load = kinds[a.kind]
     m = Model(Cfg.tiny() if a.random else Cfg())
     _random_init(m) if a.random else load(m, _loader(a.pile, a.model))
@@ -281,7 +282,7 @@ def main(argv=None) -> int:
     li.add_argument("--wav", required=True), li.add_argument("--delay", type=int), li.add_argument("--chunk", type=int, default=4)
     li.set_defaults(fn=cmd_listen)
     e = common(sub.add_parser("embed"))
-    e.add_argument("--kind", required=True, choices=["clip", "siglip", "nomic"]), e.add_argument("--image"), e.add_argument("--ids")
+    e.add_argument("--kind", required=True, choices=["clip", "siglip", "nomic", "nomic-vision"]), e.add_argument("--image"), e.add_argument("--ids")
     e.set_defaults(fn=cmd_embed)
     im = common(sub.add_parser("imagine"))
     im.add_argument("--transformer"), im.add_argument("--vae"), im.add_argument("--features", required=True), im.add_argument("--out", required=True)

@@ -23,7 +23,8 @@ def test_say_listen_embed_imagine_act_on_random_tiny_models(tmp_path, capsys):
     assert len(toks) == (sr // 2 // 160) // 8 // 2 * 2 or len(toks) >= 4
 
     np.save(tmp_path / "img.npy", np.random.default_rng(0).random((3, 40, 48), dtype=np.float32))
-    for kind, extra in (("clip", ["--image", str(tmp_path / "img.npy")]), ("siglip", ["--ids", "1,2,3"]), ("nomic", ["--ids", "4,5,6,7"])):
+    for kind, extra in (("clip", ["--image", str(tmp_path / "img.npy")]), ("siglip", ["--ids", "1,2,3"]), ("nomic", ["--ids", "4,5,6,7"]),
+                        ("nomic-vision", ["--image", str(tmp_path / "img.npy")])):
         assert families.main(["embed", "--random", "--kind", kind] + extra) == 0
         v = np.array(capsys.readouterr().out.split(), dtype=np.float64)
         assert abs(np.linalg.norm(v) - 1.0) < 1e-4

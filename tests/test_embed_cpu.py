@@ -113,3 +113,103 @@ def test_nomic_text_embedder_matches_huggingface_and_ignores_padding():
         short = m.embed_text(ids, mask, dim=16)
     assert torch.allclose(e[1], alone[0], atol=1e-5)
     assert short.shape == (2, 16) and torch.allclose(short.norm(dim=-1), torch.ones(2), atol=1e-5)
+
+
+def _nomic_vision_plain(sd, c, pixels):
+    """The nomic vision tower restated with torch.nn modules, complex-number rotation and explicit softmax: written from the
+    architecture description, sharing no code with the embedder under test."""
+    import math
+    import torch.nn.functional as F
+    H, nh, g = c.hidden, c.heads, c.grid
+    hd = H // nh
+    B = pixels.shape[0]
+    # patches as a LINEAR map over (c, p1, p2)-ordered flattened patches
+    pt = pixels.unfold(2, c.patch, c.patch).unfold(3, c.patch, c.patch)                 # [B, 3, g, g, p, p]
+    pt = pt.permute(0, 2, 3, 1, 4, 5).reshape(B, g * g, 3 * c.patch * c.patch)
+    x = pt @ sd["embeddings.proj.weight"].T + sd["embeddings.proj.bias"]
+    x = torch.cat([sd["embeddings.cls_token"].expand(B, 1, H), x], 1) + sd["embeddings.pos_embed"]
+    nb = hd // 4
+    bands = torch.tensor([1.0 / 10000.0 ** (i / nb) for i in range(nb)], dtype=torch.float64)
+    ang = torch.zeros(g * g, hd // 2, dtype=torch.float64)
+    for r in range(g):
+        for col in range(g):
+            ang[r * g + col] = torch.cat([r * bands, col * bands])
+    phase = torch.polar(torch.ones_like(ang), ang).to(torch.complex64)                 # one unit complex number per channel pair
+
+    def rope(t):                                                                     # t [B, nh, T, hd]; class token untouched
+        patches = torch.view_as_complex(t[:, :, 1:].reshape(B, nh, g * g, hd // 2, 2).contiguous()) * phase
+        return torch.cat([t[:, :, :1], torch.view_as_real(patches).reshape(B, nh, g * g, hd)], 2)
+
+    def lin(t, n):
+        return t @ sd[n + ".weight"].T + sd[n + ".bias"]
+
+    def lnorm(t, n, eps):
+        return F.layer_norm(t, (t.shape[-1],), sd[n + ".weight"], sd[n + ".bias"], eps)
+    res = None
+    T = x.shape[1]
+    for i in range(c.layers):
+        p = f"layers.{i}."
+        res = x if res is None else x + res
+        qkv = lin(lnorm(res, p + "norm1", 1e-6), p + "attn.Wqkv")
+        q, k, v = (qkv[..., j * H:(j + 1) * H].reshape(B, T, nh, hd).transpose(1, 2) for j in range(3))
+        w = torch.softmax(rope(q) @ rope(k).transpose(-1, -2) / math.sqrt(hd), -1)
+        res = lin((w @ v).transpose(1, 2).reshape(B, T, H), p + "attn.out_proj") + res
+        h = lnorm(res, p + "norm2", 1e-6)
+        x = lin(lnorm(lin(h, p + "mlp.fc11") * F.silu(lin(h, p + "mlp.fc12")), p + "mlp.norm", 1e-5), p + "mlp.fc2")
+    hid = x + res
+    q = lin(sd["selector.attn.latent"].expand(B, 1, H), "selector.attn.Wq").reshape(B, 1, nh, hd).transpose(1, 2)
+    kv = lin(hid, "selector.attn.Wkv")
+    k, v = (kv[..., j * H:(j + 1) * H].reshape(B, T, nh, hd).transpose(1, 2) for j in range(2))
+    a = lin((torch.softmax(q @ k.transpose(-1, -2) / math.sqrt(hd), -1) @ v).transpose(1, 2).reshape(B, H), "selector.attn.out_proj")
+    n = lnorm(a, "selector.norm1", 1e-6)
+    return a + lin(lin(n, "selector.mlp.fc11") * F.silu(lin(n, "selector.mlp.fc12")), "selector.mlp.fc2"), hid
+
+
+def test_nomic_vision_embedder_against_a_plain_restatement_and_inventory():
+    from mary_b200.models.embed import NomicVisionConfig, NomicVisionEmbedder
+    from mary_b200.models.embed import nomic
+    full = nomic.vision_tensor_shapes()
+    assert len(full) == 2 + 2 + 12 * 16 + 1 + 6 + 2 + 6 and full["embeddings.pos_embed"] == (1, 197, 768)
+    assert full["layers.11.mlp.norm.weight"] == (2048,) and "selector.mlp.norm.weight" not in full
+    c = NomicVisionConfig.tiny()
+    torch.manual_seed(3)
+    sd = {n: torch.randn(s) * (0.3 if len(s) > 1 else 0.1) for n, s in nomic.vision_tensor_shapes(c).items()}
+    for n in sd:
+        if n.endswith("norm1.weight") or n.endswith("norm2.weight") or n.endswith("norm.weight"):
+            sd[n] = 1 + sd[n]
+    m = NomicVisionEmbedder(c)
+    nomic.load_vision_into(m, _DictLoader(sd))
+    pixels = torch.randn(2, 3, c.image_size, c.image_size)
+    with torch.no_grad():
+        want_pool, want_hid = _nomic_vision_plain(sd, c, pixels)
+        got_hid = m.tokens(pixels)
+        got = m.embed_image(pixels)
+    assert torch.allclose(got_hid, want_hid, atol=2e-4, rtol=1e-4), (got_hid - want_hid).abs().max()
+    want = torch.nn.functional.normalize(want_pool, dim=-1)
+    assert torch.allclose(got, want, atol=1e-5), (got - want).abs().max()
+    assert torch.allclose(got.norm(dim=-1), torch.ones(2), atol=1e-6)
+    # class-token pooling is NOT the embedding
+    assert not torch.allclose(torch.nn.functional.normalize(got_hid[:, 0], dim=-1), got, atol=1e-2)
+    with pytest.raises(ValueError, match="image-only"):
+        m.embed_text([[1, 2]])
+    bad = dict(sd)
+    bad["layers.0.mlp.norm.weight"] = torch.ones(c.ffn + 1)
+    with pytest.raises(ValueError, match="architecture fixes"):
+        nomic.load_vision_into(NomicVisionEmbedder(c), _DictLoader(bad))
+
+
+def test_axial_rope_is_relative_in_both_axes_and_leaves_the_class_token():
+    from mary_b200.models.embed.nomic import axial_rope_tables, rotate_pairs
+    g, hd = 5, 16
+    cos, sin = axial_rope_tables(g, hd)
+    assert cos.shape == (g * g, hd) and torch.equal(cos[:, 0::2], cos[:, 1::2])
+    assert torch.allclose(cos[0], torch.ones(hd)) and torch.allclose(sin[0], torch.zeros(hd))
+    torch.manual_seed(0)
+    q, k = torch.randn(hd), torch.randn(hd)
+
+    def score(a, b):                     # token indices
+        return (rotate_pairs(q, cos[a], sin[a]) * rotate_pairs(k, cos[b], sin[b])).sum()
+    # the same (row, column) offset gives the same score wherever the pair sits
+    assert torch.allclose(score(0 * g + 1, 2 * g + 3), score(1 * g + 2, 3 * g + 4), atol=1e-5)
+    assert torch.allclose(score(2 * g + 0, 2 * g + 2), score(4 * g + 1, 4 * g + 3), atol=1e-5)
+    assert not torch.allclose(score(0, 1), score(0, g), atol=1e-3)          # a column step is not a row step
