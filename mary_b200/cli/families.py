@@ -7,7 +7,7 @@
     families act       --pile P --model smolvla --image i.npy --ids 1,2,3 --state s.npy                                  (``smolvla_infer``)
     families hear      --pile P --model gemma-audio --wav a.wav [--ids 2,.. --ids-after ..]                              (``gemma_hear`` / ``gemma_listen``)
     families speak     --random --ids 5,6,7 --out o.wav                                                                  (``speak`` / ``qwen3tts_say|stream``)
-    families converse  --random --wav in.wav --out agent.wav                                                             (``personaplex_listen``)
+    families converse  --pile P --model moshi --codec mimi --wav in.wav --out agent.wav                                                       (``personaplex_listen``)
 
 Checkpoints get into a pile with ``mary import`` (the reference's ``*_persist`` importers); ``--random`` instead builds the tiny
 configuration with random weights, which is what the tests drive.  Audio is read and written as 16-bit mono WAV with the standard
@@ -236,13 +236,20 @@ def cmd_converse(a) -> int:
     from ..models.codec.mimi import init_random_ as init_codec
     from ..models.moshi import LmGen, MoshiConfig
     from ..models.moshi import init_random_ as init_lm
-    if not a.random:
-        raise SystemExit("converse: only --random is wired up; the speech LM's checkpoint layout has no loader in this package yet")
-    c = MoshiConfig.tiny()
-    mc = MimiConfig.tiny()
-    mc.num_codebooks, mc.codebook_size = c.codebooks_per_stream, c.card
-    codec, lm = MimiCodec(mc), LmGen(c)
-    init_codec(codec, a.seed), init_lm(lm, a.seed)
+    from ..models.codec import mimi
+    from ..models import moshi
+    if a.random:
+        c = MoshiConfig.tiny()
+        mc = MimiConfig.tiny()
+        mc.num_codebooks, mc.codebook_size = c.codebooks_per_stream, c.card
+        codec, lm = MimiCodec(mc), LmGen(c)
+        init_codec(codec, a.seed), init_lm(lm, a.seed)
+    else:
+        c, mc = MoshiConfig(), MimiConfig()
+        codec, lm = MimiCodec(mc), LmGen(c, dtype=torch.bfloat16 if torch.cuda.is_available() else torch.float32,
+                                         device="cuda" if torch.cuda.is_available() else "cpu")
+        mimi.load_into(codec, _loader(a.pile, a.codec))
+        moshi.load_into(lm, _loader(a.pile, a.model))
     wav, sr = read_wav(a.wav)
     spf = mc.samples_per_frame
     n = len(wav) // spf
@@ -300,7 +307,7 @@ def main(argv=None) -> int:
     sp.add_argument("--prefill", type=int, default=6)
     sp.set_defaults(fn=cmd_speak)
     cv = common(sub.add_parser("converse"))
-    cv.add_argument("--wav", required=True), cv.add_argument("--out", required=True)
+    cv.add_argument("--wav", required=True), cv.add_argument("--out", required=True), cv.add_argument("--codec", default="mimi")
     cv.set_defaults(fn=cmd_converse)
     a = ap.parse_args(argv)
     return a.fn(a)

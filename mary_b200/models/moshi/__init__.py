@@ -1,1 +1,1 @@
-from .model import Depformer, LmGen, MoshiConfig, StreamCache, init_random_  # noqa: F401
+from .model import Depformer, LmGen, MoshiConfig, StreamCache, init_random_, load_into  # noqa: F401

@@ -259,3 +259,50 @@ def init_random_(m: LmGen, seed: int = 0, std: float = 0.08):
             p.data.fill_(1.0)
         else:
             p.data.normal_(0.0, std, generator=g)
+
+
+def load_into(m: LmGen, loader, prefix: str = "") -> None:
+    """Fill the whole speech LM from the Hugging Face Moshi layout: ``decoder.model.*`` (temporal transformer: ``self_attn.{q,k,v,o}
+    _proj.linear.weight``, the gated MLP's ``fc1`` = [gate; up] and ``fc2``, two RMSNorm gains per layer, the final norm),
+    ``decoder.model.embed_tokens`` (text, one padding row past the vocabulary), ``decoder.lm_head`` (text logits), top-level
+    ``embed_tokens.<s>`` (audio streams: the agent's codebooks first, then the user's) and ``depth_decoder.*`` (per-codebook
+    "flexible" linears stored as one ``[codebooks, out, in]`` tensor each).  That layout's rotary embedding is already split-half,
+    so the q / k rows are copied as they are."""
+    c = m.c
+    dt = m.text_emb.dtype
+
+    def get(n):
+        return loader.load_tensor(prefix + n, dt)
+
+    def put(p, t):
+        if tuple(p.shape) != tuple(t.shape):
+            raise ValueError(f"shape {tuple(t.shape)} does not fit {tuple(p.shape)}")
+        p.data.copy_(t.to(p.device, dt))
+    put(m.text_emb, get("decoder.model.embed_tokens.weight"))
+    put(m.text_head, get("decoder.lm_head.weight"))
+    for s in range(c.dep_q):
+        put(m.audio_emb[s], get(f"embed_tokens.{s}.weight"))
+    t = m.temporal
+    put(t.norm, get("decoder.model.norm.weight"))
+    for i, L in enumerate(t.layers):
+        p = f"decoder.model.layers.{i}."
+        put(L.w_qkv, torch.cat([get(p + f"self_attn.{x}_proj.linear.weight") for x in "qkv"], 0))
+        put(L.w_o, get(p + "self_attn.o_proj.linear.weight"))
+        put(L.w_gu, get(p + "mlp.fc1.weight"))
+        put(L.w_down, get(p + "mlp.fc2.weight"))
+        put(L.ln_attn, get(p + "input_layernorm.weight"))
+        put(L.ln_ffn, get(p + "post_attention_layernorm.weight"))
+    d = m.depformer
+    put(d.w_in, get("depth_decoder.input_projections.weight"))
+    put(d.text_emb, get("depth_decoder.text_embed_tokens.weight"))
+    put(d.heads, get("depth_decoder.lm_heads.weight"))
+    for s in range(c.dep_q - 1):
+        put(d.audio_emb[s], get(f"depth_decoder.embed_tokens.{s}.weight"))
+    for li in range(c.dep_layers):
+        p = f"depth_decoder.layers.{li}."
+        put(d.w_qkv[li], torch.cat([get(p + f"self_attn.{x}_proj.linear.weight") for x in "qkv"], 1))
+        put(d.w_o[li], get(p + "self_attn.o_proj.linear.weight"))
+        put(d.w_gu[li], get(p + "mlp.fc1.weight"))
+        put(d.w_down[li], get(p + "mlp.fc2.weight"))
+        put(d.norm1[li], get(p + "input_layernorm.weight"))
+        put(d.norm2[li], get(p + "post_attention_layernorm.weight"))

@@ -121,3 +121,68 @@ def test_depformer_matches_the_huggingface_depth_decoder():
             got.append(lg)
     got = torch.stack(got, 1)
     assert torch.allclose(got, want, atol=2e-4), float((got - want).abs().max())
+
+
+def test_whole_speech_lm_loaded_by_name_matches_huggingface_moshi():
+    """Temporal transformer + text head + depth decoder filled by ``load_into`` from the library's state-dict names; the frame
+    embedding is the sum of the text and the sixteen audio stream embeddings, as the library's conditional-generation model forms it."""
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.moshi.configuration_moshi import MoshiConfig as HFConfig, MoshiDepthConfig
+    from transformers.models.moshi.modeling_moshi import MoshiDepthDecoder, MoshiForCausalLM
+    from mary_b200.models.moshi import load_into
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200 import ops
+    c = MoshiConfig.tiny()
+    torch.manual_seed(1)
+    depth = dict(vocab_size=c.text_card, hidden_size=c.dep_dim, input_size=c.dim, num_hidden_layers=c.dep_layers,
+                 num_attention_heads=c.dep_heads, audio_vocab_size=c.card, ffn_dim=2 * c.dep_ffn, rms_norm_eps=c.eps,
+                 num_codebooks=c.dep_q, max_position_embeddings=c.dep_q + 1, sliding_window=c.dep_q)
+    hc = HFConfig(vocab_size=c.text_card, hidden_size=c.dim, num_hidden_layers=c.layers, num_attention_heads=c.heads,
+                  num_key_value_heads=c.heads, audio_vocab_size=c.card, max_position_embeddings=c.context, rope_theta=c.rope_theta,
+                  head_dim=c.dim // c.heads, ffn_dim=2 * c.ffn, rms_norm_eps=c.eps, num_codebooks=c.dep_q // 2, sliding_window=c.context,
+                  depth_decoder_config=dict(depth))
+    hc._attn_implementation = "eager"
+    lm = MoshiForCausalLM(hc).eval()
+    dc = MoshiDepthConfig(**depth)
+    dc._attn_implementation = "eager"
+    dd = MoshiDepthDecoder(dc).eval()
+    with torch.no_grad():
+        for mod in (lm, dd):
+            for n, p in mod.named_parameters():
+                p.copy_(1.0 + 0.1 * torch.randn_like(p) if "norm" in n else 0.15 * torch.randn_like(p))
+    audio_tables = [0.15 * torch.randn(c.card + 1, c.dim) for _ in range(c.dep_q)]
+    sd = {"decoder." + k: v.detach() for k, v in lm.state_dict().items()}
+    sd.update({"depth_decoder." + k: v.detach() for k, v in dd.state_dict().items()})
+    sd.update({f"embed_tokens.{s}.weight": t for s, t in enumerate(audio_tables)})
+
+    class L:
+        def load_tensor(self, n, dtype):
+            return sd[n].to(dtype)
+    m = LmGen(c)
+    init_random_(m, 5)
+    load_into(m, L())
+    T = 7
+    text = torch.randint(0, c.text_card, (T,))
+    audio = torch.randint(0, c.card, (T, c.dep_q))
+    with torch.no_grad():
+        emb = lm.model.embed_tokens(text) + sum(audio_tables[s][audio[:, s]] for s in range(c.dep_q))
+        out = lm(inputs_embeds=emb[None], attention_mask=torch.ones(1, T, dtype=torch.long))
+        want_logits, want_h = out.logits[0], out.last_hidden_state[0]
+        x = torch.cat([m.embed_frame([int(text[t])] + [int(a) for a in audio[t]]) for t in range(T)])
+        assert torch.allclose(x, emb, atol=1e-6)
+        meta = BatchMeta.build([T], [T], m.table, 16, m.dev)
+        h = m.temporal.hidden_from_embeds(x, meta, m.cache)
+        got_logits = ops.linear(h, m.text_head).float()
+    assert torch.allclose(h, want_h, atol=3e-4, rtol=1e-3), float((h - want_h).abs().max())
+    assert torch.allclose(got_logits, want_logits, atol=3e-4, rtol=1e-3), float((got_logits - want_logits).abs().max())
+    # the depth decoder, conditioned on the temporal state the two models agree on
+    ids = torch.cat([torch.randint(0, c.text_card, (T, 1)), torch.randint(0, c.card, (T, c.dep_q - 1))], 1)
+    with torch.no_grad():
+        want = dd(input_ids=ids, last_hidden_state=want_h[:, None, :], attention_mask=torch.ones(T, c.dep_q, dtype=torch.long)).logits
+        cache, got = None, []
+        for t in range(c.dep_q):
+            lg, cache = m.depformer.step(t, h, ids[:, t], cache)
+            got.append(lg)
+    got = torch.stack(got, 1)
+    assert torch.allclose(got, want, atol=5e-4, rtol=1e-3), float((got - want).abs().max())
