@@ -116,10 +116,11 @@ class Ecapa(nn.Module):
         self.fc = TDNN(2 * n, c.out_dim, 1)
 
     def pool(self, x):
-        """Attentive statistics: attention logits from ``[x, mean, std]`` (tanh bottleneck), softmax over time, weighted mean and std."""
+        """Attentive statistics: attention logits from ``[x, mean, std]`` through a ReLU time-delay layer, then tanh, then a plain
+        convolution (speaker.rs:186); softmax over time; weighted mean and std."""
         T = x.shape[1]
         mean, std = x.mean(1, keepdim=True), x.var(1, unbiased=False, keepdim=True).clamp_min(1e-12).sqrt()
-        a = self.att2(torch.tanh(self.att1(torch.cat([x, mean.expand(-1, T), std.expand(-1, T)], 0), act=False)), act=False)
+        a = self.att2(torch.tanh(self.att1(torch.cat([x, mean.expand(-1, T), std.expand(-1, T)], 0))), act=False)
         w = torch.softmax(a, dim=1)
         m = (w * x).sum(1, keepdim=True)
         s = ((w * (x - m) ** 2).sum(1, keepdim=True)).clamp_min(1e-12).sqrt()
@@ -135,3 +136,23 @@ class Ecapa(nn.Module):
             outs.append(x)
         x = self.mfa(torch.cat(outs, 0))
         return self.fc(self.pool(x), act=False)[:, 0]
+
+
+def load_into(m: Ecapa, loader, prefix: str = "speaker_encoder.") -> None:
+    """Checkpoint names of the released speaker encoder (speaker.rs:60-165): time-delay layers keep their convolution under
+    ``.conv``; the squeeze-excitation pair, the attention's output convolution and the final projection are bare convolutions:
+    ``blocks.0.conv``, ``blocks.<i>.{tdnn1.conv, res2net_block.blocks.<j>.conv, tdnn2.conv, se_block.conv1, se_block.conv2}``,
+    ``mfa.conv``, ``asp.tdnn.conv``, ``asp.conv``, ``fc``."""
+    def put(t: TDNN, name: str):
+        for p, leaf in ((t.w, ".weight"), (t.b, ".bias")):
+            x = loader.load_tensor(prefix + name + leaf, p.dtype)
+            if tuple(x.shape) != tuple(p.shape):
+                raise ValueError(f"{prefix}{name}{leaf}: stored {tuple(x.shape)}, expected {tuple(p.shape)}")
+            p.data.copy_(x)
+    put(m.tdnn0, "blocks.0.conv")
+    for i, b in enumerate(m.blocks, start=1):
+        put(b.tdnn1, f"blocks.{i}.tdnn1.conv"), put(b.tdnn2, f"blocks.{i}.tdnn2.conv")
+        for j, r in enumerate(b.res):
+            put(r, f"blocks.{i}.res2net_block.blocks.{j}.conv")
+        put(b.se1, f"blocks.{i}.se_block.conv1"), put(b.se2, f"blocks.{i}.se_block.conv2")
+    put(m.mfa, "mfa.conv"), put(m.att1, "asp.tdnn.conv"), put(m.att2, "asp.conv"), put(m.fc, "fc")

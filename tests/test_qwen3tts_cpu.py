@@ -118,3 +118,69 @@ def test_speaker_mel_matches_the_library_filterbank_and_ecapa_pooling_rules():
     b.se2.w.data.zero_(), b.se2.b.data.fill_(20.0)                      # gate = 1
     assert torch.allclose((b(h) - h)[:grp], torch.relu(b.tdnn1(h)[:grp]), atol=1e-5)
     b.tdnn2.w.data.copy_(saved)
+
+
+def test_ecapa_loads_by_released_names_and_gates_attention_through_relu_then_tanh():
+    from mary_b200.models.qwen3tts import speaker
+    from mary_b200.models.qwen3tts.speaker import Ecapa, EcapaConfig
+    c = EcapaConfig.tiny()
+    g = torch.Generator().manual_seed(4)
+    names = {"blocks.0.conv": (c.channels, c.n_mels, c.kernel0)}
+    grp, n = c.channels // c.res2net_scale, c.channels * len(c.dilations)
+    for i in range(1, len(c.dilations) + 1):
+        names[f"blocks.{i}.tdnn1.conv"] = names[f"blocks.{i}.tdnn2.conv"] = (c.channels, c.channels, 1)
+        for j in range(c.res2net_scale - 1):
+            names[f"blocks.{i}.res2net_block.blocks.{j}.conv"] = (grp, grp, 3)
+        names[f"blocks.{i}.se_block.conv1"], names[f"blocks.{i}.se_block.conv2"] = (c.se_channels, c.channels, 1), (c.channels, c.se_channels, 1)
+    names.update({"mfa.conv": (n, n, 1), "asp.tdnn.conv": (c.att_channels, 3 * n, 1), "asp.conv": (n, c.att_channels, 1), "fc": (c.out_dim, 2 * n, 1)})
+    sd = {}
+    for k, s in names.items():
+        sd["speaker_encoder." + k + ".weight"] = torch.randn(s, generator=g) * 0.2
+        sd["speaker_encoder." + k + ".bias"] = torch.randn(s[0], generator=g) * 0.1
+
+    class L:
+        def load_tensor(self, n, dtype):
+            return sd[n].to(dtype)
+    m = Ecapa(c)
+    speaker.load_into(m, L())
+    assert sum(p.numel() for p in m.parameters()) == sum(v.numel() for v in sd.values())          # every parameter came from a name
+    feats = torch.randn(c.n_mels, 29)
+    v = m(feats)
+    # the same network restated with functional calls straight from the dictionary
+    import torch.nn.functional as F
+
+    def conv(x, name, d=1, relu=True):
+        w, b = sd["speaker_encoder." + name + ".weight"], sd["speaker_encoder." + name + ".bias"]
+        tot = d * (w.shape[2] - 1)
+        x = F.pad(x[None], (tot // 2, tot - tot // 2), mode="reflect") if tot else x[None]
+        y = F.conv1d(x, w, b, dilation=d)[0]
+        return F.relu(y) if relu else y
+    h = conv(feats, "blocks.0.conv")
+    hs = []
+    for i, d in enumerate(c.dilations, start=1):
+        res = h
+        t = conv(h, f"blocks.{i}.tdnn1.conv")
+        outs = []
+        for j in range(c.res2net_scale):
+            part = t[j * grp:(j + 1) * grp]
+            outs.append(part if j == 0 else conv(part if j == 1 else part + outs[-1], f"blocks.{i}.res2net_block.blocks.{j - 1}.conv", d))
+        t = conv(torch.cat(outs), f"blocks.{i}.tdnn2.conv")
+        s = torch.sigmoid(conv(conv(t.mean(1, keepdim=True), f"blocks.{i}.se_block.conv1"), f"blocks.{i}.se_block.conv2", relu=False))
+        h = t * s + res
+        hs.append(h)
+    h = conv(torch.cat(hs), "mfa.conv")
+    T = h.shape[1]
+    mean, std = h.mean(1, keepdim=True), h.var(1, unbiased=False, keepdim=True).clamp_min(1e-12).sqrt()
+    a = conv(torch.tanh(conv(torch.cat([h, mean.expand(-1, T), std.expand(-1, T)]), "asp.tdnn.conv")), "asp.conv", relu=False).softmax(1)
+    mu = (h * a).sum(1, keepdim=True)
+    sg = ((h - mu) ** 2 * a).sum(1, keepdim=True).clamp_min(1e-12).sqrt()
+    want = conv(torch.cat([mu, sg]), "fc", relu=False)[:, 0]
+    assert torch.allclose(v, want, atol=1e-5), float((v - want).abs().max())
+    bad = dict(sd)
+    bad["speaker_encoder.fc.weight"] = torch.zeros(c.out_dim + 1, 2 * n, 1)
+
+    class LB(L):
+        def load_tensor(self, n, dtype):
+            return bad[n].to(dtype)
+    with pytest.raises(ValueError, match="speaker_encoder.fc.weight"):
+        speaker.load_into(Ecapa(c), LB())
