@@ -142,10 +142,12 @@ def cmd_imagine(a) -> int:
 
 
 def cmd_act(a) -> int:
-    from ..models.smolvla import SmolVLA, SmolVLAConfig
-    if not a.random:
-        raise SystemExit("act: only --random is wired up; the policy's checkpoint layout has no loader in this package yet")
-    m = _random_init(SmolVLA(SmolVLAConfig.tiny()), std=0.2)
+    from ..models.smolvla import SmolVLA, SmolVLAConfig, load_into
+    if a.random:
+        m = _random_init(SmolVLA(SmolVLAConfig.tiny()), std=0.2)
+    else:
+        m = SmolVLA(SmolVLAConfig())
+        load_into(m, _loader(a.pile, a.model))
     img = torch.from_numpy(np.load(a.image)).float()
     state = torch.from_numpy(np.load(a.state)).float()
     chunk = m.act([img], [int(x) for x in a.ids.split(",")], state, generator=torch.Generator().manual_seed(a.seed))

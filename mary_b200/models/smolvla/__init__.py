@@ -1,1 +1,1 @@
-from .model import SmolVLA, SmolVLAConfig, TowerConfig, euler_sample, time_embedding  # noqa: F401
+from .model import SmolVLA, SmolVLAConfig, TowerConfig, euler_sample, load_into, time_embedding  # noqa: F401

@@ -243,3 +243,44 @@ def init_random_(m: SmolVLA, seed: int = 0, std: float = 0.05) -> None:
             p.data.fill_(0.0 if (n.endswith("_b") or "b_" in n.split(".")[-1]) else 1.0)
         else:
             p.data.normal_(0.0, std, generator=g)
+
+
+def load_into(m: SmolVLA, loader, prefix: str = "model.") -> None:
+    """Fill the policy from the released checkpoint's names (src/models/smolvla/{vision,vlm,denoiser,projections}.rs): the SmolVLM
+    backbone under ``vlm_with_expert.vlm.model`` (``vision_model.*``, ``connector.modality_projection.proj``, ``text_model.*`` — only
+    the first ``vlm.n_layers`` text layers exist in the policy), the action expert under ``vlm_with_expert.lm_expert`` (cross-attention
+    layers carry k / v projections that read the backbone's kv width) and five biased projections beside them."""
+    from ..embed.clip import load_blocks
+    dt = m.embed.dtype
+
+    def get(n):
+        return loader.load_tensor(prefix + n, dt)
+
+    def put(p, n):
+        t = get(n)
+        if t.numel() != p.numel():
+            raise ValueError(f"{prefix}{n}: stored {tuple(t.shape)}, expected {tuple(p.shape)}")
+        p.data.copy_(t.reshape(p.shape))
+    vlm = "vlm_with_expert.vlm.model."
+    v = vlm + "vision_model"
+    put(m.patch_w, v + ".embeddings.patch_embedding.weight"), put(m.patch_b, v + ".embeddings.patch_embedding.bias")
+    put(m.v_pos, v + ".embeddings.position_embedding.weight")
+    put(m.v_post_w, v + ".post_layernorm.weight"), put(m.v_post_b, v + ".post_layernorm.bias")
+    load_blocks(m.v_blocks, v, get)
+    put(m.connector, vlm + "connector.modality_projection.proj.weight")
+    put(m.embed, vlm + "text_model.embed_tokens.weight")
+
+    def layer(L, p):
+        put(L.ln1, p + "input_layernorm.weight"), put(L.ln2, p + "post_attention_layernorm.weight")
+        for ours, theirs in (("wq", "q_proj"), ("wk", "k_proj"), ("wv", "v_proj"), ("wo", "o_proj")):
+            put(getattr(L, ours), p + f"self_attn.{theirs}.weight")
+        L.w_gu.data.copy_(torch.cat([get(p + "mlp.gate_proj.weight"), get(p + "mlp.up_proj.weight")], 0))
+        put(L.w_down, p + "mlp.down_proj.weight")
+    for i, L in enumerate(m.vlm_layers):
+        layer(L, vlm + f"text_model.layers.{i}.")
+    for i, L in enumerate(m.expert_layers):
+        layer(L, f"vlm_with_expert.lm_expert.layers.{i}.")
+    put(m.expert_norm, "vlm_with_expert.lm_expert.norm.weight")
+    for ours, theirs in (("state_proj", "state_proj"), ("act_in", "action_in_proj"), ("act_out", "action_out_proj"),
+                         ("at_in", "action_time_mlp_in"), ("at_out", "action_time_mlp_out")):
+        put(getattr(m, ours + "_w"), theirs + ".weight"), put(getattr(m, ours + "_b"), theirs + ".bias")

@@ -134,3 +134,58 @@ def test_vision_tower_and_pixel_shuffle_connector_match_the_huggingface_smolvlm_
         got = m.image_tokens(img)
     assert got.shape == want.shape == ((c.image_size // c.patch // c.shuffle) ** 2, c.vlm.width)
     assert torch.allclose(got, want, atol=2e-4), float((got - want).abs().max())
+
+
+def test_policy_loaded_by_released_names_reproduces_the_backbone_and_fills_every_parameter():
+    import pytest
+    pytest.importorskip("transformers")
+    from transformers.models.smolvlm import SmolVLMConfig, SmolVLMModel
+    from mary_b200.models.smolvla import load_into
+    c = SmolVLAConfig.tiny()
+    torch.manual_seed(2)
+    hc = SmolVLMConfig(
+        vision_config=dict(hidden_size=c.v_hidden, intermediate_size=c.v_ffn, num_hidden_layers=c.v_layers, num_attention_heads=c.v_heads,
+                           image_size=c.image_size, patch_size=c.patch, hidden_act="gelu_pytorch_tanh", layer_norm_eps=1e-6),
+        text_config=dict(hidden_size=c.vlm.width, intermediate_size=c.vlm.ffn_dim, num_hidden_layers=c.vlm.n_layers,
+                         num_attention_heads=c.vlm.n_heads, num_key_value_heads=c.vlm.n_kv_heads, head_dim=c.vlm.head_dim, vocab_size=c.vocab,
+                         pad_token_id=0),
+        scale_factor=c.shuffle, image_token_id=c.vocab - 1, pad_token_id=0)
+    hc._attn_implementation = "eager"
+    hc.vision_config._attn_implementation = "eager"
+    hf = SmolVLMModel(hc).eval()
+    sd = {"model.vlm_with_expert.vlm.model." + k: v.detach() for k, v in hf.state_dict().items()}
+    e, kv = c.expert, c.vlm.n_kv_heads * c.vlm.head_dim
+    g = torch.Generator().manual_seed(0)
+    for i in range(e.n_layers):
+        p = f"model.vlm_with_expert.lm_expert.layers.{i}."
+        kin = e.width if i % c.self_attn_every == 0 else kv
+        for n, s in (("input_layernorm", (e.width,)), ("post_attention_layernorm", (e.width,)), ("self_attn.q_proj", (e.n_heads * e.head_dim, e.width)),
+                     ("self_attn.k_proj", (e.n_kv_heads * e.head_dim, kin)), ("self_attn.v_proj", (e.n_kv_heads * e.head_dim, kin)),
+                     ("self_attn.o_proj", (e.width, e.n_heads * e.head_dim)), ("mlp.gate_proj", (e.ffn_dim, e.width)),
+                     ("mlp.up_proj", (e.ffn_dim, e.width)), ("mlp.down_proj", (e.width, e.ffn_dim))):
+            sd[p + n + ".weight"] = torch.randn(s, generator=g) * 0.1
+    sd["model.vlm_with_expert.lm_expert.norm.weight"] = torch.ones(e.width)
+    for n, (o, i) in {"state_proj": (c.vlm.width, c.state_dim), "action_in_proj": (e.width, c.action_dim), "action_out_proj": (c.action_dim, e.width),
+                      "action_time_mlp_in": (e.width, 2 * e.width), "action_time_mlp_out": (e.width, e.width)}.items():
+        sd[f"model.{n}.weight"], sd[f"model.{n}.bias"] = torch.randn(o, i, generator=g) * 0.1, torch.randn(o, generator=g) * 0.1
+    used = set()
+
+    class L:
+        def load_tensor(self, n, dtype):
+            used.add(n)
+            return sd[n].to(dtype)
+    m = SmolVLA(c)
+    for p in m.parameters():
+        p.data.fill_(float("nan"))
+    load_into(m, L())
+    assert all(torch.isfinite(p).all() for p in m.parameters())                         # nothing left unfilled
+    unused = set(sd) - used
+    assert all("text_model.norm" in n or "lm_head" in n for n in unused), sorted(unused)[:5]   # the policy reads K / V, never the final norm
+    img = torch.rand(3, c.image_size, c.image_size) * 2 - 1
+    with torch.no_grad():
+        out = hf.get_image_features(pixel_values=img[None, None])
+        want = (out.pooler_output if hasattr(out, "pooler_output") else out).reshape(-1, c.vlm.width) * math.sqrt(c.vlm.width)
+        assert torch.allclose(m.image_tokens(img), want, atol=2e-4)
+        chunk = m.act([img], [3, 4, 5], torch.randn(c.state_dim), generator=torch.Generator().manual_seed(0))
+    assert chunk.shape[0] == c.chunk_size and torch.isfinite(chunk).all()
+    assert torch.equal(m.vlm_layers[1].w_gu[:c.vlm.ffn_dim], sd["model.vlm_with_expert.vlm.model.text_model.layers.1.mlp.gate_proj.weight"])
