@@ -76,13 +76,35 @@ def cmd_say(a) -> int:
         n_fft, hop = 1024, 256
     wav, sr = read_wav(a.ref_wav)
     ref = mel_spectrogram(torch.from_numpy(wav), n_mels=dit.c.n_mels, n_fft=n_fft, hop=hop, sr=sr).T.contiguous()
-    chars = [ord(ch) % (dit.c.text_vocab - 1) for ch in a.ref_text + " " + a.text]            # byte-level ids when the pile holds no vocabulary
-    # duration rule of the reference front end: target frames = reference frames * (target characters / reference characters)
-    total = ref.shape[0] + max(1, int(ref.shape[0] * len(a.text) / max(1, len(a.ref_text)) / a.speed))
-    mel = CFM(dit, nfe=a.nfe, cfg_strength=a.cfg).sample(ref, chars, total, generator=torch.Generator().manual_seed(a.seed))
-    out = voc(mel[ref.shape[0]:].T.contiguous())
-    write_wav(a.out, out.numpy(), sr)
-    print(f"{out.shape[0] / sr:.2f} s of audio -> {a.out}")
+    cfm = CFM(dit, nfe=a.nfe, cfg_strength=a.cfg)
+
+    def synth(text: str, out_path: str, seed: int) -> float:
+        chars = [ord(ch) % (dit.c.text_vocab - 1) for ch in a.ref_text + " " + text]          # byte-level ids when the pile holds no vocabulary
+        # duration rule of the reference front end: target frames = reference frames * (target characters / reference characters)
+        total = ref.shape[0] + max(1, int(ref.shape[0] * len(text) / max(1, len(a.ref_text)) / a.speed))
+        mel = cfm.sample(ref, chars, total, generator=torch.Generator().manual_seed(seed))
+        out = voc(mel[ref.shape[0]:].T.contiguous())
+        write_wav(out_path, out.numpy(), sr)
+        return out.shape[0] / sr
+    if not a.serve:
+        print(f"{synth(a.text, a.out, a.seed):.2f} s of audio -> {a.out}")
+        return 0
+    # warm server (``say_serve``): weights, vocoder, mel front end and the reference voice are loaded ONCE; every line of standard
+    # input is one request ``<out.wav>\t<text>``; the per-request time is printed so that the warm / cold difference is measurable
+    import time
+    print("ready", flush=True)
+    for n, line in enumerate(sys.stdin):
+        line = line.rstrip("\n")
+        if not line:
+            continue
+        if "\t" not in line:
+            print(f"bad request (want <out.wav>\\t<text>): {line!r}", flush=True)
+            continue
+        out_path, text = line.split("\t", 1)
+        t0 = time.perf_counter()
+        secs = synth(text, out_path, a.seed + n)
+        dt = time.perf_counter() - t0
+        print(f"{out_path}\t{secs:.2f} s of audio in {dt:.2f} s (x{secs / max(dt, 1e-9):.2f} real time)", flush=True)
     return 0
 
 
@@ -284,7 +306,8 @@ def main(argv=None) -> int:
         return p
     s = common(sub.add_parser("say"))
     s.add_argument("--vocoder", default="vocos"), s.add_argument("--ref-wav", required=True), s.add_argument("--ref-text", required=True)
-    s.add_argument("--text", required=True), s.add_argument("--out", required=True), s.add_argument("--nfe", type=int, default=32)
+    s.add_argument("--text"), s.add_argument("--out"), s.add_argument("--nfe", type=int, default=32)
+    s.add_argument("--serve", action="store_true", help="load once, then one request per line of standard input: <out.wav>\\t<text>")
     s.add_argument("--cfg", type=float, default=2.0), s.add_argument("--speed", type=float, default=1.0)
     s.set_defaults(fn=cmd_say)
     li = common(sub.add_parser("listen"))

@@ -146,6 +146,49 @@ def cmd_k3_gate(a) -> int:
     return 1 if bad else 0
 
 
+def cmd_k3_experts(a) -> int:
+    """The K3 expert address book (``k3_expert_index``): gate first, bandwidth only when the gate passes."""
+    from ..models.k3.ckpt import K3Checkpoint, expert_index, fetch_sweep
+    ck = K3Checkpoint(a.dir)
+    ix = expert_index(ck)
+    print(f"address book: {len(ix['book'])} routed experts (expected {ix['expected']}), {ix['expert_bytes']} bytes each")
+    print(f"experts with another size: {len(ix['wrong_size'])}; split or interleaved: {len(ix['split'])}")
+    print("resident set (everything that is not a routed expert):")
+    for g, n in sorted(ix["resident"].items(), key=lambda kv: -kv[1]):
+        print(f"  {g:<32} {n / 2 ** 30:10.4f} GiB")
+    if not ix["ok"]:
+        print("GATE FAIL: no bandwidth number is reported")
+        ck.close()
+        return 1
+    print("GATE PASS")
+    for n, cnt, dt, gbs in fetch_sweep(ck, ix["book"], [int(x) for x in a.sweep.split(",")], a.per_level):
+        print(f"  {n:3d} readers: {cnt} experts in {dt * 1e3:.1f} ms = {gbs:.2f} GB/s")
+    ck.close()
+    return 0
+
+
+def cmd_encode(a) -> int:
+    """Text on stdin, an ids file out (``inkling_encode``): stdin is taken VERBATIM (leading space and trailing bytes included; use
+    ``printf '%s'``, not ``echo``); ids go out as little-endian i64, the form the serving CLI reads; the decode round trip is printed
+    so that a file can be checked against the string it claims to be."""
+    import numpy as np
+    text = sys.stdin.buffer.read().decode("utf-8")
+    if a.tokenizer_json:
+        from tokenizers import Tokenizer
+        tok = Tokenizer.from_file(a.tokenizer_json)
+    else:
+        from ..format.tokenizer import build_tokenizer, select_tokenizer
+        pile = Pile.open(a.pile, create=False)
+        facts = read_model_pile(pile)
+        tok = build_tokenizer(pile, facts, select_tokenizer(pile, facts, a.tokenizer))
+    ids = tok.encode(text, add_special_tokens=False).ids
+    np.asarray(ids, dtype="<i8").tofile(a.out)
+    print(f"{len(ids)} ids -> {a.out}")
+    print(f"ids: {ids[:32]}{' ...' if len(ids) > 32 else ''}")
+    print(f"decode: {tok.decode(ids)!r}")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mary")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -181,6 +224,12 @@ def main(argv=None) -> int:
     kg = sub.add_parser("k3-gate")
     kg.add_argument("dir"), kg.add_argument("--show", type=int, default=10)
     kg.set_defaults(fn=cmd_k3_gate)
+    ke = sub.add_parser("k3-experts")
+    ke.add_argument("dir"), ke.add_argument("--sweep", default="1,4,16"), ke.add_argument("--per-level", type=int, default=32)
+    ke.set_defaults(fn=cmd_k3_experts)
+    en = sub.add_parser("encode")
+    en.add_argument("out"), en.add_argument("--pile"), en.add_argument("--tokenizer"), en.add_argument("--tokenizer-json")
+    en.set_defaults(fn=cmd_encode)
     a = ap.parse_args(argv)
     return a.fn(a)
 

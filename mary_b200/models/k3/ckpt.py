@@ -227,3 +227,89 @@ class K3Checkpoint:
         if self.dims is None:
             raise CheckpointError("no config.json beside the index")
         return layout.check_headers(self.dims, self.headers())
+
+
+# ---- expert address book (src/bin/k3_expert_index.rs) --------------------------------------------------------------------------
+
+_EXPERT_MEMBERS = tuple(f"{m}.weight_{h}" for m in ("w1", "w2", "w3") for h in ("packed", "scale"))
+
+
+def expert_index(ck: K3Checkpoint) -> dict:
+    """Where every routed expert's bytes live: ``{(layer, expert): (shard, absolute file offset, length, contiguous)}`` through the
+    real name -> shard -> offset path, plus the gate's findings.  Streaming is the only way a model of this size runs on one
+    host, and a loader wants ONE read per expert, so three properties are checked instead of assumed: the count is
+    ``sparse layers x experts``; every expert totals the byte count the layout predicts; the six members of an expert
+    (w1 / w2 / w3 x codes + exponents) sit back to back in one shard.  Offsets in a shard's header are relative to the END of
+    the header; the ones returned here are absolute."""
+    d = ck.dims
+    if d is None:
+        raise CheckpointError("no config.json beside the index")
+    lat, f = d.moe_hidden_size, d.moe_intermediate_size
+    want_bytes = 3 * (lat * f // 2 + lat * f // layout.MXFP4_BLOCK)
+    book, wrong_size, split = {}, [], []
+    sparse = [i for i in range(d.num_hidden_layers) if d.is_moe_layer(i)]
+    for i in sparse:
+        for e in range(d.num_experts):
+            pre = ck._expert_prefix(i, e)
+            spans, shards = [], set()
+            for m in _EXPERT_MEMBERS:
+                name = f"{pre}.{m}"
+                if not ck.has(name):
+                    break
+                shard = ck.weight_map[name]
+                _, base = ck._shard(shard)
+                a, b = ck.raw_info(name)[2]
+                spans.append((base + a, base + b))
+                shards.add(shard)
+            if len(spans) != len(_EXPERT_MEMBERS):
+                continue
+            spans.sort()
+            total = sum(b - a for a, b in spans)
+            contiguous = len(shards) == 1 and all(spans[j][1] == spans[j + 1][0] for j in range(len(spans) - 1))
+            book[(i, e)] = (next(iter(shards)) if len(shards) == 1 else None, spans[0][0], total, contiguous)
+            if total != want_bytes:
+                wrong_size.append((i, e, total))
+            if not contiguous:
+                split.append((i, e))
+    resident: dict = {}
+    for name, shard in ck.weight_map.items():
+        if ".experts." in name:
+            continue
+        a, b = ck.raw_info(name)[2]
+        slot = layout.parse(name)
+        group = "unmapped" if slot is None else slot[0] if slot[0] != "layer" else "layer." + ".".join(str(x) for x in slot[2:4] if isinstance(x, str))
+        resident[group] = resident.get(group, 0) + (b - a)
+    return {"book": book, "expected": len(sparse) * d.num_experts, "expert_bytes": want_bytes, "wrong_size": wrong_size, "split": split,
+            "resident": resident, "ok": len(book) == len(sparse) * d.num_experts and not wrong_size and not split}
+
+
+def read_expert_bytes(ck: K3Checkpoint, entry) -> bytes:
+    """One ``pread`` covering a whole contiguous expert (an entry of :func:`expert_index`'s book)."""
+    shard, off, n, contiguous = entry
+    if not contiguous:
+        raise CheckpointError("expert is split or interleaved: a single read cannot cover it")
+    ck._shard(shard)
+    buf = os.pread(ck._fds[shard], n, off)
+    if len(buf) != n:
+        raise CheckpointError(f"short read in {shard}")
+    return buf
+
+
+def fetch_sweep(ck: K3Checkpoint, book: dict, levels=(1, 4, 16), per_level: int = 32) -> list:
+    """Expert fetch bandwidth through the address book at several concurrency levels: ``[(threads, experts, seconds, GB/s)]``.
+    Each level reads experts no earlier level touched (the page cache is not bypassed: this is the path a loader sees)."""
+    import time
+    from concurrent.futures import ThreadPoolExecutor
+    keys = [k for k in sorted(book) if book[k][3]]
+    out, pos = [], 0
+    for n in levels:
+        batch = keys[pos:pos + per_level]
+        pos += len(batch)
+        if not batch:
+            break
+        t0 = time.perf_counter()
+        with ThreadPoolExecutor(max_workers=n) as pool:
+            got = sum(pool.map(lambda k: len(read_expert_bytes(ck, book[k])), batch))
+        dt = time.perf_counter() - t0
+        out.append((n, len(batch), dt, got / dt / 1e9))
+    return out

@@ -92,3 +92,19 @@ def test_converse_streams_user_audio_through_codec_and_speech_lm(tmp_path, capsy
     toks = capsys.readouterr().out.strip().split(",")
     y, _ = families.read_wav(str(tmp_path / "a.wav"))
     assert 8 <= len(toks) <= 12 and len(y) == len(toks) * 16
+
+
+def test_say_serve_answers_one_request_per_line_with_warm_weights(tmp_path, capsys, monkeypatch):
+    import io
+    import sys
+    sr = 16000
+    t = np.arange(sr // 2) / sr
+    families.write_wav(str(tmp_path / "ref.wav"), 0.3 * np.sin(2 * np.pi * 220 * t), sr)
+    reqs = f"{tmp_path / 'a.wav'}\thello there\nnot a request\n\n{tmp_path / 'b.wav'}\thi\n"
+    monkeypatch.setattr(sys, "stdin", io.StringIO(reqs))
+    assert families.main(["say", "--random", "--serve", "--ref-wav", str(tmp_path / "ref.wav"), "--ref-text", "hello", "--nfe", "2"]) == 0
+    out = capsys.readouterr().out.splitlines()
+    assert out[0] == "ready" and out[1].startswith(str(tmp_path / "a.wav")) and "bad request" in out[2] and out[3].startswith(str(tmp_path / "b.wav"))
+    a, _ = families.read_wav(str(tmp_path / "a.wav"))
+    b, _ = families.read_wav(str(tmp_path / "b.wav"))
+    assert len(a) > len(b) > 0                                      # duration follows the character ratio

@@ -204,3 +204,55 @@ def test_cli_gate(tmp_path, capsys):
     _write_checkpoint(str(tmp_path))
     assert main(["k3-gate", str(tmp_path)]) == 0
     assert "unfilled 0, unmapped 0, mismatched 0, not_inverse 0" in capsys.readouterr().out
+
+
+def test_expert_address_book_gate_single_reads_and_cli(tmp_path, capsys):
+    from mary_b200.cli.mary import main
+    from mary_b200.models.k3.ckpt import expert_index, fetch_sweep, read_expert_bytes
+    truth = _write_checkpoint(str(tmp_path))
+    ck = K3Checkpoint(str(tmp_path))
+    ix = expert_index(ck)
+    assert ix["ok"] and len(ix["book"]) == ix["expected"] == 3 * 4
+    assert ix["expert_bytes"] == 3 * (32 * 64 // 2 + 32 * 64 // 32)
+    # one read covers the expert; its bytes are the six members in name order
+    entry = ix["book"][(2, 1)]
+    blob = read_expert_bytes(ck, entry)
+    pre = "language_model.model.layers.2.block_sparse_moe.experts.1."
+    want = b"".join(bytes(ck.raw(pre + m)[2]) for m in ("w1.weight_packed", "w1.weight_scale", "w2.weight_packed", "w2.weight_scale",
+                                                        "w3.weight_packed", "w3.weight_scale"))
+    assert blob == want
+    assert sum(ix["resident"].values()) == sum(ck.raw_info(n)[2][1] - ck.raw_info(n)[2][0] for n in ck.weight_map if ".experts." not in n)
+    sweep = fetch_sweep(ck, ix["book"], levels=(1, 2), per_level=4)
+    assert [(n, c) for n, c, _, _ in sweep] == [(1, 4), (2, 4)] and all(g > 0 for *_, g in sweep)
+    ck.close()
+    assert main(["k3-experts", str(tmp_path), "--sweep", "1,2", "--per-level", "3"]) == 0
+    assert "GATE PASS" in capsys.readouterr().out
+    # an index that lost one member of one expert fails the gate and prints no bandwidth
+    idx = os.path.join(str(tmp_path), "model.safetensors.index.json")
+    wm = json.load(open(idx))["weight_map"]
+    del wm[pre + "w2.weight_scale"]
+    json.dump({"weight_map": wm}, open(idx, "w"))
+    assert main(["k3-experts", str(tmp_path)]) == 1
+    out = capsys.readouterr().out
+    assert "GATE FAIL" in out and "readers" not in out
+
+
+def test_encode_writes_little_endian_i64_and_prints_the_round_trip(tmp_path, capsys, monkeypatch):
+    import io
+    import sys
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer, models, pre_tokenizers, decoders
+    from mary_b200.cli.mary import main
+    vocab = {"[UNK]": 0, "ĠThe": 1, "Ġcapital": 2, "Ġof": 3, "ĠFrance": 4, "Ġis": 5}
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="[UNK]"))
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    tok.decoder = decoders.ByteLevel()
+    tok.save(str(tmp_path / "tokenizer.json"))
+
+    class In:
+        buffer = io.BytesIO(" The capital of France is".encode())
+    monkeypatch.setattr(sys, "stdin", In)
+    assert main(["encode", str(tmp_path / "p.ids"), "--tokenizer-json", str(tmp_path / "tokenizer.json")]) == 0
+    ids = np.fromfile(tmp_path / "p.ids", dtype="<i8")
+    assert ids.tolist() == [1, 2, 3, 4, 5]
+    assert "decode: ' The capital of France is'" in capsys.readouterr().out
