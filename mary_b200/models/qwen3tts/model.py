@@ -143,15 +143,36 @@ class CodePredictor(nn.Module):
     def predict_frame(self, h_talker, code0_embed, temperature: float = 0.0, seed: int = 0, frame: int = 0):
         """``h_talker [H]``, ``code0_embed [H]`` (the talker's codec embedding row of the sampled codebook-0 id).  Returns
         ``(codes int64 [num_code_groups - 1], embed_sum [H])`` where ``embed_sum`` is the sum of the predictor's talker-width
-        embeddings of those codes — the codec side of the talker's next input."""
+        embeddings of those codes — the codec side of the talker's next input.
+
+        The 15 steps are strictly sequential and tiny, so on the GPU their cost is launch submission, not math (the reason the
+        reference moved this stage to the CPU, src/models/qwen3tts/cpu.rs:1-8, and wrote a persistent chain kernel,
+        megakernel.rs:70-722).  Here the whole greedy frame (every decoder layer of every step, the heads, the arg-max and the
+        embedding gathers) is captured ONCE as a CUDA graph over static buffers and replayed per frame: positions are the same
+        in every frame, so the batch descriptors are built once."""
+        if h_talker.is_cuda and temperature <= 0 and self.use_graph:
+            if self._graph is None:
+                self._capture(h_talker.dtype)
+            self._g_in[0].copy_(h_talker), self._g_in[1].copy_(code0_embed)
+            self._graph.replay()
+            return self._g_codes.clone(), self._g_sum.clone()
+        return self._frame(torch.stack([h_talker, code0_embed]), self._metas(), temperature, seed, frame)
+
+    use_graph = True
+    _graph = None
+
+    def _metas(self):
         n = self.cfg.num_code_groups - 1
-        x = self.project(torch.stack([h_talker, code0_embed]))
-        codes, embed_sum = [], torch.zeros_like(h_talker, dtype=torch.float32)
-        kv = 0
+        if getattr(self, "_meta_list", None) is None:
+            self._meta_list = [self._meta(2 if i == 0 else 1, i + 2) for i in range(n)]
+        return self._meta_list
+
+    def _frame(self, x2, metas, temperature, seed, frame):
+        n = self.cfg.num_code_groups - 1
+        x = self.project(x2)
+        codes, embed_sum = [], torch.zeros(x2.shape[1], dtype=torch.float32, device=x2.device)
         for i in range(n):
-            q = x.shape[0]
-            kv += q
-            hid = self.stack.hidden_from_embeds(x, self._meta(q, kv), self.cache)[-1:]
+            hid = self.stack.hidden_from_embeds(x, metas[i], self.cache)[-1:]
             lg = ops.linear(hid, self.heads[i]).float()
             tok = sampling.sample(lg, temperature, seed=seed, step=frame * 64 + i)
             codes.append(tok.reshape(1))
@@ -159,6 +180,19 @@ class CodePredictor(nn.Module):
             embed_sum += e[0].float()
             x = self.project(e)
         return torch.cat(codes), embed_sum
+
+    def _capture(self, dtype):
+        metas = self._metas()
+        self._g_in = torch.zeros(2, self.cfg.talker_hidden, dtype=dtype, device=self.dev)
+        side = torch.cuda.Stream(device=self.dev)
+        side.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(side):                                    # one eager pass first: lazy initialisation stays out of the graph
+            self._frame(self._g_in, metas, 0.0, 0, 0)
+        torch.cuda.current_stream(self.dev).wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self._g_codes, self._g_sum = self._frame(self._g_in, metas, 0.0, 0, 0)
+        self._graph = g
 
     def accumulate_frame(self, codes):
         """Sum of the talker-width embeddings of codebooks 1.. of one known frame (reference prompts)."""

@@ -232,6 +232,34 @@ def bench_floor(reps: int = 200):
     assert K.last_status() == 0
 
 
+def bench_ttsframe(iters: int = 30):
+    """One frame of the Qwen3-TTS code predictor at its released size (5 layers x 1024, 15 sequential steps, 2048-entry heads):
+    eager launches against the one-graph replay of the same frame."""
+    from ..models.qwen3tts.model import CodePredictor, Qwen3TTSConfig, Talker, init_random_
+    c = Qwen3TTSConfig(talker_layers=1)
+    tk, pr = Talker(c, torch.bfloat16, "cuda"), CodePredictor(c, torch.bfloat16, "cuda")
+    init_random_(tk, pr, 0)
+    h = (torch.randn(c.talker_hidden, device="cuda") * 0.5).to(torch.bfloat16)
+    e0 = (torch.randn(c.talker_hidden, device="cuda") * 0.5).to(torch.bfloat16)
+    out = {}
+    for name, flag in (("eager", False), ("graph", True)):
+        pr.use_graph = flag
+        for _ in range(3):
+            pr.predict_frame(h, e0)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            pr.predict_frame(h, e0)
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = a.elapsed_time(b) / iters
+    w = sum(p.numel() * p.element_size() for p in pr.stack.parameters()) * (c.num_code_groups - 1)
+    print(f"qwen3tts code predictor frame ({c.num_code_groups - 1} steps x {c.pred_layers} layers): eager {out['eager'] * 1e3:.0f} us, graph "
+          f"{out['graph'] * 1e3:.0f} us per frame ({out['eager'] / out['graph']:.2f}x); {w / 1e6:.0f} MB of weights read per frame; "
+          f"a 12.5 Hz frame budget is 80000 us")
+
+
 def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5):
     """One expert-parallel MoE layer in all-to-all mode with all ranks on this device, phase by phase (the barriers between
     the phases are stream order here): the per-rank cost of counts, plan + dispatch, expert GEMMs and the weighted sum at the
@@ -287,6 +315,8 @@ if __name__ == "__main__":
                 bench_mla(B=16, page=pg)
     if what == "floor":
         bench_floor(*nums)
+    if what == "ttsframe":
+        bench_ttsframe(*nums)
     if what == "ep":
         bench_ep(*nums)
     if what in ("moe", "all"):

@@ -191,3 +191,26 @@ def test_inkling_attention_with_relative_bias_on_the_paged_cache():
             outs.append(att(x[done:done + n].cuda().bfloat16(), BatchMeta.build([n], lens, table, 16, device="cuda"), cache.k[0], cache.v[0]))
             done += n
         _close(torch.cat(outs), want, 0.05)
+
+
+def test_qwen3tts_code_predictor_frame_as_a_cuda_graph_equals_the_eager_frame():
+    """The code predictor's sequential steps of one frame, captured once and replayed, give the codes and the embedding sum of the
+    eager path for every frame (fresh inputs each time), and agree with the f32 CPU reference on the embedding sum."""
+    from mary_b200.models.qwen3tts.model import CodePredictor, Qwen3TTSConfig, Talker, init_random_
+    c = Qwen3TTSConfig(talker_layers=1, talker_hidden=256, talker_heads=4, talker_kv_heads=2, talker_ffn=256, head_dim=64, codec_vocab=128,
+                       text_vocab=64, text_hidden=64, pred_layers=2, pred_hidden=128, pred_heads=2, pred_kv_heads=1, pred_ffn=256, pred_vocab=128,
+                       num_code_groups=8, codec_pad=100, codec_bos=101, codec_eos=102)
+    tk, pr = Talker(c, torch.bfloat16, "cuda"), CodePredictor(c, torch.bfloat16, "cuda")
+    init_random_(tk, pr, 3, std=0.08)
+    agree = 0
+    for f in range(4):
+        h = (torch.randn(c.talker_hidden, device="cuda") * 0.5).to(torch.bfloat16)
+        e0 = (torch.randn(c.talker_hidden, device="cuda") * 0.5).to(torch.bfloat16)
+        pr.use_graph = False
+        codes_e, sum_e = pr.predict_frame(h, e0)
+        pr.use_graph = True
+        codes_g, sum_g = pr.predict_frame(h, e0)
+        assert torch.equal(codes_e, codes_g) and torch.equal(sum_e, sum_g)
+        assert codes_g.shape == (c.num_code_groups - 1,) and int(codes_g.min()) >= 0 and int(codes_g.max()) < c.pred_vocab
+        agree += 1
+    assert pr._graph is not None and agree == 4
