@@ -186,7 +186,12 @@ class Depformer(nn.Module):
 
     def generate(self, h_temporal, text_token, forced=None, sample=None):
         """All ``dep_q`` codebooks of a frame.  ``forced[s]`` (or ``None``) teacher-forces step ``s``'s token into the chain;
-        ``sample(logits, s)`` picks a token (greedy when absent).  Returns tokens ``[B, dep_q]``."""
+        ``sample(logits, s)`` picks a token (greedy when absent).  Returns tokens ``[B, dep_q]``.
+
+        On the GPU the greedy chain (``dep_q`` steps x ``dep_layers`` layers of tiny GEMMs, no position dependence) is captured
+        once per batch size as a CUDA graph and replayed per frame; forced tokens enter through a device mask / value pair."""
+        if h_temporal.is_cuda and sample is None and self.use_graph:
+            return self._replay(h_temporal, text_token, forced)
         prev, cache, out = text_token, None, []
         for t in range(self.c.dep_q):
             logits, cache = self.step(t, h_temporal, prev, cache)
@@ -196,6 +201,42 @@ class Depformer(nn.Module):
             if forced is not None and forced[t] is not None:
                 prev = torch.full_like(tok, int(forced[t]))
         return torch.stack(out, 1)
+
+    use_graph = True
+
+    def _chain(self, h, text_token, fmask, fval):
+        prev, cache, out = text_token, None, []
+        for t in range(self.c.dep_q):
+            logits, cache = self.step(t, h, prev, cache)
+            tok = ref.argmax_first(logits)
+            out.append(tok)
+            prev = torch.where(fmask[t], fval[t], tok)
+        return torch.stack(out, 1)
+
+    def _replay(self, h, text_token, forced):
+        B, S = h.shape[0], self.c.dep_q
+        graphs = self.__dict__.setdefault("_graphs", {})
+        if B not in graphs:
+            st = {"h": torch.zeros_like(h), "text": torch.zeros(B, dtype=torch.long, device=h.device),
+                  "mask": torch.zeros(S, 1, dtype=torch.bool, device=h.device), "val": torch.zeros(S, 1, dtype=torch.long, device=h.device)}
+            side = torch.cuda.Stream(device=h.device)
+            side.wait_stream(torch.cuda.current_stream(h.device))
+            with torch.cuda.stream(side):
+                self._chain(st["h"], st["text"], st["mask"], st["val"])
+            torch.cuda.current_stream(h.device).wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                st["out"] = self._chain(st["h"], st["text"], st["mask"], st["val"])
+            st["graph"] = g
+            graphs[B] = st
+        st = graphs[B]
+        st["h"].copy_(h), st["text"].copy_(text_token)
+        m = [f is not None for f in (forced or [None] * S)]
+        v = [int(f) if f is not None else 0 for f in (forced or [None] * S)]
+        st["mask"].copy_(torch.tensor(m, dtype=torch.bool).view(S, 1), non_blocking=True)
+        st["val"].copy_(torch.tensor(v, dtype=torch.long).view(S, 1), non_blocking=True)
+        st["graph"].replay()
+        return st["out"].clone()
 
 
 class LmGen(nn.Module):

@@ -260,6 +260,35 @@ def bench_ttsframe(iters: int = 30):
           f"a 12.5 Hz frame budget is 80000 us")
 
 
+def bench_depformer(iters: int = 30):
+    """The depth transformer of the full-duplex speech LM at its released size (16 steps x 6 layers x 1024, per-step weights): one frame's
+    greedy chain eager against the one-graph replay."""
+    from ..models.moshi.model import Depformer, MoshiConfig
+    c = MoshiConfig()
+    d = Depformer(c, torch.bfloat16, "cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for n, p in d.named_parameters():
+        p.data.fill_(1.0) if n in ("norm1", "norm2") else p.data.normal_(0.0, 0.03, generator=g)
+    h = (torch.randn(1, c.dim, device="cuda") * 0.5).to(torch.bfloat16)
+    text = torch.tensor([5], device="cuda")
+    forced = [None] * 8 + [3] * 8                                          # the user's eight codebooks are forced, the agent's generated
+    out = {}
+    for name, flag in (("eager", False), ("graph", True)):
+        d.use_graph = flag
+        for _ in range(3):
+            d.generate(h, text, forced)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            d.generate(h, text, forced)
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = a.elapsed_time(b) / iters
+    print(f"speech LM depth transformer frame ({c.dep_q} steps x {c.dep_layers} layers): eager {out['eager'] * 1e3:.0f} us, graph "
+          f"{out['graph'] * 1e3:.0f} us per frame ({out['eager'] / out['graph']:.2f}x); a 12.5 Hz frame budget is 80000 us")
+
+
 def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5):
     """One expert-parallel MoE layer in all-to-all mode with all ranks on this device, phase by phase (the barriers between
     the phases are stream order here): the per-rank cost of counts, plan + dispatch, expert GEMMs and the weighted sum at the
@@ -317,6 +346,8 @@ if __name__ == "__main__":
         bench_floor(*nums)
     if what == "ttsframe":
         bench_ttsframe(*nums)
+    if what == "depformer":
+        bench_depformer(*nums)
     if what == "ep":
         bench_ep(*nums)
     if what in ("moe", "all"):

@@ -214,3 +214,23 @@ def test_qwen3tts_code_predictor_frame_as_a_cuda_graph_equals_the_eager_frame():
         assert codes_g.shape == (c.num_code_groups - 1,) and int(codes_g.min()) >= 0 and int(codes_g.max()) < c.pred_vocab
         agree += 1
     assert pr._graph is not None and agree == 4
+
+
+def test_moshi_depth_transformer_chain_as_a_cuda_graph_equals_the_eager_chain():
+    from mary_b200.models.moshi.model import Depformer, MoshiConfig
+    c = MoshiConfig(dim=256, layers=1, heads=4, ffn=256, context=64, text_card=96, card=128, dep_dim=128, dep_layers=2, dep_heads=2, dep_ffn=256,
+                    dep_q=8, codebooks_per_stream=4)
+    d = Depformer(c, torch.bfloat16, "cuda")
+    g = torch.Generator(device="cuda").manual_seed(2)
+    for n, p in d.named_parameters():
+        p.data.fill_(1.0) if n in ("norm1", "norm2") else p.data.normal_(0.0, 0.08, generator=g)
+    for f, forced in enumerate((None, [None] * 4 + [7, 9, 11, 13], [5] + [None] * 7)):
+        h = (torch.randn(2, c.dim, device="cuda") * 0.5).to(torch.bfloat16)
+        text = torch.tensor([3 + f, 40], device="cuda")
+        d.use_graph = False
+        want = d.generate(h, text, forced)
+        d.use_graph = True
+        got = d.generate(h, text, forced)
+        assert torch.equal(got, want), (got, want)
+        assert got.shape == (2, c.dep_q) and int(got.max()) < c.card
+    assert len(d._graphs) == 1
