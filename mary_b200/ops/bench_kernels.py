@@ -289,6 +289,37 @@ def bench_depformer(iters: int = 30):
           f"{out['graph'] * 1e3:.0f} us per frame ({out['eager'] / out['graph']:.2f}x); a 12.5 Hz frame budget is 80000 us")
 
 
+def bench_speechlm(frames: int = 40):
+    """The full-duplex speech LM at its released size (temporal 32 x 4096, depth 6 x 1024 x 16 steps), one conversation: milliseconds
+    per 80 ms frame of ``LmGen.step`` (stream bookkeeping on the host, temporal step on the paged cache, text head, depth chain)
+    with the user's eight codebooks provided every frame, and the real-time factor."""
+    import time
+    from ..models.moshi.model import LmGen, MoshiConfig
+    c = MoshiConfig()
+    m = LmGen(c, torch.bfloat16, "cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for n, p in m.named_parameters():
+        if p.dim() == 1 or n.endswith(("norm1", "norm2")):
+            p.data.fill_(1.0)
+        else:
+            p.data.normal_(0.0, 0.02, generator=g)
+    user = [7] * c.codebooks_per_stream
+    for _ in range(6):
+        m.step(user_audio=user)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(frames):
+        m.step(user_audio=user)
+    b.record()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / frames * 1e3
+    dev = a.elapsed_time(b) / frames
+    print(f"speech LM frame (temporal {c.layers} x {c.dim} + depth {c.dep_q} x {c.dep_layers} x {c.dep_dim}): {dev:.2f} ms device, {wall:.2f} ms wall "
+          f"per 80 ms frame = {80.0 / wall:.1f}x real time")
+
+
 def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5):
     """One expert-parallel MoE layer in all-to-all mode with all ranks on this device, phase by phase (the barriers between
     the phases are stream order here): the per-rank cost of counts, plan + dispatch, expert GEMMs and the weighted sum at the
@@ -348,6 +379,8 @@ if __name__ == "__main__":
         bench_ttsframe(*nums)
     if what == "depformer":
         bench_depformer(*nums)
+    if what == "speechlm":
+        bench_speechlm(*nums)
     if what == "ep":
         bench_ep(*nums)
     if what in ("moe", "all"):
