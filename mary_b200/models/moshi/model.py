@@ -162,25 +162,23 @@ class Depformer(nn.Module):
 
     def step(self, t: int, h_temporal, prev_token, cache):
         """One codebook step for a batch of frames: ``h_temporal [B, dim]``, ``prev_token [B]``, ``cache`` = list per layer of
-        ``(k, v)`` over the steps so far (``None`` at ``t = 0``).  Returns ``(logits [B, card], cache)``."""
+        ``(k, v)`` buffers over all steps of the frame, rows ``0 .. t - 1`` filled (``None`` at ``t = 0``: they are created).  Returns ``(logits [B, card], cache)``."""
         c = self.c
         B = h_temporal.shape[0]
         nh, hd = c.dep_heads, c.dep_dim // c.dep_heads
         emb = ops.embed(prev_token.to(torch.int32), self.text_emb if t == 0 else self.audio_emb[t - 1])
         x = ops.linear(h_temporal, self.w_in[t]) + emb
-        new_cache = []
+        if cache is None:                                                              # one [B, steps, heads, dim] pair per layer, filled step by step
+            cache = [(x.new_empty(B, c.dep_q, nh, hd), x.new_empty(B, c.dep_q, nh, hd)) for _ in range(c.dep_layers)]
+        new_cache = cache
         for li in range(c.dep_layers):
-            h = ref.rmsnorm(x, self.norm1[li], c.eps)
+            h = ops.rmsnorm(x, self.norm1[li], c.eps)
             q, k, v = ops.linear(h, self.w_qkv[li, t]).view(B, 3, nh, hd).unbind(1)
-            if cache is not None:
-                k, v = torch.cat([cache[li][0], k[:, None]], 1), torch.cat([cache[li][1], v[:, None]], 1)
-            else:
-                k, v = k[:, None], v[:, None]
-            new_cache.append((k, v))                                                   # [B, t + 1, nh, hd]
-            s = torch.einsum("bhd,bthd->bht", q.float(), k.float()) * hd ** -0.5
-            a = torch.einsum("bht,bthd->bhd", torch.softmax(s, -1), v.float()).reshape(B, c.dep_dim).to(x.dtype)
-            x = x + ops.linear(a, self.w_o[li, t])
-            h = ref.rmsnorm(x, self.norm2[li], c.eps)
+            kc, vc = cache[li]
+            kc[:, t], vc[:, t] = k, v
+            a = torch.nn.functional.scaled_dot_product_attention(q[:, :, None], kc[:, :t + 1].transpose(1, 2), vc[:, :t + 1].transpose(1, 2))
+            x = x + ops.linear(a.reshape(B, c.dep_dim), self.w_o[li, t])
+            h = ops.rmsnorm(x, self.norm2[li], c.eps)
             x = x + ops.linear(ops.linear_glu(h, self.w_gu[li, t], "swiglu"), self.w_down[li, t])
         return ops.linear(x, self.heads[t]).float(), new_cache
 
