@@ -278,6 +278,9 @@ class LmGen(nn.Module):
             return None
         if self.pos >= self.c.context:
             raise RuntimeError("conversation longer than the attention context: start a new session")
+        if self.dev.type == "cuda" and sample is None and self.use_graph:
+            text_tok, audio = self._graph_frame(p)
+            return self.stream.commit(p, text_tok, audio)
         with torch.no_grad():
             x = self.embed_frame(p["input"])
             self.pos += 1
@@ -289,6 +292,65 @@ class LmGen(nn.Module):
             forced = [p["target"][1 + s] if p["provided"][1 + s] else None for s in range(self.c.dep_q)]
             audio = self.depformer.generate(h, next_text, forced, sample)[0]
         return self.stream.commit(p, int(text_tok[0]), [int(a) for a in audio])
+
+    use_graph = True
+    _gs = None
+
+    def _frame_device(self, st):
+        """The device side of one greedy frame over static buffers: batch descriptor from the device-resident frame counter,
+        stream embeddings, temporal step, text head, forced-or-sampled text token, depth chain; the counter advances at the end."""
+        n, meta, ps = st["n"], st["meta"], 16
+        meta.positions.copy_(n.to(torch.int32))
+        meta.kv_len.copy_((n + 1).to(torch.int32))
+        page = st["table"][0].index_select(0, n // ps)
+        meta.slot_mapping.copy_(page.long() * ps + n % ps)
+        t = st["tokens"]
+        e = ops.embed(t[:1], self.text_emb).float()
+        for s in range(self.c.dep_q):
+            e = e + ops.embed(t[1 + s:2 + s], self.audio_emb[s]).float()
+        h = self.temporal.hidden_from_embeds(e.to(self.text_emb.dtype), meta, self.cache)
+        text_tok = ref.argmax_first(ops.linear(h, self.text_head).float())
+        next_text = torch.where(st["fmask"][0], st["fval"][0], text_tok)
+        audio = self.depformer._chain(h, next_text, st["fmask"][1:], st["fval"][1:])
+        st["out"] = torch.cat([text_tok, audio[0]])
+        n.add_(1)
+
+    def _graph_frame(self, p):
+        """One frame as ONE graph replay: 17 token ids and the forced-token mask go up, 17 token ids come back."""
+        S = self.c.num_streams
+        if self._gs is None:
+            dev = self.dev
+            st = {"n": torch.zeros(1, dtype=torch.long, device=dev), "tokens": torch.zeros(S, dtype=torch.int32, device=dev),
+                  "fmask": torch.zeros(S, 1, dtype=torch.bool, device=dev), "fval": torch.zeros(S, 1, dtype=torch.long, device=dev),
+                  "table": torch.from_numpy(self.table).to(dev), "meta": BatchMeta.build([1], [self.c.context], self.table, 16, dev),
+                  "host": torch.zeros(3, S, dtype=torch.long).pin_memory()}
+            # the warm-up pass below writes the cache row of the current position; the first real frame overwrites it
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side), torch.no_grad():
+                st["n"].fill_(self.pos)
+                self._frame_device(st)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g), torch.no_grad():
+                self._frame_device(st)
+            st["graph"], st["n_host"] = g, -1
+            self._gs = st
+        st = self._gs
+        if st["n_host"] != self.pos:                                          # a new session, or frames taken by the eager path
+            st["n"].fill_(self.pos)
+        host = st["host"]
+        host[0] = torch.tensor(p["input"], dtype=torch.long)
+        host[1] = torch.tensor([1 if f else 0 for f in p["provided"]], dtype=torch.long)
+        host[2] = torch.tensor([int(v) if f else 0 for v, f in zip(p["target"], p["provided"])], dtype=torch.long)
+        st["tokens"].copy_(host[0], non_blocking=True)
+        st["fmask"].copy_(host[1].view(S, 1), non_blocking=True)
+        st["fval"].copy_(host[2].view(S, 1), non_blocking=True)
+        st["graph"].replay()
+        self.pos += 1
+        st["n_host"] = self.pos
+        out = st["out"].tolist()
+        return out[0], out[1:]
 
 
 def init_random_(m: LmGen, seed: int = 0, std: float = 0.08):

@@ -234,3 +234,29 @@ def test_moshi_depth_transformer_chain_as_a_cuda_graph_equals_the_eager_chain():
         assert torch.equal(got, want), (got, want)
         assert got.shape == (2, c.dep_q) and int(got.max()) < c.card
     assert len(d._graphs) == 1
+
+
+def test_moshi_whole_frame_as_one_cuda_graph_equals_the_eager_frames():
+    """Temporal step + text head + depth chain of a frame replayed as one graph (device-resident frame counter, batch descriptor
+    rebuilt on the device) against the eager path over the same conversation: same emitted frames."""
+    from mary_b200.models.moshi.model import LmGen, MoshiConfig
+    c = MoshiConfig(dim=256, layers=2, heads=4, ffn=256, context=64, text_card=96, card=128, dep_dim=128, dep_layers=2, dep_heads=2, dep_ffn=256,
+                    dep_q=8, codebooks_per_stream=4)
+    m = LmGen(c, torch.bfloat16, "cuda")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for n, p in m.named_parameters():
+        if p.dim() == 1 or n.endswith(("norm1", "norm2")):
+            p.data.fill_(1.0)
+        else:
+            p.data.normal_(0.0, 0.08, generator=g)
+    rng = torch.Generator().manual_seed(0)
+    user = [[int(x) for x in torch.randint(0, c.card, (c.codebooks_per_stream,), generator=rng)] for _ in range(14)]
+    runs = []
+    for flag in (False, True, True):
+        m.use_graph = flag
+        m.reset_session()
+        runs.append([m.step(user_audio=u, text=(7 if i == 5 else None)) for i, u in enumerate(user)])
+    assert m._gs is not None and runs[0][-1] is not None
+    assert runs[1] == runs[2]                                                  # a second session replays the same graph from position 0
+    same = sum(a == b for a, b in zip(runs[0], runs[1]))
+    assert same == len(user), (same, runs[0], runs[1])
