@@ -195,8 +195,22 @@ class SmolVLA(nn.Module):
         h = F.silu(ops.linear(torch.cat([a, te], -1), self.at_in_w, self.at_in_b))
         return ops.linear(h, self.at_out_w, self.at_out_b)
 
-    def denoise(self, cache, noisy, t):
-        """Flow velocity ``[chunk, action_dim]`` of the noised chunk at time ``t`` given the backbone's prefix cache."""
+    def cross_kv(self, cache):
+        """The cross-attention layers' key / value projections of the prefix: they do not depend on the flow time, so one
+        inference computes them once instead of once per Euler step."""
+        c, e = self.c, self.c.expert
+        out = {}
+        for i, L in enumerate(self.expert_layers):
+            if i % c.self_attn_every:
+                pk, pv = cache[i]
+                Lp = pk.shape[0]
+                out[i] = (ops.linear(pk.reshape(Lp, -1), L.wk).view(Lp, e.n_kv_heads, e.head_dim),
+                          ops.linear(pv.reshape(Lp, -1), L.wv).view(Lp, e.n_kv_heads, e.head_dim))
+        return out
+
+    def denoise(self, cache, noisy, t, cross=None):
+        """Flow velocity ``[chunk, action_dim]`` of the noised chunk at time ``t`` given the backbone's prefix cache (``cross``:
+        the result of :meth:`cross_kv` when the caller holds it)."""
         c, e = self.c, self.c.expert
         x = self.embed_suffix(noisy, t)
         Ls, Lp = x.shape[0], cache[0][0].shape[0]
@@ -213,8 +227,11 @@ class SmolVLA(nn.Module):
                 a = _attend(q, torch.cat([pk, k], 0), torch.cat([pv, val], 0), see_all)
             else:
                 q = _rope(ops.linear(h, L.wq).view(Ls, e.n_heads, e.head_dim), pos_cross, e.rope_theta)
-                k = ops.linear(pk.reshape(Lp, -1), L.wk).view(Lp, e.n_kv_heads, e.head_dim)
-                val = ops.linear(pv.reshape(Lp, -1), L.wv).view(Lp, e.n_kv_heads, e.head_dim)
+                if cross is not None:
+                    k, val = cross[i]
+                else:
+                    k = ops.linear(pk.reshape(Lp, -1), L.wk).view(Lp, e.n_kv_heads, e.head_dim)
+                    val = ops.linear(pv.reshape(Lp, -1), L.wv).view(Lp, e.n_kv_heads, e.head_dim)
                 a = _attend(q, k, val, see_all[:, :Lp])
             x = L.mlp(x + ops.linear(a, L.wo))
         return ops.linear(ops.rmsnorm(x, self.expert_norm, e.eps), self.act_out_w, self.act_out_b)
@@ -227,8 +244,45 @@ class SmolVLA(nn.Module):
         cache = self.prefix_cache(*self.embed_prefix(images, lang_ids, state))
         if noise is None:
             noise = torch.randn(c.chunk_size, c.action_dim, generator=generator, device=self.embed.device)
-        out = euler_sample(lambda x, t: self.denoise(cache, x[0], t[0])[None], noise[None].to(self.embed.dtype), c.num_steps)[0]
+        noise = noise.to(self.embed.dtype)
+        if noise.is_cuda and self.use_graph:
+            out = self._sample_graphed(cache, noise)
+        else:
+            cross = self.cross_kv(cache)
+            out = euler_sample(lambda x, t: self.denoise(cache, x[0], t[0], cross)[None], noise[None], c.num_steps)[0]
         return out[:, :c.expressive_dim]
+
+    use_graph = True
+
+    def _sample_graphed(self, cache, noise):
+        """The whole flow sampler (cross-attention projections of the prefix once, then ``num_steps`` Euler steps through all expert
+        layers) as one CUDA graph per prefix length: the prefix cache and the noise are copied into static buffers, the graph is
+        replayed, the chunk is read back.  The sampler is thousands of small dependent kernels, so its cost is launch submission."""
+        c = self.c
+        Lp = cache[0][0].shape[0]
+        graphs = self.__dict__.setdefault("_graphs", {})
+        if Lp not in graphs:
+            st = {"cache": [(k.clone(), v.clone()) for k, v in cache], "noise": noise.clone()}
+
+            def run():
+                cross = self.cross_kv(st["cache"])
+                return euler_sample(lambda x, t: self.denoise(st["cache"], x[0], t[0], cross)[None], st["noise"][None], c.num_steps)[0]
+            side = torch.cuda.Stream(device=noise.device)
+            side.wait_stream(torch.cuda.current_stream(noise.device))
+            with torch.cuda.stream(side):
+                run()
+            torch.cuda.current_stream(noise.device).wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                st["out"] = run()
+            st["graph"] = g
+            graphs[Lp] = st
+        st = graphs[Lp]
+        for (sk, sv), (k, v) in zip(st["cache"], cache):
+            sk.copy_(k), sv.copy_(v)
+        st["noise"].copy_(noise)
+        st["graph"].replay()
+        return st["out"].clone()
 
     def flow_loss(self, cache, actions, noise, t):
         """Training objective of the expert: ``x_t = t noise + (1 - t) actions``; target velocity ``noise - actions``; mean squared error."""

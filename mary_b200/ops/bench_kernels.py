@@ -320,6 +320,40 @@ def bench_speechlm(frames: int = 40):
           f"per 80 ms frame = {80.0 / wall:.1f}x real time")
 
 
+def bench_vla(iters: int = 10):
+    """SmolVLA at its released size (SigLIP 12 x 768 at 512 px, backbone 16 x 960, action expert 16 x 720, 10 Euler steps over a chunk of
+    50 actions): one ``act`` call eager against the one-graph flow sampler."""
+    from ..models.smolvla import SmolVLA, SmolVLAConfig
+    c = SmolVLAConfig()
+    m = SmolVLA(c)
+    for p in m.parameters():
+        p.data = p.data.to("cuda", torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for n, p in m.named_parameters():
+        if p.dim() == 1:
+            p.data.fill_(0.0 if (n.endswith("_b") or "b_" in n.split(".")[-1]) else 1.0)
+        else:
+            p.data.normal_(0.0, 0.02, generator=g)
+    img = (torch.rand(3, c.image_size, c.image_size, device="cuda") * 2 - 1).to(torch.bfloat16)
+    state, noise = torch.randn(c.state_dim, device="cuda"), torch.randn(c.chunk_size, c.action_dim, device="cuda")
+    ids = list(range(3, 51))
+    out = {}
+    for name, flag in (("eager", False), ("graph", True)):
+        m.use_graph = flag
+        for _ in range(2):
+            m.act([img], ids, state, noise=noise)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            m.act([img], ids, state, noise=noise)
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = a.elapsed_time(b) / iters
+    print(f"smolvla act (1 image, 48 language tokens, {c.num_steps} Euler steps x {c.expert.n_layers} expert layers): eager {out['eager']:.2f} ms, "
+          f"flow sampler as one graph {out['graph']:.2f} ms per call ({out['eager'] / out['graph']:.2f}x)")
+
+
 def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5):
     """One expert-parallel MoE layer in all-to-all mode with all ranks on this device, phase by phase (the barriers between
     the phases are stream order here): the per-rank cost of counts, plan + dispatch, expert GEMMs and the weighted sum at the
@@ -381,6 +415,8 @@ if __name__ == "__main__":
         bench_depformer(*nums)
     if what == "speechlm":
         bench_speechlm(*nums)
+    if what == "vla":
+        bench_vla(*nums)
     if what == "ep":
         bench_ep(*nums)
     if what in ("moe", "all"):

@@ -260,3 +260,21 @@ def test_moshi_whole_frame_as_one_cuda_graph_equals_the_eager_frames():
     assert runs[1] == runs[2]                                                  # a second session replays the same graph from position 0
     same = sum(a == b for a, b in zip(runs[0], runs[1]))
     assert same == len(user), (same, runs[0], runs[1])
+
+
+def test_smolvla_flow_sampler_as_a_cuda_graph_equals_the_eager_sampler():
+    from mary_b200.models.smolvla import SmolVLA, SmolVLAConfig, TowerConfig
+    c = SmolVLAConfig(vlm=TowerConfig(128, 2, 2, 1, 64, 256), expert=TowerConfig(64, 2, 2, 1, 64, 128), vocab=100, image_size=32, patch=8,
+                      v_hidden=64, v_layers=1, v_heads=2, v_ffn=128, shuffle=2, action_dim=8, state_dim=8, expressive_dim=3, chunk_size=8, num_steps=4)
+    sg = _gpu(_init(SmolVLA(c), std=0.08))
+    for trial in range(3):
+        img = (torch.rand(3, 32, 32) * 2 - 1).cuda().bfloat16()
+        state, noise = torch.randn(8).cuda(), torch.randn(8, 8).cuda()
+        sg.use_graph = False
+        want = sg.act([img], [3, 4, 5], state, noise=noise)
+        sg.use_graph = True
+        got = sg.act([img], [3, 4, 5], state, noise=noise)
+        assert torch.equal(got, want) and got.shape == (8, 3) and torch.isfinite(got).all()
+    assert len(sg._graphs) == 1
+    sg.act([img], [3, 4, 5, 6, 7], state, noise=noise)                         # a longer prompt is a new prefix length: its own graph
+    assert len(sg._graphs) == 2
