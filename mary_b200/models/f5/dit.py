@@ -109,7 +109,7 @@ class DiT(nn.Module):
         """Scalar flow time -> ``[dim]``: sinusoid(1000 t) of ``time_freq`` -> Linear, SiLU, Linear."""
         half = self.c.time_freq // 2
         f = torch.exp(torch.arange(half, dtype=torch.float32, device=self.t1_w.device) * (-math.log(10000.0) / (half - 1)))
-        e = 1000.0 * float(t) * f
+        e = 1000.0 * t.float() * f if (torch.is_tensor(t) and t.is_cuda) else 1000.0 * float(t) * f      # a device scalar stays on the device
         e = torch.cat([e.sin(), e.cos()])[None].to(self.t1_w.dtype)
         return ops.linear(F.silu(ops.linear(e, self.t1_w, self.t1_b)), self.t2_w, self.t2_b)[0]
 
@@ -129,13 +129,15 @@ class DiT(nn.Module):
             x = b(x)
         return x
 
-    def forward(self, x, cond, text_ids, t, drop_cond: bool = False, drop_text: bool = False):
-        """Velocity ``[T, n_mels]`` at flow time ``t`` for the noised mel ``x [T, n_mels]`` and reference mel ``cond [T, n_mels]``."""
+    def forward(self, x, cond, text_ids, t, drop_cond: bool = False, drop_text: bool = False, text=None):
+        """Velocity ``[T, n_mels]`` at flow time ``t`` for the noised mel ``x [T, n_mels]`` and reference mel ``cond [T, n_mels]``.
+        ``text``: the result of :meth:`text_features` when the caller holds it (it depends on neither ``x`` nor ``t``)."""
         c = self.c
         T, D, nh = x.shape[0], c.dim, c.heads
         te = self.time_code(t)
         cond = torch.zeros_like(cond) if drop_cond else cond
-        h = ops.linear(torch.cat([x, cond, self.text_features(text_ids, T, drop_text)], -1).to(self.in_w.dtype), self.in_w, self.in_b)
+        tf = self.text_features(text_ids, T, drop_text) if text is None else text
+        h = ops.linear(torch.cat([x, cond, tf], -1).to(self.in_w.dtype), self.in_w, self.in_b)
         p = F.mish(F.conv1d(h.T[None], self.pos1_w, self.pos1_b, padding=c.pos_kernel // 2, groups=c.pos_groups))
         p = F.mish(F.conv1d(p, self.pos2_w, self.pos2_b, padding=c.pos_kernel // 2, groups=c.pos_groups))[0].T
         h = h + p
@@ -169,24 +171,50 @@ class CFM:
     def __init__(self, model: DiT, nfe: int = 32, cfg_strength: float = 2.0, sway: float | None = -1.0):
         self.model, self.nfe, self.cfg, self.sway = model, nfe, cfg_strength, sway
 
-    def velocity(self, x, cond, text_ids, t):
-        v = self.model(x, cond, text_ids, t)
+    def velocity(self, x, cond, text_ids, t, feats=None):
+        tf, tf_drop = feats if feats is not None else (None, None)
+        v = self.model(x, cond, text_ids, t, text=tf)
         if self.cfg < 1e-5:
             return v
-        return v + (v - self.model(x, cond, text_ids, t, drop_cond=True, drop_text=True)) * self.cfg
+        return v + (v - self.model(x, cond, text_ids, t, drop_cond=True, drop_text=True, text=tf_drop)) * self.cfg
+
+    use_graph = True
 
     @torch.no_grad()
     def sample(self, ref_mel, text_ids, total_frames: int, noise=None, generator=None):
         """``ref_mel [T_ref, n_mels]`` + the characters of reference and target -> mel ``[total_frames, n_mels]`` whose first ``T_ref``
-        frames are the reference and the rest the generated speech."""
+        frames are the reference and the rest the generated speech.  The text features (conditioned and dropped) are computed once
+        per utterance.  On the GPU ONE Euler step (both guidance passes through all blocks, a few hundred small kernels) is
+        captured as a CUDA graph whose flow time comes from a device-resident table and counter, and replayed ``nfe`` times."""
         n_mels = self.model.c.n_mels
         T_ref = ref_mel.shape[0]
         cond = torch.zeros(total_frames, n_mels, dtype=ref_mel.dtype, device=ref_mel.device)
         cond[:T_ref] = ref_mel
-        x = torch.randn(total_frames, n_mels, generator=generator).to(ref_mel) if noise is None else noise
+        x = torch.randn(total_frames, n_mels, generator=generator).to(ref_mel) if noise is None else noise.clone()
         ts = sway_times(self.nfe, self.sway)
-        for i in range(self.nfe):
-            x = x + (ts[i + 1] - ts[i]) * self.velocity(x, cond, text_ids, ts[i])
+        feats = (self.model.text_features(text_ids, total_frames), self.model.text_features(text_ids, total_frames, True))
+        if x.is_cuda and self.use_graph:
+            tdev, i = ts.to(x.device), torch.zeros(1, dtype=torch.long, device=x.device)
+
+            def step():
+                t0, t1 = tdev.index_select(0, i)[0], tdev.index_select(0, i + 1)[0]
+                x.add_(((t1 - t0) * self.velocity(x, cond, text_ids, t0, feats)).to(x.dtype))
+                i.add_(1)
+            keep = x.clone()
+            side = torch.cuda.Stream(device=x.device)
+            side.wait_stream(torch.cuda.current_stream(x.device))
+            with torch.cuda.stream(side):
+                step()                                              # warm-up outside the graph; undone below
+            torch.cuda.current_stream(x.device).wait_stream(side)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step()
+            x.copy_(keep), i.zero_()
+            for _ in range(self.nfe):
+                g.replay()
+        else:
+            for i in range(self.nfe):
+                x = x + (ts[i + 1] - ts[i]) * self.velocity(x, cond, text_ids, ts[i], feats)
         x[:T_ref] = ref_mel
         return x
 

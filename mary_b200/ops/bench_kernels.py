@@ -354,6 +354,40 @@ def bench_vla(iters: int = 10):
           f"flow sampler as one graph {out['graph']:.2f} ms per call ({out['eager'] / out['graph']:.2f}x)")
 
 
+def bench_f5(frames: int = 800, nfe: int = 32):
+    """F5-TTS flow sampler at the released size (DiT 22 x 1024, classifier-free guidance = two passes per step): one utterance of
+    ``frames`` mel frames, eager against the replayed one-step graph (capture included in the timed call)."""
+    from ..models.f5 import CFM, DiT, F5Config
+    c = F5Config()
+    d = DiT(c)
+    for p in d.parameters():
+        p.data = p.data.to("cuda", torch.bfloat16)
+    for k, b in list(d._buffers.items()):
+        d._buffers[k] = b.to("cuda")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for n, p in d.named_parameters():
+        p.data.normal_(0.0, 0.02, generator=g)
+    ref_mel = torch.randn(frames // 3, c.n_mels, device="cuda").to(torch.bfloat16)
+    noise = torch.randn(frames, c.n_mels, device="cuda").to(torch.bfloat16)
+    ids = [int(x) % (c.text_vocab - 1) for x in range(120)]
+    cfm = CFM(d, nfe=nfe)
+    out = {}
+    for name, flag in (("eager", False), ("graph", True)):
+        cfm.use_graph = flag
+        cfm.sample(ref_mel, ids, frames, noise=noise)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            cfm.sample(ref_mel, ids, frames, noise=noise)
+        b.record()
+        torch.cuda.synchronize()
+        out[name] = a.elapsed_time(b) / 3
+    secs = (frames - frames // 3) * 256 / 24000
+    print(f"f5 flow sampler ({frames} frames, {nfe} steps x 2 guidance passes x {c.depth} blocks): eager {out['eager']:.1f} ms, one-step graph "
+          f"{out['graph']:.1f} ms per utterance ({out['eager'] / out['graph']:.2f}x); {secs:.1f} s of generated speech")
+
+
 def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5):
     """One expert-parallel MoE layer in all-to-all mode with all ranks on this device, phase by phase (the barriers between
     the phases are stream order here): the per-rank cost of counts, plan + dispatch, expert GEMMs and the weighted sum at the
@@ -417,6 +451,8 @@ if __name__ == "__main__":
         bench_speechlm(*nums)
     if what == "vla":
         bench_vla(*nums)
+    if what == "f5":
+        bench_f5(*nums)
     if what == "ep":
         bench_ep(*nums)
     if what in ("moe", "all"):

@@ -278,3 +278,17 @@ def test_smolvla_flow_sampler_as_a_cuda_graph_equals_the_eager_sampler():
     assert len(sg._graphs) == 1
     sg.act([img], [3, 4, 5, 6, 7], state, noise=noise)                         # a longer prompt is a new prefix length: its own graph
     assert len(sg._graphs) == 2
+
+
+def test_f5_flow_sampler_with_a_graphed_euler_step_matches_the_eager_sampler():
+    from mary_b200.models.f5 import CFM, DiT, F5Config
+    d = _gpu(_init(DiT(F5Config(dim=128, depth=2, heads=2, n_mels=16, text_vocab=40, text_dim=64, conv_layers=1, pos_kernel=7, pos_groups=4, time_freq=32)), std=0.08))
+    ref_mel = torch.randn(10, 16).cuda().bfloat16()
+    noise = torch.randn(24, 16).cuda().bfloat16()
+    cfm = CFM(d, nfe=6, cfg_strength=2.0)
+    cfm.use_graph = False
+    want = cfm.sample(ref_mel, [1, 2, 3, 4], 24, noise=noise)
+    cfm.use_graph = True
+    got = cfm.sample(ref_mel, [1, 2, 3, 4], 24, noise=noise)
+    assert torch.equal(got[:10], ref_mel) and torch.isfinite(got).all()
+    _close(got, want, 0.03)
