@@ -193,7 +193,7 @@ def test_vocab_parallel_head_matches_full_argmax_and_samples_inside_top_k():
         assert seen <= set(top5[r].tolist()) and len(seen) >= 2  # draws stay inside the global top-k and do vary
 
 
-def _cp_worker(rank, world, port, out):
+def _cp_worker(rank, world, port, out, zigzag=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -219,7 +219,7 @@ def _cp_worker(rank, world, port, out):
     with torch.no_grad():
         want = m(ids, BatchMeta.build([n], lens, table, 16), cache)
     tp = _NoTP()
-    tp.cp = ContextParallel(rank, world)
+    tp.cp = ContextParallel(rank, world, zigzag=zigzag)
     for layer in m.layers:
         layer.tp = tp
     m.tp = tp
@@ -228,8 +228,12 @@ def _cp_worker(rank, world, port, out):
     with torch.no_grad():
         mine = m(tp.cp.rows(ids), meta, cache)
         got = tp.cp.gather_rows(mine)
-    lo, hi = tp.cp.bounds[rank]
-    out.put((rank, float((got - want).abs().max()), mine.shape[0] == hi - lo, float((mine - want[lo:hi]).abs().max())))
+    if zigzag:
+        idx = torch.cat([torch.arange(a, b) for a, b in (tp.cp.chunks[c] for c in tp.cp.my_chunks())])
+        out.put((rank, float((got - want).abs().max()), mine.shape[0] == len(idx), float((mine - want[idx]).abs().max())))
+    else:
+        lo, hi = tp.cp.bounds[rank]
+        out.put((rank, float((got - want).abs().max()), mine.shape[0] == hi - lo, float((mine - want[lo:hi]).abs().max())))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -245,6 +249,36 @@ def test_context_parallel_prefill_equals_the_single_rank_prefill():
     [p.join(60) for p in ps]
     for rank, err_all, rows_ok, err_mine in res:
         assert rows_ok and err_all < 1e-5 and err_mine < 1e-5, res
+
+
+def test_zigzag_context_parallel_prefill_equals_the_single_rank_prefill():
+    """Rank r takes chunks r and 2 * world - 1 - r of the prompt (two batch entries on one page-table row): same logits as one rank,
+    and every rank attends to the same number of half-chunks."""
+    world = 3
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_cp_worker, args=(r, world, port, out, True)) for r in range(world)]
+    [p.start() for p in ps]
+    res = sorted(out.get(timeout=120) for _ in range(world))
+    [p.join(60) for p in ps]
+    for rank, err_all, rows_ok, err_mine in res:
+        assert rows_ok and err_all < 1e-5 and err_mine < 1e-5, res
+    from mary_b200.parallel.cp import ContextParallel
+    import numpy as np
+    work = []
+    for r in range(4):
+        cp = ContextParallel(r, 4, zigzag=True)
+        cp.begin(4096, np.arange(256, dtype=np.int32)[None], 16)
+        work.append(sum((b - a) * (a + b) / 2 for a, b in (cp.chunks[c] for c in cp.my_chunks())))      # keys seen, summed over the rank's queries
+    assert max(work) / min(work) < 1.01
+    flat = []
+    for r in range(4):
+        cp = ContextParallel(r, 4)
+        cp.begin(4096, np.arange(256, dtype=np.int32)[None], 16)
+        a, b = cp.bounds[r]
+        flat.append((b - a) * (a + b) / 2)
+    assert max(flat) / min(flat) > 6                                    # the contiguous layout: the last rank does 7x the first rank's attention
 
 
 def _cp_mla_worker(rank, world, port, out):
