@@ -126,8 +126,9 @@ def main():
     ap.add_argument("--replicated-head", action="store_true", help="keep the whole LM head on every rank (default: vocabulary-parallel head)")
     ap.add_argument("--no-ttft", action="store_true")
     ap.add_argument("--ttft-limit", type=float, default=150.0, help="seconds after which a stalled TTFT measurement is abandoned")
-    ap.add_argument("--ttft-layout", default="cp", choices=["cp", "each"],
-                    help="all-to-all layout only: cp = one context with its rows split over the ranks, each = every rank prefills its own context")
+    ap.add_argument("--ttft-layout", default="cp", choices=["cp", "zigzag", "each"],
+                    help="all-to-all layout only: cp = one context with its rows split over the ranks (contiguous chunks), zigzag = the same with "
+                         "load-balanced chunk pairs (not yet measured on GPUs), each = every rank prefills its own context")
     ap.add_argument("--prefill-chunk", type=int, default=4096, help="tokens per prefill chunk of the TTFT measurement")
     ap.add_argument("--trace", action="store_true", help="print a per-op device-time table of one eager step and exit")
     ap.add_argument("--profile-step", action="store_true",
@@ -401,7 +402,31 @@ def main():
                               device=dev, latent_dim=spec.get("latent_dim"))
             prompt = rng.integers(0, cfg.vocab_size, (1, ctx))
             ts = []
-            if a2a and args.ttft_layout == "cp":
+            if a2a and args.ttft_layout == "zigzag":
+                # the same context-parallel prefill with load-balanced chunks: rank r takes chunks r and 2 * world - 1 - r of the prompt
+                from mary_b200.parallel.cp import ContextParallel
+                cp = ContextParallel(rank, world, zigzag=True)
+                par.cp = cp
+                pc.alloc.extend(0, ctx)
+                table, _ = pc.alloc.page_table([0])
+                ids_all = torch.as_tensor(prompt[0], dtype=torch.int32, device=dev)
+                for _ in range(3):
+                    barrier()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    with torch.no_grad():
+                        meta = cp.begin(ctx, table, page, device=dev)
+                        idx = torch.cat([torch.arange(lo, hi, device=dev) for lo, hi in (cp.chunks[c] for c in cp.my_chunks())])
+                        tok, h = model.verify(ids_all[idx], meta, pc)
+                        if k:
+                            nxt = torch.where(idx + 1 < ctx, ids_all[(idx + 1).clamp_max(ctx - 1)], tok[-1].to(torch.int32))
+                            model.draft(0, h, nxt, meta, pc)
+                    cp.end()
+                    b.record()
+                    barrier()
+                    ts.append(a.elapsed_time(b))
+                ttft_note = f"one context, rows split over {world} ranks in zigzag chunks (context-parallel prefill)"
+            elif a2a and args.ttft_layout == "cp":
                 # data-parallel attention + expert-parallel all-to-all: ONE context, its rows cut into contiguous chunks, one per rank
                 # (context parallelism: after every layer's cache append the earlier chunks' latent rows are gathered into the local
                 # cache, attention stays a local kernel); the time is that of the slowest rank, which holds the last chunk

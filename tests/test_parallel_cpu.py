@@ -281,7 +281,7 @@ def test_zigzag_context_parallel_prefill_equals_the_single_rank_prefill():
     assert max(flat) / min(flat) > 6                                    # the contiguous layout: the last rank does 7x the first rank's attention
 
 
-def _cp_mla_worker(rank, world, port, out):
+def _cp_mla_worker(rank, world, port, out, zigzag=False):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     import torch.distributed as dist
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -303,17 +303,17 @@ def _cp_mla_worker(rank, world, port, out):
     cache, (table, lens) = fresh()
     with torch.no_grad():
         want_tok, want_h = m.verify(ids, BatchMeta.build([n], lens, table, 16), cache)
-    cp = ContextParallel(rank, world)
+    cp = ContextParallel(rank, world, zigzag=zigzag)
     m.par.cp = cp
     cache, (table, lens) = fresh()
     meta = cp.begin(n, table, 16)
     with torch.no_grad():
         tok, h = m.verify(cp.rows(ids), meta, cache)
     cp.end()
-    lo, hi = cp.bounds[rank]
+    idx = torch.cat([torch.arange(a, b) for a, b in (cp.chunks[c] for c in cp.my_chunks())]) if zigzag else torch.arange(*cp.bounds[rank])
     # routing is discontinuous: judge rows individually, as the tensor-parallel tests do
-    row_err = (h - want_h[lo:hi]).abs().amax(-1) / want_h.abs().max()
-    out.put((rank, float((row_err < 1e-3).float().mean()), float((tok == want_tok[lo:hi]).float().mean())))
+    row_err = (h - want_h[idx]).abs().amax(-1) / want_h.abs().max()
+    out.put((rank, float((row_err < 1e-3).float().mean()), float((tok == want_tok[idx]).float().mean())))
     # outside begin() .. end() the hook is inert: a plain decode step of one row runs without any collective
     cache.alloc.extend(0, 1)
     table, lens = cache.alloc.page_table([0])
@@ -323,12 +323,13 @@ def _cp_mla_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_context_parallel_prefill_of_the_latent_attention_decoder():
+@pytest.mark.parametrize("zigzag", [False, True])
+def test_context_parallel_prefill_of_the_latent_attention_decoder(zigzag):
     world = 2
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
     port = _free_port()
-    ps = [ctx.Process(target=_cp_mla_worker, args=(r, world, port, out)) for r in range(world)]
+    ps = [ctx.Process(target=_cp_mla_worker, args=(r, world, port, out, zigzag)) for r in range(world)]
     [p.start() for p in ps]
     res = sorted(out.get(timeout=180) for _ in range(world))
     [p.join(60) for p in ps]
