@@ -167,6 +167,40 @@ def cmd_k3_experts(a) -> int:
     return 0
 
 
+def cmd_fit(a) -> int:
+    """Does a sparse-MoE serving configuration fit the GPUs (the question ``gemma31b_fit`` / ``resident_final`` answer by allocating)?
+    Prints the per-GPU bill — expert slabs, attention / dense / head weights, paged KV cache for ``batch x ctx`` tokens, activations,
+    workspace — against the capacity, and how many expert slabs can stay resident when not all do."""
+    from ..models.moe.config import inkling_style_config, k3_class_config
+    from ..runtime.budget import AdmissionError, check, moe_bill
+    cfg = {"k3": k3_class_config, "inkling": inkling_style_config}[a.model]()
+    cap = int(a.capacity_gib * 2 ** 30)
+    n_moe = sum(1 for i in range(cfg.num_hidden_layers) if not cfg.is_dense(i)) + cfg.num_mtp_layers
+    rc = 0
+    for world in [int(x) for x in a.gpus.split(",")]:
+        # from 4 GPUs up the serving layout is data-parallel attention + all-to-all experts: a rank caches only its own sequences
+        local = a.batch // world if (world >= 4 and not a.replicated_kv) else a.batch
+        bill = moe_bill(cfg, world, local, a.ctx, local * (1 + a.spec), cap)
+        try:
+            check(bill)
+            print(f"{world} GPU(s): fits, all {n_moe} expert slabs resident: {bill.lines()}")
+            continue
+        except AdmissionError:
+            pass
+        slabs = n_moe
+        while slabs > 0:
+            b = moe_bill(cfg, world, local, a.ctx, local * (1 + a.spec), cap, expert_slabs=slabs)
+            if b.total <= cap * 0.97:
+                break
+            slabs -= 1
+        if slabs:
+            print(f"{world} GPU(s): fits only with {slabs} of {n_moe} expert slabs resident (the rest are streamed or shared): {b.lines()}")
+        else:
+            print(f"{world} GPU(s): does NOT fit even with one resident slab: {bill.lines()}")
+            rc = 1
+    return rc
+
+
 def cmd_encode(a) -> int:
     """Text on stdin, an ids file out (``inkling_encode``): stdin is taken VERBATIM (leading space and trailing bytes included; use
     ``printf '%s'``, not ``echo``); ids go out as little-endian i64, the form the serving CLI reads; the decode round trip is printed
@@ -227,6 +261,12 @@ def main(argv=None) -> int:
     ke = sub.add_parser("k3-experts")
     ke.add_argument("dir"), ke.add_argument("--sweep", default="1,4,16"), ke.add_argument("--per-level", type=int, default=32)
     ke.set_defaults(fn=cmd_k3_experts)
+    ft = sub.add_parser("fit")
+    ft.add_argument("--model", default="k3", choices=["k3", "inkling"]), ft.add_argument("--gpus", default="1,2,4,8")
+    ft.add_argument("--batch", type=int, default=128), ft.add_argument("--ctx", type=int, default=4160), ft.add_argument("--spec", type=int, default=2)
+    ft.add_argument("--capacity-gib", type=float, default=178.0)
+    ft.add_argument("--replicated-kv", action="store_true", help="every rank caches all sequences (tensor-parallel attention) at any GPU count")
+    ft.set_defaults(fn=cmd_fit)
     en = sub.add_parser("encode")
     en.add_argument("out"), en.add_argument("--pile"), en.add_argument("--tokenizer"), en.add_argument("--tokenizer-json")
     en.set_defaults(fn=cmd_encode)

@@ -256,3 +256,11 @@ def test_encode_writes_little_endian_i64_and_prints_the_round_trip(tmp_path, cap
     ids = np.fromfile(tmp_path / "p.ids", dtype="<i8")
     assert ids.tolist() == [1, 2, 3, 4, 5]
     assert "decode: ' The capital of France is'" in capsys.readouterr().out
+
+
+def test_fit_reports_resident_slabs_per_gpu_count(capsys):
+    from mary_b200.cli.mary import main
+    assert main(["fit", "--model", "k3", "--gpus", "1,8"]) == 0
+    out = capsys.readouterr().out.splitlines()
+    assert "fits only with" in out[0] and "of 61 expert slabs" in out[0] and "8 GPU(s): fits, all 61 expert slabs resident" in out[1]
+    assert main(["fit", "--model", "k3", "--gpus", "1", "--capacity-gib", "20"]) == 1
