@@ -16,6 +16,23 @@ def _free_port():
     return p
 
 
+def _once_more(test):
+    """Multi-process tests rendezvous on a port that was free a moment ago and wait on queues with a time limit: one retry with a
+    fresh port absorbs a lost race for the port or a slow start of the child interpreters on a loaded machine."""
+    import functools
+
+    @functools.wraps(test)
+    def run(*a, **kw):
+        try:
+            return test(*a, **kw)
+        except Exception:
+            for child in mp.active_children():                      # ranks of the failed attempt must not outlive it
+                child.terminate()
+                child.join(10)
+            return test(*a, **kw)
+    return run
+
+
 def _logits(model, ids, n):
     from mary_b200.runtime.batch import BatchMeta
     from mary_b200.runtime.kv_cache import PagedKVCache
@@ -59,6 +76,7 @@ def _worker(rank, world, port, attention, out, shared_fp4=False):
 
 
 @pytest.mark.parametrize("attention,shared_fp4", [("mla", False), ("gqa", False), ("mla", True)])
+@_once_more
 def test_tp_ep_two_cpu_ranks_match_single_rank(attention, shared_fp4):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -139,6 +157,7 @@ def _pp_worker(rank, world, port, cohorts, out):
 
 
 @pytest.mark.parametrize("cohorts", [1, 3])
+@_once_more
 def test_layer_pipeline_two_stages_with_cohorts_matches_single_process(cohorts):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -172,6 +191,7 @@ def _vocab_worker(rank, world, port, out):
         dist.destroy_process_group()
 
 
+@_once_more
 def test_vocab_parallel_head_matches_full_argmax_and_samples_inside_top_k():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -238,6 +258,7 @@ def _cp_worker(rank, world, port, out, zigzag=False):
     dist.destroy_process_group()
 
 
+@_once_more
 def test_context_parallel_prefill_equals_the_single_rank_prefill():
     world = 3
     ctx = mp.get_context("spawn")
@@ -251,6 +272,7 @@ def test_context_parallel_prefill_equals_the_single_rank_prefill():
         assert rows_ok and err_all < 1e-5 and err_mine < 1e-5, res
 
 
+@_once_more
 def test_zigzag_context_parallel_prefill_equals_the_single_rank_prefill():
     """Rank r takes chunks r and 2 * world - 1 - r of the prompt (two batch entries on one page-table row): same logits as one rank,
     and every rank attends to the same number of half-chunks."""
@@ -324,6 +346,7 @@ def _cp_mla_worker(rank, world, port, out, zigzag=False):
 
 
 @pytest.mark.parametrize("zigzag", [False, True])
+@_once_more
 def test_context_parallel_prefill_of_the_latent_attention_decoder(zigzag):
     world = 2
     ctx = mp.get_context("spawn")
