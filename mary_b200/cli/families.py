@@ -4,6 +4,7 @@
     families listen    --pile P --model voxtral --wav a.wav [--delay 6]                                                  (``voxtral_listen``)
     families embed     --pile P --model clip|siglip|nomic --kind clip|siglip|nomic|nomic-vision [--image i.npy] [--ids 1,2,3]         (``local_demo``, ``embed_persist``)
     families imagine   --pile P --transformer T --vae V --features f.npy --out img.npy [--steps 4] [--seed 0]            (the FLUX.2 pipeline)
+    families rank      --pile P --model nomic --kind nomic --queries "1,2;3,4" --docs "5,6;1,2"                             (``nomic_semantic_probe``, ``embed_bakeoff``)
     families act       --pile P --model smolvla --image i.npy --ids 1,2,3 --state s.npy                                  (``smolvla_infer``)
     families hear      --pile P --model gemma-audio --wav a.wav [--ids 2,.. --ids-after ..]                              (``gemma_hear`` / ``gemma_listen``)
     families speak     --random --ids 5,6,7 --out o.wav                                                                  (``speak`` / ``qwen3tts_say|stream``)
@@ -141,6 +142,30 @@ def cmd_embed(a) -> int:
         else:
             v = m.embed_text(torch.tensor([[int(x) for x in a.ids.split(",")]]))[0]
     print(" ".join(f"{x:.6f}" for x in v.tolist()))
+    return 0
+
+
+def cmd_rank(a) -> int:
+    """Semantic probe (``nomic_semantic_probe`` / ``embed_bakeoff``): embed queries and documents (token-id lists separated by ``;``,
+    or images as ``.npy`` files for the image arm), print for every query the documents by descending cosine similarity."""
+    from ..models import embed as E
+    kinds = {"clip": (E.ClipConfig, E.ClipEmbedder, E.clip.load_into), "siglip": (E.SiglipConfig, E.SiglipEmbedder, E.siglip.load_into),
+             "nomic": (E.NomicConfig, E.NomicTextEmbedder, E.nomic.load_into)}
+    Cfg, Model, load = kinds[a.kind]
+    m = Model(Cfg.tiny() if a.random else Cfg())
+    _random_init(m) if a.random else load(m, _loader(a.pile, a.model))
+
+    def embed(item: str):
+        with torch.no_grad():
+            if item.endswith(".npy"):
+                return m.embed_image(m.preprocess(torch.from_numpy(np.load(item)).float())[None])[0]
+            return m.embed_text(torch.tensor([[int(x) for x in item.split(",")]]))[0]
+    q = torch.stack([embed(x) for x in a.queries.split(";")])
+    d = torch.stack([embed(x) for x in a.docs.split(";")])
+    sim = q @ d.T
+    for i, row in enumerate(sim):
+        order = torch.argsort(row, descending=True)
+        print(f"query {i}: " + " ".join(f"{int(j)}:{float(row[j]):.4f}" for j in order))
     return 0
 
 
@@ -316,6 +341,10 @@ def main(argv=None) -> int:
     e = common(sub.add_parser("embed"))
     e.add_argument("--kind", required=True, choices=["clip", "siglip", "nomic", "nomic-vision"]), e.add_argument("--image"), e.add_argument("--ids")
     e.set_defaults(fn=cmd_embed)
+    rk = common(sub.add_parser("rank"))
+    rk.add_argument("--kind", required=True, choices=["clip", "siglip", "nomic"]), rk.add_argument("--queries", required=True)
+    rk.add_argument("--docs", required=True)
+    rk.set_defaults(fn=cmd_rank)
     im = common(sub.add_parser("imagine"))
     im.add_argument("--transformer"), im.add_argument("--vae"), im.add_argument("--features", required=True), im.add_argument("--out", required=True)
     im.add_argument("--height", type=int, default=1024), im.add_argument("--width", type=int, default=1024), im.add_argument("--steps", type=int, default=4)

@@ -108,3 +108,11 @@ def test_say_serve_answers_one_request_per_line_with_warm_weights(tmp_path, caps
     a, _ = families.read_wav(str(tmp_path / "a.wav"))
     b, _ = families.read_wav(str(tmp_path / "b.wav"))
     assert len(a) > len(b) > 0                                      # duration follows the character ratio
+
+
+def test_rank_orders_documents_by_cosine_and_puts_the_identical_text_first(capsys):
+    assert families.main(["rank", "--random", "--kind", "nomic", "--queries", "4,5,6;9,8", "--docs", "1,2,3;4,5,6;9,8"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert lines[0].startswith("query 0: 1:1.0000") and lines[1].startswith("query 1: 2:1.0000")
+    sims = [float(x.split(":")[1]) for x in lines[0].split()[2:]]
+    assert sims == sorted(sims, reverse=True)
