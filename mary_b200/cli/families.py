@@ -7,7 +7,7 @@
     families rank      --pile P --model nomic --kind nomic --queries "1,2;3,4" --docs "5,6;1,2"                             (``nomic_semantic_probe``, ``embed_bakeoff``)
     families act       --pile P --model smolvla --image i.npy --ids 1,2,3 --state s.npy                                  (``smolvla_infer``)
     families hear      --pile P --model gemma-audio --wav a.wav [--ids 2,.. --ids-after ..]                              (``gemma_hear`` / ``gemma_listen``)
-    families speak     --random --ids 5,6,7 --out o.wav                                                                  (``speak`` / ``qwen3tts_say|stream``)
+    families speak     --pile P --model qwen3tts --codec codec --ids 5,6,7 --out o.wav                                                            (``speak`` / ``qwen3tts_say|stream``)
     families converse  --pile P --model moshi --codec mimi --wav in.wav --out agent.wav                                                       (``personaplex_listen``)
 
 Checkpoints get into a pile with ``mary import`` (the reference's ``*_persist`` importers); ``--random`` instead builds the tiny
@@ -256,7 +256,11 @@ def cmd_speak(a) -> int:
         cfg = Qwen3TTSConfig()
         talker, pred = Talker(cfg), CodePredictor(cfg)
         load_tts(talker, pred, _loader(a.pile, a.model))
-        raise SystemExit("speak: the codec decoder's checkpoint layout has no loader in this package yet; use --random")
+        from ..models.codec.mimi import load_into as load_codec
+        mc = MimiConfig()
+        mc.num_codebooks, mc.codebook_size = cfg.num_code_groups, cfg.pred_vocab
+        codec = MimiCodec(mc)
+        load_codec(codec, _loader(a.pile, a.codec))              # a codec checkpoint in the Mimi layout (``mary import`` it under this name)
     text = torch.tensor([int(x) for x in a.ids.split(",")], dtype=torch.int32)
     n0 = max(1, min(len(text), a.prefill))
     with torch.no_grad():
@@ -358,7 +362,7 @@ def main(argv=None) -> int:
     he.set_defaults(fn=cmd_hear)
     sp = common(sub.add_parser("speak"))
     sp.add_argument("--ids", required=True), sp.add_argument("--out", required=True), sp.add_argument("--max-frames", type=int, default=64)
-    sp.add_argument("--prefill", type=int, default=6)
+    sp.add_argument("--prefill", type=int, default=6), sp.add_argument("--codec", default="codec")
     sp.set_defaults(fn=cmd_speak)
     cv = common(sub.add_parser("converse"))
     cv.add_argument("--wav", required=True), cv.add_argument("--out", required=True), cv.add_argument("--codec", default="mimi")
