@@ -334,12 +334,8 @@ int make_cache_map(CUtensorMap* m, const void* cache, int heads, int hd, int num
 
 template <int DK, int DV>
 int launch_fa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FaParams& p, int NB, cudaStream_t s) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(fa_prefill_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaCfg<DK, DV>::SMEM) != cudaSuccess)
-      return MARY_ERR_CUDA;
-    attr_set = true;
-  }
+  static MarySmemSlots smem_set = {};
+  if (int rc = mary_ensure_dyn_smem((const void*)fa_prefill_kernel<DK, DV>, FaCfg<DK, DV>::SMEM, &smem_set)) return rc;
   fa_prefill_kernel<DK, DV><<<dim3(NB, p.Hq), NTHREADS, FaCfg<DK, DV>::SMEM, s>>>(tq, tk, tv, p);
   MARY_CHECK_LAUNCH();
   return MARY_OK;

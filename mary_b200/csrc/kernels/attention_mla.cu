@@ -402,11 +402,8 @@ MARY_API int mary_mla_attention(const void* q, const void* cache, void* out, con
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return MARY_ERR_CUDA;
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(mla_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return MARY_ERR_CUDA;
-    attr_set = true;
-  }
+  static MarySmemSlots smem_set = {};
+  if (int rc = mary_ensure_dyn_smem((const void*)mla_attn_kernel, SMEM, &smem_set)) return rc;
   MlaParams p;
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_row0 = blk_row0;
   p.out = (__nv_bfloat16*)out; p.part_o = scratch; p.part_ml = scratch ? scratch + (int64_t)NB * nsplit * TR * DV : nullptr;

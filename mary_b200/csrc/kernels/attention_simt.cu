@@ -214,12 +214,9 @@ template <int VPL, int RMAX>
 int launch(const AttnParams& p, int NB, cudaStream_t s) {
   if (p.RQ * p.G > RMAX) return MARY_ERR_BAD_ARG;
   size_t sm = ((size_t)MAXR * p.DK + (size_t)WARPS * MAXR * p.DV + WARPS * MAXR * 2) * sizeof(float);
-  static size_t set_sm = 0;
-  if (sm > set_sm) {
-    if (cudaFuncSetAttribute(paged_attn_kernel<VPL, RMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm) != cudaSuccess)
-      return MARY_ERR_CUDA;
-    set_sm = sm;
-  }
+  // the limit is a per-device property of the kernel: raised the first time this device sees a shape that needs more
+  static MarySmemSlots smem_set = {};
+  if (int rc = mary_ensure_dyn_smem((const void*)paged_attn_kernel<VPL, RMAX>, sm, &smem_set)) return rc;
   dim3 grid(NB, p.Hkv, p.nsplit);
   paged_attn_kernel<VPL, RMAX><<<grid, WARPS * 32, sm, s>>>(p);
   MARY_CHECK_LAUNCH();

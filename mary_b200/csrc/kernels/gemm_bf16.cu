@@ -359,12 +359,8 @@ done:
 template <int BN, bool GLU>
 int launch(const CUtensorMap& tr, const CUtensorMap& tc, const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<BN, GLU>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bf16_kernel<BN, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-      return MARY_ERR_CUDA;
-    attr_set = true;
-  }
+  static MarySmemSlots smem_set = {};
+  if (int rc = mary_ensure_dyn_smem((const void*)gemm_bf16_kernel<BN, GLU>, C::SMEM, &smem_set)) return rc;
   int total = p.tiles_r * p.tiles_c * p.split_k * p.batch;
   int grid = total < mary_num_sms() ? total : mary_num_sms();
   if (p.sk_units > 0) grid = (p.tiles_r * p.tiles_c * p.k_blocks + p.sk_units - 1) / p.sk_units;

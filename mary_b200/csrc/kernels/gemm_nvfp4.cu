@@ -214,12 +214,8 @@ done:
 template <int NT, bool GLU>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const FP4Params& p, cudaStream_t s) {
   using C = Cfg<NT, GLU>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_nvfp4_grouped_kernel<NT, GLU>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM) != cudaSuccess)
-      return MARY_ERR_CUDA;
-    attr_set = true;
-  }
+  static MarySmemSlots smem_set = {};
+  if (int rc = mary_ensure_dyn_smem((const void*)gemm_nvfp4_grouped_kernel<NT, GLU>, C::SMEM, &smem_set)) return rc;
   MARY_LAUNCH((gemm_nvfp4_grouped_kernel<NT, GLU>), mary_num_sms(), NTHREADS, C::SMEM, s, tw, tx, p);
   MARY_CHECK_LAUNCH();
   return MARY_OK;

@@ -19,6 +19,13 @@ int mary_make_tmap_2d(CUtensorMap* m, const void* base, int dtype_bytes_x2, uint
 // without it, 81.2 ms against 80.1 ms at 16 sequences).
 int mary_pdl_enabled();
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the CURRENT device only, so the "already raised" record is kept
+// per device ordinal: `slots` is a zero-initialised array of MARY_MAX_DEVICES entries owned by the call site (one per kernel
+// instantiation).  Raises the limit when `bytes` exceeds what this device has been given so far.  Returns a MaryStatus.
+#define MARY_MAX_DEVICES 64
+struct MarySmemSlots { size_t v[MARY_MAX_DEVICES]; };
+int mary_ensure_dyn_smem(const void* func, size_t bytes, MarySmemSlots* slots);
+
 // Launch with programmatic dependent launch allowed: the kernel may be scheduled while its predecessor on the stream is still
 // draining, and its threads call pdl_sync() (common.cuh) before they touch anything a predecessor wrote.  Only kernels whose
 // first statement is pdl_sync() may be launched this way.  A template kernel name goes in parentheses.

@@ -13,8 +13,10 @@
 //     the process exits, whether or not the entry point is ever called;
 //   * a problem whose partial results do not fit (see mary_paged_attention_scratch_floats) is refused with
 //     MARY_ERR_SCRATCH_TOO_LARGE and nothing is launched — use fewer splits or fewer query blocks per call;
-//   * the first call on each device looks the array's device address up (cudaGetSymbolAddress) and raises the
-//     kernel's shared-memory limit; make that first call outside any stream capture.  Later calls only launch;
+//   * the first call on each device looks the array's device address up (cudaGetSymbolAddress); make that first call
+//     outside any stream capture.  The kernel's shared-memory limit is a per-device attribute that is raised whenever a
+//     device meets a head width that needs more than it was given before (the widest so far is remembered per device), so
+//     the first call with each new, wider head shape should also come before capture; calls after that only launch;
 //   * no cudaMalloc, cudaFree or other allocating routine is called, on any path;
 //   * all calls on a device share the one array, which keeps whatever the previous call left in it.  Nothing in it
 //     needs to start at zero (every slot that the merge pass reads was written by the same call's first pass), but two

@@ -7,6 +7,7 @@
 #include <stdlib.h>
 
 namespace {
+__device__ int g_status_fallback[64];
 std::mutex g_mu;
 int* g_status[64] = {nullptr};
 PFN_encodeTiled g_encode = nullptr;
@@ -18,8 +19,15 @@ int* mary_status_ptr() {
   cudaGetDevice(&dev);
   std::lock_guard<std::mutex> g(g_mu);
   if (!g_status[dev]) {
-    cudaMalloc(&g_status[dev], 256);
-    cudaMemset(g_status[dev], 0, 256);
+    // never null: when the allocation fails the word falls back to a zero-initialised array of the library's device image
+    int* p = nullptr;
+    if (cudaMalloc(&p, 256) != cudaSuccess || cudaMemset(p, 0, 256) != cudaSuccess) {
+      cudaGetLastError();
+      void* sym = nullptr;
+      if (cudaGetSymbolAddress(&sym, g_status_fallback) != cudaSuccess) return nullptr;
+      p = (int*)sym;
+    }
+    g_status[dev] = p;
   }
   return g_status[dev];
 }
@@ -69,13 +77,25 @@ int mary_make_tmap_2d(CUtensorMap* m, const void* base, int dtype_bytes_x2, uint
 // Read and clear the status word of the current device (synchronises the device).
 MARY_API int mary_last_status() {
   int* p = mary_status_ptr();
+  if (!p) return MARY_ERR_CUDA;
   int v = 0;
-  cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+  if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return MARY_ERR_CUDA;
   if (v) cudaMemset(p, 0, sizeof(int));
   return v;
 }
 
 MARY_API int mary_sm_count() { return mary_num_sms(); }
+
+int mary_ensure_dyn_smem(const void* func, size_t bytes, MarySmemSlots* slots) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MARY_MAX_DEVICES) return MARY_ERR_CUDA;
+  std::lock_guard<std::mutex> g(g_mu);
+  if (bytes > slots->v[dev]) {
+    if (cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess) return MARY_ERR_CUDA;
+    slots->v[dev] = bytes;
+  }
+  return MARY_OK;
+}
 
 int mary_pdl_enabled() {
   static int v = -1;

@@ -13,11 +13,11 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _problem(seed):
+def _problem(seed, Hq=16, Hkv=8, D=128):
     from mary_b200.runtime.batch import BatchMeta
     from mary_b200.runtime.kv_cache import PagedKVCache
     torch.manual_seed(seed)
-    lens, Hq, Hkv, D = [700, 33, 1500, 257], 16, 8, 128
+    lens = [700, 33, 1500, 257]
     cache = PagedKVCache(1, sum((l + 15) // 16 for l in lens) + 2, 16, Hkv, D, dtype=torch.bfloat16, device="cuda")
     for s, l in enumerate(lens):
         cache.alloc.extend(s, l)
@@ -54,13 +54,22 @@ def test_noalloc_entry_point_matches_regular_entry_point_twice():
     lib.mary_noalloc_scratch_bytes.restype = ctypes.c_int64
     assert lib.mary_noalloc_scratch_bytes() == 16 << 20
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    for call, (seed, nsplit) in enumerate(((1, 4), (2, 6))):          # two calls in a row share the built-in array
-        cache, meta, q, Hq, Hkv, D = _problem(seed)
+    # calls in a row share the built-in array; the third one has 256-wide heads, whose kernel needs more dynamic shared
+    # memory than the 48 KB default, so it exercises the per-device raise of that limit on a later call
+    for call, (seed, nsplit, shape) in enumerate(((1, 4, (16, 8, 128)), (2, 6, (16, 8, 128)), (3, 3, (8, 4, 256)))):
+        cache, meta, q, Hq, Hkv, D = _problem(seed, *shape)
         got = torch.full((meta.num_seqs, Hq, D), float("nan"), dtype=torch.bfloat16, device="cuda")
         want = torch.full_like(got, float("nan"))
         a, keep, NB = _args(lib, cache, meta, q, got, Hq, Hkv, D, nsplit)
+        if call == 1:
+            # same head shape as the call before: nothing is left to set up, so the device's free memory must not move
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
         rc = lib.mary_paged_attention_noalloc(*a, stream)
         assert rc == 0, lib.mary_status_string(rc).decode()
+        if call == 1:
+            torch.cuda.synchronize()
+            assert torch.cuda.mem_get_info()[0] == free_before, "the allocation-free entry point changed the free device memory"
         n = lib.mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D)
         scratch = torch.empty(n, dtype=torch.float32, device="cuda")
         b, keep2, _ = _args(lib, cache, meta, q, want, Hq, Hkv, D, nsplit)
