@@ -205,7 +205,9 @@ def main():
     t0 = time.time()
     model = Gemma4Model(cfg, tp=par, dtype=torch.bfloat16, device=dev) if is_gemma else MoEDecoder(cfg, par=par, dtype=torch.bfloat16, device=dev)
     B_global, B = B, B_local
-    steps_total = W + args.steps + 8
+    # every step can commit up to 1 + k tokens; the decoder runs the eager census step, the capture warm-up, W warm-up steps,
+    # the timed steps and the same number again in the end-to-end loop, all from the same context
+    steps_total = W + 2 * args.steps + 8
     max_len = ctx + (steps_total + 8) * (1 + k) + 16
     max_len = (max_len + 15) // 16 * 16
     n_cache_layers = cfg.num_hidden_layers + cfg.num_mtp_layers

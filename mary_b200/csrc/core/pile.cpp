@@ -261,22 +261,28 @@ int pile_get(void* h, const uint8_t* hash32, const uint8_t** ptr, uint64_t* len)
   Pile* p = (Pile*)h;
   Key k;
   std::memcpy(k.b, hash32, 32);
-  Record* r;
+  // Everything needed from the record is copied while the lock is held: a concurrent put may grow `recs` and move it.
+  size_t slot;
+  uint64_t offset, rlen;
+  bool validated;
   {
     std::lock_guard<std::mutex> g(p->mu);
     auto it = p->index.find(k);
     if (it == p->index.end()) return -1;
-    r = &p->recs[it->second];
+    slot = it->second;
+    const Record& r = p->recs[slot];
+    offset = r.offset; rlen = r.len; validated = r.validated;
   }
-  const uint8_t* data = p->map + r->offset + HDR;
-  if (p->validate && !r->validated) {
+  const uint8_t* data = p->map + offset + HDR;
+  if (p->validate && !validated) {
     uint8_t chk[32];
-    hash_payload(data, r->len, chk);
-    if (std::memcmp(chk, r->hash.b, 32) != 0) return -2;
-    r->validated = true;
+    hash_payload(data, rlen, chk);                   // the payload itself never moves (append-only mapping)
+    if (std::memcmp(chk, k.b, 32) != 0) return -2;
+    std::lock_guard<std::mutex> g(p->mu);
+    p->recs[slot].validated = true;
   }
   *ptr = data;
-  *len = r->len;
+  *len = rlen;
   return 0;
 }
 

@@ -38,6 +38,7 @@ struct Request {
   bool finished = false;
   int32_t spec = 0;        // draft tokens appended to the next decode row group
   int32_t drafts[8];
+  int32_t need_pages = 0;  // pages the request can grow to: prompt + max_new + 8 speculative rows (fixed at admission)
 };
 
 struct Sched {
@@ -151,14 +152,18 @@ void* sched_create(void* kv, int32_t max_tokens, int32_t max_seqs, int32_t prefi
 }
 void sched_destroy(void* h) { delete (Sched*)h; }
 
-void sched_add(void* h, int64_t id, const int32_t* prompt, int32_t n, int32_t max_new) {
+// Returns 0, or -1 for a request that can never be scheduled: an empty prompt (no row to run, so it would block the head of
+// the waiting queue for ever), a negative budget, or more pages than the whole pool holds.
+int32_t sched_add(void* h, int64_t id, const int32_t* prompt, int32_t n, int32_t max_new) {
   Sched* s = (Sched*)h;
+  if (n <= 0 || max_new < 0 || pages_for(s->kv, (int64_t)n + max_new + 8) > s->kv->num_pages) return -1;
   Request r;
   r.id = id;
   r.prompt.assign(prompt, prompt + n);
   r.max_new = max_new;
   s->reqs.emplace(id, std::move(r));
   s->waiting.push_back(id);
+  return 0;
 }
 
 int32_t sched_num_waiting(void* h) { return (int32_t)((Sched*)h)->waiting.size(); }
@@ -221,12 +226,26 @@ int32_t sched_next(void* h, int32_t* token_ids, int32_t* positions, int32_t* seq
     Request& r = s->reqs[id];
     if (!r.finished && r.prefilled < (int64_t)r.prompt.size()) prefill(r);
   }
-  // 3. admit waiting requests (only if the whole prompt plus its generation budget fits in free pages)
+  // 3. admit waiting requests.  A request is admitted only if the pages it can grow to (prompt + generation budget +
+  // speculative rows) fit into the free pages that are not already PROMISED to the running requests: every running request
+  // keeps a claim on need_pages - held pages, so two requests that each fit alone are not both admitted into a pool that
+  // cannot hold them both, and a running sequence never finds the pool empty when it has to grow.
+  int64_t promised = 0;
+  for (int64_t id : s->running) {
+    const Request& r = s->reqs[id];
+    if (r.finished) continue;
+    auto it = kv->seqs.find(id);
+    const int64_t held = it == kv->seqs.end() ? 0 : (int64_t)it->second.pages.size();
+    promised += std::max<int64_t>(0, (int64_t)r.need_pages - held);
+  }
   while (!s->waiting.empty() && ns < s->max_seqs && nt < s->max_tokens) {
     Request& r = s->reqs[s->waiting.front()];
-    int64_t need = pages_for(kv, (int64_t)r.prompt.size() + r.max_new + 8);
-    if (need > (int64_t)kv->free_list.size()) break;
+    const int64_t need = pages_for(kv, (int64_t)r.prompt.size() + r.max_new + 8);
+    if (need > (int64_t)kv->free_list.size() - promised) break;
+    const int64_t free_before = (int64_t)kv->free_list.size();
     if (!prefill(r)) break;
+    r.need_pages = (int32_t)need;
+    promised += need - (free_before - (int64_t)kv->free_list.size());
     s->running.push_back(r.id);
     s->waiting.pop_front();
   }

@@ -147,21 +147,24 @@ allreduce_bf16_kernel(const CommCtx c, size_t in_off, size_t out_off, int64_t n,
 // reads is written again before the next barrier: the staging area alternates with the parity of the device-resident epoch,
 // and a rank can only pass the barrier of call k + 1 after every peer has finished reading the stage of call k.  Compared with
 // the two-shot form this saves the second barrier and the all-gather step; it moves world x the bytes, which only pays for
-// small vectors.  Same-numbered blocks of all ranks own the same slice, so the barrier is per block.
-__global__ void __launch_bounds__(512)
-allreduce_oneshot_kernel(const CommCtx c, const uint4* __restrict__ partial, uint4* __restrict__ out, size_t stage_off, size_t stage_bytes,
-                         int64_t nvec, uint32_t* epochs, int use_mc) {
-  pdl_sync();
+// small vectors.
+// Block b owns vectors [b * ONESHOT_VECS, (b + 1) * ONESHOT_VECS) of the stage WHATEVER the length of the call, and its
+// barrier and epoch are those of block b alone.  The slice must not depend on the call: the parity of block b's epoch only
+// protects bytes that no other block number ever writes, and calls of different lengths (different grids) advance the blocks'
+// epochs differently.
+constexpr int64_t ONESHOT_VECS = 2048;     // 32 KB of the vector per block
+
+__device__ void allreduce_oneshot_body(const CommCtx& c, const uint4* __restrict__ partial, uint4* __restrict__ out, size_t stage_off,
+                                       size_t stage_bytes, int64_t nvec, uint32_t* epoch_slot, int use_mc, int blk) {
   __shared__ uint32_t epoch_s;
-  if (threadIdx.x == 0) epoch_s = epochs[blockIdx.x] + 1;
+  if (threadIdx.x == 0) epoch_s = *epoch_slot + 1;
   __syncthreads();
   const uint32_t epoch = epoch_s;
   const size_t off = stage_off + (size_t)(epoch & 1u) * stage_bytes;
-  const int64_t per = (nvec + gridDim.x - 1) / gridDim.x;
-  const int64_t lo = (int64_t)blockIdx.x * per, hi = min(nvec, lo + per);
+  const int64_t lo = (int64_t)blk * ONESHOT_VECS, hi = min(nvec, lo + ONESHOT_VECS);
   uint4* mine = (uint4*)(c.bufs[c.rank] + off);
   for (int64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) mine[v] = partial[v];
-  if (!rank_barrier(c, 0, epoch, blockIdx.x)) return;
+  if (!rank_barrier(c, 0, epoch, blk)) return;
   for (int64_t v = lo + threadIdx.x; v < hi; v += blockDim.x) {
     uint4 r;
     if (use_mc) {
@@ -182,7 +185,25 @@ allreduce_oneshot_kernel(const CommCtx c, const uint4* __restrict__ partial, uin
     }
     out[v] = r;
   }
-  if (threadIdx.x == 0) epochs[blockIdx.x] = epoch;
+  if (threadIdx.x == 0) *epoch_slot = epoch;
+}
+
+__global__ void __launch_bounds__(512)
+allreduce_oneshot_kernel(const CommCtx c, const uint4* __restrict__ partial, uint4* __restrict__ out, size_t stage_off, size_t stage_bytes,
+                         int64_t nvec, uint32_t* epochs, int use_mc) {
+  pdl_sync();
+  allreduce_oneshot_body(c, partial, out, stage_off, stage_bytes, nvec, epochs + blockIdx.x, use_mc, blockIdx.x);
+}
+
+// All ranks of the one-shot form inside ONE cooperative launch on one GPU: blocks [r * nblk, (r + 1) * nblk) play rank r;
+// `partial` and `out` hold the ranks' vectors back to back (stride `nvec`), `epochs` holds world x 64 words.
+__global__ void __launch_bounds__(512)
+allreduce_oneshot_emulated_kernel(CommCtx c, const uint4* __restrict__ partial, uint4* __restrict__ out, size_t stage_off,
+                                  size_t stage_bytes, int64_t nvec, uint32_t* epochs, int nblk) {
+  c.rank = blockIdx.x / nblk;
+  const int blk = blockIdx.x % nblk;
+  allreduce_oneshot_body(c, partial + (size_t)c.rank * nvec, out + (size_t)c.rank * nvec, stage_off, stage_bytes, nvec,
+                         epochs + c.rank * 64 + blk, 0, blk);
 }
 
 // Every rank of the group inside ONE cooperative launch on one GPU (block groups play the ranks, plain loads and stores
@@ -471,18 +492,39 @@ MARY_API int mary_argmax_merge_emulated(const void* val, const void* idx, int T,
 }
 
 // One-shot form for small vectors: partial (this rank's n bf16, 16-byte aligned, any device memory) -> out (local, n bf16).
-// The symmetric buffers need two staging areas of stage_bytes >= n * 2 each at byte offset stage_off.  grid <= 64 blocks; the
-// same flag pad and epochs array as mary_allreduce_bf16 (both forms may be mixed as long as all ranks make the same calls).
+// The symmetric buffers need two staging areas of stage_bytes >= n * 2 each at byte offset stage_off.  Block b reduces the
+// fixed slice of 2048 16-byte vectors number b, so grid must be ceil(n / 8 / 2048) (at most 64); the same flag pad and epochs
+// array as mary_allreduce_bf16 (both forms, and calls of different lengths, may be mixed as long as all ranks make the same calls).
 MARY_API int mary_allreduce_bf16_oneshot(const void* partial, void* out, const uint64_t* bufs, const uint64_t* sigs, uint64_t mc, int rank,
                                          int world, uint64_t stage_off, uint64_t stage_bytes, int64_t n, uint32_t* epochs, int grid,
                                          int use_mc, uint64_t wait_ns, cudaStream_t s) {
   if (world < 1 || world > MAX_RANKS || (n % 8) || (stage_off % 16) || (stage_bytes % 16) || (uint64_t)n * 2 > stage_bytes || grid < 1 ||
-      grid > 64 || ((uintptr_t)partial & 15) || ((uintptr_t)out & 15))
+      grid > 64 || (int64_t)grid * ONESHOT_VECS < n / 8 || ((uintptr_t)partial & 15) || ((uintptr_t)out & 15))
     return MARY_ERR_BAD_ARG;
   CommCtx c;
   for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
   c.mc = (uint8_t*)mc; c.rank = rank; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
   MARY_LAUNCH(allreduce_oneshot_kernel, grid, 512, 0, s, c, (const uint4*)partial, (uint4*)out, (size_t)stage_off, (size_t)stage_bytes,
               n / 8, epochs, (use_mc && mc) ? 1 : 0);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// Single-GPU emulation of the one-shot form: `world` ranks as block groups of one cooperative launch.  partial / out hold the
+// ranks' vectors back to back ([world][n] bf16); epochs: world * 64 words (zeroed at set-up); grid = blocks PER RANK.
+MARY_API int mary_allreduce_bf16_oneshot_emulated(const void* partial, void* out, const uint64_t* bufs, const uint64_t* sigs, int world,
+                                                  uint64_t stage_off, uint64_t stage_bytes, int64_t n, uint32_t* epochs, int grid,
+                                                  uint64_t wait_ns, cudaStream_t s) {
+  if (world < 1 || world > MAX_RANKS || (n % 8) || (stage_off % 16) || (stage_bytes % 16) || (uint64_t)n * 2 > stage_bytes || grid < 1 ||
+      grid > 64 || (int64_t)grid * ONESHOT_VECS < n / 8 || grid * world > mary_num_sms())
+    return MARY_ERR_BAD_ARG;
+  CommCtx c;
+  for (int i = 0; i < world; ++i) { c.bufs[i] = (uint8_t*)bufs[i]; c.sigs[i] = (uint32_t*)sigs[i]; }
+  c.mc = nullptr; c.rank = 0; c.world = world; c.wait_ns = wait_ns; c.status = mary_status_ptr();
+  size_t so = stage_off, sb = stage_bytes;
+  int64_t nvec = n / 8;
+  void* args[] = {&c, &partial, &out, &so, &sb, &nvec, &epochs, &grid};
+  if (cudaLaunchCooperativeKernel((void*)allreduce_oneshot_emulated_kernel, dim3(grid * world), dim3(512), args, 0, s) != cudaSuccess)
+    return MARY_ERR_CUDA;
   return MARY_OK;
 }

@@ -106,8 +106,8 @@ __device__ __forceinline__ uint32_t e2m1_code(float y) {
 
 // One CTA per entry i = t * k + j.
 __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int* __restrict__ idx, int k, int E, int e_local,
-                                   int Kd, int NT, int rank, int entry_stride, const int* __restrict__ send_base, int* __restrict__ send_cnt,
-                                   Peers xq_slabs, Peers sf_slabs, Peers meta_slabs) {
+                                   int Kd, int NT, int rank, int entry_stride, int cap_rows, const int* __restrict__ send_base,
+                                   int* __restrict__ send_cnt, Peers xq_slabs, Peers sf_slabs, Peers meta_slabs, int* __restrict__ status) {
   pdl_sync();
   __shared__ int s_row;
   const int i = blockIdx.x;
@@ -116,6 +116,10 @@ __global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, int64_t 
   if (threadIdx.x == 0) s_row = send_base[e] + atomicAdd(&send_cnt[e], 1);
   __syncthreads();
   const int row = s_row, d = (e == E) ? rank : e / e_local;
+  if (row < 0 || row >= cap_rows) {              // never store outside the owner's slabs: record it and drop the row
+    if (threadIdx.x == 0) atomicCAS(status, 0, MARY_ERR_BOUNDS);
+    return;
+  }
   uint8_t* xq = (uint8_t*)xq_slabs.p[d];
   uint8_t* sf = (uint8_t*)sf_slabs.p[d];
   if (threadIdx.x == 0) ((int*)meta_slabs.p[d])[row] = rank * entry_stride + i;
@@ -193,14 +197,14 @@ MARY_API int mary_ep_plan(const int* cm, int world, int rank, int E, int e_local
 }
 
 MARY_API int mary_ep_dispatch(const void* x, int64_t ldx, const int* idx, int n_entries, int k, int E, int e_local, int K, int NT, int rank,
-                              int world, int entry_stride, const int* send_base, int* send_cnt, const uint64_t* xq_slabs,
+                              int world, int entry_stride, int cap_rows, const int* send_base, int* send_cnt, const uint64_t* xq_slabs,
                               const uint64_t* sf_slabs, const uint64_t* meta_slabs, cudaStream_t s) {
   if (n_entries <= 0) return MARY_OK;
-  if ((K % 64) || (ldx % 8) || world > MAX_RANKS) return MARY_ERR_BAD_ARG;
+  if ((K % 64) || (ldx % 8) || world > MAX_RANKS || n_entries > entry_stride) return MARY_ERR_BAD_ARG;
   const int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
-  MARY_LAUNCH(ep_dispatch_kernel, n_entries, threads, 0, s, (const __nv_bfloat16*)x, ldx, idx, k, E, e_local, K, NT, rank, entry_stride, send_base,
+  MARY_LAUNCH(ep_dispatch_kernel, n_entries, threads, 0, s, (const __nv_bfloat16*)x, ldx, idx, k, E, e_local, K, NT, rank, entry_stride, cap_rows, send_base,
                                                   send_cnt, make_peers(xq_slabs, world), make_peers(sf_slabs, world),
-                                                  make_peers(meta_slabs, world));
+                                                  make_peers(meta_slabs, world), mary_status_ptr());
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

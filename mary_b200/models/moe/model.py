@@ -152,7 +152,10 @@ class MoEFFN(nn.Module):
         idx, w = self.route(x)
         if self.par.ep_mode == "a2a" and self.par.ep_size > 1:
             # tokens are local: routed experts through the all-to-all (global expert ids), shared expert computed at home
-            big = x.shape[0] > getattr(self.par, "ep_decode_cap", 1 << 30)
+            cap = getattr(self.par, "ep_decode_cap", None)
+            if cap is None:
+                raise RuntimeError("all-to-all expert parallelism needs par.ep_decode_cap (rows per rank of the decode-sized slabs)")
+            big = x.shape[0] > cap
             if big:
                 # prefill-sized batches get slabs of their own (and 128-row token tiles) next to the decode-sized ones
                 if getattr(self, "ep_layer_big", None) is None:

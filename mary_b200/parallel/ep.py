@@ -22,7 +22,7 @@ from ..ops.moe import NVFP4Experts
 
 declare("mary_ep_counts", "piiiips")
 declare("mary_ep_plan", "piiiiippppis")
-declare("mary_ep_dispatch", "plp" + "iiiiiiiii" + "pp" + "ppp" + "s")
+declare("mary_ep_dispatch", "plp" + "iiiiiiiiii" + "pp" + "ppp" + "s")
 declare("mary_ep_return_ptrs", "pppiiiiipps")
 declare("mary_rank_barrier", "piipils")
 declare("mary_gemm_nvfp4_grouped_ex", "pppppppp" + "liiilii" + "ps")
@@ -90,7 +90,7 @@ class EPLayer:
         check(lib().mary_ep_plan(_p(b.count_mat), self.world, self.rank, b.E, self.e_local, b.nt, _p(self.tiles), _p(self.plan_meta),
                                  _p(self.send_base), _p(self.send_cnt), T if b.shared else 0, _stream()), "ep_plan")
         check(lib().mary_ep_dispatch(_p(x), x.stride(0), _p(idx), T * k, k, b.E, self.e_local, b.H, b.nt, self.rank, self.world,
-                                     b.entry_stride, _p(self.send_base), _p(self.send_cnt), self.p_xq, self.p_sf, self.p_meta,
+                                     b.entry_stride, b.cap_rows, _p(self.send_base), _p(self.send_cnt), self.p_xq, self.p_sf, self.p_meta,
                                      _stream()), "ep_dispatch")
 
     def experts(self):
@@ -115,6 +115,17 @@ class EPLayer:
         plan.row_of = self.ident
         return cuda_moe.unpermute(comb, plan, w, T, k, shared)
 
+    def check_shape(self, x, idx):
+        """Entry ids ``t * k + j`` address rows of the home rank's combine buffer and are packed into return addresses with
+        ``entry_stride = t_cap * k``: a batch beyond ``t_cap`` rows, or another ``k``, would store outside the peers' slabs."""
+        b = self.b
+        if x.shape[0] > b.t_cap:
+            raise ValueError(f"{x.shape[0]} rows exceed the expert-parallel slabs' capacity of {b.t_cap} rows per rank")
+        if idx.shape[0] != x.shape[0] or idx.shape[1] not in (b.k_routed, b.k):
+            raise ValueError(f"routing table {tuple(idx.shape)} does not match {x.shape[0]} rows x {b.k_routed} experts per token")
+        if x.shape[1] != b.H:
+            raise ValueError(f"hidden size {x.shape[1]} != {b.H}")
+
     def with_shared(self, idx, w):
         """Append the shared expert's entry (id ``E``, weight 1) to every token's routed entries."""
         T = idx.shape[0]
@@ -127,6 +138,7 @@ class EPLayer:
     def forward(self, x, idx, w, shared=None):
         """One MoE layer for this rank's tokens (``idx`` holds GLOBAL expert ids).  With a shared expert in the buffers'
         layout the caller passes the routed entries only; the shared entry is appended here."""
+        self.check_shape(x, idx)
         if self.b.shared and idx.shape[1] == self.b.k_routed:
             idx, w = self.with_shared(idx, w)
         idx = idx.to(torch.int32).contiguous()
@@ -141,6 +153,8 @@ class EPLayer:
 
 def emulate(layers: list[EPLayer], xs, idxs, ws):
     """Drive ``world`` ranks that share one device, phase by phase; returns each rank's output."""
+    for l, x, i in zip(layers, xs, idxs):
+        l.check_shape(x, i)
     if layers[0].b.shared and idxs[0].shape[1] == layers[0].b.k_routed:
         pairs = [l.with_shared(i, w) for l, i, w in zip(layers, idxs, ws)]
         idxs, ws = [p[0] for p in pairs], [p[1] for p in pairs]

@@ -27,6 +27,8 @@ class ParallelGroup:
         self.ep_rank, self.ep_size = rank, size
         self.sp = None                  # parallel.sp.SequenceParallel: reduce-scatter / all-gather arm of the dense decoders
         self.ep_factory = None          # callable(experts, cfg) -> EPLayer, set by the launcher in a2a mode
+        self.ep_decode_cap = None       # a2a mode: rows per rank the decode-sized slabs hold (larger batches take ep_prefill_cap slabs)
+        self.ep_prefill_cap = None
         self.bytes_reduced = 0
         self.calls = 0
 

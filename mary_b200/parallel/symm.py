@@ -83,7 +83,7 @@ class SymmetricHeap:
         if self.oneshot and nbytes <= self.local_out.numel() and pad == 0 and partial.is_contiguous() and partial.data_ptr() % 16 == 0:
             # small vector: stage, one barrier, every rank sums the whole vector into a local buffer
             out = self.local_out[:nbytes].view(torch.bfloat16)
-            grid = max(1, min(32, (n // 8 + 2047) // 2048))
+            grid = (n // 8 + 2047) // 2048            # block b owns vectors [2048 b, 2048 (b + 1)) whatever the length
             half = self.region // 2 // 16 * 16
             check(lib().mary_allreduce_bf16_oneshot(partial.data_ptr(), out.data_ptr(), self.buf_ptrs, self.sig_ptrs, self.mc, self.rank,
                                                     self.world, self.region, half, n, self.epochs.data_ptr(), grid, 1 if self.mc else 0,

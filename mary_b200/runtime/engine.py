@@ -55,7 +55,9 @@ class Engine:
         rid = self._next_id
         self._next_id += 1
         a = np.ascontiguousarray(ids, dtype=np.int32)
-        self.lib.sched_add(self.h, rid, a.ctypes.data, len(a), max_new)
+        if self.lib.sched_add(self.h, rid, a.ctypes.data, len(a), max_new) != 0:
+            raise ValueError(f"request refused: {len(a)} prompt tokens + {max_new} new tokens (an empty prompt, a negative budget, "
+                             "or more pages than the KV pool holds)")
         self.outputs[rid] = []
         self.submit_time[rid] = time.perf_counter()
         return rid

@@ -36,6 +36,7 @@ def _declare(lib):
     lib.sched_create.argtypes = [c.c_void_p, c.c_int32, c.c_int32, c.c_int32]
     lib.sched_destroy.argtypes = [c.c_void_p]
     lib.sched_add.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int32, c.c_int32]
+    lib.sched_add.restype = c.c_int32
     lib.sched_num_waiting.argtypes = [c.c_void_p]
     lib.sched_num_running.argtypes = [c.c_void_p]
     lib.sched_set_drafts.argtypes = [c.c_void_p, c.c_int64, c.c_void_p, c.c_int32]

@@ -47,6 +47,9 @@ class SpecDecoder:
         self.meta_d = self._static_meta(1) if spec_k > 0 else None
         self.graph = None
         self.steps = 0
+        # host-side upper bound of the longest committed length: every step may commit up to 1 + k tokens and writes rows up to
+        # 1 + k positions past the committed length, so a step is refused before launch (or replay) once it could leave max_len
+        self.len_bound = 0
 
     def _static_meta(self, q_len: int) -> BatchMeta:
         B, dev = self.B, self.dev
@@ -72,6 +75,7 @@ class SpecDecoder:
     def set_context(self, kv_len, pending, drafts=None):
         """Start decoding from a populated cache: committed lengths, the next token to feed and optional drafts."""
         self.kv_before.copy_(torch.as_tensor(kv_len, dtype=torch.int32).to(self.dev))
+        self.len_bound = int(np.max(np.asarray(kv_len))) if np.size(kv_len) else 0
         self.fed[:, 0].copy_(torch.as_tensor(pending, dtype=torch.int32).to(self.dev))
         if self.k:
             d = drafts if drafts is not None else torch.zeros(self.B, self.k, dtype=torch.int32)
@@ -104,6 +108,7 @@ class SpecDecoder:
                     nxt[:, -1] = pending
                 d_tok, d_h = self.model.draft(0, h, nxt.reshape(-1), meta, self.cache)
             self.kv_before.fill_(L)
+            self.len_bound = L
             self.fed[:, 0].copy_(pending)
             if self.k:
                 drafts = [d_tok[last].to(torch.int32)]
@@ -171,6 +176,11 @@ class SpecDecoder:
 
     def step(self):
         """Run one step; results stay on the device (``emitted``, ``n_emitted``)."""
+        R = 1 + self.k
+        if self.len_bound + 2 * R > self.max_len:
+            # the rows of this step (and the draft rows behind them) would index past the page table: refuse on the host
+            raise RuntimeError(f"decode step refused: up to {self.len_bound} committed tokens + {2 * R} rows exceed max_len {self.max_len}")
+        self.len_bound += R
         if self.graph is not None:
             self.graph.replay()
         else:

@@ -35,6 +35,40 @@ def test_emulated_allreduce_matches_sum(world):
             assert torch.equal(bufs[0][region:region + n * 2], bufs[-1][region:region + n * 2])
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_emulated_oneshot_allreduce_mixed_lengths(world):
+    """The one-shot (one barrier, staged) all-reduce on calls of alternating lengths: a call that needs one block, then calls
+    that need two and five.  Block ``b`` owns the same 32 KB slice of the stage in every call, so the blocks' epochs (which
+    advance only in the calls they take part in) always select a half of the stage that no peer still reads."""
+    from mary_b200.ops.cuda import _stream, check, declare, last_status, lib
+    declare("mary_allreduce_bf16_oneshot_emulated", "pppp" + "illlpils")
+    stage_bytes = 1 << 20
+    bufs = [torch.zeros(2 * stage_bytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
+    sigs = [torch.zeros(1024, dtype=torch.int32, device="cuda") for _ in range(world)]
+    bp = (ctypes.c_uint64 * 8)(*[b.data_ptr() for b in bufs])
+    sp = (ctypes.c_uint64 * 8)(*[s.data_ptr() for s in sigs])
+    epochs = torch.zeros(64 * world, dtype=torch.int32, device="cuda")
+    lengths = [2048 * 8, 2688 * 8, 2048 * 8, 5 * 2048 * 8 - 64, 8, 2688 * 8, 2048 * 8]
+    for call, n in enumerate(lengths):
+        torch.manual_seed(100 + call)
+        xs = torch.randn(world, n, device="cuda").bfloat16()
+        out = torch.zeros(world, n, dtype=torch.bfloat16, device="cuda")
+        grid = (n // 8 + 2047) // 2048
+        check(lib().mary_allreduce_bf16_oneshot_emulated(xs.data_ptr(), out.data_ptr(), bp, sp, world, 0, stage_bytes, n,
+                                                         epochs.data_ptr(), grid, int(2e9), _stream()), "allreduce_oneshot_emulated")
+        torch.cuda.synchronize()
+        assert last_status() == 0
+        acc = torch.zeros(n, dtype=torch.float32, device="cuda")
+        for r in range(world):                                 # the kernel's order: rank 0 first, f32 accumulation
+            acc += xs[r].float()
+        want = acc.bfloat16()
+        for r in range(world):
+            assert torch.equal(out[r], want), (call, n, r)
+    # a grid that does not cover the vector is refused
+    assert lib().mary_allreduce_bf16_oneshot_emulated(xs.data_ptr(), out.data_ptr(), bp, sp, world, 0, stage_bytes, 4096 * 8,
+                                                      epochs.data_ptr(), 1, int(2e9), _stream()) == 4
+
+
 def test_bounded_wait_reports_timeout_and_context_survives():
     from mary_b200.ops.cuda import _stream, check, declare, last_status, lib
     declare("mary_wait_flag", "piiiils")

@@ -77,3 +77,44 @@ def test_speculative_rows_commit_and_rollback_leave_no_trace():
     assert e.cache.alloc.seq_len(rid) == len(p) + 2          # pending + one accepted draft kept, one row dropped
     e.run()
     assert e.outputs[rid][:6] == plain
+
+
+def test_admission_reserves_the_pages_a_running_request_can_grow_to():
+    """Two requests that each fit the pool alone but not together: the second one must wait until the first has finished,
+    instead of both being admitted and the decode loop finding the pool empty."""
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(0, 4096, 20).tolist() for _ in range(2)]
+    # 20 prompt + 70 new + 8 speculative rows = 98 tokens = 7 pages each; the pool holds 10
+    e = _engine(max_seqs=4, pages=10)
+    rids = [e.add_request(p, 70) for p in prompts]
+    e.step()
+    assert e.lib.sched_num_running(e.h) == 1 and e.lib.sched_num_waiting(e.h) == 1
+    e.run()
+    assert all(len(e.outputs[r]) >= 70 for r in rids)
+    assert e.cache.alloc.free_pages == 10
+
+
+def test_empty_prompt_and_oversized_requests_are_refused_at_submission():
+    e = _engine(pages=8)
+    with pytest.raises(ValueError):
+        e.add_request([], 4)
+    with pytest.raises(ValueError):
+        e.add_request([1, 2, 3], 16 * 8)      # more pages than the pool holds
+    assert e.generate([[5, 6, 7]], 3)[0] is not None
+
+
+def test_spec_decoder_refuses_a_step_that_could_leave_its_page_table():
+    from mary_b200.models.moe import MoEDecoder, init_random_ as moe_init, tiny_moe_config
+    from mary_b200.runtime.spec_decode import SpecDecoder
+    cfg = tiny_moe_config("gqa")
+    m = MoEDecoder(cfg, dtype=torch.float32)
+    moe_init(m, 0)
+    spec = m.kv_spec()
+    cache = PagedKVCache(spec["num_layers"], 16, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.float32)
+    dec = SpecDecoder(m, cache, 2, spec_k=0, max_len=48, device="cpu", use_graph=False)
+    dec.set_context([40, 40], [1, 2])
+    for _ in range(6):
+        dec.step()
+    with pytest.raises(RuntimeError, match="refused"):
+        for _ in range(4):
+            dec.step()
