@@ -8,23 +8,11 @@
 // (src/models/k3/router.rs:136-143) and implemented here.
 #include "common.cuh"
 #include "host_utils.h"
+#include "router_block.cuh"
 
 using namespace mary;
 
 namespace {
-
-struct MaxIdx { float v; int i; };
-__device__ __forceinline__ MaxIdx better(MaxIdx a, MaxIdx b) {      // larger value, then smaller index
-  return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
-}
-__device__ __forceinline__ MaxIdx warp_best(MaxIdx a) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    MaxIdx b{__shfl_xor_sync(0xffffffffu, a.v, o), __shfl_xor_sync(0xffffffffu, a.i, o)};
-    a = better(a, b);
-  }
-  return a;
-}
 
 // Philox-4x32-10 counter RNG (one call -> 4 uniforms).
 __device__ __forceinline__ uint4 philox(uint2 key, uint4 ctr) {
@@ -171,117 +159,19 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, int64_t ld,
 }
 
 
-// The same router with one CTA (8 warps) per token: decode batches hold tens to hundreds of tokens, and a single warp
-// walking ~400 experts through group scoring and k arg-max rounds is a serial chain of thousands of dependent instructions
-// (tens of microseconds).  Here every thread owns at most two experts; the groups are scored by different warps at once; every
-// warp extracts the k best of its own 1/8 of the experts and warp 0 merges the 8 k candidates.  Same results, same tie rule.
+// The same router with one CTA (8 warps) per token (router_block.cuh): same results, same tie rule.
 __global__ void __launch_bounds__(256)
 router_topk_block_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ bias, int T, int E, int k, int mode,
                          int n_group, int topk_group, float scale, int renorm, int* __restrict__ out_idx, float* __restrict__ out_w,
                          int* __restrict__ counts, int* __restrict__ flag) {
   pdl_sync();
-  __shared__ float s_sc[512], s_sel[512], s_g[32], s_red[8];
-  __shared__ float s_cv[256];
-  __shared__ int s_ci[256];
-  __shared__ uint32_t s_keep;
-  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const float* row = logits + (int64_t)t * ld;
-  float v0 = -INFINITY, v1 = -INFINITY;
-  bool bad = false;
-  if (tid < E) { v0 = row[tid]; bad |= !isfinite(v0); }
-  if (tid + 256 < E) { v1 = row[tid + 256]; bad |= !isfinite(v1); }
-  if (bad && flag) atomicExch(flag, 1);
-  if (mode == 0) {
-    float mx = warp_max(fmaxf(v0, v1));
-    if (lane == 0) s_red[warp] = mx;
-    __syncthreads();
-    mx = s_red[0];
-#pragma unroll
-    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, s_red[w]);
-    __syncthreads();
-    const float e0 = tid < E ? __expf(v0 - mx) : 0.f, e1 = tid + 256 < E ? __expf(v1 - mx) : 0.f;
-    float sum = warp_sum(e0 + e1);
-    if (lane == 0) s_red[warp] = sum;
-    __syncthreads();
-    sum = 0.f;
-#pragma unroll
-    for (int w = 0; w < 8; ++w) sum += s_red[w];
-    if (tid < E) { s_sc[tid] = e0 / sum; s_sel[tid] = e0 / sum; }
-    if (tid + 256 < E) { s_sc[tid + 256] = e1 / sum; s_sel[tid + 256] = e1 / sum; }
-  } else {
-    if (tid < E) { const float sg = 1.0f / (1.0f + __expf(-v0)); s_sc[tid] = sg; s_sel[tid] = sg + (bias ? bias[tid] : 0.f); }
-    if (tid + 256 < E) { const float sg = 1.0f / (1.0f + __expf(-v1)); s_sc[tid + 256] = sg; s_sel[tid + 256] = sg + (bias ? bias[tid + 256] : 0.f); }
-  }
-  __syncthreads();
-  if (mode == 1 && n_group > 1) {
-    const int gsz = E / n_group;
-    for (int g = warp; g < n_group; g += 8) {               // group score = sum of the two best biased scores in the group
-      MaxIdx b1{-INFINITY, 0x7fffffff};
-      for (int m = lane; m < gsz; m += 32) b1 = better(b1, MaxIdx{s_sel[g * gsz + m], g * gsz + m});
-      b1 = warp_best(b1);
-      MaxIdx b2{-INFINITY, 0x7fffffff};
-      for (int m = lane; m < gsz; m += 32) { const int e = g * gsz + m; if (e != b1.i) b2 = better(b2, MaxIdx{s_sel[e], e}); }
-      b2 = warp_best(b2);
-      if (lane == 0) s_g[g] = b1.v + b2.v;
-    }
-    __syncthreads();
-    if (warp == 0) {
-      uint32_t keep = 0;
-      const float mine = lane < n_group ? s_g[lane] : -INFINITY;
-      for (int r = 0; r < topk_group; ++r) {
-        MaxIdx b = warp_best(MaxIdx{(lane < n_group && !((keep >> lane) & 1u)) ? mine : -INFINITY, lane});
-        keep |= 1u << b.i;
-      }
-      if (lane == 0) s_keep = keep;
-    }
-    __syncthreads();
-    const uint32_t keep = s_keep;
-    if (tid < E && !((keep >> (tid / gsz)) & 1u)) s_sel[tid] = -INFINITY;
-    if (tid + 256 < E && !((keep >> ((tid + 256) / gsz)) & 1u)) s_sel[tid + 256] = -INFINITY;
-    __syncthreads();
-  }
-  // every warp: the k best of its own slice of the experts
-  {
-    const int chunk = (E + 7) / 8;                            // <= 64: two experts per lane
-    const int base = warp * chunk;
-    const int ea = base + lane, eb = base + lane + 32;
-    float a = (lane < chunk && ea < E) ? s_sel[ea] : -INFINITY;
-    float b = (lane + 32 < chunk && eb < E) ? s_sel[eb] : -INFINITY;
-    for (int r = 0; r < k; ++r) {
-      MaxIdx best = warp_best(better(MaxIdx{a, ea}, MaxIdx{b, eb}));
-      if (best.i == ea) a = -INFINITY;
-      if (best.i == eb) b = -INFINITY;
-      if (lane == 0) { s_cv[warp * k + r] = best.v; s_ci[warp * k + r] = best.i; }
-    }
-  }
-  __syncthreads();
-  if (warp == 0) {
-    // merge 8 k candidates (each warp's list is in descending order, which the merge does not need)
-    const int n = 8 * k;
-    float cv[8];
-    int ci[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { const int c = lane + 32 * j; cv[j] = c < n ? s_cv[c] : -INFINITY; ci[j] = c < n ? s_ci[c] : 0x7fffffff; }
-    float wsum = 0.f, mine_w = 0.f;
-    int mine_i = 0;
-    for (int r = 0; r < k; ++r) {
-      MaxIdx best{-INFINITY, 0x7fffffff};
-#pragma unroll
-      for (int j = 0; j < 8; ++j) best = better(best, MaxIdx{cv[j], ci[j]});
-      best = warp_best(best);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) if (ci[j] == best.i) cv[j] = -INFINITY;
-      const float wv = (best.i >= 0 && best.i < E) ? s_sc[best.i] : 0.f;
-      wsum += wv;
-      if (lane == r) { mine_w = wv; mine_i = best.i; }
-    }
-    if (lane < k) {
-      float wv = mine_w;
-      if (renorm) wv = wv / (wsum + (mode == 1 ? 1e-20f : 0.f));
-      out_idx[(int64_t)t * k + lane] = mine_i;
-      out_w[(int64_t)t * k + lane] = wv * scale;
-      if (counts) atomicAdd(&counts[mine_i], 1);
-    }
+  __shared__ RouterSmem S;
+  const int t = blockIdx.x;
+  router_block(logits + (int64_t)t * ld, bias, E, k, mode, n_group, topk_group, scale, renorm, S, flag);
+  if ((int)threadIdx.x < k) {
+    out_idx[(int64_t)t * k + threadIdx.x] = S.out_i[threadIdx.x];
+    out_w[(int64_t)t * k + threadIdx.x] = S.out_w[threadIdx.x];
+    if (counts) atomicAdd(&counts[S.out_i[threadIdx.x]], 1);
   }
 }
 

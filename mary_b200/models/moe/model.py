@@ -7,6 +7,8 @@ sharded over the group (tensor parallel), routed experts are sharded by expert i
 partial sums of the hidden state that one reduction per block combines."""
 from __future__ import annotations
 
+import os
+
 import torch
 from torch import nn
 
@@ -148,6 +150,56 @@ class MoEFFN(nn.Module):
         return ops.router_topk(logits, c.num_experts_per_tok, c.router, self.router_bias, c.n_group, c.topk_group,
                                c.routed_scaling_factor, c.norm_topk_prob)
 
+    FUSED_MAX_ROWS = 512      # decode-sized batches take the four-launch pipeline; larger ones the planned path with 128-row tiles
+
+    def fused_ctx(self, x):
+        """The four-launch expert pipeline (``parallel.ep_fused``) for this batch, or ``None`` when the batch is not decode-sized,
+        lives on the CPU, or ``MARY_MOE_FUSED=0`` asks for the planned path."""
+        if not x.is_cuda or self.experts is None or os.environ.get("MARY_MOE_FUSED", "1") == "0":
+            return None
+        from ...parallel import ep_fused
+        c, par, T = self.c, self.par, x.shape[0]
+        E, k = c.n_routed_experts, c.num_experts_per_tok
+        if E > 512 or k * 8 > 256 or c.hidden_size * 4 > 48 * 1024:
+            return None
+        store = par.__dict__.setdefault("_fused_moe", {})
+        a2a = par.ep_mode == "a2a" and par.ep_size > 1
+        if a2a:
+            cap = getattr(par, "ep_decode_cap", None)
+            if cap is None or T > cap or (par.ep_size * cap * (k + 1) + 31) // 32 + self.e_local + 1 > ep_fused.MAX_TILES:
+                return None
+            if ("a2a", cap) not in store:        # collective: every rank reaches its first MoE layer with the same shapes
+                store[("a2a", cap)] = ep_fused.distributed(par.ep_rank, par.ep_size, E, c.hidden_size, c.moe_intermediate_size, cap, k,
+                                                           self.shared_in_experts, x.device)
+            return store[("a2a", cap)]
+        if T > self.FUSED_MAX_ROWS:
+            return None
+        fits = [v for (kind, cap), v in store.items() if kind == "local" and cap >= T]
+        if fits:
+            return min(fits, key=lambda v: v.t_cap)
+        cap = (T + 31) // 32 * 32
+        # worst case of token tiles: every entry's tile plus one ragged tile per expert
+        if (T * (k + 1) + 31) // 32 + self.e_local + 1 > ep_fused.MAX_TILES:
+            return None
+        store[("local", cap)] = ep_fused.FusedMoE(par.ep_rank, par.ep_size, E, c.hidden_size, c.moe_intermediate_size, cap, k,
+                                                  self.shared_in_experts, x.device, True)
+        return store[("local", cap)]
+
+    def forward_fused(self, fm, x, h, next_norm):
+        """``h += ffn(x)`` and the next block's normed input through the four-launch pipeline.  Returns ``(x_next | None, h)``."""
+        c, par = self.c, self.par
+        logits = ops.linear_f32(x, self.w_router)
+        router = dict(mode=c.router, bias=self.router_bias, n_group=c.n_group, topk_group=c.topk_group, scale=c.routed_scaling_factor,
+                      renorm=c.norm_topk_prob)
+        add = ops.linear(ops.linear_glu(x, self.shared.w_gu, c.act), self.shared.w_down) if self.shared is not None else None
+        if fm.local_only and par.ep_size > 1:
+            # replicated tokens: this rank's experts give a partial sum that the group reduces before it joins the residual
+            f = par.reduce(fm.forward(x, logits, router, self.experts, add=add))
+            if next_norm is None:
+                return None, (h.float() + f.float()).to(h.dtype)
+            return ops.add_rmsnorm(f, h, next_norm, c.rms_norm_eps)
+        return fm.forward(x, logits, router, self.experts, add=add, res=h, w_norm=next_norm, eps=c.rms_norm_eps)
+
     def forward(self, x):
         idx, w = self.route(x)
         if self.par.ep_mode == "a2a" and self.par.ep_size > 1:
@@ -201,6 +253,10 @@ class MoELayer(nn.Module):
         """``x`` normed input, ``h`` residual.  Returns ``(next normed x, h)``."""
         a = self.par.reduce(self.attn(x, meta, cache))
         x, h = ops.add_rmsnorm(a, h, self.ln_ffn, self.c.rms_norm_eps)
+        if not self.dense:
+            fm = self.ffn.fused_ctx(x)
+            if fm is not None:
+                return self.ffn.forward_fused(fm, x, h, next_norm)
         f = self.par.reduce(self.ffn(x))
         if next_norm is None:
             return None, (h.float() + f.float()).to(h.dtype)

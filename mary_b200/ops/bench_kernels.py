@@ -413,6 +413,29 @@ def bench_ep(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 
     assert K.last_status() == 0
 
 
+def bench_epf(world: int = 8, T: int = 48, E: int = 384, H: int = 7168, F: int = 2048, k: int = 8, iters: int = 5, shared: int = 1):
+    """The same layer through the four-launch pipeline (route + dispatch by atomics, counter-mode GEMMs with the quantising GLU
+    epilogue, combine), all ranks on this device phase by phase; the router GEMM is not part of either figure."""
+    from . import cuda as K
+    from .moe import NVFP4Experts
+    from ..parallel.ep_fused import emulate, emulated_ranks
+    e_local = E // world
+    slab = NVFP4Experts.random(e_local + (1 if shared else 0), H, F, "cuda", seed=0)
+    ranks = emulated_ranks(world, E, H, F, T, k, bool(shared), "cuda")
+    xs = [torch.randn(T, H, device="cuda").bfloat16() for _ in range(world)]
+    lgs = [torch.randn(T, E, device="cuda") for _ in range(world)]
+    router = dict(mode="sigmoid", bias=torch.zeros(E, device="cuda"), n_group=8, topk_group=4, scale=2.5, renorm=True)
+    exs = [slab] * world
+    ms = time_op(lambda: emulate(ranks, exs, xs, lgs, router), iters=iters)
+    torch.cuda.profiler.start()
+    emulate(ranks, exs, xs, lgs, router)
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"ep fused layer, {world} ranks on one device, T={T}/rank E={E} H={H} F={F} k={k} shared={shared}: {ms:.3f} ms for all ranks, "
+          f"{ms / world * 1e3:.1f} us per rank")
+    assert K.last_status() == 0
+
+
 if __name__ == "__main__":
     # ``gemm M N K`` / ``attn B L Hq Hkv D window`` / ``fa B L Hq Hkv DK DV window`` / ``mla B L Hq q_len`` / ``moe E H F T k`` run that one case only
     what = sys.argv[1] if len(sys.argv) > 1 else "all"
@@ -455,5 +478,7 @@ if __name__ == "__main__":
         bench_f5(*nums)
     if what == "ep":
         bench_ep(*nums)
+    if what == "epf":
+        bench_epf(*nums)
     if what in ("moe", "all"):
         bench_moe(*(nums if what == "moe" else []))

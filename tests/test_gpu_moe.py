@@ -152,3 +152,199 @@ def test_grouped_bf16_experts_match_the_per_expert_loop(E, H, F, T, k, act):
 def mary_status_ok():
     from mary_b200.ops import cuda as K
     return K.lib().mary_last_status() == 0
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# The four-launch expert pipeline (route + dispatch, counter-mode GEMMs, combine)
+def _router(mode, E, scale=1.0):
+    if mode == "softmax":
+        return dict(mode="softmax", bias=None, n_group=1, topk_group=1, scale=1.0, renorm=True)
+    return dict(mode="sigmoid", bias=torch.randn(E, device="cuda") * 0.1, n_group=4, topk_group=2, scale=scale, renorm=True)
+
+
+def _route(lg, k, r):
+    from mary_b200.ops import cuda
+    return cuda.router_topk(lg, k, r["mode"], r["bias"], r["n_group"], r["topk_group"], r["scale"], r["renorm"])
+
+
+@pytest.mark.parametrize("E,H,F,T,k,shared,mode", [(8, 512, 256, 40, 2, False, "softmax"), (16, 1024, 512, 96, 4, True, "sigmoid"),
+                                                  (32, 512, 256, 3, 8, True, "softmax")])
+def test_fused_pipeline_equals_planned_path_on_one_rank(E, H, F, T, k, shared, mode):
+    """Route + dispatch by atomics, counter-mode GEMMs with the quantising GLU epilogue and the combine kernel give the SAME bits
+    as router -> plan -> quantise -> GEMM -> quantise -> GEMM -> un-permute: rows are independent and slots are summed in the
+    same order.  Three calls in a row: the counters are back to zero and the epoch has advanced after each."""
+    from mary_b200.ops import cuda, cuda_moe
+    from mary_b200.parallel.ep_fused import FusedMoE
+    torch.manual_seed(E + T)
+    ex = NVFP4Experts.random(E + (1 if shared else 0), H, F, "cuda", std=0.05, seed=7)
+    fm = FusedMoE(0, 1, E, H, F, 128, k, shared, "cuda", True)
+    r = _router(mode, E, 2.5)
+    for call in range(3):
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        lg = torch.randn(T, E, device="cuda")
+        got = fm.forward(x, lg, r, ex)
+        idx, w = _route(lg, k, r)
+        if shared:
+            idx = torch.cat([idx.to(torch.int32), torch.full((T, 1), E, dtype=torch.int32, device="cuda")], 1)
+            w = torch.cat([w.float(), torch.ones(T, 1, device="cuda")], 1)
+        want = cuda_moe.experts_forward(x, idx, w, ex, None, 32)
+        torch.cuda.synchronize()
+        assert cuda.last_status() == 0
+        assert torch.equal(fm.idx_out[:T], idx.to(torch.int32)) and torch.equal(fm.w_out[:T], w.float())
+        assert torch.equal(got, want), (call, _rel(got, want))
+        assert int(fm.bufs["cnt"].abs().sum()) == 0 and int(fm.epoch) == call + 1
+        assert _rel(got.cpu(), experts_reference(x, idx, w, ex)) < 3e-2
+
+
+def test_fused_pipeline_adds_residual_and_norms():
+    from mary_b200.ops import cuda, cuda_moe
+    from mary_b200.parallel.ep_fused import FusedMoE
+    torch.manual_seed(5)
+    E, H, F, T, k = 8, 512, 256, 33, 2
+    ex = NVFP4Experts.random(E, H, F, "cuda", std=0.05, seed=8)
+    fm = FusedMoE(0, 1, E, H, F, 64, k, False, "cuda", True)
+    r = _router("softmax", E)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    lg = torch.randn(T, E, device="cuda")
+    add = torch.randn(T, H, device="cuda").bfloat16()
+    h = torch.randn(T, H, device="cuda").bfloat16()
+    gain = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    f = fm.forward(x, lg, r, ex, add=add)
+    want_y, want_h = cuda.add_rmsnorm(f, h.clone(), gain, 1e-6)
+    h2 = h.clone()
+    y, h_out = fm.forward(x, lg, r, ex, add=add, res=h2, w_norm=gain, eps=1e-6)
+    torch.cuda.synchronize()
+    assert cuda.last_status() == 0 and h_out.data_ptr() == h2.data_ptr()
+    assert torch.equal(h2, want_h) and torch.equal(y, want_y)
+    h3 = h.clone()
+    y3, _ = fm.forward(x, lg, r, ex, add=add, res=h3, w_norm=None)
+    assert y3 is None and torch.equal(h3, want_h)
+
+
+@pytest.mark.parametrize("world,shared", [(2, False), (4, True), (8, True)])
+def test_fused_pipeline_expert_parallel_emulated(world, shared):
+    """All ranks on one device, phase by phase (every waiting kernel runs after the kernels it waits for): each rank's output
+    equals the single-rank expert MLP over all experts, bit for bit, on two layer calls in a row."""
+    from mary_b200.ops import cuda, cuda_moe
+    from mary_b200.models.moe.shard import slice_experts
+    from mary_b200.parallel.ep_fused import emulate, emulated_ranks
+    torch.manual_seed(world)
+    E, H, F, k, T = 8 * world, 512, 256, 2, 40
+    ex = NVFP4Experts.random(E + (1 if shared else 0), H, F, "cuda", std=0.05, seed=3)
+    ranks = emulated_ranks(world, E, H, F, 64, k, shared, "cuda")
+    exs = [slice_experts(ex, r, world, tail=1 if shared else 0) for r in range(world)]
+    r_cfg = _router("sigmoid", E, 2.5)
+    for call in range(2):
+        xs = [torch.randn(T - 3 * r, H, device="cuda").bfloat16() for r in range(world)]
+        lgs = [torch.randn(x.shape[0], E, device="cuda") for x in xs]
+        outs = emulate(ranks, exs, xs, lgs, r_cfg)
+        torch.cuda.synchronize()
+        assert cuda.last_status() == 0
+        for x, lg, got in zip(xs, lgs, outs):
+            idx, w = _route(lg, k, r_cfg)
+            n = x.shape[0]
+            if shared:
+                idx = torch.cat([idx.to(torch.int32), torch.full((n, 1), E, dtype=torch.int32, device="cuda")], 1)
+                w = torch.cat([w.float(), torch.ones(n, 1, device="cuda")], 1)
+            want = cuda_moe.experts_forward(x, idx, w, ex, None, 32)
+            assert torch.equal(got, want), (call, _rel(got, want))
+        for rk in ranks:
+            assert int(rk.bufs["cnt"].abs().sum()) == 0 and int(rk.epoch) == call + 1
+
+
+def test_fused_pipeline_replicated_tokens_partial_sums():
+    """``local_only`` contexts of a 2-rank group with replicated tokens: every rank serves its own experts (and the shared expert
+    for its share of the tokens); the partial sums add up to the single-rank result."""
+    from mary_b200.ops import cuda, cuda_moe
+    from mary_b200.models.moe.shard import slice_experts
+    from mary_b200.parallel.ep_fused import FusedMoE
+    torch.manual_seed(11)
+    world, E, H, F, k, T = 2, 16, 512, 256, 2, 48
+    ex = NVFP4Experts.random(E + 1, H, F, "cuda", std=0.05, seed=4)
+    r_cfg = _router("softmax", E)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    lg = torch.randn(T, E, device="cuda")
+    parts = []
+    for rank in range(world):
+        fm = FusedMoE(rank, world, E, H, F, 64, k, True, "cuda", True)
+        parts.append(fm.forward(x, lg, r_cfg, slice_experts(ex, rank, world, tail=1)).float())
+    idx, w = _route(lg, k, r_cfg)
+    idx = torch.cat([idx.to(torch.int32), torch.full((T, 1), E, dtype=torch.int32, device="cuda")], 1)
+    w = torch.cat([w.float(), torch.ones(T, 1, device="cuda")], 1)
+    want = cuda_moe.experts_forward(x, idx, w, ex, None, 32)
+    assert cuda.last_status() == 0
+    assert _rel(sum(parts), want) < 1e-2
+
+
+def test_fused_pipeline_refuses_batches_beyond_its_slabs():
+    from mary_b200.parallel.ep_fused import FusedMoE
+    fm = FusedMoE(0, 1, 8, 512, 256, 32, 2, False, "cuda", True)
+    ex = NVFP4Experts.random(8, 512, 256, "cuda", std=0.05, seed=1)
+    with pytest.raises(ValueError):
+        fm.forward(torch.zeros(33, 512, device="cuda").bfloat16(), torch.zeros(33, 8, device="cuda"), _router("softmax", 8), ex)
+
+
+@pytest.mark.parametrize("nt,T", [(32, 70), (128, 300)])
+def test_glu_epilogue_quantises_like_the_standalone_quantiser(nt, T):
+    """GEMM -> bf16 -> quantise and GEMM with the quantising epilogue must write the same code and scale bytes."""
+    from mary_b200.ops import cuda, cuda_moe
+    from mary_b200.ops.cuda import _p, _stream, check, declare, lib
+    declare("mary_gemm_nvfp4_grouped_glu_q", "ppppppppp" + "iiiliis")
+    torch.manual_seed(nt)
+    E, H, F, k = 4, 512, 256, 2
+    ex = NVFP4Experts.random(E, H, F, "cuda", std=0.05, seed=2)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    idx, w = cuda.router_topk(torch.randn(T, E, device="cuda"), k, "softmax")
+    plan = cuda_moe.moe_plan(idx, E, nt)
+    xq, sfx = cuda_moe.quantize_entries(x, plan, k, identity=False)
+    h = cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, F, H, E, ex.act)
+    hq, sfh = cuda_moe.quantize_entries(h, plan, k, identity=True)
+    hq2 = torch.zeros_like(hq)
+    sfh2 = torch.zeros_like(sfh)
+    check(lib().mary_gemm_nvfp4_grouped_glu_q(_p(ex.w13_q), _p(ex.w13_sf), _p(ex.w13_s2), _p(xq), _p(sfx), _p(plan.tiles), _p(plan.meta),
+                                              _p(hq2), _p(sfh2), E, F, H, plan.max_rows, nt, 2, _stream()), "gemm_nvfp4_grouped")
+    torch.cuda.synchronize()
+    assert cuda.last_status() == 0
+    rows = plan.row_of[plan.row_of >= 0].long()
+    assert torch.equal(hq2[rows], hq[rows])
+    tiles = (rows // nt).unique()
+    a = unswizzle_scales(sfh2.cpu(), sfh2.shape[0] * 128, F // 16).view(-1, 128, F // 16)
+    b = unswizzle_scales(sfh.cpu(), sfh.shape[0] * 128, F // 16).view(-1, 128, F // 16)
+    rr = rows.cpu()
+    assert torch.equal(a[rr // nt, rr % nt], b[rr // nt, rr % nt]) and len(tiles) > 0
+
+
+def test_grouped_gemm_flagship_shape_against_f64_arbiter():
+    """The K3-class expert shapes (K = 7168 -> 28 K-stages for w13, 16 weight tiles of F = 2048; K = 2048 for w2) on 16 experts:
+    f64 arbiter over the SAME quantised operands.  The f32 accumulators are compared before any bf16 rounding would hide an
+    error: the quantised intermediate of the GLU epilogue equals the quantised arbiter value, and the w2 output (bf16) is
+    within half a bf16 ulp of the arbiter."""
+    from mary_b200.ops import cuda, cuda_moe
+    torch.manual_seed(21)
+    E, H, F, T, k = 16, 7168, 2048, 48, 2
+    ex = NVFP4Experts.random(E, H, F, "cuda", std=0.02, seed=6)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    idx, w = cuda.router_topk(torch.randn(T, E, device="cuda"), k, "softmax")
+    plan = cuda_moe.moe_plan(idx, E, 32)
+    xq, sfx = cuda_moe.quantize_entries(x, plan, k, identity=False)
+    h = cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, F, H, E, ex.act)
+    hq, sfh = cuda_moe.quantize_entries(h, plan, k, identity=True)
+    y = cuda_moe.grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, H, F, E, None)
+    torch.cuda.synchronize()
+    assert cuda.last_status() == 0
+    xd = ref.dequantize_nvfp4(*ref.quantize_nvfp4(x.cpu())).double()
+    row_of, idx_c = plan.row_of.cpu().view(T, k), idx.cpu()
+    worst_h = worst_y = 0.0
+    for e in idx_c.unique().tolist():
+        t, j = (idx_c == e).nonzero(as_tuple=True)
+        rows = row_of[t, j].long()
+        w13 = ex.dense("w13", e).double()
+        g, u = xd[t] @ w13[:F].T, xd[t] @ w13[F:].T
+        h64 = torch.nn.functional.silu(g) * u
+        got_h = h[rows].cpu().double()
+        worst_h = max(worst_h, ((got_h - h64).abs() / (h64.abs() + 1e-3)).max().item())
+        hd = ref.dequantize_nvfp4(*ref.quantize_nvfp4(h[rows].cpu())).double()
+        y64 = hd @ ex.dense("w2", e).double().T
+        worst_y = max(worst_y, ((y[rows].cpu().double() - y64).abs() / (y64.abs() + 1e-3)).max().item())
+    # bf16 keeps 8 bits: half an ulp is 2^-9 relative; the f32 accumulation error over K = 7168 is far below that
+    assert worst_h < 2 ** -8 and worst_y < 2 ** -8, (worst_h, worst_y)
