@@ -110,6 +110,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--arm", default="both", choices=["both", "ours", "library"],
+                    help="ours: the product arm only; library: only the same-box library baseline (torch.matmul / torch._grouped_mm / NCCL, none "
+                         "of this package's kernels); both: the product arm, then the library arm on the same GPUs, and vs_baseline = ours / library")
+    ap.add_argument("--library-steps", type=int, default=4, help="timed steps of the library arm (after 2 warm-up steps)")
+    ap.add_argument("--library-limit", type=float, default=240.0, help="seconds after which a stalled library arm is abandoned")
     ap.add_argument("--model", default="k3", choices=["k3", "inkling", "gemma12b", "tiny"],
                     help="k3 is the headline; the others time the remaining workload configurations with the same harness")
     ap.add_argument("--ep", default="auto", choices=["auto", "replicated", "a2a"],
@@ -180,6 +185,25 @@ def main():
     if args.comm == "auto":       # dense decoder: reduce-scatter / all-gather arm (measured faster at 2 and 8 GPUs); MoE decoders: all-reduce kernels
         args.comm = "sp" if (is_gemma and world > 1) else "fused"
     say(f"model {cfg.name}, {world} rank(s), batch {B}, ctx {ctx}, spec {k}, comm {args.comm}")
+    lib_layout = "single" if world == 1 else ("a2a" if a2a else "replicated")
+    if args.arm == "library":
+        assert args.model == "k3", "the library arm restates the K3-class decoder"
+        from mary_b200.library_arm import run_library_arm
+        sampler = ClockSampler(local)
+        sampler.start()
+        res = run_library_arm(cfg, rank, world, lib_layout, B_local, ctx, k, args.steps, W, dev, limit_s=args.library_limit)
+        clocks = sampler.stop()
+        if rank == 0:
+            print(json.dumps({"metric": "decode tok/s (max over ranks), K3-class MLA + MoE, 2-token MTP speculation", "impl": "library",
+                              "value": round(res["tokens_per_s"], 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": W,
+                              "ms_per_step": round(res["ms_per_step"], 4), "higher_is_better": True, "scaling": "strong",
+                              "dtype": "bf16 activations, bf16 experts", "data": "synthetic token ids, random-init weights, synthetic KV context",
+                              "config": {"model": cfg.name, "layers": cfg.num_hidden_layers, "global_batch": B, "seq_len": ctx, "spec_tokens": k,
+                                         "parallelism": lib_layout}, "library": res, "clocks": clocks,
+                              "e2e": {"value": round(res["e2e_tokens_per_s"], 2), "unit": "tokens/s"}}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if world > 1 and args.comm == "nccl":
         # the library arm is launched op by op: recording NCCL collectives into the step graph is not relied upon here
         args.no_graph = True
@@ -355,21 +379,31 @@ def main():
     status = K.last_status()
     say(f"end-to-end loop done, kernel status {status}")
 
+    baseline = {"state": "not run"}
+    graph_used = dec.graph is not None
+    head_kind = "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated"
+
     def emit_line(ttft, ttft_note):
         if rank == 0:
             tok_per_seq_step = emitted / (B_global * args.steps)
+            base_ok = isinstance(baseline.get("tokens_per_s"), float)
             line = {
                 "metric": "decode tok/s (max over ranks), K3-class MLA + NVFP4 MoE, 2-token MTP speculation" if args.model == "k3" else f"decode tok/s {cfg.name}",
                 "value": round(value, 2), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": W,
-                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "ms_per_step": round(ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": round(value / baseline["tokens_per_s"], 3) if base_ok else None,
+                "baseline_ms_per_step": round(baseline["ms_per_step"], 4) if base_ok else None,
+                "baseline": dict(baseline, what="same-box library arm of this repository (torch.matmul, torch._grouped_mm, NCCL; bf16 experts, "
+                                              "eager launches), same model, batch, context, speculation and layout; the reference itself cannot "
+                                              "be built here and publishes no number at this configuration"),
                 "dtype": "bf16 activations, NVFP4 experts", "data": "synthetic token ids, random-init weights, synthetic KV context",
                 "impl": "ours",
                 "config": {"model": cfg.name + (" (REDUCED layers: debug)" if reduced else ""), "layers": cfg.num_hidden_layers,
                            "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,
                            "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
                                            f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
-                           "kv_page_tokens": page, "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": dec.graph is not None,
-                           "lm_head": "vocabulary-parallel" if getattr(model, "vocab_parallel", False) else "replicated",
+                           "kv_page_tokens": page, "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": graph_used,
+                           "lm_head": head_kind,
                            "expert_slabs_resident": slabs, "moe_layers": n_moe,
                            "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",
                            "accepted_drafts_per_step": round(tok_per_seq_step - 1, 4)},
@@ -378,7 +412,8 @@ def main():
                 "ttft_note": ttft_note,
                 "clocks": clocks,
                 "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "h2d_bytes_per_step": B * R * 4,
-                        "d2h_bytes_per_step": B * R * 4 * 2 + B * 4},
+                        "d2h_bytes_per_step": B * R * 4 * 2 + B * 4,
+                        "vs_baseline": round(e2e_value / baseline["e2e_tokens_per_s"], 3) if base_ok else None},
                 "gpu_launches": launches_per_step * args.steps,
                 "kernel_status": status, "build_seconds": round(build_s, 1),
             }
@@ -398,6 +433,7 @@ def main():
     stall.start()
     # ---------------------------------------------------------------- TTFT: a real prefill of one context
     ttft, ttft_note = None, "one context, all ranks"
+    pc = pd = None
     if not args.no_ttft:
         try:
             pc = PagedKVCache(spec["num_layers"], (ctx + 64) // page + 2, page, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16,
@@ -476,6 +512,36 @@ def main():
 
     done.set()
     stall.cancel()
+    # ---------------------------------------------------------------- the library arm on the same GPUs (the denominator of vs_baseline)
+    if args.arm == "both" and args.model == "k3" and not reduced:
+        done2 = threading.Event()
+
+        def give_up2():
+            if not done2.is_set():
+                baseline.update(state=f"abandoned: no result within {args.library_limit} s")
+                emit_line(ttft, ttft_note)
+                sys.stdout.flush()
+                os._exit(0)
+        stall2 = threading.Timer(args.library_limit, give_up2)
+        stall2.daemon = True
+        stall2.start()
+        try:
+            import gc
+            dec.graph = None
+            pc = pd = None
+            par.cp = None
+            del dec, cache, model
+            par.__dict__.pop("_fused_moe", None)
+            gc.collect()
+            torch.cuda.empty_cache()
+            from mary_b200.library_arm import run_library_arm
+            say("library arm")
+            baseline.update(run_library_arm(cfg, rank, world, lib_layout, B, ctx, k, args.library_steps, 2, dev, limit_s=args.library_limit), state="ok")
+            say(f"library arm: {baseline['ms_per_step']:.2f} ms/step")
+        except Exception as ex:
+            baseline.update(state=f"failed: {type(ex).__name__}: {ex}")
+        done2.set()
+        stall2.cancel()
     emit_line(ttft, ttft_note)
     faulthandler.cancel_dump_traceback_later()
     if world > 1:

@@ -2,8 +2,7 @@
 
 The ids are the reference's, so that facts written by either side name the same attributes
 (src/format.rs:52-127, src/leaf.rs:51-61, src/models/inkling/pile.rs:416-464,
-src/jsonfacts.rs:89-102, src/models/gemma/lora.rs:43-53).  Ids known here only in abbreviated
-form are completed deterministically from their visible prefix and suffix.
+src/jsonfacts.rs:55-102, src/models/gemma/lora.rs:43-53).
 """
 from __future__ import annotations
 
@@ -38,32 +37,29 @@ EXPERT_INDEX = id_hex("A6ED6DBA4BE63E4E34F2787DA84AD860")
 LAYER = id_hex("BCDDFBCFF89F67EE0B1E527C4872CED7")
 
 
-def _completed(prefix: str, suffix: str) -> bytes:
-    """An id known by prefix and suffix only: the middle is derived from both so it is stable."""
-    mid_len = 32 - len(prefix) - len(suffix)
-    mid = derived_id(prefix.encode(), suffix.encode()).hex().upper()[:mid_len]
-    return id_hex(prefix + mid + suffix)
-
-
-# JSON documents as facts (src/jsonfacts.rs:89-102)
-JSON_KEY = _completed("051B2382", "A999")
-JSON_STRING = _completed("65D08DFB", "3CAD")
-JSON_INT = _completed("8657CA9A", "ACA2")
-JSON_FLOAT = _completed("3B3EC066", "1017")
-JSON_BOOL = _completed("AB52DBDC", "9B61")
-DOCUMENT_ROOT = _completed("C3BE4C8C", "41F3")
-# the remaining three of the nine JSON attributes (parent link, array position, node type / doc name)
-JSON_PARENT = derived_id(b"mary_b200.json", b"parent")
-JSON_POS = derived_id(b"mary_b200.json", b"position")
-JSON_TYPE = derived_id(b"mary_b200.json", b"type")
-DOCUMENT_NAME = derived_id(b"mary_b200.json", b"document_name")
+# The storage crate's own metadata namespace (`metadata::tag`, `metadata::name`) is not part of the reference tree, so its two
+# attribute ids cannot be read there; these stand-ins are derived from the names.
+META_TAG = derived_id(b"triblespace.metadata", b"tag")
+META_NAME = derived_id(b"triblespace.metadata", b"name")
+# JSON documents as facts (src/jsonfacts.rs:55-102): nine attributes — member and index are the format's own (reused, same
+# encodings), six are minted there, and node types are `metadata::tag` discriminants
+JSON_KEY = id_hex("051B238236962081B98F5D44BD9FA999")        # Handle<UTF8>: an object member's key
+JSON_STRING = id_hex("65D08DFB670E7E3729BE6BC2C0073CAD")     # Handle<UTF8>
+JSON_INT = id_hex("8657CA9A8F2864E21FA1793AF47AACA2")        # I256BE
+JSON_FLOAT = id_hex("3B3EC066DE93041ACB2A26709CD11017")      # F64
+JSON_BOOL = id_hex("AB52DBDC419DE0ECC7D56632D7B29B61")       # Boolean
+DOCUMENT_ROOT = id_hex("C3BE4C8C259D1A1C1BB2BF8C19DF41F3")   # GenId: document node -> JSON root
+JSON_OBJECT = id_hex("0956A91F3198144BC1E1920467F9CE1A")     # type tags (src/jsonfacts.rs:55-70)
+JSON_ARRAY = id_hex("3DDDE71CF6B902D3CE15ABF3B3FE9A06")
+JSON_NULL = id_hex("CBD6C0C8FD1DA5A4851429ABAE3CFA9F")
+JSON_DOCUMENT = id_hex("686F919B71279386F31EB34A389E3241")
 # LoRA adapters (src/models/gemma/lora.rs:43-53)
-LORA_RANK = _completed("1A682F45", "AD69")
-LORA_ALPHA = _completed("198B03AF", "E724")
-LORA_ADAPTER = _completed("B93C4E66", "6ECF")
-LORA_PROJECTION = _completed("FF8335C1", "57E9")
-LORA_A = _completed("7CD7F0DC", "8828")
-LORA_B = _completed("1F21DAE6", "124D")
+LORA_RANK = id_hex("1A682F45CE40171DD5C6FDB4F086AD69")       # U256BE
+LORA_ALPHA = id_hex("198B03AF556B7505CCC9ABD4A1D6E724")      # F64
+LORA_ADAPTER = id_hex("B93C4E66F4B9553BF0E8B5DBAD116ECF")    # GenId, repeated on the LoRA set entity
+LORA_PROJECTION = id_hex("FF8335C187823A267E26B4E33EF157E9") # ShortString
+LORA_A = id_hex("7CD7F0DC8BDA328735A22DF02B4B8828")          # Handle<F32Array> [rank, in]
+LORA_B = id_hex("1F21DAE68652A4D8CAD973400F04124D")          # Handle<F32Array> [out, rank]
 # training-state checkpoint (this build: optimizer moments, step, RNG)
 TRAIN_STEP = derived_id(b"mary_b200.train", b"step")
 TRAIN_STATE = derived_id(b"mary_b200.train", b"state_blob")

@@ -128,11 +128,19 @@ def test_experts_in_layers_is_a_query():
 def test_jsonfacts_roundtrip_exact():
     st, tb = MemoryBlobStore(), TribleBuilder()
     doc = {"hidden_size": 256, "eps": 1e-6, "one": 1.0, "flag": True, "none": None, "name": "gemma",
-           "layers": ["a", "b", {"x": [1, 2.5, False]}], "nested": {"k": {"deep": -7}}, "big": 2 ** 70}
+           "layers": ["a", "b", {"x": [1, 2.5, False]}], "nested": {"k": {"deep": -7}}, "big": 2 ** 62, "twins": [1, 1],
+           "same": {"a": 1, "b": 1}}
     jsonfacts.save_document(st, tb, "config.json", doc)
     back = jsonfacts.load_document(st, tb.build(), "config.json")
-    assert back == doc and list(back) == list(doc)
+    assert back == doc and list(back) == sorted(doc)          # canonical key order
+    assert json.dumps(back, sort_keys=True) == json.dumps(doc, sort_keys=True)
     assert isinstance(back["one"], float) and isinstance(back["hidden_size"], int)
+    with pytest.raises(ValueError):                           # an integer beyond 64 bits is refused, not rounded
+        jsonfacts.save_document(st, TribleBuilder(), "x.json", {"big": 2 ** 70})
+    # the reference's attribute ids (src/jsonfacts.rs:89-102), so either side reads the other's facts
+    from mary_b200.format import schema as S
+    assert S.JSON_KEY.hex().upper() == "051B238236962081B98F5D44BD9FA999" and S.JSON_INT.hex().upper() == "8657CA9A8F2864E21FA1793AF47AACA2"
+    assert S.LORA_A.hex().upper() == "7CD7F0DC8BDA328735A22DF02B4B8828"
     with pytest.raises(LookupError):
         jsonfacts.load_document(st, tb.build(), "missing.json")
 
