@@ -90,7 +90,7 @@ gemm_nvfp4_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   pdl_sync();
   using C = Cfg<NT, GLU>;
   __shared__ Tile s_tiles[NT == 32 ? EP_MAX_TILES : 1];
-  __shared__ int s_cnt[NT == 32 ? EP_MAX_TILES : 1];       // arrival counters (at most one slot per tile-list entry's expert)
+  __shared__ unsigned short s_cnt[NT == 32 ? EP_MAX_TILES : 1];   // arrival counters, clamped to cap_e (<= 65535); 16 bits keep the 9-stage ring
   __shared__ int s_ntiles;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~uintptr_t(1023));
@@ -130,7 +130,7 @@ gemm_nvfp4_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
     {
       // the flags were acquired above, so the counters can be read with plain L2 loads, all of them at once
       const int* cnt = (const int*)ep.cnt[ep.rank];
-      for (int e = threadIdx.x; e < ep.n_slots; e += NTHREADS) s_cnt[e] = __ldcg(cnt + e);
+      for (int e = threadIdx.x; e < ep.n_slots; e += NTHREADS) { const int v = __ldcg(cnt + e); s_cnt[e] = (unsigned short)(v < ep.cap_e ? (v < 0 ? 0 : v) : ep.cap_e); }
     }
     __syncthreads();
     if (warp == 0) {
@@ -329,6 +329,8 @@ done:
 template <int NT, bool GLU>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, const FP4Params& p, const EpCtx& ep, cudaStream_t s) {
   using C = Cfg<NT, GLU>;
+  // dynamic ring + the kernel's static shared memory (tile list, counters) must fit the 227 KB a CTA can have
+  static_assert(C::SMEM + (NT == 32 ? EP_MAX_TILES * (sizeof(Tile) + 2) + 64 : 64) <= 227 * 1024, "shared memory budget");
   static MarySmemSlots smem_set = {};
   if (int rc = mary_ensure_dyn_smem((const void*)gemm_nvfp4_grouped_kernel<NT, GLU>, C::SMEM, &smem_set)) return rc;
   MARY_LAUNCH((gemm_nvfp4_grouped_kernel<NT, GLU>), mary_num_sms(), NTHREADS, C::SMEM, s, tw, tx, p, ep);
@@ -342,7 +344,7 @@ int run(const void* wq, const void* sfw, const float* scale2, const void* xq, co
   const int rows_total = glu ? 2 * n_out : n_out;
   if ((K % KSTEP) || (n_out % BM) || (nt != 32 && nt != 128)) return MARY_ERR_BAD_ARG;
   if ((q_out != nullptr) != (q_sf != nullptr) || (q_out && (!glu || (n_out % 64)))) return MARY_ERR_BAD_ARG;
-  if (ep_mode && (nt != 32 || !ctx || ctx->NT != 32 || (ctx->cap_e % 32) || ctx->rank < 0 || ctx->rank >= EP_MAX_RANKS ||
+  if (ep_mode && (nt != 32 || !ctx || ctx->NT != 32 || (ctx->cap_e % 32) || ctx->cap_e > 65535 || ctx->n_slots > EP_MAX_TILES || ctx->rank < 0 || ctx->rank >= EP_MAX_RANKS ||
                   (int64_t)ctx->n_slots * ctx->cap_e > x_rows || (ep_mode == 2 && !meta)))
     return MARY_ERR_BAD_ARG;
   FP4Params p;
