@@ -132,7 +132,9 @@ def _auto_split_k(M: int, N: int, K: int) -> int:
         while bn > 64 and tr * ((N + bn - 1) // bn) < 148:
             bn //= 2
         tiles = tr * ((N + bn - 1) // bn)
-    if tiles >= 100:
+    # measured on a B200 at 48 and 384 rows: from ~90 tiles on, and for short K (a tile's main loop is then a few stages long and
+    # the partial-tile traffic of a split outweighs the idle SMs), the unsplit kernel is the faster one
+    if tiles >= 90 or K <= 2048:
         return 1
     return max(1, min(K // 512, (148 + tiles - 1) // tiles))
 
