@@ -145,7 +145,8 @@ def main():
     W = max(args.warmup, 3)
     # a benchmark that stops making progress must end by itself: dump the stacks and exit after the limit
     import faulthandler
-    faulthandler.dump_traceback_later(int(os.environ.get("MARY_BENCH_LIMIT_S", "540")), exit=True)
+    from mary_b200.utils import flags
+    faulthandler.dump_traceback_later(flags.get("MARY_BENCH_LIMIT_S"), exit=True)
 
     def say(msg):
         if os.environ.get("RANK", "0") == "0":

@@ -368,6 +368,9 @@ def main(argv=None) -> int:
     cv.add_argument("--wav", required=True), cv.add_argument("--out", required=True), cv.add_argument("--codec", default="mimi")
     cv.set_defaults(fn=cmd_converse)
     a = ap.parse_args(argv)
+    if argv is None:                                  # run as a program: fail loudly on any thread
+        from ..utils import fatal
+        fatal.arm()
     return a.fn(a)
 
 

@@ -19,6 +19,9 @@ def main(argv=None) -> int:
     ap.add_argument("--max-new", type=int, default=64)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     a = ap.parse_args(argv)
+    if argv is None:                                  # run as a program: fail loudly on any thread
+        from ..utils import fatal
+        fatal.arm()
     dtype = torch.bfloat16 if a.device.startswith("cuda") else torch.float32
     t0 = time.time()
     lm = GemmaLM.from_pile(a.pile, device=a.device, dtype=dtype)

@@ -25,6 +25,9 @@ def main(argv=None) -> int:
     ap.add_argument("--out")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     a = ap.parse_args(argv)
+    if argv is None:                                  # run as a program: fail loudly on any thread
+        from ..utils import fatal
+        fatal.arm()
     from ..format.persist import default_key, load_config, publish_fragment, read_model_pile
     from ..format.selection import SelectedModelIndex
     from ..models.gemma4 import Gemma4Model, Gemma4TextConfig

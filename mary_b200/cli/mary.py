@@ -223,6 +223,14 @@ def cmd_encode(a) -> int:
     return 0
 
 
+def cmd_flags(a) -> int:
+    from ..utils import flags
+    for name, kind, default, value, doc in flags.table():
+        mark = "" if value == default else "   <- set"
+        print(f"{name:<22}{kind:<6}default {default!s:<10} value {value!s:<10}{mark}\n    {doc}")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="mary")
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -270,7 +278,12 @@ def main(argv=None) -> int:
     en = sub.add_parser("encode")
     en.add_argument("out"), en.add_argument("--pile"), en.add_argument("--tokenizer"), en.add_argument("--tokenizer-json")
     en.set_defaults(fn=cmd_encode)
+    fl = sub.add_parser("flags", help="the environment flags of the package with the values in effect")
+    fl.set_defaults(fn=cmd_flags)
     a = ap.parse_args(argv)
+    if argv is None:                                  # run as a program: fail loudly on any thread
+        from ..utils import fatal
+        fatal.arm()
     return a.fn(a)
 
 

@@ -26,7 +26,16 @@ def main(argv=None) -> int:
     ap.add_argument("--spec", type=int, default=None, help="drafts per step (default: the model's MTP depth, at most 2)")
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
     ap.add_argument("--trace", action="store_true")
+    ap.add_argument("--metrics", help="append JSON-lines run metrics (steps, requests, acceptance) to this file")
     a = ap.parse_args(argv)
+    if argv is None:                                  # run as a program: any uncaught exception on any thread ends the process
+        from ..utils import fatal
+        fatal.arm()
+    from ..runtime import budget
+    from ..runtime.pool import Pool, choose_memory_config
+    from ..utils.metrics import MetricsLog
+    choose_memory_config()
+    pool, mlog = Pool(), MetricsLog(a.metrics)
     from ..models.moe.weights import load_from_pile
     from ..pile import Pile
     from ..runtime.kv_cache import PagedKVCache
@@ -58,6 +67,14 @@ def main(argv=None) -> int:
     spec = model.kv_spec()
     max_len = prompts.shape[1] + (a.max_new + 2) * (1 + k) + 16
     pages = B * ((max_len + 15) // 16) + 2
+    if dev.type == "cuda":
+        # admission: the cache and the widest prefill chunk are priced against what is free BEFORE anything is allocated
+        free, _ = torch.cuda.mem_get_info(dev)
+        row = 576 * 2 if cfg.attention == "mla" else 2 * spec["kv_heads"] * spec["head_dim"] * 2
+        kv = budget.kv_bytes(spec["num_layers"], pages * 16, row)
+        if kv > free:
+            raise budget.AdmissionError(f"the paged cache of {B} x {max_len} tokens needs {kv / 2**30:.2f} GiB, {free / 2**30:.2f} GiB are free")
+        budget.check_prefill(cfg, min(512, prompts.shape[1]) * B, free - kv)
     cache = PagedKVCache(spec["num_layers"], pages, 16, spec["kv_heads"], spec["head_dim"], dtype=dtype, device=dev,
                          latent_dim=spec.get("latent_dim"))
     dec = SpecDecoder(model, cache, B, spec_k=k, max_len=(max_len + 15) // 16 * 16, device=dev, use_graph=dev.type == "cuda" and not a.trace)
@@ -65,6 +82,9 @@ def main(argv=None) -> int:
     first = dec.prefill(prompts)
     out = [[int(t)] for t in first.tolist()]
     ttft = time.time() - t0
+    pool.after_stage()                                # prefill activations go back before the decode loop captures its graph
+    for b in range(B):
+        mlog.emit("request", slot=b, prompt_tokens=int(prompts.shape[1]), ttft_s=ttft)
     if dev.type == "cuda":
         dec.capture()
     tracer = None
@@ -74,11 +94,13 @@ def main(argv=None) -> int:
     t0 = time.time()
     steps = 0
     while min(len(o) for o in out) < a.max_new:
+        ts = time.time()
         dec.step()
         steps += 1
         em, ne = dec.emitted.cpu().numpy(), dec.n_emitted.cpu().numpy()
         for b in range(B):
             out[b].extend(int(t) for t in em[b, :ne[b]])
+        mlog.emit("step", seconds=time.time() - ts, tokens_out=int(ne.sum()), accepted=int(ne.sum()) - B, drafted=B * k, slots=B)
     dt = time.time() - t0
     if tracer is not None:
         tracer.__exit__(None, None, None)
@@ -89,6 +111,9 @@ def main(argv=None) -> int:
     n = sum(len(o) - 1 for o in out)
     print(f"ttft {ttft * 1e3:.1f} ms; {steps} steps, {n / max(dt, 1e-9):.1f} tok/s over {B} slot(s), "
           f"{n / max(steps * B, 1):.2f} tokens per sequence-step", file=sys.stderr)
+    if a.metrics:
+        print("metrics: " + str(mlog.summary()), file=sys.stderr)
+    print(pool.line(), file=sys.stderr)
     pile.close()
     return 0
 

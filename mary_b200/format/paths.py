@@ -3,11 +3,13 @@
 from __future__ import annotations
 
 import os
+
+from ..utils import flags
 from pathlib import Path
 
 
 def models_dir() -> Path | None:
-    v = os.environ.get("MARY_MODELS")
+    v = flags.get("MARY_MODELS") or None
     return Path(v) if v else None
 
 

@@ -15,6 +15,7 @@ from torch import nn
 from ... import ops
 from ...ops import reference as ref
 from ...ops.moe import NVFP4Experts, experts_forward
+from ...utils import flags
 from .config import MoEConfig
 
 
@@ -155,7 +156,7 @@ class MoEFFN(nn.Module):
     def fused_ctx(self, x):
         """The four-launch expert pipeline (``parallel.ep_fused``) for this batch, or ``None`` when the batch is not decode-sized,
         lives on the CPU, or ``MARY_MOE_FUSED=0`` asks for the planned path."""
-        if not x.is_cuda or self.experts is None or os.environ.get("MARY_MOE_FUSED", "1") == "0":
+        if not x.is_cuda or self.experts is None or not flags.get("MARY_MOE_FUSED"):
             return None
         from ...parallel import ep_fused
         c, par, T = self.c, self.par, x.shape[0]
@@ -330,9 +331,11 @@ class MoEDecoder(nn.Module):
         h = ops.embed(ids, self.embed)
         x = ops.rmsnorm(h, self.layers[0].ln_attn, c.rms_norm_eps)
         n = len(self.layers)
+        from ...utils.trace import nvtx_range
         for i, layer in enumerate(self.layers):
             nxt = self.layers[i + 1].ln_attn if i + 1 < n else None
-            x, h = layer(x, h, meta, cache, nxt)
+            with nvtx_range(f"layer {i}"):
+                x, h = layer(x, h, meta, cache, nxt)
         return h
 
     def trunk_range(self, ids_or_h, lo: int, hi: int, meta, cache):

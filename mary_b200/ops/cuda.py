@@ -75,6 +75,17 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
+_NVTX = None
+
+
+def _nvtx() -> bool:
+    global _NVTX
+    if _NVTX is None:
+        from ..utils import flags
+        _NVTX = bool(flags.get("MARY_NVTX"))
+    return _NVTX
+
+
 LAUNCHES = 0      # launcher calls made through this module (each starts at least one kernel)
 TRACE = None      # an active mary_b200.utils.trace.Tracer, or None
 
@@ -84,6 +95,8 @@ def check(rc: int, what: str):
     LAUNCHES += 1
     if TRACE is not None:
         TRACE.mark(what)
+    if _nvtx():
+        torch.cuda.nvtx.mark(what)
     if rc != 0:
         raise KernelError(f"{what}: {_STATUS.get(rc, rc)}")
 

@@ -12,6 +12,7 @@ import os
 import torch
 
 from ..ops.cuda import _stream, check, declare, lib
+from ..utils import flags
 
 declare("mary_allreduce_bf16", "pplii" + "lllpiils")
 declare("mary_allreduce_f32", "pplii" + "lllpiils")
@@ -44,7 +45,7 @@ class SymmetricHeap:
         self.buf_ptrs = (ctypes.c_uint64 * 8)(*list(self.hdl.buffer_ptrs)[:world])
         self.sig_ptrs = (ctypes.c_uint64 * 8)(*list(self.fhdl.buffer_ptrs)[:world])
         mc = 0
-        want_mc = use_multicast if use_multicast is not None else os.environ.get("MARY_MULTIMEM", "1") != "0"
+        want_mc = use_multicast if use_multicast is not None else flags.get("MARY_MULTIMEM")
         if want_mc:
             try:
                 mc = int(self.hdl.multicast_ptr or 0)
@@ -53,7 +54,7 @@ class SymmetricHeap:
         self.mc = mc
         self.epochs = torch.zeros(64 + 8, dtype=torch.int32, device=self.dev)     # per-block flag epochs (+ barrier slots)
         self.local_out = torch.empty(min(self.region // 2, ONESHOT_MAX_BYTES), dtype=torch.uint8, device=self.dev)
-        self.oneshot = os.environ.get("MARY_ONESHOT", "1") != "0"
+        self.oneshot = flags.get("MARY_ONESHOT")
         torch.cuda.synchronize()
         dist.barrier()
 

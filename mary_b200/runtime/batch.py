@@ -10,6 +10,8 @@ import os
 from dataclasses import dataclass
 
 import numpy as np
+
+from ..utils import flags
 import torch
 
 
@@ -60,7 +62,7 @@ class BatchMeta:
         pages = page_table[seq_index, pos // page_size].astype(np.int64)
         slots = pages * page_size + (pos % page_size)
         dev = torch.device(device)
-        if os.environ.get("MARY_DEBUG_CHECKS") == "1":
+        if flags.get("MARY_DEBUG_CHECKS"):
             check_batch(q_lens, kv_lens, page_table, page_size)
 
         def t(a, dt):

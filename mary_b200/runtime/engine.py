@@ -28,7 +28,7 @@ class StepStats:
 
 class Engine:
     def __init__(self, model, cache: PagedKVCache, max_tokens: int = 8192, max_seqs: int = 256,
-                 prefill_chunk: int = 2048, device="cpu", eos_ids=(), sampler=None, draft=None, spec_k: int = 0):
+                 prefill_chunk: int = 2048, device="cpu", eos_ids=(), sampler=None, draft=None, spec_k: int = 0, metrics=None):
         self.model, self.cache, self.device = model, cache, torch.device(device)
         self.lib = cache.alloc.lib
         _declare(self.lib)
@@ -49,6 +49,7 @@ class Engine:
         self._nt = ctypes.c_int32()
         self.stats: list[StepStats] = []
         self.accepted_hist: list[int] = []
+        self.metrics = metrics              # utils.metrics.MetricsLog or None: one "step" row per step, one "request" row per first token
 
     # ------------------------------------------------------------------ requests
     def add_request(self, ids, max_new: int) -> int:
@@ -132,11 +133,15 @@ class Engine:
                     break
             if rid not in self.first_token_time:
                 self.first_token_time[rid] = now
+                if self.metrics is not None:
+                    self.metrics.emit("request", id=rid, ttft_s=now - self.submit_time[rid])
             self.outputs[rid].extend(new)
             self.lib.sched_commit(self.h, rid, accepted, fed_rows, new[-1], 1 if done else 0)
             out.tokens_out += len(new)
         out.seconds = time.perf_counter() - t0
         self.stats.append(out)
+        if self.metrics is not None:
+            self.metrics.emit("step", seconds=out.seconds, tokens_in=out.tokens_in, tokens_out=out.tokens_out, seqs=out.seqs)
         return out
 
     def run(self, max_steps: int = 1 << 30) -> None:

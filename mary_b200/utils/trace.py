@@ -13,6 +13,23 @@ from collections import defaultdict
 import torch
 
 
+class nvtx_range:
+    """``with nvtx_range("layer 3"):`` — an NVTX range when ``MARY_NVTX=1`` (for Nsight timelines), nothing otherwise."""
+
+    def __init__(self, name: str):
+        from . import flags
+        self.name, self.on = name, bool(flags.get("MARY_NVTX")) and torch.cuda.is_available()
+
+    def __enter__(self):
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+        return self
+
+    def __exit__(self, *a):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+
+
 class Tracer:
     def __init__(self):
         self.events: list[tuple[str, torch.cuda.Event]] = []
