@@ -44,9 +44,23 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
     t0 = time.time()
     pile = Pile.open(a.pile, create=False)
-    model = load_from_pile(pile, device=dev, dtype=dtype)
-    cfg = model.cfg
+    # the architecture is a FACT in the pile (config.json's model_type), not a flag
+    from ..format.persist import load_config, read_model_pile
+    from ..format.selection import SelectedModelIndex
+    facts0 = read_model_pile(pile)
+    arch = load_config(pile, facts0, SelectedModelIndex.from_snapshot(pile, facts0).roots[0]).get("model_type", "mary_moe")
+    weights = None
+    if arch == "inkling":
+        from ..models.inkling.weights import load_from_pile as load_inkling
+        model, weights = load_inkling(pile, device=dev, dtype=dtype, max_slots=max(a.slots or 1, 1))
+        cfg = model.t
+        cfg.num_mtp_layers, cfg.attention, cfg.name = model.n_mtp, "gqa", "inkling"
+    else:
+        model = load_from_pile(pile, device=dev, dtype=dtype)
+        cfg = model.cfg
     print(f"loaded {cfg.name} ({cfg.num_hidden_layers} layers, {cfg.n_routed_experts} experts) in {time.time() - t0:.2f} s", file=sys.stderr)
+    if weights is not None:
+        print(weights.io_table(), file=sys.stderr)
     tok = None
     if a.prompt is not None:
         from ..format.persist import read_model_pile
@@ -70,11 +84,15 @@ def main(argv=None) -> int:
     if dev.type == "cuda":
         # admission: the cache and the widest prefill chunk are priced against what is free BEFORE anything is allocated
         free, _ = torch.cuda.mem_get_info(dev)
-        row = 576 * 2 if cfg.attention == "mla" else 2 * spec["kv_heads"] * spec["head_dim"] * 2
-        kv = budget.kv_bytes(spec["num_layers"], pages * 16, row)
+        if isinstance(spec["kv_heads"], list):
+            kv = sum(budget.kv_bytes(1, pages * 16, 2 * h * d * 2) for h, d in zip(spec["kv_heads"], spec["head_dim"]))
+        else:
+            row = 576 * 2 if cfg.attention == "mla" else 2 * spec["kv_heads"] * spec["head_dim"] * 2
+            kv = budget.kv_bytes(spec["num_layers"], pages * 16, row)
         if kv > free:
             raise budget.AdmissionError(f"the paged cache of {B} x {max_len} tokens needs {kv / 2**30:.2f} GiB, {free / 2**30:.2f} GiB are free")
-        budget.check_prefill(cfg, min(512, prompts.shape[1]) * B, free - kv)
+        if arch != "inkling":
+            budget.check_prefill(cfg, min(512, prompts.shape[1]) * B, free - kv)
     cache = PagedKVCache(spec["num_layers"], pages, 16, spec["kv_heads"], spec["head_dim"], dtype=dtype, device=dev,
                          latent_dim=spec.get("latent_dim"))
     dec = SpecDecoder(model, cache, B, spec_k=k, max_len=(max_len + 15) // 16 * 16, device=dev, use_graph=dev.type == "cuda" and not a.trace)

@@ -292,3 +292,63 @@ def test_f5_flow_sampler_with_a_graphed_euler_step_matches_the_eager_sampler():
     got = cfm.sample(ref_mel, [1, 2, 3, 4], 24, noise=noise)
     assert torch.equal(got[:10], ref_mel) and torch.isfinite(got).all()
     _close(got, want, 0.03)
+
+
+def test_inkling_decoder_on_the_gpu_matches_the_cpu_reference_and_rolls_back():
+    """The real Inkling decoder (short convolutions with ring state, relative bias, log scaling, sigmoid router with shared-expert
+    sinks, NVFP4 and bf16 expert layers, MTP heads) in bf16 on the kernels against the f32 reference operators on the CPU; then
+    greedy decoding with two MTP drafts per step (CUDA graph) emits the same tokens as plain greedy decoding."""
+    import numpy as np
+    from mary_b200.models.inkling.config import tiny_inkling_config
+    from mary_b200.models.inkling.decoder import InklingDecoder, reference_forward
+    from mary_b200.ops import cuda as K
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    from mary_b200.runtime.spec_decode import SpecDecoder
+    cfg = tiny_inkling_config(hidden_size=256, head_dim=64, swa_head_dim=64, intermediate_size=256, dense_intermediate_size=512, d_rel=16)
+    cpu = InklingDecoder(cfg, quantized={2}, dtype=torch.float32, device="cpu").init_random_(0)
+    gpu = InklingDecoder(cfg, quantized={2}, dtype=torch.bfloat16, device="cuda", max_slots=4)
+    for n, v in cpu.P.items():
+        gpu.set_tensor(n, v)
+    for layer in (1, 2, 3):
+        d = cpu._derived[("expert_dense", layer)]
+        gpu._derived[("expert_dense", layer)] = {k: v.to("cuda", torch.bfloat16) for k, v in d.items()}
+    rng = np.random.default_rng(0)
+    toks = rng.integers(0, 300, 40).tolist()
+    want = reference_forward(cpu, toks)[0]
+    s = gpu.kv_spec()
+    cache = PagedKVCache(s["num_layers"], 16, 16, s["kv_heads"], s["head_dim"], dtype=torch.bfloat16, device="cuda")
+    got = []
+    done = 0
+    for n in (33, 3, 1, 1, 1, 1):
+        cache.alloc.extend(0, n)
+        table, lens = cache.alloc.page_table([0])
+        meta = BatchMeta.build([n], lens, table, 16, "cuda")
+        got.append(gpu(torch.tensor(toks[done:done + n], dtype=torch.int32, device="cuda"), meta, cache).float().cpu())
+        done += n
+    got = torch.cat(got)
+    assert K.last_status() == 0
+    err = (got - want).abs().max() / want.abs().max()
+    assert err < 0.08, err
+    assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.85
+    outs = []
+    for k in (0, 2):
+        for rg in gpu.rings:
+            for t in rg.values():
+                t.zero_()
+        c2 = PagedKVCache(s["num_layers"], 16, 16, s["kv_heads"], s["head_dim"], dtype=torch.bfloat16, device="cuda")
+        sd = SpecDecoder(gpu, c2, 2, spec_k=k, max_len=96, device="cuda", use_graph=True)
+        first = sd.prefill(rng.integers(0, 300, (2, 9)) if k == 0 else prompts, chunk=8) if k else None
+        if k == 0:
+            prompts = rng.integers(0, 300, (2, 9))
+            first = sd.prefill(prompts, chunk=8)
+        sd.capture()
+        seqs = [[int(t)] for t in first.tolist()]
+        while min(len(q) for q in seqs) < 12:
+            sd.step()
+            em, ne = sd.emitted.cpu(), sd.n_emitted.cpu()
+            for b in range(2):
+                seqs[b].extend(em[b, :int(ne[b])].tolist())
+        outs.append([q[:12] for q in seqs])
+    assert K.last_status() == 0
+    assert outs[0] == outs[1]

@@ -174,3 +174,44 @@ def test_checkpoint_dictionary_fills_every_slot():
     assert need == have
     with pytest.raises(KeyError):
         dec.set_tensor("model.llm.layers.0.attn.nonsense.weight", torch.zeros(1))
+
+
+def test_decoder_round_trips_through_a_pile_with_config_from_facts(tmp_pile):
+    """Save to a pile (NVFP4 blobs with placement facts, bf16 leaves, config as facts), load config-free through the Weights
+    facade, same logits; the facade counts what it copied and refuses a share that cannot fit before copying."""
+    from mary_b200.models.inkling.source import Weights
+    from mary_b200.models.inkling.weights import load_from_pile, save_to_pile
+    from mary_b200.runtime.budget import AdmissionError
+    pile, key = tmp_pile
+    dec = _decoder({2, 3})
+    save_to_pile(pile, key, dec)
+    dec2, w = load_from_pile(pile, dtype=torch.float32)
+    assert dec2.quantized == {2, 3} and dec2.cfg.text_config == dec.cfg.text_config
+    ids = torch.tensor(np.random.default_rng(0).integers(0, 300, 11), dtype=torch.int32)
+    outs = []
+    for d in (dec, dec2):
+        c = _cache(d)
+        c.alloc.extend(0, 11)
+        outs.append(d(ids, _meta(c, [11], [0]), c))
+    assert (outs[0] - outs[1]).abs().max() <= 0.05 * outs[0].abs().max()       # bf16 storage of the dense tensors of an f32 model
+    assert w.stats.tensors > 100 and w.stats.bytes_requested > 0 and w.held("model.llm.embed.weight") > 0 and "GiB requested" in w.io_table()
+    assert w.stored("model.llm.embed.weight") == 320 * 128 * 2 and w.document("config.json")["model_type"] == "inkling"
+    with pytest.raises(AdmissionError, match="share"):
+        Weights.open(pile).admit(w.names(), 0, 1 << 20)
+    assert (2, 0) in w.index.experts_in_layers(2, 3)         # placement is a query over facts
+
+
+def test_moe_forward_serves_an_inkling_pile(tmp_pile, capsys):
+    """The serving entry point picks the architecture from the pile's config facts and decodes with the MTP heads drafting."""
+    from mary_b200.cli import moe_forward
+    from mary_b200.models.inkling.weights import save_to_pile
+    pile, key = tmp_pile
+    dec = _decoder(set())
+    save_to_pile(pile, key, dec)
+    path = pile.path
+    pile.close()
+    outs = []
+    for spec in ("0", "2"):
+        assert moe_forward.main(["--pile", path, "--ids", "5,6,7,8,9", "--max-new", "6", "--spec", spec, "--device", "cpu"]) == 0
+        outs.append(capsys.readouterr().out.strip().splitlines()[-1])
+    assert outs[0] == outs[1] and len(outs[0].split(",")) == 6
