@@ -332,16 +332,14 @@ def test_inkling_decoder_on_the_gpu_matches_the_cpu_reference_and_rolls_back():
     assert err < 0.08, err
     assert (got.argmax(-1) == want.argmax(-1)).float().mean() > 0.85
     outs = []
+    prompts = rng.integers(0, 300, (2, 9))
     for k in (0, 2):
         for rg in gpu.rings:
             for t in rg.values():
                 t.zero_()
         c2 = PagedKVCache(s["num_layers"], 16, 16, s["kv_heads"], s["head_dim"], dtype=torch.bfloat16, device="cuda")
         sd = SpecDecoder(gpu, c2, 2, spec_k=k, max_len=96, device="cuda", use_graph=True)
-        first = sd.prefill(rng.integers(0, 300, (2, 9)) if k == 0 else prompts, chunk=8) if k else None
-        if k == 0:
-            prompts = rng.integers(0, 300, (2, 9))
-            first = sd.prefill(prompts, chunk=8)
+        first = sd.prefill(prompts, chunk=8)
         sd.capture()
         seqs = [[int(t)] for t in first.tolist()]
         while min(len(q) for q in seqs) < 12:
