@@ -278,6 +278,9 @@ def main(argv=None) -> int:
     en = sub.add_parser("encode")
     en.add_argument("out"), en.add_argument("--pile"), en.add_argument("--tokenizer"), en.add_argument("--tokenizer-json")
     en.set_defaults(fn=cmd_encode)
+    ga = sub.add_parser("gate", help="run a correctness gate (or 'all'); --mutate runs its positive control")
+    ga.add_argument("name"), ga.add_argument("--mutate", action="store_true")
+    ga.set_defaults(fn=lambda a: __import__("mary_b200.gates", fromlist=["run"]).run(a.name, a.mutate))
     fl = sub.add_parser("flags", help="the environment flags of the package with the values in effect")
     fl.set_defaults(fn=cmd_flags)
     a = ap.parse_args(argv)

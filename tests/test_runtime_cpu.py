@@ -77,3 +77,12 @@ def test_engine_emits_metrics_rows(tmp_path):
     assert sum(r["kind"] == "request" for r in rows) == 2 and sum(r["kind"] == "step" for r in rows) >= 3
     s = log.summary()
     assert s["tokens"] >= 6 and s["ttft_p50_s"] > 0
+
+
+def test_every_gate_passes_and_every_mutant_is_caught(capsys):
+    from mary_b200 import gates
+    assert gates.run("all") == 0
+    assert gates.run("all", mutate=True) == 0
+    out = capsys.readouterr().out
+    assert out.count("PASS") == len(gates.GATES) and out.count("mutant caught") == len(gates.GATES)
+    assert gates.run("no-such-gate") == 2
