@@ -128,3 +128,36 @@ def derive_half_root(pile, key, facts: TribleSet, root: bytes, dtype: str = "f16
 
 def default_key(pile_path) -> object:
     return signing_key_file(str(pile_path) + ".key")
+
+
+def import_file_filtered_to_collection(pile, key, file, dtype: str = "f32", source: str | None = None, quantization: str | None = None,
+                                       keep=lambda name: True, name: str | None = None) -> bytes:
+    """Import ONE weight file (safetensors, GGUF or a torch pickle), keeping only the tensors ``keep(name)`` accepts, as a model
+    root of its own — a component of a larger checkpoint (a vision tower, a codec) becomes selectable by source / quantisation
+    without importing the rest (src/persist.rs:296-417).  The file name is recorded as provenance; a filter that selects no float
+    tensor is an error, and a torn pile tail refuses the import as always."""
+    pile.refresh()
+    tb = TribleBuilder()
+    members = ingest_members(pile, tb, file, dtype, keep)
+    if not members:
+        raise ValueError(f"the filtered import selected no supported float tensor from {file}")
+    root = build_model_root(pile, tb, members, name=name or Path(file).name, source=source or str(file),
+                            quantization=quantization or (None if dtype == "f32" else dtype))
+    Collection(Repository(pile, key), MODEL_GRAPH).publish(tb.build(), f"component {Path(file).name}"[:32])
+    pile.flush()
+    return root
+
+
+def load_split_index_from_pile(pile, f16_prefix: str, facts: TribleSet | None = None) -> tuple[dict, dict]:
+    """``(half-precision leaves, single-precision leaves)`` by tensor name: the roots whose MODEL NAME starts with ``f16_prefix``
+    feed the first map, all others the second (src/persist.rs:940-1014).  Serving lanes that keep the large matrices in half
+    precision and the small, precision-critical tensors (norm gains, biases) in f32 read both maps from one pile."""
+    from .model import index_keymap
+    facts = facts if facts is not None else read_model_pile(pile)
+    half, single = {}, {}
+    for root, v in facts.with_attr(S.MODEL_NAME):
+        name = get_text(pile, v)
+        target = half if (f16_prefix and name.startswith(f16_prefix)) else single
+        for n, module in index_keymap(pile, facts, root).items():
+            target[n] = load_module_leaf(pile, facts, module)
+    return half, single

@@ -376,3 +376,27 @@ def test_quantised_leaves_round_trip_and_derive_a_sibling_root(tmp_path):
         put_leaf_q(pile, TribleBuilder(), rng.standard_normal((4, 40)).astype(np.float32))
     assert MARKER["q8"] == "q8_0.v1"
     pile.close()
+
+
+def test_filtered_component_import_and_split_half_single_index(tmp_pile):
+    from mary_b200.format.persist import import_file_filtered_to_collection, load_split_index_from_pile, read_model_pile
+    import tempfile, os
+    pile, key = tmp_pile
+    rng = np.random.default_rng(0)
+    tensors = {"vision.patch.weight": rng.standard_normal((4, 8)).astype(np.float32), "vision.norm.weight": np.ones(8, np.float32),
+               "text.embed.weight": rng.standard_normal((16, 8)).astype(np.float32)}
+    d = tempfile.mkdtemp()
+    f = os.path.join(d, "model.safetensors")
+    save_file(tensors, f)
+    r1 = import_file_filtered_to_collection(pile, key, f, "f16", source="hf/x", keep=lambda n: n.startswith("vision.") and n.endswith("patch.weight"),
+                                            name="f16/vision")
+    r2 = import_file_filtered_to_collection(pile, key, f, "f32", source="hf/x", keep=lambda n: n.endswith("norm.weight"), name="f32/vision")
+    assert r1 != r2
+    with pytest.raises(ValueError, match="selected no"):
+        import_file_filtered_to_collection(pile, key, f, keep=lambda n: False)
+    half, single = load_split_index_from_pile(pile, "f16/")
+    assert set(half) == {"vision.patch.weight"} and set(single) == {"vision.norm.weight"}
+    assert half["vision.patch.weight"].elem == Elem.F16 and single["vision.norm.weight"].elem == Elem.F32
+    assert np.allclose(half["vision.patch.weight"].to_f32(), tensors["vision.patch.weight"], atol=2e-3)
+    idx = SelectedModelIndex.from_snapshot(pile, read_model_pile(pile), ModelSelector.by_source("hf/x", "f16"))
+    assert idx.names() == ["vision.patch.weight"]
