@@ -165,14 +165,60 @@ def test_tokenizer_graph_roundtrip_and_build_without_json():
     rebuilt = build_tokenizer(st, facts)
     for s in ("hello", "hello hello", "<bos>hello<turn|>"):
         assert rebuilt.encode(s).ids == tok.encode(s).ids
-    # mutant: dropping one merge fact changes the encoding (the comparison can fail)
-    from mary_b200.format.tokenizer import MERGE_RANK
-    from mary_b200.pile.trible import r_u256
-    victim = [e for e, v in facts.with_attr(MERGE_RANK) if r_u256(v) == 3][0]
-    keep = [i for i, (e, _a, _v) in enumerate(facts) if e != victim]
+    # mutant 1: the facts of one merge entity vanish -> the strict reader refuses (a missing merge would change encodings silently)
+    from mary_b200.format.tokenizer import MERGE, MERGE_RANK
+    from mary_b200.pile.trible import r_genid, r_u256
     from mary_b200.pile import TribleSet
-    mutant = TribleSet(facts.data[keep])
-    assert build_tokenizer(st, mutant).encode("hello").ids != tok.encode("hello").ids
+    merges = {r_genid(v) for _e, v in facts.with_attr(MERGE)}
+    victim = [e for e, v in facts.with_attr(MERGE_RANK) if e in merges and r_u256(v) == 1][0]
+    keep = [i for i, (e, _a, _v) in enumerate(facts) if e != victim]
+    with pytest.raises((LookupError, ValueError)):
+        build_tokenizer(st, TribleSet(facts.data[keep]))
+    # mutant 2: the tokenizer no longer points at that merge -> a gap in the ranks, refused as well
+    keep = [i for i, (_e, a, v) in enumerate(facts) if not (a == MERGE and r_genid(v) == victim)]
+    with pytest.raises(ValueError, match="merge ranks"):
+        build_tokenizer(st, TribleSet(facts.data[keep]))
+
+
+def test_tokenizer_graph_uses_the_typed_node_forms_and_keeps_what_they_cannot_say():
+    from mary_b200.format import tokenizer as T
+    from mary_b200.pile.trible import r_genid
+    doc = {"version": "1.0", "truncation": None, "padding": None,
+           "added_tokens": [{"id": 0, "content": "[UNK]", "single_word": False, "lstrip": False, "rstrip": True, "normalized": False,
+                             "special": True}],
+           "normalizer": {"type": "Sequence", "normalizers": [
+               {"type": "NFC"}, {"type": "Replace", "pattern": {"String": "  "}, "content": " "},
+               {"type": "BertNormalizer", "clean_text": True, "handle_chinese_chars": True, "strip_accents": None, "lowercase": True},
+               {"type": "NFC"}]},
+           "pre_tokenizer": {"type": "Sequence", "pretokenizers": [
+               {"type": "Split", "pattern": {"Regex": "\\d"}, "behavior": "Isolated", "invert": False},
+               {"type": "Metaspace", "replacement": "\u2581", "prepend_scheme": "always", "split": True}]},
+           "post_processor": None,
+           "decoder": {"type": "WordPiece", "prefix": "##", "cleanup": True},
+           "model": {"type": "WordPiece", "unk_token": "[UNK]", "continuing_subword_prefix": "##", "max_input_chars_per_word": 100,
+                     "vocab": {"[UNK]": 0, "a": 1, "##b": 2}}}
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    root = b"\x07" * 16
+    tid = T.save_tokenizer_json(st, tb, "wp", doc, owner=root)
+    facts = tb.build()
+    assert T.load_tokenizer_json(st, facts, tid) == doc
+    assert T.find_tokenizers(facts) == [tid]                      # the WordPiece DECODER node shares the tag but has no name
+    assert r_genid(facts.one(root, T.TOKENIZER)) == tid
+    norm = r_genid(facts.one(tid, T.NORMALIZER))
+    kids = T.ordered_members(facts, norm)
+    assert [T.ty.NFC in T.node_tags(facts, k) for k in kids] == [True, False, False, True] and len(set(kids)) == 4
+    assert T.flag.PATTERN_IS_STRING in T.node_tags(facts, kids[1]) and T.flag.LOWERCASE in T.node_tags(facts, kids[2])
+    pre = T.ordered_members(facts, r_genid(facts.one(tid, T.PRE_TOKENIZER)))
+    assert T.ty.SPLIT in T.node_tags(facts, pre[0]) and T.ty.OPAQUE in T.node_tags(facts, pre[1])
+    assert T.tokenizer_kind(facts, tid) == "WordPiece"
+    # unigram pieces written from a SentencePiece table come back typed and build a working tokenizer
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    pieces = [("<unk>", 0.0), ("\u2581a", -1.0), ("\u2581b", -1.5), ("b", -2.0)]
+    uid = T.save_spm_unigram(st, tb, "spm", pieces)
+    facts = tb.build()
+    assert [(b.decode(), t) for b, _s, t in T.load_spm_pieces(st, facts, uid)] == [("<unk>", 2), ("\u2581a", 1), ("\u2581b", 1), ("b", 1)]
+    assert T.has_add_prefix_space(facts, uid)
+    assert T.build_tokenizer(st, facts, uid).encode("a b").ids == [1, 2]
 
 
 def test_tiktoken_bpe_and_pile_roundtrip():
