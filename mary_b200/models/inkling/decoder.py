@@ -39,7 +39,8 @@ RING = 16
 def conv_ring(x, w, ring, slots, meta):
     """``y = x + depthwise_causal_conv(x)`` over the rows of a flattened batch with the history taken from (and the rows written
     to) the position ring.  ``x [T, C]``; ``w [C, taps]`` (tap ``taps - 1`` multiplies the current row, block.rs:48-127);
-    ``ring [slots, RING, C]``; ``slots [S]`` int64 ring row of every sequence of the batch."""
+    ``ring [slots + 1, RING, C]`` (the last row is a spare that takes the writes of rows too old to keep); ``slots [S]`` int64 ring
+    row of every sequence of the batch."""
     T, C = x.shape
     taps = w.shape[1]
     pos = meta.positions.long()
@@ -62,8 +63,10 @@ def conv_ring(x, w, ring, slots, meta):
         acc = acc + tap * wf[:, j]
     # only the last RING rows of a long chunk may be written (earlier ones would collide in the ring)
     n_rows = (meta.q_start[1:] - meta.q_start[:-1]).long()[seq]
+    # rows that may not be written go to the spare ring row behind the last slot instead: no data-dependent shapes, so the step
+    # can be captured in a CUDA graph
     keep = off >= n_rows - ring.shape[1]
-    ring.index_put_((slot[keep], pos[keep] % ring.shape[1]), x[keep].to(ring.dtype))
+    ring.index_put_((torch.where(keep, slot, ring.shape[0] - 1), pos % ring.shape[1]), x.to(ring.dtype))
     return acc.to(x.dtype)
 
 
@@ -87,7 +90,7 @@ class InklingDecoder(torch.nn.Module):
         self.kinds = kinds
         for kind in kinds:
             kv = t.kv_dim(kind)
-            z = lambda c: torch.zeros(max_slots, RING, c, dtype=dtype, device=self.dev)  # noqa: E731
+            z = lambda c: torch.zeros(max_slots + 1, RING, c, dtype=dtype, device=self.dev)  # noqa: E731
             self.rings.append({"k": z(kv), "v": z(kv), "attn": z(t.hidden_size), "mlp": z(t.hidden_size)})
 
     # ------------------------------------------------------------------ parameters
