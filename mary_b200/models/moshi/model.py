@@ -136,6 +136,14 @@ class StreamCache:
         self.offset += 1
         return out
 
+    def overwrite(self, snapshot) -> None:
+        """Replace the token ring wholesale with a packaged snapshot ``[streams, ring]``; the ``provided`` flags and the offset are
+        deliberately untouched (src/models/personaplex/lmgen.rs:188-201)."""
+        rows = [[int(v) for v in row] for row in snapshot]
+        if len(rows) != self.c.num_streams or any(len(r) != self.ct for r in rows):
+            raise ValueError(f"cache snapshot must be [{self.c.num_streams}, {self.ct}]")
+        self.cache = rows
+
 
 def _P(*shape, dtype=torch.float32, device="cpu"):
     return nn.Parameter(torch.empty(*shape, dtype=dtype, device=device), requires_grad=False)
@@ -281,8 +289,10 @@ class LmGen(nn.Module):
         if self.dev.type == "cuda" and sample is None and self.use_graph:
             text_tok, audio = self._graph_frame(p)
             return self.stream.commit(p, text_tok, audio)
+        return self._frame(self.embed_frame(p["input"]), p, sample)
+
+    def _frame(self, x, p, sample=None):
         with torch.no_grad():
-            x = self.embed_frame(p["input"])
             self.pos += 1
             meta = BatchMeta.build([1], [self.pos], self.table, 16, self.dev)
             h = self.temporal.hidden_from_embeds(x, meta, self.cache)                    # [1, dim], final-normed
@@ -292,6 +302,53 @@ class LmGen(nn.Module):
             forced = [p["target"][1 + s] if p["provided"][1 + s] else None for s in range(self.c.dep_q)]
             audio = self.depformer.generate(h, next_text, forced, sample)[0]
         return self.stream.commit(p, int(text_tok[0]), [int(a) for a in audio])
+
+    # ------------------------------------------------------------------ system prompt (src/models/personaplex/pipeline.rs:117-160)
+    def step_embeddings(self, x, sample=None):
+        """Voice-prompt replay step: the stream cache still advances with dummy initial audio tokens and PAD text, but the temporal
+        stack consumes the pre-recorded input embedding ``x [dim]`` instead of the embedding tables (lmgen.rs:287-302)."""
+        from .voice_prompt import TEXT_PAD_TOKEN
+        dummy = [self.c.card] * self.c.codebooks_per_stream
+        p = None
+        while p is None:
+            p = self.stream.prepare(dummy, dummy, TEXT_PAD_TOKEN)
+        if self.pos >= self.c.context:
+            raise RuntimeError("voice prompt longer than the attention context")
+        x = torch.as_tensor(x, device=self.dev).reshape(1, self.c.dim).to(self.text_emb.dtype)
+        return self._frame(x, p, sample)
+
+    def prompt_voice(self, voice) -> None:
+        for row in voice.embeddings:
+            self.step_embeddings(row)
+        self.stream.overwrite(voice.cache.tolist())
+
+    def _spacer(self, sine, silence):
+        from .voice_prompt import SILENCE_TOKENS, SINE_TOKENS
+        n = self.c.codebooks_per_stream
+        sine, silence = list(sine or SINE_TOKENS[:n]), list(silence or SILENCE_TOKENS[:n])
+        if len(sine) != n or len(silence) != n or max(sine + silence) >= self.c.card:
+            raise ValueError(f"spacer frames need {n} codec tokens below {self.c.card} per stream")
+        return sine, silence
+
+    def prompt_silence(self, frames: int, sine=None, silence=None) -> None:
+        """``frames`` steps of agent silence, the user's reference sine and PAD text (``sine`` / ``silence``: one frame of codec
+        tokens each; default the 12.5 Hz codec's)."""
+        from .voice_prompt import TEXT_PAD_TOKEN
+        sine, silence = self._spacer(sine, silence)
+        for _ in range(frames):
+            self.step(sine, silence, TEXT_PAD_TOKEN)
+
+    def prompt_text(self, tokens, sine=None, silence=None) -> None:
+        sine, silence = self._spacer(sine, silence)
+        for t in tokens:
+            self.step(sine, silence, int(t))
+
+    def run_prompt(self, prompt, sine=None, silence=None) -> None:
+        """voice replay -> silence -> text -> silence (moshi ``step_system_prompts``)."""
+        self.prompt_voice(prompt.voice)
+        self.prompt_silence(prompt.silence_frames, sine, silence)
+        self.prompt_text(prompt.text_tokens, sine, silence)
+        self.prompt_silence(prompt.silence_frames, sine, silence)
 
     use_graph = True
     _gs = None
