@@ -421,6 +421,22 @@ def argmax(logits, softcap=0.0, temperature: float = 0.0, margin: float = 20.0, 
     return idx, val
 
 
+declare("mary_sample_top_k_top_p", "pilii" + "fif" + "ll" + "pps")
+
+
+def sample_top_k_top_p(logits, temperature: float, top_k: int = 0, top_p: float = 1.0, seed: int = 0, step: int = 0, want_prob: bool = False):
+    """One token per row of ``logits [rows, V]`` (f32 or bf16) by temperature / top-k / top-p sampling in one launch, no sort and no
+    read-back; the draw of row ``r`` depends on ``(seed, step, r)`` only.  Returns int32 ids (and the drawn token's probability)."""
+    rows, V = logits.shape
+    assert logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(1) == 1 and temperature > 0 and top_p > 0
+    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    prob = torch.empty(rows, dtype=torch.float32, device=logits.device) if want_prob else None
+    check(lib().mary_sample_top_k_top_p(_p(logits), int(logits.dtype == torch.float32), logits.stride(0), rows, V, float(temperature), int(top_k),
+                                        float(top_p), int(seed) & (2**63 - 1), int(step) & (2**63 - 1), _p(idx), _p(prob), _stream()),
+          "sample_top_k_top_p")
+    return (idx, prob) if want_prob else idx
+
+
 def lm_head_argmax(h, table, softcap=0.0, vocab_limit=None):
     logits = gemm(h.contiguous(), table, epi="f32")
     if vocab_limit:

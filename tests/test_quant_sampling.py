@@ -1,3 +1,4 @@
+import pytest
 import numpy as np
 import torch
 
@@ -66,3 +67,73 @@ def test_sampling_rules():
         cnt += torch.bincount(sample(big, temperature=1.0, seed=5, step=s), minlength=4).float()
     assert ((cnt / cnt.sum()) - torch.softmax(big[0], 0)).abs().max() < 0.03
     assert torch.equal(sample(big, temperature=0.7, seed=1, step=2), sample(big, temperature=0.7, seed=1, step=2))
+
+
+def test_reference_sampler_properties_of_the_speech_models_rule():
+    from mary_b200.ops.sampling import draw_uniform, sample_reference
+    g = torch.Generator().manual_seed(3)
+    row = torch.randn(200, generator=g) * 3
+    order = torch.sort(row, descending=True, stable=True).indices.tolist()
+    # top-k truncation: only the k highest survive; ties at the cut keep the lower index
+    tok, kept = sample_reference(row, 1.0, top_k=7, u=0.5)
+    assert sorted(kept) == sorted(order[:7]) and tok in kept
+    tied = torch.tensor([1.0, 3.0, 3.0, 3.0, 0.0])
+    assert sample_reference(tied, 1.0, top_k=2, u=0.1)[1] == [1, 2]
+    # nucleus: smallest prefix whose mass reaches p, at least one token
+    p = torch.softmax(row.double(), 0)[order]
+    n = int((torch.cumsum(p, 0) >= 0.6).nonzero()[0]) + 1
+    assert sorted(sample_reference(row, 1.0, top_p=0.6, u=0.3)[1]) == sorted(order[:n])
+    assert sample_reference(row, 1.0, top_p=1e-9, u=0.9)[1] == [order[0]]
+    # temperature -> 0 is the arg-max; non-finite logits never win; an all-non-finite row falls back to the arg-max rule
+    assert sample_reference(row, 1e-4, u=0.999)[0] == order[0]
+    bad = row.clone()
+    bad[order[0]] = float("nan")
+    bad[order[1]] = float("inf")
+    assert order[0] not in sample_reference(bad, 1.0, top_k=5, u=0.0)[1] and order[1] not in sample_reference(bad, 1.0, top_k=5, u=0.0)[1]
+    assert sample_reference(torch.full((4,), float("nan")), 1.0, u=0.5)[1] == []
+    # the draw follows the distribution: frequencies over many uniforms
+    small = torch.tensor([2.0, 1.0, 0.0, -1.0])
+    cnt = torch.zeros(4)
+    for s in range(4000):
+        cnt[sample_reference(small, 1.0, u=draw_uniform(9, s, 0))[0]] += 1
+    assert (cnt / 4000 - torch.softmax(small, 0)).abs().max() < 0.03
+    us = [draw_uniform(1, s, r) for s in range(50) for r in range(4)]
+    assert len(set(us)) == 200 and all(0.0 <= u < 1.0 for u in us) and draw_uniform(1, 2, 3) == draw_uniform(1, 2, 3)
+
+
+@pytest.mark.gpu
+def test_device_sampler_picks_the_reference_token_for_every_setting():
+    from mary_b200.ops import cuda as K
+    from mary_b200.ops.sampling import draw_uniform, sample, sample_reference
+    g = torch.Generator().manual_seed(4)
+    for V, scale in ((2048, 3.0), (32000, 2.0), (50, 1.0), (262144, 1.5)):
+        rows = 6 if V > 100000 else 17
+        lg = (torch.randn(rows, V, generator=g) * scale)
+        lg[0, 5] = float("nan")
+        lg[1, 7] = float("inf")
+        lg[2, :V // 2] = float("-inf")
+        dev = lg.cuda()
+        for T, k, p in ((1.0, 0, 1.0), (0.8, 250, 1.0), (0.7, 0, 0.9), (1.2, 50, 0.8), (0.9, 1, 1.0), (1.0, 3, 1e-6), (0.5, 10 ** 6, 0.999)):
+            for step in (0, 1):
+                got, prob = K.sample_top_k_top_p(dev, T, k, p, seed=11, step=step, want_prob=True)
+                assert K.last_status() == 0
+                for r in range(rows):
+                    tok, kept = sample_reference(lg[r], T, k, p, draw_uniform(11, step, r))
+                    assert int(got[r]) in kept, (V, T, k, p, r)
+                    assert int(got[r]) == tok, (V, T, k, p, r, int(got[r]), tok)
+                assert (prob > 0).all() and (prob <= 1.0001).all()
+    # bf16 logits: many exact ties at the thresholds; the kept set must still be the stable-sort prefix
+    lg = (torch.randn(9, 4096, generator=g) * 2).bfloat16()
+    got = K.sample_top_k_top_p(lg.cuda(), 1.0, 40, 0.95, seed=3, step=7)
+    for r in range(9):
+        tok, kept = sample_reference(lg[r].float(), 1.0, 40, 0.95, draw_uniform(3, 7, r))
+        assert int(got[r]) == tok
+    # an all-non-finite row yields index 0 and the status stays clean; the public entry agrees host and device
+    assert int(K.sample_top_k_top_p(torch.full((1, 64), float("nan"), device="cuda"), 1.0)[0]) == 0
+    x = torch.randn(5, 300, generator=g)
+    assert sample(x, 0.8, 20, 0.9, seed=2, step=3).tolist() == sample(x.cuda(), 0.8, 20, 0.9, seed=2, step=3).tolist()
+    # frequencies follow the distribution
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0]]).cuda().expand(4096, 4).contiguous()
+    ids = K.sample_top_k_top_p(small, 1.0, seed=5, step=0)
+    freq = torch.bincount(ids.long(), minlength=4).float().cpu() / 4096
+    assert (freq - torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0)).abs().max() < 0.03
