@@ -446,3 +446,35 @@ def test_filtered_component_import_and_split_half_single_index(tmp_pile):
     assert np.allclose(half["vision.patch.weight"].to_f32(), tensors["vision.patch.weight"], atol=2e-3)
     idx = SelectedModelIndex.from_snapshot(pile, read_model_pile(pile), ModelSelector.by_source("hf/x", "f16"))
     assert idx.names() == ["vision.patch.weight"]
+
+
+def test_legacy_attribute_projection_is_additive_idempotent_and_counted():
+    from mary_b200.format import legacy, schema as S
+    from mary_b200.format.tokenizer import PIECE, TOKEN_ID
+    from mary_b200.pile import TribleSet
+    from mary_b200.pile.trible import v_u256
+    aliases = legacy.legacy_model_attribute_aliases()
+    assert len(aliases) == 45 and {a.label.split(".")[0] for a in aliases} == {"format", "gemma_lora", "tokenizer"}
+    by_label = {a.label: a for a in aliases}
+    assert by_label["format.index"].historical == S.INDEX and by_label["tokenizer.piece"].historical == PIECE
+    tok = _tiny_tokenizer_json()
+    st, tb = MemoryBlobStore(), TribleBuilder()
+    tid = save_tokenizer_json(st, tb, "tiny", tok.to_str())
+    other = b"\x09" * 16
+    tb.add(tid, other, v_u256(7))                                   # an attribute outside the table
+    facts = tb.build()
+    p = legacy.project_legacy_model_attributes(facts)
+    assert p.input_facts == len(facts) and p.aliases_added == p.source_facts > 0 and len(p.facts) == len(facts) + p.aliases_added
+    assert all(tuple(r) in {tuple(x) for x in p.facts.data.tolist()} for r in facts.data.tolist()[:50])       # nothing dropped
+    cnt = {c.alias.label: c for c in p.mappings}
+    assert cnt["tokenizer.token_id"].source_facts == len(facts.with_attr(TOKEN_ID)) and cnt["format.data"].source_facts == 0
+    assert not p.facts.with_attr(legacy.anchored_id("00" * 16, "U256BE")) and len(p.facts.with_attr(other)) == 1
+    again = legacy.project_legacy_model_attributes(p.facts)
+    assert again.aliases_added == 0 and again.facts == p.facts and sum(c.aliases_already_present for c in again.mappings) == p.aliases_added
+    # a fact set that carries ONLY derived ids becomes readable here through the opposite projection
+    canon = {a.historical: a.canonical for a in aliases}
+    rows = [e + canon.get(a, a) + v for e, a, v in facts]
+    only_new = TribleSet.from_tribles(rows)
+    assert not only_new.with_attr(TOKEN_ID)
+    back = legacy.project_to_literal(only_new).facts
+    assert build_tokenizer(st, back).encode("hello hello").ids == tok.encode("hello hello").ids
