@@ -11,6 +11,7 @@
 // (src/models/personaplex/temporal_metal.rs:133-454) and its windowed SIMT kernel (src/models/inkling/banded.rs:109-299).
 #include "common.cuh"
 #include "host_utils.h"
+#include <type_traits>
 
 using namespace mary;
 
@@ -28,6 +29,9 @@ struct DecParams {
   int64_t k_tok, k_page, v_tok, v_page;
   int Hq, Hkv, G, RQ, nsplit, window;
   float scale, softcap;
+  // 8-bit cache: kc / vc hold one unsigned code per element and the strides count codes; k_sz / v_sz hold (scale, zero) of every
+  // (slot, kv head) as two floats, slot-major; element = code * scale + zero
+  const float* k_sz; const float* v_sz;
 };
 
 template <int E> struct Vec;                       // E bf16 elements per lane
@@ -40,6 +44,18 @@ __device__ __forceinline__ void unpack(const typename Vec<E>::T& v, float* f) {
   const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
 #pragma unroll
   for (int j = 0; j < E / 2; ++j) { float2 t = __bfloat1622float2(h[j]); f[2 * j] = t.x; f[2 * j + 1] = t.y; }
+}
+
+template <int E> struct QVec;                      // E 8-bit codes per lane
+template <> struct QVec<2> { using T = uint16_t; };
+template <> struct QVec<4> { using T = uint32_t; };
+template <> struct QVec<8> { using T = uint2; };
+
+template <int E>
+__device__ __forceinline__ void unpack_q8(const typename QVec<E>::T& v, float sc, float zero, float* f) {
+  const uint8_t* b = (const uint8_t*)&v;
+#pragma unroll
+  for (int j = 0; j < E; ++j) f[j] = fmaf((float)b[j], sc, zero);
 }
 
 // Sums V values (a power of two, at most 32) over the 32 lanes and leaves ALL V totals in every lane.  Instead of one
@@ -69,13 +85,14 @@ __device__ __forceinline__ void warp_sum_vec(float* v, int lane) {
   for (int i = 0; i < V; ++i) v[i] = __shfl_sync(0xffffffffu, t, (lane & ~(V - 1)) | i);
 }
 
-template <int D, int RMAX>
+template <int D, int RMAX, bool Q8>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(const DecParams p) {
   pdl_sync();
   constexpr int E = D / 32;
   constexpr int KG = KG_BYTES / (4 * D) > 8 ? 8 : KG_BYTES / (4 * D);
   using V = typename Vec<E>::T;
+  using KV = typename std::conditional<Q8, typename QVec<E>::T, V>::type;
   __shared__ float red_o[WARPS][RMAX][D];
   __shared__ float red_ml[WARPS][RMAX][2];
   const int nb = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -115,20 +132,32 @@ attn_decode_kernel(const DecParams p) {
   const int* pt = p.page_table + (int64_t)seq * p.max_pages;
 
   for (int kb = s_lo + warp * KG; kb < s_hi; kb += WARPS * KG) {
-    V kv[KG], vv[KG];
+    KV kv[KG], vv[KG];
+    float2 ksz[KG], vsz[KG];
 #pragma unroll
     for (int j = 0; j < KG; ++j) {
       const int kp = min(kb + j, s_hi - 1);          // clamped: masked below
       const int page = pt[kp / p.page_size];
       const int64_t tok = kp % p.page_size;
-      kv[j] = *(const V*)(p.kc + (int64_t)page * p.k_page + tok * p.k_tok + (int64_t)kvh * D + lane * E);
-      vv[j] = *(const V*)(p.vc + (int64_t)page * p.v_page + tok * p.v_tok + (int64_t)kvh * D + lane * E);
+      if constexpr (Q8) {
+        const uint8_t* kq = (const uint8_t*)p.kc;
+        const uint8_t* vq = (const uint8_t*)p.vc;
+        kv[j] = *(const KV*)(kq + (int64_t)page * p.k_page + tok * p.k_tok + (int64_t)kvh * D + lane * E);
+        vv[j] = *(const KV*)(vq + (int64_t)page * p.v_page + tok * p.v_tok + (int64_t)kvh * D + lane * E);
+        const int64_t slot = ((int64_t)page * p.page_size + tok) * p.Hkv + kvh;
+        ksz[j] = *(const float2*)(p.k_sz + slot * 2);
+        vsz[j] = *(const float2*)(p.v_sz + slot * 2);
+      } else {
+        kv[j] = *(const KV*)(p.kc + (int64_t)page * p.k_page + tok * p.k_tok + (int64_t)kvh * D + lane * E);
+        vv[j] = *(const KV*)(p.vc + (int64_t)page * p.v_page + tok * p.v_tok + (int64_t)kvh * D + lane * E);
+      }
     }
     float s[KG][RMAX];
 #pragma unroll
     for (int j = 0; j < KG; ++j) {
       float kf[E];
-      unpack<E>(kv[j], kf);
+      if constexpr (Q8) unpack_q8<E>(kv[j], ksz[j].x, ksz[j].y, kf);
+      else unpack<E>(kv[j], kf);
 #pragma unroll
       for (int r = 0; r < RMAX; ++r) {
         float a = 0.f;
@@ -176,7 +205,8 @@ attn_decode_kernel(const DecParams p) {
             const float pj = (sv[j] == -INFINITY) ? 0.f : __expf(sv[j] - mx);
             l[r] += pj;
             float vf[E];
-            unpack<E>(vv[j], vf);
+            if constexpr (Q8) unpack_q8<E>(vv[j], vsz[j].x, vsz[j].y, vf);
+            else unpack<E>(vv[j], vf);
 #pragma unroll
             for (int e = 0; e < E; ++e) o[r][e] += pj * vf[e];
           }
@@ -244,7 +274,11 @@ __global__ void attn_decode_combine_kernel(const DecParams p, int D) {
 
 template <int D, int RMAX>
 int launch(const DecParams& p, int NB, cudaStream_t s) {
-  MARY_LAUNCH((attn_decode_kernel<D, RMAX>), dim3(NB, p.Hkv, p.nsplit), WARPS * 32, 0, s, p);
+  if (p.k_sz) {
+    MARY_LAUNCH((attn_decode_kernel<D, RMAX, true>), dim3(NB, p.Hkv, p.nsplit), WARPS * 32, 0, s, p);
+  } else {
+    MARY_LAUNCH((attn_decode_kernel<D, RMAX, false>), dim3(NB, p.Hkv, p.nsplit), WARPS * 32, 0, s, p);
+  }
   MARY_CHECK_LAUNCH();
   if (p.nsplit > 1) {
     MARY_LAUNCH(attn_decode_combine_kernel, dim3(NB, p.Hkv), 256, 0, s, p, D);
@@ -257,13 +291,14 @@ int launch(const DecParams& p, int NB, cudaStream_t s) {
 
 // Same contract as mary_paged_attention with DK == DV == D in {64, 128, 256} and RQ * (Hq / Hkv) <= 8 (<= 4 for D = 256).
 // Scratch (nsplit > 1): mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D).
-MARY_API int mary_paged_attention_decode(const void* q, const void* kc, const void* vc, void* out, const int* page_table,
-                                         const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
-                                         int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok, int64_t v_page,
-                                         int Hq, int Hkv, int D, int RQ, int nsplit, int window, float scale, float softcap,
-                                         float* scratch, cudaStream_t s) {
+static int decode_run(const void* q, const void* kc, const void* vc, const float* k_sz, const float* v_sz, void* out, const int* page_table,
+                      const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
+                      int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok, int64_t v_page,
+                      int Hq, int Hkv, int D, int RQ, int nsplit, int window, float scale, float softcap,
+                      float* scratch, cudaStream_t s) {
   if (NB <= 0) return MARY_OK;
   DecParams p;
+  p.k_sz = k_sz; p.v_sz = v_sz;
   p.q = (const __nv_bfloat16*)q; p.kc = (const __nv_bfloat16*)kc; p.vc = (const __nv_bfloat16*)vc; p.out = (__nv_bfloat16*)out;
   p.page_table = page_table; p.kv_len = kv_len; p.q_start = q_start; p.blk_seq = blk_seq; p.blk_q0 = blk_q0;
   p.max_pages = max_pages; p.page_size = page_size; p.k_tok = k_tok; p.k_page = k_page; p.v_tok = v_tok; p.v_page = v_page;
@@ -278,4 +313,67 @@ MARY_API int mary_paged_attention_decode(const void* q, const void* kc, const vo
   if (D == 128) { if (R <= 4) return launch<128, 4>(p, NB, s); if (R <= 8) return launch<128, 8>(p, NB, s); return MARY_ERR_BAD_ARG; }
   if (D == 64) { if (R <= 4) return launch<64, 4>(p, NB, s); if (R <= 8) return launch<64, 8>(p, NB, s); return MARY_ERR_BAD_ARG; }
   return MARY_ERR_BAD_ARG;
+}
+
+MARY_API int mary_paged_attention_decode(const void* q, const void* kc, const void* vc, void* out, const int* page_table,
+                                         const int* kv_len, const int* q_start, const int* blk_seq, const int* blk_q0, int NB,
+                                         int max_pages, int page_size, int64_t k_tok, int64_t k_page, int64_t v_tok, int64_t v_page,
+                                         int Hq, int Hkv, int D, int RQ, int nsplit, int window, float scale, float softcap,
+                                         float* scratch, cudaStream_t s) {
+  return decode_run(q, kc, vc, nullptr, nullptr, out, page_table, kv_len, q_start, blk_seq, blk_q0, NB, max_pages, page_size, k_tok, k_page,
+                    v_tok, v_page, Hq, Hkv, D, RQ, nsplit, window, scale, softcap, scratch, s);
+}
+
+// The same over an 8-bit cache: kc / vc are code pages [pages, page, Hkv, D] of unsigned bytes (strides in bytes), k_sz / v_sz the
+// (scale, zero) pairs [pages * page, Hkv, 2] f32 written by mary_kv_quant_append.  The cache rows are dequantised in registers
+// (one fused multiply-add per element), so the kernel streams half the bytes of the bf16 cache.
+MARY_API int mary_paged_attention_decode_q8(const void* q, const void* kc, const void* vc, const float* k_sz, const float* v_sz, void* out,
+                                            const int* page_table, const int* kv_len, const int* q_start, const int* blk_seq,
+                                            const int* blk_q0, int NB, int max_pages, int page_size, int64_t k_tok, int64_t k_page,
+                                            int64_t v_tok, int64_t v_page, int Hq, int Hkv, int D, int RQ, int nsplit, int window,
+                                            float scale, float softcap, float* scratch, cudaStream_t s) {
+  if (!k_sz || !v_sz) return MARY_ERR_BAD_ARG;
+  return decode_run(q, kc, vc, k_sz, v_sz, out, page_table, kv_len, q_start, blk_seq, blk_q0, NB, max_pages, page_size, k_tok, k_page,
+                    v_tok, v_page, Hq, Hkv, D, RQ, nsplit, window, scale, softcap, scratch, s);
+}
+
+namespace {
+
+// One warp per (row, kv head): range of the D values, codes = round((x - min) / scale) with scale = range / 255 (1 when the row is
+// constant), as the reference quantises its cache groups (src/models/gemma/gpu_quant.rs:28-90).
+__global__ void kv_quant_append_kernel(const __nv_bfloat16* __restrict__ rows, int64_t row_stride, const int64_t* __restrict__ slots,
+                                       uint8_t* __restrict__ codes, float* __restrict__ sz, int T, int Hkv, int D, int64_t n_slots,
+                                       int* status) {
+  pdl_sync();
+  const int w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (w >= T * Hkv) return;
+  const int t = w / Hkv, h = w % Hkv;
+  const int64_t slot = slots[t];
+  if (slot < 0 || slot >= n_slots) { if (lane == 0) atomicExch(status, MARY_ERR_BOUNDS); return; }
+  const __nv_bfloat16* src = rows + (int64_t)t * row_stride + (int64_t)h * D;
+  float lo = INFINITY, hi = -INFINITY;
+  for (int d = lane; d < D; d += 32) { const float x = __bfloat162float(src[d]); lo = fminf(lo, x); hi = fmaxf(hi, x); }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) { lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, o)); hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, o)); }
+  const float range = hi - lo;
+  const float sc = range > 0.f ? range / 255.f : 1.f;
+  uint8_t* dst = codes + (slot * Hkv + h) * D;
+  for (int d = lane; d < D; d += 32) {
+    const float x = __bfloat162float(src[d]);
+    dst[d] = (uint8_t)fminf(fmaxf(floorf(__fdividef(x - lo, sc) + 0.5f), 0.f), 255.f);
+  }
+  if (lane == 0) { sz[(slot * Hkv + h) * 2] = sc; sz[(slot * Hkv + h) * 2 + 1] = lo; }
+}
+
+}  // namespace
+
+// rows [T, Hkv, D] bf16 (row pitch row_stride elements) -> codes [n_slots, Hkv, D] u8 and sz [n_slots, Hkv, 2] f32 at slots[t].
+MARY_API int mary_kv_quant_append(const void* rows, int64_t row_stride, const int64_t* slots, void* codes, float* sz, int T, int Hkv, int D,
+                                  int64_t n_slots, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  const int warps = T * Hkv, per = 8;
+  MARY_LAUNCH(kv_quant_append_kernel, (warps + per - 1) / per, per * 32, 0, s, (const __nv_bfloat16*)rows, row_stride, slots, (uint8_t*)codes,
+              sz, T, Hkv, D, n_slots, mary_status_ptr());
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
 }

@@ -50,6 +50,18 @@ def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm: bool, 
     """Split ``qkv[T, (n_q+2 n_kv) D]``; per-head RMSNorm on q and k (learned gains) and optionally a weightless
     norm on v; split-half RoPE on q and k at ``meta.positions``; append k, v to the paged cache.
     Returns ``q[T, n_q, D]``."""
+    if _is_q8(kcache):
+        # 8-bit cache: norm and rotate into a bf16 staging row per token (the same kernel, slots 0..T-1), then quantise the rows
+        # into their pages
+        from types import SimpleNamespace
+        T = qkv.shape[0]
+        stage_k = torch.empty(T, 1, n_kv, head_dim, dtype=qkv.dtype, device=qkv.device)
+        stage_v = torch.empty_like(stage_k)
+        flat = SimpleNamespace(positions=meta.positions, slot_mapping=torch.arange(T, dtype=torch.int64, device=qkv.device))
+        q = qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm, inv_freq, flat, stage_k, stage_v, eps)
+        kv_quant_append(stage_k[:, 0], meta.slot_mapping, kcache)
+        kv_quant_append(stage_v[:, 0], meta.slot_mapping, vcache)
+        return q
     if _cuda(qkv):
         return _k().qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm, inv_freq, meta, kcache, vcache, eps)
     T = qkv.shape[0]
@@ -70,8 +82,34 @@ def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm: bool, 
     return q
 
 
+def _is_q8(cache) -> bool:
+    from ..runtime.kv_cache import Q8Pages
+    return isinstance(cache, Q8Pages)
+
+
+def kv_quant_append(rows, slots, pages) -> None:
+    """Quantise ``rows [T, Hkv, D]`` to 8-bit codes with a (scale, zero) pair per (token, head) and store them at the flat cache
+    slots ``slots [T]`` of ``pages`` (a ``runtime.kv_cache.Q8Pages``)."""
+    if _cuda(rows):
+        return _k().kv_quant_append(rows, slots, pages)
+    pages.append(rows, slots)
+
+
 def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, rel_bias=None):
-    """``rel_bias [T, Hq, extent]`` (f32): an additive bias on the scaled score of the key ``dist`` positions back, for ``dist < extent``."""
+    """``rel_bias [T, Hq, extent]`` (f32): an additive bias on the scaled score of the key ``dist`` positions back, for ``dist < extent``.
+    With an 8-bit cache, decode-shaped batches run the dequantising kernel; everything else dequantises the pages of the batch."""
+    if _is_q8(kcache):
+        if _cuda(q) and rel_bias is None and _k().decode_q8_supported(q, kcache, meta):
+            return _k().paged_attention_decode_q8(q, kcache, vcache, meta, scale, window, softcap)
+        import dataclasses
+        need = (meta.kv_len.long() + meta.page_size - 1) // meta.page_size
+        cols = torch.arange(meta.page_table.shape[1], device=need.device)[None]
+        used = (cols < need[:, None])
+        pages = torch.unique(meta.page_table[used].long())
+        remap = torch.zeros(kcache.shape[0], dtype=torch.int32, device=pages.device)
+        remap[pages] = torch.arange(pages.numel(), dtype=torch.int32, device=pages.device)
+        m2 = dataclasses.replace(meta, page_table=torch.where(used, remap[meta.page_table.long()], 0).to(torch.int32).contiguous())
+        return paged_attention(q, kcache.dequantize(pages, q.dtype), vcache.dequantize(pages, q.dtype), m2, scale, window, softcap, rel_bias)
     if _cuda(q):
         return _k().paged_attention(q, kcache, vcache, meta, scale, window, softcap, rel_bias=rel_bias)
     return ref.paged_attention(q, kcache, vcache, meta, scale, window, softcap, rel_bias=rel_bias)

@@ -323,6 +323,49 @@ def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsp
     return out
 
 
+declare("mary_paged_attention_decode_q8", "pppppp" + "ppppp" + "iii" + "llll" + "iiiiii" + "ffps")
+declare("mary_kv_quant_append", "plppp" + "iiils")
+
+
+def kv_quant_append(rows, slots, pages) -> None:
+    T, Hkv, D = rows.shape
+    assert rows.dtype == torch.bfloat16 and rows.stride(2) == 1 and rows.stride(1) == D and slots.dtype == torch.int64
+    assert tuple(pages.codes.shape[2:]) == (Hkv, D) and pages.codes.is_contiguous() and pages.sz.is_contiguous()
+    check(lib().mary_kv_quant_append(_p(rows), rows.stride(0), _p(slots), _p(pages.codes), _p(pages.sz), T, Hkv, D,
+                                     pages.codes.shape[0] * pages.codes.shape[1], _stream()), "kv_quant_append")
+
+
+def decode_q8_supported(q, kcache, meta) -> bool:
+    T, Hq, D = q.shape
+    Hkv = kcache.shape[2]
+    return (q.dtype == torch.bfloat16 and D == kcache.shape[3] and D in (64, 128, 256) and Hq % Hkv == 0
+            and Hq // Hkv <= (4 if D == 256 else 8) and meta.max_q_len <= 8)
+
+
+def paged_attention_decode_q8(q, kcache, vcache, meta, scale, window=0, softcap=0.0, nsplit=None):
+    """The decode kernel over an 8-bit cache (``runtime.kv_cache.Q8Pages``): rows are dequantised in registers."""
+    T, Hq, D = q.shape
+    Hkv = kcache.shape[2]
+    G = Hq // Hkv
+    cap = 4 if D == 256 else 8
+    rq = max(1, min(cap // G, meta.max_q_len))
+    blk_seq, blk_q0, NB = _q_blocks(meta, rq)
+    if nsplit is None:
+        want = max(1, DECODE_TARGET_CTAS // max(1, NB * Hkv))
+        span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
+        nsplit = max(1, min(want, 32, span // 64))
+    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    scratch = None
+    if nsplit > 1:
+        scratch = torch.empty(lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
+    kc, vc = kcache.codes, vcache.codes
+    check(lib().mary_paged_attention_decode_q8(_p(q.contiguous()), _p(kc), _p(vc), _p(kcache.sz), _p(vcache.sz), _p(out), _p(meta.page_table),
+                                               _p(meta.kv_len), _p(meta.q_start), _p(blk_seq), _p(blk_q0), NB, meta.page_table.shape[1],
+                                               meta.page_size, kc.stride(1), kc.stride(0), vc.stride(1), vc.stride(0), Hq, Hkv, D, rq,
+                                               nsplit, window, scale, softcap, _p(scratch), _stream()), "paged_attention_decode_q8")
+    return out
+
+
 declare("mary_attention_prefill", "ppppppppp" + "iiiiiiii" + "llll" + "ifis")
 declare("mary_attention_prefill_supported", "ii")
 PREFILL_MIN_ROWS = 48     # mean query tokens per sequence from which the 128-row tensor-core tiles pay off

@@ -109,17 +109,69 @@ class PageAllocator:
             pass
 
 
+class Q8Pages:
+    """The pages of one layer's K (or V) as 8-bit codes: ``codes [pages, page, Hkv, D]`` unsigned bytes and ``sz [pages, page, Hkv, 2]``
+    f32 ``(scale, zero)`` per (token, kv head); element = ``code * scale + zero``, ``scale = (max - min) / 255``, ``zero = min`` — the
+    grouping and rounding of the reference's device cache quantiser (src/models/gemma/gpu_quant.rs:28-166), which packs four codes
+    per 32-bit word where this keeps plain bytes.  Half the bytes of a bf16 cache plus 8 bytes per (token, head)."""
+
+    def __init__(self, num_pages: int, page_size: int, kv_heads: int, head_dim: int, device="cpu"):
+        self.codes = torch.zeros(num_pages, page_size, kv_heads, head_dim, dtype=torch.uint8, device=device)
+        self.sz = torch.zeros(num_pages, page_size, kv_heads, 2, dtype=torch.float32, device=device)
+        self.sz[..., 0] = 1.0
+
+    shape = property(lambda self: self.codes.shape)
+    device = property(lambda self: self.codes.device)
+    is_cuda = property(lambda self: self.codes.is_cuda)
+
+    def dim(self) -> int:
+        return 4
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.sz.numel() * 4
+
+    @staticmethod
+    def quantize(rows):
+        """``rows [..., D]`` -> ``(codes uint8, sz [..., 2] f32)`` by the rule above (round half up, as the device kernel)."""
+        x = rows.float()
+        lo, hi = x.min(-1, keepdim=True).values, x.max(-1, keepdim=True).values
+        rng = hi - lo
+        sc = torch.where(rng > 0, rng / 255.0, torch.ones_like(rng))
+        codes = torch.floor((x - lo) / sc + 0.5).clamp(0, 255).to(torch.uint8)
+        return codes, torch.cat([sc, lo], -1)
+
+    def append(self, rows, slots) -> None:
+        """Quantise ``rows [T, Hkv, D]`` into the flat slots ``slots [T]`` (page * page_size + offset)."""
+        codes, sz = self.quantize(rows)
+        self.codes.view(-1, *self.codes.shape[2:])[slots.long()] = codes
+        self.sz.view(-1, *self.sz.shape[2:])[slots.long()] = sz
+
+    def dequantize(self, pages=None, dtype=torch.bfloat16):
+        """bf16 pages ``[n, page, Hkv, D]`` of the listed pages (all when ``None``)."""
+        c = self.codes if pages is None else self.codes[pages.long()]
+        z = self.sz if pages is None else self.sz[pages.long()]
+        return (c.float() * z[..., :1] + z[..., 1:]).to(dtype)
+
+
 class PagedKVCache:
-    """Device storage for the pages of every layer."""
+    """Device storage for the pages of every layer.  ``kv_dtype="int8"`` keeps K and V as :class:`Q8Pages`."""
 
     def __init__(self, num_layers: int, num_pages: int, page_size: int, kv_heads: int | list[int], head_dim: int | list[int],
-                 dtype=torch.bfloat16, device="cpu", latent_dim: int | None = None, alias_v_to_k: bool = False):
+                 dtype=torch.bfloat16, device="cpu", latent_dim: int | None = None, alias_v_to_k: bool = False, kv_dtype: str | None = None):
         self.alloc = PageAllocator(num_pages, page_size)
         self.page_size, self.num_pages, self.num_layers = page_size, num_pages, num_layers
         self.latent = latent_dim is not None
         heads = kv_heads if isinstance(kv_heads, list) else [kv_heads] * num_layers
         dims = head_dim if isinstance(head_dim, list) else [head_dim] * num_layers
-        if self.latent:
+        self.kv_dtype = kv_dtype
+        if kv_dtype not in (None, "int8"):
+            raise ValueError(f"kv_dtype {kv_dtype!r}: only None (the activation dtype) and 'int8' are implemented")
+        if kv_dtype == "int8":
+            if self.latent or alias_v_to_k:
+                raise ValueError("the 8-bit cache holds separate K and V pages of attention heads, not a latent or aliased cache")
+            self.k = [Q8Pages(num_pages, page_size, heads[i], dims[i], device) for i in range(num_layers)]
+            self.v = [Q8Pages(num_pages, page_size, heads[i], dims[i], device) for i in range(num_layers)]
+        elif self.latent:
             self.k = [torch.zeros(num_pages, page_size, latent_dim, dtype=dtype, device=device) for _ in range(num_layers)]
             self.v = self.k
         else:
@@ -127,5 +179,7 @@ class PagedKVCache:
             self.v = self.k if alias_v_to_k else [torch.zeros_like(t) for t in self.k]
 
     def bytes(self) -> int:
+        if self.kv_dtype == "int8":
+            return sum(t.nbytes() for t in self.k) + sum(t.nbytes() for t in self.v)
         n = sum(t.numel() * t.element_size() for t in self.k)
         return n if (self.latent or self.v is self.k) else 2 * n

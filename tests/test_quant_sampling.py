@@ -137,3 +137,96 @@ def test_device_sampler_picks_the_reference_token_for_every_setting():
     ids = K.sample_top_k_top_p(small, 1.0, seed=5, step=0)
     freq = torch.bincount(ids.long(), minlength=4).float().cpu() / 4096
     assert (freq - torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0)).abs().max() < 0.03
+
+
+def _q8_case(seed=0, S=3, Hq=8, Hkv=2, D=64, page=16, lens=(40, 17, 70), device="cpu", dtype=torch.float32):
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    g = torch.Generator().manual_seed(seed)
+    pages = sum((n + page - 1) // page for n in lens) + 2
+    full = PagedKVCache(1, pages, page, Hkv, D, dtype=dtype, device=device)
+    q8 = PagedKVCache(1, pages, page, Hkv, D, dtype=dtype, device=device, kv_dtype="int8")
+    for s, n in enumerate(lens):
+        full.alloc.extend(s, n)
+        q8.alloc.extend(s, n)
+    table, kv = full.alloc.page_table(list(range(S)))
+    meta_fill = BatchMeta.build(list(lens), kv, table, page, device)
+    T = sum(lens)
+    k = (torch.randn(T, Hkv, D, generator=g) * 1.5 + 0.3).to(dtype).to(device)
+    v = torch.randn(T, Hkv, D, generator=g).to(dtype).to(device)
+    return full, q8, meta_fill, k, v, table, kv, g
+
+
+def test_int8_kv_pages_quantise_like_the_reference_and_serve_attention():
+    from mary_b200 import ops
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import Q8Pages
+    full, q8, meta, k, v, table, kv, g = _q8_case()
+    # the rule: per (token, head) range / 255, zero = min, round half up; a constant row keeps scale 1
+    codes, sz = Q8Pages.quantize(torch.tensor([[0.0, 1.0, 2.55], [3.0, 3.0, 3.0]]))
+    assert codes.tolist() == [[0, 100, 255], [0, 0, 0]] and torch.allclose(sz, torch.tensor([[0.01, 0.0], [1.0, 3.0]]))
+    full.k[0].view(-1, 2, 64)[meta.slot_mapping] = k
+    full.v[0].view(-1, 2, 64)[meta.slot_mapping] = v
+    ops.kv_quant_append(k, meta.slot_mapping, q8.k[0])
+    ops.kv_quant_append(v, meta.slot_mapping, q8.v[0])
+    back = q8.k[0].dequantize(dtype=torch.float32).view(-1, 2, 64)[meta.slot_mapping]
+    step = (k.max(-1).values - k.min(-1).values) / 255
+    assert ((back - k).abs() <= step[..., None] * 0.5001 + 1e-6).all()
+    assert q8.bytes() < 0.6 * full.bytes() * (2 / 4)                                      # half of a bf16 cache, plus the pairs
+    # decode rows and a prefill chunk against the unquantised cache: the error is the quantisation step, not more
+    for q_lens in ([1, 1, 1], [3, 0, 2], [40, 17, 70]):
+        m = BatchMeta.build(q_lens, kv, table, 16, "cpu")
+        q = torch.randn(sum(q_lens), 8, 64, generator=g)
+        for window in (0, 24):
+            want = ops.paged_attention(q, full.k[0], full.v[0], m, 0.125, window)
+            got = ops.paged_attention(q, q8.k[0], q8.v[0], m, 0.125, window)
+            assert (got - want).abs().max() < 0.03 and not torch.equal(got, want)
+            exact = ops.paged_attention(q, q8.k[0].dequantize(dtype=torch.float32), q8.v[0].dequantize(dtype=torch.float32), m, 0.125, window)
+            assert torch.allclose(got, exact, atol=1e-5)
+    with pytest.raises(ValueError):
+        from mary_b200.runtime.kv_cache import PagedKVCache
+        PagedKVCache(1, 4, 16, 1, 64, latent_dim=576, kv_dtype="int8")
+
+
+@pytest.mark.gpu
+def test_int8_kv_append_and_dequantising_decode_kernel_match_the_host_rule():
+    from mary_b200 import ops
+    from mary_b200.ops import cuda as K
+    from mary_b200.ops import reference as ref
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import Q8Pages
+    for D, Hq, Hkv, lens in ((64, 8, 2, (40, 17, 700)), (128, 8, 1, (300, 5, 64)), (256, 8, 4, (1000, 33, 250))):
+        full, q8, meta, k, v, table, kv, g = _q8_case(seed=D, Hq=Hq, Hkv=Hkv, D=D, lens=lens, device="cuda", dtype=torch.bfloat16)
+        before = K.LAUNCHES
+        ops.kv_quant_append(k, meta.slot_mapping, q8.k[0])
+        ops.kv_quant_append(v, meta.slot_mapping, q8.v[0])
+        assert K.LAUNCHES == before + 2 and K.last_status() == 0
+        codes, sz = Q8Pages.quantize(k.cpu())
+        got_codes = q8.k[0].codes.view(-1, Hkv, D)[meta.slot_mapping].cpu()
+        assert (got_codes.int() - codes.int()).abs().max() <= 1 and (got_codes == codes).float().mean() > 0.999   # fast division may move a tie
+        assert torch.allclose(q8.k[0].sz.view(-1, Hkv, 2)[meta.slot_mapping].cpu(), sz, rtol=1e-5, atol=1e-7)
+        kd, vd = q8.k[0].dequantize(dtype=torch.float32).cpu(), q8.v[0].dequantize(dtype=torch.float32).cpu()
+        for q_lens in ([1, 1, 1], [2, 1, 2]):
+            m = BatchMeta.build(q_lens, kv, table, 16, "cuda")
+            mc = BatchMeta.build(q_lens, kv, table, 16, "cpu")
+            q = torch.randn(sum(q_lens), Hq, D, generator=g).bfloat16()
+            for window, softcap in ((0, 0.0), (128, 0.0), (0, 30.0)):
+                assert K.decode_q8_supported(q.cuda(), q8.k[0], m)
+                before = K.LAUNCHES
+                got = ops.paged_attention(q.cuda(), q8.k[0], q8.v[0], m, D ** -0.5, window, softcap).float().cpu()
+                assert K.LAUNCHES > before and K.last_status() == 0
+                want = ref.paged_attention(q.float(), kd, vd, mc, D ** -0.5, window, softcap)
+                assert (got - want).abs().max() < 0.02, (D, q_lens, window, softcap)
+        # a prefill chunk takes the dequantise-the-batch path and agrees as well
+        m = BatchMeta.build(list(lens), kv, table, 16, "cuda")
+        mc = BatchMeta.build(list(lens), kv, table, 16, "cpu")
+        q = torch.randn(sum(lens), Hq, D, generator=g).bfloat16()
+        got = ops.paged_attention(q.cuda(), q8.k[0], q8.v[0], m, D ** -0.5).float().cpu()
+        want = ref.paged_attention(q.float(), kd, vd, mc, D ** -0.5)
+        assert (got - want).abs().max() < 0.03
+    # out-of-range slot: refused through the status word, nothing written
+    bad = torch.tensor([10 ** 9], dtype=torch.int64, device="cuda")
+    K.lib().mary_kv_quant_append(k[:1].data_ptr(), k.stride(0), bad.data_ptr(), q8.k[0].codes.data_ptr(), q8.k[0].sz.data_ptr(), 1, Hkv, D,
+                                 q8.k[0].codes.shape[0] * 16, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert K.last_status() != 0 and K.last_status() == 0                                 # reading clears it
