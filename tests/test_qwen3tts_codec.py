@@ -129,6 +129,8 @@ def test_decoder_in_bf16_on_the_gpu_runs_on_the_package_gemm_and_tracks_the_f32_
     cfg = C.CodecConfig(num_code_groups=4, codebook_size=64, code_dim=64, quant_out=128, latent=256, hidden=128, tr_layers=2, tr_heads=2,
                         tr_head_dim=64, tr_inter=256, tr_window=8, decoder_dim=256, upsample_rates=[4, 2], upsampling_ratios=[2])
     cpu = C.CodecDecoder(cfg).init_random_(0)
+    tail = "decoder.decoder.4.conv.weight"
+    cpu.set_tensor(tail, cpu.P[tail] * 0.02)                                             # keep the waveform inside (-1, 1): no clamping hides or blows up errors
     gpu = C.CodecDecoder(cfg, dtype=torch.bfloat16, device="cuda")
     for n, v in cpu.P.items():
         gpu.set_tensor(n, v)
@@ -137,4 +139,6 @@ def test_decoder_in_bf16_on_the_gpu_runs_on_the_package_gemm_and_tracks_the_f32_
     before = K.LAUNCHES
     got = gpu.decode(codes).cpu()
     assert K.LAUNCHES > before + 20 and K.last_status() == 0                             # the convolutions ran as this package's GEMMs
-    assert got.shape == want.shape and (got - want).abs().max() < 0.08 * max(want.abs().max().item(), 1e-3) + 0.02
+    err = (got - want).abs()
+    assert got.shape == want.shape and want.abs().max() < 1.0 and want.abs().max() > 0.1
+    assert err.max() < 0.25 * want.abs().max() and err.median() < 0.04 * want.abs().max()    # bf16 through ~20 stacked layers
