@@ -64,6 +64,9 @@ struct GemmParams {
   const int* g_tiles;
   const int* g_meta;
   int g_experts;
+  // 1: the weight operand is constant (model weights) and the launch allows programmatic dependent launch, so the producer may
+  // fetch the first weight tiles while the previous kernel of the stream is still draining; activations wait for it as always
+  int w_static;
 };
 
 // One unit of work of a CTA: K-blocks [kb0, kb1) of output tile (tr, tc) of problem bz; `seg` of `nseg` partial results of that
@@ -147,7 +150,7 @@ struct Cfg {
 template <int BN, bool GLU>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
-  pdl_sync();
+  pdl_launch();
   using C = Cfg<BN, GLU>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~uintptr_t(1023));
@@ -181,7 +184,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       int stage = 0; uint32_t phase = 0;
       WorkIter iter(p);
       WorkItem w;
-      while (iter.next(w)) {
+      bool have = false;
+      int pre = 0;                               // stages whose barrier is armed and whose weight tile is already in flight
+      if (p.w_static) {
+        // constant weights: the first tiles of this CTA's first work item are requested before the previous kernel has finished
+        have = iter.next(w);
+        if (have) {
+          pre = min(w.kb1 - w.kb0, C::STAGES);
+          for (int i = 0; i < pre; ++i) {
+            uint8_t* st = smem + i * C::STAGE_BYTES;
+            const int kb = w.kb0 + i;
+            mbar_expect_tx(&full[i], C::STAGE_BYTES);
+            if (p.swap) {
+              tma_load_3d(st, &tm_r, &full[i], kb * BK, w.tr * BM, w.bz);
+              if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[i], kb * BK, p.glu_offset + w.tr * BM, w.bz);
+            } else {
+              tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[i], kb * BK, w.tc * BN, w.bz);
+            }
+          }
+        }
+      }
+      pdl_wait();
+      if (!p.w_static) have = iter.next(w);
+      while (have) {
         const int tr = w.tr, tc = w.tc;
         int zr = w.bz, zc = w.bz;
         if (p.g_tiles) {
@@ -190,14 +215,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
           zc = p.swap ? 0 : e;
         }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
           uint8_t* st = smem + stage * C::STAGE_BYTES;
-          mbar_expect_tx(&full[stage], C::STAGE_BYTES);
-          tma_load_3d(st, &tm_r, &full[stage], kb * BK, tr * BM, zr);
-          if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[stage], kb * BK, p.glu_offset + tr * BM, zr);
-          tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, zc);
+          if (pre > 0) {
+            --pre;                               // add the activation tile to the armed stage
+            if (p.swap) tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, zc);
+            else tma_load_3d(st, &tm_r, &full[stage], kb * BK, tr * BM, zr);
+          } else {
+            if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
+            mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+            tma_load_3d(st, &tm_r, &full[stage], kb * BK, tr * BM, zr);
+            if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[stage], kb * BK, p.glu_offset + tr * BM, zr);
+            tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, zc);
+          }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
         }
+        have = iter.next(w);
       }
     }
   } else if (warp == 1) {
@@ -235,6 +267,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
+    pdl_wait();                            // before the first store: an earlier kernel may still read what this one overwrites
     const int q = warp & 3;                // TMEM lane quarter this warp may access
     int it = 0;
     WorkIter iter(p);
@@ -393,11 +426,17 @@ static int make_tmap_3d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
 }
 
 // Batched form: `batch` independent problems; operand b starts at base + b * batch_stride (elements).
+static thread_local int g_static_weights = 0;
+
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
                      const uint64_t* rs_bufs, int rs_world, int rs_src, int rs_rpr, cudaStream_t stream, float* ws = nullptr,
                      int64_t ws_floats = 0, int* counters = nullptr, int n_counters = 0, bool stream_k = false,
                      const int* g_tiles = nullptr, const int* g_meta = nullptr, int g_experts = 0, int g_nt = 0);
+
+// Tells the GEMM launchers called next on THIS thread that their W operand holds constant model weights (1) or may have been
+// written by an earlier kernel of the stream (0, the default).  Only read when programmatic dependent launch is enabled.
+MARY_API void mary_gemm_hint_static_weights(int on) { g_static_weights = on ? 1 : 0; }
 
 MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
                                     int64_t ldo, int batch, int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha,
@@ -472,6 +511,7 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   p.g_tiles = g_tiles;
   p.g_meta = g_meta;
   p.g_experts = g_experts;
+  p.w_static = (g_static_weights && mary_pdl_enabled() && !g_tiles && !(glu && !use_swap)) ? 1 : 0;
   if (g_tiles) {
     if (batch != 1 || split_k != 1) return MARY_ERR_BAD_ARG;
     if (use_swap) {

@@ -192,7 +192,36 @@ def gemm_splitk(x, w, split_k: int, out=None, f32: bool = False, bias=None, swap
     return out
 
 
+class _StaticWeights:
+    """While active, the GEMM launchers of this thread are told that their ``w`` operand holds constant model weights, so that under
+    programmatic dependent launch (``MARY_PDL=1``) a kernel may request its first weight tiles before its predecessor has finished."""
+    depth = 0
+
+    def __enter__(self):
+        from ..utils import flags
+        if flags.get("MARY_PDL"):
+            _StaticWeights.depth += 1
+            if _StaticWeights.depth == 1:
+                lib().mary_gemm_hint_static_weights(1)
+
+    def __exit__(self, *exc):
+        from ..utils import flags
+        if flags.get("MARY_PDL"):
+            _StaticWeights.depth -= 1
+            if _StaticWeights.depth == 0:
+                lib().mary_gemm_hint_static_weights(0)
+
+
+static_weights = _StaticWeights()
+declare("mary_gemm_hint_static_weights", "i")
+
+
 def linear(x, w, bias=None):
+    with static_weights:
+        return _linear(x, w, bias)
+
+
+def _linear(x, w, bias=None):
     shp = x.shape
     x2 = x.reshape(-1, shp[-1])
     if x2.stride(-1) != 1:
@@ -207,14 +236,16 @@ def linear_f32(x, w, split_k: int | None = None):
     """Row-parallel style GEMM whose f32 result feeds a norm kernel directly (no bf16 rounding in between)."""
     M, K = x.shape
     sk = split_k or _auto_split_k(M, w.shape[0], K)
-    return gemm_splitk(x, w, 0 if split_k is None else sk, f32=True) if sk > 1 else gemm(x, w, epi="f32")
+    with static_weights:
+        return gemm_splitk(x, w, 0 if split_k is None else sk, f32=True) if sk > 1 else gemm(x, w, epi="f32")
 
 
 def linear_glu(x, w_gu, act: str = "geglu"):
     M = x.shape[0]
-    if M <= 128:
-        return gemm(x, w_gu, glu=act)
-    return glu(gemm(x, w_gu), act)
+    with static_weights:
+        if M <= 128:
+            return gemm(x, w_gu, glu=act)
+        return glu(gemm(x, w_gu), act)
 
 
 # --------------------------------------------------------------------------- norms and friends
@@ -572,7 +603,8 @@ def mla_absorb_q(qb, w_uk, inv_freq, meta, H):
     """``qb[T, H*192]`` -> ``q_full[T, H, 576]``: nope part times ``w_uk[H, 512, 128]`` (absorbed W_UK), rope part rotated."""
     T = qb.shape[0]
     q_full = torch.empty(T, H, 576, dtype=torch.bfloat16, device=qb.device)
-    gemm_batched(qb, w_uk, q_full, T, 512, 128, H * 192, 128, H * 576, H, 192, 512 * 128, 576)
+    with static_weights:
+        gemm_batched(qb, w_uk, q_full, T, 512, 128, H * 192, 128, H * 576, H, 192, 512 * 128, 576)
     check(lib().mary_mla_q_rope(_p(qb), _p(inv_freq), _p(meta.positions), _p(q_full), H, T, _stream()), "mla_q_rope")
     return q_full
 
@@ -581,5 +613,6 @@ def mla_unabsorb_o(o_lat, w_uv, H):
     """``o_lat[T, H, 512]`` -> ``o[T, H*128]`` with ``w_uv[H, 128, 512]``."""
     T = o_lat.shape[0]
     o = torch.empty(T, H * 128, dtype=torch.bfloat16, device=o_lat.device)
-    gemm_batched(o_lat, w_uv, o, T, 128, 512, H * 512, 512, H * 128, H, 512, 128 * 512, 128)
+    with static_weights:
+        gemm_batched(o_lat, w_uv, o, T, 128, 512, H * 512, 512, H * 128, H, 512, 128 * 512, 128)
     return o

@@ -362,3 +362,24 @@ def test_stream_probes_copy_exactly_and_reject_misaligned_buffers():
     torch.cuda.synchronize()
     assert torch.equal(src, dst)
     assert lib().mary_stream_copy(_p(src[1:]), _p(dst), 1024, _stream()) == 4            # MARY_ERR_BAD_ARG: not 16-byte aligned
+
+
+@pytest.mark.gpu
+def test_programmatic_dependent_launch_with_early_weight_requests_changes_no_bit():
+    """A chain of GEMMs, norms and a GEMM over freshly written operands, eager and as a replayed CUDA graph with changing inputs:
+    with MARY_PDL=1 (kernels start while their predecessor drains; weight tiles are requested before the wait) every result
+    equals the serialised run bit for bit."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    digests = {}
+    for M in (48, 300):
+        for pdl in ("0", "1"):
+            env = dict(os.environ, MARY_PDL=pdl, PYTHONPATH=os.path.dirname(here))
+            r = subprocess.run([sys.executable, os.path.join(here, "pdl_worker.py"), str(M)], env=env, capture_output=True, text=True, timeout=300)
+            assert r.returncode == 0, r.stderr[-2000:]
+            line = [ln for ln in r.stdout.splitlines() if ln.startswith("DIGEST")][0].split()
+            assert line[3] == pdl
+            digests[(M, pdl)] = line[1]
+        assert digests[(M, "0")] == digests[(M, "1")]
