@@ -127,6 +127,10 @@ def main():
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl", "sp"],
                     help="fused: own all-reduce kernels over peer memory; sp: GEMM->reduce-scatter epilogue + fused norm/all-gather (dense decoders); nccl: library arm")
     ap.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (the JSON line then names a reduced config)")
+    ap.add_argument("--from-pile", default=None, metavar="PATH",
+                    help="MoE decoders: take the weights from a pile instead of initialising them on the device; rank 0 writes the pile first "
+                         "when PATH does not exist (the whole single-rank model must fit one GPU for that, so combine with --layers for k3); "
+                         "every rank then loads ITS shard config-free (placement facts for experts, the cutting rule for tensor parallelism)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--replicated-head", action="store_true", help="keep the whole LM head on every rank (default: vocabulary-parallel head)")
     ap.add_argument("--no-ttft", action="store_true")
@@ -228,7 +232,27 @@ def main():
 
     # ---------------------------------------------------------------- model
     t0 = time.time()
-    model = Gemma4Model(cfg, tp=par, dtype=torch.bfloat16, device=dev) if is_gemma else MoEDecoder(cfg, par=par, dtype=torch.bfloat16, device=dev)
+    from_pile = None
+    if args.from_pile and not is_gemma:
+        from mary_b200.models.moe.weights import load_from_pile, save_to_pile
+        from mary_b200.pile import Pile, signing_key_file
+        if rank == 0 and not os.path.exists(args.from_pile):
+            say(f"writing {args.from_pile}")
+            full = MoEDecoder(cfg, dtype=torch.bfloat16, device=dev)
+            init_random_(full, seed=0)
+            pile = Pile.open(args.from_pile)
+            save_to_pile(pile, signing_key_file(args.from_pile + ".key"), full, name=cfg.name)
+            pile.close()
+            del full
+            torch.cuda.empty_cache()
+        if world > 1:
+            dist.barrier()
+        pile = Pile.open(args.from_pile, create=False)
+        from_pile = load_from_pile(pile, par=par, device=dev)
+        pile.close()
+        say(f"loaded this rank's shard from {args.from_pile} in {time.time() - t0:.1f} s")
+    model = from_pile if from_pile is not None else (
+        Gemma4Model(cfg, tp=par, dtype=torch.bfloat16, device=dev) if is_gemma else MoEDecoder(cfg, par=par, dtype=torch.bfloat16, device=dev))
     B_global, B = B, B_local
     # every step can commit up to 1 + k tokens; the decoder runs the eager census step, the capture warm-up, W warm-up steps,
     # the timed steps and the same number again in the end-to-end loop, all from the same context
@@ -253,7 +277,10 @@ def main():
         n_moe = sum(1 for i in range(cfg.num_hidden_layers) if not cfg.is_dense(i)) + cfg.num_mtp_layers
         budget = free - kv_bytes - 12 * (1 << 30)
         slabs = int(max(1, min(n_moe, budget // slab_bytes)))
-        init_random_(model, seed=0, expert_slabs=slabs)
+        if from_pile is None:
+            init_random_(model, seed=0, expert_slabs=slabs)
+        else:
+            slabs = n_moe                                # every layer's experts came from the pile
     # non-expert weights must be identical on every rank that replicates them; experts differ per rank by construction
     spec = model.kv_spec()
     cache = PagedKVCache(spec["num_layers"], pages, page, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16, device=dev,
@@ -400,7 +427,7 @@ def main():
                 "baseline": dict(baseline, what="same-box library arm of this repository (torch.matmul, torch._grouped_mm, NCCL; bf16 experts, "
                                               "eager launches), same model, batch, context, speculation and layout; the reference itself cannot "
                                               "be built here and publishes no number at this configuration"),
-                "dtype": "bf16 activations, NVFP4 experts", "data": "synthetic token ids, random-init weights, synthetic KV context",
+                "dtype": "bf16 activations, NVFP4 experts", "data": "synthetic token ids, random-init weights" + (" written to and loaded from a pile" if from_pile is not None else "") + ", synthetic KV context",
                 "impl": "ours",
                 "config": {"model": cfg.name + (" (REDUCED layers: debug)" if reduced else ""), "layers": cfg.num_hidden_layers,
                            "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,

@@ -41,34 +41,41 @@ def slice_experts(ex: NVFP4Experts, r: int, n: int, tail: int = 0) -> NVFP4Exper
                         cut(ex.w2_q, r2), cut(ex.w2_sf, r2 // 128), cut(ex.w2_s2, 1), ex.act)
 
 
+def cut_parameter(cfg, mod, name: str, src, r: int, n: int, vocab_parallel: bool):
+    """The slice of the full parameter ``name`` (owned by module ``mod``) that tensor-parallel rank ``r`` of ``n`` holds: the one rule
+    for cutting a model in memory (``shard_from_full``) and for loading a rank's shard from a pile (``weights.load_from_pile``)."""
+    if n == 1:
+        return src
+    leaf = name.rpartition(".")[2]
+    if isinstance(mod, GQAAttention):
+        D = cfg.head_dim
+        if leaf == "w_qkv":
+            q, k, v = src.split([cfg.num_attention_heads * D, cfg.num_key_value_heads * D, cfg.num_key_value_heads * D], 0)
+            return torch.cat([_rows(q, r, n), _rows(k, r, n), _rows(v, r, n)], 0)
+        if leaf == "w_o":
+            return _cols(src, r, n)
+    elif isinstance(mod, MLAAttention):
+        if leaf in ("w_qb", "w_uk", "w_uv"):
+            return _rows(src, r, n)
+        if leaf == "w_o":
+            return _cols(src, r, n)
+    elif isinstance(mod, DenseFFN):
+        return _gu(src, r, n) if leaf == "w_gu" else _cols(src, r, n)
+    elif name == "lm_head" and vocab_parallel:
+        return _rows(src, r, n)
+    return src
+
+
 def shard_from_full(full: MoEDecoder, par, device=None) -> MoEDecoder:
     r, n = par.tp_rank, par.tp_size        # attention / dense split; experts split by the expert-parallel coordinates
     er, en = par.ep_rank, par.ep_size
     dev = device or full.embed.device
     m = MoEDecoder(full.cfg, par=par, dtype=full.dtype, device=dev)
     fm = dict(full.named_modules())
+    full_params = dict(full.named_parameters())
     with torch.no_grad():
         for name, p in m.named_parameters():
-            src = dict(full.named_parameters())[name]
-            mod_name, _, leaf = name.rpartition(".")
-            mod = fm.get(mod_name)
-            if isinstance(mod, GQAAttention):
-                c = full.cfg
-                D = c.head_dim
-                if leaf == "w_qkv":
-                    q, k, v = src.split([c.num_attention_heads * D, c.num_key_value_heads * D, c.num_key_value_heads * D], 0)
-                    src = torch.cat([_rows(q, r, n), _rows(k, r, n), _rows(v, r, n)], 0)
-                elif leaf == "w_o":
-                    src = _cols(src, r, n)
-            elif isinstance(mod, MLAAttention):
-                if leaf in ("w_qb", "w_uk", "w_uv"):
-                    src = _rows(src, r, n)
-                elif leaf == "w_o":
-                    src = _cols(src, r, n)
-            elif isinstance(mod, DenseFFN):
-                src = _gu(src, r, n) if leaf == "w_gu" else _cols(src, r, n)
-            elif name == "lm_head" and m.vocab_parallel:
-                src = _rows(src, r, n)
+            src = cut_parameter(full.cfg, fm.get(name.rpartition(".")[0]), name, full_params[name], r, n, m.vocab_parallel)
             p.copy_(src.to(dev))
     for (_, a), (_, b) in zip(m.named_modules(), full.named_modules()):
         if isinstance(a, MoEFFN):

@@ -52,12 +52,18 @@ def load_from_pile(pile, par=None, device="cpu", dtype=torch.bfloat16) -> MoEDec
     cfg = MoEConfig.from_json(load_config(pile, facts, index.roots[0]))
     full_par = par
     model = MoEDecoder(cfg, par=full_par, dtype=dtype, device=device)
-    if model.par.tp_size != 1:
-        raise NotImplementedError("load the single-rank model and cut it with models.moe.shard.shard_from_full for tensor parallelism")
+    from .shard import cut_parameter
+    mods = dict(model.named_modules())
+    tp_r, tp_n = model.par.tp_rank, model.par.tp_size
     with torch.no_grad():
         for n, p in model.named_parameters():
+            # one full tensor at a time on the host; a tensor-parallel rank keeps its slice only (the same rule that cuts a model
+            # in memory), so no rank ever holds the whole model
             leaf = index.leaf(n)
             t = leaf.torch() if leaf.elem in (Elem.BF16, Elem.F32, Elem.F16) else torch.from_numpy(leaf.to_f32())
+            t = cut_parameter(cfg, mods.get(n.rpartition(".")[0]), n, t, tp_r, tp_n, getattr(model, "vocab_parallel", False))
+            if tuple(t.shape) != tuple(p.shape):
+                raise ValueError(f"{n}: the pile holds {tuple(t.shape)} after cutting for rank {tp_r} of {tp_n}, the model wants {tuple(p.shape)}")
             p.copy_(t.to(dtype if p.dtype == dtype else p.dtype))
     moes = _moe_modules(model)
     placement = index.experts_in_layers(0, len(moes))

@@ -32,6 +32,21 @@ def test_moe_model_roundtrips_through_a_pile_config_free(tmp_path):
         tp_rank, tp_size, ep_rank, ep_size, ep_mode = 0, 1, 1, 2, "replicated"
     m3 = load_from_pile(pile, par=Par())
     assert e1[0].experts.E == 8 and [x for x in m3.modules() if hasattr(x, "experts") and x.experts is not None][0].experts.E == 4
+    # a tensor-parallel rank loads ITS shard from the pile: equal to cutting the full model in memory, for every rank
+    from mary_b200.models.moe.shard import shard_from_full
+    from mary_b200.parallel.group import ParallelGroup
+    for vocab_parallel in (False, True):
+        for r in range(2):
+            par = ParallelGroup(rank=r, size=2, vocab_parallel=vocab_parallel)
+            want, got = shard_from_full(m, par), load_from_pile(pile, par=ParallelGroup(rank=r, size=2, vocab_parallel=vocab_parallel))
+            cut = 0
+            for (n, a), (_, b) in zip(want.named_parameters(), got.named_parameters()):
+                assert a.shape == b.shape and torch.equal(a, b), n
+                cut += int(a.numel() < dict(m.named_parameters())[n].numel())
+            assert cut >= 4                                                  # attention, dense FFN (and the head) really are slices
+            for a, b in zip([x for x in want.modules() if getattr(x, "experts", None) is not None],
+                            [x for x in got.modules() if getattr(x, "experts", None) is not None]):
+                assert a.experts.E == b.experts.E and torch.equal(a.experts.w13_q, b.experts.w13_q) and torch.equal(a.experts.w2_sf, b.experts.w2_sf)
     pile.close()
 
 
