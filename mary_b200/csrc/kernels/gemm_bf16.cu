@@ -150,7 +150,6 @@ struct Cfg {
 template <int BN, bool GLU>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
-  pdl_launch();
   using C = Cfg<BN, GLU>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~uintptr_t(1023));
@@ -177,6 +176,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // dependents may start only now that this CTA holds its TMEM columns: a successor that allocated first and then waited for this
+  // kernel would leave both waiting on each other
+  pdl_launch();
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
