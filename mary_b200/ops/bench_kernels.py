@@ -92,6 +92,23 @@ def bench_attn(cases=None):
                 print(f"decode attn [{kernel}, target {ctas} CTAs] B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, "
                       f"{gb:.0f} GB/s, {gb / hbm:.2f} {tag}")
         K.DECODE_TARGET_CTAS = 2368
+        # the tensor-core kernel, with 16- and 32-token pages and a sweep of the split count
+        for page in (16, 32):
+            pages = B * ((L + page - 1) // page) + 1
+            c2 = PagedKVCache(1, pages, page, Hkv, D, dtype=torch.bfloat16, device="cuda")
+            for s in range(B):
+                c2.alloc.extend(s, L)
+            t2, l2 = c2.alloc.page_table(list(range(B)))
+            m2 = BatchMeta.build([1] * B, l2, t2, page, "cuda")
+            c2.k[0].normal_()
+            c2.v[0].normal_()
+            if not K.gqa_tc_supported(q, c2.k[0], m2):
+                continue
+            for ns in (1, 2, 4, 8, None):
+                ms = time_op(lambda: K.gqa_decode_tc(q, c2.k[0], c2.v[0], m2, D ** -0.5, win, nsplit=ns))
+                gb = B * span * Hkv * D * 2 * 2 / ms / 1e6
+                print(f"decode attn [tensor-core, page {page}, nsplit {ns}] B={B} L={L} Hq={Hq} Hkv={Hkv} D={D} window={win}: {ms:.4f} ms, "
+                      f"{gb:.0f} GB/s, {gb / hbm:.2f} {tag}")
 
 
 def bench_fa(B: int = 1, L: int = 4096, Hq: int = 16, Hkv: int = 16, DK: int = 192, DV: int = 128, window: int = 0, iters: int = 5):

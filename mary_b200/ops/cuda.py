@@ -397,6 +397,48 @@ def paged_attention_decode_q8(q, kcache, vcache, meta, scale, window=0, softcap=
     return out
 
 
+declare("mary_gqa_decode_tc", "ppppppppp" + "iiiiiiiiiii" + "ffps")
+declare("mary_gqa_tc_supported", "iiii")
+declare("mary_gqa_tc_scratch_floats", "iiii", ret64=True)
+
+
+def gqa_tc_supported(q, kcache, meta) -> bool:
+    """Decode-shaped batch of a grouped-query model that the tensor-core decode kernel takes: bf16, equal K / V widths of 128 or 256,
+    contiguous caches with 16- or 32-token pages, at most 64 (query token, head of the group) rows per kv head."""
+    if kcache.dim() != 4 or q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or not kcache.is_contiguous():
+        return False
+    T, Hq, D = q.shape
+    Hkv = kcache.shape[2]
+    if Hq % Hkv or kcache.shape[3] != D or meta.max_q_len > 8:
+        return False
+    G = Hq // Hkv
+    rq = max(1, min(64 // max(G, 1), meta.max_q_len))
+    return bool(lib().mary_gqa_tc_supported(D, meta.page_size, G, rq)) and kcache.shape[1] == meta.page_size
+
+
+def gqa_decode_tc(q, kcache, vcache, meta, scale, window=0, softcap=0.0, nsplit=None):
+    """Decode attention of a grouped-query model on the tensor cores: the (token, head-of-group) rows of one kv head are one M = 64
+    tile, K and V pages arrive by TMA, split-KV partials are merged by a second kernel."""
+    T, Hq, D = q.shape
+    Hkv = kcache.shape[2]
+    G = Hq // Hkv
+    rq = max(1, min(64 // G, meta.max_q_len))
+    blk_seq, blk_q0, NB = _q_blocks(meta, rq)
+    if nsplit is None:
+        want = max(1, (296 if D == 128 else 148) // max(1, NB * Hkv))
+        span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
+        nsplit = max(1, min(want, 32, span // (4 * meta.page_size)))
+    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    scratch = None
+    if nsplit > 1:
+        scratch = torch.empty(lib().mary_gqa_tc_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
+    assert vcache.is_contiguous() and vcache.shape == kcache.shape
+    check(lib().mary_gqa_decode_tc(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len), _p(meta.q_start),
+                                   _p(blk_seq), _p(blk_q0), NB, T, kcache.shape[0], meta.page_table.shape[1], meta.page_size, Hq, Hkv, D, rq,
+                                   nsplit, window, scale, softcap, _p(scratch), _stream()), "gqa_decode_tc")
+    return out
+
+
 declare("mary_attention_prefill", "ppppppppp" + "iiiiiiii" + "llll" + "ifis")
 declare("mary_attention_prefill_supported", "ii")
 PREFILL_MIN_ROWS = 48     # mean query tokens per sequence from which the 128-row tensor-core tiles pay off
@@ -429,6 +471,9 @@ def attention_prefill(q, kcache, vcache, meta, scale, window=0):
 declare("mary_paged_attention_rel", "ppppppppp" + "iii" + "llll" + "iiiiiii" + "ff" + "ppi" + "s")
 
 
+GQA_TC = False          # route decode-shaped grouped-query batches to the tensor-core kernel (set from MARY_GQA_TC at import)
+
+
 def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: int | None = None, nsplit: int | None = None,
                     kernel: str = "auto", rel_bias=None):
     """``q[T, Hq, DK]``; caches ``[pages, page, Hkv, D]`` (a latent cache is ``Hkv = 1`` with ``dv`` < DK and
@@ -445,6 +490,10 @@ def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: i
             and lib().mary_attention_prefill_supported(DK, DV) and q.dtype == torch.bfloat16 \
             and (kernel == "prefill" or T >= PREFILL_MIN_ROWS * meta.num_seqs):
         return attention_prefill(q, kcache, vcache, meta, scale, window)
+    if kernel in ("auto", "tc") and (kernel == "tc" or GQA_TC) and dv is None and gqa_tc_supported(q, kcache, meta):
+        return gqa_decode_tc(q, kcache, vcache, meta, scale, window, softcap, nsplit)
+    if kernel == "tc":
+        raise ValueError("the tensor-core decode kernel does not take this shape")
     if kernel != "general" and kcache.dim() == 4 and DK == DV and DK in (64, 128, 256) and G <= (4 if DK == 256 else 8) \
             and (meta.max_q_len <= 8 or kernel == "decode"):
         return _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsplit)

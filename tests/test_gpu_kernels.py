@@ -383,3 +383,45 @@ def test_programmatic_dependent_launch_with_early_weight_requests_changes_no_bit
             assert line[3] == pdl
             digests[(M, pdl)] = line[1]
         assert digests[(M, "0")] == digests[(M, "1")]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,Hq,Hkv,page", [(128, 8, 2, 16), (128, 32, 8, 32), (128, 16, 2, 16), (256, 16, 8, 16), (256, 8, 4, 32), (128, 4, 4, 32)])
+def test_tensor_core_gqa_decode_attention_matches_the_f32_reference(K, D, Hq, Hkv, page):
+    """(token, head-of-group) rows of one kv head as an M = 64 tcgen05 tile over K / V pages: ragged lengths, speculative rows,
+    sliding window, soft-cap, forced and automatic kv splits, against the plain f32 operator."""
+    from mary_b200.runtime.batch import BatchMeta
+    from mary_b200.runtime.kv_cache import PagedKVCache
+    g = torch.Generator().manual_seed(D + Hq + page)
+    lens = [1, 37, 700, 129, 2048 + 5]
+    S = len(lens)
+    pages = sum((n + page - 1) // page for n in lens) + 3
+    cache = PagedKVCache(1, pages, page, Hkv, D, dtype=torch.bfloat16, device="cuda")
+    for s, n in enumerate(lens):
+        cache.alloc.extend(s, n)
+    table, kv = cache.alloc.page_table(list(range(S)))
+    fill = BatchMeta.build(list(lens), kv, table, page, "cuda")
+    k = torch.randn(sum(lens), Hkv, D, generator=g).bfloat16()
+    v = torch.randn(sum(lens), Hkv, D, generator=g).bfloat16()
+    cache.k[0].view(-1, Hkv, D)[fill.slot_mapping] = k.cuda()
+    cache.v[0].view(-1, Hkv, D)[fill.slot_mapping] = v.cuda()
+    kc, vc = cache.k[0].float().cpu(), cache.v[0].float().cpu()
+    G = Hq // Hkv
+    for q_lens in ([1] * S, [1, 3, 3, 2, 3]):
+        q_lens = [min(a, b) for a, b in zip(q_lens, lens)]
+        if max(q_lens) * G > 64:
+            continue
+        m = BatchMeta.build(q_lens, kv, table, page, "cuda")
+        mc = BatchMeta.build(q_lens, kv, table, page, "cpu")
+        q = (torch.randn(sum(q_lens), Hq, D, generator=g) * 1.5).bfloat16()
+        assert K.gqa_tc_supported(q.cuda(), cache.k[0], m)
+        for window, softcap, nsplit in ((0, 0.0, 1), (0, 0.0, None), (0, 0.0, 5), (96, 0.0, None), (1024, 0.0, 3), (0, 30.0, None)):
+            before = K.LAUNCHES
+            got = K.paged_attention(q.cuda(), cache.k[0], cache.v[0], m, D ** -0.5, window, softcap, nsplit=nsplit, kernel="tc").float().cpu()
+            assert K.LAUNCHES == before + 1 and K.last_status() == 0
+            want = ref.paged_attention(q.float(), kc, vc, mc, D ** -0.5, window, softcap)
+            assert torch.isfinite(got).all()
+            assert (got - want).abs().max() < 0.03, (q_lens, window, softcap, nsplit, float((got - want).abs().max()))
+    with pytest.raises(ValueError):
+        m8 = BatchMeta.build([9] + [1] * (S - 1), [max(n, 9) for n in kv], table, page, "cuda")
+        K.paged_attention(torch.zeros(9 + S - 1, Hq, D, dtype=torch.bfloat16, device="cuda"), cache.k[0], cache.v[0], m8, 1.0, kernel="tc")
