@@ -7,12 +7,13 @@
 // only moves cache pages and does the softmax.  Reference twins: the split-KV partial / combine kernels of the reference's
 // speech decoder (src/models/personaplex/temporal_metal.rs:133-454) and its banded SIMT kernel (src/models/inkling/banded.rs).
 //
-// One CTA = (block of query tokens of one sequence, kv head, kv split).  PAGE (16 or 32) keys are one pipeline stage:
+// One CTA = (block of query tokens of one sequence, kv head, kv split).  32 keys (one 32-token page or two 16-token pages) are one
+// pipeline stage:
 //   warp 0   TMA: Q once — a 3-D box [64 dims, G heads, RQ tokens] per 64-dim chunk lands as dense rows r = token * G + head in the
 //            128-byte-swizzled K-major layout; per stage ONE 5-D operation for the K page and one for the V page (the tensor map
 //            orders a cache [pages, page, Hkv, D] as dims-in-chunk, tokens, chunks, kv heads, pages, so the box
 //            [64, PAGE, D / 64, 1, 1] lands chunk-major: [chunk][token][64 dims]);
-//   warp 1   MMA (M = 64): S[64 x PAGE] = Q K^T (D / 16 instructions, three S buffers in TMEM, issued two stages ahead), then
+//   warp 1   MMA (M = 64): S[64 x 32] = Q K^T (D / 16 instructions per page, three S buffers in TMEM, issued one stage ahead), then
 //            O[64 x D] += P V with V^T read from the V page as an MN-major operand and P (bf16) from shared memory;
 //   warps 2-5 softmax: row r of an M = 64 accumulator lives in TMEM lane (r % 16) + 32 * (r / 16), so each warp owns 16 rows in
 //            its lanes 0-15: scale, optional soft-cap, causal / sliding-window mask, running max with lazy rescale of O, P to
@@ -30,6 +31,7 @@ constexpr int CHUNK = 64;                     // dims per 128-byte row
 constexpr int NSBUF = 3, NPBUF = 2;
 constexpr int NTHREADS = 192;
 constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr int AHEAD = 1;                          // blocks by which Q K^T leads P V
 constexpr float LOG2E = 1.4426950408889634f;
 
 template <int D, int PAGE>
@@ -39,13 +41,15 @@ struct GCfg {
   static constexpr int Q_BYTES = NCH * Q_CHUNK_BYTES;
   static constexpr int PAGE_CHUNK_BYTES = PAGE * 128;             // one 64-dim chunk of one page
   static constexpr int PAGE_BYTES = NCH * PAGE_CHUNK_BYTES;       // K (or V) page
-  static constexpr int STAGE_BYTES = 2 * PAGE_BYTES;
-  static constexpr int STAGES = D == 256 ? (PAGE == 32 ? 4 : 6) : 8;
-  static constexpr int P_BYTES = TR * PAGE * 2;
+  static constexpr int PPB = 32 / PAGE;                           // pages per pipeline stage: a stage always holds KB = 32 keys
+  static constexpr int KB = PAGE * PPB;
+  static constexpr int STAGE_BYTES = 2 * PAGE_BYTES * PPB;        // [page of the stage][K page | V page]
+  static constexpr int STAGES = D == 256 ? 5 : 5;
+  static constexpr int P_BYTES = TR * KB * 2;
   static constexpr int SMEM = Q_BYTES + STAGES * STAGE_BYTES + NPBUF * P_BYTES + 1024 + 256;
   static constexpr int TMEM_COLS = D <= 128 ? 256 : 512;          // S: 3 x PAGE columns at 0..95, O: D columns at 128..
   static_assert(D % CHUNK == 0 && D <= 256 && (PAGE == 16 || PAGE == 32), "head dim 64..256 in chunks of 64, pages of 16 or 32 tokens");
-  static_assert(NSBUF * PAGE <= 128 && SMEM <= 232448, "budget");
+  static_assert(NSBUF * KB <= 128 && SMEM <= 232448, "budget");
 };
 
 struct GqaParams {
@@ -109,8 +113,10 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int pos0 = kvlen - qlen + (tok0 - p.q_start[seq]);           // position of the block's first query token
   const int k_hi = pos0 + nq;                                         // keys [k_lo, k_hi) are visible to some row
   const int k_lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
-  const int blk_first = k_lo / PAGE;
-  const int nblk_total = (k_hi + PAGE - 1) / PAGE - blk_first;
+  constexpr int KB = GCfg<D, PAGE>::KB, PPB = GCfg<D, PAGE>::PPB;
+  const int blk_first = k_lo / KB;
+  const int nblk_total = (k_hi + KB - 1) / KB - blk_first;
+  const int n_pages = (k_hi + PAGE - 1) / PAGE;                       // pages of this sequence that hold visible keys
   const int per = (nblk_total + p.nsplit - 1) / p.nsplit;
   const int b_lo = blk_first + split * per, b_hi = min(blk_first + nblk_total, b_lo + per);
   const int nblk = max(0, b_hi - b_lo);
@@ -127,6 +133,15 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     tma_prefetch_desc(&tm_v);
   }
   if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  {
+    // rows past the Q box are never written by the copy: give them zeros, so that their (unused) scores stay finite numbers
+    const int box_rows = p.G * p.RQ;
+    for (int i = threadIdx.x; i < C::NCH * (TR - box_rows) * 8; i += NTHREADS) {
+      const int c = i / ((TR - box_rows) * 8), rem = i % ((TR - box_rows) * 8);
+      *(uint4*)(sQ + c * C::Q_CHUNK_BYTES + (box_rows + rem / 8) * 128 + (rem % 8) * 16) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async();
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -144,16 +159,20 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       for (int b = b_lo; b < b_hi; ++b) {
         if (!mbar_wait(&k_empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
         mbar_expect_tx(&k_full[stage], C::STAGE_BYTES);
-        const int page = pt[b];
         uint8_t* st = sKV + stage * C::STAGE_BYTES;
-        tma_load_5d(st, &tm_k, &k_full[stage], 0, 0, 0, kvh, page);
-        tma_load_5d(st + C::PAGE_BYTES, &tm_v, &k_full[stage], 0, 0, 0, kvh, page);
+#pragma unroll
+        for (int pp = 0; pp < PPB; ++pp) {
+          const int pi = b * PPB + pp;
+          const int page = pt[pi < n_pages ? pi : b * PPB];       // a page past the visible keys repeats the block's first page (masked)
+          tma_load_5d(st + pp * 2 * C::PAGE_BYTES, &tm_k, &k_full[stage], 0, 0, 0, kvh, page);
+          tma_load_5d(st + pp * 2 * C::PAGE_BYTES + C::PAGE_BYTES, &tm_v, &k_full[stage], 0, 0, 0, kvh, page);
+        }
         if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else if (warp == 1) {
     if (elect_one() && nblk > 0) {
-      const uint32_t idesc_s = idesc_bf16(TR, PAGE);
+      const uint32_t idesc_s = idesc_bf16(TR, PAGE);            // one page of keys per instruction
       const uint32_t idesc_o = idesc_bf16(TR, D) | (1u << 16);           // B operand MN-major
       if (!mbar_wait(q_full, 0, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
@@ -164,31 +183,40 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_fence_after();
         const uint32_t kb_addr = smem_u32(sKV + stage * C::STAGE_BYTES);
 #pragma unroll
-        for (int c = 0; c < C::NCH; ++c) {
+        for (int pp = 0; pp < PPB; ++pp) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            umma_f16(tmem_S + sb * PAGE, umma_desc_sw128(q_addr + c * C::Q_CHUNK_BYTES + k * 32),
-                     umma_desc_sw128(kb_addr + c * C::PAGE_CHUNK_BYTES + k * 32), idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+          for (int c = 0; c < C::NCH; ++c) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              umma_f16(tmem_S + sb * KB + pp * PAGE, umma_desc_sw128(q_addr + c * C::Q_CHUNK_BYTES + k * 32),
+                       umma_desc_sw128(kb_addr + pp * 2 * C::PAGE_BYTES + c * C::PAGE_CHUNK_BYTES + k * 32), idesc_s, (c > 0 || k > 0) ? 1u : 0u);
+            }
           }
         }
         umma_commit(&s_full[sb]);
         return true;
       };
-      if (!issue_qk(0)) goto done;
-      if (nblk > 1 && !issue_qk(1)) goto done;
+      // Q K^T runs AHEAD blocks in front of P V.  A stage is held from its load until the P V of its block, so every block of
+      // lead takes one stage away from the loads in flight; one block of lead keeps the softmax warps supplied (they need S of
+      // block i + 1 only when they are done with block i) and leaves the rest of the ring to hide the load latency.
+#pragma unroll
+      for (int a = 0; a < AHEAD; ++a)
+        if (a < nblk && !issue_qk(a)) goto done;
       for (int i = 0; i < nblk; ++i) {
-        if (i + 2 < nblk && !issue_qk(i + 2)) goto done;
+        if (i + AHEAD < nblk && !issue_qk(i + AHEAD)) goto done;
         const int pb = i & 1;
         if (!mbar_wait(&p_full[pb], (i >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
         tc_fence_after();
         const int stage = i % C::STAGES;
-        const uint32_t vb_addr = smem_u32(sKV + stage * C::STAGE_BYTES + C::PAGE_BYTES);
+        const uint32_t st_addr = smem_u32(sKV + stage * C::STAGE_BYTES);
 #pragma unroll
-        for (int kk = 0; kk < PAGE / 16; ++kk) {
+        for (int kk = 0; kk < KB / 16; ++kk) {
           // A = P[:, 16 keys] (K-major, no swizzle: 16-byte key chunks TR*16 bytes apart, 8-row groups 128 bytes apart),
-          // B = V^T of those keys from the V page (MN-major, 128B swizzle: 64-dim groups one chunk apart, 8-key groups 1 KB apart)
+          // B = V^T of those keys from their V page (MN-major, 128B swizzle: 64-dim groups one chunk apart, 8-key groups 1 KB apart)
+          const int pp = kk * 16 / PAGE, in_page = kk * 16 % PAGE;
           umma_f16(tmem_O, desc_kmajor_noswz(p_addr + pb * C::P_BYTES + kk * 2 * (TR * 16), TR * 16, 128),
-                   desc_mnmajor_sw128(vb_addr + kk * 16 * 128, C::PAGE_CHUNK_BYTES, 1024), idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                   desc_mnmajor_sw128(st_addr + pp * 2 * C::PAGE_BYTES + C::PAGE_BYTES + in_page * 128, C::PAGE_CHUNK_BYTES, 1024), idesc_o,
+                   (i > 0 || kk > 0) ? 1u : 0u);
         }
         umma_commit(&k_empty[stage]);       // the stage may be overwritten once PV has read it
         umma_commit(&pv_done[pb]);
@@ -207,45 +235,66 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const int sb = i % NSBUF, pb = i & 1;
       if (!mbar_wait(&s_full[sb], (i / NSBUF) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
       tc_fence_after();
-      uint32_t sr[PAGE];
-      if constexpr (PAGE == 32) {
-        tmem_ld_32x32b_x32(tmem_S + lane_off + sb * PAGE, sr);
-      } else {
-        tmem_ld_32x32b_x8(tmem_S + lane_off + sb * PAGE, sr);
-        tmem_ld_32x32b_x8(tmem_S + lane_off + sb * PAGE + 8, sr + 8);
-      }
+      uint32_t sr[KB];
+      tmem_ld_32x32b_x32(tmem_S + lane_off + sb * KB, sr);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
-      const int key0 = (b_lo + i) * PAGE;
-      float sv[PAGE];
-      float mx = -INFINITY;
+      const int key0 = (b_lo + i) * KB;
+      // A block that every row sees entirely (all but the last of a decode step and the window's edge) takes the short path: no
+      // per-element mask, the maximum on the raw scores, one fused multiply-add and one exponential per element.  A row's scores
+      // are processed by ONE lane in sequence, so the instruction count of this loop is the kernel's cycle time.
+      const bool full_blk = p.softcap <= 0.f && key0 + KB - 1 <= pos0 && (p.window <= 0 || pos0 + nq - 1 - key0 < p.window);
+      const float* sf = (const float*)sr;
+      float sv[KB];
+      float mx;
+      if (full_blk) {
+        mx = sf[0];
 #pragma unroll
-      for (int j = 0; j < PAGE; ++j) {
-        const int kp = key0 + j;
-        const bool ok = row_ok && kp <= qpos && (p.window <= 0 || qpos - kp < p.window);
-        float x = __uint_as_float(sr[j]);
-        if (p.softcap > 0.f) x = p.softcap * tanhf(x * p.scale / p.softcap) * LOG2E;
-        else x *= sc2;
-        sv[j] = ok ? x : -INFINITY;
-        mx = fmaxf(mx, sv[j]);
+        for (int j = 1; j < KB; ++j) mx = fmaxf(mx, sf[j]);
+        mx *= sc2;
+      } else {
+        mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+          const int kp = key0 + j;
+          const bool ok = row_ok && kp <= qpos && (p.window <= 0 || qpos - kp < p.window);
+          float x = sf[j];
+          if (p.softcap > 0.f) x = p.softcap * tanhf(x * p.scale / p.softcap) * LOG2E;
+          else x *= sc2;
+          sv[j] = ok ? x : -INFINITY;
+          mx = fmaxf(mx, sv[j]);
+        }
       }
-      // lazy rescale: move the reference only when the new maximum exceeds it by more than the threshold
-      const bool need = mx > m_ref + RESCALE_THRESHOLD;
+      // lazy rescale: move the reference only when the new maximum exceeds it by more than the threshold (lanes 16-31 hold no
+      // score rows and never vote)
+      const bool need = lane < 16 && mx > m_ref + RESCALE_THRESHOLD;
       const bool first = (m_ref == -INFINITY);
       float corr = 1.f;
       if (need) { corr = first ? 0.f : exp2f(m_ref - mx); m_ref = mx; }
-      uint32_t pw[PAGE / 2];
+      uint32_t pw[KB / 2];
       float psum = 0.f;
+      if (full_blk) {
+        const float nm = -m_ref;
 #pragma unroll
-      for (int j = 0; j < PAGE / 2; ++j) {
-        const float a = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j] - m_ref);
-        const float b = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j + 1] - m_ref);
-        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-        pw[j] = *(uint32_t*)&h;
-        float2 back = __bfloat1622float2(h);
-        psum += back.x + back.y;
+        for (int j = 0; j < KB / 2; ++j) {
+          const float a = exp2f(fmaf(sf[2 * j], sc2, nm));
+          const float b = exp2f(fmaf(sf[2 * j + 1], sc2, nm));
+          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          pw[j] = *(uint32_t*)&h;
+          psum += a + b;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < KB / 2; ++j) {
+          const float a = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j] - m_ref);
+          const float b = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j + 1] - m_ref);
+          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          pw[j] = *(uint32_t*)&h;
+          float2 back = __bfloat1622float2(h);
+          psum += back.x + back.y;
+        }
       }
       l = l * corr + psum;
       if (__any_sync(0xffffffffu, need && !first) && i > 0) {
@@ -271,7 +320,7 @@ gqa_decode_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       // P (bf16) -> shared memory: chunk c holds keys 8c..8c+7 of every row, 16 bytes per row
       if (lane < 16) {
 #pragma unroll
-        for (int c = 0; c < PAGE / 8; ++c)
+        for (int c = 0; c < KB / 8; ++c)
           *(uint4*)(sP + pb * C::P_BYTES + c * (TR * 16) + r * 16) = make_uint4(pw[4 * c], pw[4 * c + 1], pw[4 * c + 2], pw[4 * c + 3]);
       }
       fence_proxy_async();       // make the generic-proxy writes of P visible to the tensor core

@@ -48,6 +48,7 @@ constexpr int SMEM = Q_BYTES + STAGES * STAGE_BYTES + NPBUF * P_BYTES + 1024 + 2
 constexpr int TMEM_COLS = 512;                    // S 3 x 32 at columns 0..95, O 256 at columns 128..383
 constexpr int NTHREADS = 192;
 constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr int AHEAD = 1;                          // blocks by which Q K^T leads P V
 
 struct MlaParams {
   const int* page_table; const int* kv_len; const int* q_start; const int* blk_seq; const int* blk_row0;
@@ -181,10 +182,14 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(&s_full[sb]);
         return true;
       };
-      if (!issue_qk(0)) goto done;
-      if (nblk > 1 && !issue_qk(1)) goto done;
+      // Q K^T runs AHEAD blocks in front of P V.  A stage is held from its load until the P V of its block, so every block of
+      // lead takes one stage away from the loads in flight; one block of lead keeps the softmax warps supplied (they need S of
+      // block i + 1 only when they are done with block i) and leaves the rest of the ring to hide the load latency.
+#pragma unroll
+      for (int a = 0; a < AHEAD; ++a)
+        if (a < nblk && !issue_qk(a)) goto done;
       for (int i = 0; i < nblk; ++i) {
-        if (i + 2 < nblk && !issue_qk(i + 2)) goto done;
+        if (i + AHEAD < nblk && !issue_qk(i + AHEAD)) goto done;
         const int pb = i & 1;
         if (!mbar_wait(&p_full[pb], (i >> 1) & 1, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;
         tc_fence_after();
@@ -212,6 +217,7 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int r = q4 * 16 + (lane & 15);            // accumulator row held by this lane (lanes 16-31 hold nothing)
     const bool row_ok = lane < 16 && r < nrows;
     const int qpos = pos_first + (row0 - seq_row0 + r) / p.Hq;
+    const int qpos_min = pos_first + (row0 - seq_row0) / p.Hq;      // the tile's first row sees the fewest keys
     const uint32_t lane_off = (uint32_t)(q4 * 32) << 16;
     float m_ref = -INFINITY, l = 0.f;
     for (int i = 0; i < nblk; ++i) {
@@ -225,30 +231,56 @@ mla_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
       const int key0 = (b_lo + i) * KB;
+      // A block that every row of the tile sees entirely (all but the last one or two of a decode step) takes the short path:
+      // no per-element mask, the maximum on the raw scores, one fused multiply-add and one exponential per element.  A row's
+      // 32 scores are processed by ONE lane in sequence, so the instruction count of this loop is the kernel's cycle time.
+      const bool full_blk = key0 + KB - 1 <= qpos_min;
+      const float* sf = (const float*)sr;
       float sv[KB];
-      float mx = -INFINITY;
+      float mx;
+      if (full_blk) {
+        mx = sf[0];
 #pragma unroll
-      for (int j = 0; j < KB; ++j) {
-        const bool ok = row_ok && (key0 + j) <= qpos;
-        sv[j] = ok ? __uint_as_float(sr[j]) * p.scale_log2 : -INFINITY;
-        mx = fmaxf(mx, sv[j]);
+        for (int j = 1; j < KB; ++j) mx = fmaxf(mx, sf[j]);
+        mx *= p.scale_log2;
+      } else {
+        mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+          const bool ok = row_ok && (key0 + j) <= qpos;
+          sv[j] = ok ? sf[j] * p.scale_log2 : -INFINITY;
+          mx = fmaxf(mx, sv[j]);
+        }
       }
-      // lazy rescale: move the reference only when the new maximum exceeds it by more than the threshold
-      const bool need = mx > m_ref + RESCALE_THRESHOLD;
+      // lazy rescale: move the reference only when the new maximum exceeds it by more than the threshold (lanes 16-31 hold no
+      // score rows and never vote)
+      const bool need = lane < 16 && mx > m_ref + RESCALE_THRESHOLD;
       const bool first = (m_ref == -INFINITY);
       float corr = 1.f;
       if (need) { corr = first ? 0.f : exp2f(m_ref - mx); m_ref = mx; }
       // probabilities in registers first: the waits below then overlap this arithmetic of the other warps
       uint32_t pw[KB / 2];
       float psum = 0.f;
+      if (full_blk) {
+        const float nm = -m_ref;
 #pragma unroll
-      for (int j = 0; j < KB / 2; ++j) {
-        const float a = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j] - m_ref);
-        const float b = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j + 1] - m_ref);
-        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-        pw[j] = *(uint32_t*)&h;
-        float2 back = __bfloat1622float2(h);
-        psum += back.x + back.y;
+        for (int j = 0; j < KB / 2; ++j) {
+          const float a = exp2f(fmaf(sf[2 * j], p.scale_log2, nm));
+          const float b = exp2f(fmaf(sf[2 * j + 1], p.scale_log2, nm));
+          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          pw[j] = *(uint32_t*)&h;
+          psum += a + b;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < KB / 2; ++j) {
+          const float a = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j] - m_ref);
+          const float b = (m_ref == -INFINITY) ? 0.f : exp2f(sv[2 * j + 1] - m_ref);
+          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          pw[j] = *(uint32_t*)&h;
+          float2 back = __bfloat1622float2(h);
+          psum += back.x + back.y;
+        }
       }
       l = l * corr + psum;
       // lanes 16-31 hold the upper value half of row (lane - 16): they rescale with that row's factor

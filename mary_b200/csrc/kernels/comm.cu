@@ -54,13 +54,17 @@ __device__ bool rank_barrier(const CommCtx& c, int which, uint32_t epoch, int bl
     __threadfence_system();
     st_release_sys(c.sigs[peer] + slot + c.rank, epoch);
     const uint32_t* mine = c.sigs[c.rank] + slot + peer;
-    const uint64_t t0 = globaltimer_ns();
+    uint64_t t0 = 0;                        // the timer is read only after a run of failed polls, never on the fast path
     uint32_t spins = 0;
     while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > c.wait_ns) {
-        atomicCAS(c.status, 0, MARY_ERR_TIMEOUT_PEER);
-        ok_s = 0;
-        break;
+      if ((++spins & 255u) == 0) {
+        const uint64_t now = globaltimer_ns();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > c.wait_ns) {
+          atomicCAS(c.status, 0, MARY_ERR_TIMEOUT_PEER);
+          ok_s = 0;
+          break;
+        }
       }
     }
   }

@@ -77,12 +77,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // already raised *abort); the caller must then leave its loop and go to the kernel's teardown.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = globaltimer_ns();
+  // The global timer is read only after a long run of failed polls: a wait that blocks for a pipeline stage (the common case in
+  // the issuing threads of every kernel) must not pay for a timer read each time.
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 255u) == 0) {
+    if ((++spins & 2047u) == 0) {
       if (*abort) return false;
-      if (globaltimer_ns() - t0 > MARY_WAIT_NS) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > MARY_WAIT_NS) {
         *abort = 1;
         atomicCAS(status, 0, code);
         return false;

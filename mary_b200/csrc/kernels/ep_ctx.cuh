@@ -65,12 +65,16 @@ __device__ __forceinline__ uint32_t ep_ld_acquire_sys(const uint32_t* p) {
 // Bounded wait until flag word `p` reaches `target`.  Returns false (and records MARY_ERR_TIMEOUT_PEER) when it does not.
 __device__ __forceinline__ bool ep_wait_flag(const uint32_t* p, uint32_t target, unsigned long long wait_ns, int* status) {
   if ((int32_t)(ep_ld_acquire_sys(p) - target) >= 0) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;                          // the timer is read only after a run of failed polls, never on the fast path
   uint32_t spins = 0;
   while ((int32_t)(ep_ld_acquire_sys(p) - target) < 0) {
-    if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > wait_ns) {
-      atomicCAS(status, 0, MARY_ERR_TIMEOUT_PEER);
-      return false;
+    if ((++spins & 255u) == 0) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > wait_ns) {
+        atomicCAS(status, 0, MARY_ERR_TIMEOUT_PEER);
+        return false;
+      }
     }
   }
   return true;

@@ -471,7 +471,12 @@ def attention_prefill(q, kcache, vcache, meta, scale, window=0):
 declare("mary_paged_attention_rel", "ppppppppp" + "iii" + "llll" + "iiiiiii" + "ff" + "ppi" + "s")
 
 
-GQA_TC = False          # route decode-shaped grouped-query batches to the tensor-core kernel (set from MARY_GQA_TC at import)
+def _gqa_tc_default() -> bool:
+    from ..utils import flags
+    return bool(flags.get("MARY_GQA_TC"))
+
+
+GQA_TC = _gqa_tc_default()          # route decode-shaped grouped-query batches to the tensor-core kernel (MARY_GQA_TC)
 
 
 def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: int | None = None, nsplit: int | None = None,
