@@ -38,3 +38,44 @@ def linear_frozen(x, w, wt=None):
     if wt is None:
         wt = w.t().contiguous()
     return _LinearFrozen.apply(x, w, wt)
+
+
+def _own(t):
+    """A group reduction may answer with a view of its communication buffer that the next reduction overwrites; autograd keeps
+    results for the backward pass, so they get storage of their own."""
+    return t.clone() if t._base is not None else t
+
+
+class _CopyToTP(torch.autograd.Function):
+    """Entry of a tensor-parallel region: the activation is the same on every rank and feeds every rank's weight shard, so its
+    gradient is the SUM of the ranks' partial gradients (forward identity, backward all-reduce)."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        ctx.tp = tp
+        return x
+
+    @staticmethod
+    def backward(ctx, dy):
+        return _own(ctx.tp.all_reduce(dy.contiguous().clone())), None     # never reduce in place into autograd's buffer
+
+
+class _ReduceFromTP(torch.autograd.Function):
+    """Exit of a tensor-parallel region: the ranks' partial sums are reduced (forward all-reduce); the gradient of the reduced
+    activation is the gradient of every partial sum (backward identity)."""
+
+    @staticmethod
+    def forward(ctx, x, tp):
+        return _own(tp.all_reduce(x.contiguous().clone()))
+
+    @staticmethod
+    def backward(ctx, dy):
+        return dy, None
+
+
+def copy_to_tp(x, tp):
+    return _CopyToTP.apply(x, tp) if tp is not None and tp.size > 1 else x
+
+
+def reduce_from_tp(x, tp):
+    return _ReduceFromTP.apply(x, tp) if tp is not None and tp.size > 1 else x

@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--checkpoint", action="store_true", help="recompute each layer in the backward pass (activation checkpointing)")
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size; the world is (world / tp) data-parallel replicas of tp ranks each")
     a = ap.parse_args()
     from ..models.gemma4 import Gemma4Model, gemma_12b_config
     from ..models.gemma4.weights import init_random_
@@ -34,19 +35,42 @@ def main():
     cfg = gemma_12b_config()
     cfg.num_hidden_layers = a.layers
     cfg.layer_types = cfg.layer_types[:a.layers]
-    model = Gemma4Model(cfg, dtype=torch.bfloat16, device=dev)
-    init_random_(model, 0)
-    reduce_fn = None
+    tp = a.tp
+    assert world % tp == 0, "--tp must divide the number of ranks"
+    dp = world // tp
+    tp_rank, dp_rank = rank % tp, rank // tp
+    reduce_fn = tp_reduce_fn = par = None
     if world > 1:
         import torch.distributed as dist
-        if a.comm == "fused":
+        from ..parallel.group import ParallelGroup
+        tp_groups = [dist.new_group(list(range(d * tp, (d + 1) * tp))) for d in range(dp)] if 1 < tp < world else None
+        dp_groups = [dist.new_group(list(range(t, world, tp))) for t in range(tp)] if 1 < tp < world else None
+        heap = None
+        if a.comm == "fused" and (tp == 1 or tp == world):
+            # one group spans the world: this package's all-reduce kernels over peer memory carry the activations of the
+            # tensor-parallel regions (bf16, one sequence batch) and the adapter gradients (f32)
             from ..parallel.symm import SymmetricHeap
-            heap = SymmetricHeap(rank, world, dev, max_bytes=8 << 20)
-            reduce_fn = heap.all_reduce_f32_
-        else:
-            reduce_fn = lambda g: dist.all_reduce(g)  # noqa: E731
-    tr = LoraTrainer(model, rank=16, alpha=32.0, lr=1e-4, dp_size=world, reduce_fn=reduce_fn, overlap=not a.no_overlap, checkpoint=a.checkpoint)
-    g = torch.Generator(device=dev).manual_seed(rank)
+            heap = SymmetricHeap(rank, world, dev, max_bytes=max(8 << 20, a.batch * a.seq * cfg.hidden_size * 4 if tp > 1 else 0))
+        if tp > 1:
+            if heap is not None:
+                par = ParallelGroup(tp_rank, tp, "fused", symm=heap)
+                # the gradient buckets are reduced on a side stream while the backward pass reduces activations: a heap of their own
+                tp_reduce_fn = SymmetricHeap(rank, world, dev, max_bytes=8 << 20).all_reduce_f32_
+            else:
+                grp = tp_groups[dp_rank] if tp_groups else None
+                par = ParallelGroup(tp_rank, tp, "nccl", group=grp)
+                tp_reduce_fn = lambda g_, grp=grp: dist.all_reduce(g_, group=grp)  # noqa: E731
+        if dp > 1:
+            if heap is not None and tp == 1:
+                reduce_fn = heap.all_reduce_f32_
+            else:
+                grp = dp_groups[tp_rank] if dp_groups else None
+                reduce_fn = lambda g_, grp=grp: dist.all_reduce(g_, group=grp)  # noqa: E731
+    model = Gemma4Model(cfg, tp=par, dtype=torch.bfloat16, device=dev)
+    init_random_(model, 0)
+    tr = LoraTrainer(model, rank=16, alpha=32.0, lr=1e-4, dp_size=dp, reduce_fn=reduce_fn, tp_reduce_fn=tp_reduce_fn, overlap=not a.no_overlap,
+                     checkpoint=a.checkpoint)
+    g = torch.Generator(device=dev).manual_seed(dp_rank)                    # the ranks of one tensor-parallel group see the same sequences
     ids = torch.randint(0, cfg.vocab_size, (a.batch, a.seq), device=dev, generator=g)
     for _ in range(a.warmup):
         loss = tr.step(ids)
@@ -66,7 +90,7 @@ def main():
     ms = float(ms) / a.steps
     if rank == 0:
         print(json.dumps({"metric": "LoRA finetune tokens/s (Gemma-4-12B-style, rank 16, seq %d)" % a.seq,
-                          "value": round(world * a.batch * a.seq / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world,
+                          "value": round(dp * a.batch * a.seq / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "parallelism": f"dp{dp} x tp{tp}",
                           "ms_per_step": round(ms, 2), "loss": round(loss, 4), "layers": a.layers, "comm": a.comm if world > 1 else "none",
                           "overlap": not a.no_overlap, "checkpointing": a.checkpoint, "gpu_launches_per_step": K.LAUNCHES // a.steps,
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1), "kernel_status": K.last_status()}))

@@ -19,7 +19,7 @@ from torch import nn
 from ..format import schema as S
 from ..format.leaf import put_array, resolve
 from ..ops import reference as ref
-from ..ops.autograd import linear_frozen
+from ..ops.autograd import copy_to_tp, linear_frozen, reduce_from_tp
 from ..pile.trible import TribleBuilder, r_f64, r_genid, r_shortstring, r_u256, v_f64, v_genid, v_shortstring, v_u256
 
 PROJECTIONS = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
@@ -65,6 +65,46 @@ class LoraWeights(nn.Module):
     def get(self, layer: int, proj: str):
         k = f"{layer}_{proj}"
         return self.adapters[k] if k in self.adapters else None
+
+    @staticmethod
+    def tp_replicated(proj: str, which: str, kv_replicated: bool = False) -> bool:
+        """Whether factor ``which`` ("A" / "B") of a ``proj`` adapter is held identically by every tensor-parallel rank (its
+        gradient is then a partial sum over the group) or is a shard (its gradient is complete on its rank).  ``kv_replicated``:
+        the model has fewer kv heads than ranks, so the k / v projections themselves are replicated."""
+        if proj in ("o_proj", "down_proj"):
+            return which == "B"
+        if proj in ("k_proj", "v_proj") and kv_replicated:
+            return True
+        return which == "A"
+
+    @staticmethod
+    def shard_from_full(full: "LoraWeights", model, full_model) -> "LoraWeights":
+        """The adapters of tensor-parallel rank ``model.tp.rank`` cut out of unsharded ones, by the rule that cuts the base weights
+        (``models.gemma4.weights.shard_from_full``): column-parallel ``B`` by output rows (whole heads), row-parallel ``A`` by
+        input columns, the other factor copied."""
+        have = {k.split("_", 1)[1] for k in full.adapters}
+        lw = LoraWeights.init_gemma4(model, full.rank, full.alpha, targets=tuple(p for p in PROJECTIONS if p in have))   # one order on every rank
+        r, n = model.tp.rank, model.tp.size
+        with torch.no_grad():
+            for i, (L, Fl) in enumerate(zip(model.layers, full_model.layers)):
+                D = L.D
+                kv0 = (r * Fl.n_kv) // n if Fl.n_kv >= n else 0
+                rows = {"q_proj": (r * L.n_q * D, L.n_q * D), "k_proj": (kv0 * D, L.n_kv * D), "v_proj": (kv0 * D, L.n_kv * D),
+                        "gate_proj": (r * L.F, L.F), "up_proj": (r * L.F, L.F)}
+                cols = {"o_proj": (r * L.n_q * D, L.n_q * D), "down_proj": (r * L.F, L.F)}
+                for p in PROJECTIONS:
+                    src, dst = full.get(i, p), lw.get(i, p)
+                    if src is None:
+                        continue
+                    if p in rows:
+                        o, k = rows[p]
+                        dst.A.copy_(src.A)
+                        dst.B.copy_(src.B[o:o + k])
+                    else:
+                        o, k = cols[p]
+                        dst.A.copy_(src.A[:, o:o + k])
+                        dst.B.copy_(src.B)
+        return lw
 
     # ------------------------------------------------------------------ persistence
     def peft_state_dict(self) -> dict:
@@ -156,7 +196,9 @@ class Gemma4LoraForward(nn.Module):
         if L.kv_source is not None or L.moe or L.ple:
             raise NotImplementedError("LoRA training of decoders with KV-shared layers, a routed-expert block or per-layer embeddings is not built")
         ad = lambda p: self.lora.get(i, p)  # noqa: E731
-        x = ref.rmsnorm(h, L.ln_in.detach(), c.rms_norm_eps)
+        # tensor parallel: the normed activation enters the sharded region (its gradient is summed over the group), the partial
+        # sums of the row-parallel projections leave it through the group reduction
+        x = copy_to_tp(ref.rmsnorm(h, L.ln_in.detach(), c.rms_norm_eps), m.tp)
         qkv = self._lin(x, L.w_qkv)
         nq, nkv, D = L.n_q * L.D, L.n_kv * L.D, L.D
         deltas = [ad(p)(x) if ad(p) is not None else None for p in ("q_proj", "k_proj", "v_proj")]
@@ -173,9 +215,9 @@ class Gemma4LoraForward(nn.Module):
         a = self._lin(o, L.w_o)
         if ad("o_proj") is not None:
             a = a + ad("o_proj")(o)
-        a = m.tp.all_reduce(a) if m.tp.size > 1 else a
+        a = reduce_from_tp(a, m.tp)
         h = h + ref.rmsnorm(a, L.ln_post_attn.detach(), c.rms_norm_eps)
-        x = ref.rmsnorm(h, L.ln_pre_ffn.detach(), c.rms_norm_eps)
+        x = copy_to_tp(ref.rmsnorm(h, L.ln_pre_ffn.detach(), c.rms_norm_eps), m.tp)
         gu = self._lin(x, L.w_gu)
         g_, u_ = gu[..., :L.F], gu[..., L.F:]
         if ad("gate_proj") is not None:
@@ -186,7 +228,7 @@ class Gemma4LoraForward(nn.Module):
         d = self._lin(mm, L.w_down)
         if ad("down_proj") is not None:
             d = d + ad("down_proj")(mm)
-        d = m.tp.all_reduce(d) if m.tp.size > 1 else d
+        d = reduce_from_tp(d, m.tp)
         return (h + ref.rmsnorm(d, L.ln_post_ffn.detach(), c.rms_norm_eps)) * L.layer_scalar
 
     def forward(self, ids):

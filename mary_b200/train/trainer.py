@@ -75,16 +75,31 @@ class FlatAdamW:
 
 class LoraTrainer:
     def __init__(self, model, rank: int = 16, alpha: float = 32.0, lr: float = 1e-4, seed: int = 0, dp_group=None, dp_size: int = 1,
-                 reduce_fn=None, overlap: bool = True, checkpoint: bool = False):
+                 reduce_fn=None, overlap: bool = True, checkpoint: bool = False, tp_reduce_fn=None, lora=None):
+        """``reduce_fn(g)``: in-place sum of a gradient slice over the DATA-parallel group (all replicas of this rank's shard).
+        ``tp_reduce_fn(g)``: in-place sum over the TENSOR-parallel group, applied to the factors every rank of the group holds
+        identically (their gradients are partial sums, see ``LoraWeights.tp_replicated``).  ``lora``: adapters to train instead of
+        freshly initialised ones (already cut for this rank)."""
         self.model = model
-        self.lora = LoraWeights.init_gemma4(model, rank, alpha, seed)
+        self.lora = lora if lora is not None else LoraWeights.init_gemma4(model, rank, alpha, seed)
         self.fwd = Gemma4LoraForward(model, self.lora)
         self.fwd.checkpoint = checkpoint          # recompute every layer in the backward pass instead of keeping its activations
-        # parameters ordered by layer so that a layer's gradients are one contiguous bucket
-        self.layer_params = []
-        for i in range(len(model.layers)):
-            ps = [p for k, ad in self.lora.adapters.items() if k.split("_", 1)[0] == str(i) for p in (ad.A, ad.B)]
-            self.layer_params.append(ps)
+        # parameters ordered by layer so that a layer's gradients are one contiguous bucket; inside a layer the factors that are
+        # replicated over the tensor-parallel group come first, so that their partial gradients are one contiguous slice too
+        tp = getattr(model, "tp", None)
+        tp_size = tp.size if tp is not None else 1
+        self.layer_params, self.rep_counts = [], []
+        for i, L in enumerate(model.layers):
+            kv_rep = tp_size > 1 and model.cfg.layer_kv_heads(i) < tp_size
+            rep, shard = [], []
+            for k, ad in self.lora.adapters.items():
+                li, proj = k.split("_", 1)
+                if li != str(i):
+                    continue
+                for which, p in (("A", ad.A), ("B", ad.B)):
+                    (rep if LoraWeights.tp_replicated(proj, which, kv_rep) else shard).append(p)
+            self.layer_params.append(rep + shard)
+            self.rep_counts.append(sum(p.numel() for p in rep))
         self.opt = FlatAdamW([p for ps in self.layer_params for p in ps], lr=lr)
         self.buckets = []
         o = 0
@@ -93,12 +108,16 @@ class LoraTrainer:
             self.buckets.append((o, k))
             o += k
         self.dp_group, self.dp_size = dp_group, dp_size
-        self.reduce_fn = reduce_fn               # callable(tensor) -> in-place sum over the data/tensor-parallel group
-        self.overlap = overlap and reduce_fn is not None
+        self.reduce_fn = reduce_fn               # callable(tensor) -> in-place sum over the data-parallel group
+        self.tp_reduce_fn = tp_reduce_fn if tp_size > 1 else None
+        if tp_size > 1 and tp_reduce_fn is None:
+            raise ValueError("a tensor-parallel model needs tp_reduce_fn: the replicated adapter factors hold partial gradients")
+        any_reduce = self.reduce_fn is not None or self.tp_reduce_fn is not None
+        self.overlap = overlap and any_reduce
         self.side = torch.cuda.Stream() if (self.overlap and model.embed.is_cuda) else None
         self._pending = [0] * len(self.layer_params)
         self.reduced_bytes = 0
-        if self.reduce_fn is not None:
+        if any_reduce:
             for li, ps in enumerate(self.layer_params):
                 for p in ps:
                     p.register_post_accumulate_grad_hook(self._make_hook(li))
@@ -114,13 +133,21 @@ class LoraTrainer:
     def _reduce_bucket(self, li):
         o, k = self.buckets[li]
         g = self.opt.grad[o:o + k]
-        self.reduced_bytes += k * 4
+        g_rep = self.opt.grad[o:o + self.rep_counts[li]]
+
+        def run():
+            if self.tp_reduce_fn is not None and g_rep.numel():
+                self.tp_reduce_fn(g_rep)             # partial gradients of the replicated factors: sum over the tensor-parallel group
+                self.reduced_bytes += g_rep.numel() * 4
+            if self.reduce_fn is not None:
+                self.reduce_fn(g)                    # every factor: sum over the replicas of this shard
+                self.reduced_bytes += k * 4
         if self.side is not None:
             self.side.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.side):
-                self.reduce_fn(g)
+                run()
         else:
-            self.reduce_fn(g)
+            run()
 
     def step(self, ids) -> float:
         self.opt.zero_grad()

@@ -358,3 +358,95 @@ def test_context_parallel_prefill_of_the_latent_attention_decoder(zigzag):
     [p.join(60) for p in ps]
     for rank, rows_ok, toks_ok in res:
         assert rows_ok >= 0.95 and toks_ok >= 0.95, res
+
+
+def _lora_tp_worker(rank, world, port, tp_size, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mary_b200.models.gemma4 import Gemma4Model, tiny_config
+    from mary_b200.models.gemma4.weights import init_random_, shard_from_full
+    from mary_b200.parallel.group import ParallelGroup
+    from mary_b200.train.lora import LoraWeights
+    from mary_b200.train.trainer import LoraTrainer
+    torch.manual_seed(0)
+    cfg = tiny_config()
+    full = Gemma4Model(cfg, dtype=torch.float32)
+    init_random_(full, 0)
+    full_lora = LoraWeights.init_gemma4(full, rank=4, alpha=8.0, seed=1)
+    g = torch.Generator().manual_seed(2)
+    for ad in full_lora.adapters.values():
+        ad.B.data.normal_(0.0, 0.05, generator=g)                         # non-zero B: every factor gets a gradient
+    dp_size = world // tp_size
+    tp_rank, dp_rank = rank % tp_size, rank // tp_size
+    tp_groups = [dist.new_group(list(range(d * tp_size, (d + 1) * tp_size))) for d in range(dp_size)]
+    dp_groups = [dist.new_group(list(range(t, world, tp_size))) for t in range(tp_size)]
+    par = ParallelGroup(tp_rank, tp_size, "nccl", group=tp_groups[dp_rank])
+    model = shard_from_full(full, par)
+    lora = LoraWeights.shard_from_full(full_lora, model, full)
+    tr = LoraTrainer(model, rank=4, alpha=8.0, lr=1e-2, dp_size=dp_size, lora=lora, overlap=False,
+                     reduce_fn=(lambda t: dist.all_reduce(t, group=dp_groups[tp_rank])) if dp_size > 1 else None,
+                     tp_reduce_fn=(lambda t: dist.all_reduce(t, group=tp_groups[dp_rank])) if tp_size > 1 else None)
+    ids_all = torch.randint(0, cfg.vocab_size, (dp_size, 2, 24), generator=torch.Generator().manual_seed(3))
+    # the same computation on ONE rank: the full model over all replicas' sequences, plain autograd
+    ref_tr = LoraTrainer(full, rank=4, alpha=8.0, lr=1e-2, lora=full_lora, overlap=False)
+    ref_tr.opt.zero_grad()
+    ref_loss = sum(ref_tr.fwd.loss(ids_all[d]) for d in range(dp_size)) / dp_size
+    ref_loss.backward()
+    ref_grads = {k: (ad.A.grad.clone(), ad.B.grad.clone()) for k, ad in full_lora.adapters.items()}
+    tr.opt.zero_grad()
+    loss = tr.fwd.loss(ids_all[dp_rank])
+    loss.backward()
+    worst = 0.0
+    for i, (L, Fl) in enumerate(zip(model.layers, full.layers)):
+        D = L.D
+        kv0 = (tp_rank * Fl.n_kv) // tp_size if Fl.n_kv >= tp_size else 0
+        rows = {"q_proj": (tp_rank * L.n_q * D, L.n_q * D), "k_proj": (kv0 * D, L.n_kv * D), "v_proj": (kv0 * D, L.n_kv * D),
+                "gate_proj": (tp_rank * L.F, L.F), "up_proj": (tp_rank * L.F, L.F)}
+        cols = {"o_proj": (tp_rank * L.n_q * D, L.n_q * D), "down_proj": (tp_rank * L.F, L.F)}
+        for p in ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"):
+            ad = lora.get(i, p)
+            ga, gb = ref_grads[f"{i}_{p}"]
+            if p in rows:
+                o, k = rows[p]
+                want_a, want_b = ga, gb[o:o + k]
+            else:
+                o, k = cols[p]
+                want_a, want_b = ga[:, o:o + k], gb
+            # after the hooks: gradients are summed over the data-parallel replicas (the step divides by dp_size)
+            for got, want in ((ad.A.grad / dp_size, want_a), (ad.B.grad / dp_size, want_b)):
+                worst = max(worst, float((got - want).abs().max() / want.abs().max().clamp_min(1e-9)))
+    losses = [torch.zeros(()) for _ in range(world)]
+    dist.all_gather(losses, loss.detach())
+    mean_loss = float(sum(losses[d * tp_size] for d in range(dp_size)) / dp_size)
+    # two optimiser steps keep the replicas in lockstep: replicated factors stay identical over the tensor-parallel group
+    tr.step(ids_all[dp_rank])
+    tr.step(ids_all[dp_rank])
+    a0 = lora.get(0, "q_proj").A.detach().clone()
+    gathered = [torch.zeros_like(a0) for _ in range(world)]
+    dist.all_gather(gathered, a0)
+    drift = max(float((t - gathered[0]).abs().max()) for t in gathered)
+    if rank == 0:
+        out.put((worst, mean_loss, float(ref_loss.detach()), drift, tr.reduced_bytes))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,tp_size", [(2, 2), (4, 2)])
+@_once_more
+def test_lora_training_under_tensor_and_data_parallelism_has_the_single_rank_gradients(world, tp_size):
+    """LoRA training with the base model cut over a tensor-parallel group (and replicated over a data-parallel one): loss and EVERY
+    adapter gradient equal plain autograd on the unsharded model — shards compare with their slice, replicated factors after the
+    group sum; the replicas stay in lockstep over optimiser steps."""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_lora_tp_worker, args=(r, world, port, tp_size, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    worst, loss, ref_loss, drift, reduced = out.get(timeout=240)
+    for p in procs:
+        p.join(60)
+    assert abs(loss - ref_loss) < 1e-4 * max(1.0, abs(ref_loss)), (loss, ref_loss)
+    assert worst < 2e-3, worst
+    assert drift == 0.0 and reduced > 0
