@@ -225,14 +225,27 @@ fa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[sb]);
       const int key0 = (b_lo + i) * KB;
-      float mx = -INFINITY;
+      // A block that every row of the tile sees entirely (all blocks left of the diagonal band and inside the window) takes the
+      // short path: no per-element mask, the maximum on the raw scores, one fused multiply-add and one exponential per element.
+      // A thread owns one query row and walks its 64 scores in sequence, so this loop's instruction count bounds the block rate.
+      const bool full_blk = key0 + KB - 1 <= pos_first && (p.window <= 0 || key0 >= pos_first + TR - p.window);
+      const float* sf = (const float*)sr;
+      float mx;
+      if (full_blk) {
+        mx = sf[0];
 #pragma unroll
-      for (int j = 0; j < KB; ++j) {
-        const int kj = key0 + j;
-        const bool ok = row_ok && kj <= qpos && kj >= lo_key;
-        const float v = ok ? __uint_as_float(sr[j]) * p.scale_log2 : -INFINITY;
-        sr[j] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+        for (int j = 1; j < KB; ++j) mx = fmaxf(mx, sf[j]);
+        mx *= p.scale_log2;
+      } else {
+        mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < KB; ++j) {
+          const int kj = key0 + j;
+          const bool ok = row_ok && kj <= qpos && kj >= lo_key;
+          const float v = ok ? __uint_as_float(sr[j]) * p.scale_log2 : -INFINITY;
+          sr[j] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
       }
       const bool need = mx > m_ref + RESCALE_THRESHOLD;
       const bool first = (m_ref == -INFINITY);
@@ -240,14 +253,26 @@ fa_prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (need) { corr = first ? 0.f : exp2f(m_ref - mx); m_ref = mx; }
       uint32_t pw[KB / 2];
       float psum = 0.f;
+      if (full_blk) {
+        const float nm = -m_ref;
 #pragma unroll
-      for (int j = 0; j < KB / 2; ++j) {
-        const float a = (m_ref == -INFINITY) ? 0.f : exp2f(__uint_as_float(sr[2 * j]) - m_ref);
-        const float b = (m_ref == -INFINITY) ? 0.f : exp2f(__uint_as_float(sr[2 * j + 1]) - m_ref);
-        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-        pw[j] = *(uint32_t*)&h;
-        float2 back = __bfloat1622float2(h);
-        psum += back.x + back.y;
+        for (int j = 0; j < KB / 2; ++j) {
+          const float a = exp2f(fmaf(sf[2 * j], p.scale_log2, nm));
+          const float b = exp2f(fmaf(sf[2 * j + 1], p.scale_log2, nm));
+          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          pw[j] = *(uint32_t*)&h;
+          psum += a + b;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < KB / 2; ++j) {
+          const float a = (m_ref == -INFINITY) ? 0.f : exp2f(__uint_as_float(sr[2 * j]) - m_ref);
+          const float b = (m_ref == -INFINITY) ? 0.f : exp2f(__uint_as_float(sr[2 * j + 1]) - m_ref);
+          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          pw[j] = *(uint32_t*)&h;
+          float2 back = __bfloat1622float2(h);
+          psum += back.x + back.y;
+        }
       }
       l = l * corr + psum;
       if (__any_sync(0xffffffffu, need && !first) && i > 0) {
