@@ -67,6 +67,10 @@ struct GemmParams {
   // 1: the weight operand is constant (model weights) and the launch allows programmatic dependent launch, so the producer may
   // fetch the first weight tiles while the previous kernel of the stream is still draining; activations wait for it as always
   int w_static;
+  // > 0: tiles are walked in bands of `raster` column tiles, row tiles fastest inside a band, so the CTAs that run together cover a
+  // compact block of the output: the band's weight tiles stay in L2 while the row operand streams past them once per band.  With
+  // column tiles fastest (raster 0) a wide output re-reads every weight tile once per row tile.
+  int raster;
 };
 
 // One unit of work of a CTA: K-blocks [kb0, kb1) of output tile (tr, tc) of problem bz; `seg` of `nseg` partial results of that
@@ -107,9 +111,18 @@ struct WorkIter {
     if (tt >= per_batch * p.batch) return false;
     const int t = tt % per_batch;
     w.bz = tt / per_batch;
-    w.tc = t % p.tiles_c;
-    const int ks = (t / p.tiles_c) % p.split_k;
-    w.tr = t / (p.tiles_c * p.split_k);
+    int ks;
+    if (p.raster > 0) {                       // split_k == 1 here
+      const int band = t / (p.raster * p.tiles_r), base = band * p.raster;
+      const int gw = min(p.raster, p.tiles_c - base), in = t - band * p.raster * p.tiles_r;
+      w.tr = in / gw;
+      w.tc = base + in % gw;
+      ks = 0;
+    } else {
+      w.tc = t % p.tiles_c;
+      ks = (t / p.tiles_c) % p.split_k;
+      w.tr = t / (p.tiles_c * p.split_k);
+    }
     w.kb0 = ks * p.k_blocks_per_split;
     w.kb1 = min(w.kb0 + p.k_blocks_per_split, p.k_blocks);
     w.tile = (w.bz * p.tiles_r + w.tr) * p.tiles_c + w.tc;
@@ -514,6 +527,7 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   p.g_meta = g_meta;
   p.g_experts = g_experts;
   p.w_static = (g_static_weights && mary_pdl_enabled() && !g_tiles && !(glu && !use_swap)) ? 1 : 0;
+  p.raster = (!g_tiles && p.split_k == 1 && !sk_epi && p.tiles_c >= 16 && p.tiles_r >= 4) ? 8 : 0;
   if (g_tiles) {
     if (batch != 1 || split_k != 1) return MARY_ERR_BAD_ARG;
     if (use_swap) {
