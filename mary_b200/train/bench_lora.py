@@ -2,15 +2,20 @@
 data parallel over the ranks of a ``torchrun`` launch with the adapter gradients reduced per layer bucket, overlapped with
 the backward pass of the earlier layers.
 
-    python -m mary_b200.train.bench_lora [--seq 4096] [--batch 1] [--steps 5] [--layers 48] [--comm fused|nccl|none]
+    python -m mary_b200.train.bench_lora [--seq 4096] [--batch 1] [--steps 5] [--layers 48] [--comm fused|nccl] [--tp T] [--checkpoint]
 
 Prints one JSON line: tokens/s over all ranks (device time, max over ranks).  Data are synthetic token ids, weights random."""
 from __future__ import annotations
 
 import argparse
 import json
+import os
 
-import torch
+# a 4096-token step without activation checkpointing fills a 180 GB GPU to within a few GB: segments that can grow keep the
+# caching allocator from failing on fragmentation (must be set before the first CUDA allocation)
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+import torch  # noqa: E402
 
 
 def main():
