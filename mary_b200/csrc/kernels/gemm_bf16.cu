@@ -71,6 +71,8 @@ struct GemmParams {
   // compact block of the output: the band's weight tiles stay in L2 while the row operand streams past them once per band.  With
   // column tiles fastest (raster 0) a wide output re-reads every weight tile once per row tile.
   int raster;
+  // batched problems may SHARE an operand (batch stride 0): its tensor map then has one batch entry and every problem reads it
+  int zr_mul, zc_mul;
 };
 
 // One unit of work of a CTA: K-blocks [kb0, kb1) of output tile (tr, tc) of problem bz; `seg` of `nseg` partial results of that
@@ -211,10 +213,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
             const int kb = w.kb0 + i;
             mbar_expect_tx(&full[i], C::STAGE_BYTES);
             if (p.swap) {
-              tma_load_3d(st, &tm_r, &full[i], kb * BK, w.tr * BM, w.bz);
-              if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[i], kb * BK, p.glu_offset + w.tr * BM, w.bz);
+              tma_load_3d(st, &tm_r, &full[i], kb * BK, w.tr * BM, w.bz * p.zr_mul);
+              if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[i], kb * BK, p.glu_offset + w.tr * BM, w.bz * p.zr_mul);
             } else {
-              tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[i], kb * BK, w.tc * BN, w.bz);
+              tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[i], kb * BK, w.tc * BN, w.bz * p.zc_mul);
             }
           }
         }
@@ -223,7 +225,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       if (!p.w_static) have = iter.next(w);
       while (have) {
         const int tr = w.tr, tc = w.tc;
-        int zr = w.bz, zc = w.bz;
+        int zr = w.bz * p.zr_mul, zc = w.bz * p.zc_mul;
         if (p.g_tiles) {
           const int e = min(max(p.g_tiles[4 * (p.swap ? tc : tr)], 0), p.g_experts - 1);
           zr = p.swap ? e : 0;
@@ -556,9 +558,12 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
     if (tiles > n_counters || slots * BM * bn > ws_floats) return MARY_ERR_BAD_ARG;     // workspace too small
   }
   CUtensorMap tr, tc;
-  int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, (g_tiles && use_swap) ? g_experts : batch, bsr, BM);
+  const bool r_shared = batch > 1 && bsr == 0 && !g_tiles, c_shared = batch > 1 && bsc == 0 && !g_tiles;
+  p.zr_mul = r_shared ? 0 : 1;
+  p.zc_mul = c_shared ? 0 : 1;
+  int rc = make_tmap_3d(&tr, R, rows_r_total, K, ldr, (g_tiles && use_swap) ? g_experts : (r_shared ? 1 : batch), bsr, BM);
   if (rc) return rc;
-  rc = make_tmap_3d(&tc, Cc, p.rows_c, K, ldc, (g_tiles && !use_swap) ? g_experts : batch, bsc, bn);
+  rc = make_tmap_3d(&tc, Cc, p.rows_c, K, ldc, (g_tiles && !use_swap) ? g_experts : (c_shared ? 1 : batch), bsc, bn);
   if (rc) return rc;
   if (glu) {
     switch (bn) {

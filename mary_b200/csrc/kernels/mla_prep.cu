@@ -66,8 +66,8 @@ __global__ void mla_prep_kernel(const __nv_bfloat16* __restrict__ qakv, int64_t 
 }
 
 // qb [T, H, 192] = [nope 128 | rope 64] per head -> q_full[T, H, 512 + i] for the rope part
-__global__ void mla_q_rope_kernel(const __nv_bfloat16* __restrict__ qb, const float* __restrict__ inv_freq, const int* __restrict__ positions,
-                                  __nv_bfloat16* __restrict__ q_full, int H, int T) {
+__global__ void mla_q_rope_kernel(const __nv_bfloat16* qb, const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                  __nv_bfloat16* q_full, int H, int T, int64_t dst_stride, int dst_off) {
   pdl_sync();
   const int64_t gw = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (gw >= (int64_t)T * H) return;
@@ -80,9 +80,21 @@ __global__ void mla_q_rope_kernel(const __nv_bfloat16* __restrict__ qb, const fl
     const float ra = a * c - b * s, rb = a * s + b * c;
     a = ra; b = rb;
   }
-  __nv_bfloat16* dst = q_full + gw * 576 + 512;
+  __nv_bfloat16* dst = q_full + gw * dst_stride + dst_off;        // may be the source row itself: every lane has read its pair
   dst[i] = __float2bfloat16(a);
   dst[32 + i] = __float2bfloat16(b);
+}
+
+// K rows of the expanded prefill: the 64 rotated dims every head shares, copied from the latent row behind each head's 128 own dims.
+__global__ void mla_fill_k_rope_kernel(const __nv_bfloat16* __restrict__ lat, int64_t lat_stride, __nv_bfloat16* __restrict__ k, int H,
+                                       int64_t n_rows) {
+  pdl_sync();
+  const int64_t gw = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (gw >= n_rows * H) return;
+  const int64_t n = gw / H;
+  const int i = threadIdx.x & 31;
+  const uint32_t v = *(const uint32_t*)(lat + n * lat_stride + 512 + 2 * i);
+  *(uint32_t*)(k + gw * 192 + 128 + 2 * i) = v;
 }
 
 }  // namespace
@@ -100,7 +112,28 @@ MARY_API int mary_mla_prep(const void* qakv, int64_t ld, int q_lora, const void*
 MARY_API int mary_mla_q_rope(const void* qb, const float* inv_freq, const int* positions, void* q_full, int H, int T, cudaStream_t s) {
   if (T <= 0) return MARY_OK;
   const int64_t warps = (int64_t)T * H;
-  MARY_LAUNCH(mla_q_rope_kernel, (int)((warps + 7) / 8), 256, 0, s, (const __nv_bfloat16*)qb, inv_freq, positions, (__nv_bfloat16*)q_full, H, T);
+  MARY_LAUNCH(mla_q_rope_kernel, (int)((warps + 7) / 8), 256, 0, s, (const __nv_bfloat16*)qb, inv_freq, positions, (__nv_bfloat16*)q_full, H, T,
+              (int64_t)576, 512);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// The same rotation written back over the 64 rope dims of qb [T, H, 192] itself (the expanded prefill attends with 192-wide queries).
+MARY_API int mary_mla_q_rope_inplace(void* qb, const float* inv_freq, const int* positions, int H, int T, cudaStream_t s) {
+  if (T <= 0) return MARY_OK;
+  const int64_t warps = (int64_t)T * H;
+  MARY_LAUNCH(mla_q_rope_kernel, (int)((warps + 7) / 8), 256, 0, s, (const __nv_bfloat16*)qb, inv_freq, positions, (__nv_bfloat16*)qb, H, T,
+              (int64_t)192, 128);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// k [n_rows, H, 192]: dims 128..191 of every head <- dims 512..575 of latent row n (row pitch lat_stride elements).
+MARY_API int mary_mla_fill_k_rope(const void* lat, int64_t lat_stride, void* k, int H, int64_t n_rows, cudaStream_t s) {
+  if (n_rows <= 0) return MARY_OK;
+  if (lat_stride & 1) return MARY_ERR_BAD_ARG;
+  const int64_t warps = n_rows * H;
+  MARY_LAUNCH(mla_fill_k_rope_kernel, (int)((warps + 7) / 8), 256, 0, s, (const __nv_bfloat16*)lat, lat_stride, (__nv_bfloat16*)k, H, n_rows);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

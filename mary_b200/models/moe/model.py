@@ -82,19 +82,25 @@ class MLAAttention(nn.Module):
         576 / 512-wide latent space, which is what long query blocks are bound by.  The scores are identical
         (q_nope . W_UK^T c_kv = W_UK q_nope . c_kv); decode keeps the absorbed form, where the cache stream is the bound."""
         T, H = qb.shape[0], self.H
-        q = qb.view(T, H, 192)
-        if self.inv_freq is not None:
-            q = torch.cat([q[..., :128], ref.rope(q[..., 128:], meta.positions, self.inv_freq).to(q.dtype)], -1)
         lat = cache.k[self.li]                                              # [pages, page, 576]
         pick, meta2 = meta.repage(64)                                       # the same for every layer of this step
         rows = lat[pick].view(-1, 64, 576)                                  # context of every sequence in 64-token pages
         P, ps = rows.shape[0], 64
-        ckv = rows[..., :512].reshape(P * ps, 512)
         if getattr(self, "_w_uk_t", None) is None:
             self._w_uk_t = self.w_uk.permute(0, 2, 1).reshape(H * 128, 512).contiguous()      # k_nope[h, n] = sum_k c_kv[k] W_UK[h, k, n]
-        k_nope = ops.linear(ckv, self._w_uk_t).view(P, ps, H, 128)
-        v = ops.linear(ckv, self.w_uv.reshape(H * 128, 512)).view(P, ps, H, 128)
-        k = torch.cat([k_nope, rows[..., 512:].unsqueeze(2).expand(P, ps, H, 64)], -1).contiguous()
+        if qb.is_cuda:
+            # the rope dims of q rotated in place, K and V written straight into their paged layout: no concatenation copies
+            q = (ops.mla_q_rope_inplace(qb, self.inv_freq, meta, H) if self.inv_freq is not None else qb).view(T, H, 192)
+            k, v = ops.mla_expand_kv(rows.view(P * ps, 576), self._w_uk_t, self.w_uv.reshape(H * 128, 512), H)
+            k, v = k.view(P, ps, H, 192), v.view(P, ps, H, 128)
+        else:
+            q = qb.view(T, H, 192)
+            if self.inv_freq is not None:
+                q = torch.cat([q[..., :128], ref.rope(q[..., 128:], meta.positions, self.inv_freq).to(q.dtype)], -1)
+            ckv = rows[..., :512].reshape(P * ps, 512)
+            k_nope = ops.linear(ckv, self._w_uk_t).view(P, ps, H, 128)
+            v = ops.linear(ckv, self.w_uv.reshape(H * 128, 512)).view(P, ps, H, 128)
+            k = torch.cat([k_nope, rows[..., 512:].unsqueeze(2).expand(P, ps, H, 64)], -1).contiguous()
         o = ops.paged_attention(q.contiguous(), k, v, meta2, self.c.attn_scale)
         return self.par.row_linear(o.reshape(T, H * 128), self.w_o)
 

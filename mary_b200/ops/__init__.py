@@ -123,6 +123,15 @@ def mla_attention(q, cache, meta, scale):
     return ref.paged_attention(q, cache, cache, meta, scale, dv=512)
 
 
+def mla_expand_kv(rows, w_uk_t, w_uv, H):
+    """GPU only (the host path concatenates): see ``ops.cuda.mla_expand_kv``."""
+    return _k().mla_expand_kv(rows, w_uk_t, w_uv, H)
+
+
+def mla_q_rope_inplace(qb, inv_freq, meta, H):
+    return _k().mla_q_rope_inplace(qb, inv_freq, meta, H)
+
+
 def mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps):
     """Norm the q_a part, norm the latent, rotate the carried rope dims and append ``[c_kv | k_rope]`` to the cache."""
     if _cuda(qakv):

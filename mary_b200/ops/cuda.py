@@ -645,6 +645,30 @@ def gemm_batched(x, w, out, M, N, K, ldx, ldw, ldo, batch, bsx, bsw, bso):
     return out
 
 
+declare("mary_mla_q_rope_inplace", "pppiis")
+declare("mary_mla_fill_k_rope", "plpils")
+
+
+def mla_expand_kv(rows, w_uk_t, w_uv, H):
+    """Keys and values of the expanded (non-absorbed) prefill straight into their final layout, without concatenation copies:
+    ``rows [N, 576]`` latent rows -> ``k [N, H, 192]`` (``W_UK^T c_kv`` per head by a batched GEMM over the heads that shares the
+    row operand and writes each head's 128 columns at pitch 192, then the 64 rotated dims every head shares copied behind them) and
+    ``v [N, H, 128]`` (one GEMM).  ``w_uk_t [H * 128, 512]``, ``w_uv [H * 128, 512]``."""
+    N = rows.shape[0]
+    k = torch.empty(N, H, 192, dtype=torch.bfloat16, device=rows.device)
+    with static_weights:
+        gemm_batched(rows, w_uk_t, k, N, 128, 512, rows.stride(0), 512, H * 192, H, 0, 128 * 512, 192)
+        v = gemm(rows[:, :512], w_uv)
+    check(lib().mary_mla_fill_k_rope(_p(rows), rows.stride(0), _p(k), H, N, _stream()), "mla_fill_k_rope")
+    return k, v.view(N, H, 128)
+
+
+def mla_q_rope_inplace(qb, inv_freq, meta, H):
+    """Rotate the 64 rope dims of every head of ``qb [T, H * 192]`` in place."""
+    check(lib().mary_mla_q_rope_inplace(_p(qb), _p(inv_freq), _p(meta.positions), H, qb.shape[0], _stream()), "mla_q_rope")
+    return qb
+
+
 def mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps):
     T = qakv.shape[0]
     qa = torch.empty(T, q_lora, dtype=torch.bfloat16, device=qakv.device)
