@@ -305,8 +305,11 @@ def main():
         prompt = rng.integers(0, cfg.vocab_size, (1, ctx))
         pd.prefill(prompt, chunk=args.prefill_chunk)
         torch.cuda.synchronize()
+        torch.cuda.profiler.start()          # a profiler started with its capture off sees exactly this prefill
         with Tracer() as tr:
             pd.prefill(prompt, chunk=args.prefill_chunk)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
         if rank == 0:
             print(tr.report())
         return
@@ -490,10 +493,11 @@ def main():
                     with torch.no_grad():
                         meta = cp.begin(ctx, table, page, device=dev)
                         idx = torch.cat([torch.arange(lo, hi, device=dev) for lo, hi in (cp.chunks[c] for c in cp.my_chunks())])
-                        tok, h = model.verify(ids_all[idx], meta, pc)
+                        head = torch.tensor([idx.numel() - 1], device=dev)     # the vocabulary projection for the last local row only
+                        tok, h = model.verify(ids_all[idx], meta, pc, rows=head)
                         if k:
                             nxt = torch.where(idx + 1 < ctx, ids_all[(idx + 1).clamp_max(ctx - 1)], tok[-1].to(torch.int32))
-                            model.draft(0, h, nxt, meta, pc)
+                            model.draft(0, h, nxt, meta, pc, rows=head)
                     cp.end()
                     b.record()
                     barrier()
@@ -516,10 +520,11 @@ def main():
                     with torch.no_grad():
                         meta = cp.begin(ctx, table, page, device=dev)
                         lo, hi = cp.bounds[rank]
-                        tok, h = model.verify(ids_all[lo:hi], meta, pc)
+                        head = torch.tensor([hi - lo - 1], device=dev)         # the vocabulary projection for the last local row only
+                        tok, h = model.verify(ids_all[lo:hi], meta, pc, rows=head)
                         if k:                                   # the draft layer's cache rows of this chunk, as the plain prefill fills them
                             nxt = torch.cat([ids_all[lo + 1:hi], ids_all[hi:hi + 1] if hi < ctx else tok[-1:].to(torch.int32)])
-                            model.draft(0, h, nxt, meta, pc)
+                            model.draft(0, h, nxt, meta, pc, rows=head)
                     cp.end()
                     b.record()
                     barrier()

@@ -159,7 +159,11 @@ gemm_nvfp4_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
   } else {
     n_tiles = *p.n_tiles;
   }
-  const int total = n_tiles * p.w_tiles;          // work item = (weight row tile, token tile), token tile fastest
+  const int total = n_tiles * p.w_tiles;          // work item = (weight row tile, token tile), token tile fastest ...
+  // ... except with 128-token tiles (prefill-sized batches): there the quantised activations of all tiles outgrow L2, while an
+  // expert has one or two token tiles, so the weight tile runs fastest: a token tile is read from memory once and serves all
+  // weight tiles of its expert from L2, and the few token tiles of one expert meet their weight tiles within one wave of CTAs
+  constexpr bool WT_FAST = NT == 128;
   const int sf_per_tile = p.k_blocks * SF_STAGE;  // scale bytes of one 128-row block over the whole K
 
   // stage layout: [A gate 16K][A up 16K]? [B NT*128][SFA gate 2K][SFA up 2K]? [SFB 2K]
@@ -172,8 +176,8 @@ gemm_nvfp4_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
       int stage = 0; uint32_t phase = 0;
       if (p.ep_mode) fence_proxy_async_global();
       for (int w = blockIdx.x; w < total; w += gridDim.x) {
-        const Tile t = tiles[w % n_tiles];
-        const int wt = w / n_tiles;
+        const Tile t = tiles[WT_FAST ? w / p.w_tiles : w % n_tiles];
+        const int wt = WT_FAST ? w % p.w_tiles : w / n_tiles;
         const int wrow = t.expert * p.rows_total + wt * BM;
         const uint8_t* sfa = p.sfw + ((int64_t)t.expert * (p.rows_total / BM) + wt) * sf_per_tile;
         const uint8_t* sfa_up = sfa + (int64_t)(p.n_out / BM) * sf_per_tile;
@@ -232,8 +236,8 @@ gemm_nvfp4_grouped_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid
     const int q = warp & 3;
     int it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
-      const Tile t = tiles[w % n_tiles];
-      const int wt = w / n_tiles;
+      const Tile t = tiles[WT_FAST ? w / p.w_tiles : w % n_tiles];
+      const int wt = WT_FAST ? w % p.w_tiles : w / n_tiles;
       const int buf = C::ACC_BUFS == 2 ? (it & 1) : 0;
       const uint32_t acc_phase = C::ACC_BUFS == 2 ? ((it >> 1) & 1) : (it & 1);
       if (!mbar_wait(&acc_full[buf], acc_phase, abort_flag, p.status, MARY_ERR_TIMEOUT_MMA)) goto done;

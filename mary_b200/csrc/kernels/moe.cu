@@ -104,6 +104,32 @@ __device__ __forceinline__ uint32_t e2m1_code(float y) {
 // Scales go to the 512-byte block layout of the row's NT-row tile; optionally also row-major (tests, dense users).
 // With row_of (entry -> padded row, k entries per token) the grid runs over the ENTRIES instead of the padded rows: a decode
 // batch has a few hundred entries but thousands of padded rows, most of them padding.
+// 16 consecutive values -> 8 code bytes and the scale byte of their block
+__device__ __forceinline__ uint2 nvfp4_block16(const __nv_bfloat16* __restrict__ src, uint8_t* sb_out) {
+  const uint4 v0 = *(const uint4*)src, v1 = *(const uint4*)(src + 8);
+  float f[16];
+  const __nv_bfloat162* p0 = (const __nv_bfloat162*)&v0;
+  const __nv_bfloat162* p1 = (const __nv_bfloat162*)&v1;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float2 a = __bfloat1622float2(p0[j]), c = __bfloat1622float2(p1[j]);
+    f[2 * j] = a.x; f[2 * j + 1] = a.y; f[8 + 2 * j] = c.x; f[8 + 2 * j + 1] = c.y;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  const float sfv = fminf(__fdiv_rn(amax, 6.0f), 448.0f);
+  const __nv_fp8_storage_t sb = __nv_cvt_float_to_fp8(sfv, __NV_SATFINITE, __NV_E4M3);
+  const float s = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3)));
+  uint32_t lo = 0, hi = 0;
+  if (s > 0.f) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { lo |= e2m1_code(__fdiv_rn(f[j], s)) << (4 * j); hi |= e2m1_code(__fdiv_rn(f[8 + j], s)) << (4 * j); }
+  }
+  *sb_out = (uint8_t)sb;
+  return make_uint2(lo, hi);
+}
+
 __global__ void quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int* __restrict__ src_of, int identity,
                                         int Kd, int NT, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf_tiles,
                                         uint8_t* __restrict__ sf_rowmajor, const int* __restrict__ n_rows,
@@ -123,29 +149,40 @@ __global__ void quant_nvfp4_rows_kernel(const __nv_bfloat16* __restrict__ x, int
   const int tile = row / NT, r = row % NT;
   const int64_t sf_base = (int64_t)tile * (Kd / 64) * 512 + (r % 32) * 16 + (r / 32) * 4;
   for (int b = threadIdx.x; b < Kd / 16; b += blockDim.x) {
-    const uint4 v0 = *(const uint4*)(xr + b * 16), v1 = *(const uint4*)(xr + b * 16 + 8);
-    float f[16];
-    const __nv_bfloat162* p0 = (const __nv_bfloat162*)&v0;
-    const __nv_bfloat162* p1 = (const __nv_bfloat162*)&v1;
+    uint8_t sb;
+    const uint2 code = nvfp4_block16(xr + b * 16, &sb);
+    *(uint2*)(xq + (int64_t)row * (Kd / 2) + b * 8) = code;
+    if (sf_tiles) sf_tiles[sf_base + (int64_t)(b / 4) * 512 + (b % 4)] = sb;
+    if (sf_rowmajor) sf_rowmajor[(int64_t)row * (Kd / 16) + b] = sb;
+  }
+}
+
+// Token-driven form for batches with many tokens: one CTA per TOKEN quantises the row once and writes the bytes to the padded
+// row of each of its k routed entries (the entry-driven form above repeats the arithmetic k times, which dominates once the
+// batch has thousands of tokens).  K_ENT: entries per token held in registers (k <= K_ENT).
+template <int K_ENT>
+__global__ void quant_nvfp4_tokens_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const int* __restrict__ row_of, int k, int Kd,
+                                          int NT, uint8_t* __restrict__ xq, uint8_t* __restrict__ sf_tiles) {
+  pdl_sync();
+  const int t = blockIdx.x;
+  int rows[K_ENT];
+  int64_t sfb[K_ENT];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 a = __bfloat1622float2(p0[j]), c = __bfloat1622float2(p1[j]);
-      f[2 * j] = a.x; f[2 * j + 1] = a.y; f[8 + 2 * j] = c.x; f[8 + 2 * j + 1] = c.y;
-    }
-    float amax = 0.f;
+  for (int j = 0; j < K_ENT; ++j) {
+    rows[j] = j < k ? row_of[t * k + j] : -1;
+    const int tile = rows[j] / NT, r = rows[j] % NT;
+    sfb[j] = (int64_t)tile * (Kd / 64) * 512 + (r % 32) * 16 + (r / 32) * 4;
+  }
+  const __nv_bfloat16* xr = x + (int64_t)t * ldx;
+  for (int b = threadIdx.x; b < Kd / 16; b += blockDim.x) {
+    uint8_t sb;
+    const uint2 code = nvfp4_block16(xr + b * 16, &sb);
 #pragma unroll
-    for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
-    const float sfv = fminf(__fdiv_rn(amax, 6.0f), 448.0f);
-    const __nv_fp8_storage_t sb = __nv_cvt_float_to_fp8(sfv, __NV_SATFINITE, __NV_E4M3);
-    const float s = __half2float(__half(__nv_cvt_fp8_to_halfraw(sb, __NV_E4M3)));
-    uint32_t lo = 0, hi = 0;
-    if (s > 0.f) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { lo |= e2m1_code(__fdiv_rn(f[j], s)) << (4 * j); hi |= e2m1_code(__fdiv_rn(f[8 + j], s)) << (4 * j); }
-    }
-    *(uint2*)(xq + (int64_t)row * (Kd / 2) + b * 8) = make_uint2(lo, hi);
-    if (sf_tiles) sf_tiles[sf_base + (int64_t)(b / 4) * 512 + (b % 4)] = (uint8_t)sb;
-    if (sf_rowmajor) sf_rowmajor[(int64_t)row * (Kd / 16) + b] = (uint8_t)sb;
+    for (int j = 0; j < K_ENT; ++j)
+      if (rows[j] >= 0) {
+        *(uint2*)(xq + (int64_t)rows[j] * (Kd / 2) + b * 8) = code;
+        sf_tiles[sfb[j] + (int64_t)(b / 4) * 512 + (b % 4)] = sb;
+      }
   }
 }
 
@@ -217,6 +254,17 @@ MARY_API int mary_quant_nvfp4_entries(const void* x, int64_t ldx, const int* row
   if (n_entries <= 0) return MARY_OK;
   if ((K % 64) || (ldx % 8) || k < 1) return MARY_ERR_BAD_ARG;
   int threads = K / 16 < 256 ? ((K / 16 + 31) / 32 * 32) : 256;
+  if (!identity && k > 1 && k <= 16 && n_entries >= 2048 && n_entries % k == 0) {
+    if (k <= 8) {
+      MARY_LAUNCH(quant_nvfp4_tokens_kernel<8>, n_entries / k, threads, 0, s, (const __nv_bfloat16*)x, ldx, row_of, k, K, NT, (uint8_t*)xq,
+                                                                  (uint8_t*)sf_tiles);
+    } else {
+      MARY_LAUNCH(quant_nvfp4_tokens_kernel<16>, n_entries / k, threads, 0, s, (const __nv_bfloat16*)x, ldx, row_of, k, K, NT, (uint8_t*)xq,
+                                                                   (uint8_t*)sf_tiles);
+    }
+    MARY_CHECK_LAUNCH();
+    return MARY_OK;
+  }
   MARY_LAUNCH(quant_nvfp4_rows_kernel, n_entries, threads, 0, s, (const __nv_bfloat16*)x, ldx, nullptr, identity, K, NT, (uint8_t*)xq,
                                                         (uint8_t*)sf_tiles, nullptr, nullptr, row_of, k);
   MARY_CHECK_LAUNCH();

@@ -272,11 +272,19 @@ class InklingDecoder(torch.nn.Module):
         return ref.argmax_first(self.logits(h))
 
     # ------------------------------------------------------------------ speculative decoding (runtime.spec_decode protocol)
-    def verify(self, ids, meta, cache, slots=None):
-        h = self.trunk(ids, meta, cache, slots)
-        return self.head_argmax(h), h
+    def _head_rows(self, h, rows):
+        """Arg-max token of the rows ``rows`` of ``h`` (None: every row; an empty index: no un-embedding at all)."""
+        if rows is not None:
+            if rows.numel() == 0:
+                return torch.empty(0, dtype=torch.int64, device=h.device)
+            h = h[rows]
+        return self.head_argmax(h)
 
-    def draft(self, d: int, h_prev, next_ids, meta, cache, slots=None):
+    def verify(self, ids, meta, cache, slots=None, rows=None):
+        h = self.trunk(ids, meta, cache, slots)
+        return self._head_rows(h, rows), h
+
+    def draft(self, d: int, h_prev, next_ids, meta, cache, slots=None, rows=None):
         """MTP head ``d`` over rows ``(hidden of row j, token after row j)``: hidden first in the concatenation (mtp.rs:108-244),
         one DENSE block with its own cache rows and rings, the shared un-embedding."""
         slots = self.slots_default[:meta.num_seqs] if slots is None else slots
@@ -287,7 +295,7 @@ class InklingDecoder(torch.nn.Module):
         x = torch.cat([ops.rmsnorm(h_prev, self.P[pre + "hidden_norm.weight"], eps), ops.rmsnorm(e, self.P[pre + "embed_norm.weight"], eps)], -1)
         h = ops.linear(x, self.P[pre + "input_proj.weight"])
         h = self.block(pre + "transformer_block.", self.n_llm + d, -1, True, h, meta, cache, slots)
-        return self.head_argmax(h), h
+        return self._head_rows(h, rows), h
 
     def greedy(self, ids, meta, cache, rows, slots=None):
         return self.head_argmax(self.trunk(ids, meta, cache, slots)[rows])

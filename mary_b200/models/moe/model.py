@@ -375,18 +375,25 @@ class MoEDecoder(nn.Module):
         return self.head_argmax(self.hidden(ids, meta, cache)[rows])
 
     # -- speculative decoding -------------------------------------------------
-    def verify(self, ids, meta, cache):
-        """One forward over the fed rows.  Returns ``(arg-max token of every row, trunk hidden of every row)``."""
-        h = self.trunk(ids, meta, cache)
-        x = ops.rmsnorm(h, self.norm, self.cfg.rms_norm_eps)
-        return self.head_argmax(x), h
+    def _head_rows(self, h, norm, rows):
+        """Arg-max token of the rows ``rows`` of ``h`` (None: every row; an empty index: no head at all).  A prompt chunk of
+        thousands of rows needs the vocabulary projection for its last row only."""
+        if rows is not None:
+            if rows.numel() == 0:
+                return torch.empty(0, dtype=torch.int64, device=h.device)
+            h = h[rows]
+        return self.head_argmax(ops.rmsnorm(h, norm, self.cfg.rms_norm_eps))
 
-    def draft(self, d: int, h_prev, next_ids, meta, cache):
-        """Draft head ``d``: hidden of the rows + the token that follows each row -> ``(draft token, its hidden)``."""
+    def verify(self, ids, meta, cache, rows=None):
+        """One forward over the fed rows.  Returns ``(arg-max token of the rows ``rows`` (default all), trunk hidden of every row)``."""
+        h = self.trunk(ids, meta, cache)
+        return self._head_rows(h, self.norm, rows), h
+
+    def draft(self, d: int, h_prev, next_ids, meta, cache, rows=None):
+        """Draft head ``d``: hidden of the rows + the token that follows each row -> ``(draft token of ``rows``, hidden of every row)``."""
         emb = ops.embed(next_ids, self.embed)
         h = self.mtp[min(d, len(self.mtp) - 1)](h_prev, emb, meta, cache)
-        x = ops.rmsnorm(h, self.mtp[min(d, len(self.mtp) - 1)].out_norm, self.cfg.rms_norm_eps)
-        return self.head_argmax(x), h
+        return self._head_rows(h, self.mtp[min(d, len(self.mtp) - 1)].out_norm, rows), h
 
 
 def init_random_(model: MoEDecoder, seed: int = 0, std: float = 0.02, expert_slabs: int | None = None) -> None:

@@ -182,6 +182,39 @@ def bench_moe(E: int = 48, H: int = 7168, F: int = 2048, T: int = 384, k: int = 
     assert K.last_status() == 0
 
 
+def bench_moeprefill(E: int = 384, H: int = 7168, F: int = 2048, T: int = 4096, k: int = 8, iters: int = 5):
+    """Prefill-shaped expert MLP (128-token tiles): a prompt of T tokens puts about T k / E rows on every expert, so below a few
+    hundred rows per expert the layer is still bound by streaming the expert weights once."""
+    from . import cuda as K, cuda_moe
+    from .moe import NVFP4Experts
+    hbm, tf, tag = peaks()
+    ex = NVFP4Experts.random(E, H, F, "cuda", seed=0)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    idx, w = K.router_topk(torch.randn(T, E, device="cuda"), k, "softmax")
+    plan = cuda_moe.moe_plan(idx, E, 128)
+    parts = {}
+    parts["quantise x"] = time_op(lambda: cuda_moe.quantize_entries(x, plan, k, False), iters=iters)
+    xq, sfx = cuda_moe.quantize_entries(x, plan, k, False)
+    parts["w13+glu"] = time_op(lambda: cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, F, H, E, "swiglu"), iters=iters)
+    h = cuda_moe.grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, F, H, E, "swiglu")
+    parts["quantise h"] = time_op(lambda: cuda_moe.quantize_entries(h, plan, k, True), iters=iters)
+    hq, sfh = cuda_moe.quantize_entries(h, plan, k, True)
+    parts["w2"] = time_op(lambda: cuda_moe.grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, H, F, E, None), iters=iters)
+    y = cuda_moe.grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, H, F, E, None)
+    parts["un-permute"] = time_op(lambda: cuda_moe.unpermute(y, plan, w, T, k, None), iters=iters)
+    b13 = E * 2 * F * H * (0.5 + 1 / 16)
+    b2 = E * H * F * (0.5 + 1 / 16)
+    fl = 2.0 * T * k * 3 * F * H
+    print(f"nvfp4 expert MLP, prefill-shaped: E={E} H={H} F={F} T={T} k={k}, {int(plan.meta[0])} token tiles of 128")
+    for name, ms in parts.items():
+        b = b13 if name == "w13+glu" else b2 if name == "w2" else 0
+        print(f"  {name:<12}{ms:8.4f} ms" + (f"  weights {b / 1e6:.0f} MB, {b / ms / 1e6:.0f} GB/s ({b / ms / 1e6 / hbm:.2f} {tag})" if b else ""))
+    full = time_op(lambda: cuda_moe.experts_forward(x, idx, w, ex), iters=iters)
+    print(f"  whole layer {full:8.4f} ms: weights at {(b13 + b2) / full / 1e6:.0f} GB/s ({(b13 + b2) / full / 1e6 / hbm:.2f} {tag}), "
+          f"{fl / full / 1e9:.0f} TFLOP/s on the routed rows")
+    assert K.last_status() == 0
+
+
 def bench_membw(gib: int = 2, iters: int = 10):
     """Own read and copy sweeps over a buffer far larger than L2 (the reference's ``inkling_membw``), beside the measured copy peak."""
     from .cuda import _p, _stream, check, declare, lib
@@ -459,6 +492,8 @@ if __name__ == "__main__":
     nums = [int(v) for v in sys.argv[2:]]
     if what == "membw":
         bench_membw(*nums)
+    if what == "moeprefill":
+        bench_moeprefill(*nums)
     if what == "bf16moe":
         bench_bf16moe(*nums)
     if what in ("gemm", "all"):

@@ -77,6 +77,29 @@ def grouped_gemm(wq, sfw, scale2, xq, sfx, plan: Plan, n_out: int, K: int, E: in
     return out
 
 
+declare("mary_gemm_nvfp4_grouped_glu_q", "ppppppppp" + "iiiliis")
+# with 32-token tiles the w13 GEMM of ``experts_forward`` leaves its GLU result quantised (same bytes as GEMM -> bf16 ->
+# quantiser, one launch less).  With 128-token tiles the GEMM has one accumulator buffer and the longer epilogue stalls its main
+# loop (measured on a 4096-token prefill: +65 ms in the GEMMs against 10 ms saved), so the quantiser stays a launch of its own.
+def _glu_quant_default() -> bool:
+    from ..utils import flags
+    return bool(flags.get("MARY_MOE_GLU_QUANT"))
+
+
+FUSED_GLU_QUANT = _glu_quant_default()
+
+
+def grouped_gemm_glu_q(wq, sfw, scale2, xq, sfx, plan: Plan, n_out: int, K: int, E: int, glu: str):
+    """The GLU GEMM with the quantising epilogue: ``(codes [rows, n_out / 2], scale tiles)`` ready for the next NVFP4 GEMM."""
+    rows, nt = plan.max_rows, plan.nt
+    hq = torch.empty(rows, n_out // 2, dtype=torch.uint8, device=xq.device)
+    sfh = torch.empty(rows // nt, n_out // 64, 512, dtype=torch.uint8, device=xq.device)
+    g = {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
+    check(lib().mary_gemm_nvfp4_grouped_glu_q(_p(wq), _p(sfw), _p(scale2), _p(xq), _p(sfx), _p(plan.tiles), _p(plan.meta), _p(hq), _p(sfh),
+                                              E, n_out, K, rows, nt, g, _stream()), "gemm_nvfp4_grouped")
+    return hq, sfh
+
+
 def unpermute(y, plan: Plan, w, T: int, k: int, add=None):
     H = y.shape[1]
     out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
@@ -91,8 +114,11 @@ def experts_forward(x, idx, w, ex, shared=None, nt: int | None = None):
         nt = 32 if T * k <= 32 * ex.E else 128
     plan = moe_plan(idx, ex.E, nt)
     xq, sfx = quantize_entries(x, plan, k, identity=False)
-    h = grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
-    hq, sfh = quantize_entries(h, plan, k, identity=True)
+    if FUSED_GLU_QUANT and nt == 32:
+        hq, sfh = grouped_gemm_glu_q(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
+    else:
+        h = grouped_gemm(ex.w13_q, ex.w13_sf, ex.w13_s2, xq, sfx, plan, ex.F, ex.H, ex.E, ex.act)
+        hq, sfh = quantize_entries(h, plan, k, identity=True)
     y = grouped_gemm(ex.w2_q, ex.w2_sf, ex.w2_s2, hq, sfh, plan, ex.H, ex.F, ex.E, None)
     return unpermute(y, plan, w, T, k, shared)
 

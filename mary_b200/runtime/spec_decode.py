@@ -101,17 +101,19 @@ class SpecDecoder:
                     else:
                         self.model.trunk(flat, meta, self.cache)
                     continue
-                tok, h = self.model.verify(flat, meta, self.cache)
+                # the vocabulary projection runs for the last row of each prompt in the last chunk only
+                head = last if c0 + n == L else last[:0]
+                tok, h = self.model.verify(flat, meta, self.cache, rows=head)
                 nxt = torch.cat([ids[:, c0 + 1:c0 + n], ids[:, min(c0 + n, L - 1):min(c0 + n, L - 1) + 1]], 1)
                 if c0 + n == L:
-                    pending = tok[last].to(torch.int32)
+                    pending = tok.to(torch.int32)
                     nxt[:, -1] = pending
-                d_tok, d_h = self.model.draft(0, h, nxt.reshape(-1), meta, self.cache)
+                d_tok, d_h = self.model.draft(0, h, nxt.reshape(-1), meta, self.cache, rows=head)
             self.kv_before.fill_(L)
             self.len_bound = L
             self.fed[:, 0].copy_(pending)
             if self.k:
-                drafts = [d_tok[last].to(torch.int32)]
+                drafts = [d_tok.to(torch.int32)]
                 h_last = d_h[last]
                 for d in range(1, self.k):
                     self._set_meta(self.meta_d, self.kv_before + (d - 1), 1)

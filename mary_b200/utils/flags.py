@@ -67,6 +67,7 @@ declare("MARY_GQA_TC", bool, True, "decode-shaped batches of grouped-query model
 declare("MARY_PDL", bool, False, "launch the decode-path kernels with programmatic dependent launch")
 declare("MARY_MULTIMEM", bool, True, "use the NVSwitch multicast address (multimem.ld_reduce / multimem.st) where the allocation has one")
 declare("MARY_ONESHOT", bool, True, "small all-reduces take the one-barrier staged form")
+declare("MARY_MOE_GLU_QUANT", bool, True, "with 32-token tiles the first expert GEMM of the planned MoE path quantises its GLU result in the epilogue (0: a second quantiser launch)")
 declare("MARY_MOE_FUSED", bool, True, "decode-sized MoE layers take the four-launch pipeline (0: the planned path)")
 declare("MARY_DEBUG_CHECKS", bool, False, "validate every batch description on the host before launch (lengths, page ids, page reuse)")
 declare("MARY_NVTX", bool, False, "emit NVTX ranges per decoder layer and marks per kernel launch")

@@ -36,6 +36,28 @@ def test_activation_quantiser_is_bit_exact():
     assert codes[3, :8].tolist() == [0x17, 0x32, 0x54, 0x76, 0xA9, 0xCB, 0xED, 0x0F]
 
 
+@pytest.mark.parametrize("T,k,nt", [(1200, 2, 128), (300, 8, 128), (512, 4, 32), (256, 9, 128)])
+def test_token_driven_quantiser_writes_the_bytes_of_the_row_quantiser(T, k, nt):
+    """Batches of 2048 entries and more quantise each token once and copy the bytes to its k padded rows: same codes and
+    scales as the quantiser that works row by row."""
+    from mary_b200.ops import cuda, cuda_moe
+    torch.manual_seed(T)
+    E, H = 16, 1024
+    x = (torch.randn(T, H, device="cuda") * 2).bfloat16()
+    idx, _ = cuda.router_topk(torch.randn(T, E, device="cuda"), k, "softmax")
+    plan = cuda_moe.moe_plan(idx, E, nt)
+    assert T * k >= 2048
+    xq, sf = cuda_moe.quantize_entries(x, plan, k, identity=False)
+    wq, wsf, _ = cuda_moe.quantize_rows(x, nt=nt, src_of=plan.src_of, identity=False, rows=plan.max_rows)
+    torch.cuda.synchronize()
+    rows = plan.row_of.long()
+    assert (rows >= 0).all() and torch.equal(xq[rows], wq[rows])
+    a = unswizzle_scales(sf.cpu(), sf.shape[0] * 128, H // 16).view(-1, 128, H // 16)
+    b = unswizzle_scales(wsf.cpu(), wsf.shape[0] * 128, H // 16).view(-1, 128, H // 16)
+    rr = rows.cpu()
+    assert torch.equal(a[rr // nt, rr % nt], b[rr // nt, rr % nt])
+
+
 @pytest.mark.parametrize("E,H,F,T,k,nt", [(4, 512, 256, 24, 2, 32), (16, 1024, 512, 200, 4, 32), (8, 512, 256, 700, 2, 128),
                                           (8, 1024, 256, 3, 2, 32)])
 def test_moe_pipeline_matches_oracle(E, H, F, T, k, nt):
