@@ -1,0 +1,438 @@
+// Training-path kernels of the LoRA fine-tuning step (forward AND backward of the element-wise pieces, and the adapter weight
+// gradients), all bf16 in memory and f32 in registers.  The reference trains with burn's autodiff over its own ops
+// (src/bin/gemma_train_lora.rs:259-319, adapter math src/models/gemma/lora.rs:413-428); here every piece is one launch:
+//
+//   rmsnorm_train_fwd / _bwd   out = (res + x * rstd(x) * w) * alpha        (w, res optional; frozen w: no weight gradient)
+//   geglu_train_fwd / _bwd     out = gelu_tanh(g) * u over gu = [g | u]
+//   qkv_norm_rope_fwd / _bwd   per-head RMS norm (q, k with gains, v without) followed by the split-half rotation of q and k
+//   lora_wgrad                 out[r, c] = sum_m small[m, r] * big[m, c]    (dA = (dL/du)^T x and dB^T = (s u)^T dy, r <= 48)
+//
+// Every pointer comes with its row pitch, so that producers write straight into the widened buffers of the adapter GEMMs
+// ([x | s u] and [dy | dL/du]) and no concatenation copy exists.
+#include "common.cuh"
+#include "host_utils.h"
+
+namespace {
+using namespace mary;
+
+__device__ __forceinline__ void ld8(const __nv_bfloat16* p, float* f) {
+  const uint4 v = *(const uint4*)p;
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { const float2 a = __bfloat1622float2(h[j]); f[2 * j] = a.x; f[2 * j + 1] = a.y; }
+}
+__device__ __forceinline__ void st8(__nv_bfloat16* p, const float* f) {
+  uint4 v;
+  __nv_bfloat162* h = (__nv_bfloat162*)&v;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+  *(uint4*)p = v;
+}
+
+// N consecutive bf16 values (N = 1, 2, 4 or 8; the address is a multiple of 2 N bytes)
+template <int N>
+__device__ __forceinline__ void ldn(const __nv_bfloat16* p, float* f) {
+  if (N == 1) { f[0] = __bfloat162float(*p); return; }
+  if (N == 8) { ld8(p, f); return; }
+  if (N == 4) {
+    const uint2 v = *(const uint2*)p;
+    const __nv_bfloat162* h = (const __nv_bfloat162*)&v;
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    return;
+  }
+  const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)p);
+  f[0] = a.x; f[1] = a.y;
+}
+template <int N>
+__device__ __forceinline__ void stn(__nv_bfloat16* p, const float* f) {
+  if (N == 1) { *p = __float2bfloat16(f[0]); return; }
+  if (N == 8) { st8(p, f); return; }
+  if (N == 4) {
+    uint2 v;
+    __nv_bfloat162* h = (__nv_bfloat162*)&v;
+    h[0] = __floats2bfloat162_rn(f[0], f[1]); h[1] = __floats2bfloat162_rn(f[2], f[3]);
+    *(uint2*)p = v;
+    return;
+  }
+  *(__nv_bfloat162*)p = __floats2bfloat162_rn(f[0], f[1]);
+}
+
+// sum over the CTA (blockDim.x <= 1024, a multiple of 32); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[w] = v;
+  __syncthreads();
+  float t = (int)threadIdx.x < nw ? red[threadIdx.x] : 0.f;
+  if (w == 0) { t = warp_sum(t); if (threadIdx.x == 0) red[0] = t; }
+  __syncthreads();
+  return red[0];
+}
+
+// ----------------------------------------------------------------------------- RMS norm over rows of width H (H % 8 == 0)
+// one CTA per row; the row stays in registers between the reduction and the write (H <= 8 * 8 * blockDim.x)
+constexpr int RN_MAX = 4;   // 8-element chunks per thread
+
+__global__ void rmsnorm_train_fwd_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
+                                         const __nv_bfloat16* __restrict__ res, int64_t ldr, float alpha, float eps,
+                                         __nv_bfloat16* __restrict__ out, int64_t ldo, int H) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * ldx;
+  float v[RN_MAX][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_MAX; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < H) {
+      ld8(xr + c, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < RN_MAX; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < H) {
+      float g[8], r[8], o[8];
+      if (w) ld8(w + c, g);
+      if (res) ld8(res + row * ldr + c, r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float y = v[i][j] * rstd;
+        if (w) y *= g[j];
+        if (res) y += r[j];
+        o[j] = y * alpha;
+      }
+      st8(out + row * ldo + c, o);
+    }
+  }
+}
+
+// dx = alpha * rstd * (g - xhat * mean(g * xhat)),  g = dy * w,  xhat = x * rstd  (rstd recomputed from x)
+// d_res (optional) = alpha * dy
+__global__ void rmsnorm_train_bwd_kernel(const __nv_bfloat16* __restrict__ dy, int64_t ldy, const __nv_bfloat16* __restrict__ x, int64_t ldx,
+                                         const __nv_bfloat16* __restrict__ w, float alpha, float eps, __nv_bfloat16* __restrict__ dx,
+                                         int64_t lddx, __nv_bfloat16* __restrict__ dres, int64_t lddr, int H) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  float xv[RN_MAX][8], gv[RN_MAX][8];
+  float ss = 0.f, sg = 0.f;
+#pragma unroll
+  for (int i = 0; i < RN_MAX; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < H) {
+      float g[8];
+      ld8(x + row * ldx + c, xv[i]);
+      ld8(dy + row * ldy + c, gv[i]);
+      if (dres) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = gv[i][j] * alpha;
+        st8(dres + row * lddr + c, o);
+      }
+      if (w) ld8(w + c, g);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (w) gv[i][j] *= g[j];
+        ss = fmaf(xv[i][j], xv[i][j], ss);
+        sg = fmaf(gv[i][j], xv[i][j], sg);
+      }
+    }
+  }
+  ss = block_sum(ss, red);
+  sg = block_sum(sg, red);
+  const float rstd = rsqrtf(ss / (float)H + eps);
+  const float k = sg * rstd * rstd / (float)H;        // mean(g * xhat) * rstd
+#pragma unroll
+  for (int i = 0; i < RN_MAX; ++i) {
+    const int c = (i * blockDim.x + threadIdx.x) * 8;
+    if (c < H) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = alpha * rstd * (gv[i][j] - xv[i][j] * k);
+      st8(dx + row * lddx + c, o);
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------- GeGLU (tanh form)
+__device__ __forceinline__ void gelu_tanh_and_grad(float x, float* val, float* grad) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float t = tanhf(k0 * (x + k1 * x * x * x));
+  *val = 0.5f * x * (1.0f + t);
+  *grad = 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k0 * (1.0f + 3.0f * k1 * x * x);
+}
+
+__global__ void geglu_train_fwd_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg, __nv_bfloat16* __restrict__ out, int64_t ldo, int F) {
+  const int64_t row = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= F) return;
+  float g[8], u[8], o[8];
+  ld8(gu + row * ldg + c, g);
+  ld8(gu + row * ldg + F + c, u);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) o[j] = gelu_tanh_f(g[j]) * u[j];
+  st8(out + row * ldo + c, o);
+}
+
+__global__ void geglu_train_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int64_t ldd, const __nv_bfloat16* __restrict__ gu, int64_t ldg,
+                                       __nv_bfloat16* __restrict__ dgu, int64_t lddg, int F) {
+  const int64_t row = blockIdx.y;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (c >= F) return;
+  float g[8], u[8], d[8], dg[8], du[8];
+  ld8(gu + row * ldg + c, g);
+  ld8(gu + row * ldg + F + c, u);
+  ld8(dout + row * ldd + c, d);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float val, grad;
+    gelu_tanh_and_grad(g[j], &val, &grad);
+    dg[j] = d[j] * u[j] * grad;
+    du[j] = d[j] * val;
+  }
+  st8(dgu + row * lddg + c, dg);
+  st8(dgu + row * lddg + F + c, du);
+}
+
+// ----------------------------------------------------------------------------- per-head norm + rotation of a fused q | k | v row
+// one warp per (token, head); head dim D = 8 * 32 * CH / ... : every lane holds D / 32 values as pairs (i, i + D / 2) so that the
+// rotation needs no exchange: lane l holds elements [l * D/64, (l + 1) * D/64) of each half.
+template <int D, bool BWD>
+__global__ void qkv_norm_rope_kernel(const __nv_bfloat16* __restrict__ in, int64_t ldi, const __nv_bfloat16* __restrict__ x, int64_t ldx,
+                                     const int* __restrict__ pos, const float* __restrict__ inv_freq, const __nv_bfloat16* __restrict__ qw,
+                                     const __nv_bfloat16* __restrict__ kw, float eps, __nv_bfloat16* __restrict__ out, int64_t ldo, int n_q,
+                                     int n_kv, int64_t n_rows) {
+  constexpr int PER = D / 64;                     // values per lane and half
+  const int heads = n_q + 2 * n_kv;
+  const int64_t wid = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= n_rows * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int64_t t = wid / heads;
+  const int h = (int)(wid % heads);
+  const bool is_v = h >= n_q + n_kv;
+  const __nv_bfloat16* gain = h < n_q ? qw : (is_v ? nullptr : kw);
+  const int c0 = h * D + lane * PER;
+  float a[PER], b[PER], ga[PER], gb[PER], cs[PER], sn[PER];
+  if (gain) { ldn<PER>(gain + lane * PER, ga); ldn<PER>(gain + D / 2 + lane * PER, gb); }
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    if (!gain) { ga[j] = 1.f; gb[j] = 1.f; }
+    if (!is_v) {
+      const float ang = (float)pos[t] * inv_freq[lane * PER + j];
+      sincosf(ang, &sn[j], &cs[j]);
+    } else { cs[j] = 1.f; sn[j] = 0.f; }
+  }
+  if (!BWD) {
+    // forward: in = raw projection row; out = rope(norm(in))
+    float ss = 0.f;
+    ldn<PER>(in + t * ldi + c0, a);
+    ldn<PER>(in + t * ldi + c0 + D / 2, b);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) ss = fmaf(a[j], a[j], fmaf(b[j], b[j], ss));
+    const float rstd = rsqrtf(warp_sum(ss) / (float)D + eps);
+    float o1[PER], o2[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      // the normed value is rounded to the storage type before it is rotated (two ops in the reference)
+      const float na = __bfloat162float(__float2bfloat16(a[j] * rstd * ga[j])), nb = __bfloat162float(__float2bfloat16(b[j] * rstd * gb[j]));
+      o1[j] = na * cs[j] - nb * sn[j];
+      o2[j] = na * sn[j] + nb * cs[j];
+    }
+    stn<PER>(out + t * ldo + c0, o1);
+    stn<PER>(out + t * ldo + c0 + D / 2, o2);
+  } else {
+    // backward: in = gradient of the rotated row, x = raw projection row; out = gradient of the raw row
+    float xa[PER], xb[PER], d1[PER], d2[PER];
+    float ss = 0.f, sg = 0.f;
+    ldn<PER>(in + t * ldi + c0, d1);
+    ldn<PER>(in + t * ldi + c0 + D / 2, d2);
+    ldn<PER>(x + t * ldx + c0, xa);
+    ldn<PER>(x + t * ldx + c0 + D / 2, xb);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      a[j] = (d1[j] * cs[j] + d2[j] * sn[j]) * ga[j];            // transpose of the rotation, then the gain
+      b[j] = (-d1[j] * sn[j] + d2[j] * cs[j]) * gb[j];
+      ss = fmaf(xa[j], xa[j], fmaf(xb[j], xb[j], ss));
+      sg = fmaf(a[j], xa[j], fmaf(b[j], xb[j], sg));
+    }
+    ss = warp_sum(ss);
+    sg = warp_sum(sg);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    const float k = sg * rstd * rstd / (float)D;
+    float o1[PER], o2[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      o1[j] = rstd * (a[j] - xa[j] * k);
+      o2[j] = rstd * (b[j] - xb[j] * k);
+    }
+    stn<PER>(out + t * ldo + c0, o1);
+    stn<PER>(out + t * ldo + c0 + D / 2, o2);
+  }
+}
+
+// ----------------------------------------------------------------------------- adapter weight gradients
+// ws[split, r, c] = sum over the split's rows m of small[m, r] * big[m, c], r < Rv <= R; 128 threads x CPT columns per CTA
+template <int R, int CPT>
+__global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __restrict__ small, int64_t lds, const __nv_bfloat16* __restrict__ big,
+                                                         int64_t ldb, int M, int C, int rows_per_split, float* __restrict__ ws, int Rv) {
+  __shared__ __align__(16) float sm[32][R];
+  const int c0 = (blockIdx.x * 128 + threadIdx.x) * CPT;
+  const int m_lo = blockIdx.y * rows_per_split, m_hi = min(M, m_lo + rows_per_split);
+  float acc[R][CPT];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) acc[r][j] = 0.f;
+  for (int m0 = m_lo; m0 < m_hi; m0 += 32) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 32 * R; i += 128) {
+      const int mi = i / R, r = i % R;
+      sm[mi][r] = (m0 + mi < m_hi && r < Rv) ? __bfloat162float(small[(int64_t)(m0 + mi) * lds + r]) : 0.f;
+    }
+    __syncthreads();
+    if (c0 < C) {
+      const int n = min(32, m_hi - m0);
+#pragma unroll 2
+      for (int mi = 0; mi < n; ++mi) {
+        float v[CPT];
+        const __nv_bfloat16* bp = big + (int64_t)(m0 + mi) * ldb + c0;
+        if (CPT == 8) ld8(bp, v);
+        else {
+#pragma unroll
+          for (int j = 0; j < CPT; j += 2) { const float2 f = __bfloat1622float2(*(const __nv_bfloat162*)(bp + j)); v[j] = f.x; v[j + 1] = f.y; }
+        }
+#pragma unroll
+        for (int r4 = 0; r4 < R; r4 += 4) {
+          const float4 s = *(const float4*)&sm[mi][r4];
+#pragma unroll
+          for (int j = 0; j < CPT; ++j) {
+            acc[r4][j] = fmaf(s.x, v[j], acc[r4][j]);
+            acc[r4 + 1][j] = fmaf(s.y, v[j], acc[r4 + 1][j]);
+            acc[r4 + 2][j] = fmaf(s.z, v[j], acc[r4 + 2][j]);
+            acc[r4 + 3][j] = fmaf(s.w, v[j], acc[r4 + 3][j]);
+          }
+        }
+      }
+    }
+  }
+  if (c0 < C) {
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (r < Rv) {
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) ws[((int64_t)blockIdx.y * Rv + r) * C + c0 + j] = acc[r][j];
+      }
+  }
+}
+
+// out[r, c] = sum over splits of ws[split, r, c]
+__global__ void lora_wgrad_reduce_kernel(const float* __restrict__ ws, int splits, int64_t n, float* __restrict__ out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.f;
+  for (int k = 0; k < splits; ++k) s += ws[(int64_t)k * n + i];
+  out[i] = s;
+}
+}  // namespace
+
+static inline int rn_threads(int H) {
+  int t = (H / 8 + RN_MAX - 1) / RN_MAX;
+  t = (t + 31) / 32 * 32;
+  return t < 32 ? 32 : t;
+}
+
+MARY_API int mary_rmsnorm_train_fwd(const void* x, int64_t ldx, const void* w, const void* res, int64_t ldr, float alpha, float eps, void* out,
+                                    int64_t ldo, int64_t rows, int H, cudaStream_t s) {
+  if (rows <= 0) return MARY_OK;
+  if ((H & 7) || (ldx & 7) || (ldo & 7) || (res && (ldr & 7)) || H > 8 * RN_MAX * 1024) return MARY_ERR_BAD_ARG;
+  rmsnorm_train_fwd_kernel<<<(unsigned)rows, rn_threads(H), 0, s>>>((const __nv_bfloat16*)x, ldx, (const __nv_bfloat16*)w, (const __nv_bfloat16*)res,
+                                                                   ldr, alpha, eps, (__nv_bfloat16*)out, ldo, H);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_rmsnorm_train_bwd(const void* dy, int64_t ldy, const void* x, int64_t ldx, const void* w, float alpha, float eps, void* dx,
+                                    int64_t lddx, void* dres, int64_t lddr, int64_t rows, int H, cudaStream_t s) {
+  if (rows <= 0) return MARY_OK;
+  if ((H & 7) || (ldx & 7) || (ldy & 7) || (lddx & 7) || (dres && (lddr & 7)) || H > 8 * RN_MAX * 1024) return MARY_ERR_BAD_ARG;
+  rmsnorm_train_bwd_kernel<<<(unsigned)rows, rn_threads(H), 0, s>>>((const __nv_bfloat16*)dy, ldy, (const __nv_bfloat16*)x, ldx,
+                                                                   (const __nv_bfloat16*)w, alpha, eps, (__nv_bfloat16*)dx, lddx,
+                                                                   (__nv_bfloat16*)dres, lddr, H);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_geglu_train_fwd(const void* gu, int64_t ldg, void* out, int64_t ldo, int64_t rows, int F, cudaStream_t s) {
+  if (rows <= 0) return MARY_OK;
+  if ((F & 7) || (ldg & 7) || (ldo & 7) || rows > 65535) return MARY_ERR_BAD_ARG;
+  const dim3 grid((F / 8 + 255) / 256, (unsigned)rows);
+  geglu_train_fwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)out, ldo, F);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+MARY_API int mary_geglu_train_bwd(const void* dout, int64_t ldd, const void* gu, int64_t ldg, void* dgu, int64_t lddg, int64_t rows, int F,
+                                  cudaStream_t s) {
+  if (rows <= 0) return MARY_OK;
+  if ((F & 7) || (ldg & 7) || (ldd & 7) || (lddg & 7) || rows > 65535) return MARY_ERR_BAD_ARG;
+  const dim3 grid((F / 8 + 255) / 256, (unsigned)rows);
+  geglu_train_bwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dout, ldd, (const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)dgu, lddg, F);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// bwd == 0: out = rope(norm(in)); bwd != 0: in = gradient of the output, x = the forward's input, out = gradient of that input
+MARY_API int mary_qkv_norm_rope_train(const void* in, int64_t ldi, const void* x, int64_t ldx, const int* pos, const float* inv_freq,
+                                      const void* qw, const void* kw, float eps, void* out, int64_t ldo, int n_q, int n_kv, int D,
+                                      int64_t rows, int bwd, cudaStream_t s) {
+  if (rows <= 0) return MARY_OK;
+  if ((D != 64 && D != 128 && D != 256 && D != 512) || n_q < 1 || n_kv < 1 || (bwd && !x) || (ldi & 7) || (ldo & 7) || (bwd && (ldx & 7))) return MARY_ERR_BAD_ARG;
+  const int64_t warps = rows * (n_q + 2 * n_kv);
+  const unsigned grid = (unsigned)((warps + 7) / 8);
+#define QNR(D_)                                                                                                                             \
+  if (bwd) qkv_norm_rope_kernel<D_, true><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, ldi, (const __nv_bfloat16*)x, ldx, pos, inv_freq,   \
+                                                               (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, eps, (__nv_bfloat16*)out, \
+                                                               ldo, n_q, n_kv, rows);                                                       \
+  else qkv_norm_rope_kernel<D_, false><<<grid, 256, 0, s>>>((const __nv_bfloat16*)in, ldi, (const __nv_bfloat16*)x, ldx, pos, inv_freq,      \
+                                                            (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, eps, (__nv_bfloat16*)out,    \
+                                                            ldo, n_q, n_kv, rows)
+  if (D == 64) { QNR(64); } else if (D == 128) { QNR(128); } else if (D == 256) { QNR(256); } else { QNR(512); }
+#undef QNR
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// out[R, C] (f32) = small[M, R]^T big[M, C], 1 <= R <= 48; ws: scratch of mary_lora_wgrad_splits(M, C, R) * R * C floats
+MARY_API int mary_lora_wgrad_splits(int M, int C, int R) {
+  const int cpt = R <= 16 ? 8 : (R <= 32 ? 4 : 2);
+  const int slabs = (C + 128 * cpt - 1) / (128 * cpt);
+  int splits = (2 * mary_num_sms() + slabs - 1) / slabs;
+  const int max_splits = (M + 31) / 32;
+  if (splits > max_splits) splits = max_splits;
+  if (splits > 64) splits = 64;
+  return splits < 1 ? 1 : splits;
+}
+
+MARY_API int mary_lora_wgrad(const void* small, int64_t lds, const void* big, int64_t ldb, int M, int R, int C, float* ws, float* out,
+                             cudaStream_t s) {
+  if (M <= 0 || C <= 0) return MARY_OK;
+  if (R < 1 || R > 48 || (C & 7) || (ldb & 7)) return MARY_ERR_BAD_ARG;
+  const int splits = mary_lora_wgrad_splits(M, C, R);
+  int rps = (M + splits - 1) / splits;
+  rps = (rps + 31) / 32 * 32;
+  const int cpt = R <= 16 ? 8 : (R <= 32 ? 4 : 2);
+  const dim3 grid((C + 128 * cpt - 1) / (128 * cpt), splits);
+  if (R <= 16) lora_wgrad_kernel<16, 8><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+  else if (R <= 32) lora_wgrad_kernel<32, 4><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+  else lora_wgrad_kernel<48, 2><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+  MARY_CHECK_LAUNCH();
+  const int64_t n = (int64_t)R * C;
+  lora_wgrad_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ws, splits, n, out);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}

@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--checkpoint", action="store_true", help="recompute each layer in the backward pass (activation checkpointing)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size; the world is (world / tp) data-parallel replicas of tp ranks each")
+    ap.add_argument("--kernel-table", action="store_true", help="after the timed steps run one more step under torch.profiler and print "
+                    "the 30 kernels with the largest device time (shares only: times under a profiler are not benchmark values)")
     a = ap.parse_args()
     from ..models.gemma4 import Gemma4Model, gemma_12b_config
     from ..models.gemma4.weights import init_random_
@@ -99,6 +101,12 @@ def main():
                           "ms_per_step": round(ms, 2), "loss": round(loss, 4), "layers": a.layers, "comm": a.comm if world > 1 else "none",
                           "overlap": not a.no_overlap, "checkpointing": a.checkpoint, "gpu_launches_per_step": K.LAUNCHES // a.steps,
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1), "kernel_status": K.last_status()}))
+    if a.kernel_table and rank == 0:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            tr.step(ids)
+            torch.cuda.synchronize()
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=30, max_name_column_width=90))
     if world > 1:
         dist.destroy_process_group()
 

@@ -153,13 +153,37 @@ class LoraWeights(nn.Module):
 class Gemma4LoraForward(nn.Module):
     """Training forward of the Gemma-4 decoder over whole sequences ``ids[B, S]`` with frozen base weights.
 
-    The base projections run through the hand-written GEMM (``linear_frozen``: forward and input-gradient); norms, RoPE and
-    the causal (sliding-window) attention are differentiable PyTorch code, the adapters plain autograd parameters."""
+    Every linear layer is a ``train_ops.LoraLinear`` (the adapters folded into the base GEMMs, forward and backward on the
+    hand-written GEMM, weight gradients by a streaming kernel); norms, the q / k / v head norm with rotation and GeGLU are
+    ``train_ops`` functions with a forward and a backward kernel each; the attention itself is PyTorch's fused causal attention.
+    The widened operands REPLACE the model's own weight storage (the parameters become views of them)."""
 
     def __init__(self, model, lora: LoraWeights):
         super().__init__()
+        from ..ops.train_ops import LoraLinear
         self.model, self.lora = model, lora
         self._wt: dict[int, torch.Tensor] = {}
+        self._flash = None                     # None: not tried yet; True / False: the flash-attention library works / does not
+        self.fused: list[dict] = []
+        s = lora.alpha / lora.rank
+        for i, L in enumerate(model.layers):
+            if L.kv_source is not None or L.moe or L.ple:
+                raise NotImplementedError("LoRA training of decoders with KV-shared layers, a routed-expert block or per-layer embeddings is not built")
+            ad = lambda p: lora.get(i, p)  # noqa: E731
+            nq, nkv, F = L.n_q * L.D, L.n_kv * L.D, L.F
+            f = {"qkv": LoraLinear(L.w_qkv, [(ad("q_proj"), 0, nq), (ad("k_proj"), nq, nkv), (ad("v_proj"), nq + nkv, nkv)], s),
+                 "o": LoraLinear(L.w_o, [(ad("o_proj"), 0, L.w_o.shape[0])], s),
+                 "gu": LoraLinear(L.w_gu, [(ad("gate_proj"), 0, F), (ad("up_proj"), F, F)], s),
+                 "down": LoraLinear(L.w_down, [(ad("down_proj"), 0, L.w_down.shape[0])], s)}
+            for name, key in (("w_qkv", "qkv"), ("w_o", "o"), ("w_gu", "gu"), ("w_down", "down")):
+                getattr(L, name).data = f[key].base_view()          # one copy of every base weight stays alive
+            self.fused.append(f)
+
+    def refresh(self):
+        """Copy the adapters' master parameters into the widened GEMM operands (after every optimiser step)."""
+        for f in self.fused:
+            for m in f.values():
+                m.refresh()
 
     def _lin(self, x, w):
         wt = self._wt.get(id(w))
@@ -174,6 +198,20 @@ class Gemma4LoraForward(nn.Module):
         tokens) can only see keys of chunks ``c - 1`` and ``c``, so the scores are ``[W, 2W]`` blocks instead of ``[S, S]``."""
         B, Sq, Hq, D = q.shape
         g = Hq // k.shape[2]
+        if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and self._flash is not False:
+            # the flash-attention library where the machine has it: grouped heads and the sliding window natively, forward and
+            # backward on tensor cores (PyTorch's fused attention refuses masks together with grouped heads and falls back to
+            # f32 matrix products for the sliding layers)
+            try:
+                from flash_attn import flash_attn_func
+                o = flash_attn_func(q, k, v, softmax_scale=1.0, causal=True,
+                                    window_size=(window - 1, 0) if window and window < Sq else (-1, -1))
+                self._flash = True
+                return o
+            except Exception:
+                if self._flash:
+                    raise
+                self._flash = False
         qt = q.transpose(1, 2)
         kt, vt = k.transpose(1, 2), v.transpose(1, 2)
         sdpa = torch.nn.functional.scaled_dot_product_attention
@@ -191,61 +229,43 @@ class Gemma4LoraForward(nn.Module):
         return torch.cat(outs, 2).transpose(1, 2)
 
     def _layer(self, i, h, pos, B, Sq):
+        """``h [B * Sq, H]`` -> the residual stream after layer ``i``."""
+        from ..ops import train_ops as T
         m, c = self.model, self.model.cfg
-        L = m.layers[i]
-        if L.kv_source is not None or L.moe or L.ple:
-            raise NotImplementedError("LoRA training of decoders with KV-shared layers, a routed-expert block or per-layer embeddings is not built")
-        ad = lambda p: self.lora.get(i, p)  # noqa: E731
+        L, f = m.layers[i], self.fused[i]
+        eps = c.rms_norm_eps
+        nq, nkv, D = L.n_q * L.D, L.n_kv * L.D, L.D
         # tensor parallel: the normed activation enters the sharded region (its gradient is summed over the group), the partial
         # sums of the row-parallel projections leave it through the group reduction
-        x = copy_to_tp(ref.rmsnorm(h, L.ln_in.detach(), c.rms_norm_eps), m.tp)
-        qkv = self._lin(x, L.w_qkv)
-        nq, nkv, D = L.n_q * L.D, L.n_kv * L.D, L.D
-        deltas = [ad(p)(x) if ad(p) is not None else None for p in ("q_proj", "k_proj", "v_proj")]
+        x = copy_to_tp(T.rmsnorm(h, L.ln_in, eps, out_extra=f["qkv"].R), m.tp)
+        qkv = f["qkv"](x)
+        qkv = T.qkv_norm_rope(qkv, pos, L.inv_freq, L.q_norm, L.k_norm, eps, L.n_q, L.n_kv, D, grad_extra=f["qkv"].R)
         q, k, v = qkv.split([nq, nkv, nkv], -1)
-        q = q + deltas[0] if deltas[0] is not None else q
-        k = k + deltas[1] if deltas[1] is not None else k
-        v = v + deltas[2] if deltas[2] is not None else v
-        q = ref.rmsnorm(q.reshape(B * Sq, L.n_q, D), L.q_norm.detach(), c.rms_norm_eps)
-        k = ref.rmsnorm(k.reshape(B * Sq, L.n_kv, D), L.k_norm.detach(), c.rms_norm_eps)
-        v = ref.rmsnorm(v.reshape(B * Sq, L.n_kv, D), None, c.rms_norm_eps)
-        q, k = ref.rope(q, pos, L.inv_freq), ref.rope(k, pos, L.inv_freq)
         o = self._attn(q.view(B, Sq, L.n_q, D), k.view(B, Sq, L.n_kv, D), v.view(B, Sq, L.n_kv, D), L.window)
-        o = o.reshape(B, Sq, nq)
-        a = self._lin(o, L.w_o)
-        if ad("o_proj") is not None:
-            a = a + ad("o_proj")(o)
-        a = reduce_from_tp(a, m.tp)
-        h = h + ref.rmsnorm(a, L.ln_post_attn.detach(), c.rms_norm_eps)
-        x = copy_to_tp(ref.rmsnorm(h, L.ln_pre_ffn.detach(), c.rms_norm_eps), m.tp)
-        gu = self._lin(x, L.w_gu)
-        g_, u_ = gu[..., :L.F], gu[..., L.F:]
-        if ad("gate_proj") is not None:
-            g_ = g_ + ad("gate_proj")(x)
-        if ad("up_proj") is not None:
-            u_ = u_ + ad("up_proj")(x)
-        mm = ref.geglu(g_, u_)
-        d = self._lin(mm, L.w_down)
-        if ad("down_proj") is not None:
-            d = d + ad("down_proj")(mm)
-        d = reduce_from_tp(d, m.tp)
-        return (h + ref.rmsnorm(d, L.ln_post_ffn.detach(), c.rms_norm_eps)) * L.layer_scalar
+        a = reduce_from_tp(f["o"](o.reshape(B * Sq, nq)), m.tp)
+        h = T.rmsnorm(a, L.ln_post_attn, eps, res=h)
+        x = copy_to_tp(T.rmsnorm(h, L.ln_pre_ffn, eps, out_extra=f["gu"].R), m.tp)
+        gu = f["gu"](x)
+        mm = T.geglu(gu, out_extra=f["down"].R, grad_extra=f["gu"].R)
+        d = reduce_from_tp(f["down"](mm), m.tp)
+        return T.rmsnorm(d, L.ln_post_ffn, eps, res=h, alpha=float(L.layer_scalar))
 
     def forward(self, ids):
         """``checkpoint = True`` keeps only every layer's input for the backward pass and recomputes the layer there: the
         activations of a 4096-token sequence through 48 layers otherwise take on the order of 100 GB."""
         m, c = self.model, self.model.cfg
         B, Sq = ids.shape
-        h = (m.embed.detach()[ids.long()].float() * m.embed_scale).to(m.dtype)
-        pos = torch.arange(Sq, device=ids.device).repeat(B)
+        self.refresh()
+        h = (m.embed.detach()[ids.long()].float() * m.embed_scale).to(m.dtype).view(B * Sq, -1)
+        pos = torch.arange(Sq, device=ids.device, dtype=torch.int32).repeat(B)
         for i in range(len(m.layers)):
             if getattr(self, "checkpoint", False) and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
                 h = checkpoint(self._layer, i, h, pos, B, Sq, use_reentrant=False)
             else:
                 h = self._layer(i, h, pos, B, Sq)
-        x = ref.rmsnorm(h, m.norm.detach(), c.rms_norm_eps)
-        return x
+        from ..ops import train_ops as T
+        return T.rmsnorm(h, m.norm, c.rms_norm_eps).view(B, Sq, -1)
 
     def loss(self, ids, chunk: int = 1024):
         """Mean next-token cross-entropy (labels = ids shifted by one); the vocabulary projection is chunked over tokens so
