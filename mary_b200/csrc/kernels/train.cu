@@ -330,6 +330,108 @@ __global__ void __launch_bounds__(128) lora_wgrad_kernel(const __nv_bfloat16* __
   }
 }
 
+// The same product on the tensor cores (mma.sync m16n8k16, bf16 in, f32 out): the contraction runs over the TOKENS, which is
+// the strided dimension of both operands, so both fragments are read with ldmatrix.trans from row-major shared tiles.  The
+// kernel is bound by streaming `big` once; tcgen05 would need both operands MN-major and brings nothing at 16-48 output rows.
+//   CTA: 128 threads, 256 columns (64 per warp = 8 n-tiles), rows of its split in chunks of 32 (two k-steps)
+//   RT: 16-row tiles of the output (Rv <= 16 RT, Rv % 8 == 0)
+constexpr int WG_COLS = 256, WG_KT = 32;
+constexpr int WG_BPITCH = WG_COLS * 2 + 16;     // bytes; the 16 spreads the 8 rows of an ldmatrix over the banks
+constexpr int WG_SPITCH = 48 * 2 + 16;
+
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int RT>
+__global__ void __launch_bounds__(128) lora_wgrad_tc_kernel(const __nv_bfloat16* __restrict__ small, int64_t lds,
+                                                            const __nv_bfloat16* __restrict__ big, int64_t ldb, int M, int C,
+                                                            int rows_per_split, float* __restrict__ ws, int Rv) {
+  __shared__ __align__(16) uint8_t sb[WG_KT * WG_BPITCH];
+  __shared__ __align__(16) uint8_t ss[WG_KT * WG_SPITCH];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int col0 = blockIdx.x * WG_COLS;
+  const int m_lo = blockIdx.y * rows_per_split, m_hi = min(M, m_lo + rows_per_split);
+  float acc[RT][8][4];
+#pragma unroll
+  for (int a = 0; a < RT; ++a)
+#pragma unroll
+    for (int n = 0; n < 8; ++n)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[a][n][j] = 0.f;
+  uint4 pb[8], ps[2];
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  auto fetch = [&](int m0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int id = i * 128 + tid, row = id >> 5, ch = id & 31;
+      const int m = m0 + row, c = col0 + ch * 8;
+      pb[i] = (m < m_hi && c < C) ? *(const uint4*)(big + (int64_t)m * ldb + c) : zero;
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int id = i * 128 + tid, row = id / (2 * RT), ch = id % (2 * RT);
+      const int m = m0 + row;
+      ps[i] = (id < WG_KT * 2 * RT && m < m_hi && ch * 8 < Rv) ? *(const uint4*)(small + (int64_t)m * lds + ch * 8) : zero;
+    }
+  };
+  fetch(m_lo);
+  const uint32_t sb_u = smem_u32(sb), ss_u = smem_u32(ss);
+  for (int m0 = m_lo; m0 < m_hi; m0 += WG_KT) {
+    __syncthreads();                                   // the previous chunk's fragments have been read
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int id = i * 128 + tid, row = id >> 5, ch = id & 31;
+      *(uint4*)(sb + row * WG_BPITCH + ch * 16) = pb[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int id = i * 128 + tid, row = id / (2 * RT), ch = id % (2 * RT);
+      if (id < WG_KT * 2 * RT) *(uint4*)(ss + row * WG_SPITCH + ch * 16) = ps[i];
+    }
+    __syncthreads();
+    if (m0 + WG_KT < m_hi) fetch(m0 + WG_KT);          // the next chunk travels while this one is multiplied
+#pragma unroll
+    for (int ks = 0; ks < WG_KT / 16; ++ks) {
+      uint32_t a[RT][4];
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        // matrices: (r0, k0) (r0 + 8, k0) (r0, k0 + 8) (r0 + 8, k0 + 8), each the transpose of ss[k .. k + 8][r .. r + 8]
+        const int mrow = ks * 16 + (lane >> 4) * 8 + (lane & 7), rcol = rt * 16 + ((lane >> 3) & 1) * 8;
+        ldsm_x4_trans(ss_u + mrow * WG_SPITCH + rcol * 2, a[rt][0], a[rt][1], a[rt][2], a[rt][3]);
+      }
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        // matrices: (k0, c0) (k0 + 8, c0) (k0, c0 + 8) (k0 + 8, c0 + 8): b0, b1 of two neighbouring n-tiles
+        const int mrow = ks * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), ccol = warp * 64 + np * 16 + (lane >> 4) * 8;
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_trans(sb_u + mrow * WG_BPITCH + ccol * 2, b0, b1, b2, b3);
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+          mma_bf16_16816(acc[rt][2 * np], a[rt], b0, b1);
+          mma_bf16_16816(acc[rt][2 * np + 1], a[rt], b2, b3);
+        }
+      }
+    }
+  }
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int c = col0 + warp * 64 + n * 8 + 2 * t;
+      if (c < C) {
+        const int r0 = rt * 16 + g, r1 = r0 + 8;
+        if (r0 < Rv) *(float2*)(ws + ((int64_t)blockIdx.y * Rv + r0) * C + c) = make_float2(acc[rt][n][0], acc[rt][n][1]);
+        if (r1 < Rv) *(float2*)(ws + ((int64_t)blockIdx.y * Rv + r1) * C + c) = make_float2(acc[rt][n][2], acc[rt][n][3]);
+      }
+    }
+}
+
 // out[r, c] = sum over splits of ws[split, r, c]
 __global__ void lora_wgrad_reduce_kernel(const float* __restrict__ ws, int splits, int64_t n, float* __restrict__ out) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -407,11 +509,17 @@ MARY_API int mary_qkv_norm_rope_train(const void* in, int64_t ldi, const void* x
   return MARY_OK;
 }
 
-// out[R, C] (f32) = small[M, R]^T big[M, C], 1 <= R <= 48; ws: scratch of mary_lora_wgrad_splits(M, C, R) * R * C floats
+// out[R, C] (f32) = small[M, R]^T big[M, C], 1 <= R <= 48; ws: scratch of mary_lora_wgrad_splits(M, C, R) * R * C floats.
+// R % 8 == 0 with 16-byte aligned operands takes the tensor-core kernel, anything else the SIMT one.
+static inline bool wgrad_tc_ok(const void* small, int64_t lds, const void* big, int R) {
+  return (R & 7) == 0 && (lds & 7) == 0 && ((uintptr_t)small & 15) == 0 && ((uintptr_t)big & 15) == 0;
+}
+
 MARY_API int mary_lora_wgrad_splits(int M, int C, int R) {
   const int cpt = R <= 16 ? 8 : (R <= 32 ? 4 : 2);
-  const int slabs = (C + 128 * cpt - 1) / (128 * cpt);
-  int splits = (2 * mary_num_sms() + slabs - 1) / slabs;
+  const int per_cta = (R & 7) == 0 ? WG_COLS : 128 * cpt;
+  const int slabs = (C + per_cta - 1) / per_cta;
+  int splits = (((R & 7) == 0 ? 4 : 2) * mary_num_sms() + slabs - 1) / slabs;
   const int max_splits = (M + 31) / 32;
   if (splits > max_splits) splits = max_splits;
   if (splits > 64) splits = 64;
@@ -425,11 +533,18 @@ MARY_API int mary_lora_wgrad(const void* small, int64_t lds, const void* big, in
   const int splits = mary_lora_wgrad_splits(M, C, R);
   int rps = (M + splits - 1) / splits;
   rps = (rps + 31) / 32 * 32;
-  const int cpt = R <= 16 ? 8 : (R <= 32 ? 4 : 2);
-  const dim3 grid((C + 128 * cpt - 1) / (128 * cpt), splits);
-  if (R <= 16) lora_wgrad_kernel<16, 8><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
-  else if (R <= 32) lora_wgrad_kernel<32, 4><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
-  else lora_wgrad_kernel<48, 2><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+  if (wgrad_tc_ok(small, lds, big, R)) {
+    const dim3 grid((C + WG_COLS - 1) / WG_COLS, splits);
+    if (R <= 16) lora_wgrad_tc_kernel<1><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+    else if (R <= 32) lora_wgrad_tc_kernel<2><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+    else lora_wgrad_tc_kernel<3><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+  } else {
+    const int cpt = R <= 16 ? 8 : (R <= 32 ? 4 : 2);
+    const dim3 grid((C + 128 * cpt - 1) / (128 * cpt), splits);
+    if (R <= 16) lora_wgrad_kernel<16, 8><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+    else if (R <= 32) lora_wgrad_kernel<32, 4><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+    else lora_wgrad_kernel<48, 2><<<grid, 128, 0, s>>>((const __nv_bfloat16*)small, lds, (const __nv_bfloat16*)big, ldb, M, C, rps, ws, R);
+  }
   MARY_CHECK_LAUNCH();
   const int64_t n = (int64_t)R * C;
   lora_wgrad_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ws, splits, n, out);

@@ -148,11 +148,17 @@ def test_lora_linear_equals_base_plus_adapters_with_all_gradients(device, n_ad, 
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("R,C,M", [(16, 3840, 4096), (32, 1032, 517), (48, 8192, 1000), (24, 512, 100), (96, 256, 300)])
+@pytest.mark.parametrize("R,C,M", [(16, 3840, 4096), (32, 1032, 517), (48, 8192, 1000), (24, 512, 100), (96, 256, 300), (8, 264, 31),
+                                   (20, 512, 333), (3, 1024, 64)])
 def test_adapter_weight_gradient_kernel(R, C, M):
+    """Ranks that are a multiple of 8 take the tensor-core kernel (operands as column slices of one wide buffer, as the adapter
+    layers pass them), the others the SIMT kernel."""
     torch.manual_seed(R)
-    buf = torch.randn(M, C + R, device="cuda").bfloat16()
-    small, big = buf[:, C:], buf[:, :C]
+    if R % 8 == 0:
+        buf = torch.randn(M, C + R, device="cuda").bfloat16()
+        small, big = buf[:, C:], buf[:, :C]
+    else:
+        small, big = torch.randn(M, R, device="cuda").bfloat16(), torch.randn(M, C, device="cuda").bfloat16()
     got = T.lora_wgrad(small, big)
     want = small.double().t() @ big.double()
     assert (got.double() - want).abs().max().item() < 2e-3 * want.abs().max().item()
