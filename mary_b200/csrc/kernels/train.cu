@@ -432,6 +432,78 @@ __global__ void __launch_bounds__(128) lora_wgrad_tc_kernel(const __nv_bfloat16*
     }
 }
 
+// ----------------------------------------------------------------------------- soft-capped cross-entropy, loss and gradient
+// One CTA per row of logits [rows, V] (bf16): z = cap * tanh(l / cap) (cap <= 0: z = l); loss = logsumexp(z) - z[label];
+// the row is OVERWRITTEN with d loss / d l * scale = scale * (softmax(z) - onehot) * (1 - tanh^2).  Two passes over the row:
+// an online (max, sum) pass and the write pass, which finds the row in L2 (a row is 2 V bytes, the concurrently processed rows
+// of all SMs stay below the L2 size for vocabularies up to 400k).
+// tanh through exp: the fast-math tanh approximation (relative error near 1e-3) would move a soft-capped logit by 0.01 and more
+__device__ __forceinline__ float tanh_exp(float x) { return 1.f - __fdividef(2.f, __expf(2.f * x) + 1.f); }
+
+__device__ __forceinline__ void ms_merge(float& m, float& s, float m2, float s2) {
+  const float mn = fmaxf(m, m2);
+  if (mn == -INFINITY) return;                       // two empty partials: (-inf) - (-inf) would be NaN
+  s = s * __expf(m - mn) + s2 * __expf(m2 - mn);
+  m = mn;
+}
+
+__global__ void __launch_bounds__(1024) softcap_ce_kernel(__nv_bfloat16* __restrict__ logits, int64_t ld, const int64_t* __restrict__ labels,
+                                                          int V, float cap, float scale, float* __restrict__ loss) {
+  __shared__ float red_m[32], red_s[32];
+  __shared__ float sh_lse, sh_zy;
+  const int64_t row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  const int label = (int)labels[row];
+  float m = -INFINITY, sum = 0.f;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    float v[8];
+    ld8(lr + c, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float z = cap > 0.f ? cap * tanh_exp(v[j] * inv_cap) : v[j];
+      if (c + j == label) sh_zy = z;
+      if (z > m) { sum = sum * __expf(m - z) + 1.f; m = z; } else sum += __expf(z - m);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, sum, o);
+    ms_merge(m, sum, m2, s2);
+  }
+  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if ((threadIdx.x & 31) == 0) { red_m[w] = m; red_s[w] = sum; }
+  __syncthreads();
+  if (w == 0) {
+    m = (int)threadIdx.x < nw ? red_m[threadIdx.x] : -INFINITY;
+    sum = (int)threadIdx.x < nw ? red_s[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, sum, o);
+      ms_merge(m, sum, m2, s2);
+    }
+    if (threadIdx.x == 0) {
+      sh_lse = m + __logf(sum);
+      loss[row] = (label >= 0 && label < V) ? sh_lse - sh_zy : 0.f;
+    }
+  }
+  __syncthreads();
+  const float lse = sh_lse;
+  const float on = (label >= 0 && label < V) ? scale : 0.f;      // a label outside the vocabulary: the row is ignored
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    float v[8], o[8];
+    ld8(lr + c, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float t = 0.f, z = v[j];
+      if (cap > 0.f) { t = tanh_exp(v[j] * inv_cap); z = cap * t; }
+      const float p = __expf(z - lse);
+      o[j] = on * (p - (c + j == label ? 1.f : 0.f)) * (1.f - t * t);
+    }
+    st8(lr + c, o);
+  }
+}
+
 // out[r, c] = sum over splits of ws[split, r, c]
 __global__ void lora_wgrad_reduce_kernel(const float* __restrict__ ws, int splits, int64_t n, float* __restrict__ out) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -548,6 +620,17 @@ MARY_API int mary_lora_wgrad(const void* small, int64_t lds, const void* big, in
   MARY_CHECK_LAUNCH();
   const int64_t n = (int64_t)R * C;
   lora_wgrad_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(ws, splits, n, out);
+  MARY_CHECK_LAUNCH();
+  return MARY_OK;
+}
+
+// Soft-capped cross-entropy of rows of logits: loss[row] and, in place of the logits, scale * d loss / d logits.
+MARY_API int mary_softcap_ce(void* logits, int64_t ld, const int64_t* labels, int64_t rows, int V, float cap, float scale, float* loss,
+                             cudaStream_t s) {
+  if (rows <= 0) return MARY_OK;
+  if ((V & 7) || (ld & 7)) return MARY_ERR_BAD_ARG;
+  const int threads = V >= 8192 ? 1024 : (V >= 2048 ? 256 : 64);
+  softcap_ce_kernel<<<(unsigned)rows, threads, 0, s>>>((__nv_bfloat16*)logits, ld, labels, V, cap, scale, loss);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

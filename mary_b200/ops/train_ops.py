@@ -29,6 +29,7 @@ declare("mary_geglu_train_bwd", "plplplli" + "s")
 declare("mary_qkv_norm_rope_train", "plplppppfpliiili" + "s")
 declare("mary_lora_wgrad_splits", "iii")
 declare("mary_lora_wgrad", "plpliiipp" + "s")
+declare("mary_softcap_ce", "plpliffp" + "s")
 
 
 def wide(rows: int, cols: int, extra: int, like) -> torch.Tensor:
@@ -333,3 +334,49 @@ class _LoraLinearFn(torch.autograd.Function):
             grads.append(dA[j * r:(j + 1) * r])
             grads.append(dBt[j * r:(j + 1) * r, r0:r0 + n].t())
         return ((dx if ctx.grad_extra else dx.view(ctx.shape)), None, None, *grads)
+
+
+# --------------------------------------------------------------------------------------------------------------- head + loss
+class _HeadLoss(torch.autograd.Function):
+    """Mean soft-capped cross-entropy of ``x W^T`` against ``labels``, chunked over the rows so that the ``[rows, vocab]`` logits
+    exist one chunk at a time and only in bf16: per chunk the head GEMM, ONE kernel that turns the logits into loss values and
+    (in place) their gradient, and the GEMM that carries that gradient back to ``x``.  Nothing of vocabulary width is kept for
+    the backward pass: the gradient with respect to ``x`` is complete when the forward returns."""
+
+    @staticmethod
+    def forward(ctx, x, w, wt, labels, cap, chunk):
+        n, V = x.shape[0], w.shape[0]
+        dx = torch.empty_like(x)
+        total = torch.zeros((), dtype=torch.float32, device=x.device)
+        lab = labels.to(torch.int64).contiguous()
+        for i in range(0, n, chunk):
+            xc = x[i:i + chunk]
+            if x.is_cuda:
+                from . import cuda as K
+                lg = K.gemm(xc.contiguous(), w)
+                rows = lg.shape[0]
+                loss = torch.empty(rows, dtype=torch.float32, device=x.device)
+                check(lib().mary_softcap_ce(_p(lg), lg.stride(0), _p(lab[i:i + chunk]), rows, V, float(cap or 0.0), 1.0 / n, _p(loss), _stream()),
+                      "softcap_ce")
+                total += loss.sum()
+                K.gemm(lg, wt, out=dx[i:i + chunk])
+            else:
+                lg = (xc.float() @ w.float().t()).requires_grad_()
+                with torch.enable_grad():
+                    z = cap * torch.tanh(lg / cap) if cap and cap > 0 else lg
+                    ls = torch.nn.functional.cross_entropy(z, lab[i:i + chunk], reduction="sum")
+                (g,) = torch.autograd.grad(ls, lg)
+                total += ls.detach()
+                dx[i:i + chunk] = ((g / n) @ w.float()).to(x.dtype)
+        ctx.save_for_backward(dx)
+        return total / n
+
+    @staticmethod
+    def backward(ctx, g):
+        (dx,) = ctx.saved_tensors
+        return dx * g.to(dx.dtype), None, None, None, None, None
+
+
+def head_loss(x, w, wt, labels, cap: float | None, chunk: int = 1024):
+    """Mean cross-entropy of the (soft-capped) logits ``x @ w^T`` against ``labels``; ``wt = w^T`` contiguous."""
+    return _HeadLoss.apply(x, w.detach(), wt, labels, float(cap or 0.0), int(chunk))

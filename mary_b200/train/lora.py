@@ -186,10 +186,10 @@ class Gemma4LoraForward(nn.Module):
                 m.refresh()
 
     def _lin(self, x, w):
-        wt = self._wt.get(id(w))
+        wt = self._wt.get(w.data_ptr())
         if wt is None:
             wt = w.detach().t().contiguous()
-            self._wt[id(w)] = wt
+            self._wt[w.data_ptr()] = wt
         return linear_frozen(x, w.detach(), wt)
 
     def _attn(self, q, k, v, window):
@@ -273,10 +273,9 @@ class Gemma4LoraForward(nn.Module):
         x = self.forward(ids)[:, :-1].reshape(-1, self.model.cfg.hidden_size)
         y = ids[:, 1:].reshape(-1).long()
         W = self.model.head_weight().detach()
-        cap = self.model.cfg.final_logit_softcapping
-        total = x.new_zeros((), dtype=torch.float32)
-        for i in range(0, x.shape[0], chunk):
-            lg = self._lin(x[i:i + chunk], W).float()
-            lg = cap * torch.tanh(lg / cap)
-            total = total + torch.nn.functional.cross_entropy(lg, y[i:i + chunk], reduction="sum")
-        return total / x.shape[0]
+        wt = self._wt.get(W.data_ptr())               # keyed by storage: ``detach()`` makes a new tensor object every call
+        if wt is None:
+            wt = W.t().contiguous()
+            self._wt[W.data_ptr()] = wt
+        from ..ops import train_ops as T
+        return T.head_loss(x.contiguous(), W, wt, y, self.model.cfg.final_logit_softcapping, chunk)

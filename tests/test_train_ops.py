@@ -162,3 +162,31 @@ def test_adapter_weight_gradient_kernel(R, C, M):
     got = T.lora_wgrad(small, big)
     want = small.double().t() @ big.double()
     assert (got.double() - want).abs().max().item() < 2e-3 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("cap,V", [(30.0, 4104), (0.0, 520), (30.0, 262144)])
+def test_head_loss_equals_chunked_cross_entropy_with_its_gradient(device, cap, V):
+    if device == "cpu" and V > 10000:
+        pytest.skip("vocabulary-sized case runs on the GPU only")
+    dt, tol = _setup(device)
+    torch.manual_seed(V)
+    n, H = 77, 256
+    x = torch.randn(n, H, device=device).to(dt).requires_grad_()
+    w = (torch.randn(V, H, device=device) * 0.2).to(dt)
+    y = torch.randint(0, V, (n,), device=device)
+    loss = T.head_loss(x, w, w.t().contiguous(), y, cap, chunk=32)
+    loss.backward()
+    xf = x.detach().float().requires_grad_()
+    lg = (xf @ w.float().t()).to(dt).float() if device == "cuda" else xf @ w.float().t()
+    lg = cap * torch.tanh(lg / cap) if cap else lg
+    want = torch.nn.functional.cross_entropy(lg, y)
+    assert abs(float(loss.detach()) - float(want.detach())) < (2e-3 if device == "cuda" else 1e-5) * abs(float(want.detach()))
+    if device == "cpu":
+        want.backward()
+        _close(x.grad, xf.grad, tol)
+    else:
+        # the GPU reference without the bf16 rounding of the logits (which autograd cannot see through)
+        lg2 = xf @ w.float().t()
+        torch.nn.functional.cross_entropy(cap * torch.tanh(lg2 / cap) if cap else lg2, y).backward()
+        _close(x.grad, xf.grad, 5e-2)
