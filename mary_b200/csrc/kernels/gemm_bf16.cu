@@ -79,6 +79,10 @@ struct GemmParams {
 // tile, stored in scratch slot `slot`.
 struct WorkItem { int bz, tr, tc, tile, kb0, kb1, seg, nseg, slot; };
 
+// LEAN: compile-time promise of the decode-shaped launches (weights are the row operand, plain bf16 store, no routing plan, no
+// band walk, no reduce-scatter): the kernel instantiated with it carries none of the other paths' code, which matters for launches
+// of a few microseconds that start with a cold instruction cache.
+template <bool LEAN>
 struct WorkIter {
   const GemmParams& p;
   int tt, unit, end;
@@ -105,7 +109,7 @@ struct WorkIter {
       return true;
     }
     const int per_batch = p.tiles_r * p.tiles_c * p.split_k;
-    if (p.g_tiles) {
+    if (!LEAN && p.g_tiles) {
       // token tiles the plan does not use: column tiles with swap, row tiles without
       const int used = p.g_meta[0];
       while (tt < per_batch && (p.swap ? tt % p.tiles_c : tt / (p.tiles_c * p.split_k)) >= used) tt += gridDim.x;
@@ -114,7 +118,7 @@ struct WorkIter {
     const int t = tt % per_batch;
     w.bz = tt / per_batch;
     int ks;
-    if (p.raster > 0) {                       // split_k == 1 here
+    if (!LEAN && p.raster > 0) {              // split_k == 1 here
       const int band = t / (p.raster * p.tiles_r), base = band * p.raster;
       const int gw = min(p.raster, p.tiles_c - base), in = t - band * p.raster * p.tiles_r;
       w.tr = in / gw;
@@ -162,10 +166,12 @@ struct Cfg {
 // 128-row tiles, two accumulators of BN columns); without swap they are the column operand and the two
 // BN-row tiles are... handled by launching the swapped roles only: GLU without swap is expressed by the host
 // as two B tiles, see launch code.  To keep one device code path, GLU always means "two row-operand tiles".
-template <int BN, bool GLU>
+template <int BN, bool GLU, bool LEAN>
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
   using C = Cfg<BN, GLU>;
+  const bool swap = LEAN ? true : p.swap != 0;
+  const int* const g_tiles = LEAN ? nullptr : p.g_tiles;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~uintptr_t(1023));
   uint64_t* full = (uint64_t*)(smem + C::STAGES * C::STAGE_BYTES);
@@ -199,7 +205,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
     // ------------------------------------------------------------------ TMA producer
     if (elect_one()) {
       int stage = 0; uint32_t phase = 0;
-      WorkIter iter(p);
+      WorkIter<LEAN> iter(p);
       WorkItem w;
       bool have = false;
       int pre = 0;                               // stages whose barrier is armed and whose weight tile is already in flight
@@ -212,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
             uint8_t* st = smem + i * C::STAGE_BYTES;
             const int kb = w.kb0 + i;
             mbar_expect_tx(&full[i], C::STAGE_BYTES);
-            if (p.swap) {
+            if (swap) {
               tma_load_3d(st, &tm_r, &full[i], kb * BK, w.tr * BM, w.bz * p.zr_mul);
               if (GLU) tma_load_3d(st + C::A_BYTES, &tm_r, &full[i], kb * BK, p.glu_offset + w.tr * BM, w.bz * p.zr_mul);
             } else {
@@ -226,16 +232,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       while (have) {
         const int tr = w.tr, tc = w.tc;
         int zr = w.bz * p.zr_mul, zc = w.bz * p.zc_mul;
-        if (p.g_tiles) {
-          const int e = min(max(p.g_tiles[4 * (p.swap ? tc : tr)], 0), p.g_experts - 1);
-          zr = p.swap ? e : 0;
-          zc = p.swap ? 0 : e;
+        if (g_tiles) {
+          const int e = min(max(g_tiles[4 * (swap ? tc : tr)], 0), p.g_experts - 1);
+          zr = swap ? e : 0;
+          zc = swap ? 0 : e;
         }
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           uint8_t* st = smem + stage * C::STAGE_BYTES;
           if (pre > 0) {
             --pre;                               // add the activation tile to the armed stage
-            if (p.swap) tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, zc);
+            if (swap) tma_load_3d(st + C::A_BYTES * (GLU ? 2 : 1), &tm_c, &full[stage], kb * BK, tc * BN, zc);
             else tma_load_3d(st, &tm_r, &full[stage], kb * BK, tr * BM, zr);
           } else {
             if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, MARY_ERR_TIMEOUT_TMA)) goto done;
@@ -255,7 +261,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       const uint32_t idesc = idesc_bf16(BM, BN);
       int stage = 0; uint32_t phase = 0;
       int it = 0;
-      WorkIter iter(p);
+      WorkIter<LEAN> iter(p);
       WorkItem w;
       for (; iter.next(w); ++it) {
         const int kb0 = w.kb0, kb1 = w.kb1;
@@ -287,7 +293,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
     pdl_wait();                            // before the first store: an earlier kernel may still read what this one overwrites
     const int q = warp & 3;                // TMEM lane quarter this warp may access
     int it = 0;
-    WorkIter iter(p);
+    WorkIter<LEAN> iter(p);
     WorkItem w;
     for (; iter.next(w); ++it) {
       const int bz = w.bz, tc = w.tc, tr = w.tr;
@@ -299,14 +305,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
       const int i = tr * BM + q * 32 + lane;              // row-operand index of this thread
       const uint32_t taddr = tmem_base + buf * C::ACC_COLS + ((uint32_t)(q * 32) << 16);
       const bool sk_epi = p.epi == EPI_SK_BF16 || p.epi == EPI_SK_F32;
-      const int final_epi = p.epi == EPI_SK_BF16 ? EPI_STORE_BF16 : (p.epi == EPI_SK_F32 ? EPI_STORE_F32 : p.epi);
+      const int final_epi = LEAN ? (int)EPI_STORE_BF16 : (p.epi == EPI_SK_BF16 ? EPI_STORE_BF16 : (p.epi == EPI_SK_F32 ? EPI_STORE_F32 : p.epi));
       const bool sk = sk_epi && w.nseg > 1;             // a tile computed by one CTA alone is stored directly
       const int tile = w.tile;
       float* slot = sk ? p.ws + (int64_t)tile * (BM * BN) : nullptr;      // the tile's f32 accumulator (zero between calls)
       // stores 32 finished values of this thread's row (columns tc * BN + c0 ..) in the requested form
       auto emit = [&](int c0, const float* v, int epi) {
         const int j0 = tc * BN + c0;
-        if (p.swap) {
+        if (swap) {
           // i = output feature, j = token: out[j * ldo + i]; a warp writes 32 consecutive features per token
           if (i < p.rows_r) {
             const float b = p.bias ? p.bias[i] : 0.f;
@@ -314,8 +320,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant
             for (int j = 0; j < 32; ++j) {
               if (j0 + j < p.rows_c) {
                 const int64_t o = obase + (int64_t)(j0 + j) * p.ldo + i;
-                if (epi == EPI_RS_BF16) rs_row(p, j0 + j)[i] = __float2bfloat16(v[j] + b);
-                else if (epi == EPI_STORE_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16(v[j] + b);
+                if (LEAN || epi == EPI_STORE_BF16) ((__nv_bfloat16*)p.out)[o] = __float2bfloat16(v[j] + b);
+                else if (epi == EPI_RS_BF16) rs_row(p, j0 + j)[i] = __float2bfloat16(v[j] + b);
                 else if (epi == EPI_STORE_F32) ((float*)p.out)[o] = v[j] + b;
                 else atomicAdd((float*)p.out + o, v[j]);
               }
@@ -406,15 +412,15 @@ done:
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
-template <int BN, bool GLU>
+template <int BN, bool GLU, bool LEAN = false>
 int launch(const CUtensorMap& tr, const CUtensorMap& tc, const GemmParams& p, cudaStream_t stream) {
   using C = Cfg<BN, GLU>;
   static MarySmemSlots smem_set = {};
-  if (int rc = mary_ensure_dyn_smem((const void*)gemm_bf16_kernel<BN, GLU>, C::SMEM, &smem_set)) return rc;
+  if (int rc = mary_ensure_dyn_smem((const void*)gemm_bf16_kernel<BN, GLU, LEAN>, C::SMEM, &smem_set)) return rc;
   int total = p.tiles_r * p.tiles_c * p.split_k * p.batch;
   int grid = total < mary_num_sms() ? total : mary_num_sms();
   if (p.sk_units > 0) grid = (p.tiles_r * p.tiles_c * p.k_blocks + p.sk_units - 1) / p.sk_units;
-  MARY_LAUNCH((gemm_bf16_kernel<BN, GLU>), grid, NTHREADS, C::SMEM, stream, tr, tc, p);
+  MARY_LAUNCH((gemm_bf16_kernel<BN, GLU, LEAN>), grid, NTHREADS, C::SMEM, stream, tr, tc, p);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -565,6 +571,22 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   if (rc) return rc;
   rc = make_tmap_3d(&tc, Cc, p.rows_c, K, ldc, (g_tiles && !use_swap) ? g_experts : (c_shared ? 1 : batch), bsc, bn);
   if (rc) return rc;
+  // decode-shaped launches (see WorkIter): the instantiation without the other paths' code
+  const bool lean = use_swap && !g_tiles && p.raster == 0 && (epi == EPI_STORE_BF16 || epi == EPI_SK_BF16) && bn <= 128;
+  if (lean) {
+    if (glu) {
+      switch (bn) {
+        case 32: return launch<32, true, true>(tr, tc, p, stream);
+        case 64: return launch<64, true, true>(tr, tc, p, stream);
+        default: return launch<128, true, true>(tr, tc, p, stream);
+      }
+    }
+    switch (bn) {
+      case 32: return launch<32, false, true>(tr, tc, p, stream);
+      case 64: return launch<64, false, true>(tr, tc, p, stream);
+      default: return launch<128, false, true>(tr, tc, p, stream);
+    }
+  }
   if (glu) {
     switch (bn) {
       case 32: return launch<32, true>(tr, tc, p, stream);

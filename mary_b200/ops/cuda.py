@@ -10,6 +10,7 @@ import math
 import torch
 
 from .. import _native
+from ..utils.canary import empty as _empty
 
 _SIG = {
     # name: argument codes — p pointer, i int32, l int64, f float, s stream
@@ -179,7 +180,7 @@ def gemm_splitk(x, w, split_k: int, out=None, f32: bool = False, bias=None, swap
     N = w.shape[0]
     ws, cnt = _sk_workspace(x.device)
     if out is None:
-        out = torch.empty(M, N, dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
+        out = _empty(M, N, dtype=torch.float32 if f32 else torch.bfloat16, device=x.device)
     rc = lib().mary_gemm_bf16_splitk(_p(x), _p(w), _p(out), M, N, K, x.stride(0), w.stride(0), out.stride(0), _p(bias), 1.0, int(f32),
                                      split_k, swap, _p(ws), ws.numel(), _p(cnt), cnt.numel(), _stream())
     if rc == 4:                                             # scratch too small for this shape
@@ -254,7 +255,7 @@ def rmsnorm(x, weight=None, eps=1e-6):
     x2 = x.reshape(-1, shp[-1])
     if x2.stride(-1) != 1:
         x2 = x2.contiguous()
-    y = torch.empty(x2.shape, dtype=torch.bfloat16, device=x.device)
+    y = _empty(x2.shape, dtype=torch.bfloat16, device=x.device)
     check(lib().mary_rmsnorm(_p(x2), int(x2.dtype == torch.float32), _p(weight), _p(y), x2.shape[0], x2.shape[1],
                              x2.stride(0), y.stride(0), eps, _stream()), "rmsnorm")
     return y.reshape(shp)
@@ -276,21 +277,21 @@ def norm_add_norm(a, w_post, h, w_next, eps=1e-6, scalar=1.0):
 
 def glu(gate_up, act="geglu"):
     T, F2 = gate_up.shape
-    out = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=gate_up.device)
+    out = _empty(T, F2 // 2, dtype=torch.bfloat16, device=gate_up.device)
     check(lib().mary_glu(_p(gate_up.contiguous()), _p(out), T, F2 // 2, {"geglu": 0, "swiglu": 1, "situ": 2}[act], _stream()), "glu")
     return out
 
 
 def embed(ids, table, scale=1.0):
     ids = ids.to(torch.int32)
-    out = torch.empty(ids.shape[0], table.shape[1], dtype=torch.bfloat16, device=table.device)
+    out = _empty(ids.shape[0], table.shape[1], dtype=torch.bfloat16, device=table.device)
     check(lib().mary_embed(_p(ids), _p(table), _p(out), ids.shape[0], table.shape[1], scale, table.shape[0], _stream()), "embed")
     return out
 
 
 def qk_norm_rope_append(qkv, n_q, n_kv, head_dim, q_norm, k_norm, v_norm, inv_freq, meta, kcache, vcache, eps):
     T = qkv.shape[0]
-    q = torch.empty(T, n_q, head_dim, dtype=torch.bfloat16, device=qkv.device)
+    q = _empty(T, n_q, head_dim, dtype=torch.bfloat16, device=qkv.device)
     check(lib().mary_qk_norm_rope_append(_p(qkv.contiguous()), n_q, n_kv, head_dim, _p(q_norm), _p(k_norm), int(bool(v_norm)),
                                          _p(inv_freq), _p(meta.positions), _p(meta.slot_mapping), _p(q), _p(kcache), _p(vcache),
                                          eps, T, kcache.shape[0] * kcache.shape[1] if n_kv else 0, _stream()), "qk_norm_rope_append")
@@ -343,10 +344,10 @@ def _paged_attention_decode(q, kcache, vcache, meta, scale, window, softcap, nsp
         want = max(1, DECODE_TARGET_CTAS // max(1, NB * Hkv))
         span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
         nsplit = max(1, min(want, 32, span // 64))
-    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    out = _empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
     scratch = None
     if nsplit > 1:
-        scratch = torch.empty(lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
+        scratch = _empty(lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
     check(lib().mary_paged_attention_decode(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
                                             _p(meta.q_start), _p(blk_seq), _p(blk_q0), NB, meta.page_table.shape[1], meta.page_size,
                                             kcache.stride(1), kcache.stride(0), vcache.stride(1), vcache.stride(0), Hq, Hkv, D, rq,
@@ -385,10 +386,10 @@ def paged_attention_decode_q8(q, kcache, vcache, meta, scale, window=0, softcap=
         want = max(1, DECODE_TARGET_CTAS // max(1, NB * Hkv))
         span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
         nsplit = max(1, min(want, 32, span // 64))
-    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    out = _empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
     scratch = None
     if nsplit > 1:
-        scratch = torch.empty(lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
+        scratch = _empty(lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
     kc, vc = kcache.codes, vcache.codes
     check(lib().mary_paged_attention_decode_q8(_p(q.contiguous()), _p(kc), _p(vc), _p(kcache.sz), _p(vcache.sz), _p(out), _p(meta.page_table),
                                                _p(meta.kv_len), _p(meta.q_start), _p(blk_seq), _p(blk_q0), NB, meta.page_table.shape[1],
@@ -428,10 +429,10 @@ def gqa_decode_tc(q, kcache, vcache, meta, scale, window=0, softcap=0.0, nsplit=
         want = max(1, (296 if D == 128 else 148) // max(1, NB * Hkv))
         span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
         nsplit = max(1, min(want, 32, span // (4 * meta.page_size)))
-    out = torch.empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
+    out = _empty(T, Hq, D, dtype=torch.bfloat16, device=q.device)
     scratch = None
     if nsplit > 1:
-        scratch = torch.empty(lib().mary_gqa_tc_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
+        scratch = _empty(lib().mary_gqa_tc_scratch_floats(NB, Hkv, nsplit, D), dtype=torch.float32, device=q.device)
     assert vcache.is_contiguous() and vcache.shape == kcache.shape
     check(lib().mary_gqa_decode_tc(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len), _p(meta.q_start),
                                    _p(blk_seq), _p(blk_q0), NB, T, kcache.shape[0], meta.page_table.shape[1], meta.page_size, Hq, Hkv, D, rq,
@@ -460,7 +461,7 @@ def attention_prefill(q, kcache, vcache, meta, scale, window=0):
         ps = 64
     assert ps in (16, 64)
     blk_seq, blk_tok0, NB = _q_blocks(meta, 128)
-    out = torch.empty(T, Hq, DV, dtype=torch.bfloat16, device=q.device)
+    out = _empty(T, Hq, DV, dtype=torch.bfloat16, device=q.device)
     check(lib().mary_attention_prefill(_p(q.contiguous()), _p(kcache), _p(vcache), _p(out), _p(meta.page_table), _p(meta.kv_len),
                                        _p(meta.q_start), _p(blk_seq), _p(blk_tok0), NB, T, Hq, Hkv, DK, DV, kcache.shape[0],
                                        meta.page_table.shape[1], kcache.stride(1), kcache.stride(0), vcache.stride(1), vcache.stride(0),
@@ -513,11 +514,11 @@ def paged_attention(q, kcache, vcache, meta, scale, window=0, softcap=0.0, dv: i
         want = max(1, 296 // max(1, NB * Hkv))
         span = meta.max_kv_len if window <= 0 else min(meta.max_kv_len, window + rq)
         nsplit = max(1, min(want, 32, span // 128))
-    out = torch.empty(T, Hq, DV, dtype=torch.bfloat16, device=q.device)
+    out = _empty(T, Hq, DV, dtype=torch.bfloat16, device=q.device)
     scratch = None
     if nsplit > 1:
         n = lib().mary_paged_attention_scratch_floats(NB, Hkv, nsplit, DV)
-        scratch = torch.empty(n, dtype=torch.float32, device=q.device)
+        scratch = _empty(n, dtype=torch.float32, device=q.device)
     ktok, kpage = kcache.stride(1), kcache.stride(0)
     vtok, vpage = vcache.stride(1), vcache.stride(0)
     if rel_bias is not None:
@@ -542,8 +543,8 @@ def argmax(logits, softcap=0.0, temperature: float = 0.0, margin: float = 20.0, 
     """Per-row arg-max (first maximum wins) or, with ``temperature > 0``, a Gumbel-max sample.  Returns ``(ids, value)``."""
     rows, V = logits.shape
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
-    idx = torch.empty(rows, dtype=torch.int64, device=logits.device)
-    val = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    idx = _empty(rows, dtype=torch.int64, device=logits.device)
+    val = _empty(rows, dtype=torch.float32, device=logits.device)
     check(lib().mary_argmax(_p(logits), logits.stride(0), rows, V, softcap, 1 if temperature > 0 else 0, temperature, margin,
                             seed, step, _p(idx), _p(val), _stream()), "argmax")
     return idx, val
@@ -557,8 +558,8 @@ def sample_top_k_top_p(logits, temperature: float, top_k: int = 0, top_p: float 
     read-back; the draw of row ``r`` depends on ``(seed, step, r)`` only.  Returns int32 ids (and the drawn token's probability)."""
     rows, V = logits.shape
     assert logits.dtype in (torch.float32, torch.bfloat16) and logits.stride(1) == 1 and temperature > 0 and top_p > 0
-    idx = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    prob = torch.empty(rows, dtype=torch.float32, device=logits.device) if want_prob else None
+    idx = _empty(rows, dtype=torch.int32, device=logits.device)
+    prob = _empty(rows, dtype=torch.float32, device=logits.device) if want_prob else None
     check(lib().mary_sample_top_k_top_p(_p(logits), int(logits.dtype == torch.float32), logits.stride(0), rows, V, float(temperature), int(top_k),
                                         float(top_p), int(seed) & (2**63 - 1), int(step) & (2**63 - 1), _p(idx), _p(prob), _stream()),
           "sample_top_k_top_p")
@@ -575,8 +576,8 @@ def lm_head_argmax(h, table, softcap=0.0, vocab_limit=None):
 def router_topk(logits, k, mode="softmax", bias=None, n_group=1, topk_group=1, scale=1.0, renorm=True, counts=None, flag=None):
     T, E = logits.shape
     lg = logits if logits.dtype == torch.float32 else logits.float()
-    idx = torch.empty(T, k, dtype=torch.int32, device=logits.device)
-    w = torch.empty(T, k, dtype=torch.float32, device=logits.device)
+    idx = _empty(T, k, dtype=torch.int32, device=logits.device)
+    w = _empty(T, k, dtype=torch.float32, device=logits.device)
     b = bias.float().contiguous() if bias is not None else None
     check(lib().mary_router_topk(_p(lg), lg.stride(0), _p(b), T, E, k, 0 if mode == "softmax" else 1, n_group, topk_group, scale,
                                  int(renorm), _p(idx), _p(w), _p(counts), _p(flag), _stream()), "router_topk")
@@ -622,10 +623,10 @@ def mla_attention(q, cache, meta, scale, nsplit: int | None = None):
     blk_seq, blk_r0, NB = _row_tiles(meta, Hq)
     if nsplit is None:
         nsplit = max(1, min(8, 148 // max(1, NB), meta.max_kv_len // 512))
-    out = torch.empty(T, Hq, 512, dtype=torch.bfloat16, device=q.device)
+    out = _empty(T, Hq, 512, dtype=torch.bfloat16, device=q.device)
     scratch = None
     if nsplit > 1:
-        scratch = torch.empty(lib().mary_mla_scratch_floats(NB, nsplit), dtype=torch.float32, device=q.device)
+        scratch = _empty(lib().mary_mla_scratch_floats(NB, nsplit), dtype=torch.float32, device=q.device)
     c = cache.view(cache.shape[0], ps, 576)
     check(lib().mary_mla_attention(_p(q.contiguous()), _p(c), _p(out), _p(meta.page_table), _p(meta.kv_len), _p(meta.q_start),
                                    _p(blk_seq), _p(blk_r0), NB, T * Hq, c.shape[0], meta.page_table.shape[1], c.stride(1),
@@ -655,7 +656,7 @@ def mla_expand_kv(rows, w_uk_t, w_uv, H):
     row operand and writes each head's 128 columns at pitch 192, then the 64 rotated dims every head shares copied behind them) and
     ``v [N, H, 128]`` (one GEMM).  ``w_uk_t [H * 128, 512]``, ``w_uv [H * 128, 512]``."""
     N = rows.shape[0]
-    k = torch.empty(N, H, 192, dtype=torch.bfloat16, device=rows.device)
+    k = _empty(N, H, 192, dtype=torch.bfloat16, device=rows.device)
     with static_weights:
         gemm_batched(rows, w_uk_t, k, N, 128, 512, rows.stride(0), 512, H * 192, H, 0, 128 * 512, 192)
         v = gemm(rows[:, :512], w_uv)
@@ -671,7 +672,7 @@ def mla_q_rope_inplace(qb, inv_freq, meta, H):
 
 def mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps):
     T = qakv.shape[0]
-    qa = torch.empty(T, q_lora, dtype=torch.bfloat16, device=qakv.device)
+    qa = _empty(T, q_lora, dtype=torch.bfloat16, device=qakv.device)
     check(lib().mary_mla_prep(_p(qakv), qakv.stride(0), q_lora, _p(w_qa), _p(w_kv), _p(inv_freq), _p(meta.positions),
                               _p(meta.slot_mapping), _p(qa), _p(cache), eps, T, cache.shape[0] * cache.shape[1], _stream()), "mla_prep")
     return qa
@@ -680,7 +681,7 @@ def mla_prep(qakv, q_lora, w_qa, w_kv, inv_freq, meta, cache, eps):
 def mla_absorb_q(qb, w_uk, inv_freq, meta, H):
     """``qb[T, H*192]`` -> ``q_full[T, H, 576]``: nope part times ``w_uk[H, 512, 128]`` (absorbed W_UK), rope part rotated."""
     T = qb.shape[0]
-    q_full = torch.empty(T, H, 576, dtype=torch.bfloat16, device=qb.device)
+    q_full = _empty(T, H, 576, dtype=torch.bfloat16, device=qb.device)
     with static_weights:
         gemm_batched(qb, w_uk, q_full, T, 512, 128, H * 192, 128, H * 576, H, 192, 512 * 128, 576)
     check(lib().mary_mla_q_rope(_p(qb), _p(inv_freq), _p(meta.positions), _p(q_full), H, T, _stream()), "mla_q_rope")
@@ -690,7 +691,7 @@ def mla_absorb_q(qb, w_uk, inv_freq, meta, H):
 def mla_unabsorb_o(o_lat, w_uv, H):
     """``o_lat[T, H, 512]`` -> ``o[T, H*128]`` with ``w_uv[H, 128, 512]``."""
     T = o_lat.shape[0]
-    o = torch.empty(T, H * 128, dtype=torch.bfloat16, device=o_lat.device)
+    o = _empty(T, H * 128, dtype=torch.bfloat16, device=o_lat.device)
     with static_weights:
         gemm_batched(o_lat, w_uv, o, T, 128, 512, H * 512, 512, H * 128, H, 512, 128 * 512, 128)
     return o

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import torch
 
+from ..utils.canary import empty as _empty
 from .cuda import _p, _stream, check, declare, lib
 
 declare("mary_moe_plan", "piiiiippppps")
@@ -20,9 +21,9 @@ def quantize_rows(x, nt: int = 128, src_of=None, identity: bool = True, rows: in
     K = x.shape[1]
     rows = rows if rows is not None else x.shape[0]
     tiles = (rows + nt - 1) // nt
-    xq = torch.empty(rows, K // 2, dtype=torch.uint8, device=x.device)
+    xq = _empty(rows, K // 2, dtype=torch.uint8, device=x.device)
     sf = (torch.zeros if zero_sf else torch.empty)(tiles, K // 64, 512, dtype=torch.uint8, device=x.device)
-    rm = torch.empty(rows, K // 16, dtype=torch.uint8, device=x.device) if rowmajor else None
+    rm = _empty(rows, K // 16, dtype=torch.uint8, device=x.device) if rowmajor else None
     check(lib().mary_quant_nvfp4_rows(_p(x), x.stride(0), _p(src_of), int(identity), rows, K, nt, _p(xq), _p(sf), _p(rm),
                                       _p(n_rows), _stream()), "quant_nvfp4_rows")
     return xq, sf, rm
@@ -36,8 +37,8 @@ def quantize_entries(x, plan, k: int, identity: bool):
     padded row.  Padding rows keep whatever bytes the buffers held; their products stay inside those rows, which nothing reads."""
     K = x.shape[1]
     rows, nt = plan.max_rows, plan.nt
-    xq = torch.empty(rows, K // 2, dtype=torch.uint8, device=x.device)
-    sf = torch.empty(rows // nt, K // 64, 512, dtype=torch.uint8, device=x.device)
+    xq = _empty(rows, K // 2, dtype=torch.uint8, device=x.device)
+    sf = _empty(rows // nt, K // 64, 512, dtype=torch.uint8, device=x.device)
     check(lib().mary_quant_nvfp4_entries(_p(x), x.stride(0), _p(plan.row_of), plan.row_of.numel(), k, int(identity), K, nt, _p(xq), _p(sf),
                                          _stream()), "quant_nvfp4_rows")
     return xq, sf
@@ -59,18 +60,18 @@ def moe_plan(idx, E: int, nt: int) -> Plan:
     p.nt = nt
     p.max_rows = lib().mary_moe_max_rows(T * k, E, nt)
     dev = idx.device
-    p.row_of = torch.empty(T * k, dtype=torch.int32, device=dev)
-    p.src_of = torch.empty(p.max_rows, dtype=torch.int32, device=dev)
-    p.tiles = torch.empty(p.max_rows // nt, 4, dtype=torch.int32, device=dev)
-    p.meta = torch.empty(2, dtype=torch.int32, device=dev)
-    p.counts = torch.empty(E, dtype=torch.int32, device=dev)
+    p.row_of = _empty(T * k, dtype=torch.int32, device=dev)
+    p.src_of = _empty(p.max_rows, dtype=torch.int32, device=dev)
+    p.tiles = _empty(p.max_rows // nt, 4, dtype=torch.int32, device=dev)
+    p.meta = _empty(2, dtype=torch.int32, device=dev)
+    p.counts = _empty(E, dtype=torch.int32, device=dev)
     check(lib().mary_moe_plan(_p(idx.contiguous()), T * k, k, E, nt, p.max_rows, _p(p.row_of), _p(p.src_of), _p(p.tiles),
                               _p(p.meta), _p(p.counts), _stream()), "moe_plan")
     return p
 
 
 def grouped_gemm(wq, sfw, scale2, xq, sfx, plan: Plan, n_out: int, K: int, E: int, glu: str | None):
-    out = torch.empty(plan.max_rows, n_out, dtype=torch.bfloat16, device=xq.device)
+    out = _empty(plan.max_rows, n_out, dtype=torch.bfloat16, device=xq.device)
     g = 0 if glu is None else {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
     check(lib().mary_gemm_nvfp4_grouped(_p(wq), _p(sfw), _p(scale2), _p(xq), _p(sfx), _p(plan.tiles), _p(plan.meta), _p(out),
                                         out.stride(0), E, n_out, K, plan.max_rows, plan.nt, g, _stream()), "gemm_nvfp4_grouped")
@@ -92,8 +93,8 @@ FUSED_GLU_QUANT = _glu_quant_default()
 def grouped_gemm_glu_q(wq, sfw, scale2, xq, sfx, plan: Plan, n_out: int, K: int, E: int, glu: str):
     """The GLU GEMM with the quantising epilogue: ``(codes [rows, n_out / 2], scale tiles)`` ready for the next NVFP4 GEMM."""
     rows, nt = plan.max_rows, plan.nt
-    hq = torch.empty(rows, n_out // 2, dtype=torch.uint8, device=xq.device)
-    sfh = torch.empty(rows // nt, n_out // 64, 512, dtype=torch.uint8, device=xq.device)
+    hq = _empty(rows, n_out // 2, dtype=torch.uint8, device=xq.device)
+    sfh = _empty(rows // nt, n_out // 64, 512, dtype=torch.uint8, device=xq.device)
     g = {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
     check(lib().mary_gemm_nvfp4_grouped_glu_q(_p(wq), _p(sfw), _p(scale2), _p(xq), _p(sfx), _p(plan.tiles), _p(plan.meta), _p(hq), _p(sfh),
                                               E, n_out, K, rows, nt, g, _stream()), "gemm_nvfp4_grouped")
@@ -102,7 +103,7 @@ def grouped_gemm_glu_q(wq, sfw, scale2, xq, sfx, plan: Plan, n_out: int, K: int,
 
 def unpermute(y, plan: Plan, w, T: int, k: int, add=None):
     H = y.shape[1]
-    out = torch.empty(T, H, dtype=torch.bfloat16, device=y.device)
+    out = _empty(T, H, dtype=torch.bfloat16, device=y.device)
     check(lib().mary_moe_unpermute(_p(y), y.stride(0), _p(plan.row_of), _p(w.float().contiguous()), T, k, H, _p(add), _p(out),
                                    _stream()), "moe_unpermute")
     return out
@@ -130,7 +131,7 @@ def grouped_gemm_bf16(xg, w, plan: Plan, n_out: int, glu: str | None, swap: bool
     """``out[r] = act_glu(xg[r] @ w[expert of r's tile]^T)`` over the plan's padded rows; ``w [E, n_out or 2 n_out, K]`` unquantised.
     ``swap=False`` (plans with 128-row tiles, no GLU): tokens as the 128-row tensor-core operand, for prefill-sized batches."""
     E, _, K = w.shape
-    out = torch.empty(plan.max_rows, n_out, dtype=torch.bfloat16, device=xg.device)
+    out = _empty(plan.max_rows, n_out, dtype=torch.bfloat16, device=xg.device)
     g = 0 if glu is None else {"geglu": 1, "swiglu": 2, "situ": 3}[glu]
     check(lib().mary_gemm_bf16_grouped(_p(xg), _p(w), _p(out), plan.max_rows, n_out, K, xg.stride(0), w.stride(1), out.stride(0), E,
                                        w.stride(0), _p(plan.tiles), _p(plan.meta), plan.nt, g, int(swap), _stream()), "gemm_bf16_grouped")

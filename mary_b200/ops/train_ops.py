@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import torch
 
+from ..utils.canary import empty as _empty
 from .cuda import _p, _stream, check, declare, lib
 
 declare("mary_rmsnorm_train_fwd", "plpplffplli" + "s")
@@ -34,7 +35,7 @@ declare("mary_softcap_ce", "plpliffp" + "s")
 
 def wide(rows: int, cols: int, extra: int, like) -> torch.Tensor:
     """``[rows, cols]`` view of a fresh ``[rows, cols + extra]`` buffer."""
-    return torch.empty(rows, cols + extra, dtype=like.dtype, device=like.device)[:, :cols]
+    return _empty(rows, cols + extra, dtype=like.dtype, device=like.device)[:, :cols]
 
 
 def _wide_base(t: torch.Tensor, extra: int):
@@ -84,10 +85,10 @@ class _RmsNorm(torch.autograd.Function):
         d2 = _rows(dy)
         alpha = ctx.alpha
         if x2.is_cuda:
-            dx = torch.empty(rows, H, dtype=x2.dtype, device=x2.device)
+            dx = _empty(rows, H, dtype=x2.dtype, device=x2.device)
             dres = None
             if ctx.has_res:
-                dres = d2 if alpha == 1.0 else torch.empty(rows, H, dtype=x2.dtype, device=x2.device)
+                dres = d2 if alpha == 1.0 else _empty(rows, H, dtype=x2.dtype, device=x2.device)
             wr = dres if (dres is not None and dres is not d2) else None
             check(lib().mary_rmsnorm_train_bwd(_p(d2), d2.stride(0), _p(x2), x2.stride(0), _p(w), alpha, ctx.eps, _p(dx), dx.stride(0), _p(wr),
                                                wr.stride(0) if wr is not None else 0, rows, H, _stream()), "rmsnorm_train_bwd")
@@ -175,7 +176,7 @@ class _QkvNormRope(torch.autograd.Function):
         p32 = pos.to(torch.int32)
         ctx.save_for_backward(x2, p32, inv_freq, qw, kw)
         ctx.cfg = (eps, n_q, n_kv, D, grad_extra, qkv.shape)
-        out = torch.empty(rows, heads * D, dtype=x2.dtype, device=x2.device)
+        out = _empty(rows, heads * D, dtype=x2.dtype, device=x2.device)
         if x2.is_cuda:
             check(lib().mary_qkv_norm_rope_train(_p(x2), x2.stride(0), None, 0, _p(p32), _p(inv_freq), _p(qw), _p(kw), eps, _p(out), out.stride(0),
                                                  n_q, n_kv, D, rows, 0, _stream()), "qkv_norm_rope_fwd")
@@ -237,11 +238,11 @@ def lora_wgrad(small, big):
     C = big.shape[1]
     if not small.is_cuda:
         return small.float().t() @ big.float()
-    out = torch.empty(R, C, dtype=torch.float32, device=small.device)
+    out = _empty(R, C, dtype=torch.float32, device=small.device)
     for g in range(0, R, 48):
         n = min(48, R - g)
         splits = lib().mary_lora_wgrad_splits(M, C, n)
-        ws = torch.empty(splits, n, C, dtype=torch.float32, device=small.device)
+        ws = _empty(splits, n, C, dtype=torch.float32, device=small.device)
         sg = small[:, g:g + n]
         check(lib().mary_lora_wgrad(_p(sg), sg.stride(0), _p(big), big.stride(0), M, n, C, _p(ws), _p(out[g:g + n]), _stream()), "lora_wgrad")
     return out
@@ -299,7 +300,7 @@ class _LoraLinearFn(torch.autograd.Function):
         M = x2.shape[0]
         xe = _wide_base(x2, R) if R else None
         if R and xe is None:
-            xe = torch.empty(M, K + R, dtype=x2.dtype, device=x2.device)
+            xe = _empty(M, K + R, dtype=x2.dtype, device=x2.device)
             xe[:, :K].copy_(x2)
         if R:
             _mm(xe[:, :K], mod.a16, out=xe[:, K:], alpha=mod.scale)            # s u = s x A^T into the spare columns
@@ -323,7 +324,7 @@ class _LoraLinearFn(torch.autograd.Function):
         (xe,) = ctx.saved_tensors
         de = _wide_base(d2, R)
         if de is None:
-            de = torch.empty(M, N + R, dtype=d2.dtype, device=d2.device)
+            de = _empty(M, N + R, dtype=d2.dtype, device=d2.device)
             de[:, :N].copy_(d2)
         _mm(de[:, :N], mod.bt, out=de[:, N:], alpha=mod.scale)                 # dL/du = s dy B into the spare columns
         _mm(de, mod.wb, out=dx)                                                # dy W + (dL/du) A
@@ -355,7 +356,7 @@ class _HeadLoss(torch.autograd.Function):
                 from . import cuda as K
                 lg = K.gemm(xc.contiguous(), w)
                 rows = lg.shape[0]
-                loss = torch.empty(rows, dtype=torch.float32, device=x.device)
+                loss = _empty(rows, dtype=torch.float32, device=x.device)
                 check(lib().mary_softcap_ce(_p(lg), lg.stride(0), _p(lab[i:i + chunk]), rows, V, float(cap or 0.0), 1.0 / n, _p(loss), _stream()),
                       "softcap_ce")
                 total += loss.sum()

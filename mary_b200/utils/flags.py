@@ -69,6 +69,7 @@ declare("MARY_MULTIMEM", bool, True, "use the NVSwitch multicast address (multim
 declare("MARY_ONESHOT", bool, True, "small all-reduces take the one-barrier staged form")
 declare("MARY_MOE_GLU_QUANT", bool, True, "with 32-token tiles the first expert GEMM of the planned MoE path quantises its GLU result in the epilogue (0: a second quantiser launch)")
 declare("MARY_MOE_FUSED", bool, True, "decode-sized MoE layers take the four-launch pipeline (0: the planned path)")
+declare("MARY_CANARY", bool, False, "guard bands around every output buffer the op wrappers allocate; utils.canary.check_all() verifies them")
 declare("MARY_DEBUG_CHECKS", bool, False, "validate every batch description on the host before launch (lengths, page ids, page reuse)")
 declare("MARY_NVTX", bool, False, "emit NVTX ranges per decoder layer and marks per kernel launch")
 declare("MARY_BENCH_LIMIT_S", int, 540, "bench.py ends itself with a stack dump after this many seconds")
