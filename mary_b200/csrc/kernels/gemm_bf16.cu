@@ -16,6 +16,7 @@
 //     accumulators and writes act(gate) * up;
 //   * optional split-K with an f32 reduction epilogue (red.global.add.f32) into a zeroed buffer, which is also
 //     the hook for reducing into peer GPUs' buffers.
+#include <cstdlib>
 #include "common.cuh"
 #include "host_utils.h"
 
@@ -145,7 +146,9 @@ __device__ __forceinline__ __nv_bfloat16* rs_row(const GemmParams& p, int token_
   return (__nv_bfloat16*)p.rs_bufs[owner] + ((int64_t)p.rs_src * p.rs_rpr + lr) * p.ldo;
 }
 
-template <int BN, bool GLU>
+// SHORT: few pipeline stages (under 100 KB of shared memory) so that two CTAs fit one SM: with programmatic dependent launch the
+// next decode-sized GEMM of the stream then sets up and requests its first weight tiles while this one drains.
+template <int BN, bool GLU, bool SHORT = false>
 struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;                       // 16 KB
   static constexpr int B_BYTES = BN * BK * 2;
@@ -157,7 +160,8 @@ struct Cfg {
                                    : TMEM_COLS_RAW <= 256 ? 256 : 512;
   static constexpr int MAX_SMEM = 220 * 1024;
   static constexpr int STAGES_RAW = (MAX_SMEM - 1024) / STAGE_BYTES;
-  static constexpr int STAGES = STAGES_RAW > 12 ? 12 : STAGES_RAW;
+  static constexpr int STAGES_SHORT = (96 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = SHORT ? STAGES_SHORT : (STAGES_RAW > 12 ? 12 : STAGES_RAW);
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   static_assert(TMEM_COLS_RAW <= 512, "accumulators exceed TMEM");
 };
@@ -166,10 +170,11 @@ struct Cfg {
 // 128-row tiles, two accumulators of BN columns); without swap they are the column operand and the two
 // BN-row tiles are... handled by launching the swapped roles only: GLU without swap is expressed by the host
 // as two B tiles, see launch code.  To keep one device code path, GLU always means "two row-operand tiles".
-template <int BN, bool GLU, bool LEAN>
+template <int BN, bool GLU, int LEAN_MODE>          // 0: every path; 1: decode-shaped launches only; 2: the same with the short pipeline
 __global__ void __launch_bounds__(NTHREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tm_r, const __grid_constant__ CUtensorMap tm_c, const GemmParams p) {
-  using C = Cfg<BN, GLU>;
+  constexpr bool LEAN = LEAN_MODE != 0;
+  using C = Cfg<BN, GLU, LEAN_MODE == 2>;
   const bool swap = LEAN ? true : p.swap != 0;
   const int* const g_tiles = LEAN ? nullptr : p.g_tiles;
   extern __shared__ uint8_t smem_raw[];
@@ -412,9 +417,9 @@ done:
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
-template <int BN, bool GLU, bool LEAN = false>
+template <int BN, bool GLU, int LEAN = 0>
 int launch(const CUtensorMap& tr, const CUtensorMap& tc, const GemmParams& p, cudaStream_t stream) {
-  using C = Cfg<BN, GLU>;
+  using C = Cfg<BN, GLU, LEAN == 2>;
   static MarySmemSlots smem_set = {};
   if (int rc = mary_ensure_dyn_smem((const void*)gemm_bf16_kernel<BN, GLU, LEAN>, C::SMEM, &smem_set)) return rc;
   int total = p.tiles_r * p.tiles_c * p.split_k * p.batch;
@@ -450,6 +455,12 @@ static int make_tmap_3d(CUtensorMap* m, const void* base, uint64_t rows, uint64_
 
 // Batched form: `batch` independent problems; operand b starts at base + b * batch_stride (elements).
 static thread_local int g_static_weights = 0;
+// decode-shaped launches take the short pipeline (two CTAs per SM): on when the environment says MARY_GEMM_SHORT=1
+static int short_pipeline_default() {
+  const char* e = getenv("MARY_GEMM_SHORT");
+  return (e && e[0] == '1') ? 1 : 0;
+}
+static int g_short_pipeline = short_pipeline_default();
 
 static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int batch,
                      int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha, int glu, int epi, int split_k, int swap,
@@ -460,6 +471,7 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
 // Tells the GEMM launchers called next on THIS thread that their W operand holds constant model weights (1) or may have been
 // written by an earlier kernel of the stream (0, the default).  Only read when programmatic dependent launch is enabled.
 MARY_API void mary_gemm_hint_static_weights(int on) { g_static_weights = on ? 1 : 0; }
+MARY_API void mary_gemm_short_pipeline(int on) { g_short_pipeline = on ? 1 : 0; }
 
 MARY_API int mary_gemm_bf16_batched(const void* X, const void* W, void* out, int M, int N, int K, int64_t ldx, int64_t ldw,
                                     int64_t ldo, int batch, int64_t bsx, int64_t bsw, int64_t bso, const float* bias, float alpha,
@@ -576,15 +588,22 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
   if (lean) {
     if (glu) {
       switch (bn) {
-        case 32: return launch<32, true, true>(tr, tc, p, stream);
-        case 64: return launch<64, true, true>(tr, tc, p, stream);
-        default: return launch<128, true, true>(tr, tc, p, stream);
+        case 32: return launch<32, true, 1>(tr, tc, p, stream);
+        case 64: return launch<64, true, 1>(tr, tc, p, stream);
+        default: return launch<128, true, 1>(tr, tc, p, stream);
+      }
+    }
+    if (g_short_pipeline) {
+      switch (bn) {
+        case 32: return launch<32, false, 2>(tr, tc, p, stream);
+        case 64: return launch<64, false, 2>(tr, tc, p, stream);
+        default: return launch<128, false, 2>(tr, tc, p, stream);
       }
     }
     switch (bn) {
-      case 32: return launch<32, false, true>(tr, tc, p, stream);
-      case 64: return launch<64, false, true>(tr, tc, p, stream);
-      default: return launch<128, false, true>(tr, tc, p, stream);
+      case 32: return launch<32, false, 1>(tr, tc, p, stream);
+      case 64: return launch<64, false, 1>(tr, tc, p, stream);
+      default: return launch<128, false, 1>(tr, tc, p, stream);
     }
   }
   if (glu) {

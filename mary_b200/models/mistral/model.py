@@ -105,6 +105,23 @@ class _NoTP:
         return x
 
 
+_LAYER_STEP = None
+
+
+def _layer_step_enabled() -> bool:
+    global _LAYER_STEP
+    if _LAYER_STEP is None:
+        from ...utils import flags
+        _LAYER_STEP = bool(flags.get("MARY_LAYER_STEP"))
+    return _LAYER_STEP
+
+
+def set_layer_step(on: bool) -> None:
+    """Switch the fused one-token layer step on or off (tests compare the two paths)."""
+    global _LAYER_STEP
+    _LAYER_STEP = bool(on)
+
+
 class MistralLayer(nn.Module):
     def __init__(self, cfg: MistralConfig, i: int, tp, inv_freq, q_scale: float, dtype, device):
         super().__init__()
@@ -133,6 +150,26 @@ class MistralLayer(nn.Module):
         if next_norm is None:
             return None, (h.float() + d.float()).to(h.dtype)
         return ops.add_rmsnorm(d, h, next_norm, c.rms_norm_eps)
+
+    def step_supported(self, h, meta, cache) -> bool:
+        """Whether the fused one-token step (``csrc/kernels/layer_step.cu``) applies: one new token of one sequence on the GPU,
+        bf16 weights and cache, head dim 128, no tensor parallelism, widths the kernels hold in shared memory."""
+        c = self.cfg
+        k = cache.k[self.i]
+        return (h.is_cuda and h.dtype == torch.bfloat16 and h.shape[0] == 1 and meta.num_seqs == 1 and c.head_dim == 128
+                and self.tp.size == 1 and isinstance(k, torch.Tensor) and k.dtype == torch.bfloat16 and c.hidden_size <= 8192
+                and self.F <= 8192 and self.n_q * c.head_dim <= 8192 and _layer_step_enabled())
+
+    def step(self, h, meta, cache):
+        """One new token of one sequence in five launches: ``h [1, H]`` (residual stream) -> the residual stream after this layer."""
+        from ...ops import cuda as K
+        c = self.cfg
+        qkv = K.step_matvec(h, self.w_qkv, self.ln_attn, c.rms_norm_eps)
+        o = K.step_attention(qkv, self.q_norm, self.k_norm, self.inv_freq, meta, cache.k[self.i], cache.v[self.i], self.n_q, self.n_kv,
+                             c.head_dim, c.rms_norm_eps, self.scale)
+        h = K.step_matvec(o, self.w_o, res=h, mode="residual")
+        m = K.step_matvec(h, self.w_gu, self.ln_ffn, c.rms_norm_eps, mode="swiglu")
+        return K.step_matvec(m, self.w_down, res=h, mode="residual")
 
 
 class MistralModel(nn.Module):
@@ -168,6 +205,10 @@ class MistralModel(nn.Module):
     def hidden_from_embeds(self, h, meta, cache):
         """The stack over given input embeddings ``[T, H]`` (speech models assemble them from several tables)."""
         c = self.cfg
+        if self.layers[0].step_supported(h, meta, cache):
+            for layer in self.layers:
+                h = layer.step(h, meta, cache)
+            return ops.rmsnorm(h, self.norm, c.rms_norm_eps)
         x = ops.rmsnorm(h, self.layers[0].ln_attn, c.rms_norm_eps)
         n = len(self.layers)
         for i, layer in enumerate(self.layers):

@@ -261,6 +261,13 @@ def bench_floor(reps: int = 200):
         "gemm 48x7168x8192 (stream-K)": (lambda a=torch.randn(48, 8192, device="cuda").bfloat16(), w=(torch.randn(7168, 8192, device="cuda") * 0.02).bfloat16(): K.linear(a, w)),
         "gemm 48x384x7168 f32 (router)": (lambda w=(torch.randn(384, 7168, device="cuda") * 0.02).bfloat16(): K.linear_f32(x, w)),
         "rmsnorm 48x7168": (lambda g=torch.ones(7168, device="cuda").bfloat16(): K.rmsnorm(x, g)),
+        # one token: the tensor-core GEMM against the matrix-vector stage of the fused layer step (weights L2-resident: the floor)
+        "gemm 1x2048x1024": (lambda a=torch.randn(1, 1024, device="cuda").bfloat16(), w=(torch.randn(2048, 1024, device="cuda") * 0.02).bfloat16(): K.gemm(a, w)),
+        "step_matvec 1x2048x1024": (lambda a=torch.randn(1, 1024, device="cuda").bfloat16(), w=(torch.randn(2048, 1024, device="cuda") * 0.02).bfloat16(): K.step_matvec(a, w)),
+        "gemm 1x7168x8192 (117 MB)": (lambda a=torch.randn(1, 8192, device="cuda").bfloat16(), w=(torch.randn(7168, 8192, device="cuda") * 0.02).bfloat16(): K.linear(a, w)),
+        "step_matvec 1x7168x8192 (117 MB)": (lambda a=torch.randn(1, 8192, device="cuda").bfloat16(), w=(torch.randn(7168, 8192, device="cuda") * 0.02).bfloat16(): K.step_matvec(a, w)),
+        "step_matvec 1x151936x4096 (1.2 GB head)": (lambda a=torch.randn(1, 4096, device="cuda").bfloat16(), w=(torch.randn(151936, 4096, device="cuda") * 0.02).bfloat16(): K.step_matvec(a, w)),
+        "gemm 1x151936x4096 (1.2 GB head)": (lambda a=torch.randn(1, 4096, device="cuda").bfloat16(), w=(torch.randn(151936, 4096, device="cuda") * 0.02).bfloat16(): K.linear(a, w)),
     }
     for name, fn in cases.items():
         for _ in range(3):
@@ -291,9 +298,12 @@ def bench_ttsframe(iters: int = 30):
     init_random_(tk, pr, 0)
     h = (torch.randn(c.talker_hidden, device="cuda") * 0.5).to(torch.bfloat16)
     e0 = (torch.randn(c.talker_hidden, device="cuda") * 0.5).to(torch.bfloat16)
+    from ..models.mistral import model as mistral
     out = {}
-    for name, flag in (("eager", False), ("graph", True)):
+    for name, flag, fused in (("eager", False, True), ("graph", True, True), ("graph9", True, False)):
         pr.use_graph = flag
+        pr._graph = None
+        mistral.set_layer_step(fused)
         for _ in range(3):
             pr.predict_frame(h, e0)
         torch.cuda.synchronize()
@@ -306,8 +316,10 @@ def bench_ttsframe(iters: int = 30):
         out[name] = a.elapsed_time(b) / iters
     w = sum(p.numel() * p.element_size() for p in pr.stack.parameters()) * (c.num_code_groups - 1)
     print(f"qwen3tts code predictor frame ({c.num_code_groups - 1} steps x {c.pred_layers} layers): eager {out['eager'] * 1e3:.0f} us, graph "
-          f"{out['graph'] * 1e3:.0f} us per frame ({out['eager'] / out['graph']:.2f}x); {w / 1e6:.0f} MB of weights read per frame; "
+          f"{out['graph'] * 1e3:.0f} us per frame ({out['eager'] / out['graph']:.2f}x); the graph with the nine-launch layers instead of the "
+          f"five-launch fused layer step: {out['graph9'] * 1e3:.0f} us; {w / 1e6:.0f} MB of weights read per frame; "
           f"a 12.5 Hz frame budget is 80000 us")
+    mistral.set_layer_step(True)
 
 
 def bench_depformer(iters: int = 30):

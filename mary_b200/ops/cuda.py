@@ -695,3 +695,31 @@ def mla_unabsorb_o(o_lat, w_uv, H):
     with static_weights:
         gemm_batched(o_lat, w_uv, o, T, 128, 512, H * 512, 512, H * 128, H, 512, 128 * 512, 128)
     return o
+
+
+# ------------------------------------------------------------------------------------------------- one-token decoder layer step
+declare("mary_step_matvec", "ppfpliippi" + "s")
+declare("mary_step_attention", "pppppppppp" + "iiiilffp" + "s")
+
+
+def step_matvec(h, w, gain=None, eps: float = 1e-6, res=None, mode: str = "plain"):
+    """One-token matrix-vector stage of the fused layer step: ``W x`` (``plain``), ``res + W x`` (``residual``) or
+    ``silu(W_gate x) * (W_up x)`` over ``w = [gate; up]`` (``swiglu``), with ``x = rms(h) * gain`` when ``gain`` is given,
+    else ``x = h``.  ``h [1, K]`` -> ``[1, N]``."""
+    m = {"plain": 0, "residual": 1, "swiglu": 2}[mode]
+    K = h.shape[-1]
+    N = w.shape[0] // 2 if m == 2 else w.shape[0]
+    y = _empty(1, N, dtype=torch.bfloat16, device=h.device)
+    check(lib().mary_step_matvec(_p(h), _p(gain), eps, _p(w), w.stride(0), N, K, _p(res), _p(y), m, _stream()), "step_matvec")
+    return y
+
+
+def step_attention(qkv, q_gain, k_gain, inv_freq, meta, kcache, vcache, n_q: int, n_kv: int, head_dim: int, eps: float, scale: float):
+    """Head norms, rotation, cache append and attention of ONE new token of ONE sequence (head dim 128): ``qkv [1, (n_q + 2 n_kv) D]``
+    -> ``[1, n_q * D]``."""
+    out = _empty(1, n_q * head_dim, dtype=torch.bfloat16, device=qkv.device)
+    n_slots = kcache.shape[0] * kcache.shape[1]
+    check(lib().mary_step_attention(_p(qkv), _p(q_gain), _p(k_gain), _p(inv_freq), _p(meta.positions), _p(meta.slot_mapping), _p(meta.page_table),
+                                    _p(meta.kv_len), _p(kcache), _p(vcache), n_q, n_kv, head_dim, meta.page_size, n_slots, eps, scale, _p(out),
+                                    _stream()), "step_attention")
+    return out

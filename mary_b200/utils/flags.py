@@ -64,6 +64,8 @@ def table() -> list[tuple[str, str, object, object, str]]:
 
 declare("MARY_MODELS", str, "", "directory that holds model piles and checkpoints; never guessed (format.paths)")
 declare("MARY_GQA_TC", bool, True, "decode-shaped batches of grouped-query models (head dim 128 / 256, 16- or 32-token pages) run the tensor-core decode attention kernel")
+declare("MARY_GEMM_SHORT", bool, False, "decode-shaped bf16 GEMMs use a short pipeline (two CTAs fit one SM), so that under MARY_PDL=1 the next GEMM sets up while this one drains")
+declare("MARY_LAYER_STEP", bool, True, "one-token steps of one sequence through the dense pre-norm decoders take the five-launch fused layer step")
 declare("MARY_PDL", bool, False, "launch the decode-path kernels with programmatic dependent launch")
 declare("MARY_MULTIMEM", bool, True, "use the NVSwitch multicast address (multimem.ld_reduce / multimem.st) where the allocation has one")
 declare("MARY_ONESHOT", bool, True, "small all-reduces take the one-barrier staged form")
