@@ -60,25 +60,38 @@ __device__ __forceinline__ void stage_input(const __nv_bfloat16* __restrict__ h,
   __syncthreads();
 }
 
-// dot products of four weight rows with xs, the lanes of a warp striding over K in 16-byte chunks
+// dot products of up to four weight rows with xs, the lanes of a warp striding over K in 16-byte chunks; four chunks per row are
+// requested before the first is used (16 loads of 16 bytes in flight per lane: a one-token product is a pure weight stream and
+// its speed is the number of bytes in flight)
 __device__ __forceinline__ void warp_dot4(const __nv_bfloat16* __restrict__ w, int64_t ldw, const int* rows, int n_rows, const float* xs, int K,
                                           float* out) {
   const int lane = threadIdx.x & 31;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  for (int c = lane * 8; c < K; c += 256) {
-    float wv[4][8];
+  constexpr int U = 4;
+  for (int c = lane * 8; c < K; c += 256 * U) {
+    uint4 wv[U][4];
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
-      if (r < n_rows) ld8f(w + (int64_t)rows[r] * ldw + c, wv[r]);
-    const float4 x0 = *(const float4*)(xs + c), x1 = *(const float4*)(xs + c + 4);
+    for (int u = 0; u < U; ++u)
 #pragma unroll
-    for (int r = 0; r < 4; ++r)
-      if (r < n_rows) {
-        acc[r] = fmaf(wv[r][0], x0.x, acc[r]); acc[r] = fmaf(wv[r][1], x0.y, acc[r]);
-        acc[r] = fmaf(wv[r][2], x0.z, acc[r]); acc[r] = fmaf(wv[r][3], x0.w, acc[r]);
-        acc[r] = fmaf(wv[r][4], x1.x, acc[r]); acc[r] = fmaf(wv[r][5], x1.y, acc[r]);
-        acc[r] = fmaf(wv[r][6], x1.z, acc[r]); acc[r] = fmaf(wv[r][7], x1.w, acc[r]);
+      for (int r = 0; r < 4; ++r)
+        if (r < n_rows && c + u * 256 < K) wv[u][r] = __ldg((const uint4*)(w + (int64_t)rows[r] * ldw + c + u * 256));
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int cc = c + u * 256;
+      if (cc < K) {
+        const float4 x0 = *(const float4*)(xs + cc), x1 = *(const float4*)(xs + cc + 4);
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+          if (r < n_rows) {
+            const __nv_bfloat162* h = (const __nv_bfloat162*)&wv[u][r];
+            const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), d = __bfloat1622float2(h[2]), e = __bfloat1622float2(h[3]);
+            acc[r] = fmaf(a.x, x0.x, acc[r]); acc[r] = fmaf(a.y, x0.y, acc[r]);
+            acc[r] = fmaf(b.x, x0.z, acc[r]); acc[r] = fmaf(b.y, x0.w, acc[r]);
+            acc[r] = fmaf(d.x, x1.x, acc[r]); acc[r] = fmaf(d.y, x1.y, acc[r]);
+            acc[r] = fmaf(e.x, x1.z, acc[r]); acc[r] = fmaf(e.y, x1.w, acc[r]);
+          }
       }
+    }
   }
 #pragma unroll
   for (int r = 0; r < 4; ++r) out[r] = warp_sum(acc[r]);

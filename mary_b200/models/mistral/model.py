@@ -106,6 +106,10 @@ class _NoTP:
 
 
 _LAYER_STEP = None
+# The matrix-vector stages of the fused step beat a one-token tensor-core GEMM launch while the matrix is small (4.0 against 6.1 us
+# at 4 MB) and lose to it on wide ones (38 against 25 us at 117 MB: 7168 rows over 2368 warps leave a quarter of the machine idle
+# in the last pass), so layers whose gate / up matrix is larger than this stay on the GEMM path.
+_STEP_MAX_BYTES = 24 << 20
 
 
 def _layer_step_enabled() -> bool:
@@ -158,7 +162,8 @@ class MistralLayer(nn.Module):
         k = cache.k[self.i]
         return (h.is_cuda and h.dtype == torch.bfloat16 and h.shape[0] == 1 and meta.num_seqs == 1 and c.head_dim == 128
                 and self.tp.size == 1 and isinstance(k, torch.Tensor) and k.dtype == torch.bfloat16 and c.hidden_size <= 8192
-                and self.F <= 8192 and self.n_q * c.head_dim <= 8192 and _layer_step_enabled())
+                and self.F <= 8192 and self.n_q * c.head_dim <= 8192 and 2 * self.F * c.hidden_size * 2 <= _STEP_MAX_BYTES
+                and _layer_step_enabled())
 
     def step(self, h, meta, cache):
         """One new token of one sequence in five launches: ``h [1, H]`` (residual stream) -> the residual stream after this layer."""
