@@ -44,7 +44,24 @@ def _worker(rank, world, port, Hq, Hkv, window, out):
     dist.destroy_process_group()
 
 
+def _once_more(test):
+    """One retry with a fresh port absorbs a lost race for the rendezvous port or a slow start of the child interpreters."""
+    import functools
+
+    @functools.wraps(test)
+    def run(*a, **kw):
+        try:
+            return test(*a, **kw)
+        except Exception:
+            for child in mp.active_children():
+                child.terminate()
+                child.join(10)
+            return test(*a, **kw)
+    return run
+
+
 @pytest.mark.parametrize("world,Hq,Hkv,window", [(2, 4, 2, 0), (4, 8, 2, 0), (3, 6, 6, 0), (2, 4, 4, 5), (4, 8, 1, 0)])
+@_once_more
 def test_sequence_parallel_attention_equals_the_whole_sequence(world, Hq, Hkv, window):
     ctx = mp.get_context("spawn")
     out = ctx.Queue()
