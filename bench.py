@@ -172,6 +172,12 @@ def main():
         cfg.name, cfg.num_mtp_layers, cfg.attention = "gemma-4-12b-style", 0, "gqa"
     else:
         cfg = {"k3": k3_class_config, "inkling": inkling_style_config, "tiny": tiny_moe_config}[args.model]()
+    pdl = bool(int(os.environ["MARY_PDL"])) if os.environ.get("MARY_PDL", "") in ("0", "1") else (is_gemma and world == 1)
+    if pdl != bool(int(os.environ.get("MARY_PDL", "0") or 0)):
+        # a dense decoder's step is a chain of small GEMMs, where programmatic dependent launch gains (10.2 -> 9.4 ms measured);
+        # with the expert pipeline in the chain it loses, and it has not run with the peer-flag kernels of the multi-GPU layouts
+        from mary_b200.ops import cuda as _K
+        _K.set_pdl(pdl)
     B = args.batch or {"k3": 128, "inkling": 64, "tiny": 8, "gemma12b": 32}[args.model]
     ctx = args.ctx or {"k3": 4096, "inkling": 1024, "tiny": 256, "gemma12b": 2048}[args.model]
     k = args.spec if args.spec is not None else (2 if cfg.num_mtp_layers else 0)
@@ -436,7 +442,7 @@ def main():
                            "global_batch": B_global, "seq_len": ctx, "spec_tokens": k,
                            "parallelism": ("single" if world == 1 else f"tp{world}" if is_gemma else
                                            f"ep{world}-all-to-all+dp{world}-attention" if a2a else f"ep{world}+tp{world}-attention"),
-                           "kv_page_tokens": page, "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": graph_used,
+                           "kv_page_tokens": page, "comm": ("sp: gemm->reduce-scatter + fused norm/all-gather" if par.sp is not None else par.mode) if world > 1 else "none", "cuda_graph": graph_used, "dependent_launch": pdl,
                            "lm_head": head_kind,
                            "expert_slabs_resident": slabs, "moe_layers": n_moe,
                            "l2": "each step streams >100x the 126 MB L2 (expert slabs, KV pages), so no flush is needed between steps",

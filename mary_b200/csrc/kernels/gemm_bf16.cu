@@ -538,6 +538,17 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
     const int sms = mary_num_sms();
     bn = 256;
     while (bn > 64 && (int64_t)p.tiles_r * ((p.rows_c + bn - 1) / bn) * split_k * batch < sms) bn >>= 1;
+    if (bn == 256 && split_k == 1 && !sk_epi && !g_tiles && batch == 1) {
+      // wave quantisation: the tiles run in waves of one per SM, and a last wave that is a quarter full costs a whole wave (480
+      // tiles of 128 x 256 on 148 SMs are 3.24 waves = 4).  A slightly narrower tile can end closer to a full wave: take the width
+      // whose waves x width (the time of the slowest SM) is smallest; the narrower widths pay a little per tile, hence the margin.
+      int64_t best = 0;
+      for (int cand : {256, 224, 192}) {
+        const int64_t tiles = (int64_t)p.tiles_r * ((p.rows_c + cand - 1) / cand);
+        const int64_t cost = ((tiles + sms - 1) / sms) * cand * (cand == 256 ? 100 : 103);
+        if (best == 0 || cost < best) { best = cost; bn = cand; }
+      }
+    }
   }
   p.tiles_c = (p.rows_c + bn - 1) / bn;
   p.ws = ws;
@@ -617,6 +628,8 @@ static int gemm_impl(const void* X, const void* W, void* out, int M, int N, int 
     case 32: return launch<32, false>(tr, tc, p, stream);
     case 64: return launch<64, false>(tr, tc, p, stream);
     case 128: return launch<128, false>(tr, tc, p, stream);
+    case 192: return launch<192, false>(tr, tc, p, stream);
+    case 224: return launch<224, false>(tr, tc, p, stream);
     default: return launch<256, false>(tr, tc, p, stream);
   }
 }

@@ -63,12 +63,16 @@ __device__ __forceinline__ void stage_input(const __nv_bfloat16* __restrict__ h,
 // dot products of up to four weight rows with xs, the lanes of a warp striding over K in 16-byte chunks; four chunks per row are
 // requested before the first is used (16 loads of 16 bytes in flight per lane: a one-token product is a pure weight stream and
 // its speed is the number of bytes in flight)
+// `rot` staggers where in K a warp starts (it walks all of K, wrapping): rows are a power-of-two number of bytes apart, and warps
+// that all read the same columns of different rows at the same time would queue on a few memory channels
 __device__ __forceinline__ void warp_dot4(const __nv_bfloat16* __restrict__ w, int64_t ldw, const int* rows, int n_rows, const float* xs, int K,
-                                          float* out) {
+                                          float* out, int rot) {
   const int lane = threadIdx.x & 31;
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   constexpr int U = 4;
-  for (int c = lane * 8; c < K; c += 256 * U) {
+  const int span = 256 * U, iters = (K + span - 1) / span;
+  for (int it = 0; it < iters; ++it) {
+    const int c = ((it + rot) % iters) * span + lane * 8;
     uint4 wv[U][4];
 #pragma unroll
     for (int u = 0; u < U; ++u)
@@ -116,7 +120,7 @@ __global__ void __launch_bounds__(LS_THREADS) step_matvec_kernel(const __nv_bflo
       const int rows[4] = {n0, n0 + N, n0 + 1, n0 + 1 + N};
       const int cnt = (pw == 2 && n0 + 1 < N) ? 4 : 2;
       float d[4];
-      warp_dot4(w, ldw, rows, cnt, xs, K, d);
+      warp_dot4(w, ldw, rows, cnt, xs, K, d, gw);
       if (lane == 0) {
         y[n0] = __float2bfloat16(silu_f(d[0]) * d[1]);           // on the f32 sums, as the GEMM's GLU epilogue does
         if (cnt == 4) y[n0 + 1] = __float2bfloat16(silu_f(d[2]) * d[3]);
@@ -127,7 +131,7 @@ __global__ void __launch_bounds__(LS_THREADS) step_matvec_kernel(const __nv_bflo
       const int rows[4] = {n0, n0 + 1, n0 + 2, n0 + 3};
       const int cnt = min(rpw, N - n0);
       float d[4];
-      warp_dot4(w, ldw, rows, cnt, xs, K, d);
+      warp_dot4(w, ldw, rows, cnt, xs, K, d, gw);
       if (lane < cnt) {
         float v = lane == 0 ? d[0] : (lane == 1 ? d[1] : (lane == 2 ? d[2] : d[3]));
         if (mode == 1) v = __bfloat162float(res[n0 + lane]) + __bfloat162float(__float2bfloat16(v));

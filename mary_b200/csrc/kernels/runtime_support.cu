@@ -97,11 +97,17 @@ int mary_ensure_dyn_smem(const void* func, size_t bytes, MarySmemSlots* slots) {
   return MARY_OK;
 }
 
+static int g_pdl = -1;          // -1: not decided yet (the environment decides at the first launch)
+
 int mary_pdl_enabled() {
-  static int v = -1;
-  if (v < 0) {
+  if (g_pdl < 0) {
     const char* e = getenv("MARY_PDL");
-    v = (e && e[0] == '1') ? 1 : 0;
+    g_pdl = (e && e[0] == '1') ? 1 : 0;
   }
-  return v;
+  return g_pdl;
 }
+
+// Switch programmatic dependent launch on or off for the launches that follow (a model whose step is a chain of small dense GEMMs
+// gains from it, one with the expert pipeline in the chain loses: the caller that knows the model decides).  Graphs captured
+// before the call keep what they were captured with.
+MARY_API void mary_set_pdl(int on) { g_pdl = on ? 1 : 0; }

@@ -289,6 +289,19 @@ def bench_floor(reps: int = 200):
     assert K.last_status() == 0
 
 
+def bench_matvec(N: int = 7168, K: int = 8192, iters: int = 10):
+    """One-token product ``W[N, K] x``: the SIMT matrix-vector stage of the fused layer step against the tensor-core GEMM launch
+    (L2 flushed between iterations: a weight stream from memory)."""
+    from . import cuda as K_
+    hbm, tf, tag = peaks()
+    a = torch.randn(1, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
+    for name, fn in (("step_matvec", lambda: K_.step_matvec(a, w)), ("gemm (linear)", lambda: K_.linear(a, w))):
+        ms = time_op(fn, iters=iters)
+        print(f"{name} 1 x {N} x {K}: {ms * 1e3:.1f} us, {N * K * 2 / ms / 1e6:.0f} GB/s ({N * K * 2 / ms / 1e6 / hbm:.2f} {tag})")
+    assert K_.last_status() == 0
+
+
 def bench_ttsframe(iters: int = 30):
     """One frame of the Qwen3-TTS code predictor at its released size (5 layers x 1024, 15 sequential steps, 2048-entry heads):
     eager launches against the one-graph replay of the same frame."""
@@ -528,6 +541,8 @@ if __name__ == "__main__":
                 bench_mla(page=pg)
                 bench_mla(Hq=8, page=pg)
                 bench_mla(B=16, page=pg)
+    if what == "matvec":
+        bench_matvec(*nums)
     if what == "floor":
         bench_floor(*nums)
     if what == "ttsframe":

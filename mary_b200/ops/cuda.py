@@ -723,3 +723,12 @@ def step_attention(qkv, q_gain, k_gain, inv_freq, meta, kcache, vcache, n_q: int
                                     _p(meta.kv_len), _p(kcache), _p(vcache), n_q, n_kv, head_dim, meta.page_size, n_slots, eps, scale, _p(out),
                                     _stream()), "step_attention")
     return out
+
+
+declare("mary_set_pdl", "i")
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch for the launches that follow (``MARY_PDL`` decides when nobody calls this): a gain for steps
+    that are chains of small dense GEMMs, a loss with the expert pipeline in the chain."""
+    lib().mary_set_pdl(int(bool(on)))

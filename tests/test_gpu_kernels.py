@@ -20,7 +20,8 @@ def _rel(a, b):
 
 
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 512), (300, 520, 1096), (1024, 1024, 2048), (32, 3840, 4096), (1, 128, 64),
-                                     (64, 264, 7168), (257, 4104, 1536)])
+                                     (64, 264, 7168), (257, 4104, 1536),
+                                     (2048, 3840, 512), (4096, 1344, 256), (2000, 3848, 264)])     # column tiles of 224 / 192 (wave count)
 def test_gemm_bf16_vs_fp32(K, M, N, K_):
     torch.manual_seed(M + N)
     x = torch.randn(M, K_, device="cuda").bfloat16()
