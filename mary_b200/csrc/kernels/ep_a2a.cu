@@ -16,6 +16,10 @@
 //                     the tensor-core tile layout) and the return address of the row into the owner's slabs -> barrier
 //   4. grouped GEMMs  w13 (+GLU) -> re-quantise -> w2 with row_ptrs built by ep_return_ptrs            -> barrier
 //   5. un-permute     out[t] = sum_j w[t, j] * comb[t * k + j]  (moe_unpermute with an identity row map)
+// Row order: inside one expert's block of the owner's slab the rows of one source rank are handed out by an atomic counter
+// (ep_dispatch: send_cnt), so WHICH padded row a token lands in differs from run to run.  The layer's output does not depend
+// on it (every row of the grouped GEMMs is independent and the home rank sums a token's k results in fixed slot order); a
+// combine that added rows in arrival order, or a row-by-row dump of the slabs, would inherit the nondeterminism.
 // The reference has no expert parallelism at all (experts are per-node residents of a layer range,
 // src/bin/inkling_forward.rs:2103-2438); this is new.
 #include <cuda_fp8.h>
