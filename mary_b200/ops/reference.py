@@ -1,6 +1,6 @@
 """Plain PyTorch implementations of every op.
 
-They serve three purposes: the CPU execution path (BASELINE config 1 runs on CPU in f32), the fp32
+They serve three purposes: the CPU execution path (the tiny-decoder configuration runs on CPU in f32), the fp32
 oracle each CUDA kernel is tested against, and the "NCCL + library" baseline arm of the benchmarks.
 All of them accept any device and dtype; reductions are done in float32."""
 from __future__ import annotations

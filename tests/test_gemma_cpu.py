@@ -1,4 +1,4 @@
-"""BASELINE config 1: tiny Gemma-4-style decoder on CPU from a pile; token-exact, logits within 1e-4 relative."""
+"""The CPU configuration: tiny Gemma-4-style decoder on CPU from a pile; token-exact, logits within 1e-4 relative."""
 import numpy as np
 import pytest
 import torch
