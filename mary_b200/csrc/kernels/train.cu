@@ -71,6 +71,18 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[0];
 }
 
+// two sums over the CTA at once (one round of barriers instead of two)
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2* red) {
+  a = warp_sum(a);
+  b = warp_sum(b);
+  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if ((threadIdx.x & 31) == 0) red[w] = make_float2(a, b);
+  __syncthreads();
+  float2 t = make_float2(0.f, 0.f);
+  for (int i = 0; i < nw; ++i) { t.x += red[i].x; t.y += red[i].y; }      // every thread sums the few warp totals itself
+  return t;
+}
+
 // ----------------------------------------------------------------------------- RMS norm over rows of width H (H % 8 == 0)
 // one CTA per row; the row stays in registers between the reduction and the write (H <= 8 * 8 * blockDim.x)
 constexpr int RN_MAX = 4;   // 8-element chunks per thread
@@ -78,7 +90,7 @@ constexpr int RN_MAX = 4;   // 8-element chunks per thread
 __global__ void rmsnorm_train_fwd_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, const __nv_bfloat16* __restrict__ w,
                                          const __nv_bfloat16* __restrict__ res, int64_t ldr, float alpha, float eps,
                                          __nv_bfloat16* __restrict__ out, int64_t ldo, int H) {
-  __shared__ float red[32];
+  __shared__ float2 red[32];
   const int64_t row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * ldx;
   float v[RN_MAX][8];
@@ -92,7 +104,7 @@ __global__ void rmsnorm_train_fwd_kernel(const __nv_bfloat16* __restrict__ x, in
       for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
     }
   }
-  const float rstd = rsqrtf(block_sum(ss, red) / (float)H + eps);
+  const float rstd = rsqrtf(block_sum2(ss, 0.f, red).x / (float)H + eps);
 #pragma unroll
   for (int i = 0; i < RN_MAX; ++i) {
     const int c = (i * blockDim.x + threadIdx.x) * 8;
@@ -117,7 +129,7 @@ __global__ void rmsnorm_train_fwd_kernel(const __nv_bfloat16* __restrict__ x, in
 __global__ void rmsnorm_train_bwd_kernel(const __nv_bfloat16* __restrict__ dy, int64_t ldy, const __nv_bfloat16* __restrict__ x, int64_t ldx,
                                          const __nv_bfloat16* __restrict__ w, float alpha, float eps, __nv_bfloat16* __restrict__ dx,
                                          int64_t lddx, __nv_bfloat16* __restrict__ dres, int64_t lddr, int H) {
-  __shared__ float red[32];
+  __shared__ float2 red[32];
   const int64_t row = blockIdx.x;
   float xv[RN_MAX][8], gv[RN_MAX][8];
   float ss = 0.f, sg = 0.f;
@@ -143,8 +155,9 @@ __global__ void rmsnorm_train_bwd_kernel(const __nv_bfloat16* __restrict__ dy, i
       }
     }
   }
-  ss = block_sum(ss, red);
-  sg = block_sum(sg, red);
+  const float2 tot = block_sum2(ss, sg, red);
+  ss = tot.x;
+  sg = tot.y;
   const float rstd = rsqrtf(ss / (float)H + eps);
   const float k = sg * rstd * rstd / (float)H;        // mean(g * xhat) * rstd
 #pragma unroll
