@@ -180,36 +180,39 @@ __device__ __forceinline__ void gelu_tanh_and_grad(float x, float* val, float* g
   *grad = 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * k0 * (1.0f + 3.0f * k1 * x * x);
 }
 
-__global__ void geglu_train_fwd_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg, __nv_bfloat16* __restrict__ out, int64_t ldo, int F) {
-  const int64_t row = blockIdx.y;
+__global__ void geglu_train_fwd_kernel(const __nv_bfloat16* __restrict__ gu, int64_t ldg, __nv_bfloat16* __restrict__ out, int64_t ldo, int F,
+                                       int64_t rows) {
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= F) return;
-  float g[8], u[8], o[8];
-  ld8(gu + row * ldg + c, g);
-  ld8(gu + row * ldg + F + c, u);
+  for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
+    float g[8], u[8], o[8];
+    ld8(gu + row * ldg + c, g);
+    ld8(gu + row * ldg + F + c, u);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) o[j] = gelu_tanh_f(g[j]) * u[j];
-  st8(out + row * ldo + c, o);
+    for (int j = 0; j < 8; ++j) o[j] = gelu_tanh_f(g[j]) * u[j];
+    st8(out + row * ldo + c, o);
+  }
 }
 
 __global__ void geglu_train_bwd_kernel(const __nv_bfloat16* __restrict__ dout, int64_t ldd, const __nv_bfloat16* __restrict__ gu, int64_t ldg,
-                                       __nv_bfloat16* __restrict__ dgu, int64_t lddg, int F) {
-  const int64_t row = blockIdx.y;
+                                       __nv_bfloat16* __restrict__ dgu, int64_t lddg, int F, int64_t rows) {
   const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (c >= F) return;
-  float g[8], u[8], d[8], dg[8], du[8];
-  ld8(gu + row * ldg + c, g);
-  ld8(gu + row * ldg + F + c, u);
-  ld8(dout + row * ldd + c, d);
+  for (int64_t row = blockIdx.y; row < rows; row += gridDim.y) {
+    float g[8], u[8], d[8], dg[8], du[8];
+    ld8(gu + row * ldg + c, g);
+    ld8(gu + row * ldg + F + c, u);
+    ld8(dout + row * ldd + c, d);
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float val, grad;
-    gelu_tanh_and_grad(g[j], &val, &grad);
-    dg[j] = d[j] * u[j] * grad;
-    du[j] = d[j] * val;
+    for (int j = 0; j < 8; ++j) {
+      float val, grad;
+      gelu_tanh_and_grad(g[j], &val, &grad);
+      dg[j] = d[j] * u[j] * grad;
+      du[j] = d[j] * val;
+    }
+    st8(dgu + row * lddg + c, dg);
+    st8(dgu + row * lddg + F + c, du);
   }
-  st8(dgu + row * lddg + c, dg);
-  st8(dgu + row * lddg + F + c, du);
 }
 
 // ----------------------------------------------------------------------------- per-head norm + rotation of a fused q | k | v row
@@ -556,9 +559,9 @@ MARY_API int mary_rmsnorm_train_bwd(const void* dy, int64_t ldy, const void* x, 
 
 MARY_API int mary_geglu_train_fwd(const void* gu, int64_t ldg, void* out, int64_t ldo, int64_t rows, int F, cudaStream_t s) {
   if (rows <= 0) return MARY_OK;
-  if ((F & 7) || (ldg & 7) || (ldo & 7) || rows > 65535) return MARY_ERR_BAD_ARG;
-  const dim3 grid((F / 8 + 255) / 256, (unsigned)rows);
-  geglu_train_fwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)out, ldo, F);
+  if ((F & 7) || (ldg & 7) || (ldo & 7)) return MARY_ERR_BAD_ARG;
+  const dim3 grid((F / 8 + 255) / 256, (unsigned)(rows < 65535 ? rows : 65535));
+  geglu_train_fwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)out, ldo, F, rows);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }
@@ -566,9 +569,9 @@ MARY_API int mary_geglu_train_fwd(const void* gu, int64_t ldg, void* out, int64_
 MARY_API int mary_geglu_train_bwd(const void* dout, int64_t ldd, const void* gu, int64_t ldg, void* dgu, int64_t lddg, int64_t rows, int F,
                                   cudaStream_t s) {
   if (rows <= 0) return MARY_OK;
-  if ((F & 7) || (ldg & 7) || (ldd & 7) || (lddg & 7) || rows > 65535) return MARY_ERR_BAD_ARG;
-  const dim3 grid((F / 8 + 255) / 256, (unsigned)rows);
-  geglu_train_bwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dout, ldd, (const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)dgu, lddg, F);
+  if ((F & 7) || (ldg & 7) || (ldd & 7) || (lddg & 7)) return MARY_ERR_BAD_ARG;
+  const dim3 grid((F / 8 + 255) / 256, (unsigned)(rows < 65535 ? rows : 65535));
+  geglu_train_bwd_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)dout, ldd, (const __nv_bfloat16*)gu, ldg, (__nv_bfloat16*)dgu, lddg, F, rows);
   MARY_CHECK_LAUNCH();
   return MARY_OK;
 }

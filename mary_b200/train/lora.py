@@ -198,7 +198,7 @@ class Gemma4LoraForward(nn.Module):
         tokens) can only see keys of chunks ``c - 1`` and ``c``, so the scores are ``[W, 2W]`` blocks instead of ``[S, S]``."""
         B, Sq, Hq, D = q.shape
         g = Hq // k.shape[2]
-        if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and self._flash is not False:
+        if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and D <= 256 and self._flash is not False:
             # the flash-attention library where the machine has it: grouped heads and the sliding window natively, forward and
             # backward on tensor cores (PyTorch's fused attention refuses masks together with grouped heads and falls back to
             # f32 matrix products for the sliding layers)
