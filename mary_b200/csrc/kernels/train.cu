@@ -58,19 +58,6 @@ __device__ __forceinline__ void stn(__nv_bfloat16* p, const float* f) {
   *(__nv_bfloat162*)p = __floats2bfloat162_rn(f[0], f[1]);
 }
 
-// sum over the CTA (blockDim.x <= 1024, a multiple of 32); every thread gets the result
-__device__ __forceinline__ float block_sum(float v, float* red) {
-  v = warp_sum(v);
-  const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  __syncthreads();
-  if ((threadIdx.x & 31) == 0) red[w] = v;
-  __syncthreads();
-  float t = (int)threadIdx.x < nw ? red[threadIdx.x] : 0.f;
-  if (w == 0) { t = warp_sum(t); if (threadIdx.x == 0) red[0] = t; }
-  __syncthreads();
-  return red[0];
-}
-
 // two sums over the CTA at once (one round of barriers instead of two)
 __device__ __forceinline__ float2 block_sum2(float a, float b, float2* red) {
   a = warp_sum(a);

@@ -14,8 +14,6 @@ The collectives are ``torch.distributed`` (NCCL over NVLink on GPUs, gloo on CPU
 memory and read there by local kernels — no kernel touches a peer's memory."""
 from __future__ import annotations
 
-import math
-
 import torch
 import torch.distributed as dist
 

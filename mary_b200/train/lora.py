@@ -18,9 +18,8 @@ from torch import nn
 
 from ..format import schema as S
 from ..format.leaf import put_array, resolve
-from ..ops import reference as ref
-from ..ops.autograd import copy_to_tp, linear_frozen, reduce_from_tp
-from ..pile.trible import TribleBuilder, r_f64, r_genid, r_shortstring, r_u256, v_f64, v_genid, v_shortstring, v_u256
+from ..ops.autograd import copy_to_tp, reduce_from_tp
+from ..pile.trible import TribleBuilder, r_genid, r_shortstring, r_u256, v_f64, v_genid, v_shortstring, v_u256
 
 PROJECTIONS = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
 
@@ -184,13 +183,6 @@ class Gemma4LoraForward(nn.Module):
         for f in self.fused:
             for m in f.values():
                 m.refresh()
-
-    def _lin(self, x, w):
-        wt = self._wt.get(w.data_ptr())
-        if wt is None:
-            wt = w.detach().t().contiguous()
-            self._wt[w.data_ptr()] = wt
-        return linear_frozen(x, w.detach(), wt)
 
     def _attn(self, q, k, v, window):
         """q [B,S,Hq,D], k/v [B,S,Hkv,D]; scale 1.0; causal, optional sliding window.  Global layers take the fused causal path
