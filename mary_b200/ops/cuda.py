@@ -222,12 +222,18 @@ def linear(x, w, bias=None):
         return _linear(x, w, bias)
 
 
+MATVEC_MAX_BYTES = 8 << 20       # one-token products up to this weight size take the SIMT matrix-vector stage (4 us against 6 us per launch)
+
+
 def _linear(x, w, bias=None):
     shp = x.shape
     x2 = x.reshape(-1, shp[-1])
     if x2.stride(-1) != 1:
         x2 = x2.contiguous()
     M, K = x2.shape
+    if (M == 1 and bias is None and K % 8 == 0 and K <= 8192 and w.shape[0] * K * 2 <= MATVEC_MAX_BYTES and w.stride(1) == 1
+            and w.stride(0) % 8 == 0 and x2.dtype == torch.bfloat16 and w.dtype == torch.bfloat16):
+        return step_matvec(x2, w).reshape(*shp[:-1], w.shape[0])
     sk = _auto_split_k(M, w.shape[0], K)
     out = gemm_splitk(x2, w, 0, bias=bias) if sk > 1 else gemm(x2, w, bias=bias)
     return out.reshape(*shp[:-1], w.shape[0])
