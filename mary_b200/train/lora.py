@@ -61,6 +61,10 @@ class LoraWeights(nn.Module):
                 lw.adapters[f"{i}_{p}"] = LoraAdapter(fin, fout, rank, alpha, dev, g)
         return lw
 
+    def num_params(self) -> int:
+        """Trainable scalars over all adapters (src/models/gemma/lora.rs:166-178)."""
+        return sum(ad.A.numel() + ad.B.numel() for ad in self.adapters.values())
+
     def get(self, layer: int, proj: str):
         k = f"{layer}_{proj}"
         return self.adapters[k] if k in self.adapters else None

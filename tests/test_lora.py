@@ -23,6 +23,7 @@ def test_adapter_init_rules_and_zero_delta():
     ad = lw.get(0, "q_proj")
     assert ad.A.abs().max() <= (3.0 / 64) ** 0.5 + 1e-6 and ad.B.abs().max() == 0 and ad.scale == 2.0
     assert len(lw.adapters) == 2 * 7
+    assert lw.num_params() == sum(p.numel() for p in lw.parameters()) > 0
     ids = torch.randint(0, 97, (2, 12))
     fwd = Gemma4LoraForward(m, lw)
     base = fwd.forward(ids)
