@@ -296,7 +296,7 @@ def bench_matvec(N: int = 7168, K: int = 8192, iters: int = 10):
     hbm, tf, tag = peaks()
     a = torch.randn(1, K, device="cuda").bfloat16()
     w = (torch.randn(N, K, device="cuda") * 0.02).bfloat16()
-    for name, fn in (("step_matvec", lambda: K_.step_matvec(a, w)), ("gemm (linear)", lambda: K_.linear(a, w))):
+    for name, fn in (("step_matvec", lambda: K_.step_matvec(a, w)), ("gemm", lambda: K_.gemm_splitk(a, w, 0) if K_._auto_split_k(1, N, K) > 1 else K_.gemm(a, w))):
         ms = time_op(fn, iters=iters)
         print(f"{name} 1 x {N} x {K}: {ms * 1e3:.1f} us, {N * K * 2 / ms / 1e6:.0f} GB/s ({N * K * 2 / ms / 1e6 / hbm:.2f} {tag})")
     assert K_.last_status() == 0
@@ -333,6 +333,54 @@ def bench_ttsframe(iters: int = 30):
           f"five-launch fused layer step: {out['graph9'] * 1e3:.0f} us; {w / 1e6:.0f} MB of weights read per frame; "
           f"a 12.5 Hz frame budget is 80000 us")
     mistral.set_layer_step(True)
+
+
+def bench_talker(steps: int = 32):
+    """One-token decode steps of the Qwen3-TTS talker stack (28 layers x 2048, FFN 6144, 16 / 8 heads of 128) in a CUDA graph: the
+    nine-launch layers against the five-launch fused layer step (whose matrix-vector stages lose to a GEMM launch on matrices of
+    this size; the launch count decides)."""
+    import numpy as np
+    from ..models.mistral import model as M
+    from ..models.qwen3tts.model import Qwen3TTSConfig
+    from ..runtime.batch import BatchMeta
+    from ..runtime.kv_cache import PagedKVCache
+    cfg = Qwen3TTSConfig().talker_cfg()
+    model = M.MistralModel(cfg, dtype=torch.bfloat16, device="cuda")
+    M.init_random_(model, 0)
+    spec = model.kv_spec()
+    ctx = 512
+    out = {}
+    saved = M._STEP_MAX_BYTES
+    for name, fused in (("nine-launch layers", False), ("five-launch layer step", True)):
+        M.set_layer_step(fused)
+        M._STEP_MAX_BYTES = 1 << 40
+        cache = PagedKVCache(spec["num_layers"], (ctx + steps) // 16 + 2, 16, spec["kv_heads"], spec["head_dim"], dtype=torch.bfloat16, device="cuda")
+        cache.alloc.extend(0, ctx + steps)
+        table, _ = cache.alloc.page_table([0])
+        h = (torch.randn(1, cfg.hidden_size, device="cuda") * 0.5).bfloat16()
+        metas = [BatchMeta.build([1], [ctx + i + 1], table, 16, "cuda") for i in range(steps)]
+        with torch.no_grad():
+            for m in metas:                                   # every step once eagerly: per-step descriptors are built on the host
+                model.hidden_from_embeds(h, m, cache)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for m in metas:
+                    model.hidden_from_embeds(h, m, cache)
+            g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(3):
+                g.replay()
+            b.record()
+            torch.cuda.synchronize()
+        out[name] = a.elapsed_time(b) / (3 * steps)
+    M._STEP_MAX_BYTES = saved
+    M.set_layer_step(True)
+    w = sum(p.numel() * p.element_size() for n, p in model.named_parameters() if "layers" in n)
+    print(f"talker one-token step ({cfg.num_hidden_layers} layers, {w / 1e6:.0f} MB of layer weights, context {ctx}): " +
+          ", ".join(f"{k} {v * 1e3:.0f} us" for k, v in out.items()))
 
 
 def bench_depformer(iters: int = 30):
@@ -547,6 +595,8 @@ if __name__ == "__main__":
         bench_floor(*nums)
     if what == "ttsframe":
         bench_ttsframe(*nums)
+    if what == "talker":
+        bench_talker(*nums)
     if what == "depformer":
         bench_depformer(*nums)
     if what == "speechlm":
