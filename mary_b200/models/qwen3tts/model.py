@@ -135,6 +135,9 @@ class CodePredictor(nn.Module):
     def project(self, x):
         if not self.has_proj:
             return x
+        if x.is_cuda and x.shape[0] == 1 and x.dtype == torch.bfloat16 and self.proj_w.shape[1] <= 8192:
+            from ...ops import cuda as K                # one token: product and bias in one matrix-vector launch
+            return K.step_matvec(x, self.proj_w, res=self.proj_b, mode="residual")
         return (ops.linear(x, self.proj_w).float() + self.proj_b.float()).to(x.dtype)
 
     def _meta(self, q, kv):
@@ -170,16 +173,16 @@ class CodePredictor(nn.Module):
     def _frame(self, x2, metas, temperature, seed, frame):
         n = self.cfg.num_code_groups - 1
         x = self.project(x2)
-        codes, embed_sum = [], torch.zeros(x2.shape[1], dtype=torch.float32, device=x2.device)
+        codes, rows = [], []
         for i in range(n):
             hid = self.stack.hidden_from_embeds(x, metas[i], self.cache)[-1:]
             lg = ops.linear(hid, self.heads[i]).float()
             tok = sampling.sample(lg, temperature, seed=seed, step=frame * 64 + i)
             codes.append(tok.reshape(1))
             e = ops.embed(tok.reshape(1).to(torch.int32), self.embeddings[i])
-            embed_sum += e[0].float()
+            rows.append(e[0])
             x = self.project(e)
-        return torch.cat(codes), embed_sum
+        return torch.cat(codes), torch.stack(rows).float().sum(0)          # one sum over the frame's rows instead of a cast and an add per step
 
     def _capture(self, dtype):
         metas = self._metas()
