@@ -179,15 +179,28 @@ class Depformer(nn.Module):
         if cache is None:                                                              # one [B, steps, heads, dim] pair per layer, filled step by step
             cache = [(x.new_empty(B, c.dep_q, nh, hd), x.new_empty(B, c.dep_q, nh, hd)) for _ in range(c.dep_layers)]
         new_cache = cache
+        # one frame on the GPU: every product is one token times a small matrix, so the norms and the residual adds ride in the
+        # matrix-vector launches (rms folded into the product that follows it, the residual into the one before it)
+        fused = B == 1 and x.is_cuda and x.dtype == torch.bfloat16 and max(c.dep_dim, c.dep_ffn) <= 8192
+        if fused:
+            from ...ops import cuda as K
         for li in range(c.dep_layers):
-            h = ops.rmsnorm(x, self.norm1[li], c.eps)
-            q, k, v = ops.linear(h, self.w_qkv[li, t]).view(B, 3, nh, hd).unbind(1)
+            if fused:
+                qkv = K.step_matvec(x, self.w_qkv[li, t], self.norm1[li], c.eps)
+            else:
+                qkv = ops.linear(ops.rmsnorm(x, self.norm1[li], c.eps), self.w_qkv[li, t])
+            q, k, v = qkv.view(B, 3, nh, hd).unbind(1)
             kc, vc = cache[li]
             kc[:, t], vc[:, t] = k, v
             a = torch.nn.functional.scaled_dot_product_attention(q[:, :, None], kc[:, :t + 1].transpose(1, 2), vc[:, :t + 1].transpose(1, 2))
-            x = x + ops.linear(a.reshape(B, c.dep_dim), self.w_o[li, t])
-            h = ops.rmsnorm(x, self.norm2[li], c.eps)
-            x = x + ops.linear(ops.linear_glu(h, self.w_gu[li, t], "swiglu"), self.w_down[li, t])
+            if fused:
+                x = K.step_matvec(a.reshape(B, c.dep_dim), self.w_o[li, t], res=x, mode="residual")
+                m = K.step_matvec(x, self.w_gu[li, t], self.norm2[li], c.eps, mode="swiglu")
+                x = K.step_matvec(m, self.w_down[li, t], res=x, mode="residual")
+            else:
+                x = x + ops.linear(a.reshape(B, c.dep_dim), self.w_o[li, t])
+                h = ops.rmsnorm(x, self.norm2[li], c.eps)
+                x = x + ops.linear(ops.linear_glu(h, self.w_gu[li, t], "swiglu"), self.w_down[li, t])
         return ops.linear(x, self.heads[t]).float(), new_cache
 
     def generate(self, h_temporal, text_token, forced=None, sample=None):
