@@ -175,7 +175,11 @@ class Depformer(nn.Module):
         B = h_temporal.shape[0]
         nh, hd = c.dep_heads, c.dep_dim // c.dep_heads
         emb = ops.embed(prev_token.to(torch.int32), self.text_emb if t == 0 else self.audio_emb[t - 1])
-        x = ops.linear(h_temporal, self.w_in[t]) + emb
+        if B == 1 and emb.is_cuda and emb.dtype == torch.bfloat16 and c.dim <= 8192:
+            from ...ops import cuda as K
+            x = K.step_matvec(h_temporal, self.w_in[t], res=emb, mode="residual")        # input projection + embedding in one launch
+        else:
+            x = ops.linear(h_temporal, self.w_in[t]) + emb
         if cache is None:                                                              # one [B, steps, heads, dim] pair per layer, filled step by step
             cache = [(x.new_empty(B, c.dep_q, nh, hd), x.new_empty(B, c.dep_q, nh, hd)) for _ in range(c.dep_layers)]
         new_cache = cache
