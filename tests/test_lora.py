@@ -141,3 +141,22 @@ def test_activation_checkpointing_gives_the_same_gradients():
         f.loss(ids).backward()
         grads.append(torch.cat([p.grad.flatten() for p in lw.parameters()]))
     assert torch.allclose(grads[0], grads[1], atol=1e-6)
+
+
+def test_activation_checkpointing_gives_the_same_loss_and_gradients():
+    """Recomputing every layer in the backward pass (the widened GEMM operands are rebuilt by the recomputation) changes nothing."""
+    def run(ckpt):
+        m = _model()
+        lw = LoraWeights.init_gemma4(m, rank=4, seed=1)
+        g = torch.Generator().manual_seed(2)
+        for ad in lw.adapters.values():
+            ad.B.data.normal_(0, 0.05, generator=g)
+        tr = LoraTrainer(m, rank=4, lr=1e-2, lora=lw, checkpoint=ckpt)
+        ids = torch.randint(0, 97, (2, 12), generator=torch.Generator().manual_seed(3))
+        tr.opt.zero_grad()
+        loss = tr.fwd.loss(ids)
+        loss.backward()
+        return float(loss.detach()), tr.opt.grad.clone()
+    a, ga = run(False)
+    b, gb = run(True)
+    assert a == b and torch.equal(ga, gb) and ga.abs().max() > 0
