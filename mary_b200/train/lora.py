@@ -167,6 +167,10 @@ class Gemma4LoraForward(nn.Module):
         self.model, self.lora = model, lora
         self._wt: dict[int, torch.Tensor] = {}
         self._flash = None                     # None: not tried yet; True / False: the flash-attention library works / does not
+        # (rank, world, group) of a sequence-parallel group, or None: every rank then runs the layers on its contiguous chunk of
+        # the sequence's rows, attention goes through two all-to-alls (rows <-> heads, ``parallel.seq_attention``), the loss is
+        # normalised by the tokens of the whole sequence, and the caller sums the adapter gradients over the group
+        self.sp = None
         self.fused: list[dict] = []
         s = lora.alpha / lora.rank
         for i, L in enumerate(model.layers):
@@ -194,6 +198,19 @@ class Gemma4LoraForward(nn.Module):
         tokens) can only see keys of chunks ``c - 1`` and ``c``, so the scores are ``[W, 2W]`` blocks instead of ``[S, S]``."""
         B, Sq, Hq, D = q.shape
         g = Hq // k.shape[2]
+        if self.sp is not None and not getattr(self, "_inside_sp", False):
+            # rows -> heads: this rank attends the WHOLE sequence for its share of the heads with the local attention below
+            from ..parallel.seq_attention import ulysses_attention
+            rank, world, group = self.sp
+
+            def local(qh, kh, vh, scale, causal, w):
+                self._inside_sp = True
+                try:
+                    return self._attn(qh[None], kh[None], vh[None], w)[0]
+                finally:
+                    self._inside_sp = False
+            return torch.stack([ulysses_attention(q[b], k[b], v[b], rank, world, group, scale=1.0, causal=True, window=window, attn_fn=local)
+                                for b in range(B)])
         if q.is_cuda and q.dtype in (torch.bfloat16, torch.float16) and D <= 256 and self._flash is not False:
             # the flash-attention library where the machine has it: grouped heads and the sliding window natively, forward and
             # backward on tensor cores (PyTorch's fused attention refuses masks together with grouped heads and falls back to
@@ -250,10 +267,18 @@ class Gemma4LoraForward(nn.Module):
         """``checkpoint = True`` keeps only every layer's input for the backward pass and recomputes the layer there: the
         activations of a 4096-token sequence through 48 layers otherwise take on the order of 100 GB."""
         m, c = self.model, self.model.cfg
+        p0 = 0
+        if self.sp is not None:
+            rank, world, _ = self.sp
+            if ids.shape[1] % world:
+                raise ValueError(f"a sequence of {ids.shape[1]} tokens cannot be cut into {world} equal chunks")
+            n = ids.shape[1] // world
+            p0 = rank * n
+            ids = ids[:, p0:p0 + n]
         B, Sq = ids.shape
         self.refresh()
         h = (m.embed.detach()[ids.long()].float() * m.embed_scale).to(m.dtype).view(B * Sq, -1)
-        pos = torch.arange(Sq, device=ids.device, dtype=torch.int32).repeat(B)
+        pos = torch.arange(p0, p0 + Sq, device=ids.device, dtype=torch.int32).repeat(B)
         for i in range(len(m.layers)):
             if getattr(self, "checkpoint", False) and torch.is_grad_enabled():
                 from torch.utils.checkpoint import checkpoint
@@ -266,6 +291,8 @@ class Gemma4LoraForward(nn.Module):
     def loss(self, ids, chunk: int = 1024):
         """Mean next-token cross-entropy (labels = ids shifted by one); the vocabulary projection is chunked over tokens so
         the [tokens, vocab] logits never exist at once."""
+        if self.sp is not None:
+            return self._loss_sp(ids, chunk)
         x = self.forward(ids)[:, :-1].reshape(-1, self.model.cfg.hidden_size)
         y = ids[:, 1:].reshape(-1).long()
         W = self.model.head_weight().detach()
@@ -275,3 +302,23 @@ class Gemma4LoraForward(nn.Module):
             self._wt[W.data_ptr()] = wt
         from ..ops import train_ops as T
         return T.head_loss(x.contiguous(), W, wt, y, self.model.cfg.final_logit_softcapping, chunk)
+
+    def _loss_sp(self, ids, chunk: int):
+        """This rank's share of the mean next-token cross-entropy: the sum over its rows' tokens divided by the token count of the
+        WHOLE sequence, so that the ranks' losses (and adapter gradients) add up to the single-rank values."""
+        from ..ops import train_ops as T
+        rank, world, _ = self.sp
+        B, S = ids.shape
+        n = S // world
+        p0 = rank * n
+        x = self.forward(ids)                                            # [B, n, H]: rows p0 .. p0 + n - 1
+        keep = n if p0 + n < S else n - 1                                # the sequence's last row has no label
+        x = x[:, :keep].reshape(-1, self.model.cfg.hidden_size)
+        y = ids[:, p0 + 1:p0 + 1 + keep].reshape(-1).long()
+        W = self.model.head_weight().detach()
+        wt = self._wt.get(W.data_ptr())
+        if wt is None:
+            wt = W.t().contiguous()
+            self._wt[W.data_ptr()] = wt
+        total = B * (S - 1)
+        return T.head_loss(x.contiguous(), W, wt, y, self.model.cfg.final_logit_softcapping, chunk) * (x.shape[0] / total)

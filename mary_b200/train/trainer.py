@@ -75,15 +75,21 @@ class FlatAdamW:
 
 class LoraTrainer:
     def __init__(self, model, rank: int = 16, alpha: float = 32.0, lr: float = 1e-4, seed: int = 0, dp_group=None, dp_size: int = 1,
-                 reduce_fn=None, overlap: bool = True, checkpoint: bool = False, tp_reduce_fn=None, lora=None):
+                 reduce_fn=None, overlap: bool = True, checkpoint: bool = False, tp_reduce_fn=None, lora=None, seq_parallel=None):
         """``reduce_fn(g)``: in-place sum of a gradient slice over the DATA-parallel group (all replicas of this rank's shard).
         ``tp_reduce_fn(g)``: in-place sum over the TENSOR-parallel group, applied to the factors every rank of the group holds
         identically (their gradients are partial sums, see ``LoraWeights.tp_replicated``).  ``lora``: adapters to train instead of
-        freshly initialised ones (already cut for this rank)."""
+        freshly initialised ones (already cut for this rank).  ``seq_parallel = (rank, world, group)``: the ranks of the group
+        share ONE sequence, each running the layers on its chunk of the rows (attention through all-to-alls); every rank's loss
+        and adapter gradients are its share of the whole sequence's, so ``reduce_fn`` must SUM over that group and ``dp_size``
+        stays the number of data-parallel replicas (1 when the group is the world)."""
         self.model = model
         self.lora = lora if lora is not None else LoraWeights.init_gemma4(model, rank, alpha, seed)
         self.fwd = Gemma4LoraForward(model, self.lora)
         self.fwd.checkpoint = checkpoint          # recompute every layer in the backward pass instead of keeping its activations
+        self.fwd.sp = seq_parallel
+        if seq_parallel is not None and reduce_fn is None:
+            raise ValueError("sequence-parallel training needs reduce_fn: every rank holds a share of the adapter gradients")
         # parameters ordered by layer so that a layer's gradients are one contiguous bucket; inside a layer the factors that are
         # replicated over the tensor-parallel group come first, so that their partial gradients are one contiguous slice too
         tp = getattr(model, "tp", None)
@@ -156,7 +162,12 @@ class LoraTrainer:
         if self.side is not None:
             torch.cuda.current_stream().wait_stream(self.side)
         self.opt.step(grad_scale=1.0 / self.dp_size)
-        return float(loss.detach())
+        loss = loss.detach()
+        if self.fwd.sp is not None:
+            import torch.distributed as dist
+            loss = loss.clone()
+            dist.all_reduce(loss, group=self.fwd.sp[2])           # the shares add up to the sequence's mean loss
+        return float(loss)
 
     # ------------------------------------------------------------------ checkpoint / resume through the pile
     def save_checkpoint(self, store, tb: TribleBuilder, model_root: bytes | None = None) -> bytes:

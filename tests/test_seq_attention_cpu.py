@@ -72,3 +72,59 @@ def test_sequence_parallel_attention_equals_the_whole_sequence(world, Hq, Hkv, w
     [p.join(60) for p in ps]
     for rank, err in res:
         assert max(err[:4]) < 1e-9 and max(err) < 1e-5, (rank, err)      # the ring form accumulates in f32
+
+
+def _lora_sp_worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from mary_b200.models.gemma4 import Gemma4Model, Gemma4TextConfig
+    from mary_b200.models.gemma4.weights import init_random_
+    from mary_b200.train.lora import LoraWeights
+    from mary_b200.train.trainer import LoraTrainer
+
+    def build():
+        cfg = Gemma4TextConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+                               intermediate_size=128, vocab_size=97, sliding_window=8)
+        m = Gemma4Model(cfg, dtype=torch.float32)
+        init_random_(m, 0, std=0.08)
+        lw = LoraWeights.init_gemma4(m, rank=4, seed=1)
+        g = torch.Generator().manual_seed(2)
+        for ad in lw.adapters.values():
+            ad.B.data.normal_(0, 0.05, generator=g)
+        return m, lw
+    ids = torch.randint(0, 97, (2, 16), generator=torch.Generator().manual_seed(3))
+    m, lw = build()
+    ref_tr = LoraTrainer(m, rank=4, lr=1e-2, lora=lw, overlap=False)
+    ref_tr.opt.zero_grad()
+    want = ref_tr.fwd.loss(ids)
+    want.backward()
+    m2, lw2 = build()
+    tr = LoraTrainer(m2, rank=4, lr=1e-2, lora=lw2, overlap=False, reduce_fn=lambda g_: dist.all_reduce(g_), seq_parallel=(rank, world, None))
+    tr.opt.zero_grad()
+    loss = tr.fwd.loss(ids)
+    loss.backward()
+    share = loss.detach().clone()
+    dist.all_reduce(share)
+    grad = tr.opt.grad.clone()
+    if not tr.reduce_fn or tr.reduced_bytes == 0:              # hooks reduce per layer bucket; be explicit if they did not run
+        dist.all_reduce(grad)
+    out.put((rank, abs(float(share) - float(want.detach())), (grad - ref_tr.opt.grad).abs().max().item(), float(ref_tr.opt.grad.abs().max())))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@_once_more
+def test_sequence_parallel_lora_training_has_the_single_rank_loss_and_gradients(world):
+    """The ranks of a sequence-parallel group share one sequence: their loss shares and adapter gradients add up to the single-rank
+    values (attention through the all-to-all form, sliding and global layers)."""
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _port()
+    ps = [ctx.Process(target=_lora_sp_worker, args=(r, world, port, out)) for r in range(world)]
+    [p.start() for p in ps]
+    res = [out.get(timeout=180) for _ in range(world)]
+    [p.join(60) for p in ps]
+    for rank, dl, dg, gmax in res:
+        assert dl < 1e-5 and dg < 1e-5 * max(1.0, gmax) and gmax > 0, res
