@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--no-overlap", action="store_true")
     ap.add_argument("--checkpoint", action="store_true", help="recompute each layer in the backward pass (activation checkpointing)")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel group size; the world is (world / tp) data-parallel replicas of tp ranks each")
+    ap.add_argument("--sp", action="store_true", help="sequence parallelism over all ranks: ONE sequence per step, every rank runs the layers "
+                    "on its chunk of the rows, attention through all-to-alls (excludes --tp)")
     ap.add_argument("--kernel-table", action="store_true", help="after the timed steps run one more step under torch.profiler and print "
                     "the 30 kernels with the largest device time (shares only: times under a profiler are not benchmark values)")
     a = ap.parse_args()
@@ -44,7 +46,8 @@ def main():
     cfg.layer_types = cfg.layer_types[:a.layers]
     tp = a.tp
     assert world % tp == 0, "--tp must divide the number of ranks"
-    dp = world // tp
+    assert not (a.sp and tp > 1), "--sp and --tp are separate layouts"
+    dp = 1 if a.sp else world // tp
     tp_rank, dp_rank = rank % tp, rank // tp
     reduce_fn = tp_reduce_fn = par = None
     if world > 1:
@@ -67,7 +70,9 @@ def main():
                 grp = tp_groups[dp_rank] if tp_groups else None
                 par = ParallelGroup(tp_rank, tp, "nccl", group=grp)
                 tp_reduce_fn = lambda g_, grp=grp: dist.all_reduce(g_, group=grp)  # noqa: E731
-        if dp > 1:
+        if a.sp:
+            reduce_fn = heap.all_reduce_f32_ if heap is not None else (lambda g_: dist.all_reduce(g_))
+        elif dp > 1:
             if heap is not None and tp == 1:
                 reduce_fn = heap.all_reduce_f32_
             else:
@@ -76,7 +81,9 @@ def main():
     model = Gemma4Model(cfg, tp=par, dtype=torch.bfloat16, device=dev)
     init_random_(model, 0)
     tr = LoraTrainer(model, rank=16, alpha=32.0, lr=1e-4, dp_size=dp, reduce_fn=reduce_fn, tp_reduce_fn=tp_reduce_fn, overlap=not a.no_overlap,
-                     checkpoint=a.checkpoint)
+                     checkpoint=a.checkpoint, seq_parallel=(rank, world, None) if a.sp and world > 1 else None)
+    if a.sp:
+        dp_rank = 0                                                         # every rank of the group works on the same sequence
     g = torch.Generator(device=dev).manual_seed(dp_rank)                    # the ranks of one tensor-parallel group see the same sequences
     ids = torch.randint(0, cfg.vocab_size, (a.batch, a.seq), device=dev, generator=g)
     for _ in range(a.warmup):
@@ -97,7 +104,7 @@ def main():
     ms = float(ms) / a.steps
     if rank == 0:
         print(json.dumps({"metric": "LoRA finetune tokens/s (Gemma-4-12B-style, rank 16, seq %d)" % a.seq,
-                          "value": round(dp * a.batch * a.seq / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "parallelism": f"dp{dp} x tp{tp}",
+                          "value": round(dp * a.batch * a.seq / (ms / 1e3), 1), "unit": "tokens/s", "n_gpus": world, "parallelism": f"sp{world}" if a.sp else f"dp{dp} x tp{tp}",
                           "ms_per_step": round(ms, 2), "loss": round(loss, 4), "layers": a.layers, "comm": a.comm if world > 1 else "none",
                           "overlap": not a.no_overlap, "checkpointing": a.checkpoint, "gpu_launches_per_step": K.LAUNCHES // a.steps,
                           "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 1), "kernel_status": K.last_status()}))
