@@ -8,7 +8,8 @@ query blocking); these are the multi-GPU counterparts for the long training and 
   heads that do not divide are gathered whole (they are few) and the rank picks the heads its query heads use.
 * ``ring_attention``: K / V chunks travel around the ring while every rank keeps its query chunk; each step attends one chunk
   (earlier chunks fully visible, the own chunk causally, later chunks skipped) and the partial results are merged by their
-  log-sum-exp.  No head-count constraint, peak memory of one remote chunk.  Forward only (prefill).
+  log-sum-exp.  No head-count constraint, peak memory of one remote chunk.  ``ring_attention`` is the forward (prefill);
+  ``ring_attention_autograd`` adds the backward pass, in which the chunks go around once more together with their gradients.
 
 The collectives are ``torch.distributed`` (NCCL over NVLink on GPUs, gloo on CPU ranks): whole chunks are brought into local
 memory and read there by local kernels — no kernel touches a peer's memory."""
@@ -159,6 +160,89 @@ def ring_attention(q, k, v, rank: int, world: int, group=None, scale: float | No
                 w.wait()
             kc, vc = recv[1], recv[2]
     return acc[0].to(q.dtype)
+
+
+def _ring_pass(tensors, rank, world, group):
+    """Send ``tensors`` to the next rank of the ring and receive the previous rank's (blocking)."""
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    recv = [torch.empty_like(t) for t in tensors]
+    ops_ = [dist.P2POp(dist.isend, t.contiguous(), _global(nxt, group), group) for t in tensors]
+    ops_ += [dist.P2POp(dist.irecv, r, _global(prv, group), group) for r in recv]
+    for w in dist.batch_isend_irecv(ops_):
+        w.wait()
+    return recv
+
+
+class _RingAttention(torch.autograd.Function):
+    """The ring form with its backward pass: K / V chunks go around once more, now together with the gradients they have
+    collected so far, so that after ``world`` steps every chunk is home again with its complete dK / dV; dQ stays local.  The
+    per-chunk arithmetic is the f32 formula of the forward (P = exp(S - lse), dS = P (dP - rowsum(dO O)))."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, rank, world, group, scale):
+        out32, lse = _ring_forward(q, k, v, rank, world, group, scale)
+        ctx.save_for_backward(q, k, v, out32, lse)
+        ctx.cfg = (rank, world, group, scale)
+        return out32.to(q.dtype)
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, out32, lse = ctx.saved_tensors
+        rank, world, group, scale = ctx.cfg
+        g = q.shape[1] // k.shape[1]
+        qf, dof = q.float(), do.float()
+        delta = (dof * out32).sum(-1)                                  # [Sq, Hq]
+        dq = torch.zeros_like(qf)
+        kc, vc = k.contiguous(), v.contiguous()
+        dk, dv = torch.zeros_like(kc, dtype=torch.float32), torch.zeros_like(vc, dtype=torch.float32)
+        for step in range(world):
+            src = (rank - step) % world
+            if src <= rank:
+                kf = kc.float().repeat_interleave(g, 1) if g > 1 else kc.float()
+                vf = vc.float().repeat_interleave(g, 1) if g > 1 else vc.float()
+                s = torch.einsum("qhd,khd->hqk", qf, kf) * scale
+                if src == rank:
+                    n = s.shape[-1]
+                    s = s.masked_fill(torch.ones(qf.shape[0], n, dtype=torch.bool, device=q.device).triu(1), float("-inf"))
+                p = torch.exp(s - lse.transpose(0, 1)[..., None])      # [Hq, Sq, Sk]
+                dp = torch.einsum("qhd,khd->hqk", dof, vf)
+                ds = p * (dp - delta.transpose(0, 1)[..., None]) * scale
+                dq += torch.einsum("hqk,khd->qhd", ds, kf)
+                dkh = torch.einsum("hqk,qhd->khd", ds, qf)
+                dvh = torch.einsum("hqk,qhd->khd", p, dof)
+                if g > 1:                                              # the query heads of a group share their key / value head
+                    dkh = dkh.view(dkh.shape[0], -1, g, dkh.shape[-1]).sum(2)
+                    dvh = dvh.view(dvh.shape[0], -1, g, dvh.shape[-1]).sum(2)
+                dk += dkh
+                dv += dvh
+            # after the last step's pass every chunk (and its gradients) is back on its own rank
+            kc, vc, dk, dv = _ring_pass([kc, vc, dk, dv], rank, world, group)
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, None, None
+
+
+def _ring_forward(q, k, v, rank, world, group, scale):
+    acc = None
+    kc, vc = k.contiguous(), v.contiguous()
+    for step in range(world):
+        src = (rank - step) % world
+        if src <= rank:
+            o, lse = _chunk_attention(q, kc, vc, scale, "causal" if src == rank else "full")
+            if acc is None:
+                acc = (o.float(), lse.float())
+            else:
+                o0, l0 = acc
+                l = torch.logaddexp(l0, lse.float())
+                acc = (o0 * torch.exp(l0 - l)[..., None] + o.float() * torch.exp(lse.float() - l)[..., None], l)
+        if step + 1 < world:
+            kc, vc = _ring_pass([kc, vc], rank, world, group)
+    return acc
+
+
+def ring_attention_autograd(q, k, v, rank: int, world: int, group=None, scale: float | None = None):
+    """``ring_attention`` with gradients (f32 PyTorch arithmetic per chunk pair): for sequences that are too long for the
+    all-to-all form's whole-sequence attention on one rank."""
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    return _RingAttention.apply(q, k, v, rank, world, group, scale)
 
 
 def _global(r: int, group) -> int:

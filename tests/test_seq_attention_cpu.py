@@ -39,6 +39,12 @@ def _worker(rank, world, port, Hq, Hkv, window, out):
     if not window:
         ring = ring_attention(ql.detach(), kl.detach(), vl.detach(), rank, world)
         err.append((ring - want[sl].detach()).abs().max().item())
+        from mary_b200.parallel.seq_attention import ring_attention_autograd
+        q2, k2, v2 = (t.detach()[sl].clone().requires_grad_() for t in (q, k, v))
+        r2 = ring_attention_autograd(q2, k2, v2, rank, world)
+        (r2 * w[sl]).sum().backward()
+        err += [(r2 - want[sl]).abs().max().item(), (q2.grad - q.grad[sl]).abs().max().item(), (k2.grad - k.grad[sl]).abs().max().item(),
+                (v2.grad - v.grad[sl]).abs().max().item()]
     out.put((rank, err))
     dist.barrier()
     dist.destroy_process_group()
